@@ -1,0 +1,224 @@
+"""TEST INFRASTRUCTURE: numpy front-ends to the two CPU checkers.
+
+``Restated``  -> oracle/libd8oracle.so, the plain-C restatement (d8_oracle.c).
+``Reference`` -> oracle/_ref/libd8ref.so, the reference's own CPU sources compiled unmodified (ref_wrap.cpp).
+
+Both expose the same methods so a test can run either.  Array conventions:
+  matmul : x [xb, xr, xc], y [yb, xc, yc], z [max(xb, yb), xr, yc]   (a batch of 1 is broadcast)
+  conv   : x [b, ih, iw, ic], w [oc, fh, fw, ic], z [b, oh, ow, oc]  (the reference's NHWC / OHWI layout)
+Gradient methods return ``d0 + gradient`` (the reference accumulates into the gradient tensor); ``d0`` defaults to zeros.
+
+Only tests, the smoke check and the benchmark's CPU-baseline leg may import this module.
+"""
+import ctypes
+import os
+import subprocess
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+RESTATED_LIB = os.path.join(_HERE, "libd8oracle.so")
+REFERENCE_LIB = os.path.join(_HERE, "_ref", "libd8ref.so")
+
+
+def build(ref=True):
+    """Run oracle/Makefile (the restatement always; the reference library when its source tree is present)."""
+    targets = ["oracle"] + (["ref"] if ref else [])
+    subprocess.run(["make", "-s", "-C", _HERE] + targets, check=True)
+
+
+def _ptr(a):
+    return a.ctypes.data_as(ctypes.c_void_p) if a is not None else None
+
+
+def _suffix(dtype):
+    if dtype == np.float32:
+        return "f32"
+    if dtype == np.float64:
+        return "f64"
+    raise TypeError("the CPU path of the reference supports float32 and float64 only, got %s" % dtype)
+
+
+def conv2d_out_dim(size, f, stride, dilation, covered):
+    """deep8/src/nodes/Conv2d.cpp:47-63."""
+    real = f + (f - 1) * (dilation - 1)
+    return (size - 1) // stride + 1 if covered else (size - real) // stride + 1
+
+
+def deconv2d_out_dim(size, f, stride, covered):
+    """deep8/src/nodes/DeConv2d.cpp:36-52."""
+    return (size - 1) * stride + 1 if covered else (size - 1) * stride + f
+
+
+class _Base:
+    def _check(self, *arrays):
+        dt = arrays[0].dtype
+        for a in arrays:
+            assert a.dtype == dt and a.flags.c_contiguous, "arrays must share a dtype and be C-contiguous"
+        return dt
+
+    @staticmethod
+    def _grad0(d0, shape, dtype):
+        return np.zeros(shape, dtype) if d0 is None else np.array(d0, dtype=dtype, order="C", copy=True)
+
+    # shared shape logic ------------------------------------------------------------------------------------------
+    def conv2d_forward(self, x, w, covered, stride, dilation):
+        b, ih, iw, ic = x.shape
+        oc, fh, fw, _ = w.shape
+        oh = conv2d_out_dim(ih, fh, stride[0], dilation[0], covered)
+        ow = conv2d_out_dim(iw, fw, stride[1], dilation[1], covered)
+        z = np.zeros((b, oh, ow, oc), x.dtype)
+        self._conv(0, x, None, w, None, z, None, covered, stride, dilation)
+        return z
+
+    def conv2d_grad_x(self, x, w, dz, covered, stride, dilation, d0=None):
+        dx = self._grad0(d0, x.shape, x.dtype)
+        self._conv(1, x, dx, w, None, np.zeros_like(dz), dz, covered, stride, dilation)
+        return dx
+
+    def conv2d_grad_y(self, x, w, dz, covered, stride, dilation, d0=None):
+        dw = self._grad0(d0, w.shape, x.dtype)
+        self._conv(2, x, None, w, dw, np.zeros_like(dz), dz, covered, stride, dilation)
+        return dw
+
+    def deconv2d_forward(self, x, w, covered, stride):
+        b, ih, iw, ic = x.shape
+        oc, fh, fw, _ = w.shape
+        oh = deconv2d_out_dim(ih, fh, stride[0], covered)
+        ow = deconv2d_out_dim(iw, fw, stride[1], covered)
+        z = np.zeros((b, oh, ow, oc), x.dtype)
+        self._deconv(0, x, None, w, None, z, None, covered, stride)
+        return z
+
+    def deconv2d_grad_x(self, x, w, dz, covered, stride, d0=None):
+        dx = self._grad0(d0, x.shape, x.dtype)
+        self._deconv(1, x, dx, w, None, np.zeros_like(dz), dz, covered, stride)
+        return dx
+
+    def deconv2d_grad_y(self, x, w, dz, covered, stride, d0=None):
+        dw = self._grad0(d0, w.shape, x.dtype)
+        self._deconv(2, x, None, w, dw, np.zeros_like(dz), dz, covered, stride)
+        return dw
+
+    def matmul_forward(self, x, y):
+        zb = max(x.shape[0], y.shape[0])
+        z = np.zeros((zb, x.shape[1], y.shape[2]), x.dtype)
+        self._matmul(0, x, None, y, None, z, None)
+        return z
+
+    def matmul_grad_x(self, x, y, dz, d0=None):
+        dx = self._grad0(d0, x.shape, x.dtype)
+        self._matmul(1, x, dx, y, None, np.zeros_like(dz), dz)
+        return dx
+
+    def matmul_grad_y(self, x, y, dz, d0=None):
+        dy = self._grad0(d0, y.shape, x.dtype)
+        self._matmul(2, x, None, y, dy, np.zeros_like(dz), dz)
+        return dy
+
+
+class Restated(_Base):
+    kind = "port"
+
+    def __init__(self):
+        if not os.path.exists(RESTATED_LIB):
+            build(ref=False)
+        self.lib = ctypes.CDLL(RESTATED_LIB)
+
+    def threads(self):
+        return os.cpu_count() or 1
+
+    def _matmul(self, which, x, dx, y, dy, z, dz):
+        dt = self._check(x, y)
+        s = _suffix(dt)
+        xb, xr, xc = x.shape
+        yb, yr, yc = y.shape
+        assert yr == xc
+        sz = ctypes.c_size_t
+        if which == 0:
+            getattr(self.lib, "d8o_matmul_forward_" + s)(_ptr(x), sz(xb), sz(xr), sz(xc), _ptr(y), sz(yb), sz(yc), _ptr(z))
+        elif which == 1:
+            getattr(self.lib, "d8o_matmul_grad_x_" + s)(_ptr(dx), sz(xb), sz(xr), sz(xc), _ptr(y), sz(yb), sz(yc), _ptr(dz))
+        else:
+            getattr(self.lib, "d8o_matmul_grad_y_" + s)(_ptr(x), sz(xb), sz(xr), sz(xc), _ptr(dy), sz(yb), sz(yc), _ptr(dz))
+
+    def _conv(self, which, x, dx, w, dw, z, dz, covered, stride, dilation):
+        dt = self._check(x, w)
+        s = _suffix(dt)
+        b, ih, iw, ic = x.shape
+        oc, fh, fw, _ = w.shape
+        _, oh, ow, _ = z.shape
+        tail = (oh, ow, stride[0], stride[1], dilation[0], dilation[1])
+        if which == 0:
+            getattr(self.lib, "d8o_conv2d_forward_" + s)(_ptr(x), b, ih, iw, ic, _ptr(w), oc, fh, fw, _ptr(z), *tail)
+        elif which == 1:
+            getattr(self.lib, "d8o_conv2d_grad_x_" + s)(_ptr(dx), b, ih, iw, ic, _ptr(w), oc, fh, fw, _ptr(dz), *tail)
+        else:
+            getattr(self.lib, "d8o_conv2d_grad_y_" + s)(_ptr(x), b, ih, iw, ic, _ptr(dw), oc, fh, fw, _ptr(dz), *tail)
+
+    def _deconv(self, which, x, dx, w, dw, z, dz, covered, stride):
+        dt = self._check(x, w)
+        s = _suffix(dt)
+        b, ih, iw, ic = x.shape
+        oc, fh, fw, _ = w.shape
+        _, oh, ow, _ = z.shape
+        tail = (oh, ow, stride[0], stride[1])
+        if which == 0:
+            getattr(self.lib, "d8o_deconv2d_forward_" + s)(_ptr(x), b, ih, iw, ic, _ptr(w), oc, fh, fw, _ptr(z), *tail)
+        elif which == 1:
+            getattr(self.lib, "d8o_deconv2d_grad_x_" + s)(_ptr(dx), b, ih, iw, ic, _ptr(w), oc, fh, fw, _ptr(dz), *tail)
+        else:
+            getattr(self.lib, "d8o_deconv2d_grad_y_" + s)(_ptr(x), b, ih, iw, ic, _ptr(dw), oc, fh, fw, _ptr(dz), *tail)
+
+
+class Reference(_Base):
+    kind = "reference"
+
+    @staticmethod
+    def available():
+        return os.path.exists(REFERENCE_LIB)
+
+    def __init__(self, path=REFERENCE_LIB):
+        self.lib = ctypes.CDLL(path)
+        self.lib.d8ref_last_error.restype = ctypes.c_char_p
+
+    def threads(self):
+        return int(self.lib.d8ref_threads())
+
+    def _ok(self, rc):
+        if rc != 0:
+            raise RuntimeError(self.lib.d8ref_last_error().decode())
+
+    def _matmul(self, which, x, dx, y, dy, z, dz):
+        dt = self._check(x, y)
+        code = 0 if dt == np.float32 else 1
+        _suffix(dt)
+        xb, xr, xc = x.shape
+        yb, yr, yc = y.shape
+        sz = ctypes.c_size_t
+        self._ok(self.lib.d8ref_matmul(which, code, _ptr(x), _ptr(dx), sz(xb), 2, sz(xr), sz(xc),
+                                       _ptr(y), _ptr(dy), sz(yb), 1 if yc == 1 else 2, sz(yr), sz(yc), _ptr(z), _ptr(dz)))
+
+    def _conv(self, which, x, dx, w, dw, z, dz, covered, stride, dilation):
+        dt = self._check(x, w)
+        code = 0 if dt == np.float32 else 1
+        _suffix(dt)
+        sz = ctypes.c_size_t
+        b, ih, iw, ic = x.shape
+        oc, fh, fw, _ = w.shape
+        _, oh, ow, _ = z.shape
+        self._ok(self.lib.d8ref_conv2d(which, code, _ptr(x), _ptr(dx), sz(b), sz(ih), sz(iw), sz(ic), _ptr(w), _ptr(dw),
+                                       sz(oc), sz(fh), sz(fw), _ptr(z), _ptr(dz), sz(oh), sz(ow), int(bool(covered)),
+                                       stride[0], stride[1], dilation[0], dilation[1]))
+
+    def _deconv(self, which, x, dx, w, dw, z, dz, covered, stride):
+        dt = self._check(x, w)
+        code = 0 if dt == np.float32 else 1
+        _suffix(dt)
+        sz = ctypes.c_size_t
+        b, ih, iw, ic = x.shape
+        oc, fh, fw, _ = w.shape
+        _, oh, ow, _ = z.shape
+        self._ok(self.lib.d8ref_deconv2d(which, code, _ptr(x), _ptr(dx), sz(b), sz(ih), sz(iw), sz(ic), _ptr(w), _ptr(dw),
+                                         sz(oc), sz(fh), sz(fw), _ptr(z), _ptr(dz), sz(oh), sz(ow), int(bool(covered)),
+                                         stride[0], stride[1]))
