@@ -1,0 +1,361 @@
+"""Benchmark of the dense-contraction path: fp16 two-layer MLP (MatrixMultiply forward + backward), batch-sharded.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload (per GPU, weak scaling): X 8192x4096, W1 4096x16384, ReLU, W2 16384x4096, upstream gradient dY 8192x4096;
+fp16 storage, fp32 accumulation.  One step = zero the gradients, H = X W1, A = relu(H), Y = A W2, then
+dA += dY W2^T, dW2 += A^T dY, dH += relu'(H) dA, dX += dH W1^T, dW1 += X^T dH (six contractions of
+2*8192*4096*16384 FLOP each), and for N > 1 the NCCL all-reduce (sum) of dW1 and dW2.  Inputs are seeded synthetic
+data (X N(0,1), weights N(0,0.02), dY N(0,1)*0.01, seed 10, rank-offset for X and dY).
+
+Prints ONE JSON line.  `value` is the aggregate TFLOP/s over all GPUs with inputs resident in HBM; `e2e` is the same
+metric with X and dY copied from pinned host memory and Y copied back inside every step; `roofline` is for the
+contraction kernel (tensor bound) against the measured cuBLAS bf16 peak of this pool; `cpu_baseline` is the reference's
+own CPU code on a row slice of the same workload.  `--impl reference` times only that CPU code.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+M_PER_GPU, D_IN, D_HID = 8192, 4096, 16384
+FLOP_PER_GEMM = 2.0 * M_PER_GPU * D_IN * D_HID
+FLOP_PER_STEP = 6.0 * FLOP_PER_GEMM
+METRIC = "mlp_fwd_bwd_tflops"
+UNIT = "TFLOP/s"
+# nominal dense fp16 tensor peak of one B200, for the "fraction of nominal peak" the north star quotes
+NOMINAL_FP16_TFLOPS = 2250.0
+CPU_SAMPLE_ROWS = 256
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return float(d["bf16_tflops_sustained"]), "measured (cuBLAS bf16, sustained)"
+    return 1400.0, "fallback (sustained figure of an earlier measurement on this pool)"
+
+
+# ------------------------------------------------------------------------------------------------ clocks
+class ClockSampler:
+    """Samples nvidia-smi while the timed region runs: SM clock, its maximum and the active throttle reasons."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.proc, self.lines = index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.FIELDS,
+                                          "--format=csv,noheader,nounits", "-lms", "100"], stdout=subprocess.PIPE, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, v in zip(names, parts[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# ------------------------------------------------------------------------------------------------ CPU reference arm
+class CpuMlp:
+    """One fwd+bwd step of the MLP on CPU_SAMPLE_ROWS rows through a CPU implementation's MatrixMultiply entry points,
+    buffers allocated once (as the GPU arm does) so that the timed region is the reference's arithmetic."""
+
+    def __init__(self, impl, x, w1, w2, dy):
+        self.impl, self.x, self.w1, self.w2, self.dy = impl, x, w1, w2, dy
+        r = x.shape[1]
+        z = lambda *s: np.zeros(s, np.float32)
+        self.h, self.a, self.y = z(1, r, D_HID), z(1, r, D_HID), z(1, r, D_IN)
+        self.da, self.dh, self.dx = z(1, r, D_HID), z(1, r, D_HID), z(1, r, D_IN)
+        self.dw1, self.dw2 = np.zeros_like(w1), np.zeros_like(w2)
+
+    def step(self):
+        m = self.impl._matmul
+        for g in (self.da, self.dh, self.dx, self.dw1, self.dw2):
+            g.fill(0)
+        m(0, self.x, None, self.w1, None, self.h, None)
+        np.maximum(self.h, 0, out=self.a)
+        m(0, self.a, None, self.w2, None, self.y, None)
+        m(1, self.a, self.da, self.w2, None, self.y, self.dy)
+        m(2, self.a, None, self.w2, self.dw2, self.y, self.dy)
+        np.multiply(self.da, self.h > 0, out=self.dh)
+        m(1, self.x, self.dx, self.w1, None, self.h, self.dh)
+        m(2, self.x, None, self.w1, self.dw1, self.h, self.dh)
+
+
+def cpu_arm(steps, warmup):
+    """The reference's own CPU path (oracle/_ref) if it was built, else the restated oracle; float32 (no CPU half in
+    the reference, deep8/src/math/MatrixMultiply.cpp:126-129) on a row slice, FLOPs counted for that slice."""
+    from oracle import pyoracle
+    if pyoracle.Reference.available():
+        impl = pyoracle.Reference()
+        cores = 1  # Eigen dense Map product without OpenMP: MatrixMultiply runs on one thread in the reference
+    else:
+        impl = pyoracle.Restated()
+        cores = impl.threads()
+    rng = np.random.Generator(np.random.Philox(10))
+    x = rng.standard_normal((1, CPU_SAMPLE_ROWS, D_IN)).astype(np.float32)
+    w1 = (rng.standard_normal((1, D_IN, D_HID)) * 0.02).astype(np.float32)
+    w2 = (rng.standard_normal((1, D_HID, D_IN)) * 0.02).astype(np.float32)
+    dy = (rng.standard_normal((1, CPU_SAMPLE_ROWS, D_IN)) * 0.01).astype(np.float32)
+    mlp = CpuMlp(impl, x, w1, w2, dy)
+    for _ in range(warmup):
+        mlp.step()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        mlp.step()
+    dt = (time.perf_counter() - t0) / steps
+    flop = FLOP_PER_STEP * CPU_SAMPLE_ROWS / M_PER_GPU
+    return {"value": flop / dt / 1e12, "unit": UNIT, "cores": cores, "kind": impl.kind,
+            "sample": "%d of %d rows per step, float32, %d step(s) of %.1f s" % (CPU_SAMPLE_ROWS, M_PER_GPU, steps, dt)}, dt
+
+
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    base, dt = cpu_arm(max(1, min(args.steps, 3)), 1 if args.warmup > 0 else 0)
+    line = {"impl": "reference", "metric": METRIC, "value": base["value"], "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f32", "data": "synthetic", "config": workload_config(args.gpus), "cpu_baseline": base,
+            "e2e": {"value": base["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(n):
+    return {"workload": "config 5: fp16 2-layer MLP fwd+bwd via MatrixMultiply, X %dx%d per GPU, W1 %dx%d, ReLU, W2 %dx%d" %
+            (M_PER_GPU, D_IN, D_IN, D_HID, D_HID, D_IN), "rows_per_gpu": M_PER_GPU, "global_rows": M_PER_GPU * n,
+            "parallelism": "batch-sharded x%d, weight gradients all-reduced" % n,
+            "flop_per_gpu_step": FLOP_PER_STEP, "l2": "inputs exceed L2 (weights 2x128 MiB, activations 4x256 MiB per GPU)"}
+
+
+# ------------------------------------------------------------------------------------------------ GPU arm
+class MlpStep:
+    """The MLP step on one GPU through the d8k C ABI; buffers allocated once, as an executor would keep them."""
+
+    def __init__(self, ctx, torch, device, rank):
+        self.ctx, self.torch = ctx, torch
+        g = torch.Generator(device=device)
+        g.manual_seed(10)
+        h = torch.float16
+        self.W1 = (torch.randn((1, D_IN, D_HID), device=device, generator=g) * 0.02).to(h)
+        self.W2 = (torch.randn((1, D_HID, D_IN), device=device, generator=g) * 0.02).to(h)
+        g.manual_seed(10 + 1000 * (rank + 1))
+        self.X = torch.randn((1, M_PER_GPU, D_IN), device=device, generator=g).to(h)
+        self.dY = (torch.randn((1, M_PER_GPU, D_IN), device=device, generator=g) * 0.01).to(h)
+        e = lambda *s: torch.empty(s, device=device, dtype=h)
+        self.H, self.A, self.Y = e(1, M_PER_GPU, D_HID), e(1, M_PER_GPU, D_HID), e(1, M_PER_GPU, D_IN)
+        self.dA, self.dH = e(1, M_PER_GPU, D_HID), e(1, M_PER_GPU, D_HID)
+        self.dX, self.dW1, self.dW2 = torch.empty_like(self.X), torch.empty_like(self.W1), torch.empty_like(self.W2)
+        self.gemm_events = []
+
+    def _gemm(self, fn, timed):
+        if timed:
+            a, b = self.torch.cuda.Event(enable_timing=True), self.torch.cuda.Event(enable_timing=True)
+            a.record()
+            fn()
+            b.record()
+            self.gemm_events.append((a, b))
+        else:
+            fn()
+
+    def step(self, dist=None, timed=False):
+        c = self.ctx
+        for t in (self.dA, self.dH, self.dX, self.dW1, self.dW2):
+            c.zero(t)
+        self._gemm(lambda: c.matmul_forward(self.X, self.W1, out=self.H), timed)
+        c.relu_forward(self.H, out=self.A)
+        self._gemm(lambda: c.matmul_forward(self.A, self.W2, out=self.Y), timed)
+        self._gemm(lambda: c.matmul_grad_x(self.A, self.dA, self.W2, self.dY), timed)
+        self._gemm(lambda: c.matmul_grad_y(self.A, self.W2, self.dW2, self.dY), timed)
+        work = []
+        if dist is not None:
+            work.append(dist.all_reduce(self.dW2, async_op=True))  # overlaps the rest of the backward pass
+        c.relu_backward(self.H, self.dH, self.dA)
+        self._gemm(lambda: c.matmul_grad_x(self.X, self.dX, self.W1, self.dH), timed)
+        self._gemm(lambda: c.matmul_grad_y(self.X, self.W1, self.dW1, self.dH), timed)
+        if dist is not None:
+            work.append(dist.all_reduce(self.dW1, async_op=True))
+            for w in work:
+                w.wait()
+
+
+def run_gpu_arm(args):
+    import torch
+    import deep8_b200
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if world != args.gpus:
+        raise SystemExit("--gpus %d but WORLD_SIZE=%d: launch with torch.distributed.run --nproc-per-node %d" % (args.gpus, world, args.gpus))
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=device)
+
+    ctx = deep8_b200.Context(local_rank)
+    stream = torch.cuda.current_stream()
+    ctx.use_stream(stream if stream.cuda_stream != 0 else None)
+    mlp = MlpStep(ctx, torch, device, rank)
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(ms):
+        if dist is None:
+            return ms
+        t = torch.tensor([ms], device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    for _ in range(args.warmup):
+        mlp.step(dist)
+    barrier()
+    if ctx.status() != 0:
+        raise SystemExit("kernel status non-zero after warm-up")
+
+    # ---- device-resident timed region
+    sampler = ClockSampler(local_rank)
+    if rank == 0 and not args.profile:
+        sampler.start()
+        time.sleep(0.3)
+    launches0 = ctx.launch_count()
+    barrier()
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0.record()
+    for _ in range(args.steps):
+        mlp.step(dist, timed=True)
+    t1.record()
+    barrier()
+    launches = ctx.launch_count() - launches0
+    clocks = sampler.stop() if (rank == 0 and not args.profile) else None
+    ms_total = max_over_ranks(t0.elapsed_time(t1))
+    ms_step = ms_total / args.steps
+    gemm_ms = [a.elapsed_time(b) for a, b in mlp.gemm_events]
+    mlp.gemm_events = []
+    if ctx.status() != 0:
+        raise SystemExit("kernel status non-zero after the timed region")
+
+    if args.profile:
+        if rank == 0:
+            print(json.dumps({"profile_run": True, "ms_per_step": ms_step, "gpu_launches": launches}), flush=True)
+        return
+    # ---- end-to-end: X and dY from pinned host memory every step, Y back to the host
+    hX = torch.empty(mlp.X.shape, dtype=torch.float16).pin_memory()
+    hdY = torch.empty(mlp.dY.shape, dtype=torch.float16).pin_memory()
+    hY = torch.empty(mlp.Y.shape, dtype=torch.float16).pin_memory()
+    hX.copy_(mlp.X)
+    hdY.copy_(mlp.dY)
+    e2e_steps = max(2, min(args.steps, 10))
+
+    def e2e_step():
+        mlp.X.copy_(hX, non_blocking=True)
+        mlp.dY.copy_(hdY, non_blocking=True)
+        mlp.step(dist)
+        hY.copy_(mlp.Y, non_blocking=True)
+
+    e2e_step()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    e1.record()
+    barrier()
+    e2e_ms = max_over_ranks(e0.elapsed_time(e1)) / e2e_steps
+    h2d = hX.numel() * 2 + hdY.numel() * 2
+    d2h = hY.numel() * 2
+
+    if rank == 0:
+        peak, peak_src = measured_peaks()
+        avg_gemm_ms = sum(gemm_ms) / len(gemm_ms)
+        achieved = FLOP_PER_GEMM / (avg_gemm_ms * 1e-3) / 1e12
+        per_gpu = FLOP_PER_STEP / (ms_step * 1e-3) / 1e12
+        line = {
+            "metric": METRIC, "value": per_gpu * world, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16 (f32 accumulate)",
+            "data": "synthetic", "config": workload_config(world),
+            "per_gpu_tflops": per_gpu, "frac_of_nominal_fp16_peak": per_gpu / NOMINAL_FP16_TFLOPS,
+            "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
+                         "traffic": TRAFFIC_BYTES_PER_LAUNCH, "kernel": "d8k_gemm_kernel (TMA-fed fp16, 128x256 tiles)",
+                         "peak_source": peak_src, "flop_per_launch": FLOP_PER_GEMM, "avg_launch_ms": avg_gemm_ms,
+                         "gemm_share_of_step": sum(gemm_ms) / (ms_step * args.steps)},
+            "e2e": {"value": FLOP_PER_STEP * world / (e2e_ms * 1e-3) / 1e12, "unit": UNIT, "h2d_bytes_per_step": h2d,
+                    "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms, "steps": e2e_steps},
+            "gpu_launches": launches, "clocks": clocks,
+        }
+        if world == 1 and not args.no_cpu:
+            line["cpu_baseline"], _ = cpu_arm(1, 0)
+        print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+# DRAM bytes (read + write) of one contraction launch of this workload from an ncu capture; None until captured.
+TRAFFIC_BYTES_PER_LAUNCH = None
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--profile", action="store_true", help="for runs under a profiler: no clock sampling, no end-to-end or CPU leg, "
+                    "warm-up as given; the printed numbers are not benchmark values")
+    args = ap.parse_args()
+    if args.impl == "ours" and not args.profile:
+        args.warmup = max(args.warmup, 3)  # timing rule: at least three untimed steps
+    if args.impl == "reference":
+        run_reference_arm(args)
+    else:
+        run_gpu_arm(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,457 @@
+// extern "C" layer (include/d8k.h): context management and the mapping of MatrixMultiply / Conv2d / DeConv2d,
+// forward and gradients, onto the one contraction kernel, plus the two element-wise neighbours (ReLU, zero fill).
+#include <atomic>
+#include <cstdint>
+#include <cstring>
+#include <string>
+
+#include "../../include/d8k.h"
+#include "gemm_host.h"
+
+struct d8k_ctx : public d8k::Ctx {};
+
+namespace d8k {
+
+static thread_local std::string g_error;
+static std::atomic<unsigned long long> g_launches{0};
+
+void set_error(const std::string& msg) { g_error = msg; }
+int fail(int code, const std::string& msg) {
+    g_error = msg;
+    return code;
+}
+void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
+
+namespace {
+
+#define D8K_CUDA(call)                                                                             \
+    do {                                                                                           \
+        cudaError_t e__ = (call);                                                                  \
+        if (e__ != cudaSuccess) return fail(D8K_ERR_CUDA, std::string(#call) + ": " + cudaGetErrorString(e__)); \
+    } while (0)
+
+int check_ctx(const d8k_ctx* ctx) {
+    if (!ctx) return fail(D8K_ERR_ARGUMENT, "null context");
+    return 0;
+}
+
+int check_dtype(int dtype) {
+    if (dtype != D8K_F16 && dtype != D8K_F32) return fail(D8K_ERR_ARGUMENT, "type is not support: dtype must be D8K_F16 or D8K_F32");
+    return 0;
+}
+
+int max0(int v) { return v > 0 ? v : 0; }
+
+// deep8/src/math/Conv2d.cu:334-335
+int conv_pad_before(int in, int out, int f, int stride, int dilation) {
+    int real = f + (f - 1) * (dilation - 1);
+    return -(max0((out - 1) * stride + real - in) / 2);
+}
+// deep8/src/math/DeConv2d.cu:99-100
+int deconv_pad_before(int in, int out, int f, int stride) { return -(max0(out + f - (in - 1) * stride - 2) / 2); }
+
+struct ConvDims {
+    int batch, ih, iw, ic, oc, fh, fw, oh, ow;
+};
+
+int check_conv(const ConvDims& d, int sy, int sx, int dy, int dx) {
+    if (d.batch < 1 || d.ih < 1 || d.iw < 1 || d.ic < 1 || d.oc < 1 || d.fh < 1 || d.fw < 1 || d.oh < 1 || d.ow < 1)
+        return fail(D8K_ERR_ARGUMENT, "the shape is error");
+    if (sy < 1 || sx < 1 || dy < 1 || dx < 1) return fail(D8K_ERR_ARGUMENT, "the stride or dilation is error");
+    long long m_in = 1LL * d.batch * d.ih * d.iw, m_out = 1LL * d.batch * d.oh * d.ow;
+    long long kc = 1LL * d.fh * d.fw * (d.ic > d.oc ? d.ic : d.oc);
+    if (m_in >= (1LL << 31) || m_out >= (1LL << 31) || kc >= (1LL << 31)) return fail(D8K_ERR_ARGUMENT, "the shape is too large");
+    return 0;
+}
+
+ConvRule rule(int RH, int RW, int SH, int SW, int C, int FW, int mul_y, int mul_x, int e_y, int e_x, int off_y, int off_x, int div_y,
+              int div_x) {
+    ConvRule r;
+    r.RH = RH; r.RW = RW; r.SH = SH; r.SW = SW; r.C = C; r.FW = FW;
+    r.mul_y = mul_y; r.mul_x = mul_x; r.e_y = e_y; r.e_x = e_x; r.off_y = off_y; r.off_x = off_x; r.div_y = div_y; r.div_x = div_x;
+    return r;
+}
+
+HostOperand plain(const void* ptr, bool mn, long long ld) {
+    HostOperand o;
+    o.ptr = ptr;
+    o.mn = mn;
+    o.ld = ld;
+    return o;
+}
+
+HostOperand virt(const void* ptr, bool mn, const ConvRule& cr) {
+    HostOperand o;
+    o.ptr = ptr;
+    o.mn = mn;
+    o.is_virtual = true;
+    o.cr = cr;
+    return o;
+}
+
+// filter [oc, T, ic] read as the matrix W'[(t, co)][ci]: row g = t * oc + co lives at co * (T * ic) + t * ic
+HostOperand filter_by_tap(const void* ptr, int oc, int taps, int ic) {
+    HostOperand o;
+    o.ptr = ptr;
+    o.mn = true;
+    o.rmod = oc;
+    o.ld = 1LL * taps * ic;
+    o.ld2 = ic;
+    return o;
+}
+
+// The three contractions of a convolution-like operator over virtual im2col matrices.
+//   forward : z[Mout x oc]      = V(x)[Mout x T*ic] * y^T
+//   grad x  : dx[Min x ic]     += V'(dz)[Min x T*oc] * W'
+//   grad y  : dy[oc x T*ic]    += dz^T[oc x Mout] * V(x)[Mout x T*ic]
+// `fwd` is the rule of V (rows = output pixels, source = x); `bwd` the rule of V' (rows = input pixels, source = dz).
+int conv_like(d8k_ctx* ctx, int which, int dtype, const ConvDims& d, const ConvRule& fwd, const ConvRule& bwd, const void* x, void* dx,
+              const void* y, void* dy, void* z, const void* dz, void* interim, size_t interim_bytes, bool plan_only, size_t* need) {
+    const int taps = d.fh * d.fw;
+    GemmProblem g;
+    g.dtype = dtype;
+    g.ws = interim;
+    g.ws_bytes = interim_bytes;
+    if (which == 0) {
+        g.M = d.batch * d.oh * d.ow; g.N = d.oc; g.K = taps * d.ic;
+        g.a = virt(x, false, fwd);
+        g.b = plain(y, false, g.K);
+        g.C = z; g.ldc = d.oc; g.beta = 0;
+    } else if (which == 1) {
+        g.M = d.batch * d.ih * d.iw; g.N = d.ic; g.K = taps * d.oc;
+        g.a = virt(dz, false, bwd);
+        g.b = filter_by_tap(y, d.oc, taps, d.ic);
+        g.C = dx; g.ldc = d.ic; g.beta = 1;
+    } else {
+        g.M = d.oc; g.N = taps * d.ic; g.K = d.batch * d.oh * d.ow;
+        g.a = plain(dz, true, d.oc);
+        g.b = virt(x, true, fwd);
+        g.C = dy; g.ldc = g.N; g.beta = 1;
+    }
+    if (plan_only) {
+        *need = gemm_scratch_need(ctx, g);
+        return 0;
+    }
+    return run_gemm(ctx, g);
+}
+
+void conv_rules(const ConvDims& d, int sy, int sx, int dly, int dlx, ConvRule* fwd, ConvRule* bwd) {
+    int pt = conv_pad_before(d.ih, d.oh, d.fh, sy, dly), pl = conv_pad_before(d.iw, d.ow, d.fw, sx, dlx);
+    // deep8/src/math/Conv2d.cu:44-45: inY = padTop + oy*strideY + fy*dilationY
+    *fwd = rule(d.oh, d.ow, d.ih, d.iw, d.ic, d.fw, sy, sx, dly, dlx, pt, pl, 1, 1);
+    // deep8/src/math/Conv2d.cu:99-113: oy = (iy - padTop - fy*dilationY) / strideY when divisible and inside
+    *bwd = rule(d.ih, d.iw, d.oh, d.ow, d.oc, d.fw, 1, 1, -dly, -dlx, -pt, -pl, sy, sx);
+}
+
+void deconv_rules(const ConvDims& d, int sy, int sx, ConvRule* fwd, ConvRule* bwd) {
+    int pt = deconv_pad_before(d.ih, d.oh, d.fh, sy), pl = deconv_pad_before(d.iw, d.ow, d.fw, sx);
+    // deep8/src/math/DeConv2d.cu:41-48: iy = (oy + padTop + fy) / strideY when divisible and inside
+    *fwd = rule(d.oh, d.ow, d.ih, d.iw, d.ic, d.fw, 1, 1, 1, 1, pt, pl, sy, sx);
+    // deep8/src/math/DeConv2d.cu:342-343: oy = iy*strideY - padTop - fy
+    *bwd = rule(d.ih, d.iw, d.oh, d.ow, d.oc, d.fw, sy, sx, -1, -1, -pt, -pl, 1, 1);
+}
+
+// ------------------------------------------------------------------------------------------------ element-wise
+template <typename T>
+__device__ __forceinline__ float to_f(T v);
+template <>
+__device__ __forceinline__ float to_f<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ float to_f<__half>(__half v) { return __half2float(v); }
+template <typename T>
+__device__ __forceinline__ T from_f(float v);
+template <>
+__device__ __forceinline__ float from_f<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ __half from_f<__half>(float v) { return __float2half_rn(v); }
+
+// 16 bytes per thread per step; the tail and unaligned buffers go element by element.
+template <typename T>
+__global__ void relu_forward_kernel(const T* __restrict__ x, T* __restrict__ y, size_t n, bool vec) {
+    constexpr int V = 16 / sizeof(T);
+    size_t tid = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x;
+    size_t stride = gridDim.x * static_cast<size_t>(blockDim.x);
+    size_t nv = vec ? n / V : 0;
+    for (size_t i = tid; i < nv; i += stride) {
+        uint4 in = reinterpret_cast<const uint4*>(x)[i];
+        T* e = reinterpret_cast<T*>(&in);
+#pragma unroll
+        for (int k = 0; k < V; ++k) e[k] = to_f(e[k]) > 0.f ? e[k] : from_f<T>(0.f);
+        reinterpret_cast<uint4*>(y)[i] = in;
+    }
+    for (size_t i = nv * V + tid; i < n; i += stride) y[i] = to_f(x[i]) > 0.f ? x[i] : from_f<T>(0.f);
+}
+
+template <typename T>
+__global__ void relu_backward_kernel(const T* __restrict__ x, T* __restrict__ dx, const T* __restrict__ dy, size_t n, bool vec) {
+    constexpr int V = 16 / sizeof(T);
+    size_t tid = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x;
+    size_t stride = gridDim.x * static_cast<size_t>(blockDim.x);
+    size_t nv = vec ? n / V : 0;
+    for (size_t i = tid; i < nv; i += stride) {
+        uint4 xin = reinterpret_cast<const uint4*>(x)[i];
+        uint4 gin = reinterpret_cast<const uint4*>(dy)[i];
+        uint4 acc = reinterpret_cast<const uint4*>(dx)[i];
+        const T* xe = reinterpret_cast<const T*>(&xin);
+        const T* ge = reinterpret_cast<const T*>(&gin);
+        T* ae = reinterpret_cast<T*>(&acc);
+#pragma unroll
+        for (int k = 0; k < V; ++k)
+            if (to_f(xe[k]) > 0.f) ae[k] = from_f<T>(to_f(ae[k]) + to_f(ge[k]));
+        reinterpret_cast<uint4*>(dx)[i] = acc;
+    }
+    for (size_t i = nv * V + tid; i < n; i += stride)
+        if (to_f(x[i]) > 0.f) dx[i] = from_f<T>(to_f(dx[i]) + to_f(dy[i]));
+}
+
+bool aligned16(const void* a, const void* b, const void* c) {
+    return ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b) | reinterpret_cast<uintptr_t>(c)) & 15) == 0;
+}
+
+int elementwise_grid(const d8k_ctx* ctx, size_t n, int per_thread) {
+    size_t blocks = (n / per_thread + 255) / 256;
+    size_t cap = static_cast<size_t>(ctx->num_sms) * 8;
+    if (blocks > cap) blocks = cap;
+    if (blocks < 1) blocks = 1;
+    return static_cast<int>(blocks);
+}
+
+}  // namespace
+}  // namespace d8k
+
+using namespace d8k;
+
+extern "C" {
+
+const char* d8k_last_error(void) { return g_error.c_str(); }
+unsigned long long d8k_launch_count(void) { return g_launches.load(); }
+
+int d8k_ctx_create(int device, size_t scratch_bytes, d8k_ctx** out) {
+    if (!out) return fail(D8K_ERR_ARGUMENT, "d8k_ctx_create: null output pointer");
+    *out = nullptr;
+    int count = 0;
+    D8K_CUDA(cudaGetDeviceCount(&count));
+    if (device < 0 || device >= count) return fail(D8K_ERR_ARGUMENT, "d8k_ctx_create: no such device");
+    D8K_CUDA(cudaSetDevice(device));
+    cudaDeviceProp prop;
+    D8K_CUDA(cudaGetDeviceProperties(&prop, device));
+    if (prop.major != 10) return fail(D8K_ERR_CUDA, "d8k_ctx_create: these kernels are built for sm_100a (B200) only");
+    d8k_ctx* ctx = new d8k_ctx();
+    ctx->device = device;
+    ctx->num_sms = prop.multiProcessorCount;
+    ctx->scratch_bytes = scratch_bytes ? scratch_bytes : (static_cast<size_t>(64) << 20);
+    cudaError_t e = cudaMalloc(&ctx->scratch, ctx->scratch_bytes);
+    if (e == cudaSuccess) e = cudaMalloc(&ctx->counters, (kMaxCounters + 1) * sizeof(int));
+    if (e == cudaSuccess) e = cudaMemset(ctx->counters, 0, (kMaxCounters + 1) * sizeof(int));
+    if (e != cudaSuccess) {
+        cudaFree(ctx->scratch);
+        cudaFree(ctx->counters);
+        delete ctx;
+        return fail(D8K_ERR_CUDA, std::string("d8k_ctx_create: ") + cudaGetErrorString(e));
+    }
+    ctx->status = ctx->counters + kMaxCounters;
+    *out = ctx;
+    return 0;
+}
+
+int d8k_ctx_destroy(d8k_ctx* ctx) {
+    if (!ctx) return 0;
+    cudaSetDevice(ctx->device);
+    cudaFree(ctx->scratch);
+    cudaFree(ctx->counters);
+    delete ctx;
+    return 0;
+}
+
+int d8k_ctx_set_stream(d8k_ctx* ctx, void* stream) {
+    if (int rc = check_ctx(ctx)) return rc;
+    ctx->stream = static_cast<cudaStream_t>(stream);
+    return 0;
+}
+
+int d8k_ctx_num_sms(const d8k_ctx* ctx) { return ctx ? ctx->num_sms : 0; }
+
+int d8k_ctx_status(d8k_ctx* ctx, int* status) {
+    if (int rc = check_ctx(ctx)) return rc;
+    D8K_CUDA(cudaStreamSynchronize(ctx->stream));
+    int host = 0;
+    D8K_CUDA(cudaMemcpy(&host, ctx->status, sizeof(int), cudaMemcpyDeviceToHost));
+    if (status) *status = host;
+    if (host != 0) {
+        // a kernel left early: its tile tickets may be half-counted
+        cudaMemset(ctx->counters, 0, (kMaxCounters + 1) * sizeof(int));
+        return fail(D8K_ERR_KERNEL, "a kernel gave up on a bounded wait, status " + std::to_string(host));
+    }
+    return 0;
+}
+
+int d8k_gemm(d8k_ctx* ctx, int dtype, int transA, int transB, int M, int N, int K, const void* A, long long lda, int batchA,
+             long long strideA, const void* B, long long ldb, int batchB, long long strideB, void* C, long long ldc, long long strideC,
+             int batch, int beta, int reduce_batch) {
+    if (int rc = check_ctx(ctx)) return rc;
+    if (int rc = check_dtype(dtype)) return rc;
+    if (batchA < 1 || batchB < 1 || batch < 0) return fail(D8K_ERR_ARGUMENT, "d8k_gemm: batch counts must be positive");
+    GemmProblem g;
+    g.dtype = dtype;
+    g.M = M; g.N = N; g.K = K;
+    g.a = plain(A, transA != 0, lda);
+    g.a.batch_count = batchA;
+    g.a.batch_stride = strideA;
+    g.b = plain(B, transB == 0, ldb);
+    g.b.batch_count = batchB;
+    g.b.batch_stride = strideB;
+    g.C = C; g.ldc = ldc; g.c_batch_stride = strideC;
+    g.batch = reduce_batch ? 1 : batch;
+    g.kbatch = reduce_batch ? (batch > 0 ? batch : 1) : 1;
+    if (reduce_batch && batch == 0) g.K = 0;
+    g.beta = beta;
+    return run_gemm(ctx, g);
+}
+
+static int check_matmul(int xb, int xr, int xc, int yb, int yc) {
+    if (xb < 1 || yb < 1 || xr < 1 || xc < 1 || yc < 1) return fail(D8K_ERR_ARGUMENT, "the shape is error");
+    if (xb != yb && xb != 1 && yb != 1) return fail(D8K_ERR_ARGUMENT, "the shape is error");  // deep8/src/nodes/MatrixMultiply.cpp:15-17
+    if (1LL * (xb > yb ? xb : yb) * xr >= (1LL << 31)) return fail(D8K_ERR_ARGUMENT, "the shape is too large");
+    return 0;
+}
+
+int d8k_matmul_forward(d8k_ctx* ctx, int dtype, const void* x, int xb, int xr, int xc, const void* y, int yb, int yc, void* z) {
+    if (int rc = check_ctx(ctx)) return rc;
+    if (int rc = check_dtype(dtype)) return rc;
+    if (int rc = check_matmul(xb, xr, xc, yb, yc)) return rc;
+    if (yb == 1)  // deep8/src/math/MatrixMultiply.cu:31-36: the batch folds into M
+        return d8k_gemm(ctx, dtype, 0, 0, xb * xr, yc, xc, x, xc, 1, 0, y, yc, 1, 0, z, yc, 0, 1, 0, 0);
+    int zb = xb > yb ? xb : yb;
+    return d8k_gemm(ctx, dtype, 0, 0, xr, yc, xc, x, xc, xb, 1LL * xr * xc, y, yc, yb, 1LL * xc * yc, z, yc, 1LL * xr * yc, zb, 0, 0);
+}
+
+int d8k_matmul_grad_x(d8k_ctx* ctx, int dtype, void* dx, int xb, int xr, int xc, const void* y, int yb, int yc, const void* dz) {
+    if (int rc = check_ctx(ctx)) return rc;
+    if (int rc = check_dtype(dtype)) return rc;
+    if (int rc = check_matmul(xb, xr, xc, yb, yc)) return rc;
+    // dx[M x xc] += dz[M x yc] * y^T ; y is [xc x yc], i.e. already "N x K" for this product
+    if (yb == 1) return d8k_gemm(ctx, dtype, 0, 1, xb * xr, xc, yc, dz, yc, 1, 0, y, yc, 1, 0, dx, xc, 0, 1, 1, 0);
+    int zb = xb > yb ? xb : yb;
+    if (xb == 1 && zb > 1)  // broadcast x: every batch entry adds into the one dx (deep8/src/math/MatrixMultiply.cu:220-231)
+        return d8k_gemm(ctx, dtype, 0, 1, xr, xc, yc, dz, yc, zb, 1LL * xr * yc, y, yc, yb, 1LL * xc * yc, dx, xc, 0, zb, 1, 1);
+    return d8k_gemm(ctx, dtype, 0, 1, xr, xc, yc, dz, yc, zb, 1LL * xr * yc, y, yc, yb, 1LL * xc * yc, dx, xc, 1LL * xr * xc, zb, 1, 0);
+}
+
+int d8k_matmul_grad_y(d8k_ctx* ctx, int dtype, const void* x, int xb, int xr, int xc, void* dy, int yb, int yc, const void* dz) {
+    if (int rc = check_ctx(ctx)) return rc;
+    if (int rc = check_dtype(dtype)) return rc;
+    if (int rc = check_matmul(xb, xr, xc, yb, yc)) return rc;
+    // dy[xc x yc] += x^T * dz ; with yb == 1 the batch joins the contraction: K = xb * xr (deep8/src/math/MatrixMultiply.cu:393-398)
+    if (yb == 1) return d8k_gemm(ctx, dtype, 1, 0, xc, yc, xb * xr, x, xc, 1, 0, dz, yc, 1, 0, dy, yc, 0, 1, 1, 0);
+    return d8k_gemm(ctx, dtype, 1, 0, xc, yc, xr, x, xc, xb, 1LL * xr * xc, dz, yc, yb, 1LL * xr * yc, dy, yc, 1LL * xc * yc, yb, 1, 0);
+}
+
+int d8k_conv2d_out_dim(int in, int filter, int stride, int dilation, int covered) {
+    int real = filter + (filter - 1) * (dilation - 1);
+    return covered ? (in - 1) / stride + 1 : (in - real) / stride + 1;
+}
+int d8k_deconv2d_out_dim(int in, int filter, int stride, int covered) { return covered ? (in - 1) * stride + 1 : (in - 1) * stride + filter; }
+
+size_t d8k_conv2d_interim_size(const d8k_ctx* ctx, int which, int dtype, int batch, int ih, int iw, int ic, int oc, int fh, int fw, int oh,
+                               int ow) {
+    if (!ctx || which < 0 || which > 2) return 0;
+    ConvDims d{batch, ih, iw, ic, oc, fh, fw, oh, ow};
+    ConvRule f, b;
+    conv_rules(d, 1, 1, 1, 1, &f, &b);
+    size_t need = 0;
+    conv_like(const_cast<d8k_ctx*>(ctx), which, dtype, d, f, b, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, 0, true, &need);
+    return need;
+}
+size_t d8k_deconv2d_interim_size(const d8k_ctx* ctx, int which, int dtype, int batch, int ih, int iw, int ic, int oc, int fh, int fw,
+                                 int oh, int ow) {
+    return d8k_conv2d_interim_size(ctx, which, dtype, batch, ih, iw, ic, oc, fh, fw, oh, ow);  // same contraction shapes
+}
+
+#define D8K_CONV_PROLOGUE(strideY, strideX, dilY, dilX)                    \
+    if (int rc = check_ctx(ctx)) return rc;                                \
+    if (int rc = check_dtype(dtype)) return rc;                            \
+    ConvDims d{batch, ih, iw, ic, oc, fh, fw, oh, ow};                     \
+    if (int rc = check_conv(d, strideY, strideX, dilY, dilX)) return rc;   \
+    ConvRule fwd, bwd;
+
+int d8k_conv2d_forward(d8k_ctx* ctx, int dtype, const void* x, int batch, int ih, int iw, int ic, const void* y, int oc, int fh, int fw,
+                       void* z, int oh, int ow, int strideY, int strideX, int dilationY, int dilationX, void* interim, size_t interim_bytes) {
+    D8K_CONV_PROLOGUE(strideY, strideX, dilationY, dilationX)
+    conv_rules(d, strideY, strideX, dilationY, dilationX, &fwd, &bwd);
+    return conv_like(ctx, 0, dtype, d, fwd, bwd, x, nullptr, y, nullptr, z, nullptr, interim, interim_bytes, false, nullptr);
+}
+int d8k_conv2d_grad_x(d8k_ctx* ctx, int dtype, void* dx, int batch, int ih, int iw, int ic, const void* y, int oc, int fh, int fw,
+                      const void* dz, int oh, int ow, int strideY, int strideX, int dilationY, int dilationX, void* interim,
+                      size_t interim_bytes) {
+    D8K_CONV_PROLOGUE(strideY, strideX, dilationY, dilationX)
+    conv_rules(d, strideY, strideX, dilationY, dilationX, &fwd, &bwd);
+    return conv_like(ctx, 1, dtype, d, fwd, bwd, nullptr, dx, y, nullptr, nullptr, dz, interim, interim_bytes, false, nullptr);
+}
+int d8k_conv2d_grad_y(d8k_ctx* ctx, int dtype, const void* x, int batch, int ih, int iw, int ic, void* dy, int oc, int fh, int fw,
+                      const void* dz, int oh, int ow, int strideY, int strideX, int dilationY, int dilationX, void* interim,
+                      size_t interim_bytes) {
+    D8K_CONV_PROLOGUE(strideY, strideX, dilationY, dilationX)
+    conv_rules(d, strideY, strideX, dilationY, dilationX, &fwd, &bwd);
+    return conv_like(ctx, 2, dtype, d, fwd, bwd, x, nullptr, nullptr, dy, nullptr, dz, interim, interim_bytes, false, nullptr);
+}
+
+int d8k_deconv2d_forward(d8k_ctx* ctx, int dtype, const void* x, int batch, int ih, int iw, int ic, const void* y, int oc, int fh, int fw,
+                         void* z, int oh, int ow, int strideY, int strideX, void* interim, size_t interim_bytes) {
+    D8K_CONV_PROLOGUE(strideY, strideX, 1, 1)
+    deconv_rules(d, strideY, strideX, &fwd, &bwd);
+    return conv_like(ctx, 0, dtype, d, fwd, bwd, x, nullptr, y, nullptr, z, nullptr, interim, interim_bytes, false, nullptr);
+}
+int d8k_deconv2d_grad_x(d8k_ctx* ctx, int dtype, void* dx, int batch, int ih, int iw, int ic, const void* y, int oc, int fh, int fw,
+                        const void* dz, int oh, int ow, int strideY, int strideX, void* interim, size_t interim_bytes) {
+    D8K_CONV_PROLOGUE(strideY, strideX, 1, 1)
+    deconv_rules(d, strideY, strideX, &fwd, &bwd);
+    return conv_like(ctx, 1, dtype, d, fwd, bwd, nullptr, dx, y, nullptr, nullptr, dz, interim, interim_bytes, false, nullptr);
+}
+int d8k_deconv2d_grad_y(d8k_ctx* ctx, int dtype, const void* x, int batch, int ih, int iw, int ic, void* dy, int oc, int fh, int fw,
+                        const void* dz, int oh, int ow, int strideY, int strideX, void* interim, size_t interim_bytes) {
+    D8K_CONV_PROLOGUE(strideY, strideX, 1, 1)
+    deconv_rules(d, strideY, strideX, &fwd, &bwd);
+    return conv_like(ctx, 2, dtype, d, fwd, bwd, x, nullptr, nullptr, dy, nullptr, dz, interim, interim_bytes, false, nullptr);
+}
+
+int d8k_relu_forward(d8k_ctx* ctx, int dtype, const void* x, void* y, size_t n) {
+    if (int rc = check_ctx(ctx)) return rc;
+    if (int rc = check_dtype(dtype)) return rc;
+    if (n == 0) return 0;
+    if (!x || !y) return fail(D8K_ERR_ARGUMENT, "relu: null pointer");
+    bool vec = aligned16(x, y, nullptr);
+    if (dtype == D8K_F32)
+        relu_forward_kernel<float><<<elementwise_grid(ctx, n, 4), 256, 0, ctx->stream>>>(static_cast<const float*>(x), static_cast<float*>(y), n, vec);
+    else
+        relu_forward_kernel<__half><<<elementwise_grid(ctx, n, 8), 256, 0, ctx->stream>>>(static_cast<const __half*>(x), static_cast<__half*>(y), n, vec);
+    D8K_CUDA(cudaGetLastError());
+    count_launch();
+    return 0;
+}
+
+int d8k_relu_backward(d8k_ctx* ctx, int dtype, const void* x, void* dx, const void* dy, size_t n) {
+    if (int rc = check_ctx(ctx)) return rc;
+    if (int rc = check_dtype(dtype)) return rc;
+    if (n == 0) return 0;
+    if (!x || !dx || !dy) return fail(D8K_ERR_ARGUMENT, "relu: null pointer");
+    bool vec = aligned16(x, dx, dy);
+    if (dtype == D8K_F32)
+        relu_backward_kernel<float><<<elementwise_grid(ctx, n, 4), 256, 0, ctx->stream>>>(static_cast<const float*>(x), static_cast<float*>(dx),
+                                                                                        static_cast<const float*>(dy), n, vec);
+    else
+        relu_backward_kernel<__half><<<elementwise_grid(ctx, n, 8), 256, 0, ctx->stream>>>(static_cast<const __half*>(x), static_cast<__half*>(dx),
+                                                                                         static_cast<const __half*>(dy), n, vec);
+    D8K_CUDA(cudaGetLastError());
+    count_launch();
+    return 0;
+}
+
+int d8k_zero(d8k_ctx* ctx, void* ptr, size_t bytes) {
+    if (int rc = check_ctx(ctx)) return rc;
+    if (bytes == 0) return 0;
+    if (!ptr) return fail(D8K_ERR_ARGUMENT, "zero: null pointer");
+    D8K_CUDA(cudaMemsetAsync(ptr, 0, bytes, ctx->stream));
+    return 0;
+}
+
+}  // extern "C"

@@ -1,0 +1,78 @@
+// Host-side description of one contraction and the context that launches it.
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <cstddef>
+#include <string>
+
+#include "gemm_kernel.cuh"
+
+namespace d8k {
+
+struct Ctx {
+    int device = 0;
+    int num_sms = 148;
+    cudaStream_t stream = nullptr;
+    float* scratch = nullptr;  // split-K partial tiles
+    size_t scratch_bytes = 0;
+    int* counters = nullptr;   // kMaxCounters tile tickets, zero between launches
+    int* status = nullptr;     // device status word
+};
+constexpr int kMaxCounters = 4096;
+
+// One operand as the host sees it.  mn == false: K-major (the contraction index is contiguous); mn == true: MN-major.
+struct HostOperand {
+    const void* ptr = nullptr;
+    bool mn = false;
+    bool is_virtual = false;   // virtual im2col matrix (cr) over the image at ptr
+    long long ld = 0;          // pitch in elements of the stored matrix
+    int rmod = 0;              // > 0: stored row g lives at (g % rmod) * ld + (g / rmod) * ld2
+    long long ld2 = 0;
+    long long batch_stride = 0;
+    int batch_count = 1;
+    ConvRule cr = {};
+};
+
+struct GemmProblem {
+    int dtype = 0;
+    int M = 0, N = 0, K = 0;
+    HostOperand a, b;
+    void* C = nullptr;
+    long long ldc = 0, c_batch_stride = 0;
+    int batch = 1;    // independent outputs
+    int kbatch = 1;   // batches summed into one output
+    int beta = 0;
+    void* ws = nullptr;  // optional caller scratch for split-K
+    size_t ws_bytes = 0;
+};
+
+// error reporting shared by the API layer
+void set_error(const std::string& msg);
+int fail(int code, const std::string& msg);
+void count_launch();
+
+int run_gemm(Ctx* ctx, const GemmProblem& g);
+// scratch bytes run_gemm would use for this problem with its default split choice (0 when it runs unsplit)
+size_t gemm_scratch_need(const Ctx* ctx, const GemmProblem& g);
+
+typedef cudaError_t (*GemmLaunchFn)(int grid, cudaStream_t stream, const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p);
+// one table per translation unit of instantiations; index [a_mn][b_mn][bn slot]
+GemmLaunchFn lookup_f16_tma(bool a_mn, bool b_mn, int bn);
+GemmLaunchFn lookup_f16_gather(bool a_mn, bool b_mn, int bn);
+GemmLaunchFn lookup_f32_gather(bool a_mn, bool b_mn, int bn);
+
+template <class Cfg>
+cudaError_t launch_cfg(int grid, cudaStream_t stream, const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p) {
+    static bool configured[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64 || !configured[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(d8k_gemm_kernel<Cfg>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
+        if (e != cudaSuccess) return e;
+        if (dev >= 0 && dev < 64) configured[dev] = true;
+    }
+    d8k_gemm_kernel<Cfg><<<grid, Cfg::THREADS, Cfg::SMEM_BYTES, stream>>>(ta, tb, p);
+    return cudaGetLastError();
+}
+
+}  // namespace d8k

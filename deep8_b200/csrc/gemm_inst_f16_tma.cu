@@ -1,0 +1,20 @@
+// Instantiations of the TMA-fed fp16 kernel: 128 x {128, 256} tiles, every operand-major combination.
+#include "gemm_host.h"
+
+namespace d8k {
+
+template <bool A_MN, bool B_MN>
+static GemmLaunchFn pick(int bn) {
+    if (bn == 256) return launch_cfg<GemmCfg<false, A_MN, B_MN, 256, 4, false>>;
+    if (bn == 128) return launch_cfg<GemmCfg<false, A_MN, B_MN, 128, 6, false>>;
+    return nullptr;
+}
+
+GemmLaunchFn lookup_f16_tma(bool a_mn, bool b_mn, int bn) {
+    if (!a_mn && !b_mn) return pick<false, false>(bn);
+    if (!a_mn && b_mn) return pick<false, true>(bn);
+    if (a_mn && !b_mn) return pick<true, false>(bn);
+    return pick<true, true>(bn);
+}
+
+}  // namespace d8k

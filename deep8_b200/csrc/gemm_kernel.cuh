@@ -1,0 +1,629 @@
+// One warp-specialised, persistent tcgen05 GEMM kernel for every contraction of the path:
+//
+//     D[b][M x N] (+)= sum_k A[b](m, k) * B[b](n, k)
+//
+// Operands are staged in shared memory as 128-byte rows under the 128-byte swizzle and multiplied by
+// tcgen05.mma (cta_group::1, UMMA 128 x BN x {16 | 8}) into fp32 accumulators in tensor memory; two accumulator
+// buffers let the epilogue of one tile overlap the main loop of the next.  Two ways of filling a stage:
+//
+//   TMA    (fp16 only)  one thread issues cp.async.bulk.tensor loads; needs 16-byte aligned pitches.
+//   GATHER (fp16/fp32)  four loader warps read global memory with plain 16-byte loads and write the swizzled rows
+//                       themselves.  An operand is either a strided matrix or a *virtual im2col matrix* whose
+//                       rows are pixels and whose columns are (filter tap, channel): the column buffer of the
+//                       reference's Conv2d/DeConv2d (deep8/src/math/Conv2d.cu:10-61, DeConv2d.cu:311-351) is never
+//                       written to memory.  For fp32 the loaders split every value into a tf32 "hi" and a tf32 "lo"
+//                       part (3xTF32): D += A_lo*B_hi + A_hi*B_lo + A_hi*B_hi, accumulated in fp32.
+//
+// Split-K: when the output has few tiles and K is long, `splits` CTAs share one tile.  Each writes its fp32 partial
+// tile to scratch memory, takes a ticket with atomicAdd, and the CTA that draws the last ticket sums the partials
+// in split order (so the result does not depend on arrival order), applies beta and stores.  Nobody waits on another CTA.
+//
+// Every mbarrier wait is bounded: on expiry the CTA records a status code, all roles leave their loops, and the
+// kernel returns through the normal teardown (TMEM freed).
+#pragma once
+#include <cuda.h>
+#include <cuda_fp16.h>
+#include <cstdint>
+#include <type_traits>
+
+#include "ptx_sm100.cuh"
+
+namespace d8k {
+
+constexpr int kBM = 128;                          // UMMA M
+constexpr long long kWaitLimitCycles = 4000000000LL;  // ~2 s at the maximum SM clock
+
+// status word values written by a kernel that gave up on a wait: (role << 8) | which barrier
+enum : int { kStatusOk = 0, kRoleProducer = 1, kRoleMma = 2, kRoleEpilogue = 3, kRoleLoader = 4 };
+
+// Pixel/tap rule of a virtual im2col matrix.  Row g = (n, py, px) over an RH x RW grid; column = tap * C + c with
+// tap = fy * FW + fx.  The source pixel is ((py*mul_y + fy*e_y + off_y) / div_y, likewise x) in an SH x SW image with
+// C channels; the element is zero unless the numerators are >= 0, divisible, and the quotients are inside the image.
+struct ConvRule {
+    int RH, RW, SH, SW, C, FW;
+    int mul_y, mul_x, e_y, e_x, off_y, off_x, div_y, div_x;
+};
+
+// Where the loader warps find one operand.  Logical view: `rows` x `cols` elements, 128-byte windows of a row are
+// fetched at a time.  kind 0: matrix, row g at base + g * ld, or with rmod > 0 at base + (g % rmod) * ld + (g / rmod) * ld2 (+ batch).  kind 1: virtual
+// im2col matrix described by `cr` over the NHWC image at base.
+struct GatherSrc {
+    const void* base;
+    int kind;
+    int rows, cols;
+    int rmod;
+    long long ld, ld2;
+    long long batch_stride;
+    int batch_count;
+    ConvRule cr;
+};
+
+struct GemmParams {
+    int M, N, K;
+    int batch;         // output batches (independent problems)
+    int kbatch;        // batches folded into the contraction (sum over b of A[b] * B[b]); 1 otherwise
+    int num_kb;        // k-blocks per batch = ceil(K / BK)
+    int splits, kb_per_split;
+    int tiles_m, tiles_n, raster_group;
+    int total_work;    // batch * tiles_m * tiles_n * splits
+    int beta;          // 0: overwrite, 1: accumulate into C
+    void* C;
+    long long ldc, c_batch_stride;
+    float* ws;         // split-K partial tiles: total_work * 128 * BN floats
+    int* counters;     // one ticket counter per output tile, zero on entry and on exit
+    int* status;
+    int a_batch_mod, b_batch_mod;  // TMA: batch coordinate = b % mod
+    GatherSrc a, b;
+};
+
+template <bool F32_, bool A_MN_, bool B_MN_, int BN_, int STAGES_, bool GATHER_>
+struct GemmCfg {
+    static constexpr bool F32 = F32_, A_MN = A_MN_, B_MN = B_MN_, GATHER = GATHER_;
+    static constexpr int BN = BN_, STAGES = STAGES_;
+    static constexpr int ESIZE = F32 ? 4 : 2;
+    static constexpr int CE = 128 / ESIZE;       // elements in one 128-byte row
+    static constexpr int BK = CE;                // k extent of one stage
+    static constexpr int VEC = 16 / ESIZE;       // elements in one 16-byte chunk
+    static constexpr int UMMA_K = 32 / ESIZE;
+    static constexpr int KSTEPS = BK / UMMA_K;   // 4
+    static constexpr int PARTS = F32 ? 2 : 1;    // hi and lo images for 3xTF32
+    // MN-major tf32 operands must use the 128-byte swizzle with 32-byte atoms (4-row groups)
+    static constexpr bool A_B32 = F32 && A_MN, B_B32 = F32 && B_MN;
+    static constexpr int A_BYTES = kBM * 128;
+    static constexpr int B_BYTES = BN * 128;
+    static constexpr int STAGE_BYTES = PARTS * (A_BYTES + B_BYTES);
+    static constexpr int TMEM_COLS = (2 * BN <= 32) ? 32 : (2 * BN <= 64) ? 64 : (2 * BN <= 128) ? 128 : (2 * BN <= 256) ? 256 : 512;
+    // fp32 only: the tensor core adds into its fp32 accumulator with truncation, so a long chain drifts (about
+    // 2e-5 of the result after 1300 accumulations).  Every CHUNK_KB k-blocks the accumulator buffer is handed to the
+    // epilogue warps, which add it to register accumulators with round-to-nearest, and a fresh chain starts in the
+    // other buffer.  0 = one chain per work item (fp16, whose output rounding is far coarser).
+    static constexpr int CHUNK_KB = F32 ? 8 : 0;
+    static constexpr int EPI_WARPS = 4;
+    static constexpr int PRODUCER_WARP = 4, MMA_WARP = 5, LOADER_WARP0 = 6, LOADER_WARPS = 4;
+    static constexpr int THREADS = GATHER ? 32 * (LOADER_WARP0 + LOADER_WARPS) : 32 * 6;
+    static constexpr int BAR_BYTES = 256;
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + BAR_BYTES + 1024;  // + slack to align the ring to 1024
+    static_assert(BN % 16 == 0 && BN >= 16 && BN <= 256, "UMMA N");
+    static_assert(BN % CE == 0, "an MN-major B tile is whole 128-byte chunks");
+    static_assert(!F32 || GATHER, "the fp32 path needs the loader warps for the hi/lo split");
+    static_assert(SMEM_BYTES <= 227 * 1024, "shared memory");
+    static_assert(SMEM_BYTES > 114 * 1024, "one CTA per SM: two would compete for tensor memory");
+};
+
+struct WorkItem {
+    int tile, split, batch, m0, n0, kb_begin, kb_end;
+};
+
+__device__ __forceinline__ WorkItem decode_work(const GemmParams& p, int w, int BN) {
+    WorkItem it;
+    it.tile = w / p.splits;
+    it.split = w - it.tile * p.splits;
+    int tpb = p.tiles_m * p.tiles_n;
+    it.batch = it.tile / tpb;
+    int t = it.tile - it.batch * tpb;
+    int group_size = p.raster_group * p.tiles_n;
+    int gid = t / group_size;
+    int first_m = gid * p.raster_group;
+    int gm = min(p.tiles_m - first_m, p.raster_group);
+    int in_group = t - gid * group_size;
+    int nt = in_group / gm;
+    int mt = first_m + (in_group - nt * gm);
+    it.m0 = mt * kBM;
+    it.n0 = nt * BN;
+    it.kb_begin = it.split * p.kb_per_split;
+    it.kb_end = min(p.kbatch * p.num_kb, it.kb_begin + p.kb_per_split);
+    return it;
+}
+
+__device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
+    if (ptx::mbar_try_wait(bar, parity)) return true;
+    long long t0 = clock64();
+    int spins = 0;
+    while (!ptx::mbar_try_wait(bar, parity)) {
+        if ((++spins & 63) == 0) {
+            if (*abort_flag) return false;
+            if (clock64() - t0 > kWaitLimitCycles) {
+                *abort_flag = 1;
+                atomicCAS(status, 0, code);
+                return false;
+            }
+        }
+    }
+    return true;
+}
+
+// ------------------------------------------------------------------------------------------------ gather loaders
+// 16 bytes of row g starting at column `col` of an operand, zero outside the logical extent.
+template <typename T, int VEC>
+__device__ __forceinline__ uint4 fetch16(const GatherSrc& s, int g, int col, int batch) {
+    uint4 out = make_uint4(0u, 0u, 0u, 0u);
+    if (g >= s.rows || col >= s.cols) return out;
+    const T* base = reinterpret_cast<const T*>(s.base);
+    if (s.kind == 0) {
+        const T* p = base + static_cast<long long>(batch % s.batch_count) * s.batch_stride + col;
+        if (s.rmod > 0) p += static_cast<long long>(g % s.rmod) * s.ld + static_cast<long long>(g / s.rmod) * s.ld2;
+        else p += static_cast<long long>(g) * s.ld;
+        if (col + VEC <= s.cols && (reinterpret_cast<uintptr_t>(p) & 15) == 0) {
+            out = __ldg(reinterpret_cast<const uint4*>(p));
+        } else {
+            T tmp[VEC];
+#pragma unroll
+            for (int i = 0; i < VEC; ++i) tmp[i] = (col + i < s.cols) ? __ldg(p + i) : T(0);
+            out = *reinterpret_cast<uint4*>(tmp);
+        }
+        return out;
+    }
+    const ConvRule& r = s.cr;
+    int plane = r.RH * r.RW;
+    int n = g / plane;
+    int rem = g - n * plane;
+    int py = rem / r.RW;
+    int px = rem - py * r.RW;
+    auto source = [&](int column, long long& offset) -> bool {
+        int tap = column / r.C;
+        int c = column - tap * r.C;
+        int fy = tap / r.FW;
+        int fx = tap - fy * r.FW;
+        int ny = py * r.mul_y + fy * r.e_y + r.off_y;
+        int nx = px * r.mul_x + fx * r.e_x + r.off_x;
+        if (ny < 0 || nx < 0) return false;
+        int sy = ny / r.div_y, sx = nx / r.div_x;
+        if (sy * r.div_y != ny || sx * r.div_x != nx || sy >= r.SH || sx >= r.SW) return false;
+        offset = ((static_cast<long long>(n) * r.SH + sy) * r.SW + sx) * r.C + c;
+        return true;
+    };
+    int c0 = col % r.C;
+    if (c0 + VEC <= r.C && col + VEC <= s.cols) {  // the chunk stays inside one tap
+        long long off;
+        if (!source(col, off)) return out;
+        const T* p = base + off;
+        if ((reinterpret_cast<uintptr_t>(p) & 15) == 0) return __ldg(reinterpret_cast<const uint4*>(p));
+        T tmp[VEC];
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) tmp[i] = __ldg(p + i);
+        return *reinterpret_cast<uint4*>(tmp);
+    }
+    T tmp[VEC];
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) {
+        long long off;
+        tmp[i] = (col + i < s.cols && source(col + i, off)) ? __ldg(base + off) : T(0);
+    }
+    return *reinterpret_cast<uint4*>(tmp);
+}
+
+// Swizzled position of 16-byte chunk j of row r inside a tile of 128-byte rows (tile base 1024-byte aligned).
+// BASE32 == false: address bits [4,7) are XORed with bits [7,10), the pattern TMA and tcgen05 call SWIZZLE_128B.
+// BASE32 == true : address bits [5,7) are XORed with bits [7,9) (32-byte atoms), for MN-major tf32 operands.
+template <bool BASE32>
+__device__ __forceinline__ uint32_t swz(int r, int j) {
+    if constexpr (BASE32) return static_cast<uint32_t>(r * 128 + ((((j >> 1) ^ (r & 3)) << 5) | ((j & 1) << 4)));
+    else return static_cast<uint32_t>(r * 128 + ((j ^ (r & 7)) << 4));
+}
+
+__device__ __forceinline__ void st_shared_v4(uint32_t addr, uint4 v) {
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+
+// Write one fetched chunk: fp16 as is; fp32 as a tf32 hi image and a tf32 lo image `lo_offset` bytes further.
+template <bool F32>
+__device__ __forceinline__ void store_chunk_smem(uint32_t addr, uint32_t lo_offset, uint4 v) {
+    if constexpr (!F32) {
+        st_shared_v4(addr, v);
+    } else {
+        float f[4] = {__uint_as_float(v.x), __uint_as_float(v.y), __uint_as_float(v.z), __uint_as_float(v.w)};
+        uint4 hi, lo;
+        uint32_t* h = &hi.x;
+        uint32_t* l = &lo.x;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            float fh = ptx::to_tf32(f[i]);
+            h[i] = __float_as_uint(fh);
+            l[i] = __float_as_uint(ptx::to_tf32(f[i] - fh));
+        }
+        st_shared_v4(addr, hi);
+        st_shared_v4(addr + lo_offset, lo);
+    }
+}
+
+// ------------------------------------------------------------------------------------------------ epilogue helpers
+template <typename OutT>
+__device__ __forceinline__ void store_row_chunk(const GemmParams& p, OutT* crow, int col0, const float* acc) {
+    // crow points at C(row, 0); stores acc[0..32) to columns [col0, col0 + 32) clipped to N, adding C first if beta
+    constexpr int VEC = 16 / sizeof(OutT);
+    OutT* dst = crow + col0;
+    bool vec_ok = (col0 + 32 <= p.N) && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0);
+    if (vec_ok) {
+#pragma unroll
+        for (int v = 0; v < 32 / VEC; ++v) {
+            uint4* q = reinterpret_cast<uint4*>(dst) + v;
+            if constexpr (sizeof(OutT) == 4) {
+                float4 o = make_float4(acc[v * 4 + 0], acc[v * 4 + 1], acc[v * 4 + 2], acc[v * 4 + 3]);
+                if (p.beta) {
+                    float4 old = *reinterpret_cast<const float4*>(q);
+                    o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+                }
+                *reinterpret_cast<float4*>(q) = o;
+            } else {
+                uint4 packed;
+                __half2* h = reinterpret_cast<__half2*>(&packed);
+                if (p.beta) {
+                    uint4 oldv = *q;
+                    const __half2* oh = reinterpret_cast<const __half2*>(&oldv);
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        float2 of = __half22float2(oh[i]);
+                        h[i] = __floats2half2_rn(acc[v * 8 + 2 * i] + of.x, acc[v * 8 + 2 * i + 1] + of.y);
+                    }
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) h[i] = __floats2half2_rn(acc[v * 8 + 2 * i], acc[v * 8 + 2 * i + 1]);
+                }
+                *q = packed;
+            }
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+            if (col0 + i < p.N) {
+                float v = acc[i];
+                if constexpr (sizeof(OutT) == 4) {
+                    if (p.beta) v += dst[i];
+                    dst[i] = v;
+                } else {
+                    if (p.beta) v += __half2float(dst[i]);
+                    dst[i] = __float2half_rn(v);
+                }
+            }
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------------ the kernel
+template <class Cfg>
+__global__ void __launch_bounds__(Cfg::THREADS, 1)
+d8k_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmParams p) {
+    using OutT = typename std::conditional<Cfg::F32, float, __half>::type;
+    using InT = OutT;
+    constexpr int BN = Cfg::BN, STAGES = Cfg::STAGES, BK = Cfg::BK, CE = Cfg::CE;
+
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;  // ring of stages, 1024-byte aligned
+    const uint32_t bar_base = smem_base + STAGES * Cfg::STAGE_BYTES;
+    // barrier block: full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2], then the TMEM base address word
+    auto full_bar = [&](int s) { return bar_base + 8u * s; };
+    auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
+    auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + a); };
+    auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + 2 + a); };
+    const uint32_t tmem_slot = bar_base + 8u * (2 * STAGES + 4);
+    static_assert(8 * (2 * Cfg::STAGES + 4) + 8 <= Cfg::BAR_BYTES, "barrier block");
+
+    __shared__ volatile int s_abort;
+    __shared__ int s_last;
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        s_abort = 0;
+        for (int s = 0; s < STAGES; ++s) {
+            ptx::mbar_init(full_bar(s), Cfg::GATHER ? 32 * Cfg::LOADER_WARPS : 1);
+            ptx::mbar_init(empty_bar(s), 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            ptx::mbar_init(tfull_bar(a), 1);
+            ptx::mbar_init(tempty_bar(a), 32 * Cfg::EPI_WARPS);
+        }
+        ptx::fence_mbar_init();
+    }
+    if (warp == Cfg::MMA_WARP) {
+        ptx::tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
+        ptx::tmem_relinquish();
+    }
+    if (!Cfg::GATHER && warp == Cfg::PRODUCER_WARP && lane == 0) {
+        ptx::tma_prefetch_desc(&tmA);
+        ptx::tma_prefetch_desc(&tmB);
+    }
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    ptx::tc_fence_after_sync();
+    uint32_t tmem_base;
+    asm volatile("ld.shared.b32 %0, [%1];" : "=r"(tmem_base) : "r"(tmem_slot) : "memory");
+
+    auto stage_a = [&](int s) { return smem_base + s * Cfg::STAGE_BYTES; };
+    auto stage_b = [&](int s) { return smem_base + s * Cfg::STAGE_BYTES + Cfg::PARTS * Cfg::A_BYTES; };
+
+    if (!Cfg::GATHER && warp == Cfg::PRODUCER_WARP) {
+        // ============================================================================ TMA producer
+        int stage = 0;
+        uint32_t phase = 0;
+        bool ok = true;
+        for (int w = blockIdx.x; ok && w < p.total_work; w += gridDim.x) {
+            WorkItem it = decode_work(p, w, BN);
+            for (int kk = it.kb_begin; kk < it.kb_end; ++kk) {
+                ok = wait_bar(empty_bar(stage), phase ^ 1, &s_abort, p.status, (kRoleProducer << 8) | 1);
+                if (!ok) break;
+                if (lane == 0) {
+                    int b = it.batch, kb = kk;
+                    if (p.kbatch > 1) {
+                        b = kk / p.num_kb;
+                        kb = kk - b * p.num_kb;
+                    }
+                    int k0 = kb * BK;
+                    ptx::mbar_arrive_expect_tx(full_bar(stage), Cfg::STAGE_BYTES);
+                    if constexpr (!Cfg::A_MN) {
+                        ptx::tma_load_3d(stage_a(stage), &tmA, full_bar(stage), k0, it.m0, b % p.a_batch_mod);
+                    } else {
+#pragma unroll
+                        for (int c = 0; c < kBM / CE; ++c)
+                            ptx::tma_load_3d(stage_a(stage) + c * BK * 128, &tmA, full_bar(stage), it.m0 + c * CE, k0, b % p.a_batch_mod);
+                    }
+                    if constexpr (!Cfg::B_MN) {
+                        ptx::tma_load_3d(stage_b(stage), &tmB, full_bar(stage), k0, it.n0, b % p.b_batch_mod);
+                    } else {
+#pragma unroll
+                        for (int c = 0; c < BN / CE; ++c)
+                            ptx::tma_load_3d(stage_b(stage) + c * BK * 128, &tmB, full_bar(stage), it.n0 + c * CE, k0, b % p.b_batch_mod);
+                    }
+                }
+                __syncwarp();
+                if (++stage == STAGES) { stage = 0; phase ^= 1; }
+            }
+        }
+    } else if (warp == Cfg::MMA_WARP) {
+        // ============================================================================ MMA issuer
+        constexpr uint32_t idesc = ptx::make_idesc(Cfg::F32 ? 2u : 0u, Cfg::A_MN, Cfg::B_MN, kBM, BN);
+        // descriptor step per UMMA_K: K-major advances 32 bytes inside the swizzled row; MN-major advances UMMA_K rows
+        constexpr uint32_t a_step = Cfg::A_MN ? Cfg::UMMA_K * 128 : 32;
+        constexpr uint32_t b_step = Cfg::B_MN ? Cfg::UMMA_K * 128 : 32;
+        constexpr uint32_t a_lbo = Cfg::A_MN ? BK * 128 : 16;
+        constexpr uint32_t b_lbo = Cfg::B_MN ? BK * 128 : 16;
+        constexpr uint32_t a_sbo = Cfg::A_B32 ? 512 : 1024, b_sbo = Cfg::B_B32 ? 512 : 1024;
+        constexpr uint32_t a_lay = Cfg::A_B32 ? ptx::kLayoutSw128Base32 : ptx::kLayoutSw128;
+        constexpr uint32_t b_lay = Cfg::B_B32 ? ptx::kLayoutSw128Base32 : ptx::kLayoutSw128;
+        int stage = 0;
+        uint32_t phase = 0;
+        int acc = 0;
+        uint32_t acc_phase = 0;
+        bool ok = true;
+        for (int w = blockIdx.x; ok && w < p.total_work; w += gridDim.x) {
+            WorkItem it = decode_work(p, w, BN);
+            uint32_t d_tmem = 0;
+            for (int kk = it.kb_begin; kk < it.kb_end; ++kk) {
+                const int in_chain = Cfg::CHUNK_KB > 0 ? (kk - it.kb_begin) % (Cfg::CHUNK_KB > 0 ? Cfg::CHUNK_KB : 1) : kk - it.kb_begin;
+                if (in_chain == 0) {  // a new accumulation chain needs a drained accumulator buffer
+                    ok = wait_bar(tempty_bar(acc), acc_phase ^ 1, &s_abort, p.status, (kRoleMma << 8) | 2);
+                    if (!ok) break;
+                    ptx::tc_fence_after_sync();
+                    d_tmem = tmem_base + acc * BN;
+                }
+                ok = wait_bar(full_bar(stage), phase, &s_abort, p.status, (kRoleMma << 8) | 1);
+                if (!ok) break;
+                ptx::tc_fence_after_sync();
+                const bool chain_ends = (kk + 1 == it.kb_end) || (Cfg::CHUNK_KB > 0 && in_chain + 1 == Cfg::CHUNK_KB);
+                if (lane == 0) {
+                    const uint32_t a_hi = stage_a(stage), b_hi = stage_b(stage);
+#pragma unroll
+                    for (int s = 0; s < Cfg::KSTEPS; ++s) {
+                        uint64_t da = ptx::smem_desc(a_hi + s * a_step, a_lbo, a_sbo, a_lay);
+                        uint64_t db = ptx::smem_desc(b_hi + s * b_step, b_lbo, b_sbo, b_lay);
+                        uint32_t accumulate = (in_chain > 0 || s > 0) ? 1u : 0u;
+                        if constexpr (Cfg::F32) {
+                            uint64_t da_lo = ptx::smem_desc(a_hi + Cfg::A_BYTES + s * a_step, a_lbo, a_sbo, a_lay);
+                            uint64_t db_lo = ptx::smem_desc(b_hi + Cfg::B_BYTES + s * b_step, b_lbo, b_sbo, b_lay);
+                            ptx::mma_tf32(d_tmem, da_lo, db, idesc, accumulate);  // small terms first
+                            ptx::mma_tf32(d_tmem, da, db_lo, idesc, 1u);
+                            ptx::mma_tf32(d_tmem, da, db, idesc, 1u);
+                        } else {
+                            ptx::mma_f16(d_tmem, da, db, idesc, accumulate);
+                        }
+                    }
+                    ptx::tc_commit(empty_bar(stage));  // the stage may be refilled once these MMAs have read it
+                    if (chain_ends) ptx::tc_commit(tfull_bar(acc));
+                }
+                __syncwarp();
+                if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                if (chain_ends) {
+                    if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+                }
+            }
+        }
+    } else if (warp < Cfg::EPI_WARPS) {
+        // ============================================================================ epilogue (TMEM -> C)
+        const int quarter = warp;  // warp w may read TMEM lanes [32 (w % 4), +32)
+        const int row_in_tile = quarter * 32 + lane;
+        int acc = 0;
+        uint32_t acc_phase = 0;
+        bool ok = true;
+        for (int w = blockIdx.x; ok && w < p.total_work; w += gridDim.x) {
+            WorkItem it = decode_work(p, w, BN);
+            const int row = it.m0 + row_in_tile;
+            OutT* crow = reinterpret_cast<OutT*>(p.C) + static_cast<long long>(it.batch) * p.c_batch_stride +
+                         static_cast<long long>(row) * p.ldc;
+            float* part = p.ws + (static_cast<size_t>(w) * kBM + row_in_tile) * BN;
+            if constexpr (Cfg::CHUNK_KB == 0) {
+                ok = wait_bar(tfull_bar(acc), acc_phase, &s_abort, p.status, (kRoleEpilogue << 8) | 3);
+                if (!ok) break;
+                ptx::tc_fence_after_sync();
+                const uint32_t taddr = tmem_base + acc * BN + (static_cast<uint32_t>(quarter * 32) << 16);
+#pragma unroll 1
+                for (int c = 0; c < BN / 32; ++c) {
+                    uint32_t r[32];
+                    __syncwarp();
+                    ptx::tmem_ld_32x32(taddr + c * 32, r);
+                    ptx::tmem_ld_wait();
+                    if (p.splits == 1) {
+                        if (row < p.M && it.n0 + c * 32 < p.N) {
+                            float accv[32];
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) accv[i] = __uint_as_float(r[i]);
+                            store_row_chunk<OutT>(p, crow, it.n0 + c * 32, accv);
+                        }
+                    } else {
+#pragma unroll
+                        for (int v = 0; v < 8; ++v)
+                            __stcg(reinterpret_cast<uint4*>(part + c * 32) + v, make_uint4(r[4 * v], r[4 * v + 1], r[4 * v + 2], r[4 * v + 3]));
+                    }
+                }
+                ptx::tc_fence_before_sync();
+                ptx::mbar_arrive(tempty_bar(acc));  // accumulator buffer free for the tile after next
+                if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+            } else {
+                // one accumulation chain per CHUNK_KB k-blocks: add each finished chain into registers (round to nearest)
+                float accv[BN];
+#pragma unroll
+                for (int i = 0; i < BN; ++i) accv[i] = 0.f;
+                const int chains = (it.kb_end - it.kb_begin + Cfg::CHUNK_KB - 1) / Cfg::CHUNK_KB;
+                for (int ch = 0; ch < chains; ++ch) {
+                    ok = wait_bar(tfull_bar(acc), acc_phase, &s_abort, p.status, (kRoleEpilogue << 8) | 3);
+                    if (!ok) break;
+                    ptx::tc_fence_after_sync();
+                    const uint32_t taddr = tmem_base + acc * BN + (static_cast<uint32_t>(quarter * 32) << 16);
+#pragma unroll
+                    for (int c = 0; c < BN / 32; ++c) {
+                        uint32_t r[32];
+                        __syncwarp();
+                        ptx::tmem_ld_32x32(taddr + c * 32, r);
+                        ptx::tmem_ld_wait();
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) accv[c * 32 + i] += __uint_as_float(r[i]);
+                    }
+                    ptx::tc_fence_before_sync();
+                    ptx::mbar_arrive(tempty_bar(acc));
+                    if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+                }
+                if (!ok) break;
+#pragma unroll
+                for (int c = 0; c < BN / 32; ++c) {
+                    if (p.splits == 1) {
+                        if (row < p.M && it.n0 + c * 32 < p.N) store_row_chunk<OutT>(p, crow, it.n0 + c * 32, &accv[c * 32]);
+                    } else {
+#pragma unroll
+                        for (int v = 0; v < 8; ++v)
+                            __stcg(reinterpret_cast<float4*>(part + c * 32) + v,
+                                   make_float4(accv[c * 32 + 4 * v], accv[c * 32 + 4 * v + 1], accv[c * 32 + 4 * v + 2], accv[c * 32 + 4 * v + 3]));
+                    }
+                }
+            }
+
+            if (p.splits > 1) {
+                __threadfence();
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (threadIdx.x == 0) {
+                    int ticket = atomicAdd(p.counters + it.tile, 1);
+                    s_last = (ticket == p.splits - 1);
+                    if (s_last) p.counters[it.tile] = 0;
+                }
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (s_last) {
+                    __threadfence();
+                    if (row < p.M) {
+                        const float* first = p.ws + (static_cast<size_t>(it.tile) * p.splits * kBM + row_in_tile) * BN;
+#pragma unroll 1
+                        for (int c = 0; c < BN / 32; ++c) {
+                            if (it.n0 + c * 32 >= p.N) break;
+                            float accv[32];
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) accv[i] = 0.f;
+                            for (int s = 0; s < p.splits; ++s) {
+                                const float4* src = reinterpret_cast<const float4*>(first + static_cast<size_t>(s) * kBM * BN + c * 32);
+#pragma unroll
+                                for (int v = 0; v < 8; ++v) {
+                                    float4 t = __ldcg(src + v);
+                                    accv[4 * v] += t.x; accv[4 * v + 1] += t.y; accv[4 * v + 2] += t.z; accv[4 * v + 3] += t.w;
+                                }
+                            }
+                            store_row_chunk<OutT>(p, crow, it.n0 + c * 32, accv);
+                        }
+                    }
+                }
+            }
+        }
+    } else if (Cfg::GATHER && warp >= Cfg::LOADER_WARP0) {
+        // ============================================================================ gather loaders
+        const int lw = warp - Cfg::LOADER_WARP0;
+        const int sub = lane >> 3;  // row inside a group of four
+        const int j = lane & 7;     // 16-byte chunk of the row
+        constexpr int A_ITERS = kBM / 16, B_ITERS = BN / 16;
+        int stage = 0;
+        uint32_t phase = 0;
+        bool ok = true;
+        for (int w = blockIdx.x; ok && w < p.total_work; w += gridDim.x) {
+            WorkItem it = decode_work(p, w, BN);
+            for (int kk = it.kb_begin; kk < it.kb_end; ++kk) {
+                ok = wait_bar(empty_bar(stage), phase ^ 1, &s_abort, p.status, (kRoleLoader << 8) | 1);
+                if (!ok) break;
+                int b = it.batch, kb = kk;
+                if (p.kbatch > 1) {
+                    b = kk / p.num_kb;
+                    kb = kk - b * p.num_kb;
+                }
+                const int k0 = kb * BK;
+                uint4 va[A_ITERS], vb[B_ITERS];
+#pragma unroll
+                for (int i = 0; i < A_ITERS; ++i) {
+                    int r = (i * 4 + lw) * 4 + sub;
+                    int g, col;
+                    if constexpr (!Cfg::A_MN) { g = it.m0 + r; col = k0 + j * Cfg::VEC; }
+                    else { g = k0 + (r % BK); col = it.m0 + (r / BK) * CE + j * Cfg::VEC; }
+                    va[i] = fetch16<InT, Cfg::VEC>(p.a, g, col, b);
+                }
+#pragma unroll
+                for (int i = 0; i < B_ITERS; ++i) {
+                    int r = (i * 4 + lw) * 4 + sub;
+                    int g, col;
+                    if constexpr (!Cfg::B_MN) { g = it.n0 + r; col = k0 + j * Cfg::VEC; }
+                    else { g = k0 + (r % BK); col = it.n0 + (r / BK) * CE + j * Cfg::VEC; }
+                    vb[i] = fetch16<InT, Cfg::VEC>(p.b, g, col, b);
+                }
+#pragma unroll
+                for (int i = 0; i < A_ITERS; ++i) {
+                    int r = (i * 4 + lw) * 4 + sub;
+                    store_chunk_smem<Cfg::F32>(stage_a(stage) + swz<Cfg::A_B32>(r, j), Cfg::A_BYTES, va[i]);
+                }
+#pragma unroll
+                for (int i = 0; i < B_ITERS; ++i) {
+                    int r = (i * 4 + lw) * 4 + sub;
+                    store_chunk_smem<Cfg::F32>(stage_b(stage) + swz<Cfg::B_B32>(r, j), Cfg::B_BYTES, vb[i]);
+                }
+                ptx::fence_proxy_async_smem();
+                ptx::mbar_arrive(full_bar(stage));
+                if (++stage == STAGES) { stage = 0; phase ^= 1; }
+            }
+        }
+    }
+
+    // ================================================================================ teardown
+    if (s_abort) {
+        // give copies and MMAs still in flight time to land before shared and tensor memory are released
+        for (int i = 0; i < 200; ++i) __nanosleep(1000);
+    }
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    if (warp == Cfg::MMA_WARP) {
+        ptx::tc_fence_after_sync();
+        ptx::tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+    }
+}
+
+}  // namespace d8k

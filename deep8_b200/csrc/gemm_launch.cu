@@ -1,0 +1,191 @@
+// Host side of the contraction kernel: picks the tile configuration and the split, encodes TMA tensor maps, launches.
+#include <cstdlib>
+#include <cstring>
+#include <mutex>
+#include <sstream>
+
+#include "gemm_host.h"
+
+namespace d8k {
+
+namespace {
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* sym = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(sym);
+    });
+    return fn;
+}
+
+int env_int(const char* name, int fallback) {
+    const char* v = std::getenv(name);
+    return v ? std::atoi(v) : fallback;
+}
+
+bool tma_ok(const HostOperand& o, int esize) {
+    if (o.is_virtual || o.rmod > 0) return false;
+    if (reinterpret_cast<uintptr_t>(o.ptr) & 15) return false;
+    if ((o.ld * esize) % 16 != 0) return false;
+    if (o.batch_count > 1 && (o.batch_stride * esize) % 16 != 0) return false;
+    return true;
+}
+
+// 3-D map {inner, rows, batch} over a row-major fp16 matrix stack, 128-byte swizzle, zero fill outside.
+bool make_map(CUtensorMap* map, const HostOperand& o, long long inner, long long rows, int box_rows) {
+    EncodeTiledFn enc = encode_tiled();
+    if (!enc) return false;
+    cuuint64_t dims[3] = {static_cast<cuuint64_t>(inner), static_cast<cuuint64_t>(rows), static_cast<cuuint64_t>(o.batch_count)};
+    long long bstride = o.batch_count > 1 ? o.batch_stride : rows * o.ld;
+    cuuint64_t strides[2] = {static_cast<cuuint64_t>(o.ld * 2), static_cast<cuuint64_t>(bstride * 2)};
+    cuuint32_t box[3] = {64u, static_cast<cuuint32_t>(box_rows), 1u};
+    cuuint32_t estr[3] = {1u, 1u, 1u};
+    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<void*>(o.ptr), dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS;
+}
+
+GatherSrc to_gather(const HostOperand& o, int rows, int cols) {
+    GatherSrc s;
+    std::memset(&s, 0, sizeof(s));
+    s.base = o.ptr;
+    s.kind = o.is_virtual ? 1 : 0;
+    s.rows = rows;
+    s.cols = cols;
+    s.rmod = o.rmod;
+    s.ld = o.ld;
+    s.ld2 = o.ld2;
+    s.batch_stride = o.batch_stride;
+    s.batch_count = o.batch_count > 0 ? o.batch_count : 1;
+    s.cr = o.cr;
+    return s;
+}
+
+struct Plan {
+    bool f32, tma;
+    int bn, bk, tiles_m, tiles_n, tiles, num_kb, total_kb, splits, kb_per_split;
+    size_t scratch;
+};
+
+Plan make_plan(const Ctx* ctx, const GemmProblem& g, size_t scratch_limit) {
+    Plan pl;
+    pl.f32 = g.dtype == 1;
+    int esize = pl.f32 ? 4 : 2;
+    pl.tma = !pl.f32 && tma_ok(g.a, esize) && tma_ok(g.b, esize) && encode_tiled() != nullptr && !env_int("D8K_FORCE_GATHER", 0);
+    if (pl.tma) pl.bn = g.N > 128 ? 256 : 128;
+    else pl.bn = g.N > 64 ? 128 : 64;
+    int forced_bn = env_int("D8K_BN", 0);
+    if (forced_bn == 64 && !pl.tma) pl.bn = 64;
+    if (forced_bn == 128) pl.bn = 128;
+    if (forced_bn == 256 && pl.tma) pl.bn = 256;
+    pl.bk = 128 / esize;
+    pl.tiles_m = (g.M + kBM - 1) / kBM;
+    pl.tiles_n = (g.N + pl.bn - 1) / pl.bn;
+    pl.tiles = g.batch * pl.tiles_m * pl.tiles_n;
+    pl.num_kb = (g.K + pl.bk - 1) / pl.bk;
+    pl.total_kb = pl.num_kb * g.kbatch;
+    // split the contraction when the output alone cannot occupy half of the SMs
+    int splits = 1;
+    if (pl.tiles * 2 <= ctx->num_sms && pl.total_kb >= 8 && pl.tiles <= kMaxCounters) {
+        splits = ctx->num_sms / pl.tiles;
+        if (splits > pl.total_kb / 4) splits = pl.total_kb / 4;
+    }
+    int forced = env_int("D8K_SPLITS", 0);
+    if (forced > 0 && pl.tiles <= kMaxCounters) splits = forced < pl.total_kb ? forced : pl.total_kb;
+    size_t per_split = static_cast<size_t>(pl.tiles) * kBM * pl.bn * sizeof(float);
+    if (splits > 1 && per_split * splits > scratch_limit) splits = static_cast<int>(scratch_limit / per_split);
+    if (splits < 1) splits = 1;
+    pl.kb_per_split = (pl.total_kb + splits - 1) / splits;
+    pl.splits = (pl.total_kb + pl.kb_per_split - 1) / pl.kb_per_split;
+    pl.scratch = pl.splits > 1 ? per_split * pl.splits : 0;
+    return pl;
+}
+
+}  // namespace
+
+size_t gemm_scratch_need(const Ctx* ctx, const GemmProblem& g) {
+    if (g.M <= 0 || g.N <= 0 || g.K <= 0 || g.batch <= 0) return 0;
+    return make_plan(ctx, g, ~static_cast<size_t>(0)).scratch;
+}
+
+int run_gemm(Ctx* ctx, const GemmProblem& g) {
+    if (g.M < 0 || g.N < 0 || g.K < 0 || g.batch < 0 || g.kbatch < 1) return fail(1, "gemm: negative extent");
+    if (g.M == 0 || g.N == 0 || g.batch == 0) return 0;
+    if (!g.C || (g.K > 0 && (!g.a.ptr || !g.b.ptr))) return fail(1, "gemm: null pointer");
+    if (g.dtype != 0 && g.dtype != 1) return fail(1, "gemm: dtype must be D8K_F16 or D8K_F32");
+    if (g.beta != 0 && g.beta != 1) return fail(1, "gemm: beta must be 0 or 1");
+    const int esize = g.dtype == 1 ? 4 : 2;
+    if (g.K == 0) {  // an empty contraction is a zero matrix
+        if (g.beta == 0) {
+            for (int b = 0; b < g.batch; ++b) {
+                char* c = static_cast<char*>(g.C) + static_cast<size_t>(b) * g.c_batch_stride * esize;
+                cudaError_t e = cudaMemset2DAsync(c, g.ldc * esize, 0, static_cast<size_t>(g.N) * esize, g.M, ctx->stream);
+                if (e != cudaSuccess) return fail(2, std::string("gemm: cudaMemset2DAsync: ") + cudaGetErrorString(e));
+            }
+        }
+        return 0;
+    }
+
+    const bool own_scratch = g.ws == nullptr;
+    float* scratch = own_scratch ? ctx->scratch : static_cast<float*>(g.ws);
+    size_t scratch_limit = own_scratch ? ctx->scratch_bytes : g.ws_bytes;
+    if (reinterpret_cast<uintptr_t>(scratch) & 15) return fail(1, "gemm: scratch memory must be 16-byte aligned");
+    Plan pl = make_plan(ctx, g, scratch_limit);
+
+    GemmParams p;
+    std::memset(&p, 0, sizeof(p));
+    p.M = g.M; p.N = g.N; p.K = g.K;
+    p.batch = g.batch;
+    p.kbatch = g.kbatch;
+    p.num_kb = pl.num_kb;
+    p.splits = pl.splits;
+    p.kb_per_split = pl.kb_per_split;
+    p.tiles_m = pl.tiles_m;
+    p.tiles_n = pl.tiles_n;
+    p.raster_group = env_int("D8K_RASTER", 16);
+    if (p.raster_group < 1) p.raster_group = 1;
+    p.total_work = pl.tiles * pl.splits;
+    p.beta = g.beta;
+    p.C = g.C;
+    p.ldc = g.ldc;
+    p.c_batch_stride = g.c_batch_stride;
+    p.ws = scratch;
+    p.counters = ctx->counters;
+    p.status = ctx->status;
+    p.a_batch_mod = g.a.batch_count > 0 ? g.a.batch_count : 1;
+    p.b_batch_mod = g.b.batch_count > 0 ? g.b.batch_count : 1;
+
+    CUtensorMap ta, tb;
+    std::memset(&ta, 0, sizeof(ta));
+    std::memset(&tb, 0, sizeof(tb));
+    GemmLaunchFn fn = nullptr;
+    if (pl.tma) {
+        // K-major: {K, rows}; MN-major: {rows(M or N), K}
+        bool oka = g.a.mn ? make_map(&ta, g.a, g.M, g.K, 64) : make_map(&ta, g.a, g.K, g.M, kBM);
+        bool okb = g.b.mn ? make_map(&tb, g.b, g.N, g.K, 64) : make_map(&tb, g.b, g.K, g.N, pl.bn);
+        if (!oka || !okb) return fail(2, "gemm: cuTensorMapEncodeTiled failed");
+        fn = lookup_f16_tma(g.a.mn, g.b.mn, pl.bn);
+    } else {
+        p.a = g.a.mn ? to_gather(g.a, g.K, g.M) : to_gather(g.a, g.M, g.K);
+        p.b = g.b.mn ? to_gather(g.b, g.K, g.N) : to_gather(g.b, g.N, g.K);
+        fn = pl.f32 ? lookup_f32_gather(g.a.mn, g.b.mn, pl.bn) : lookup_f16_gather(g.a.mn, g.b.mn, pl.bn);
+    }
+    if (!fn) return fail(2, "gemm: no kernel for this configuration");
+    int grid = p.total_work < ctx->num_sms ? p.total_work : ctx->num_sms;
+    cudaError_t e = fn(grid, ctx->stream, ta, tb, p);
+    if (e != cudaSuccess) return fail(2, std::string("gemm: launch failed: ") + cudaGetErrorString(e));
+    count_launch();
+    return 0;
+}
+
+}  // namespace d8k

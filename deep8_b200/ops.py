@@ -1,0 +1,220 @@
+"""Operator front-end over the C ABI, with torch tensors as device buffers.
+
+Mirrors the reference's operator interface for the path: forward returns a new tensor, gradient calls ACCUMULATE into
+the gradient tensor passed in (deep8/src/nodes/MatrixMultiply.cpp:36-52, Conv2d.cpp:74-152, DeConv2d.cpp:63-126).
+Layouts are the reference's: matrices [batch, rows, cols]; images [batch, height, width, channel]; filters
+[outChannel, filterHeight, filterWidth, inChannel].
+"""
+import ctypes
+
+import torch
+
+from . import _lib
+from ._lib import F16, F32, check
+
+
+def _dtype_code(t):
+    if t.dtype == torch.float16:
+        return F16
+    if t.dtype == torch.float32:
+        return F32
+    raise TypeError("type %s is not support" % t.dtype)  # the reference's message for an unsupported element type
+
+
+def _p(t):
+    return ctypes.c_void_p(t.data_ptr()) if t is not None else None
+
+
+def _same(*ts):
+    d0 = ts[0]
+    for t in ts:
+        if t.device != d0.device:
+            raise ValueError("the device type must be same")
+        if t.dtype != d0.dtype:
+            raise ValueError("the data type must be same")
+        if not t.is_contiguous():
+            raise ValueError("tensors must be contiguous")
+    return _dtype_code(d0)
+
+
+class Context:
+    """One d8k context: a device, a stream and the split-K scratch memory.  Not for concurrent use."""
+
+    def __init__(self, device=0, scratch_bytes=0):
+        self.lib = _lib.load()
+        self.device = device
+        h = ctypes.c_void_p()
+        check(self.lib.d8k_ctx_create(device, scratch_bytes, ctypes.byref(h)))
+        self.h = h
+        self.num_sms = self.lib.d8k_ctx_num_sms(h)
+
+    def close(self):
+        if getattr(self, "h", None):
+            self.lib.d8k_ctx_destroy(self.h)
+            self.h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def use_stream(self, stream):
+        """Enqueue on a torch.cuda.Stream (or None for the legacy default stream)."""
+        check(self.lib.d8k_ctx_set_stream(self.h, ctypes.c_void_p(stream.cuda_stream if stream is not None else 0)))
+
+    def status(self):
+        s = ctypes.c_int(0)
+        check(self.lib.d8k_ctx_status(self.h, ctypes.byref(s)))
+        return s.value
+
+    def launch_count(self):
+        return int(self.lib.d8k_launch_count())
+
+    # ------------------------------------------------------------------------------------------------ gemm
+    def gemm(self, A, B, C, transA=False, transB=False, beta=0, reduce_batch=False):
+        """C[b] (+)= op(A[b % batchA]) op(B[b % batchB]); A, B, C are [batch, rows, cols] tensors."""
+        dt = _same(A, B, C)
+        batchA, ar, ac = A.shape
+        batchB, br, bc = B.shape
+        M, K = (ac, ar) if transA else (ar, ac)
+        K2, N = (bc, br) if transB else (br, bc)
+        if K != K2:
+            raise ValueError("the shape is error")
+        batch = max(batchA, batchB)
+        if reduce_batch:
+            assert C.shape == (1, M, N)
+        else:
+            assert C.shape == (batch, M, N)
+        check(self.lib.d8k_gemm(self.h, dt, int(transA), int(transB), M, N, K, _p(A), ac, batchA, ar * ac, _p(B), bc, batchB, br * bc,
+                                _p(C), N, M * N, batch, int(beta), int(reduce_batch)))
+        return C
+
+    # ------------------------------------------------------------------------------------------------ MatrixMultiply
+    @staticmethod
+    def _mm_dims(x, y):
+        xb, xr, xc = x.shape
+        yb, yr, yc = y.shape
+        if yr != xc or (xb != yb and xb != 1 and yb != 1):
+            raise ValueError("the shape is error")
+        return xb, xr, xc, yb, yc
+
+    def matmul_forward(self, x, y, out=None):
+        dt = _same(x, y)
+        xb, xr, xc, yb, yc = self._mm_dims(x, y)
+        z = out if out is not None else torch.empty((max(xb, yb), xr, yc), dtype=x.dtype, device=x.device)
+        check(self.lib.d8k_matmul_forward(self.h, dt, _p(x), xb, xr, xc, _p(y), yb, yc, _p(z)))
+        return z
+
+    def matmul_grad_x(self, x, dx, y, dz):
+        dt = _same(x, dx, y, dz)
+        xb, xr, xc, yb, yc = self._mm_dims(x, y)
+        if dx.shape != x.shape or tuple(dz.shape) != (max(xb, yb), xr, yc):
+            raise ValueError("the shape is error")
+        check(self.lib.d8k_matmul_grad_x(self.h, dt, _p(dx), xb, xr, xc, _p(y), yb, yc, _p(dz)))
+        return dx
+
+    def matmul_grad_y(self, x, y, dy, dz):
+        dt = _same(x, y, dy, dz)
+        xb, xr, xc, yb, yc = self._mm_dims(x, y)
+        if dy.shape != y.shape or tuple(dz.shape) != (max(xb, yb), xr, yc):
+            raise ValueError("the shape is error")
+        check(self.lib.d8k_matmul_grad_y(self.h, dt, _p(x), xb, xr, xc, _p(dy), yb, yc, _p(dz)))
+        return dy
+
+    # ------------------------------------------------------------------------------------------------ Conv2d
+    def conv2d_out_shape(self, x, w, covered, stride, dilation):
+        b, ih, iw, ic = x.shape
+        oc, fh, fw, wc = w.shape
+        if wc != ic:
+            raise ValueError("the shape is error")
+        oh = self.lib.d8k_conv2d_out_dim(ih, fh, stride[0], dilation[0], int(covered))
+        ow = self.lib.d8k_conv2d_out_dim(iw, fw, stride[1], dilation[1], int(covered))
+        return (b, oh, ow, oc)
+
+    def conv2d_forward(self, x, w, covered=False, stride=(1, 1), dilation=(1, 1), out=None):
+        dt = _same(x, w)
+        b, oh, ow, oc = self.conv2d_out_shape(x, w, covered, stride, dilation)
+        z = out if out is not None else torch.empty((b, oh, ow, oc), dtype=x.dtype, device=x.device)
+        _, ih, iw, ic = x.shape
+        _, fh, fw, _ = w.shape
+        check(self.lib.d8k_conv2d_forward(self.h, dt, _p(x), b, ih, iw, ic, _p(w), oc, fh, fw, _p(z), oh, ow, stride[0], stride[1],
+                                          dilation[0], dilation[1], None, 0))
+        return z
+
+    def conv2d_grad_x(self, x, dx, w, dz, covered=False, stride=(1, 1), dilation=(1, 1)):
+        dt = _same(x, dx, w, dz)
+        b, oh, ow, oc = self.conv2d_out_shape(x, w, covered, stride, dilation)
+        if tuple(dz.shape) != (b, oh, ow, oc) or dx.shape != x.shape:
+            raise ValueError("the shape is error")
+        _, ih, iw, ic = x.shape
+        _, fh, fw, _ = w.shape
+        check(self.lib.d8k_conv2d_grad_x(self.h, dt, _p(dx), b, ih, iw, ic, _p(w), oc, fh, fw, _p(dz), oh, ow, stride[0], stride[1],
+                                         dilation[0], dilation[1], None, 0))
+        return dx
+
+    def conv2d_grad_y(self, x, w, dw, dz, covered=False, stride=(1, 1), dilation=(1, 1)):
+        dt = _same(x, w, dw, dz)
+        b, oh, ow, oc = self.conv2d_out_shape(x, w, covered, stride, dilation)
+        if tuple(dz.shape) != (b, oh, ow, oc) or dw.shape != w.shape:
+            raise ValueError("the shape is error")
+        _, ih, iw, ic = x.shape
+        _, fh, fw, _ = w.shape
+        check(self.lib.d8k_conv2d_grad_y(self.h, dt, _p(x), b, ih, iw, ic, _p(dw), oc, fh, fw, _p(dz), oh, ow, stride[0], stride[1],
+                                         dilation[0], dilation[1], None, 0))
+        return dw
+
+    # ------------------------------------------------------------------------------------------------ DeConv2d
+    def deconv2d_out_shape(self, x, w, covered, stride):
+        b, ih, iw, ic = x.shape
+        oc, fh, fw, wc = w.shape
+        if wc != ic:
+            raise ValueError("the shape is error")
+        oh = self.lib.d8k_deconv2d_out_dim(ih, fh, stride[0], int(covered))
+        ow = self.lib.d8k_deconv2d_out_dim(iw, fw, stride[1], int(covered))
+        return (b, oh, ow, oc)
+
+    def deconv2d_forward(self, x, w, covered=False, stride=(1, 1), out=None):
+        dt = _same(x, w)
+        b, oh, ow, oc = self.deconv2d_out_shape(x, w, covered, stride)
+        z = out if out is not None else torch.empty((b, oh, ow, oc), dtype=x.dtype, device=x.device)
+        _, ih, iw, ic = x.shape
+        _, fh, fw, _ = w.shape
+        check(self.lib.d8k_deconv2d_forward(self.h, dt, _p(x), b, ih, iw, ic, _p(w), oc, fh, fw, _p(z), oh, ow, stride[0], stride[1], None, 0))
+        return z
+
+    def deconv2d_grad_x(self, x, dx, w, dz, covered=False, stride=(1, 1)):
+        dt = _same(x, dx, w, dz)
+        b, oh, ow, oc = self.deconv2d_out_shape(x, w, covered, stride)
+        if tuple(dz.shape) != (b, oh, ow, oc) or dx.shape != x.shape:
+            raise ValueError("the shape is error")
+        _, ih, iw, ic = x.shape
+        _, fh, fw, _ = w.shape
+        check(self.lib.d8k_deconv2d_grad_x(self.h, dt, _p(dx), b, ih, iw, ic, _p(w), oc, fh, fw, _p(dz), oh, ow, stride[0], stride[1], None, 0))
+        return dx
+
+    def deconv2d_grad_y(self, x, w, dw, dz, covered=False, stride=(1, 1)):
+        dt = _same(x, w, dw, dz)
+        b, oh, ow, oc = self.deconv2d_out_shape(x, w, covered, stride)
+        if tuple(dz.shape) != (b, oh, ow, oc) or dw.shape != w.shape:
+            raise ValueError("the shape is error")
+        _, ih, iw, ic = x.shape
+        _, fh, fw, _ = w.shape
+        check(self.lib.d8k_deconv2d_grad_y(self.h, dt, _p(x), b, ih, iw, ic, _p(dw), oc, fh, fw, _p(dz), oh, ow, stride[0], stride[1], None, 0))
+        return dw
+
+    # ------------------------------------------------------------------------------------------------ neighbours
+    def relu_forward(self, x, out=None):
+        dt = _same(x)
+        y = out if out is not None else torch.empty_like(x)
+        check(self.lib.d8k_relu_forward(self.h, dt, _p(x), _p(y), x.numel()))
+        return y
+
+    def relu_backward(self, x, dx, dy):
+        dt = _same(x, dx, dy)
+        check(self.lib.d8k_relu_backward(self.h, dt, _p(x), _p(dx), _p(dy), x.numel()))
+        return dx
+
+    def zero(self, t):
+        check(self.lib.d8k_zero(self.h, _p(t), t.numel() * t.element_size()))
+        return t

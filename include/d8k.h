@@ -1,0 +1,124 @@
+/* deep8_b200 C ABI: the B200 (sm_100a) kernels behind Deep8's dense-contraction operators.
+ *
+ * Every entry point below stands where one GPU function of the reference stands; the reference's `Tensor` arguments
+ * are flattened to raw device pointers and dims (row-major, batch outermost; images [batch, height, width, channel],
+ * filters [outChannel, filterHeight, filterWidth, inChannel]).  Paths in the citations are relative to the
+ * reference project.
+ *
+ * Conventions (the reference's, deep8/include/math/{MatrixMultiply,Conv2d,DeConv2d}.h):
+ *   - forward overwrites z; every gradient entry point ACCUMULATES (+=) into dx / dy;
+ *   - dtype is D8K_F16 (fp16 storage, fp32 accumulation) or D8K_F32 (3xTF32 split precision, fp32 accumulation);
+ *   - all pointers are device pointers on the context's device; work is enqueued on the context's stream and the
+ *     call returns without waiting;
+ *   - return value 0 on success; otherwise an error code, with the text available from d8k_last_error()
+ *     (D8K_ERR_ARGUMENT maps to the reference's std::invalid_argument, the others to std::runtime_error).
+ * A context is to be used by one host thread / one stream at a time (it owns the split-K scratch memory), like the
+ * cuBLAS handle inside the reference's GPUDevice (deep8/include/model/GPUDevice.h:12-70).
+ */
+#ifndef D8K_H
+#define D8K_H
+
+#include <stddef.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define D8K_F16 0
+#define D8K_F32 1
+
+#define D8K_OK 0
+#define D8K_ERR_ARGUMENT 1 /* bad shape, null pointer, unsupported dtype */
+#define D8K_ERR_CUDA 2     /* a CUDA runtime or driver call failed */
+#define D8K_ERR_KERNEL 3   /* a kernel gave up on a bounded wait; see d8k_ctx_status */
+
+#if defined(__GNUC__)
+#define D8K_API __attribute__((visibility("default")))
+#else
+#define D8K_API
+#endif
+
+typedef struct d8k_ctx d8k_ctx;
+
+/* Replaces the GPU half of GPUDevice's constructor (deep8/src/model/GPUDevice.cu:10-65): selects `device`, allocates
+ * the split-K scratch memory (scratch_bytes, 0 = default 64 MiB) and the kernel status word. */
+D8K_API int d8k_ctx_create(int device, size_t scratch_bytes, d8k_ctx** out);
+D8K_API int d8k_ctx_destroy(d8k_ctx* ctx);
+/* Stream the kernels are enqueued on (a cudaStream_t); the default is the legacy default stream, as in the reference. */
+D8K_API int d8k_ctx_set_stream(d8k_ctx* ctx, void* stream);
+/* Waits for the stream, then reports the device status word: 0, or (role << 8 | barrier) of the first wait that
+ * expired inside a kernel.  Returns D8K_ERR_KERNEL when it is non-zero (and clears it). */
+D8K_API int d8k_ctx_status(d8k_ctx* ctx, int* status);
+D8K_API int d8k_ctx_num_sms(const d8k_ctx* ctx);
+D8K_API const char* d8k_last_error(void);
+
+/* Number of kernels this library has launched from the calling process since it was loaded. */
+D8K_API unsigned long long d8k_launch_count(void);
+
+/* General contraction, row-major:  C[b] (+)= op(A[b % batchA]) * op(B[b % batchB]),  b < batch.
+ *   transA == 0: A[b] is M x K with pitch lda;  transA != 0: A[b] is K x M with pitch lda (its transpose is used)
+ *   transB == 0: B[b] is K x N with pitch ldb;  transB != 0: B[b] is N x K with pitch ldb
+ *   beta is 0 (overwrite C) or 1 (accumulate into C)
+ *   reduce_batch != 0: one output C[0] (+)= sum over b < batch of op(A[b]) * op(B[b])  (the batch joins the contraction)
+ * This is the cublas{S,H}gemm call of the reference (deep8/src/math/MatrixMultiply.cu:31-56, 205-231, 393-419) with the
+ * host loop over the batch folded into one launch. */
+D8K_API int d8k_gemm(d8k_ctx* ctx, int dtype, int transA, int transB, int M, int N, int K,
+             const void* A, long long lda, int batchA, long long strideA,
+             const void* B, long long ldb, int batchB, long long strideB,
+             void* C, long long ldc, long long strideC, int batch, int beta, int reduce_batch);
+
+/* MatrixMultiplyGPU (deep8/src/math/MatrixMultiply.cu:139-176): z[b] = x[b % xb] * y[b % yb];
+ * x is xb matrices xr x xc, y is yb matrices xc x yc, z is max(xb, yb) matrices xr x yc; xb, yb equal or 1. */
+D8K_API int d8k_matmul_forward(d8k_ctx* ctx, int dtype, const void* x, int xb, int xr, int xc, const void* y, int yb, int yc, void* z);
+/* MatrixMultiplyGradXGPU (MatrixMultiply.cu:320-363): dx[b % xb] += dz[b] * y[b % yb]^T (summed over b when xb == 1). */
+D8K_API int d8k_matmul_grad_x(d8k_ctx* ctx, int dtype, void* dx, int xb, int xr, int xc, const void* y, int yb, int yc, const void* dz);
+/* MatrixMultiplyGradYGPU (MatrixMultiply.cu:508-551): dy[b % yb] += x[b % xb]^T * dz[b] (summed over b when yb == 1). */
+D8K_API int d8k_matmul_grad_y(d8k_ctx* ctx, int dtype, const void* x, int xb, int xr, int xc, void* dy, int yb, int yc, const void* dz);
+
+/* Conv2d shape helpers: output extent (deep8/src/nodes/Conv2d.cpp:47-63) and DeConv2d's (deep8/src/nodes/DeConv2d.cpp:36-52). */
+D8K_API int d8k_conv2d_out_dim(int in, int filter, int stride, int dilation, int covered);
+D8K_API int d8k_deconv2d_out_dim(int in, int filter, int stride, int covered);
+
+/* Conv2dInterimSize / GradXInterimSize / GradYInterimSize and the DeConv2d ones (deep8/src/math/Conv2d.cpp:6-44, 98-137,
+ * 195-234; DeConv2d.cpp:6-41, 84-120, 164-200).  The reference returns the byte size of its im2col column buffer; these
+ * kernels build the tiles in shared memory, so the answer is 0 unless the call will run split-K and the caller wants to
+ * supply the scratch itself (`interim`); with interim == NULL the context's scratch is used.
+ * which: 0 forward, 1 gradient of x, 2 gradient of the filter. */
+D8K_API size_t d8k_conv2d_interim_size(const d8k_ctx* ctx, int which, int dtype, int batch, int ih, int iw, int ic, int oc, int fh, int fw,
+                               int oh, int ow);
+D8K_API size_t d8k_deconv2d_interim_size(const d8k_ctx* ctx, int which, int dtype, int batch, int ih, int iw, int ic, int oc, int fh, int fw,
+                                 int oh, int ow);
+
+/* Conv2dGPU (deep8/src/math/Conv2d.cu:308-411).  x [batch, ih, iw, ic], y [oc, fh, fw, ic], z [batch, oh, ow, oc].
+ * Padding follows the reference: the first input row read is -(max(0, (oh-1)*strideY + realFh - ih) / 2). */
+D8K_API int d8k_conv2d_forward(d8k_ctx* ctx, int dtype, const void* x, int batch, int ih, int iw, int ic, const void* y, int oc, int fh, int fw,
+                       void* z, int oh, int ow, int strideY, int strideX, int dilationY, int dilationX, void* interim, size_t interim_bytes);
+/* Conv2dGradXGPU (Conv2d.cu:607-721): dx += col2im(dz * y). */
+D8K_API int d8k_conv2d_grad_x(d8k_ctx* ctx, int dtype, void* dx, int batch, int ih, int iw, int ic, const void* y, int oc, int fh, int fw,
+                      const void* dz, int oh, int ow, int strideY, int strideX, int dilationY, int dilationX, void* interim,
+                      size_t interim_bytes);
+/* Conv2dGradYGPU (Conv2d.cu:917-1031): dy += dz^T * im2col(x). */
+D8K_API int d8k_conv2d_grad_y(d8k_ctx* ctx, int dtype, const void* x, int batch, int ih, int iw, int ic, void* dy, int oc, int fh, int fw,
+                      const void* dz, int oh, int ow, int strideY, int strideX, int dilationY, int dilationX, void* interim,
+                      size_t interim_bytes);
+
+/* DeConv2dGPU (deep8/src/math/DeConv2d.cu:251-308).  x [batch, ih, iw, ic], y [oc, fh, fw, ic], z [batch, oh, ow, oc]. */
+D8K_API int d8k_deconv2d_forward(d8k_ctx* ctx, int dtype, const void* x, int batch, int ih, int iw, int ic, const void* y, int oc, int fh, int fw,
+                         void* z, int oh, int ow, int strideY, int strideX, void* interim, size_t interim_bytes);
+/* DeConv2dGradXGPU (DeConv2d.cu:557-622). */
+D8K_API int d8k_deconv2d_grad_x(d8k_ctx* ctx, int dtype, void* dx, int batch, int ih, int iw, int ic, const void* y, int oc, int fh, int fw,
+                        const void* dz, int oh, int ow, int strideY, int strideX, void* interim, size_t interim_bytes);
+/* DeConv2dGradYGPU (DeConv2d.cu:826-891). */
+D8K_API int d8k_deconv2d_grad_y(d8k_ctx* ctx, int dtype, const void* x, int batch, int ih, int iw, int ic, void* dy, int oc, int fh, int fw,
+                        const void* dz, int oh, int ow, int strideY, int strideX, void* interim, size_t interim_bytes);
+
+/* ReLuGPU / ReLuGradGPU (deep8/src/math/ReLu.cu:17-110): y = max(x, 0);  dx += (x > 0 ? dy : 0). */
+D8K_API int d8k_relu_forward(d8k_ctx* ctx, int dtype, const void* x, void* y, size_t n);
+D8K_API int d8k_relu_backward(d8k_ctx* ctx, int dtype, const void* x, void* dx, const void* dy, size_t n);
+/* Math::Constant with scalar 0 as used by Variable::zeroGradient (deep8/src/nodes/Variable.cpp:119-123). */
+D8K_API int d8k_zero(d8k_ctx* ctx, void* ptr, size_t bytes);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* D8K_H */

@@ -1,0 +1,287 @@
+"""GPU parity tests: the CUDA path, called through the C ABI, against the CPU oracle on the same seeded inputs.
+
+Tolerances (per output tensor, max |got - want| / max |want|):
+  fp32 (3xTF32)              1e-5   against the oracle (the exact contraction, correctly rounded)
+  fp16 in, fp32 accumulate   2e-2   against the fp32 oracle on the fp16-rounded inputs (the reference has no CPU half)
+  integer-valued data        exact  (what the reference's own unit tests assert)
+"""
+import glob
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import cases
+from test_oracle import load_golden, GOLDEN
+
+pytestmark = pytest.mark.gpu
+
+F32_TOL = 1e-5
+F16_TOL = 2e-2
+DEV = "cuda:0"
+
+
+def dev(a, dtype=None):
+    t = torch.from_numpy(np.ascontiguousarray(a)).to(DEV)
+    return t if dtype is None else t.to(dtype)
+
+
+def host(t):
+    return t.float().cpu().numpy()
+
+
+def check(ctx, got, want, tol, what=""):
+    assert ctx.status() == 0
+    got = host(got)
+    assert got.shape == want.shape, what
+    err = cases.rel_max(got, want)
+    assert err <= tol, "%s: rel_max %.3e > %.1e" % (what, err, tol)
+    return err
+
+
+class Runner:
+    """Runs forward and both gradients of one operator on the GPU and on an oracle, gradients starting from d0."""
+
+    def __init__(self, ctx, oracle, kind, meta):
+        self.ctx, self.oracle, self.kind, self.meta = ctx, oracle, kind, meta
+
+    def gpu(self, x, w, dz, dx0, dw0, tdtype):
+        c = self.ctx
+        X, W = dev(x, tdtype), dev(w, tdtype)
+        if self.kind == "matmul":
+            z = c.matmul_forward(X, W)
+        elif self.kind == "conv":
+            cov, st, dil = self.meta
+            z = c.conv2d_forward(X, W, cov, st, dil)
+        else:
+            cov, st = self.meta
+            z = c.deconv2d_forward(X, W, cov, st)
+        if dz is None:
+            return z, None, None
+        DZ, DX, DW = dev(dz, tdtype), dev(dx0, tdtype), dev(dw0, tdtype)
+        if self.kind == "matmul":
+            c.matmul_grad_x(X, DX, W, DZ)
+            c.matmul_grad_y(X, W, DW, DZ)
+        elif self.kind == "conv":
+            c.conv2d_grad_x(X, DX, W, DZ, cov, st, dil)
+            c.conv2d_grad_y(X, W, DW, DZ, cov, st, dil)
+        else:
+            c.deconv2d_grad_x(X, DX, W, DZ, cov, st)
+            c.deconv2d_grad_y(X, W, DW, DZ, cov, st)
+        return z, DX, DW
+
+    def cpu(self, x, w, dz, dx0, dw0):
+        o = self.oracle
+        if self.kind == "matmul":
+            z = o.matmul_forward(x, w)
+            if dz is None:
+                return z, None, None
+            return z, o.matmul_grad_x(x, w, dz, dx0), o.matmul_grad_y(x, w, dz, dw0)
+        if self.kind == "conv":
+            z = o.conv2d_forward(x, w, *self.meta)
+            if dz is None:
+                return z, None, None
+            return z, o.conv2d_grad_x(x, w, dz, *self.meta, d0=dx0), o.conv2d_grad_y(x, w, dz, *self.meta, d0=dw0)
+        z = o.deconv2d_forward(x, w, *self.meta)
+        if dz is None:
+            return z, None, None
+        return z, o.deconv2d_grad_x(x, w, dz, *self.meta, d0=dx0), o.deconv2d_grad_y(x, w, dz, *self.meta, d0=dw0)
+
+    def zshape(self, x, w):
+        return self.cpu(x, w, None, None, None)[0].shape
+
+
+def parity(ctx, oracle, kind, xs, ws, meta, tdtype, tol, seed=0, gen="float"):
+    r = Runner(ctx, oracle, kind, meta)
+    if gen == "float":
+        x, w = cases.uniform(seed, xs), cases.normal(seed + 1, ws, 0.25)
+    else:
+        hi = 4 if tdtype == torch.float16 else 20
+        x, w = cases.small_ints(seed, xs, hi), cases.small_ints(seed + 1, ws, hi)
+    if tdtype == torch.float16:  # the oracle sees exactly the values the GPU sees
+        x, w = x.astype(np.float16).astype(np.float32), w.astype(np.float16).astype(np.float32)
+    zs = r.zshape(x, w)
+    if gen == "float":
+        dz, dx0, dw0 = cases.normal(seed + 2, zs), cases.normal(seed + 3, xs), cases.normal(seed + 4, ws)
+    else:
+        dz, dx0, dw0 = cases.small_ints(seed + 2, zs, hi), cases.small_ints(seed + 3, xs, hi), cases.small_ints(seed + 4, ws, hi)
+    if tdtype == torch.float16:
+        dz, dx0, dw0 = (a.astype(np.float16).astype(np.float32) for a in (dz, dx0, dw0))
+    got = r.gpu(x, w, dz, dx0, dw0, tdtype)
+    want = r.cpu(x, w, dz, dx0, dw0)
+    errs = [check(ctx, g, wnt, tol, name) for name, g, wnt in zip(("z", "dx", "dy"), got, want)]
+    return errs
+
+
+# ------------------------------------------------------------------------------------------------ MatrixMultiply
+@pytest.mark.parametrize("xs,ys", cases.MATMUL_REFERENCE_TESTS + cases.MATMUL_EDGE + [cases.MATMUL_CFG1, cases.MATMUL_CFG2])
+def test_matmul_f32(ctx, restated, xs, ys):
+    parity(ctx, restated, "matmul", xs, ys, None, torch.float32, F32_TOL)
+
+
+@pytest.mark.parametrize("xs,ys", cases.MATMUL_REFERENCE_TESTS + cases.MATMUL_EDGE + [cases.MATMUL_CFG1, cases.MATMUL_CFG2])
+def test_matmul_f16(ctx, restated, xs, ys):
+    parity(ctx, restated, "matmul", xs, ys, None, torch.float16, F16_TOL)
+
+
+@pytest.mark.parametrize("xs,ys", cases.MATMUL_REFERENCE_TESTS + cases.MATMUL_EDGE)
+def test_matmul_integers_exact_f32(ctx, restated, xs, ys):
+    """test/MatrixMultiplyTest.h asserts equality on rand() % 50 data; so do we."""
+    parity(ctx, restated, "matmul", xs, ys, None, torch.float32, 0.0, gen="int")
+
+
+def test_matmul_integers_exact_f16(ctx, restated):
+    parity(ctx, restated, "matmul", (3, 40, 24), (1, 24, 56), None, torch.float16, 0.0, gen="int")
+    parity(ctx, restated, "matmul", (1, 129, 17), (2, 17, 31), None, torch.float16, 0.0, gen="int")
+
+
+# ------------------------------------------------------------------------------------------------ Conv2d
+@pytest.mark.parametrize("xs,ws,cov,st,dil", cases.CONV_REFERENCE_TESTS + cases.CONV_EDGE)
+def test_conv_f32(ctx, restated, xs, ws, cov, st, dil):
+    parity(ctx, restated, "conv", xs, ws, (cov, st, dil), torch.float32, F32_TOL)
+
+
+@pytest.mark.parametrize("xs,ws,cov,st,dil", cases.CONV_REFERENCE_TESTS + cases.CONV_EDGE)
+def test_conv_f16(ctx, restated, xs, ws, cov, st, dil):
+    parity(ctx, restated, "conv", xs, ws, (cov, st, dil), torch.float16, F16_TOL)
+
+
+@pytest.mark.parametrize("xs,ws,cov,st,dil", cases.CONV_REFERENCE_TESTS + cases.CONV_EDGE)
+def test_conv_integers_exact(ctx, restated, xs, ws, cov, st, dil):
+    parity(ctx, restated, "conv", xs, ws, (cov, st, dil), torch.float32, 0.0, gen="int")
+
+
+def test_conv_cfg3_full_size(ctx, restated):
+    xs, ws, cov, st, dil = cases.CONV_CFG3
+    parity(ctx, restated, "conv", xs, ws, (cov, st, dil), torch.float32, F32_TOL, seed=4)
+
+
+# ------------------------------------------------------------------------------------------------ DeConv2d
+@pytest.mark.parametrize("xs,ws,cov,st", cases.DECONV_REFERENCE_TESTS + cases.DECONV_EDGE)
+def test_deconv_f32(ctx, restated, xs, ws, cov, st):
+    parity(ctx, restated, "deconv", xs, ws, (cov, st), torch.float32, F32_TOL)
+
+
+@pytest.mark.parametrize("xs,ws,cov,st", cases.DECONV_EDGE)
+def test_deconv_f16(ctx, restated, xs, ws, cov, st):
+    parity(ctx, restated, "deconv", xs, ws, (cov, st), torch.float16, F16_TOL)
+
+
+@pytest.mark.parametrize("xs,ws,cov,st", cases.DECONV_REFERENCE_TESTS + cases.DECONV_EDGE)
+def test_deconv_integers_exact(ctx, restated, xs, ws, cov, st):
+    parity(ctx, restated, "deconv", xs, ws, (cov, st), torch.float32, 0.0, gen="int")
+
+
+def test_deconv_cfg4_full_size(ctx, restated):
+    xs, ws, cov, st = cases.DECONV_CFG4
+    parity(ctx, restated, "deconv", xs, ws, (cov, st), torch.float32, F32_TOL, seed=7)
+
+
+# ------------------------------------------------------------------------------------------------ golden vectors
+@pytest.mark.parametrize("path", GOLDEN, ids=[os.path.basename(p)[:-4] for p in GOLDEN])
+def test_gpu_matches_reference_golden(ctx, path):
+    """Against the committed outputs of the reference's own CPU code (float accumulation: 1e-5 covers both sides)."""
+    kind, x, w, dz_seed, meta, want = load_golden(path)
+    r = Runner(ctx, None, kind, meta)
+    dz = cases.normal(dz_seed, want[0].shape)
+    got = r.gpu(x, w, dz, np.zeros_like(x), np.zeros_like(w), torch.float32)
+    for name, g, wnt in zip(("z", "dx", "dy"), got, want):
+        check(ctx, g, wnt, F32_TOL, name)
+
+
+def test_gpu_matches_reference_library(ctx, reference):
+    """Where the reference's CPU library travelled with the repo, compare with it directly on config 1."""
+    xs, ys = cases.MATMUL_CFG1
+    x, y = cases.uniform(0, xs), cases.uniform(10, ys)
+    dz = cases.uniform(1, (1, xs[1], ys[2]))
+    r = Runner(ctx, reference, "matmul", None)
+    got = r.gpu(x, y, dz, np.zeros_like(x), np.zeros_like(y), torch.float32)
+    want = r.cpu(x, y, dz, None, None)
+    for g, wnt in zip(got, want):
+        check(ctx, g, wnt, F32_TOL)
+
+
+# ------------------------------------------------------------------------------------------------ full-size properties
+def test_cfg5_mlp_layer_sampled_rows(ctx, restated):
+    """Config 5 sizes do not fit the oracle; check rows sampled from the full-size product against it, and linearity."""
+    torch.manual_seed(10)
+    M, K, N = 8192, 4096, 16384
+    X = torch.randn(1, M, K, device=DEV, dtype=torch.float16)
+    W = (torch.randn(1, K, N, device=DEV) * 0.02).to(torch.float16)
+    H = ctx.matmul_forward(X, W)
+    assert ctx.status() == 0
+    rows = [0, 1, 127, 128, 4095, 8191]
+    want = restated.matmul_forward(np.ascontiguousarray(host(X[:, rows, :])), host(W))
+    assert cases.rel_max(host(H[:, rows, :]), want) <= F16_TOL
+    # gradient of the weights over the full batch: sampled columns against the oracle (K of this product = 8192 rows)
+    dH = (torch.randn(1, M, N, device=DEV) * 0.01).to(torch.float16)
+    dW = torch.zeros_like(W)
+    ctx.matmul_grad_y(X, W, dW, dH)
+    assert ctx.status() == 0
+    cols = [0, 255, 256, 16383]
+    want = restated.matmul_grad_y(host(X), np.zeros((1, K, len(cols)), np.float32), np.ascontiguousarray(host(dH[:, :, cols])))
+    assert cases.rel_max(host(dW[:, :, cols]), want) <= F16_TOL
+    # dx = dH W^T on sampled rows
+    dX = torch.zeros_like(X)
+    ctx.matmul_grad_x(X, dX, W, dH)
+    assert ctx.status() == 0
+    want = restated.matmul_grad_x(np.zeros((1, len(rows), K), np.float32), host(W), np.ascontiguousarray(host(dH[:, rows, :])))
+    assert cases.rel_max(host(dX[:, rows, :]), want) <= F16_TOL
+
+
+def test_gradients_accumulate(ctx):
+    """Calling a gradient twice adds twice (beta = 1 in the reference's gemm calls, MatrixMultiply.cu:203, 391)."""
+    x = dev(cases.small_ints(1, (2, 64, 32), 4))
+    y = dev(cases.small_ints(2, (1, 32, 48), 4))
+    dz = dev(cases.small_ints(3, (2, 64, 48), 4))
+    dx = torch.zeros_like(x)
+    ctx.matmul_grad_x(x, dx, y, dz)
+    once = dx.clone()
+    ctx.matmul_grad_x(x, dx, y, dz)
+    assert ctx.status() == 0
+    assert torch.equal(dx, 2 * once)
+
+
+def test_empty_and_bad_arguments(ctx):
+    import deep8_b200
+    x = torch.zeros(1, 4, 8, device=DEV)
+    y = torch.zeros(3, 9, 2, device=DEV)
+    with pytest.raises(ValueError):
+        ctx.matmul_forward(x, y)                       # inner extents differ
+    with pytest.raises(ValueError):
+        ctx.matmul_forward(torch.zeros(2, 4, 8, device=DEV), torch.zeros(3, 8, 2, device=DEV))  # batches 2 and 3
+    with pytest.raises(TypeError):
+        ctx.matmul_forward(x.double(), torch.zeros(1, 8, 2, device=DEV).double())   # "type ... is not support"
+    with pytest.raises(deep8_b200.D8kError):
+        deep8_b200._lib.check(ctx.lib.d8k_matmul_forward(ctx.h, 0, None, 1, 4, 8, None, 1, 2, None))  # null pointers
+    # K = 0 through the general entry point: an empty contraction overwrites C with zeros
+    C = torch.ones(1, 4, 6, device=DEV)
+    ctx.gemm(torch.zeros(1, 4, 0, device=DEV), torch.zeros(1, 0, 6, device=DEV), C)
+    assert ctx.status() == 0 and float(C.abs().sum()) == 0.0
+
+
+def test_relu_matches_reference_rule(ctx):
+    for dt in (torch.float32, torch.float16):
+        x = torch.randn(1000003, device=DEV).to(dt)
+        y = ctx.relu_forward(x)
+        assert torch.equal(y, torch.where(x > 0, x, torch.zeros_like(x)))
+        dy = torch.randn_like(x)
+        dx0 = torch.randn_like(x)
+        dx = dx0.clone()
+        ctx.relu_backward(x, dx, dy)
+        want = torch.where(x > 0, (dx0.float() + dy.float()).to(dt), dx0)
+        assert torch.equal(dx, want)
+    assert ctx.status() == 0
+
+
+def test_split_k_is_deterministic(ctx):
+    """The split-K reduction sums partial tiles in split order: two runs give identical bits."""
+    x = dev(cases.normal(2, (64, 128, 256), 0.05))
+    dz = dev(cases.normal(3, (64, 128, 256)))
+    y = dev(cases.normal(4, (1, 256, 256), 0.05))
+    a, b = torch.zeros_like(y), torch.zeros_like(y)
+    ctx.matmul_grad_y(x, y, a, dz)
+    ctx.matmul_grad_y(x, y, b, dz)
+    assert ctx.status() == 0
+    assert torch.equal(a, b)
