@@ -67,6 +67,17 @@ D8K_API int d8k_gemm(d8k_ctx* ctx, int dtype, int transA, int transB, int M, int
              const void* B, long long ldb, int batchB, long long strideB,
              void* C, long long ldc, long long strideC, int batch, int beta, int reduce_batch);
 
+/* No counterpart in the reference.  The same contraction as d8k_gemm for one matrix pair (no batch), for callers that
+ * may not allocate device memory and therefore cannot create a context: the split-K scratch is a static device array
+ * inside the library, 16 MiB of partial tiles (+ 20 KiB of bookkeeping) held by every GPU that loads the library until
+ * the process exits.  Runs on the current device, on `stream` (a cudaStream_t, NULL = legacy default stream).  A
+ * contraction whose split-K partial tiles need more than the 16 MiB is rejected with D8K_ERR_ARGUMENT.  The first call
+ * on a device looks up the array's device address: make it before any stream capture.  Calls share the array: two calls
+ * whose kernels overlap on the GPU race; issue them on one stream or serialise them.  A bounded wait that expires inside
+ * the kernel is not reported through this entry point. */
+D8K_API int d8k_gemm_static(int dtype, int transA, int transB, int M, int N, int K, const void* A, long long lda,
+                            const void* B, long long ldb, void* C, long long ldc, int beta, void* stream);
+
 /* MatrixMultiplyGPU (deep8/src/math/MatrixMultiply.cu:139-176): z[b] = x[b % xb] * y[b % yb];
  * x is xb matrices xr x xc, y is yb matrices xc x yc, z is max(xb, yb) matrices xr x yc; xb, yb equal or 1. */
 D8K_API int d8k_matmul_forward(d8k_ctx* ctx, int dtype, const void* x, int xb, int xr, int xc, const void* y, int yb, int yc, void* z);
