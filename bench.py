@@ -320,7 +320,7 @@ def run_gpu_arm(args):
             "data": "synthetic", "config": workload_config(world),
             "per_gpu_tflops": per_gpu, "frac_of_nominal_fp16_peak": per_gpu / NOMINAL_FP16_TFLOPS,
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
-                         "traffic": TRAFFIC_BYTES_PER_LAUNCH, "kernel": "d8k_gemm_kernel (TMA-fed fp16, 128x256 tiles)",
+                         "traffic": TRAFFIC_BYTES_PER_LAUNCH, "kernel": "d8k_gemm_pair_kernel (TMA-fed fp16, CTA pairs on 256x256 tiles)",
                          "peak_source": peak_src, "flop_per_launch": FLOP_PER_GEMM, "avg_launch_ms": avg_gemm_ms,
                          "gemm_share_of_step": sum(gemm_ms) / (ms_step * args.steps)},
             "e2e": {"value": FLOP_PER_STEP * world / (e2e_ms * 1e-3) / 1e12, "unit": UNIT, "h2d_bytes_per_step": h2d,
@@ -335,14 +335,15 @@ def run_gpu_arm(args):
         dist.destroy_process_group()
 
 
-# DRAM bytes (read + write) of one contraction launch of this workload from an ncu capture; None until captured.
-TRAFFIC_BYTES_PER_LAUNCH = None
+# DRAM bytes (read + write) of one contraction launch of this workload: mean of the three launches captured with ncu
+# (profiles/d8k_gemm_pair_kernel_f16_mlp_config5.md); algorithmic bytes are 0.47e9.
+TRAFFIC_BYTES_PER_LAUNCH = 1.10e9
 
 
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")

@@ -60,6 +60,8 @@ typedef cudaError_t (*GemmLaunchFn)(int grid, cudaStream_t stream, const CUtenso
 GemmLaunchFn lookup_f16_tma(bool a_mn, bool b_mn, int bn);
 GemmLaunchFn lookup_f16_gather(bool a_mn, bool b_mn, int bn);
 GemmLaunchFn lookup_f32_gather(bool a_mn, bool b_mn, int bn);
+// paired-CTA kernel: the first argument of the launch function is the number of CTA pairs
+GemmLaunchFn lookup_f16_pair(bool a_mn, bool b_mn);
 
 template <class Cfg>
 cudaError_t launch_cfg(int grid, cudaStream_t stream, const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p) {

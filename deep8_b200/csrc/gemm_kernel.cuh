@@ -73,6 +73,7 @@ struct GemmParams {
     int* counters;     // one ticket counter per output tile, zero on entry and on exit
     int* status;
     int a_batch_mod, b_batch_mod;  // TMA: batch coordinate = b % mod
+    long long* prof;   // optional, normally null: per CTA 8 counters of cycles each role spent waiting (paired kernel only)
     GatherSrc a, b;
 };
 
@@ -135,11 +136,16 @@ __device__ __forceinline__ WorkItem decode_work(const GemmParams& p, int w, int 
     return it;
 }
 
-__device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
+// Bounded wait on an mbarrier phase.  `backoff_ns` > 0 sleeps between polls: used by roles that are not on the
+// critical path (the epilogue waiting for a finished tile), because a warp that spins on mbarrier.try_wait competes
+// with TMA writes and tensor-core operand reads for shared-memory bandwidth.
+__device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code,
+                                         unsigned backoff_ns = 0) {
     if (ptx::mbar_try_wait(bar, parity)) return true;
     long long t0 = clock64();
     int spins = 0;
     while (!ptx::mbar_try_wait(bar, parity)) {
+        if (backoff_ns) __nanosleep(backoff_ns);
         if ((++spins & 63) == 0) {
             if (*abort_flag) return false;
             if (clock64() - t0 > kWaitLimitCycles) {
@@ -150,6 +156,14 @@ __device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity, volatile
         }
     }
     return true;
+}
+
+// One lane waits, the warp learns the outcome: 32 lanes polling the same barrier buy nothing.
+__device__ __forceinline__ bool warp_wait_bar(int lane, uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code,
+                                              unsigned backoff_ns = 0) {
+    int ok = 1;
+    if (lane == 0) ok = wait_bar(bar, parity, abort_flag, status, code, backoff_ns) ? 1 : 0;
+    return __shfl_sync(0xffffffffu, ok, 0) != 0;
 }
 
 // ------------------------------------------------------------------------------------------------ gather loaders

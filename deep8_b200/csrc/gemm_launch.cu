@@ -55,6 +55,27 @@ bool make_map(CUtensorMap* map, const HostOperand& o, long long inner, long long
     return r == CUDA_SUCCESS;
 }
 
+// 4-D map for the paired kernel, one 32 KB box per operand and stage (two k-blocks of 64).
+//   K-major  (mn == false): {64 k, rows, K / 64, batch},  box {64, 128, 2, 1}   - needs K % 64 == 0
+//   MN-major (mn == true) : {64 m/n, K, extent / 64, batch}, box {64, 128, 2, 1} - needs extent % 64 == 0
+// The second and third strides are not in increasing order (the 128-byte step comes after the row pitch); TMA only
+// computes addresses from them.
+bool make_pair_map(CUtensorMap* map, const HostOperand& o, long long extent, long long K) {
+    EncodeTiledFn enc = encode_tiled();
+    if (!enc) return false;
+    long long rows = o.mn ? K : extent;           // stored rows
+    long long groups = (o.mn ? extent : K) / 64;  // 64-element groups along the stored row
+    cuuint64_t dims[4] = {64u, static_cast<cuuint64_t>(rows), static_cast<cuuint64_t>(groups), static_cast<cuuint64_t>(o.batch_count)};
+    long long bstride = o.batch_count > 1 ? o.batch_stride : rows * o.ld;
+    cuuint64_t strides[3] = {static_cast<cuuint64_t>(o.ld * 2), 128u, static_cast<cuuint64_t>(bstride * 2)};
+    cuuint32_t box[4] = {64u, 128u, 2u, 1u};
+    cuuint32_t estr[4] = {1u, 1u, 1u, 1u};
+    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, const_cast<void*>(o.ptr), dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS;
+}
+
 GatherSrc to_gather(const HostOperand& o, int rows, int cols) {
     GatherSrc s;
     std::memset(&s, 0, sizeof(s));
@@ -72,7 +93,7 @@ GatherSrc to_gather(const HostOperand& o, int rows, int cols) {
 }
 
 struct Plan {
-    bool f32, tma;
+    bool f32, tma, pair;
     int bn, bk, tiles_m, tiles_n, tiles, num_kb, total_kb, splits, kb_per_split;
     size_t scratch;
 };
@@ -108,6 +129,15 @@ Plan make_plan(const Ctx* ctx, const GemmProblem& g, size_t scratch_limit) {
     pl.kb_per_split = (pl.total_kb + splits - 1) / splits;
     pl.splits = (pl.total_kb + pl.kb_per_split - 1) / pl.kb_per_split;
     pl.scratch = pl.splits > 1 ? per_split * pl.splits : 0;
+    // CTA pairs on 256 x 256 tiles once the output alone fills the machine (74 pairs) and nothing is split
+    int tiles256 = g.batch * ((g.M + 255) / 256) * ((g.N + 255) / 256);
+    pl.pair = pl.tma && pl.bn == 256 && pl.splits == 1 && tiles256 * 2 >= ctx->num_sms && env_int("D8K_PAIR", 1) != 0 &&
+              g.K % 64 == 0 && (!g.a.mn || g.M % 64 == 0) && (!g.b.mn || g.N % 64 == 0);
+    if (pl.pair) {
+        pl.tiles_m = (g.M + 255) / 256;
+        pl.tiles_n = (g.N + 255) / 256;
+        pl.tiles = tiles256;
+    }
     return pl;
 }
 
@@ -152,7 +182,7 @@ int run_gemm(Ctx* ctx, const GemmProblem& g) {
     p.kb_per_split = pl.kb_per_split;
     p.tiles_m = pl.tiles_m;
     p.tiles_n = pl.tiles_n;
-    p.raster_group = env_int("D8K_RASTER", 16);
+    p.raster_group = env_int("D8K_RASTER", pl.pair ? 8 : 16);
     if (p.raster_group < 1) p.raster_group = 1;
     p.total_work = pl.tiles * pl.splits;
     p.beta = g.beta;
@@ -169,7 +199,10 @@ int run_gemm(Ctx* ctx, const GemmProblem& g) {
     std::memset(&ta, 0, sizeof(ta));
     std::memset(&tb, 0, sizeof(tb));
     GemmLaunchFn fn = nullptr;
-    if (pl.tma) {
+    if (pl.pair) {
+        if (!make_pair_map(&ta, g.a, g.M, g.K) || !make_pair_map(&tb, g.b, g.N, g.K)) return fail(2, "gemm: cuTensorMapEncodeTiled (4-D) failed");
+        fn = lookup_f16_pair(g.a.mn, g.b.mn);
+    } else if (pl.tma) {
         // K-major: {K, rows}; MN-major: {rows(M or N), K}
         bool oka = g.a.mn ? make_map(&ta, g.a, g.M, g.K, 64) : make_map(&ta, g.a, g.K, g.M, kBM);
         bool okb = g.b.mn ? make_map(&tb, g.b, g.N, g.K, 64) : make_map(&tb, g.b, g.K, g.N, pl.bn);
@@ -182,6 +215,7 @@ int run_gemm(Ctx* ctx, const GemmProblem& g) {
     }
     if (!fn) return fail(2, "gemm: no kernel for this configuration");
     int grid = p.total_work < ctx->num_sms ? p.total_work : ctx->num_sms;
+    if (pl.pair) grid = p.total_work < ctx->num_sms / 2 ? p.total_work : ctx->num_sms / 2;  // pairs
     cudaError_t e = fn(grid, ctx->stream, ta, tb, p);
     if (e != cudaSuccess) return fail(2, std::string("gemm: launch failed: ") + cudaGetErrorString(e));
     count_launch();

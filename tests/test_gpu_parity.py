@@ -230,6 +230,21 @@ def test_cfg5_mlp_layer_sampled_rows(ctx, restated):
     assert cases.rel_max(host(dX[:, rows, :]), want) <= F16_TOL
 
 
+@pytest.mark.parametrize("tA,tB", [(False, False), (False, True), (True, False), (True, True)])
+def test_paired_cta_kernel(ctx, restated, tA, tB):
+    """Large aligned fp16 problems run on CTA pairs (256 x 256 tiles, cta_group::2): ragged edges, every operand layout, beta = 1."""
+    M, N, K = 2240, 2112, 192   # ragged against the 256-tiles, an odd number of k-blocks
+    a = cases.uniform(11, (1, K, M) if tA else (1, M, K)).astype(np.float16).astype(np.float32)
+    b = cases.normal(12, (1, N, K) if tB else (1, K, N), 0.25).astype(np.float16).astype(np.float32)
+    c0 = cases.normal(13, (1, M, N)).astype(np.float16).astype(np.float32)
+    C = dev(c0, torch.float16)
+    ctx.gemm(dev(a, torch.float16), dev(b, torch.float16), C, transA=tA, transB=tB, beta=1)
+    a_eff = np.ascontiguousarray(a.transpose(0, 2, 1)) if tA else a
+    b_eff = np.ascontiguousarray(b.transpose(0, 2, 1)) if tB else b
+    want = restated.matmul_forward(a_eff, b_eff) + c0
+    check(ctx, C, want, F16_TOL)
+
+
 def test_gradients_accumulate(ctx):
     """Calling a gradient twice adds twice (beta = 1 in the reference's gemm calls, MatrixMultiply.cu:203, 391)."""
     x = dev(cases.small_ints(1, (2, 64, 32), 4))
