@@ -3,9 +3,12 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
 
 Workload (per GPU, weak scaling): X 8192x4096, W1 4096x16384, ReLU, W2 16384x4096, upstream gradient dY 8192x4096;
-fp16 storage, fp32 accumulation.  One step = zero the gradients, H = X W1, A = relu(H), Y = A W2, then
-dA += dY W2^T, dW2 += A^T dY, dH += relu'(H) dA, dX += dH W1^T, dW1 += X^T dH (six contractions of
-2*8192*4096*16384 FLOP each), and for N > 1 the NCCL all-reduce (sum) of dW1 and dW2.  Inputs are seeded synthetic
+fp16 storage, fp32 accumulation.  One step = H = X W1, A = relu(H), Y = A W2, then dA = dY W2^T, dW2 = A^T dY,
+dH = relu'(H) dA, dX = dH W1^T, dW1 = X^T dH (six contractions of 2*8192*4096*16384 FLOP each), and for N > 1 the NCCL
+all-reduce (sum) of dW1 and dW2.  By default the two ReLU passes run inside the epilogues of the contractions that
+produce their inputs and every gradient is written by its first (here: only) contribution, so no zero fill is needed;
+`--unfused` runs the reference's call sequence instead (zero every gradient, eight separate operator calls, += everywhere).
+Both give bit-identical tensors (tests/test_gpu_parity.py::test_fused_step_equals_unfused).  Inputs are seeded synthetic
 data (X N(0,1), weights N(0,0.02), dY N(0,1)*0.01, seed 10, rank-offset for X and dY).
 
 Prints ONE JSON line.  `value` is the aggregate TFLOP/s over all GPUs with inputs resident in HBM; `e2e` is the same
@@ -169,22 +172,26 @@ def workload_config(n):
 
 # ------------------------------------------------------------------------------------------------ GPU arm
 class MlpStep:
-    """The MLP step on one GPU through the d8k C ABI; buffers allocated once, as an executor would keep them."""
+    """The MLP step on one GPU through the d8k C ABI; buffers allocated once, as an executor would keep them.
+    X, dY and Y are double-buffered so that the end-to-end loop can copy step i+1 in and step i-1 out while step i runs."""
 
-    def __init__(self, ctx, torch, device, rank):
-        self.ctx, self.torch = ctx, torch
+    def __init__(self, ctx, torch, device, rank, fused=True):
+        self.ctx, self.torch, self.fused = ctx, torch, fused
         g = torch.Generator(device=device)
         g.manual_seed(10)
         h = torch.float16
         self.W1 = (torch.randn((1, D_IN, D_HID), device=device, generator=g) * 0.02).to(h)
         self.W2 = (torch.randn((1, D_HID, D_IN), device=device, generator=g) * 0.02).to(h)
         g.manual_seed(10 + 1000 * (rank + 1))
-        self.X = torch.randn((1, M_PER_GPU, D_IN), device=device, generator=g).to(h)
-        self.dY = (torch.randn((1, M_PER_GPU, D_IN), device=device, generator=g) * 0.01).to(h)
         e = lambda *s: torch.empty(s, device=device, dtype=h)
-        self.H, self.A, self.Y = e(1, M_PER_GPU, D_HID), e(1, M_PER_GPU, D_HID), e(1, M_PER_GPU, D_IN)
+        self.X = [torch.randn((1, M_PER_GPU, D_IN), device=device, generator=g).to(h)]
+        self.dY = [(torch.randn((1, M_PER_GPU, D_IN), device=device, generator=g) * 0.01).to(h)]
+        self.X.append(self.X[0].clone())
+        self.dY.append(self.dY[0].clone())
+        self.Y = [e(1, M_PER_GPU, D_IN), e(1, M_PER_GPU, D_IN)]
+        self.H, self.A = e(1, M_PER_GPU, D_HID), e(1, M_PER_GPU, D_HID)
         self.dA, self.dH = e(1, M_PER_GPU, D_HID), e(1, M_PER_GPU, D_HID)
-        self.dX, self.dW1, self.dW2 = torch.empty_like(self.X), torch.empty_like(self.W1), torch.empty_like(self.W2)
+        self.dX, self.dW1, self.dW2 = torch.empty_like(self.X[0]), torch.empty_like(self.W1), torch.empty_like(self.W2)
         self.gemm_events = []
 
     def _gemm(self, fn, timed):
@@ -197,22 +204,36 @@ class MlpStep:
         else:
             fn()
 
-    def step(self, dist=None, timed=False):
+    def step(self, dist=None, timed=False, buf=0):
         c = self.ctx
-        for t in (self.dA, self.dH, self.dX, self.dW1, self.dW2):
-            c.zero(t)
-        self._gemm(lambda: c.matmul_forward(self.X, self.W1, out=self.H), timed)
-        c.relu_forward(self.H, out=self.A)
-        self._gemm(lambda: c.matmul_forward(self.A, self.W2, out=self.Y), timed)
-        self._gemm(lambda: c.matmul_grad_x(self.A, self.dA, self.W2, self.dY), timed)
-        self._gemm(lambda: c.matmul_grad_y(self.A, self.W2, self.dW2, self.dY), timed)
+        X, dY, Y = self.X[buf], self.dY[buf], self.Y[buf]
+        overlap = os.environ.get("D8_BENCH_ALLREDUCE", "overlap") == "overlap"
         work = []
+        if self.fused:
+            self._gemm(lambda: c.matmul_forward_relu(X, self.W1, self.H, self.A), timed)
+            self._gemm(lambda: c.matmul_forward(self.A, self.W2, out=Y), timed)
+            self._gemm(lambda: c.matmul_grad_x_relu(self.A, self.dA, self.W2, dY, self.H, self.dH, False, False), timed)
+            self._gemm(lambda: c.matmul_grad_y(self.A, self.W2, self.dW2, dY, accumulate=False), timed)
+            if dist is not None and overlap:
+                work.append(dist.all_reduce(self.dW2, async_op=True))  # overlaps the rest of the backward pass
+            self._gemm(lambda: c.matmul_grad_x(X, self.dX, self.W1, self.dH, accumulate=False), timed)
+            self._gemm(lambda: c.matmul_grad_y(X, self.W1, self.dW1, self.dH, accumulate=False), timed)
+        else:
+            for t in (self.dA, self.dH, self.dX, self.dW1, self.dW2):
+                c.zero(t)
+            self._gemm(lambda: c.matmul_forward(X, self.W1, out=self.H), timed)
+            c.relu_forward(self.H, out=self.A)
+            self._gemm(lambda: c.matmul_forward(self.A, self.W2, out=Y), timed)
+            self._gemm(lambda: c.matmul_grad_x(self.A, self.dA, self.W2, dY), timed)
+            self._gemm(lambda: c.matmul_grad_y(self.A, self.W2, self.dW2, dY), timed)
+            if dist is not None and overlap:
+                work.append(dist.all_reduce(self.dW2, async_op=True))
+            c.relu_backward(self.H, self.dH, self.dA)
+            self._gemm(lambda: c.matmul_grad_x(X, self.dX, self.W1, self.dH), timed)
+            self._gemm(lambda: c.matmul_grad_y(X, self.W1, self.dW1, self.dH), timed)
         if dist is not None:
-            work.append(dist.all_reduce(self.dW2, async_op=True))  # overlaps the rest of the backward pass
-        c.relu_backward(self.H, self.dH, self.dA)
-        self._gemm(lambda: c.matmul_grad_x(self.X, self.dX, self.W1, self.dH), timed)
-        self._gemm(lambda: c.matmul_grad_y(self.X, self.W1, self.dW1, self.dH), timed)
-        if dist is not None:
+            if not overlap:
+                work.append(dist.all_reduce(self.dW2, async_op=True))
             work.append(dist.all_reduce(self.dW1, async_op=True))
             for w in work:
                 w.wait()
@@ -237,7 +258,7 @@ def run_gpu_arm(args):
     ctx = deep8_b200.Context(local_rank)
     stream = torch.cuda.current_stream()
     ctx.use_stream(stream if stream.cuda_stream != 0 else None)
-    mlp = MlpStep(ctx, torch, device, rank)
+    mlp = MlpStep(ctx, torch, device, rank, fused=not args.unfused)
 
     def barrier():
         if dist is not None:
@@ -282,32 +303,65 @@ def run_gpu_arm(args):
     if args.profile:
         if rank == 0:
             print(json.dumps({"profile_run": True, "ms_per_step": ms_step, "gpu_launches": launches}), flush=True)
+        if dist is not None:
+            dist.barrier()
+            dist.destroy_process_group()
         return
-    # ---- end-to-end: X and dY from pinned host memory every step, Y back to the host
-    hX = torch.empty(mlp.X.shape, dtype=torch.float16).pin_memory()
-    hdY = torch.empty(mlp.dY.shape, dtype=torch.float16).pin_memory()
-    hY = torch.empty(mlp.Y.shape, dtype=torch.float16).pin_memory()
-    hX.copy_(mlp.X)
-    hdY.copy_(mlp.dY)
-    e2e_steps = max(2, min(args.steps, 10))
+    # ---- end-to-end: X and dY from pinned host memory every step, Y back to the host.  Copies run on their own
+    # streams into the other half of the double buffers, so step i computes while step i+1 arrives and step i-1 leaves.
+    hX = torch.empty(mlp.X[0].shape, dtype=torch.float16).pin_memory()
+    hdY = torch.empty(mlp.dY[0].shape, dtype=torch.float16).pin_memory()
+    hY = [torch.empty(mlp.Y[0].shape, dtype=torch.float16).pin_memory() for _ in range(2)]
+    hX.copy_(mlp.X[0])
+    hdY.copy_(mlp.dY[0])
+    e2e_steps = max(4, min(args.steps, 20))
+    s_in, s_out = torch.cuda.Stream(device=device), torch.cuda.Stream(device=device)
+    main = torch.cuda.current_stream()
 
-    def e2e_step():
-        mlp.X.copy_(hX, non_blocking=True)
-        mlp.dY.copy_(hdY, non_blocking=True)
-        mlp.step(dist)
-        hY.copy_(mlp.Y, non_blocking=True)
+    def e2e_loop(n):
+        in_ready = [None, None]    # event: inputs of buffer b have arrived
+        out_done = [None, None]    # event: Y of buffer b has left
+        comp_done = [None, None]   # event: the step that used buffer b has finished
 
-    e2e_step()
+        def feed(i):
+            b = i % 2
+            with torch.cuda.stream(s_in):
+                if comp_done[b] is not None:
+                    s_in.wait_event(comp_done[b])       # the step that last read X[b], dY[b] is over
+                mlp.X[b].copy_(hX, non_blocking=True)
+                mlp.dY[b].copy_(hdY, non_blocking=True)
+                in_ready[b] = torch.cuda.Event()
+                in_ready[b].record(s_in)
+
+        feed(0)
+        for i in range(n):
+            b = i % 2
+            if i + 1 < n:
+                feed(i + 1)
+            main.wait_event(in_ready[b])
+            if out_done[b] is not None:
+                main.wait_event(out_done[b])            # Y[b] of two steps ago has been read
+            mlp.step(dist, buf=b)
+            comp_done[b] = torch.cuda.Event()
+            comp_done[b].record(main)
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(comp_done[b])
+                hY[b].copy_(mlp.Y[b], non_blocking=True)
+                out_done[b] = torch.cuda.Event()
+                out_done[b].record(s_out)
+        main.wait_stream(s_out)
+        main.wait_stream(s_in)
+
+    e2e_loop(2)
     barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
-    for _ in range(e2e_steps):
-        e2e_step()
+    e2e_loop(e2e_steps)
     e1.record()
     barrier()
     e2e_ms = max_over_ranks(e0.elapsed_time(e1)) / e2e_steps
     h2d = hX.numel() * 2 + hdY.numel() * 2
-    d2h = hY.numel() * 2
+    d2h = hY[0].numel() * 2
 
     if rank == 0:
         peak, peak_src = measured_peaks()
@@ -317,14 +371,16 @@ def run_gpu_arm(args):
         line = {
             "metric": METRIC, "value": per_gpu * world, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16 (f32 accumulate)",
-            "data": "synthetic", "config": workload_config(world),
+            "data": "synthetic", "config": dict(workload_config(world), step="fused epilogues, first-touch gradients" if not args.unfused
+                                                  else "reference call sequence (zero fill, separate ReLU passes)"),
             "per_gpu_tflops": per_gpu, "frac_of_nominal_fp16_peak": per_gpu / NOMINAL_FP16_TFLOPS,
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
                          "traffic": TRAFFIC_BYTES_PER_LAUNCH, "kernel": "d8k_gemm_pair_kernel (TMA-fed fp16, CTA pairs on 256x256 tiles)",
                          "peak_source": peak_src, "flop_per_launch": FLOP_PER_GEMM, "avg_launch_ms": avg_gemm_ms,
                          "gemm_share_of_step": sum(gemm_ms) / (ms_step * args.steps)},
             "e2e": {"value": FLOP_PER_STEP * world / (e2e_ms * 1e-3) / 1e12, "unit": UNIT, "h2d_bytes_per_step": h2d,
-                    "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms, "steps": e2e_steps},
+                    "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms, "steps": e2e_steps,
+                    "overlap": "copies on side streams, double-buffered inputs and outputs"},
             "gpu_launches": launches, "clocks": clocks,
         }
         if world == 1 and not args.no_cpu:
@@ -347,6 +403,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--unfused", action="store_true", help="the reference's call sequence: zero fill, separate ReLU passes, += everywhere")
     ap.add_argument("--profile", action="store_true", help="for runs under a profiler: no clock sampling, no end-to-end or CPU leg, "
                     "warm-up as given; the printed numbers are not benchmark values")
     args = ap.parse_args()

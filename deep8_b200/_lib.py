@@ -7,7 +7,8 @@ import ctypes
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libdeep8_b200.so")
+# D8K_LIB_PATH selects another build of the same library (A/B measurements); there is still no fallback.
+LIB_PATH = os.environ.get("D8K_LIB_PATH") or os.path.join(_HERE, "libdeep8_b200.so")
 
 F16, F32 = 0, 1
 
@@ -27,6 +28,10 @@ SIGNATURES = {
     "d8k_matmul_forward": (_i, [_vp, _i, _vp, _i, _i, _i, _vp, _i, _i, _vp]),
     "d8k_matmul_grad_x": (_i, [_vp, _i, _vp, _i, _i, _i, _vp, _i, _i, _vp]),
     "d8k_matmul_grad_y": (_i, [_vp, _i, _vp, _i, _i, _i, _vp, _i, _i, _vp]),
+    "d8k_matmul_grad_x_into": (_i, [_vp, _i, _vp, _i, _i, _i, _vp, _i, _i, _vp, _i]),
+    "d8k_matmul_grad_y_into": (_i, [_vp, _i, _vp, _i, _i, _i, _vp, _i, _i, _vp, _i]),
+    "d8k_matmul_forward_relu": (_i, [_vp, _i, _vp, _i, _i, _i, _vp, _i, _i, _vp, _vp]),
+    "d8k_matmul_grad_x_relu": (_i, [_vp, _i, _vp, _i, _i, _i, _vp, _i, _i, _vp, _i, _vp, _vp, _i]),
     "d8k_conv2d_out_dim": (_i, [_i, _i, _i, _i, _i]),
     "d8k_deconv2d_out_dim": (_i, [_i, _i, _i, _i]),
     "d8k_conv2d_interim_size": (_sz, [_vp, _i, _i] + [_i] * 9),
@@ -59,6 +64,8 @@ def load():
             raise ImportError("%s is missing: build it with `python -m deep8_b200.build` (needs nvcc)" % LIB_PATH)
         lib = ctypes.CDLL(LIB_PATH)
         for name, (res, args) in SIGNATURES.items():
+            if os.environ.get("D8K_LIB_PATH") and not hasattr(lib, name):
+                continue  # an older build under test may lack newer entry points
             fn = getattr(lib, name)  # AttributeError here means header and library disagree
             fn.restype = res
             fn.argtypes = args

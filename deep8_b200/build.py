@@ -84,6 +84,30 @@ def build(force=False, verbose=False):
     return LIB, "\n".join(logs)
 
 
+def build_cpp_tests():
+    """Compile tests/cpp/*.cu into tests/cpp/bin/ against libdeep8_b200.so and the CPU oracle (a checker, linked by the tests only)."""
+    nvcc = _nvcc()
+    root = os.path.dirname(HERE)
+    src_dir = os.path.join(root, "tests", "cpp")
+    out_dir = os.path.join(src_dir, "bin")
+    os.makedirs(out_dir, exist_ok=True)
+    built = []
+    for src in sorted(glob.glob(os.path.join(src_dir, "*.cu"))):
+        exe = os.path.join(out_dir, os.path.basename(src)[:-3])
+        deps = [src, LIB, os.path.join(INCLUDE, "deep8", "Deep8.h"), os.path.join(root, "oracle", "libd8oracle.so")]
+        if os.path.exists(exe) and os.path.getmtime(exe) >= _newest([d for d in deps if os.path.exists(d)]):
+            built.append(exe)
+            continue
+        cmd = [nvcc, "-std=c++17", "-O2", "-gencode", "arch=compute_100a,code=sm_100a", "-I", INCLUDE, src, "-o", exe,
+               "-L", HERE, "-ldeep8_b200", "-L", os.path.join(root, "oracle"), "-ld8oracle",
+               "-Xlinker", "-rpath", "-Xlinker", "$ORIGIN/../../../deep8_b200", "-Xlinker", "-rpath", "-Xlinker", "$ORIGIN/../../../oracle"]
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        if r.returncode != 0:
+            raise RuntimeError("nvcc failed for %s:\n%s\n%s" % (src, r.stdout, r.stderr))
+        built.append(exe)
+    return built
+
+
 if __name__ == "__main__":
     lib, log = build(force="--force" in sys.argv, verbose="-v" in sys.argv)
     if log.strip():

@@ -285,9 +285,9 @@ int d8k_ctx_status(d8k_ctx* ctx, int* status) {
     return 0;
 }
 
-int d8k_gemm(d8k_ctx* ctx, int dtype, int transA, int transB, int M, int N, int K, const void* A, long long lda, int batchA,
-             long long strideA, const void* B, long long ldb, int batchB, long long strideB, void* C, long long ldc, long long strideC,
-             int batch, int beta, int reduce_batch) {
+static int gemm_call(d8k_ctx* ctx, int dtype, int transA, int transB, int M, int N, int K, const void* A, long long lda, int batchA,
+                     long long strideA, const void* B, long long ldb, int batchB, long long strideB, void* C, long long ldc, long long strideC,
+                     int batch, int beta, int reduce_batch, int epi = 0, void* E1 = nullptr, void* E2 = nullptr, int beta2 = 0) {
     if (int rc = check_ctx(ctx)) return rc;
     if (int rc = check_dtype(dtype)) return rc;
     if (batchA < 1 || batchB < 1 || batch < 0) return fail(D8K_ERR_ARGUMENT, "d8k_gemm: batch counts must be positive");
@@ -305,7 +305,15 @@ int d8k_gemm(d8k_ctx* ctx, int dtype, int transA, int transB, int M, int N, int 
     g.kbatch = reduce_batch ? (batch > 0 ? batch : 1) : 1;
     if (reduce_batch && batch == 0) g.K = 0;
     g.beta = beta;
+    g.epi = epi; g.E1 = E1; g.E2 = E2; g.beta2 = beta2;
     return run_gemm(ctx, g);
+}
+
+int d8k_gemm(d8k_ctx* ctx, int dtype, int transA, int transB, int M, int N, int K, const void* A, long long lda, int batchA,
+             long long strideA, const void* B, long long ldb, int batchB, long long strideB, void* C, long long ldc, long long strideC,
+             int batch, int beta, int reduce_batch) {
+    return gemm_call(ctx, dtype, transA, transB, M, N, K, A, lda, batchA, strideA, B, ldb, batchB, strideB, C, ldc, strideC, batch, beta,
+                     reduce_batch);
 }
 
 static int check_matmul(int xb, int xr, int xc, int yb, int yc) {
@@ -315,35 +323,71 @@ static int check_matmul(int xb, int xr, int xc, int yb, int yc) {
     return 0;
 }
 
-int d8k_matmul_forward(d8k_ctx* ctx, int dtype, const void* x, int xb, int xr, int xc, const void* y, int yb, int yc, void* z) {
+static int matmul_forward_impl(d8k_ctx* ctx, int dtype, const void* x, int xb, int xr, int xc, const void* y, int yb, int yc, void* z,
+                               int epi, void* relu_out) {
     if (int rc = check_ctx(ctx)) return rc;
     if (int rc = check_dtype(dtype)) return rc;
     if (int rc = check_matmul(xb, xr, xc, yb, yc)) return rc;
     if (yb == 1)  // deep8/src/math/MatrixMultiply.cu:31-36: the batch folds into M
-        return d8k_gemm(ctx, dtype, 0, 0, xb * xr, yc, xc, x, xc, 1, 0, y, yc, 1, 0, z, yc, 0, 1, 0, 0);
+        return gemm_call(ctx, dtype, 0, 0, xb * xr, yc, xc, x, xc, 1, 0, y, yc, 1, 0, z, yc, 0, 1, 0, 0, epi, relu_out);
     int zb = xb > yb ? xb : yb;
-    return d8k_gemm(ctx, dtype, 0, 0, xr, yc, xc, x, xc, xb, 1LL * xr * xc, y, yc, yb, 1LL * xc * yc, z, yc, 1LL * xr * yc, zb, 0, 0);
+    return gemm_call(ctx, dtype, 0, 0, xr, yc, xc, x, xc, xb, 1LL * xr * xc, y, yc, yb, 1LL * xc * yc, z, yc, 1LL * xr * yc, zb, 0, 0, epi,
+                     relu_out);
 }
 
-int d8k_matmul_grad_x(d8k_ctx* ctx, int dtype, void* dx, int xb, int xr, int xc, const void* y, int yb, int yc, const void* dz) {
+static int matmul_grad_x_impl(d8k_ctx* ctx, int dtype, void* dx, int xb, int xr, int xc, const void* y, int yb, int yc, const void* dz,
+                              int accumulate, int epi, const void* h, void* dh, int accumulate_dh) {
     if (int rc = check_ctx(ctx)) return rc;
     if (int rc = check_dtype(dtype)) return rc;
     if (int rc = check_matmul(xb, xr, xc, yb, yc)) return rc;
-    // dx[M x xc] += dz[M x yc] * y^T ; y is [xc x yc], i.e. already "N x K" for this product
-    if (yb == 1) return d8k_gemm(ctx, dtype, 0, 1, xb * xr, xc, yc, dz, yc, 1, 0, y, yc, 1, 0, dx, xc, 0, 1, 1, 0);
+    void* hh = const_cast<void*>(h);
+    const int beta = accumulate ? 1 : 0, beta2 = accumulate_dh ? 1 : 0;
+    // dx[M x xc] (+)= dz[M x yc] * y^T ; y is [xc x yc], i.e. already "N x K" for this product
+    if (yb == 1) return gemm_call(ctx, dtype, 0, 1, xb * xr, xc, yc, dz, yc, 1, 0, y, yc, 1, 0, dx, xc, 0, 1, beta, 0, epi, hh, dh, beta2);
     int zb = xb > yb ? xb : yb;
     if (xb == 1 && zb > 1)  // broadcast x: every batch entry adds into the one dx (deep8/src/math/MatrixMultiply.cu:220-231)
-        return d8k_gemm(ctx, dtype, 0, 1, xr, xc, yc, dz, yc, zb, 1LL * xr * yc, y, yc, yb, 1LL * xc * yc, dx, xc, 0, zb, 1, 1);
-    return d8k_gemm(ctx, dtype, 0, 1, xr, xc, yc, dz, yc, zb, 1LL * xr * yc, y, yc, yb, 1LL * xc * yc, dx, xc, 1LL * xr * xc, zb, 1, 0);
+        return gemm_call(ctx, dtype, 0, 1, xr, xc, yc, dz, yc, zb, 1LL * xr * yc, y, yc, yb, 1LL * xc * yc, dx, xc, 0, zb, beta, 1, epi, hh, dh,
+                         beta2);
+    return gemm_call(ctx, dtype, 0, 1, xr, xc, yc, dz, yc, zb, 1LL * xr * yc, y, yc, yb, 1LL * xc * yc, dx, xc, 1LL * xr * xc, zb, beta, 0, epi,
+                     hh, dh, beta2);
 }
 
-int d8k_matmul_grad_y(d8k_ctx* ctx, int dtype, const void* x, int xb, int xr, int xc, void* dy, int yb, int yc, const void* dz) {
+static int matmul_grad_y_impl(d8k_ctx* ctx, int dtype, const void* x, int xb, int xr, int xc, void* dy, int yb, int yc, const void* dz,
+                              int accumulate) {
     if (int rc = check_ctx(ctx)) return rc;
     if (int rc = check_dtype(dtype)) return rc;
     if (int rc = check_matmul(xb, xr, xc, yb, yc)) return rc;
-    // dy[xc x yc] += x^T * dz ; with yb == 1 the batch joins the contraction: K = xb * xr (deep8/src/math/MatrixMultiply.cu:393-398)
-    if (yb == 1) return d8k_gemm(ctx, dtype, 1, 0, xc, yc, xb * xr, x, xc, 1, 0, dz, yc, 1, 0, dy, yc, 0, 1, 1, 0);
-    return d8k_gemm(ctx, dtype, 1, 0, xc, yc, xr, x, xc, xb, 1LL * xr * xc, dz, yc, yb, 1LL * xr * yc, dy, yc, 1LL * xc * yc, yb, 1, 0);
+    const int beta = accumulate ? 1 : 0;
+    // dy[xc x yc] (+)= x^T * dz ; with yb == 1 the batch joins the contraction: K = xb * xr (deep8/src/math/MatrixMultiply.cu:393-398)
+    if (yb == 1) return gemm_call(ctx, dtype, 1, 0, xc, yc, xb * xr, x, xc, 1, 0, dz, yc, 1, 0, dy, yc, 0, 1, beta, 0);
+    return gemm_call(ctx, dtype, 1, 0, xc, yc, xr, x, xc, xb, 1LL * xr * xc, dz, yc, yb, 1LL * xr * yc, dy, yc, 1LL * xc * yc, yb, beta, 0);
+}
+
+int d8k_matmul_forward(d8k_ctx* ctx, int dtype, const void* x, int xb, int xr, int xc, const void* y, int yb, int yc, void* z) {
+    return matmul_forward_impl(ctx, dtype, x, xb, xr, xc, y, yb, yc, z, 0, nullptr);
+}
+int d8k_matmul_grad_x(d8k_ctx* ctx, int dtype, void* dx, int xb, int xr, int xc, const void* y, int yb, int yc, const void* dz) {
+    return matmul_grad_x_impl(ctx, dtype, dx, xb, xr, xc, y, yb, yc, dz, 1, 0, nullptr, nullptr, 0);
+}
+int d8k_matmul_grad_y(d8k_ctx* ctx, int dtype, const void* x, int xb, int xr, int xc, void* dy, int yb, int yc, const void* dz) {
+    return matmul_grad_y_impl(ctx, dtype, x, xb, xr, xc, dy, yb, yc, dz, 1);
+}
+int d8k_matmul_grad_x_into(d8k_ctx* ctx, int dtype, void* dx, int xb, int xr, int xc, const void* y, int yb, int yc, const void* dz,
+                           int accumulate) {
+    return matmul_grad_x_impl(ctx, dtype, dx, xb, xr, xc, y, yb, yc, dz, accumulate, 0, nullptr, nullptr, 0);
+}
+int d8k_matmul_grad_y_into(d8k_ctx* ctx, int dtype, const void* x, int xb, int xr, int xc, void* dy, int yb, int yc, const void* dz,
+                           int accumulate) {
+    return matmul_grad_y_impl(ctx, dtype, x, xb, xr, xc, dy, yb, yc, dz, accumulate);
+}
+int d8k_matmul_forward_relu(d8k_ctx* ctx, int dtype, const void* x, int xb, int xr, int xc, const void* y, int yb, int yc, void* z, void* a) {
+    if (!a) return fail(D8K_ERR_ARGUMENT, "d8k_matmul_forward_relu: null pointer");
+    return matmul_forward_impl(ctx, dtype, x, xb, xr, xc, y, yb, yc, z, 1, a);
+}
+int d8k_matmul_grad_x_relu(d8k_ctx* ctx, int dtype, void* dx, int xb, int xr, int xc, const void* y, int yb, int yc, const void* dz,
+                           int accumulate_dx, const void* h, void* dh, int accumulate_dh) {
+    if (!h || !dh) return fail(D8K_ERR_ARGUMENT, "d8k_matmul_grad_x_relu: null pointer");
+    return matmul_grad_x_impl(ctx, dtype, dx, xb, xr, xc, y, yb, yc, dz, accumulate_dx, 2, h, dh, accumulate_dh);
 }
 
 int d8k_conv2d_out_dim(int in, int filter, int stride, int dilation, int covered) {

@@ -287,8 +287,7 @@ d8k_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
         for (int w = pair; ok && w < p.total_work; w += num_pairs) {
             PairWork it = decode_pair_work(p, w);
             const int row = it.m0 + 128 * static_cast<int>(rank) + row_in_tile;
-            OutT* crow = reinterpret_cast<OutT*>(p.C) + static_cast<long long>(it.batch) * p.c_batch_stride +
-                         static_cast<long long>(row) * p.ldc;
+            const long long crow = static_cast<long long>(it.batch) * p.c_batch_stride + static_cast<long long>(row) * p.ldc;
             const long long tw = p.prof ? clock64() : 0;
             ok = wait_bar(tfull_bar(acc), acc_phase, &s_abort, p.status, (kRoleEpilogue << 8) | 3);
             if (!ok) break;

@@ -42,6 +42,9 @@ struct GemmProblem {
     int batch = 1;    // independent outputs
     int kbatch = 1;   // batches summed into one output
     int beta = 0;
+    int epi = 0, beta2 = 0;  // fused element-wise tail (GemmParams::epi)
+    void* E1 = nullptr;
+    void* E2 = nullptr;
     void* ws = nullptr;  // optional caller scratch for split-K
     size_t ws_bytes = 0;
 };

@@ -67,6 +67,9 @@ struct GemmParams {
     int tiles_m, tiles_n, raster_group;
     int total_work;    // batch * tiles_m * tiles_n * splits
     int beta;          // 0: overwrite, 1: accumulate into C
+    int epi, beta2;    // fused element-wise tail, see store_row_chunk
+    void* E1;          // epi 1: relu(C) is written here; epi 2: ReLu's input is read here
+    void* E2;          // epi 2: ReLu's input gradient, overwritten (beta2 == 0) or accumulated (beta2 == 1)
     void* C;
     long long ldc, c_batch_stride;
     float* ws;         // split-K partial tiles: total_work * 128 * BN floats
@@ -261,56 +264,124 @@ __device__ __forceinline__ void store_chunk_smem(uint32_t addr, uint32_t lo_offs
 }
 
 // ------------------------------------------------------------------------------------------------ epilogue helpers
+__device__ __forceinline__ float epi_to_float(float v) { return v; }
+__device__ __forceinline__ float epi_to_float(__half v) { return __half2float(v); }
+template <typename T>
+__device__ __forceinline__ T epi_from_float(float v);
+template <>
+__device__ __forceinline__ float epi_from_float<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ __half epi_from_float<__half>(float v) { return __float2half_rn(v); }
+
+// 16 bytes of OutT <-> floats, two halves per conversion instruction
 template <typename OutT>
-__device__ __forceinline__ void store_row_chunk(const GemmParams& p, OutT* crow, int col0, const float* acc) {
-    // crow points at C(row, 0); stores acc[0..32) to columns [col0, col0 + 32) clipped to N, adding C first if beta
-    constexpr int VEC = 16 / sizeof(OutT);
-    OutT* dst = crow + col0;
+struct EpiVec;
+template <>
+struct EpiVec<float> {
+    static constexpr int N = 4;
+    static __device__ __forceinline__ void unpack(const uint4& w, float* f) {
+        f[0] = __uint_as_float(w.x); f[1] = __uint_as_float(w.y); f[2] = __uint_as_float(w.z); f[3] = __uint_as_float(w.w);
+    }
+    static __device__ __forceinline__ uint4 pack(const float* f) {
+        return make_uint4(__float_as_uint(f[0]), __float_as_uint(f[1]), __float_as_uint(f[2]), __float_as_uint(f[3]));
+    }
+};
+template <>
+struct EpiVec<__half> {
+    static constexpr int N = 8;
+    static __device__ __forceinline__ void unpack(const uint4& w, float* f) {
+        const __half2* h = reinterpret_cast<const __half2*>(&w);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            float2 t = __half22float2(h[i]);
+            f[2 * i] = t.x;
+            f[2 * i + 1] = t.y;
+        }
+    }
+    static __device__ __forceinline__ uint4 pack(const float* f) {
+        uint4 w;
+        __half2* h = reinterpret_cast<__half2*>(&w);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) h[i] = __floats2half2_rn(f[2 * i], f[2 * i + 1]);
+        return w;
+    }
+};
+
+// Element-wise tail of the epilogue for one row and 32 columns [col0, col0 + 32), clipped to N.  `off` is the element
+// offset of C(row, 0); E1 and E2 have C's shape and pitch.  With c = OutT(acc + (beta ? C : 0)):
+//   EPI 0: C = c
+//   EPI 1: C = c; E1 = c > 0 ? c : 0                     MatrixMultiply followed by ReLu (deep8/src/math/ReLu.cu:11-15)
+//   EPI 2: C = c; E2 = (beta2 ? E2 : 0) + (E1 > 0 ? c : 0)   gradient of x followed by ReLu's gradient with E1 = ReLu's
+//                                                        input (deep8/src/math/ReLu.cu:58-63); sums are rounded to OutT
+template <typename OutT, int EPI>
+__device__ __forceinline__ void store_row_chunk_epi(const GemmParams& p, long long off, int col0, const float* acc) {
+    using V = EpiVec<OutT>;
+    constexpr int VEC = V::N;
+    OutT* dst = reinterpret_cast<OutT*>(p.C) + off + col0;
+    OutT* e1 = reinterpret_cast<OutT*>(p.E1) + off + col0;
+    OutT* e2 = reinterpret_cast<OutT*>(p.E2) + off + col0;
     bool vec_ok = (col0 + 32 <= p.N) && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0);
+    if (EPI >= 1) vec_ok = vec_ok && ((reinterpret_cast<uintptr_t>(e1) & 15) == 0);
+    if (EPI == 2) vec_ok = vec_ok && ((reinterpret_cast<uintptr_t>(e2) & 15) == 0);
     if (vec_ok) {
 #pragma unroll
         for (int v = 0; v < 32 / VEC; ++v) {
-            uint4* q = reinterpret_cast<uint4*>(dst) + v;
-            if constexpr (sizeof(OutT) == 4) {
-                float4 o = make_float4(acc[v * 4 + 0], acc[v * 4 + 1], acc[v * 4 + 2], acc[v * 4 + 3]);
-                if (p.beta) {
-                    float4 old = *reinterpret_cast<const float4*>(q);
-                    o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
-                }
-                *reinterpret_cast<float4*>(q) = o;
-            } else {
-                uint4 packed;
-                __half2* h = reinterpret_cast<__half2*>(&packed);
-                if (p.beta) {
-                    uint4 oldv = *q;
-                    const __half2* oh = reinterpret_cast<const __half2*>(&oldv);
+            float c[VEC];
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        float2 of = __half22float2(oh[i]);
-                        h[i] = __floats2half2_rn(acc[v * 8 + 2 * i] + of.x, acc[v * 8 + 2 * i + 1] + of.y);
-                    }
+            for (int i = 0; i < VEC; ++i) c[i] = acc[v * VEC + i];
+            if (p.beta) {
+                float old[VEC];
+                V::unpack(reinterpret_cast<const uint4*>(dst)[v], old);
+#pragma unroll
+                for (int i = 0; i < VEC; ++i) c[i] += old[i];
+            }
+            const uint4 cw = V::pack(c);
+            reinterpret_cast<uint4*>(dst)[v] = cw;
+            if (EPI != 0) V::unpack(cw, c);  // the stored (rounded) values drive the fused tails
+            if (EPI == 1) {
+#pragma unroll
+                for (int i = 0; i < VEC; ++i) c[i] = c[i] > 0.f ? c[i] : 0.f;
+                reinterpret_cast<uint4*>(e1)[v] = V::pack(c);
+            } else if (EPI == 2) {
+                float x[VEC], g[VEC];
+                V::unpack(reinterpret_cast<const uint4*>(e1)[v], x);
+                if (p.beta2) {
+                    V::unpack(reinterpret_cast<const uint4*>(e2)[v], g);
                 } else {
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) h[i] = __floats2half2_rn(acc[v * 8 + 2 * i], acc[v * 8 + 2 * i + 1]);
+                    for (int i = 0; i < VEC; ++i) g[i] = 0.f;
                 }
-                *q = packed;
+#pragma unroll
+                for (int i = 0; i < VEC; ++i)
+                    if (x[i] > 0.f) g[i] += c[i];
+                reinterpret_cast<uint4*>(e2)[v] = V::pack(g);
             }
         }
     } else {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
+        for (int i = 0; i < 32; ++i) {  // fully unrolled: a dynamic index would push the accumulators to local memory
             if (col0 + i < p.N) {
                 float v = acc[i];
-                if constexpr (sizeof(OutT) == 4) {
-                    if (p.beta) v += dst[i];
-                    dst[i] = v;
-                } else {
-                    if (p.beta) v += __half2float(dst[i]);
-                    dst[i] = __float2half_rn(v);
+                if (p.beta) v += epi_to_float(dst[i]);
+                OutT c = epi_from_float<OutT>(v);
+                dst[i] = c;
+                if (EPI == 1) {
+                    e1[i] = epi_to_float(c) > 0.f ? c : epi_from_float<OutT>(0.f);
+                } else if (EPI == 2) {
+                    OutT g = p.beta2 ? e2[i] : epi_from_float<OutT>(0.f);
+                    if (epi_to_float(e1[i]) > 0.f) g = epi_from_float<OutT>(epi_to_float(g) + epi_to_float(c));
+                    e2[i] = g;
                 }
             }
         }
     }
+}
+
+template <typename OutT>
+__device__ __forceinline__ void store_row_chunk(const GemmParams& p, long long off, int col0, const float* acc) {
+    if (p.epi == 0) store_row_chunk_epi<OutT, 0>(p, off, col0, acc);
+    else if (p.epi == 1) store_row_chunk_epi<OutT, 1>(p, off, col0, acc);
+    else store_row_chunk_epi<OutT, 2>(p, off, col0, acc);
 }
 
 // ------------------------------------------------------------------------------------------------ the kernel
@@ -472,8 +543,7 @@ d8k_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         for (int w = blockIdx.x; ok && w < p.total_work; w += gridDim.x) {
             WorkItem it = decode_work(p, w, BN);
             const int row = it.m0 + row_in_tile;
-            OutT* crow = reinterpret_cast<OutT*>(p.C) + static_cast<long long>(it.batch) * p.c_batch_stride +
-                         static_cast<long long>(row) * p.ldc;
+            const long long crow = static_cast<long long>(it.batch) * p.c_batch_stride + static_cast<long long>(row) * p.ldc;
             float* part = p.ws + (static_cast<size_t>(w) * kBM + row_in_tile) * BN;
             if constexpr (Cfg::CHUNK_KB == 0) {
                 ok = wait_bar(tfull_bar(acc), acc_phase, &s_abort, p.status, (kRoleEpilogue << 8) | 3);

@@ -154,6 +154,7 @@ int run_gemm(Ctx* ctx, const GemmProblem& g) {
     if (!g.C || (g.K > 0 && (!g.a.ptr || !g.b.ptr))) return fail(1, "gemm: null pointer");
     if (g.dtype != 0 && g.dtype != 1) return fail(1, "gemm: dtype must be D8K_F16 or D8K_F32");
     if (g.beta != 0 && g.beta != 1) return fail(1, "gemm: beta must be 0 or 1");
+    if (g.epi < 0 || g.epi > 2 || (g.epi >= 1 && !g.E1) || (g.epi == 2 && !g.E2)) return fail(1, "gemm: bad fused epilogue arguments");
     const int esize = g.dtype == 1 ? 4 : 2;
     if (g.K == 0) {  // an empty contraction is a zero matrix
         if (g.beta == 0) {
@@ -186,6 +187,10 @@ int run_gemm(Ctx* ctx, const GemmProblem& g) {
     if (p.raster_group < 1) p.raster_group = 1;
     p.total_work = pl.tiles * pl.splits;
     p.beta = g.beta;
+    p.epi = g.epi;
+    p.beta2 = g.beta2;
+    p.E1 = g.E1;
+    p.E2 = g.E2;
     p.C = g.C;
     p.ldc = g.ldc;
     p.c_batch_stride = g.c_batch_stride;

@@ -106,21 +106,41 @@ class Context:
         check(self.lib.d8k_matmul_forward(self.h, dt, _p(x), xb, xr, xc, _p(y), yb, yc, _p(z)))
         return z
 
-    def matmul_grad_x(self, x, dx, y, dz):
+    def matmul_grad_x(self, x, dx, y, dz, accumulate=True):
+        """dx (+)= dz y^T.  accumulate=False overwrites (first contribution, no zeroGradient needed)."""
         dt = _same(x, dx, y, dz)
         xb, xr, xc, yb, yc = self._mm_dims(x, y)
         if dx.shape != x.shape or tuple(dz.shape) != (max(xb, yb), xr, yc):
             raise ValueError("the shape is error")
-        check(self.lib.d8k_matmul_grad_x(self.h, dt, _p(dx), xb, xr, xc, _p(y), yb, yc, _p(dz)))
+        check(self.lib.d8k_matmul_grad_x_into(self.h, dt, _p(dx), xb, xr, xc, _p(y), yb, yc, _p(dz), int(accumulate)))
         return dx
 
-    def matmul_grad_y(self, x, y, dy, dz):
+    def matmul_grad_y(self, x, y, dy, dz, accumulate=True):
         dt = _same(x, y, dy, dz)
         xb, xr, xc, yb, yc = self._mm_dims(x, y)
         if dy.shape != y.shape or tuple(dz.shape) != (max(xb, yb), xr, yc):
             raise ValueError("the shape is error")
-        check(self.lib.d8k_matmul_grad_y(self.h, dt, _p(x), xb, xr, xc, _p(dy), yb, yc, _p(dz)))
+        check(self.lib.d8k_matmul_grad_y_into(self.h, dt, _p(x), xb, xr, xc, _p(dy), yb, yc, _p(dz), int(accumulate)))
         return dy
+
+    def matmul_forward_relu(self, x, y, z, a):
+        """z = x y and a = relu(z) in one launch (MatrixMultiply node followed by ReLu node)."""
+        dt = _same(x, y, z, a)
+        xb, xr, xc, yb, yc = self._mm_dims(x, y)
+        if tuple(z.shape) != (max(xb, yb), xr, yc) or a.shape != z.shape:
+            raise ValueError("the shape is error")
+        check(self.lib.d8k_matmul_forward_relu(self.h, dt, _p(x), xb, xr, xc, _p(y), yb, yc, _p(z), _p(a)))
+        return z, a
+
+    def matmul_grad_x_relu(self, x, dx, y, dz, h, dh, accumulate_dx=True, accumulate_dh=True):
+        """For x = relu(h): dx (+)= dz y^T, then dh (+)= (h > 0 ? dx : 0), in one launch."""
+        dt = _same(x, dx, y, dz, h, dh)
+        xb, xr, xc, yb, yc = self._mm_dims(x, y)
+        if dx.shape != x.shape or tuple(dz.shape) != (max(xb, yb), xr, yc) or h.shape != x.shape or dh.shape != x.shape:
+            raise ValueError("the shape is error")
+        check(self.lib.d8k_matmul_grad_x_relu(self.h, dt, _p(dx), xb, xr, xc, _p(y), yb, yc, _p(dz), int(accumulate_dx), _p(h), _p(dh),
+                                              int(accumulate_dh)))
+        return dx, dh
 
     # ------------------------------------------------------------------------------------------------ Conv2d
     def conv2d_out_shape(self, x, w, covered, stride, dilation):

@@ -86,6 +86,22 @@ D8K_API int d8k_matmul_grad_x(d8k_ctx* ctx, int dtype, void* dx, int xb, int xr,
 /* MatrixMultiplyGradYGPU (MatrixMultiply.cu:508-551): dy[b % yb] += x[b % xb]^T * dz[b] (summed over b when yb == 1). */
 D8K_API int d8k_matmul_grad_y(d8k_ctx* ctx, int dtype, const void* x, int xb, int xr, int xc, void* dy, int yb, int yc, const void* dz);
 
+/* The two gradient entry points with the accumulation made explicit: accumulate != 0 is the reference's += (beta = 1 in
+ * its gemm calls, MatrixMultiply.cu:203, 391); accumulate == 0 overwrites, for an executor that knows this is the first
+ * contribution to the gradient and skips Variable::zeroGradient (deep8/src/model/EagerExecutor.cpp:51-65). */
+D8K_API int d8k_matmul_grad_x_into(d8k_ctx* ctx, int dtype, void* dx, int xb, int xr, int xc, const void* y, int yb, int yc, const void* dz,
+                           int accumulate);
+D8K_API int d8k_matmul_grad_y_into(d8k_ctx* ctx, int dtype, const void* x, int xb, int xr, int xc, void* dy, int yb, int yc, const void* dz,
+                           int accumulate);
+/* MatrixMultiplyGPU followed by ReLuGPU (deep8/src/math/ReLu.cu:17-56) in one launch: z = x * y and a = max(z, 0), both
+ * written from the accumulator in the epilogue; the results are those of the two separate calls. */
+D8K_API int d8k_matmul_forward_relu(d8k_ctx* ctx, int dtype, const void* x, int xb, int xr, int xc, const void* y, int yb, int yc, void* z, void* a);
+/* MatrixMultiplyGradXGPU followed by ReLuGradGPU (deep8/src/math/ReLu.cu:58-110) in one launch, for x = relu(h):
+ * dx (+)= dz * y^T, then dh (+)= (h > 0 ? dx : 0) with the dx just stored.  Valid when this product is dx's only remaining
+ * contribution, which holds for a chain x = relu(h), z = x * y.  Same rounding as the separate calls. */
+D8K_API int d8k_matmul_grad_x_relu(d8k_ctx* ctx, int dtype, void* dx, int xb, int xr, int xc, const void* y, int yb, int yc, const void* dz,
+                           int accumulate_dx, const void* h, void* dh, int accumulate_dh);
+
 /* Conv2d shape helpers: output extent (deep8/src/nodes/Conv2d.cpp:47-63) and DeConv2d's (deep8/src/nodes/DeConv2d.cpp:36-52). */
 D8K_API int d8k_conv2d_out_dim(int in, int filter, int stride, int dilation, int covered);
 D8K_API int d8k_deconv2d_out_dim(int in, int filter, int stride, int covered);

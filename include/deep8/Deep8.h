@@ -1,0 +1,484 @@
+// C++ host side of the path: Deep8's operator / executor / device interface for MatrixMultiply, Conv2d, DeConv2d
+// (and their neighbour ReLu), implemented over the C ABI of include/d8k.h.  Same class names, members, argument meaning
+// and error behaviour as the reference (paths below are relative to the reference project):
+//
+//   Shape, ElementType/DType        deep8/include/model/Shape.h, ElementType.h
+//   Device, GPUDevice, GPUMemoryPool deep8/include/model/Device.h, GPUDevice.h, GPUMemoryPool.h
+//   TensorStorage, Tensor           deep8/include/model/TensorStorage.h, Tensor.h
+//   Node, Variable, Function        deep8/include/nodes/Node.h, Variable.h, Function.h
+//   MatrixMultiply, Conv2d, DeConv2d, ReLu   deep8/include/nodes/*.h
+//   Executor, EagerExecutor         deep8/include/model/Executor.h, EagerExecutor.h
+//   Math::*                          deep8/include/math/{MatrixMultiply,Conv2d,DeConv2d,ReLu}.h
+//   parameter(), operator*, conv2d(), deConv2d(), relu(), backward()   deep8/include/model/Net.h
+//
+// There is no CPU device here: every tensor lives on a GPU and every operator runs the sm_100a kernels.
+#ifndef DEEP8_B200_DEEP8_H
+#define DEEP8_B200_DEEP8_H
+
+#include <cstddef>
+#include <cstdint>
+#include <map>
+#include <sstream>
+#include <stdexcept>
+#include <string>
+#include <unordered_map>
+#include <unordered_set>
+#include <vector>
+
+#include "../d8k.h"
+
+// Error convention of deep8/include/basic/Exception.h: "<file>:<line>: <text>."
+#define DEEP8_RUNTIME_ERROR(message)                        \
+    {                                                       \
+        std::ostringstream d8_oss__;                        \
+        d8_oss__ << __FILE__ << ":" << __LINE__ << ": " << message << "."; \
+        throw std::runtime_error(d8_oss__.str());           \
+    }
+
+#define DEEP8_ARGUMENT_CHECK(condition, message)            \
+    if (!(condition)) {                                     \
+        std::ostringstream d8_oss__;                        \
+        d8_oss__ << __FILE__ << ":" << __LINE__ << ": " << message << "."; \
+        throw std::invalid_argument(d8_oss__.str());        \
+    }
+
+#define DEEP8_ASSERT(condition, message) DEEP8_ARGUMENT_CHECK(condition, message)
+
+#define MAX_TENSOR_DIMS 4
+#define DEEP8_API __attribute__((visibility("default")))
+
+namespace Deep8 {
+
+// ------------------------------------------------------------------------------------------------ element types
+enum class DType {
+    UnKnown = 0, Bool = 1, Uint8 = 2, Int8 = 3, Uint16 = 4, Int16 = 5, Uint32 = 6, Int32 = 7, Uint64 = 8, Int64 = 9,
+    Float16 = 10, Float32 = 11, Float64 = 12,
+};
+
+struct half_t {  // storage-only stand-in for the reference's `half` on the host side
+    uint16_t bits;
+};
+
+class DEEP8_API ElementType {
+    ElementType(DType d, size_t bw, std::string n) : id(d), byteWidth(bw), name(std::move(n)) {}
+
+public:
+    DType id;
+    size_t byteWidth;
+    std::string name;
+
+    bool operator==(const ElementType& o) const { return id == o.id; }
+    bool operator!=(const ElementType& o) const { return id != o.id; }
+
+    static ElementType unknown() { return ElementType(DType::UnKnown, 0, "unknown"); }
+    static ElementType from(DType type);
+    template <typename T>
+    static ElementType from();
+    template <typename T>
+    bool is() const { return id == from<T>().id; }
+};
+template <> inline ElementType ElementType::from<float>() { return from(DType::Float32); }
+template <> inline ElementType ElementType::from<double>() { return from(DType::Float64); }
+template <> inline ElementType ElementType::from<half_t>() { return from(DType::Float16); }
+template <> inline ElementType ElementType::from<int32_t>() { return from(DType::Int32); }
+template <> inline ElementType ElementType::from<int64_t>() { return from(DType::Int64); }
+template <> inline ElementType ElementType::from<uint8_t>() { return from(DType::Uint8); }
+
+// ------------------------------------------------------------------------------------------------ Shape
+class DEEP8_API Shape {
+public:
+    size_t batch;
+    size_t nDims;
+    size_t dims[MAX_TENSOR_DIMS];
+    size_t strides[MAX_TENSOR_DIMS];
+
+    Shape();
+    Shape(const Shape&) = default;
+    Shape(size_t batch, const Shape& other);
+    explicit Shape(std::vector<size_t> list);
+    explicit Shape(size_t batch, std::vector<size_t> list);
+    Shape& operator=(const Shape&) = default;
+
+    bool operator==(const Shape&) const;
+    bool operator!=(const Shape& o) const { return !(*this == o); }
+    size_t operator[](size_t d) const { return dim(d); }
+
+    void reShape(Shape& other);
+    bool equalExceptBatch(const Shape& other) const;
+    size_t size() const;       // batch * dims[0] * dims[1] ...
+    size_t batchSize() const;  // size() / batch
+    size_t dim(size_t d) const;
+    size_t stride(size_t d) const;
+    size_t row() const;
+    size_t col() const;
+    std::string toStr() const;
+
+private:
+    void updateStrides();
+};
+
+// ------------------------------------------------------------------------------------------------ devices
+enum class DeviceType { CPU = 0, GPU = 1 };
+
+class DEEP8_API Device {
+public:
+    DeviceType type;
+    explicit Device(DeviceType t) : type(t) {}
+    virtual ~Device() = default;
+
+    virtual void* malloc(size_t size) = 0;
+    virtual void free(void* ptr) = 0;
+    virtual void zero(void* ptr, size_t size) = 0;
+    virtual void copy(const void* from, void* to, size_t size) = 0;
+    virtual void copyFromCPUToGPU(const void* from, void* to, size_t size) = 0;
+    virtual void copyFromGPUToCPU(const void* from, void* to, size_t size) = 0;
+    virtual void copyFromGPUToGPU(const void* from, void* to, size_t size) = 0;
+    virtual void* mallocCPU(size_t size) = 0;
+    virtual void freeCPU(void* ptr) = 0;
+};
+
+// Buddy allocator over cudaMalloc'd blocks (deep8/include/model/GPUMemoryPool.h, MemoryPool.h:13-23): requests are rounded
+// up to a power of two of at least 128 bytes, served from the smallest free chunk that fits (split in halves), and a
+// freed chunk merges with its free buddy.  A request larger than one block throws; malloc(0) returns nullptr.  All
+// bookkeeping is on the host.  The block size defaults to the reference's 512 MiB and can be raised for 180 GB parts.
+class DEEP8_API GPUMemoryPool {
+public:
+    int deviceId;
+    size_t gpuBlockSize;
+
+    explicit GPUMemoryPool(int id = 0, size_t blockSize = (static_cast<size_t>(1) << 29));
+    ~GPUMemoryPool();
+    GPUMemoryPool(const GPUMemoryPool&) = delete;
+    GPUMemoryPool& operator=(const GPUMemoryPool&) = delete;
+
+    void* malloc(size_t size);
+    void free(void* ptr);
+    void zero(void* ptr, size_t size);
+    void copy(const void* from, void* to, size_t size);  // device to device
+    void copyFromCPUToGPU(const void* from, void* to, size_t size);
+    void copyFromGPUToCPU(const void* from, void* to, size_t size);
+    void copyFromGPUToGPU(const void* from, void* to, size_t size);
+    void* mallocCPU(size_t size);
+    void freeCPU(void* ptr);
+
+    size_t blockCount() const { return blocks.size(); }
+    size_t bytesInUse() const { return inUse; }
+    std::string toString() const;
+    void printInfo() const;
+
+private:
+    struct Chunk {
+        size_t block;   // which cudaMalloc'd block
+        size_t offset;  // byte offset inside the block, a multiple of its size
+        int level;      // size = 128 << level
+    };
+    int maxLevel;
+    std::vector<char*> blocks;
+    std::vector<std::map<std::pair<size_t, size_t>, bool>> freeByLevel;  // (block, offset) of free chunks per level
+    std::unordered_map<void*, Chunk> live;
+    size_t inUse = 0;
+    void addBlock();
+    static int levelFor(size_t size);
+};
+
+class DEEP8_API GPUDevice : public Device {
+public:
+    GPUMemoryPool* memoryPool;
+    int deviceId;
+    d8k_ctx* kernels;  // stands where the reference keeps its cuBLAS handle
+
+    GPUDevice();
+    explicit GPUDevice(int id, size_t poolBlockSize = (static_cast<size_t>(1) << 29));
+    ~GPUDevice() override;
+
+    void* malloc(size_t size) override;
+    void free(void* ptr) override;
+    void* mallocCPU(size_t size) override;
+    void freeCPU(void* ptr) override;
+    void zero(void* ptr, size_t size) override;
+    void copy(const void* from, void* to, size_t size) override;
+    void copyFromCPUToGPU(const void* from, void* to, size_t size) override;
+    void copyFromGPUToCPU(const void* from, void* to, size_t size) override;
+    void copyFromGPUToGPU(const void* from, void* to, size_t size) override;
+    void synchronize();
+};
+
+// ------------------------------------------------------------------------------------------------ tensors
+// Reference-counted handle on a pool allocation; the last copy returns the memory to the device (TensorStorage.cpp).
+class DEEP8_API TensorStorage {
+public:
+    void* ptr;
+    size_t* refPtr;
+    size_t size;
+    Device* device;
+
+    TensorStorage();
+    TensorStorage(void* p, size_t* refP, size_t s, Device* d);
+    TensorStorage(const TensorStorage& other);
+    ~TensorStorage();
+    TensorStorage& operator=(const TensorStorage& other);
+
+private:
+    void release();
+};
+
+class DEEP8_API Tensor {
+public:
+    TensorStorage storage;
+    size_t offset;  // bytes into the storage
+    Shape shape;
+    ElementType elementType;
+
+    Tensor();
+    explicit Tensor(Shape& s);
+    Tensor(TensorStorage& ts, size_t off, Shape& s, ElementType et);
+    Tensor(TensorStorage& ts, size_t off, std::vector<size_t>& list, ElementType et);
+    Tensor(TensorStorage& ts, size_t off, size_t batch, std::vector<size_t>& list, ElementType et);
+
+    DeviceType deviceType() const;
+    Device* device() const;
+    size_t* refPtr() const { return storage.refPtr; }
+    size_t refCount() const { return storage.refPtr ? *storage.refPtr : 0; }
+    void* raw() const;
+    bool isScalar() const;
+    void zero();
+    size_t byteCount() const;
+    size_t batch() const { return shape.batch; }
+    size_t nDims() const { return shape.nDims; }
+    size_t size() const { return shape.size(); }
+    size_t batchSize() const { return shape.batchSize(); }
+    size_t row() const { return shape.row(); }
+    size_t col() const { return shape.col(); }
+    size_t dim(size_t d) const { return shape.dim(d); }
+    size_t stride(size_t d) const { return shape.stride(d); }
+
+    template <typename T>
+    T* data() const {
+        DEEP8_ARGUMENT_CHECK(elementType.is<T>(), "Tensor type is error, type is: " << elementType.name);
+        return static_cast<T*>(raw());
+    }
+    template <typename T>
+    bool is() const { return elementType.is<T>(); }
+};
+
+// ------------------------------------------------------------------------------------------------ math (GPU only)
+namespace Math {
+DEEP8_API void MatrixMultiply(const Tensor& x, const Tensor& y, Tensor& z);
+DEEP8_API void MatrixMultiplyGPU(const Tensor& x, const Tensor& y, Tensor& z);
+DEEP8_API void MatrixMultiplyGradX(const Tensor& x, Tensor& dx, const Tensor& y, const Tensor& z, const Tensor& dz);
+DEEP8_API void MatrixMultiplyGradXGPU(const Tensor& x, Tensor& dx, const Tensor& y, const Tensor& z, const Tensor& dz);
+DEEP8_API void MatrixMultiplyGradY(const Tensor& x, const Tensor& y, Tensor& dy, const Tensor& z, const Tensor& dz);
+DEEP8_API void MatrixMultiplyGradYGPU(const Tensor& x, const Tensor& y, Tensor& dy, const Tensor& z, const Tensor& dz);
+
+DEEP8_API size_t Conv2dInterimSize(const Tensor& x, const Tensor& y, Tensor& z, bool covered, int strideY, int strideX, int dilationY, int dilationX);
+DEEP8_API void Conv2d(const Tensor& x, const Tensor& y, Tensor& z, bool covered, int strideY, int strideX, int dilationY, int dilationX, void* interimPtr);
+DEEP8_API void Conv2dGPU(const Tensor& x, const Tensor& y, Tensor& z, bool covered, int strideY, int strideX, int dilationY, int dilationX, void* xcol);
+DEEP8_API size_t Conv2dGradXInterimSize(const Tensor& x, Tensor& dx, const Tensor& y, const Tensor& z, const Tensor& dz, bool covered, int strideY, int strideX, int dilationY, int dilationX);
+DEEP8_API void Conv2dGradX(const Tensor& x, Tensor& dx, const Tensor& y, const Tensor& z, const Tensor& dz, bool covered, int strideY, int strideX, int dilationY, int dilationX, void* interimPtr);
+DEEP8_API void Conv2dGradXGPU(const Tensor& x, Tensor& dx, const Tensor& y, const Tensor& z, const Tensor& dz, bool covered, int strideY, int strideX, int dilationY, int dilationX, void* dxcol);
+DEEP8_API size_t Conv2dGradYInterimSize(const Tensor& x, const Tensor& y, Tensor& dy, const Tensor& z, const Tensor& dz, bool covered, int strideY, int strideX, int dilationY, int dilationX);
+DEEP8_API void Conv2dGradY(const Tensor& x, const Tensor& y, Tensor& dy, const Tensor& z, const Tensor& dz, bool covered, int strideY, int strideX, int dilationY, int dilationX, void* interimPtr);
+DEEP8_API void Conv2dGradYGPU(const Tensor& x, const Tensor& y, Tensor& dy, const Tensor& z, const Tensor& dz, bool covered, int strideY, int strideX, int dilationY, int dilationX, void* xcol);
+
+DEEP8_API size_t DeConv2dInterimSize(const Tensor& x, const Tensor& y, Tensor& z, bool covered, int strideY, int strideX);
+DEEP8_API void DeConv2d(const Tensor& x, const Tensor& y, Tensor& z, bool covered, int strideY, int strideX, void* interimPtr);
+DEEP8_API void DeConv2dGPU(const Tensor& x, const Tensor& y, Tensor& z, bool covered, int strideY, int strideX, void* interimPtr);
+DEEP8_API size_t DeConv2dGradXInterimSize(const Tensor& x, Tensor& dx, const Tensor& y, const Tensor& z, const Tensor& dz, bool covered, int strideY, int strideX);
+DEEP8_API void DeConv2dGradX(const Tensor& x, Tensor& dx, const Tensor& y, const Tensor& z, const Tensor& dz, bool covered, int strideY, int strideX, void* interimPtr);
+DEEP8_API void DeConv2dGradXGPU(const Tensor& x, Tensor& dx, const Tensor& y, const Tensor& z, const Tensor& dz, bool covered, int strideY, int strideX, void* interimPtr);
+DEEP8_API size_t DeConv2dGradYInterimSize(const Tensor& x, const Tensor& y, Tensor& dy, const Tensor& z, const Tensor& dz, bool covered, int strideY, int strideX);
+DEEP8_API void DeConv2dGradY(const Tensor& x, const Tensor& y, Tensor& dy, const Tensor& z, const Tensor& dz, bool covered, int strideY, int strideX, void* interimPtr);
+DEEP8_API void DeConv2dGradYGPU(const Tensor& x, const Tensor& y, Tensor& dy, const Tensor& z, const Tensor& dz, bool covered, int strideY, int strideX, void* interimPtr);
+
+DEEP8_API void ReLu(const Tensor& x, Tensor& y);
+DEEP8_API void ReLuGrad(const Tensor& x, Tensor& dx, const Tensor& y, const Tensor& dy);
+DEEP8_API void Constant(Tensor& x, float scalar);  // only 0 is supported: what zeroGradient needs
+}  // namespace Math
+
+// ------------------------------------------------------------------------------------------------ graph nodes
+class Executor;
+class Node;
+
+class DEEP8_API OutputEntry {
+public:
+    std::unordered_map<Node*, size_t> entries;
+    void add(Node* node, size_t i) { entries[node] = i; }
+    void remove(Node* node) { entries.erase(node); }
+    void clear() { entries.clear(); }
+    size_t size() const { return entries.size(); }
+    Node* first() const;
+};
+
+enum class NodeType { Unknow = 0, Variable, Function };
+
+class DEEP8_API Node {
+public:
+    NodeType type;
+    int64_t id;
+    std::string name;
+    Executor* executor;
+    std::vector<Node*> inputs;
+    OutputEntry outputs;
+
+protected:
+    Node();
+    explicit Node(Node* input);
+    explicit Node(std::vector<Node*>& inputs);
+    Node(int64_t id, std::string name, Executor* exe);
+    Node(int64_t id, std::string name, Executor* exe, Node* input);
+
+public:
+    virtual ~Node();
+    virtual void forward();
+    virtual void backward();
+    virtual std::string toString();
+};
+
+class DEEP8_API Variable : public Node {
+public:
+    Tensor value;
+    Tensor gradient;
+    bool updateGradient;
+
+    Variable(int64_t id, std::string name, Executor* exe, Tensor& v);
+    Variable(int64_t id, std::string name, Executor* exe, Tensor& v, Tensor& g);
+    Variable(int64_t id, std::string name, Executor* exe, Node* input, Tensor& v);
+    Variable(int64_t id, std::string name, Executor* exe, Node* input, Tensor& v, Tensor& g);
+
+    Shape shape() const { return value.shape; }
+    ElementType elementType() const { return value.elementType; }
+    DeviceType deviceType() const { return value.deviceType(); }
+    bool isScalar() const { return value.isScalar(); }
+    void zeroGradient();
+    void removeGradient();
+    void forward() override {}
+    void backward() override {}
+
+    Variable& feed(const void* cpuPtr);  // host -> value (synchronous, as in the reference)
+    Variable& fetch(void* cpuPtr);       // value -> host
+    Variable& feedGradient(const void* cpuPtr);
+    Variable& fetchGradient(void* cpuPtr);
+    Variable& zero();
+
+    Variable& matrixMultiply(Variable& y);
+    Variable& conv2d(Variable& filter, bool covered = true, int strideY = 1, int strideX = 1, int dilationY = 1, int dilationX = 1);
+    Variable& deConv2d(Variable& filter, bool covered = false, int strideY = 1, int strideX = 1);
+    Variable& relu();
+};
+
+enum class FunctionType { Unkown = 0, Conv2d, DeConv2d, MatrixMultiply, ReLu };
+
+class DEEP8_API Function : public Node {
+protected:
+    explicit Function(std::vector<Node*>& inputs);
+
+public:
+    virtual bool isShared() { return false; }
+    virtual Shape checkShape(std::vector<Shape>& inputShapes);
+    virtual ElementType checkElementType(std::vector<ElementType>& inputTypes);
+    virtual void forward(const std::vector<const Tensor*>& inputs, Tensor* output);
+    virtual void backward(const std::vector<const Tensor*>& inputs, const Tensor* output, const Tensor* outputGradient, size_t index,
+                          Tensor* iGradient);
+    void forward() override;
+    void backward() override;
+};
+
+class DEEP8_API MatrixMultiply : public Function {
+public:
+    explicit MatrixMultiply(std::vector<Node*>& inputs);
+    Shape checkShape(std::vector<Shape>& inputShapes) override;
+    void forward(const std::vector<const Tensor*>& inputs, Tensor* output) override;
+    void backward(const std::vector<const Tensor*>& inputs, const Tensor* output, const Tensor* outputGradient, size_t index,
+                  Tensor* iGradient) override;
+};
+
+class DEEP8_API Conv2d : public Function {
+public:
+    bool covered;
+    int strideY, strideX, dilationY, dilationX;
+    explicit Conv2d(std::vector<Node*>& inputs, bool covered = false, int strideY = 1, int strideX = 1, int dilationY = 1, int dilationX = 1);
+    Shape checkShape(std::vector<Shape>& inputShapes) override;
+    void forward(const std::vector<const Tensor*>& inputs, Tensor* output) override;
+    void backward(const std::vector<const Tensor*>& inputs, const Tensor* output, const Tensor* outputGradient, size_t index,
+                  Tensor* iGradient) override;
+};
+
+class DEEP8_API DeConv2d : public Function {
+public:
+    bool forwardCovered;
+    int forwardStrideY, forwardStrideX;
+    explicit DeConv2d(std::vector<Node*>& inputs, bool covered = false, int strideY = 1, int strideX = 1);
+    Shape checkShape(std::vector<Shape>& inputShapes) override;
+    void forward(const std::vector<const Tensor*>& inputs, Tensor* output) override;
+    void backward(const std::vector<const Tensor*>& inputs, const Tensor* output, const Tensor* outputGradient, size_t index,
+                  Tensor* iGradient) override;
+};
+
+class DEEP8_API ReLu : public Function {
+public:
+    explicit ReLu(std::vector<Node*>& inputs);
+    Shape checkShape(std::vector<Shape>& inputShapes) override;
+    void forward(const std::vector<const Tensor*>& inputs, Tensor* output) override;
+    void backward(const std::vector<const Tensor*>& inputs, const Tensor* output, const Tensor* outputGradient, size_t index,
+                  Tensor* iGradient) override;
+};
+
+// ------------------------------------------------------------------------------------------------ executors
+class DEEP8_API Executor {
+protected:
+    int64_t uniqueId;
+    Device* device;
+    std::unordered_map<std::string, Node*> allNodes;
+    std::unordered_map<std::string, Variable*> retainVariables;
+    std::unordered_map<std::string, Node*> interimNodes;
+
+    explicit Executor(DeviceType deviceType, int deviceId);
+    int64_t generateUniqueId() { return uniqueId++; }
+    std::string generateUniqueName(const char* prefix);
+    Tensor createTensor(Shape& shape, ElementType type);
+    Variable* createVariableByFunction(Function* func);
+
+public:
+    virtual ~Executor();
+    Device* getDevice() const { return device; }
+
+    Variable* addVariable(Shape& shape, ElementType type, bool updateGradient = true, bool retain = true);
+    Variable* addVariable(std::vector<size_t> list, ElementType type, bool updateGradient = true, bool retain = true);
+    Variable* addVariable(size_t batch, std::vector<size_t> list, ElementType type, bool updateGradient = true, bool retain = true);
+    Variable* addVariable(size_t batch, std::vector<size_t> list, DType type, bool updateGradient = true, bool retain = true);
+
+    void clearInterimNodes();
+    void removeGradient();
+    std::vector<Variable*> trainableParameters();
+
+    virtual Variable* addFunction(Function* func) = 0;
+    virtual void forward(Node* last) = 0;
+    virtual void backward(Node* last, bool clearInterim = true) = 0;
+};
+
+class DEEP8_API EagerExecutor : public Executor {
+public:
+    // deviceId is an addition: the reference pins device 0 (deep8/src/model/Executor.cu:6-8); one executor per GPU needs it.
+    explicit EagerExecutor(DeviceType deviceType = DeviceType::GPU, int deviceId = 0);
+    Variable* addFunction(Function* func) override;
+    void forward(Node* last) override;
+    // the reference's rule: `last` must be a scalar Variable; its gradient is set to one
+    void backward(Node* last, bool clearInterim = true) override;
+    // addition: start from `last` with an upstream gradient given on the host (the benchmark configurations supply one)
+    void backward(Variable* last, const void* hostGradient, bool clearInterim = true);
+};
+
+// ------------------------------------------------------------------------------------------------ Net.h sugar for the path
+DEEP8_API void backward(Variable& v, bool clearInterim = true);
+DEEP8_API Variable& parameter(Executor* executor, std::vector<size_t> list, bool updateGradient = true, DType type = DType::Float32);
+DEEP8_API Variable& parameter(Executor* executor, size_t batch, std::vector<size_t> list, bool updateGradient = true, DType type = DType::Float32);
+DEEP8_API Variable& parameter(Executor* executor, Shape& shape, bool updateGradient = true, DType type = DType::Float32);
+DEEP8_API Variable& operator*(Variable& x, Variable& y);
+DEEP8_API Variable& matrixMultiply(Variable& x, Variable& y);
+DEEP8_API Variable& conv2d(Variable& x, Variable& filter, bool covered = true, int strideY = 1, int strideX = 1, int dilationY = 1, int dilationX = 1);
+DEEP8_API Variable& deConv2d(Variable& x, Variable& filter, bool covered = false, int strideY = 1, int strideX = 1);
+DEEP8_API Variable& relu(Variable& x);
+
+}  // namespace Deep8
+
+#endif  // DEEP8_B200_DEEP8_H

@@ -1,0 +1,293 @@
+// GPU tests of the C++ host interface (include/deep8/Deep8.h) in the style of the reference's own node tests
+// (test/MatrixMultiplyTest.h, test/Conv2dTest.h, test/DeConv2dTest.h): tensors of small integers ("rand() % 50"), the
+// operator run through the node / executor interface, results compared for equality with the CPU oracle
+// (oracle/d8_oracle.c, linked as a checker).  Prints one line per test; exits non-zero on the first failure.
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <functional>
+#include <string>
+#include <vector>
+
+#include "../../include/deep8/Deep8.h"
+
+extern "C" {
+void d8o_matmul_forward_f32(const float* x, size_t xb, size_t xr, size_t xc, const float* y, size_t yb, size_t yc, float* z);
+void d8o_matmul_grad_x_f32(float* dx, size_t xb, size_t xr, size_t xc, const float* y, size_t yb, size_t yc, const float* dz);
+void d8o_matmul_grad_y_f32(const float* x, size_t xb, size_t xr, size_t xc, float* dy, size_t yb, size_t yc, const float* dz);
+void d8o_conv2d_forward_f32(const float* x, int b, int ih, int iw, int ic, const float* y, int oc, int fh, int fw, float* z, int oh, int ow,
+                            int sy, int sx, int dy, int dx);
+void d8o_conv2d_grad_x_f32(float* dx, int b, int ih, int iw, int ic, const float* y, int oc, int fh, int fw, const float* dz, int oh, int ow,
+                           int sy, int sx, int dy, int dxx);
+void d8o_conv2d_grad_y_f32(const float* x, int b, int ih, int iw, int ic, float* dy, int oc, int fh, int fw, const float* dz, int oh, int ow,
+                           int sy, int sx, int dyy, int dx);
+void d8o_deconv2d_forward_f32(const float* x, int b, int ih, int iw, int ic, const float* y, int oc, int fh, int fw, float* z, int oh, int ow,
+                              int sy, int sx);
+void d8o_deconv2d_grad_x_f32(float* dx, int b, int ih, int iw, int ic, const float* y, int oc, int fh, int fw, const float* dz, int oh, int ow,
+                             int sy, int sx);
+void d8o_deconv2d_grad_y_f32(const float* x, int b, int ih, int iw, int ic, float* dy, int oc, int fh, int fw, const float* dz, int oh, int ow,
+                             int sy, int sx);
+}
+
+using namespace Deep8;
+
+static int g_failed = 0;
+#define EXPECT(cond)                                                         \
+    do {                                                                     \
+        if (!(cond)) {                                                       \
+            std::printf("  FAILED %s:%d: %s\n", __FILE__, __LINE__, #cond);  \
+            ++g_failed;                                                      \
+            return;                                                          \
+        }                                                                    \
+    } while (0)
+
+static std::vector<float> ints(size_t n, int hi = 50) {
+    std::vector<float> v(n);
+    for (auto& e : v) e = static_cast<float>(std::rand() % hi);
+    return v;
+}
+
+static bool same(const std::vector<float>& a, const std::vector<float>& b) {
+    return a.size() == b.size() && 0 == std::memcmp(a.data(), b.data(), a.size() * sizeof(float));
+}
+
+// a tensor on `device` holding `host` (what test/TestUtils.h createTensor does)
+static Tensor makeTensor(GPUDevice& device, size_t batch, std::vector<size_t> dims, const std::vector<float>& host) {
+    Shape shape(batch, dims);
+    size_t bytes = sizeof(float) * shape.size();
+    void* ptr = device.malloc(bytes);
+    auto ref = static_cast<size_t*>(device.mallocCPU(sizeof(size_t)));
+    TensorStorage storage(ptr, ref, bytes, &device);
+    device.copyFromCPUToGPU(host.data(), ptr, bytes);
+    return Tensor(storage, 0, shape, ElementType::from<float>());
+}
+
+static std::vector<float> download(GPUDevice& device, const Tensor& t) {
+    std::vector<float> host(t.size());
+    device.synchronize();
+    device.copyFromGPUToCPU(t.raw(), host.data(), t.byteCount());
+    return host;
+}
+
+// ---- test/MatrixMultiplyTest.h GPU1_float / GPU2_float shapes at the Math:: level
+static void matmulMath(size_t xb, size_t xr, size_t xc, size_t yb, size_t yc) {
+    GPUDevice device;
+    size_t zb = std::max(xb, yb);
+    auto hx = ints(xb * xr * xc), hy = ints(yb * xc * yc), hdz = ints(zb * xr * yc), hdx0 = ints(xb * xr * xc), hdy0 = ints(yb * xc * yc);
+    Tensor x = makeTensor(device, xb, {xr, xc}, hx), y = makeTensor(device, yb, {xc, yc}, hy);
+    Tensor z = makeTensor(device, zb, {xr, yc}, std::vector<float>(zb * xr * yc, -1.f));
+    Tensor dz = makeTensor(device, zb, {xr, yc}, hdz), dx = makeTensor(device, xb, {xr, xc}, hdx0), dy = makeTensor(device, yb, {xc, yc}, hdy0);
+    Math::MatrixMultiply(x, y, z);
+    Math::MatrixMultiplyGradX(x, dx, y, z, dz);
+    Math::MatrixMultiplyGradY(x, y, dy, z, dz);
+    std::vector<float> rz(zb * xr * yc), rdx = hdx0, rdy = hdy0;
+    d8o_matmul_forward_f32(hx.data(), xb, xr, xc, hy.data(), yb, yc, rz.data());
+    d8o_matmul_grad_x_f32(rdx.data(), xb, xr, xc, hy.data(), yb, yc, hdz.data());
+    d8o_matmul_grad_y_f32(hx.data(), xb, xr, xc, rdy.data(), yb, yc, hdz.data());
+    EXPECT(same(download(device, z), rz));
+    EXPECT(same(download(device, dx), rdx));   // += on top of the initial gradient
+    EXPECT(same(download(device, dy), rdy));
+}
+
+// ---- graph level: parameter, feed, x * w, relu, backward from a host gradient, fetch (README usage of the reference)
+static void mlpGraph() {
+    EagerExecutor executor(DeviceType::GPU);
+    const size_t rows = 96, din = 40, dhid = 72;
+    auto hx = ints(rows * din, 5), hw1 = ints(din * dhid, 5), hw2 = ints(dhid * din, 5), hdy = ints(rows * din, 5);
+    for (auto& v : hw1) v -= 2.f;  // make the ReLU cut something
+    Variable& x = parameter(&executor, {rows, din});
+    Variable& w1 = parameter(&executor, {din, dhid});
+    Variable& w2 = parameter(&executor, {dhid, din});
+    x.feed(hx.data());
+    w1.feed(hw1.data());
+    w2.feed(hw2.data());
+    Variable& h = x * w1;
+    Variable& a = relu(h);
+    Variable& yv = matrixMultiply(a, w2);
+    std::vector<float> gy(rows * din);
+    yv.fetch(gy.data());
+    // oracle
+    std::vector<float> rh(rows * dhid), ra(rows * dhid), ry(rows * din);
+    d8o_matmul_forward_f32(hx.data(), 1, rows, din, hw1.data(), 1, dhid, rh.data());
+    for (size_t i = 0; i < rh.size(); ++i) ra[i] = rh[i] > 0 ? rh[i] : 0;
+    d8o_matmul_forward_f32(ra.data(), 1, rows, dhid, hw2.data(), 1, din, ry.data());
+    EXPECT(same(gy, ry));
+    executor.backward(&yv, hdy.data(), false);
+    std::vector<float> rda(rows * dhid, 0.f), rdw2(dhid * din, 0.f), rdh(rows * dhid, 0.f), rdx(rows * din, 0.f), rdw1(din * dhid, 0.f);
+    d8o_matmul_grad_x_f32(rda.data(), 1, rows, dhid, hw2.data(), 1, din, hdy.data());
+    d8o_matmul_grad_y_f32(ra.data(), 1, rows, dhid, rdw2.data(), 1, din, hdy.data());
+    for (size_t i = 0; i < rdh.size(); ++i) rdh[i] = rh[i] > 0 ? rda[i] : 0;
+    d8o_matmul_grad_x_f32(rdx.data(), 1, rows, din, hw1.data(), 1, dhid, rdh.data());
+    d8o_matmul_grad_y_f32(hx.data(), 1, rows, din, rdw1.data(), 1, dhid, rdh.data());
+    std::vector<float> gdx(rows * din), gdw1(din * dhid), gdw2(dhid * din);
+    x.fetchGradient(gdx.data());
+    w1.fetchGradient(gdw1.data());
+    w2.fetchGradient(gdw2.data());
+    EXPECT(same(gdx, rdx));
+    EXPECT(same(gdw1, rdw1));
+    EXPECT(same(gdw2, rdw2));
+    EXPECT(executor.trainableParameters().size() == 3);
+    executor.clearInterimNodes();
+}
+
+// ---- test/Conv2dTest.h forwardGPU_float / backwardGPU_float through the node
+static void convNode(size_t b, size_t ih, size_t iw, size_t ic, size_t oc, size_t fh, size_t fw, bool covered, int s, int d) {
+    EagerExecutor executor(DeviceType::GPU);
+    auto hx = ints(b * ih * iw * ic, 20), hw = ints(oc * fh * fw * ic, 20);
+    Variable& x = parameter(&executor, b, {ih, iw, ic});
+    Variable& w = parameter(&executor, {oc, fh, fw, ic});
+    x.feed(hx.data());
+    w.feed(hw.data());
+    Variable& z = conv2d(x, w, covered, s, s, d, d);
+    Shape zs = z.shape();
+    int oh = (int)zs.dim(0), ow = (int)zs.dim(1);
+    std::vector<float> gz(zs.size()), rz(zs.size());
+    z.fetch(gz.data());
+    d8o_conv2d_forward_f32(hx.data(), (int)b, (int)ih, (int)iw, (int)ic, hw.data(), (int)oc, (int)fh, (int)fw, rz.data(), oh, ow, s, s, d, d);
+    EXPECT(same(gz, rz));
+    auto hdz = ints(zs.size(), 20);
+    executor.backward(&z, hdz.data(), false);
+    std::vector<float> rdx(hx.size(), 0.f), rdw(hw.size(), 0.f), gdx(hx.size()), gdw(hw.size());
+    d8o_conv2d_grad_x_f32(rdx.data(), (int)b, (int)ih, (int)iw, (int)ic, hw.data(), (int)oc, (int)fh, (int)fw, hdz.data(), oh, ow, s, s, d, d);
+    d8o_conv2d_grad_y_f32(hx.data(), (int)b, (int)ih, (int)iw, (int)ic, rdw.data(), (int)oc, (int)fh, (int)fw, hdz.data(), oh, ow, s, s, d, d);
+    x.fetchGradient(gdx.data());
+    w.fetchGradient(gdw.data());
+    EXPECT(same(gdx, rdx));
+    EXPECT(same(gdw, rdw));
+}
+
+// ---- test/DeConv2dTest.h forwarGPU_float / backwarGPU_float through the node
+static void deconvNode(size_t b, size_t ih, size_t iw, size_t ic, size_t oc, size_t fh, size_t fw, bool covered, int s) {
+    EagerExecutor executor(DeviceType::GPU);
+    auto hx = ints(b * ih * iw * ic, 20), hw = ints(oc * fh * fw * ic, 20);
+    Variable& x = parameter(&executor, b, {ih, iw, ic});
+    Variable& w = parameter(&executor, {oc, fh, fw, ic});
+    x.feed(hx.data());
+    w.feed(hw.data());
+    Variable& z = deConv2d(x, w, covered, s, s);
+    Shape zs = z.shape();
+    int oh = (int)zs.dim(0), ow = (int)zs.dim(1);
+    std::vector<float> gz(zs.size()), rz(zs.size());
+    z.fetch(gz.data());
+    d8o_deconv2d_forward_f32(hx.data(), (int)b, (int)ih, (int)iw, (int)ic, hw.data(), (int)oc, (int)fh, (int)fw, rz.data(), oh, ow, s, s);
+    EXPECT(same(gz, rz));
+    auto hdz = ints(zs.size(), 20);
+    executor.backward(&z, hdz.data(), false);
+    std::vector<float> rdx(hx.size(), 0.f), rdw(hw.size(), 0.f), gdx(hx.size()), gdw(hw.size());
+    d8o_deconv2d_grad_x_f32(rdx.data(), (int)b, (int)ih, (int)iw, (int)ic, hw.data(), (int)oc, (int)fh, (int)fw, hdz.data(), oh, ow, s, s);
+    d8o_deconv2d_grad_y_f32(hx.data(), (int)b, (int)ih, (int)iw, (int)ic, rdw.data(), (int)oc, (int)fh, (int)fw, hdz.data(), oh, ow, s, s);
+    x.fetchGradient(gdx.data());
+    w.fetchGradient(gdw.data());
+    EXPECT(same(gdx, rdx));
+    EXPECT(same(gdw, rdw));
+}
+
+// ---- the buddy pool contract (deep8/src/model/GPUMemoryPool.cu:132-279)
+static void memoryPool() {
+    GPUMemoryPool pool(0, static_cast<size_t>(1) << 24);  // 16 MiB blocks keep the test small
+    EXPECT(pool.malloc(0) == nullptr);
+    char* a = static_cast<char*>(pool.malloc(100));     // rounds to 128
+    char* b = static_cast<char*>(pool.malloc(128));
+    char* c = static_cast<char*>(pool.malloc(129));     // rounds to 256
+    EXPECT(a && b && c && pool.blockCount() == 1);
+    EXPECT(pool.bytesInUse() == 128 + 128 + 256);
+    EXPECT((reinterpret_cast<uintptr_t>(c) & 255) == 0);   // a chunk is aligned to its own size
+    EXPECT(b == a + 128);                                  // buddies
+    pool.free(a);
+    pool.free(b);
+    char* d = static_cast<char*>(pool.malloc(256));     // the two freed buddies merged
+    EXPECT(d == a);
+    pool.free(c);
+    pool.free(d);
+    EXPECT(pool.bytesInUse() == 0);
+    char* whole = static_cast<char*>(pool.malloc(static_cast<size_t>(1) << 24));   // everything merged back: one whole block fits
+    EXPECT(whole && pool.blockCount() == 1);
+    char* more = static_cast<char*>(pool.malloc(1024));  // needs a second block
+    EXPECT(more && pool.blockCount() == 2);
+    pool.free(whole);
+    pool.free(more);
+    bool threw = false;
+    try {
+        pool.malloc((static_cast<size_t>(1) << 24) + 1);  // larger than a block: "malloc too much memory"
+    } catch (const std::invalid_argument&) {
+        threw = true;
+    }
+    EXPECT(threw);
+}
+
+template <typename E>
+static bool throws(const std::function<void()>& f) {
+    try {
+        f();
+    } catch (const E&) {
+        return true;
+    } catch (...) {
+        return false;
+    }
+    return false;
+}
+
+// ---- error behaviour: std::invalid_argument for argument checks, std::runtime_error for the rest
+static void errors() {
+    EXPECT(throws<std::runtime_error>([] { EagerExecutor cpu(DeviceType::CPU); }));
+    EagerExecutor executor(DeviceType::GPU);
+    Variable& x = parameter(&executor, {8, 16});
+    Variable& bad = parameter(&executor, {15, 4});
+    EXPECT(throws<std::invalid_argument>([&] { x * bad; }));                        // "the col of input1 must same to the row of input2"
+    Variable& xb = parameter(&executor, 2, {8, 16});
+    Variable& yb = parameter(&executor, 3, {16, 4});
+    EXPECT(throws<std::invalid_argument>([&] { xb * yb; }));                        // "the batch of input is error"
+    Variable& y = parameter(&executor, {16, 4});
+    Variable& z = x * y;
+    EXPECT(throws<std::invalid_argument>([&] { backward(z); }));                    // "the last Variable gradient must be scalar"
+    Variable& dx = parameter(&executor, {8, 16}, true, DType::Float64);
+    Variable& dy = parameter(&executor, {16, 4}, true, DType::Float64);
+    EXPECT(throws<std::runtime_error>([&] { dx * dy; }));                           // "type double is not support"
+    Variable& img = parameter(&executor, 1, {5, 5, 3});
+    Variable& flt = parameter(&executor, {4, 7, 7, 3});
+    EXPECT(throws<std::invalid_argument>([&] { conv2d(img, flt, false); }));        // filter larger than the image, not covered
+    // scalar loss path of the reference: a 1x1 product can be differentiated without a supplied gradient
+    Variable& p = parameter(&executor, {1, 4});
+    Variable& q = parameter(&executor, {4, 1});
+    float hp[4] = {1, 2, 3, 4}, hq[4] = {5, 6, 7, 8}, gp[4];
+    p.feed(hp);
+    q.feed(hq);
+    Variable& s = p * q;
+    backward(s, false);
+    p.fetchGradient(gp);
+    EXPECT(gp[0] == 5 && gp[1] == 6 && gp[2] == 7 && gp[3] == 8);
+}
+
+int main() {
+    std::srand(1234);
+    struct Case {
+        const char* name;
+        std::function<void()> run;
+    };
+    std::vector<Case> cases = {
+        {"matmul Math:: x[10,400,200] * y[1,200,300] (test/MatrixMultiplyTest.h GPU1_float)", [] { matmulMath(10, 400, 200, 1, 300); }},
+        {"matmul Math:: x[1,300,100] * y[10,100,1] (GPU2_float)", [] { matmulMath(1, 300, 100, 10, 1); }},
+        {"matmul Math:: x[3,17,5] * y[3,5,9] (per-batch branch)", [] { matmulMath(3, 17, 5, 3, 9); }},
+        {"graph: parameter, feed, x*w1, relu, *w2, backward(host gradient), fetch", mlpGraph},
+        {"Conv2d node 2x32x32x64, 4x4x64->32, covered, stride 2, dilation 2 (test/Conv2dTest.h)", [] { convNode(2, 32, 32, 64, 32, 4, 4, true, 2, 2); }},
+        {"Conv2d node 2x32x32x64, 5x5, covered, stride 1", [] { convNode(2, 32, 32, 64, 32, 5, 5, true, 1, 1); }},
+        {"Conv2d node not covered, stride 2, dilation 2", [] { convNode(2, 32, 32, 64, 32, 4, 4, false, 2, 2); }},
+        {"DeConv2d node 2x32x32x64, 4x4, not covered, stride 3 (test/DeConv2dTest.h)", [] { deconvNode(2, 32, 32, 64, 32, 4, 4, false, 3); }},
+        {"DeConv2d node covered, stride 3", [] { deconvNode(2, 32, 32, 64, 32, 4, 4, true, 3); }},
+        {"GPUMemoryPool buddy contract", memoryPool},
+        {"error behaviour", errors},
+    };
+    for (auto& c : cases) {
+        int before = g_failed;
+        try {
+            c.run();
+        } catch (const std::exception& e) {
+            std::printf("  EXCEPTION: %s\n", e.what());
+            ++g_failed;
+        }
+        std::printf("[%s] %s\n", g_failed == before ? "  OK  " : "FAILED", c.name);
+        std::fflush(stdout);
+    }
+    std::printf("%d failed\n", g_failed);
+    return g_failed ? 1 : 0;
+}

@@ -245,6 +245,48 @@ def test_paired_cta_kernel(ctx, restated, tA, tB):
     check(ctx, C, want, F16_TOL)
 
 
+@pytest.mark.parametrize("tdtype,rows,din,dhid", [(torch.float16, 2304, 256, 2304), (torch.float16, 200, 72, 136),
+                                                   (torch.float32, 200, 72, 136), (torch.float16, 130, 33, 50)])
+def test_fused_step_equals_unfused(ctx, tdtype, rows, din, dhid):
+    """ReLU inside the contraction epilogues and first-touch gradients give the tensors of the reference's call sequence
+    (zero fill, MatrixMultiply, ReLu, ..., ReLuGrad, +=) bit for bit: paired kernel, single-CTA TMA kernel, loader kernels."""
+    X = dev(cases.normal(21, (1, rows, din)), tdtype)
+    W1 = dev(cases.normal(22, (1, din, dhid), 0.1), tdtype)
+    W2 = dev(cases.normal(23, (1, dhid, din), 0.1), tdtype)
+    dY = dev(cases.normal(24, (1, rows, din), 0.1), tdtype)
+    z = lambda t: torch.zeros_like(t)
+    # reference sequence
+    H = ctx.matmul_forward(X, W1)
+    A = ctx.relu_forward(H)
+    Y = ctx.matmul_forward(A, W2)
+    dA, dH, dX, dW1, dW2 = z(A), z(H), z(X), z(W1), z(W2)
+    ctx.matmul_grad_x(A, dA, W2, dY)
+    ctx.matmul_grad_y(A, W2, dW2, dY)
+    ctx.relu_backward(H, dH, dA)
+    ctx.matmul_grad_x(X, dX, W1, dH)
+    ctx.matmul_grad_y(X, W1, dW1, dH)
+    # fused sequence into buffers full of garbage
+    g = lambda t: torch.full_like(t, 7.0)
+    H2, A2, Y2, dA2, dH2, dX2, dW12, dW22 = g(H), g(A), g(Y), g(dA), g(dH), g(dX), g(dW1), g(dW2)
+    ctx.matmul_forward_relu(X, W1, H2, A2)
+    ctx.matmul_forward(A2, W2, out=Y2)
+    ctx.matmul_grad_x_relu(A2, dA2, W2, dY, H2, dH2, accumulate_dx=False, accumulate_dh=False)
+    ctx.matmul_grad_y(A2, W2, dW22, dY, accumulate=False)
+    ctx.matmul_grad_x(X, dX2, W1, dH2, accumulate=False)
+    ctx.matmul_grad_y(X, W1, dW12, dH2, accumulate=False)
+    assert ctx.status() == 0
+    for name, a, b in (("H", H, H2), ("A", A, A2), ("Y", Y, Y2), ("dA", dA, dA2), ("dH", dH, dH2), ("dX", dX, dX2), ("dW1", dW1, dW12),
+                       ("dW2", dW2, dW22)):
+        assert torch.equal(a, b), name
+    # accumulating variants: run the fused backward once more on top
+    ctx.matmul_grad_x_relu(A2, dA2, W2, dY, H2, dH2, accumulate_dx=True, accumulate_dh=True)
+    ctx.matmul_grad_x(A, dA, W2, dY)
+    dH_ref = dH.clone()
+    ctx.relu_backward(H, dH_ref, dA)
+    assert ctx.status() == 0
+    assert torch.equal(dA, dA2) and torch.equal(dH_ref, dH2)
+
+
 def test_gradients_accumulate(ctx):
     """Calling a gradient twice adds twice (beta = 1 in the reference's gemm calls, MatrixMultiply.cu:203, 391)."""
     x = dev(cases.small_ints(1, (2, 64, 32), 4))
@@ -300,3 +342,15 @@ def test_split_k_is_deterministic(ctx):
     ctx.matmul_grad_y(x, y, b, dz)
     assert ctx.status() == 0
     assert torch.equal(a, b)
+
+
+def test_cpp_host_interface():
+    """The C++ Deep8:: interface (include/deep8/Deep8.h) over the C ABI: node, executor, pool and error-behaviour tests in
+    the style of the reference's gtest headers, compiled by deep8_b200.build.build_cpp_tests() (tests/cpp/)."""
+    import subprocess
+    exe = os.path.join(os.path.dirname(os.path.abspath(__file__)), "cpp", "bin", "test_deep8_host")
+    assert os.path.exists(exe), "tests/cpp/bin/test_deep8_host is missing: run __graft_entry__.build()"
+    r = subprocess.run([exe], capture_output=True, text=True, timeout=600)
+    print(r.stdout)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-2000:]
+    assert "0 failed" in r.stdout
