@@ -396,12 +396,113 @@ def run_gpu_arm(args):
 TRAFFIC_BYTES_PER_LAUNCH = 1.10e9
 
 
+# ------------------------------------------------------------------------------------------------ configs 1-4 (fp32)
+def run_small_config(args):
+    """BASELINE configurations 1-4 (fp32, 3xTF32): forward + gradient of x + gradient of y of ONE operator on one GPU,
+    timed with CUDA events with an L2 flush between iterations, checked against the oracle, with the reference's CPU
+    code timed beside it.  An auxiliary report (one JSON line), not the benchmark line of the default run."""
+    import torch
+    import deep8_b200
+    from oracle import pyoracle
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import cases
+
+    n = args.config
+    dev = torch.device("cuda", 0)
+    ctx = deep8_b200.Context(0)
+    if n == 1:
+        name = "fp32 MatrixMultiply 256x512 * 512x128"
+        x, w = cases.uniform(0, (1, 256, 512)), cases.uniform(10, (1, 512, 128))
+        dz = cases.uniform(1, (1, 256, 128))
+        kind, meta, flop = "matmul", None, 3 * 2.0 * 256 * 512 * 128
+    elif n == 2:
+        name = "fp32 MatrixMultiply batch 64 of 128x256 * batch 1 of 256x256"
+        x, w = cases.normal(2, (64, 128, 256), 0.05), cases.normal(12, (1, 256, 256), 0.05)
+        dz = cases.normal(3, (64, 128, 256))
+        kind, meta, flop = "matmul", None, 3 * 2.0 * 8192 * 256 * 256
+    elif n == 3:
+        name = "fp32 Conv2d 32x56x56x64, 3x3x64 -> 64, stride 1, covered"
+        x, w = cases.uniform(4, (32, 56, 56, 64)), cases.normal(5, (64, 3, 3, 64), (2.0 / 576) ** 0.5)
+        dz = cases.normal(6, (32, 56, 56, 64))
+        kind, meta, flop = "conv", (True, (1, 1), (1, 1)), 3 * 2.0 * 100352 * 576 * 64
+    else:
+        name = "fp32 DeConv2d 16x14x14x256, 4x4x256 -> 128, stride 2, covered (output 27x27)"
+        x, w = cases.uniform(7, (16, 14, 14, 256)), cases.normal(8, (128, 4, 4, 256), 1.0 / 64)
+        dz = cases.normal(9, (16, 27, 27, 128))
+        kind, meta, flop = "deconv", (True, (2, 2)), 3 * 2.0 * 3136 * 256 * 2048
+    X, W, DZ = (torch.from_numpy(a).to(dev) for a in (x, w, dz))
+    DX, DW = torch.zeros_like(X), torch.zeros_like(W)
+
+    def step():
+        ctx.zero(DX)
+        ctx.zero(DW)
+        if kind == "matmul":
+            z = ctx.matmul_forward(X, W, out=Z)
+            ctx.matmul_grad_x(X, DX, W, DZ)
+            ctx.matmul_grad_y(X, W, DW, DZ)
+        elif kind == "conv":
+            z = ctx.conv2d_forward(X, W, *meta, out=Z)
+            ctx.conv2d_grad_x(X, DX, W, DZ, *meta)
+            ctx.conv2d_grad_y(X, W, DW, DZ, *meta)
+        else:
+            z = ctx.deconv2d_forward(X, W, *meta, out=Z)
+            ctx.deconv2d_grad_x(X, DX, W, DZ, *meta)
+            ctx.deconv2d_grad_y(X, W, DW, DZ, *meta)
+        return z
+
+    Z = torch.empty(tuple(dz.shape), device=dev)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)  # larger than the 126 MB L2
+    for _ in range(max(args.warmup, 3)):
+        step()
+    torch.cuda.synchronize()
+    times = []
+    for _ in range(args.steps):
+        flush.zero_()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        step()
+        e1.record()
+        torch.cuda.synchronize()
+        times.append(e0.elapsed_time(e1))
+    assert ctx.status() == 0
+    ms = statistics.median(times)
+    # parity against the oracle and the reference's CPU time
+    oracle = pyoracle.Restated()
+    ref = pyoracle.Reference() if pyoracle.Reference.available() else oracle
+
+    def cpu(impl):
+        if kind == "matmul":
+            return impl.matmul_forward(x, w), impl.matmul_grad_x(x, w, dz), impl.matmul_grad_y(x, w, dz)
+        if kind == "conv":
+            return impl.conv2d_forward(x, w, *meta), impl.conv2d_grad_x(x, w, dz, *meta), impl.conv2d_grad_y(x, w, dz, *meta)
+        return impl.deconv2d_forward(x, w, *meta), impl.deconv2d_grad_x(x, w, dz, *meta), impl.deconv2d_grad_y(x, w, dz, *meta)
+
+    want = cpu(oracle)
+    got = (Z.cpu().numpy(), DX.cpu().numpy(), DW.cpu().numpy())
+    err = max(cases.rel_max(g, r) for g, r in zip(got, want))
+    cpu(ref)
+    cpu_times = []
+    for _ in range(3):
+        t0 = time.perf_counter()
+        cpu(ref)
+        cpu_times.append(time.perf_counter() - t0)
+    cpu_ms = min(cpu_times) * 1e3
+    line = {"report": "config %d" % n, "workload": name, "dtype": "f32 (3xTF32)", "ms_per_step": ms, "tflops": flop / ms / 1e9,
+            "frac_of_tf32_peak_over_3": flop / ms / 1e9 / (1100.0 / 3), "max_rel_err_vs_oracle": err, "tolerance": 1e-5,
+            "l2": "flushed between iterations (256 MiB write)", "steps": args.steps,
+            "cpu": {"ms": cpu_ms, "kind": ref.kind, "threads": 1 if kind == "matmul" else ref.threads(),
+                    "gflops": flop / cpu_ms / 1e6}}
+    print(json.dumps(line), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--config", type=int, default=5, choices=[1, 2, 3, 4, 5], help="BASELINE configuration; 5 (default) is the benchmark "
+                    "line, 1-4 print an auxiliary fp32 report for one operator")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--unfused", action="store_true", help="the reference's call sequence: zero fill, separate ReLU passes, += everywhere")
     ap.add_argument("--profile", action="store_true", help="for runs under a profiler: no clock sampling, no end-to-end or CPU leg, "
@@ -409,7 +510,9 @@ def main():
     args = ap.parse_args()
     if args.impl == "ours" and not args.profile:
         args.warmup = max(args.warmup, 3)  # timing rule: at least three untimed steps
-    if args.impl == "reference":
+    if args.config != 5 and args.impl == "ours":
+        run_small_config(args)
+    elif args.impl == "reference":
         run_reference_arm(args)
     else:
         run_gpu_arm(args)
