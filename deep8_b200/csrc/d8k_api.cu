@@ -69,6 +69,7 @@ ConvRule rule(int RH, int RW, int SH, int SW, int C, int FW, int mul_y, int mul_
     ConvRule r;
     r.RH = RH; r.RW = RW; r.SH = SH; r.SW = SW; r.C = C; r.FW = FW;
     r.mul_y = mul_y; r.mul_x = mul_x; r.e_y = e_y; r.e_x = e_x; r.off_y = off_y; r.off_x = off_x; r.div_y = div_y; r.div_x = div_x;
+    finish_rule(r);
     return r;
 }
 

@@ -5,7 +5,7 @@
 // tensor rate) and only four stages fit in shared memory; measured, the tensor pipe then waits on operand delivery
 // 43 % of the time.  In a pair, CTA r stages rows [128 r, 128 r + 128) of the A tile and rows [128 r, 128 r + 128) of the
 // B tile (N side) - 32 KB per k-block - and the pair's MMA reads both halves of B from both CTAs' shared memory, so each
-// SM moves two thirds of the bytes and six stages fit.
+// SM moves two thirds of the bytes.
 //
 // Protocol (all barriers live at the same shared-memory offsets in both CTAs; "leader" = cluster rank 0):
 //   full[s]    leader only, count 1: the leader's producer arrives with expect_tx = both CTAs' bytes; both CTAs' TMA
@@ -14,6 +14,9 @@
 //   tfull[a]   both CTAs, count 1: same commit form once a tile's last MMA is issued; each CTA's epilogue warps then
 //              read their own 128 accumulator rows from their own tensor memory.
 //   tempty[a]  leader only, count 2 x 128: every epilogue thread of both CTAs arrives (the peer's remotely).
+// Epilogue: accumulator rows leave tensor memory one thread per row; each warp transposes its 32 x 32 chunk through a
+// private shared-memory slot so that global memory sees whole 64-byte row segments (and reads C, ReLu's input and its
+// gradient the same way when beta or a fused tail needs them).
 // One TMA instruction per operand per stage: measured on B200, a CTA's TMA unit retires about two tile loads per 260 ns
 // whatever their size (16 KB or 32 KB), so a stage holds SUB = 2 k-blocks of 64 and each operand arrives as ONE 32 KB box
 // of a 4-D tensor map {64 elements, rows, k-blocks (or 64-element chunks), batch}; with 16 KB boxes (one k-block per
@@ -40,7 +43,9 @@ struct Gemm2Cfg {
     static constexpr int EPI_WARPS = 4, PRODUCER_WARP = 4, MMA_WARP = 5;
     static constexpr int THREADS = 32 * 6;
     static constexpr int BAR_BYTES = 256;
-    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + BAR_BYTES + 1024;
+    // epilogue staging: per epilogue warp three slots (C, E1, E2) of 32 rows x 64 bytes (32 fp16 columns)
+    static constexpr int SLOT_BYTES = 32 * 64, STAGING_BYTES = EPI_WARPS * 3 * SLOT_BYTES;
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + BAR_BYTES + STAGING_BYTES + 1024;
     static_assert(SMEM_BYTES <= 227 * 1024, "shared memory");
     static_assert(SMEM_BYTES > 114 * 1024, "one CTA per SM");
 };
@@ -101,7 +106,18 @@ __device__ __forceinline__ void tc_commit_pair(uint32_t bar, uint16_t mask) {
                  : "memory");
 }
 
+__device__ __forceinline__ uint4 ld_shared_v4(uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr) : "memory");
+    return v;
+}
+
 }  // namespace ptx
+
+// 16-byte chunk c16 (0..3) of row r (0..31) inside a staging slot of 64-byte rows: the chunk index is XORed with bits of
+// the row so that both access patterns of the epilogue - one thread per row, and four threads per row over eight rows -
+// touch every bank group once.
+__device__ __forceinline__ uint32_t slot_off(int r, int c16) { return static_cast<uint32_t>(r * 64 + ((c16 ^ ((r >> 1) & 3)) << 4)); }
 
 struct PairWork {
     int batch, m0, n0;
@@ -279,6 +295,11 @@ d8k_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
         const int row_in_tile = quarter * 32 + lane;
         const uint32_t tempty_leader0 = ptx::map_to_rank(tempty_bar(0), 0);
         const uint32_t tempty_leader1 = ptx::map_to_rank(tempty_bar(1), 0);
+        const uint32_t staging = bar_base + Cfg::BAR_BYTES + warp * (3 * Cfg::SLOT_BYTES);
+        // whole 16-byte pieces everywhere: bases, pitch and batch stride multiples of 8 elements
+        const bool coalesced = ((reinterpret_cast<uintptr_t>(p.C) | (p.epi ? reinterpret_cast<uintptr_t>(p.E1) : 0) |
+                                 (p.epi == 2 ? reinterpret_cast<uintptr_t>(p.E2) : 0)) & 15) == 0 &&
+                               (p.ldc & 7) == 0 && (p.c_batch_stride & 7) == 0;
         int acc = 0;
         uint32_t acc_phase = 0;
         bool ok = true;
@@ -294,17 +315,86 @@ d8k_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
             if (p.prof) waited += clock64() - tw;
             ptx::tc_fence_after_sync();
             const uint32_t taddr = tmem_base + acc * 256 + (static_cast<uint32_t>(quarter * 32) << 16);
+            const int warp_row0 = it.m0 + 128 * static_cast<int>(rank) + quarter * 32;  // first row of this warp
+            const long long warp_off = static_cast<long long>(it.batch) * p.c_batch_stride + static_cast<long long>(warp_row0) * p.ldc;
 #pragma unroll 1
             for (int c = 0; c < 256 / 32; ++c) {
                 uint32_t r[32];
                 __syncwarp();
                 ptx::tmem_ld_32x32(taddr + c * 32, r);
                 ptx::tmem_ld_wait();
-                if (row < p.M && it.n0 + c * 32 < p.N) {
+                const int col0 = it.n0 + c * 32;
+                if (col0 >= p.N) continue;
+                if (coalesced && col0 + 32 <= p.N) {
+                    // Rows leave as whole 64-byte segments: the values cross from "one thread per row" (the tensor
+                    // memory layout) to "four threads per row" through this warp's private staging slots.
+                    const uint32_t s0 = staging + 0 * Cfg::SLOT_BYTES, s1 = staging + 1 * Cfg::SLOT_BYTES, s2 = staging + 2 * Cfg::SLOT_BYTES;
+                    const int lr = lane >> 2, lc = lane & 3;  // coalesced pattern: row 8 i + lr, 16-byte chunk lc
+                    if (p.beta || p.epi == 2) {
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            const int rr = 8 * i + lr;
+                            if (warp_row0 + rr < p.M) {
+                                const long long e = warp_off + static_cast<long long>(rr) * p.ldc + col0 + lc * 8;
+                                if (p.beta) st_shared_v4(s0 + slot_off(rr, lc), *reinterpret_cast<const uint4*>(reinterpret_cast<const OutT*>(p.C) + e));
+                                if (p.epi == 2) {
+                                    st_shared_v4(s1 + slot_off(rr, lc), *reinterpret_cast<const uint4*>(reinterpret_cast<const OutT*>(p.E1) + e));
+                                    if (p.beta2) st_shared_v4(s2 + slot_off(rr, lc), *reinterpret_cast<const uint4*>(reinterpret_cast<const OutT*>(p.E2) + e));
+                                }
+                            }
+                        }
+                        __syncwarp();
+                    }
+                    using V = EpiVec<OutT>;
+#pragma unroll
+                    for (int v = 0; v < 4; ++v) {  // this thread's row, eight columns at a time
+                        float cv[8];
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) cv[i] = __uint_as_float(r[v * 8 + i]);
+                        if (p.beta) {
+                            float old[8];
+                            V::unpack(ptx::ld_shared_v4(s0 + slot_off(lane, v)), old);
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) cv[i] += old[i];
+                        }
+                        const uint4 cw = V::pack(cv);
+                        st_shared_v4(s0 + slot_off(lane, v), cw);
+                        if (p.epi != 0) V::unpack(cw, cv);  // the stored (rounded) values drive the fused tails
+                        if (p.epi == 1) {
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) cv[i] = cv[i] > 0.f ? cv[i] : 0.f;
+                            st_shared_v4(s1 + slot_off(lane, v), V::pack(cv));
+                        } else if (p.epi == 2) {
+                            float x[8], g[8];
+                            V::unpack(ptx::ld_shared_v4(s1 + slot_off(lane, v)), x);
+                            if (p.beta2) {
+                                V::unpack(ptx::ld_shared_v4(s2 + slot_off(lane, v)), g);
+                            } else {
+#pragma unroll
+                                for (int i = 0; i < 8; ++i) g[i] = 0.f;
+                            }
+#pragma unroll
+                            for (int i = 0; i < 8; ++i)
+                                if (x[i] > 0.f) g[i] += cv[i];
+                            st_shared_v4(s2 + slot_off(lane, v), V::pack(g));
+                        }
+                    }
+                    __syncwarp();
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const int rr = 8 * i + lr;
+                        if (warp_row0 + rr < p.M) {
+                            const long long e = warp_off + static_cast<long long>(rr) * p.ldc + col0 + lc * 8;
+                            *reinterpret_cast<uint4*>(reinterpret_cast<OutT*>(p.C) + e) = ptx::ld_shared_v4(s0 + slot_off(rr, lc));
+                            if (p.epi == 1) *reinterpret_cast<uint4*>(reinterpret_cast<OutT*>(p.E1) + e) = ptx::ld_shared_v4(s1 + slot_off(rr, lc));
+                            if (p.epi == 2) *reinterpret_cast<uint4*>(reinterpret_cast<OutT*>(p.E2) + e) = ptx::ld_shared_v4(s2 + slot_off(rr, lc));
+                        }
+                    }
+                } else if (row < p.M) {
                     float accv[32];
 #pragma unroll
                     for (int i = 0; i < 32; ++i) accv[i] = __uint_as_float(r[i]);
-                    store_row_chunk<OutT>(p, crow, it.n0 + c * 32, accv);
+                    store_row_chunk<OutT>(p, crow, col0, accv);
                 }
             }
             ptx::tc_fence_before_sync();

@@ -36,22 +36,49 @@ constexpr long long kWaitLimitCycles = 4000000000LL;  // ~2 s at the maximum SM 
 // status word values written by a kernel that gave up on a wait: (role << 8) | which barrier
 enum : int { kStatusOk = 0, kRoleProducer = 1, kRoleMma = 2, kRoleEpilogue = 3, kRoleLoader = 4 };
 
+// Exact n / d for 0 <= n < 2^32 without a divide instruction: the high 64 bits of n * ceil(2^64 / d).  With
+// M = (2^64 + e) / d, 0 <= e < d, n * M / 2^64 = n / d + n e / (d 2^64) and n e < 2^64, so the floor is n / d.
+// The loader warps decode pixel and tap indices for every 16-byte chunk; real divisions made them the bottleneck.
+struct FastDiv {
+    unsigned long long magic;  // 0 stands for d == 1
+    int d;
+};
+inline FastDiv make_fastdiv(int d) {
+    FastDiv f;
+    f.d = d;
+    f.magic = d <= 1 ? 0ull : (~0ull / static_cast<unsigned long long>(d)) + 1ull;
+    return f;
+}
+__device__ __forceinline__ int fdiv(int n, const FastDiv& f) {
+    return f.magic ? static_cast<int>(__umul64hi(static_cast<unsigned long long>(static_cast<unsigned>(n)), f.magic)) : n;
+}
+
 // Pixel/tap rule of a virtual im2col matrix.  Row g = (n, py, px) over an RH x RW grid; column = tap * C + c with
 // tap = fy * FW + fx.  The source pixel is ((py*mul_y + fy*e_y + off_y) / div_y, likewise x) in an SH x SW image with
 // C channels; the element is zero unless the numerators are >= 0, divisible, and the quotients are inside the image.
 struct ConvRule {
     int RH, RW, SH, SW, C, FW;
     int mul_y, mul_x, e_y, e_x, off_y, off_x, div_y, div_x;
+    FastDiv f_plane, f_rw, f_c, f_fw, f_divy, f_divx;  // RH*RW, RW, C, FW, div_y, div_x
 };
+inline void finish_rule(ConvRule& r) {
+    r.f_plane = make_fastdiv(r.RH * r.RW);
+    r.f_rw = make_fastdiv(r.RW);
+    r.f_c = make_fastdiv(r.C);
+    r.f_fw = make_fastdiv(r.FW);
+    r.f_divy = make_fastdiv(r.div_y);
+    r.f_divx = make_fastdiv(r.div_x);
+}
 
 // Where the loader warps find one operand.  Logical view: `rows` x `cols` elements, 128-byte windows of a row are
-// fetched at a time.  kind 0: matrix, row g at base + g * ld, or with rmod > 0 at base + (g % rmod) * ld + (g / rmod) * ld2 (+ batch).  kind 1: virtual
-// im2col matrix described by `cr` over the NHWC image at base.
+// fetched at a time.  kind 0: matrix, row g at base + g * ld, or with rmod > 0 at base + (g % rmod) * ld + (g / rmod) * ld2
+// (+ batch).  kind 1: virtual im2col matrix described by `cr` over the NHWC image at base.
 struct GatherSrc {
     const void* base;
     int kind;
     int rows, cols;
     int rmod;
+    FastDiv f_rmod;
     long long ld, ld2;
     long long batch_stride;
     int batch_count;
@@ -76,6 +103,7 @@ struct GemmParams {
     int* counters;     // one ticket counter per output tile, zero on entry and on exit
     int* status;
     int a_batch_mod, b_batch_mod;  // TMA: batch coordinate = b % mod
+    int a_chunked, b_chunked;      // single-CTA TMA kernel: the MN-major operand comes through a 4-D {64, k, chunk, batch} map, one box per stage
     long long* prof;   // optional, normally null: per CTA 8 counters of cycles each role spent waiting (paired kernel only)
     GatherSrc a, b;
 };
@@ -103,8 +131,12 @@ struct GemmCfg {
     // other buffer.  0 = one chain per work item (fp16, whose output rounding is far coarser).
     static constexpr int CHUNK_KB = F32 ? 8 : 0;
     static constexpr int EPI_WARPS = 4;
+    // GATHER: LOADER_GROUPS groups of four loader warps take the k-blocks in turn, so one group's address arithmetic and
+    // conversions overlap the other group's global-load latency (a lone group spent 4-8 us per k-block).
     static constexpr int PRODUCER_WARP = 4, MMA_WARP = 5, LOADER_WARP0 = 6, LOADER_WARPS = 4;
-    static constexpr int THREADS = GATHER ? 32 * (LOADER_WARP0 + LOADER_WARPS) : 32 * 6;
+    // fp32 with 128 columns keeps 128 accumulators per epilogue thread in registers: no room for a second group there
+    static constexpr int LOADER_GROUPS = (F32 && BN_ > 64) ? 1 : 2;
+    static constexpr int THREADS = GATHER ? 32 * (LOADER_WARP0 + LOADER_WARPS * LOADER_GROUPS) : 32 * 6;
     static constexpr int BAR_BYTES = 256;
     static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + BAR_BYTES + 1024;  // + slack to align the ring to 1024
     static_assert(BN % 16 == 0 && BN >= 16 && BN <= 256, "UMMA N");
@@ -170,61 +202,82 @@ __device__ __forceinline__ bool warp_wait_bar(int lane, uint32_t bar, uint32_t p
 }
 
 // ------------------------------------------------------------------------------------------------ gather loaders
-// 16 bytes of row g starting at column `col` of an operand, zero outside the logical extent.
+// Column part of a virtual-matrix address: which tap and channel, and the tap's contribution to the pixel numerators.
+struct ColCtx {
+    int c, ty, tx;
+    bool inside;  // the VEC-wide chunk starting here stays inside one tap and inside the matrix
+};
+template <int VEC>
+__device__ __forceinline__ ColCtx col_ctx(const GatherSrc& s, int col) {
+    const ConvRule& r = s.cr;
+    ColCtx k;
+    int tap = fdiv(col, r.f_c);
+    k.c = col - tap * r.C;
+    int fy = fdiv(tap, r.f_fw);
+    int fx = tap - fy * r.FW;
+    k.ty = fy * r.e_y + r.off_y;
+    k.tx = fx * r.e_x + r.off_x;
+    k.inside = (k.c + VEC <= r.C) && (col + VEC <= s.cols);
+    return k;
+}
+
+// Element offset of (pixel row g, column context) in the source image; false where the tap falls on padding.
+__device__ __forceinline__ bool locate(const ConvRule& r, int g, const ColCtx& k, long long& off) {
+    int n = fdiv(g, r.f_plane);
+    int rem = g - n * (r.RH * r.RW);
+    int py = fdiv(rem, r.f_rw);
+    int px = rem - py * r.RW;
+    int ny = py * r.mul_y + k.ty, nx = px * r.mul_x + k.tx;
+    if ((ny | nx) < 0) return false;
+    int sy = fdiv(ny, r.f_divy), sx = fdiv(nx, r.f_divx);
+    if (sy * r.div_y != ny || sx * r.div_x != nx || sy >= r.SH || sx >= r.SW) return false;
+    off = (static_cast<long long>(n) * (r.SH * r.SW) + sy * r.SW + sx) * r.C + k.c;
+    return true;
+}
+
 template <typename T, int VEC>
-__device__ __forceinline__ uint4 fetch16(const GatherSrc& s, int g, int col, int batch) {
+__device__ __forceinline__ uint4 load16(const T* p) {  // 16 bytes at p, by elements when p is not 16-byte aligned
+    if ((reinterpret_cast<uintptr_t>(p) & 15) == 0) return __ldg(reinterpret_cast<const uint4*>(p));
+    T tmp[VEC];
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) tmp[i] = __ldg(p + i);
+    return *reinterpret_cast<uint4*>(tmp);
+}
+
+// 16 bytes of row g starting at column `col` of an operand, zero outside the logical extent.  `k` is the column context
+// of `col` for a virtual matrix (the caller computes it once for all rows that share the column); `boff` the batch offset.
+template <typename T, int VEC>
+__device__ __forceinline__ uint4 fetch16(const GatherSrc& s, int g, int col, long long boff, const ColCtx& k) {
     uint4 out = make_uint4(0u, 0u, 0u, 0u);
     if (g >= s.rows || col >= s.cols) return out;
     const T* base = reinterpret_cast<const T*>(s.base);
     if (s.kind == 0) {
-        const T* p = base + static_cast<long long>(batch % s.batch_count) * s.batch_stride + col;
-        if (s.rmod > 0) p += static_cast<long long>(g % s.rmod) * s.ld + static_cast<long long>(g / s.rmod) * s.ld2;
-        else p += static_cast<long long>(g) * s.ld;
-        if (col + VEC <= s.cols && (reinterpret_cast<uintptr_t>(p) & 15) == 0) {
-            out = __ldg(reinterpret_cast<const uint4*>(p));
+        const T* p = base + boff + col;
+        if (s.rmod > 0) {
+            int q = fdiv(g, s.f_rmod);
+            p += static_cast<long long>(g - q * s.rmod) * s.ld + static_cast<long long>(q) * s.ld2;
         } else {
-            T tmp[VEC];
-#pragma unroll
-            for (int i = 0; i < VEC; ++i) tmp[i] = (col + i < s.cols) ? __ldg(p + i) : T(0);
-            out = *reinterpret_cast<uint4*>(tmp);
+            p += static_cast<long long>(g) * s.ld;
         }
-        return out;
-    }
-    const ConvRule& r = s.cr;
-    int plane = r.RH * r.RW;
-    int n = g / plane;
-    int rem = g - n * plane;
-    int py = rem / r.RW;
-    int px = rem - py * r.RW;
-    auto source = [&](int column, long long& offset) -> bool {
-        int tap = column / r.C;
-        int c = column - tap * r.C;
-        int fy = tap / r.FW;
-        int fx = tap - fy * r.FW;
-        int ny = py * r.mul_y + fy * r.e_y + r.off_y;
-        int nx = px * r.mul_x + fx * r.e_x + r.off_x;
-        if (ny < 0 || nx < 0) return false;
-        int sy = ny / r.div_y, sx = nx / r.div_x;
-        if (sy * r.div_y != ny || sx * r.div_x != nx || sy >= r.SH || sx >= r.SW) return false;
-        offset = ((static_cast<long long>(n) * r.SH + sy) * r.SW + sx) * r.C + c;
-        return true;
-    };
-    int c0 = col % r.C;
-    if (c0 + VEC <= r.C && col + VEC <= s.cols) {  // the chunk stays inside one tap
-        long long off;
-        if (!source(col, off)) return out;
-        const T* p = base + off;
-        if ((reinterpret_cast<uintptr_t>(p) & 15) == 0) return __ldg(reinterpret_cast<const uint4*>(p));
+        if (col + VEC <= s.cols) return load16<T, VEC>(p);
         T tmp[VEC];
 #pragma unroll
-        for (int i = 0; i < VEC; ++i) tmp[i] = __ldg(p + i);
+        for (int i = 0; i < VEC; ++i) tmp[i] = (col + i < s.cols) ? __ldg(p + i) : T(0);
         return *reinterpret_cast<uint4*>(tmp);
     }
-    T tmp[VEC];
+    long long off;
+    if (k.inside) {
+        if (!locate(s.cr, g, k, off)) return out;
+        return load16<T, VEC>(base + off);
+    }
+    T tmp[VEC];  // the chunk straddles taps (channel count not a multiple of the chunk) or the matrix edge
 #pragma unroll
     for (int i = 0; i < VEC; ++i) {
-        long long off;
-        tmp[i] = (col + i < s.cols && source(col + i, off)) ? __ldg(base + off) : T(0);
+        tmp[i] = T(0);
+        if (col + i < s.cols) {
+            ColCtx ke = col_ctx<1>(s, col + i);
+            if (locate(s.cr, g, ke, off)) tmp[i] = __ldg(base + off);
+        }
     }
     return *reinterpret_cast<uint4*>(tmp);
 }
@@ -459,16 +512,24 @@ d8k_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                     if constexpr (!Cfg::A_MN) {
                         ptx::tma_load_3d(stage_a(stage), &tmA, full_bar(stage), k0, it.m0, b % p.a_batch_mod);
                     } else {
+                        if (p.a_chunked) {  // one box for all 64-wide chunks of the tile: the TMA unit is bound by box count
+                            ptx::tma_load_4d(stage_a(stage), &tmA, full_bar(stage), 0, k0, it.m0 / CE, b % p.a_batch_mod);
+                        } else {
 #pragma unroll
-                        for (int c = 0; c < kBM / CE; ++c)
-                            ptx::tma_load_3d(stage_a(stage) + c * BK * 128, &tmA, full_bar(stage), it.m0 + c * CE, k0, b % p.a_batch_mod);
+                            for (int c = 0; c < kBM / CE; ++c)
+                                ptx::tma_load_3d(stage_a(stage) + c * BK * 128, &tmA, full_bar(stage), it.m0 + c * CE, k0, b % p.a_batch_mod);
+                        }
                     }
                     if constexpr (!Cfg::B_MN) {
                         ptx::tma_load_3d(stage_b(stage), &tmB, full_bar(stage), k0, it.n0, b % p.b_batch_mod);
                     } else {
+                        if (p.b_chunked) {
+                            ptx::tma_load_4d(stage_b(stage), &tmB, full_bar(stage), 0, k0, it.n0 / CE, b % p.b_batch_mod);
+                        } else {
 #pragma unroll
-                        for (int c = 0; c < BN / CE; ++c)
-                            ptx::tma_load_3d(stage_b(stage) + c * BK * 128, &tmB, full_bar(stage), it.n0 + c * CE, k0, b % p.b_batch_mod);
+                            for (int c = 0; c < BN / CE; ++c)
+                                ptx::tma_load_3d(stage_b(stage) + c * BK * 128, &tmB, full_bar(stage), it.n0 + c * CE, k0, b % p.b_batch_mod);
+                        }
                     }
                 }
                 __syncwarp();
@@ -645,16 +706,19 @@ d8k_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         }
     } else if (Cfg::GATHER && warp >= Cfg::LOADER_WARP0) {
         // ============================================================================ gather loaders
-        const int lw = warp - Cfg::LOADER_WARP0;
+        const int lw = (warp - Cfg::LOADER_WARP0) % Cfg::LOADER_WARPS;
+        const int group = (warp - Cfg::LOADER_WARP0) / Cfg::LOADER_WARPS;
         const int sub = lane >> 3;  // row inside a group of four
         const int j = lane & 7;     // 16-byte chunk of the row
         constexpr int A_ITERS = kBM / 16, B_ITERS = BN / 16;
-        int stage = 0;
-        uint32_t phase = 0;
+        int t = 0;                  // running k-block count of this CTA: k-block t uses stage t % STAGES
         bool ok = true;
         for (int w = blockIdx.x; ok && w < p.total_work; w += gridDim.x) {
             WorkItem it = decode_work(p, w, BN);
-            for (int kk = it.kb_begin; kk < it.kb_end; ++kk) {
+            for (int kk = it.kb_begin; kk < it.kb_end; ++kk, ++t) {
+                if (t % Cfg::LOADER_GROUPS != group) continue;
+                const int stage = t % STAGES;
+                const uint32_t phase = (t / STAGES) & 1;
                 ok = wait_bar(empty_bar(stage), phase ^ 1, &s_abort, p.status, (kRoleLoader << 8) | 1);
                 if (!ok) break;
                 int b = it.batch, kb = kk;
@@ -663,22 +727,40 @@ d8k_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                     kb = kk - b * p.num_kb;
                 }
                 const int k0 = kb * BK;
+                const long long boff_a = p.a.batch_count > 1 ? static_cast<long long>(b % p.a.batch_count) * p.a.batch_stride : 0;
+                const long long boff_b = p.b.batch_count > 1 ? static_cast<long long>(b % p.b.batch_count) * p.b.batch_stride : 0;
+                // K-major operands: every row of this thread reads the same columns, one column context per k-block
+                ColCtx ka = {}, kbx = {};
+                if (!Cfg::A_MN && p.a.kind == 1) ka = col_ctx<Cfg::VEC>(p.a, k0 + j * Cfg::VEC);
+                if (!Cfg::B_MN && p.b.kind == 1) kbx = col_ctx<Cfg::VEC>(p.b, k0 + j * Cfg::VEC);
                 uint4 va[A_ITERS], vb[B_ITERS];
 #pragma unroll
                 for (int i = 0; i < A_ITERS; ++i) {
                     int r = (i * 4 + lw) * 4 + sub;
                     int g, col;
-                    if constexpr (!Cfg::A_MN) { g = it.m0 + r; col = k0 + j * Cfg::VEC; }
-                    else { g = k0 + (r % BK); col = it.m0 + (r / BK) * CE + j * Cfg::VEC; }
-                    va[i] = fetch16<InT, Cfg::VEC>(p.a, g, col, b);
+                    if constexpr (!Cfg::A_MN) {
+                        g = it.m0 + r;
+                        col = k0 + j * Cfg::VEC;
+                    } else {
+                        g = k0 + (r % BK);
+                        col = it.m0 + (r / BK) * CE + j * Cfg::VEC;
+                        if (p.a.kind == 1) ka = col_ctx<Cfg::VEC>(p.a, col);
+                    }
+                    va[i] = fetch16<InT, Cfg::VEC>(p.a, g, col, boff_a, ka);
                 }
 #pragma unroll
                 for (int i = 0; i < B_ITERS; ++i) {
                     int r = (i * 4 + lw) * 4 + sub;
                     int g, col;
-                    if constexpr (!Cfg::B_MN) { g = it.n0 + r; col = k0 + j * Cfg::VEC; }
-                    else { g = k0 + (r % BK); col = it.n0 + (r / BK) * CE + j * Cfg::VEC; }
-                    vb[i] = fetch16<InT, Cfg::VEC>(p.b, g, col, b);
+                    if constexpr (!Cfg::B_MN) {
+                        g = it.n0 + r;
+                        col = k0 + j * Cfg::VEC;
+                    } else {
+                        g = k0 + (r % BK);
+                        col = it.n0 + (r / BK) * CE + j * Cfg::VEC;
+                        if (p.b.kind == 1) kbx = col_ctx<Cfg::VEC>(p.b, col);
+                    }
+                    vb[i] = fetch16<InT, Cfg::VEC>(p.b, g, col, boff_b, kbx);
                 }
 #pragma unroll
                 for (int i = 0; i < A_ITERS; ++i) {
@@ -692,7 +774,6 @@ d8k_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                 }
                 ptx::fence_proxy_async_smem();
                 ptx::mbar_arrive(full_bar(stage));
-                if (++stage == STAGES) { stage = 0; phase ^= 1; }
             }
         }
     }

@@ -60,7 +60,7 @@ bool make_map(CUtensorMap* map, const HostOperand& o, long long inner, long long
 //   MN-major (mn == true) : {64 m/n, K, extent / 64, batch}, box {64, 128, 2, 1} - needs extent % 64 == 0
 // The second and third strides are not in increasing order (the 128-byte step comes after the row pitch); TMA only
 // computes addresses from them.
-bool make_pair_map(CUtensorMap* map, const HostOperand& o, long long extent, long long K) {
+bool make_pair_map(CUtensorMap* map, const HostOperand& o, long long extent, long long K, int box_k = 128, int box_groups = 2) {
     EncodeTiledFn enc = encode_tiled();
     if (!enc) return false;
     long long rows = o.mn ? K : extent;           // stored rows
@@ -68,7 +68,7 @@ bool make_pair_map(CUtensorMap* map, const HostOperand& o, long long extent, lon
     cuuint64_t dims[4] = {64u, static_cast<cuuint64_t>(rows), static_cast<cuuint64_t>(groups), static_cast<cuuint64_t>(o.batch_count)};
     long long bstride = o.batch_count > 1 ? o.batch_stride : rows * o.ld;
     cuuint64_t strides[3] = {static_cast<cuuint64_t>(o.ld * 2), 128u, static_cast<cuuint64_t>(bstride * 2)};
-    cuuint32_t box[4] = {64u, 128u, 2u, 1u};
+    cuuint32_t box[4] = {64u, static_cast<cuuint32_t>(box_k), static_cast<cuuint32_t>(box_groups), 1u};  // MN-major: {64, k rows, chunks}
     cuuint32_t estr[4] = {1u, 1u, 1u, 1u};
     CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, const_cast<void*>(o.ptr), dims, strides, box, estr,
                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -84,6 +84,7 @@ GatherSrc to_gather(const HostOperand& o, int rows, int cols) {
     s.rows = rows;
     s.cols = cols;
     s.rmod = o.rmod;
+    s.f_rmod = make_fastdiv(o.rmod > 0 ? o.rmod : 1);
     s.ld = o.ld;
     s.ld2 = o.ld2;
     s.batch_stride = o.batch_stride;
@@ -104,6 +105,7 @@ Plan make_plan(const Ctx* ctx, const GemmProblem& g, size_t scratch_limit) {
     int esize = pl.f32 ? 4 : 2;
     pl.tma = !pl.f32 && tma_ok(g.a, esize) && tma_ok(g.b, esize) && encode_tiled() != nullptr && !env_int("D8K_FORCE_GATHER", 0);
     if (pl.tma) pl.bn = g.N > 128 ? 256 : 128;
+    else if (pl.f32) pl.bn = 64;  // the 64-column fp32 kernel runs two loader groups (see GemmCfg::LOADER_GROUPS)
     else pl.bn = g.N > 64 ? 128 : 64;
     int forced_bn = env_int("D8K_BN", 0);
     if (forced_bn == 64 && !pl.tma) pl.bn = 64;
@@ -209,8 +211,13 @@ int run_gemm(Ctx* ctx, const GemmProblem& g) {
         fn = lookup_f16_pair(g.a.mn, g.b.mn);
     } else if (pl.tma) {
         // K-major: {K, rows}; MN-major: {rows(M or N), K}
-        bool oka = g.a.mn ? make_map(&ta, g.a, g.M, g.K, 64) : make_map(&ta, g.a, g.K, g.M, kBM);
-        bool okb = g.b.mn ? make_map(&tb, g.b, g.N, g.K, 64) : make_map(&tb, g.b, g.K, g.N, pl.bn);
+        // an MN-major operand whose extent is a multiple of 64 arrives as one 4-D box {64, 64 k-rows, chunks of 64, 1}
+        p.a_chunked = g.a.mn && g.M % 64 == 0 && env_int("D8K_CHUNKED", 1);
+        p.b_chunked = g.b.mn && g.N % 64 == 0 && env_int("D8K_CHUNKED", 1);
+        bool oka = p.a_chunked ? make_pair_map(&ta, g.a, g.M, g.K, 64, kBM / 64)
+                               : (g.a.mn ? make_map(&ta, g.a, g.M, g.K, 64) : make_map(&ta, g.a, g.K, g.M, kBM));
+        bool okb = p.b_chunked ? make_pair_map(&tb, g.b, g.N, g.K, 64, pl.bn / 64)
+                               : (g.b.mn ? make_map(&tb, g.b, g.N, g.K, 64) : make_map(&tb, g.b, g.K, g.N, pl.bn));
         if (!oka || !okb) return fail(2, "gemm: cuTensorMapEncodeTiled failed");
         fn = lookup_f16_tma(g.a.mn, g.b.mn, pl.bn);
     } else {
