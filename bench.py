@@ -163,10 +163,18 @@ def run_reference_arm(args):
     print(json.dumps(line), flush=True)
 
 
+def exchange_name(n):
+    if n == 1:
+        return "single GPU: nothing to exchange"
+    mode = os.environ.get("D8_BENCH_ALLREDUCE", "peer")
+    return {"peer": "peer memory: copy-engine reduce-scatter/all-gather + fixed-order sum kernel on a side stream",
+            "end": "NCCL all-reduce after the last contraction"}.get(mode, "NCCL all-reduce started as each gradient completes")
+
+
 def workload_config(n):
     return {"workload": "config 5: fp16 2-layer MLP fwd+bwd via MatrixMultiply, X %dx%d per GPU, W1 %dx%d, ReLU, W2 %dx%d" %
             (M_PER_GPU, D_IN, D_IN, D_HID, D_HID, D_IN), "rows_per_gpu": M_PER_GPU, "global_rows": M_PER_GPU * n,
-            "parallelism": "batch-sharded x%d, weight gradients all-reduced" % n,
+            "parallelism": "batch-sharded x%d, weight gradients summed across GPUs (%s)" % (n, exchange_name(n)),
             "flop_per_gpu_step": FLOP_PER_STEP, "l2": "inputs exceed L2 (weights 2x128 MiB, activations 4x256 MiB per GPU)"}
 
 
@@ -175,8 +183,9 @@ class MlpStep:
     """The MLP step on one GPU through the d8k C ABI; buffers allocated once, as an executor would keep them.
     X, dY and Y are double-buffered so that the end-to-end loop can copy step i+1 in and step i-1 out while step i runs."""
 
-    def __init__(self, ctx, torch, device, rank, fused=True):
+    def __init__(self, ctx, torch, device, rank, fused=True, exchange=None):
         self.ctx, self.torch, self.fused = ctx, torch, fused
+        self.ar1 = self.ar2 = None
         g = torch.Generator(device=device)
         g.manual_seed(10)
         h = torch.float16
@@ -192,7 +201,19 @@ class MlpStep:
         self.H, self.A = e(1, M_PER_GPU, D_HID), e(1, M_PER_GPU, D_HID)
         self.dA, self.dH = e(1, M_PER_GPU, D_HID), e(1, M_PER_GPU, D_HID)
         self.dX, self.dW1, self.dW2 = torch.empty_like(self.X[0]), torch.empty_like(self.W1), torch.empty_like(self.W2)
+        if exchange is not None:
+            # weight gradients live in memory the peers map; the sums arrive in ar.result
+            self.ar1, self.ar2 = exchange(self.W1.numel()), exchange(self.W2.numel())
+            self.dW1, self.dW2 = self.ar1.partial.view(self.W1.shape), self.ar2.partial.view(self.W2.shape)
         self.gemm_events = []
+        self.tail_events = []  # (after the last contraction, after the exchange has been waited for)
+
+    def _reduce(self, which, dist, work, overlap):
+        ar, grad = (self.ar1, self.dW1) if which == 1 else (self.ar2, self.dW2)
+        if ar is not None:
+            ar.start()
+        elif dist is not None and overlap:
+            work.append(dist.all_reduce(grad, async_op=True))
 
     def _gemm(self, fn, timed):
         if timed:
@@ -207,34 +228,47 @@ class MlpStep:
     def step(self, dist=None, timed=False, buf=0):
         c = self.ctx
         X, dY, Y = self.X[buf], self.dY[buf], self.Y[buf]
-        overlap = os.environ.get("D8_BENCH_ALLREDUCE", "overlap") == "overlap"
+        overlap = os.environ.get("D8_BENCH_ALLREDUCE", "peer") != "end"
         work = []
+        if self.ar1 is not None:
+            self.ar2.before_write()
+            self.ar1.before_write()
         if self.fused:
+            # Weight gradients are produced as early as their inputs allow, so that each exchange has contractions
+            # still to run behind it: dW2 needs only A and dY, dW1 needs dH, and dX (no exchange) goes last.
             self._gemm(lambda: c.matmul_forward_relu(X, self.W1, self.H, self.A), timed)
             self._gemm(lambda: c.matmul_forward(self.A, self.W2, out=Y), timed)
-            self._gemm(lambda: c.matmul_grad_x_relu(self.A, self.dA, self.W2, dY, self.H, self.dH, False, False), timed)
             self._gemm(lambda: c.matmul_grad_y(self.A, self.W2, self.dW2, dY, accumulate=False), timed)
-            if dist is not None and overlap:
-                work.append(dist.all_reduce(self.dW2, async_op=True))  # overlaps the rest of the backward pass
-            self._gemm(lambda: c.matmul_grad_x(X, self.dX, self.W1, self.dH, accumulate=False), timed)
+            self._reduce(2, dist, work, overlap)
+            self._gemm(lambda: c.matmul_grad_x_relu(self.A, self.dA, self.W2, dY, self.H, self.dH, False, False), timed)
             self._gemm(lambda: c.matmul_grad_y(X, self.W1, self.dW1, self.dH, accumulate=False), timed)
+            self._reduce(1, dist, work, overlap)
+            self._gemm(lambda: c.matmul_grad_x(X, self.dX, self.W1, self.dH, accumulate=False), timed)
         else:
             for t in (self.dA, self.dH, self.dX, self.dW1, self.dW2):
                 c.zero(t)
             self._gemm(lambda: c.matmul_forward(X, self.W1, out=self.H), timed)
             c.relu_forward(self.H, out=self.A)
             self._gemm(lambda: c.matmul_forward(self.A, self.W2, out=Y), timed)
-            self._gemm(lambda: c.matmul_grad_x(self.A, self.dA, self.W2, dY), timed)
             self._gemm(lambda: c.matmul_grad_y(self.A, self.W2, self.dW2, dY), timed)
-            if dist is not None and overlap:
-                work.append(dist.all_reduce(self.dW2, async_op=True))
+            self._reduce(2, dist, work, overlap)
+            self._gemm(lambda: c.matmul_grad_x(self.A, self.dA, self.W2, dY), timed)
             c.relu_backward(self.H, self.dH, self.dA)
-            self._gemm(lambda: c.matmul_grad_x(X, self.dX, self.W1, self.dH), timed)
             self._gemm(lambda: c.matmul_grad_y(X, self.W1, self.dW1, self.dH), timed)
-        if dist is not None:
+            self._reduce(1, dist, work, overlap)
+            self._gemm(lambda: c.matmul_grad_x(X, self.dX, self.W1, self.dH), timed)
+        if self.ar1 is not None:
+            if timed:
+                self.tail_events.append((self.torch.cuda.Event(enable_timing=True), self.torch.cuda.Event(enable_timing=True)))
+                self.tail_events[-1][0].record()
+            self.ar2.finish()
+            self.ar1.finish()
+            if timed:
+                self.tail_events[-1][1].record()
+        elif dist is not None:
             if not overlap:
                 work.append(dist.all_reduce(self.dW2, async_op=True))
-            work.append(dist.all_reduce(self.dW1, async_op=True))
+                work.append(dist.all_reduce(self.dW1, async_op=True))
             for w in work:
                 w.wait()
 
@@ -258,7 +292,17 @@ def run_gpu_arm(args):
     ctx = deep8_b200.Context(local_rank)
     stream = torch.cuda.current_stream()
     ctx.use_stream(stream if stream.cuda_stream != 0 else None)
-    mlp = MlpStep(ctx, torch, device, rank, fused=not args.unfused)
+    exchange = None
+    mode = os.environ.get("D8_BENCH_ALLREDUCE", "peer")
+    if world > 1 and mode == "peer":
+        # gradient exchange through peer memory on a side stream (deep8_b200.dp.PeerAllReduce); D8_BENCH_ALLREDUCE=overlap
+        # or =end selects NCCL all-reduce instead, started as each gradient completes or after the last contraction
+        from deep8_b200.dp import PeerAllReduce
+        side = torch.cuda.Stream(device=device)
+        ctx_side = deep8_b200.Context(local_rank, scratch_bytes=1 << 20)
+        ctx_side.use_stream(side)
+        exchange = lambda numel: PeerAllReduce(ctx, ctx_side, side, numel, torch.float16, device)
+    mlp = MlpStep(ctx, torch, device, rank, fused=not args.unfused, exchange=exchange)
 
     def barrier():
         if dist is not None:
@@ -275,7 +319,7 @@ def run_gpu_arm(args):
     for _ in range(args.warmup):
         mlp.step(dist)
     barrier()
-    if ctx.status() != 0:
+    if ctx.status() != 0 or (exchange is not None and ctx_side.status() != 0):
         raise SystemExit("kernel status non-zero after warm-up")
 
     # ---- device-resident timed region
@@ -297,7 +341,12 @@ def run_gpu_arm(args):
     ms_step = ms_total / args.steps
     gemm_ms = [a.elapsed_time(b) for a, b in mlp.gemm_events]
     mlp.gemm_events = []
-    if ctx.status() != 0:
+    if os.environ.get("D8_BENCH_DIAG"):  # per rank: where the step's time went
+        tail = [a.elapsed_time(b) for a, b in mlp.tail_events]
+        print("rank %d: step %.3f ms, contractions %.3f ms, exchange left after the last contraction %.3f ms" %
+              (rank, t0.elapsed_time(t1) / args.steps, sum(gemm_ms) / args.steps, sum(tail) / max(1, args.steps)), file=sys.stderr, flush=True)
+    mlp.tail_events = []
+    if ctx.status() != 0 or (exchange is not None and ctx_side.status() != 0):
         raise SystemExit("kernel status non-zero after the timed region")
 
     if args.profile:
@@ -477,6 +526,10 @@ def run_small_config(args):
             return impl.conv2d_forward(x, w, *meta), impl.conv2d_grad_x(x, w, dz, *meta), impl.conv2d_grad_y(x, w, dz, *meta)
         return impl.deconv2d_forward(x, w, *meta), impl.deconv2d_grad_x(x, w, dz, *meta), impl.deconv2d_grad_y(x, w, dz, *meta)
 
+    if args.no_cpu:
+        print(json.dumps({"report": "config %d" % n, "workload": name, "ms_per_step": ms, "tflops": flop / ms / 1e9,
+                          "steps": args.steps, "cpu": None}), flush=True)
+        return
     want = cpu(oracle)
     got = (Z.cpu().numpy(), DX.cpu().numpy(), DW.cpu().numpy())
     err = max(cases.rel_max(g, r) for g, r in zip(got, want))

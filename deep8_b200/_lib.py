@@ -45,7 +45,17 @@ SIGNATURES = {
     "d8k_relu_forward": (_i, [_vp, _i, _vp, _vp, _sz]),
     "d8k_relu_backward": (_i, [_vp, _i, _vp, _vp, _vp, _sz]),
     "d8k_zero": (_i, [_vp, _vp, _sz]),
+    "d8k_peer_alloc": (_i, [_vp, _sz, ctypes.POINTER(_vp), ctypes.c_char_p]),
+    "d8k_peer_free": (_i, [_vp, _vp]),
+    "d8k_peer_open": (_i, [_vp, ctypes.c_char_p, ctypes.POINTER(_vp)]),
+    "d8k_peer_close": (_i, [_vp, _vp]),
+    "d8k_peer_signal": (_i, [_vp, ctypes.POINTER(_vp), _i, ctypes.c_uint]),
+    "d8k_peer_wait": (_i, [_vp, ctypes.POINTER(_vp), _i, ctypes.c_uint, ctypes.c_double]),
+    "d8k_peer_copy": (_i, [_vp, _vp, _vp, _sz]),
+    "d8k_sum_shards": (_i, [_vp, _i, _vp, ctypes.POINTER(_vp), _i, _sz]),
 }
+
+IPC_HANDLE_BYTES = 64
 
 _lib = None
 

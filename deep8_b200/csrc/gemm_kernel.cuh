@@ -282,6 +282,54 @@ __device__ __forceinline__ uint4 fetch16(const GatherSrc& s, int g, int col, lon
     return *reinterpret_cast<uint4*>(tmp);
 }
 
+// The common case of fetch16 split in two so that the loader can issue all of a k-block's loads back to back:
+// plan16 only computes where the 16 bytes are - kFetchZero (padding or outside the matrix), kFetchSlow (needs the
+// element-wise path of fetch16) or the address of an aligned 16-byte load - and ldg_pred performs the load as ONE
+// predicated instruction.  Loading inside fetch16's branches made the compiler merge each loaded value at a branch
+// join, which serialised the loads: about one global-memory latency per chunk.
+constexpr uintptr_t kFetchZero = 0, kFetchSlow = 1;
+template <typename T, int VEC>
+__device__ __forceinline__ uintptr_t plan16(const GatherSrc& s, int g, int col, long long boff, const ColCtx& k) {
+    if (g >= s.rows || col >= s.cols) return kFetchZero;
+    const T* base = reinterpret_cast<const T*>(s.base);
+    const T* p;
+    if (s.kind == 0) {
+        p = base + boff + col;
+        if (s.rmod > 0) {
+            int q = fdiv(g, s.f_rmod);
+            p += static_cast<long long>(g - q * s.rmod) * s.ld + static_cast<long long>(q) * s.ld2;
+        } else {
+            p += static_cast<long long>(g) * s.ld;
+        }
+        if (col + VEC > s.cols) return kFetchSlow;
+    } else {
+        if (!k.inside) return kFetchSlow;
+        long long off;
+        if (!locate(s.cr, g, k, off)) return kFetchZero;
+        p = base + off;
+    }
+    uintptr_t a = reinterpret_cast<uintptr_t>(p);
+    return (a & 15) ? kFetchSlow : a;
+}
+
+__device__ __forceinline__ uint4 ldg_pred(uintptr_t addr) {  // zeros unless addr is a real address
+    uint4 v;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred q;\n\t"
+        "setp.gt.u64 q, %4, 1;\n\t"
+        "mov.b32 %0, 0;\n\t"
+        "mov.b32 %1, 0;\n\t"
+        "mov.b32 %2, 0;\n\t"
+        "mov.b32 %3, 0;\n\t"
+        "@q ld.global.nc.v4.b32 {%0, %1, %2, %3}, [%4];\n\t"
+        "}"
+        : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+        : "l"(addr)
+        : "memory");
+    return v;
+}
+
 // Swizzled position of 16-byte chunk j of row r inside a tile of 128-byte rows (tile base 1024-byte aligned).
 // BASE32 == false: address bits [4,7) are XORed with bits [7,10), the pattern TMA and tcgen05 call SWIZZLE_128B.
 // BASE32 == true : address bits [5,7) are XORed with bits [7,9) (32-byte atoms), for MN-major tf32 operands.
@@ -734,6 +782,8 @@ d8k_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                 if (!Cfg::A_MN && p.a.kind == 1) ka = col_ctx<Cfg::VEC>(p.a, k0 + j * Cfg::VEC);
                 if (!Cfg::B_MN && p.b.kind == 1) kbx = col_ctx<Cfg::VEC>(p.b, k0 + j * Cfg::VEC);
                 uint4 va[A_ITERS], vb[B_ITERS];
+                uintptr_t pa[A_ITERS], pb[B_ITERS];
+                bool any_slow = false;
 #pragma unroll
                 for (int i = 0; i < A_ITERS; ++i) {
                     int r = (i * 4 + lw) * 4 + sub;
@@ -746,7 +796,8 @@ d8k_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                         col = it.m0 + (r / BK) * CE + j * Cfg::VEC;
                         if (p.a.kind == 1) ka = col_ctx<Cfg::VEC>(p.a, col);
                     }
-                    va[i] = fetch16<InT, Cfg::VEC>(p.a, g, col, boff_a, ka);
+                    pa[i] = plan16<InT, Cfg::VEC>(p.a, g, col, boff_a, ka);
+                    any_slow |= pa[i] == kFetchSlow;
                 }
 #pragma unroll
                 for (int i = 0; i < B_ITERS; ++i) {
@@ -760,7 +811,34 @@ d8k_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                         col = it.n0 + (r / BK) * CE + j * Cfg::VEC;
                         if (p.b.kind == 1) kbx = col_ctx<Cfg::VEC>(p.b, col);
                     }
-                    vb[i] = fetch16<InT, Cfg::VEC>(p.b, g, col, boff_b, kbx);
+                    pb[i] = plan16<InT, Cfg::VEC>(p.b, g, col, boff_b, kbx);
+                    any_slow |= pb[i] == kFetchSlow;
+                }
+#pragma unroll
+                for (int i = 0; i < A_ITERS; ++i) va[i] = ldg_pred(pa[i]);
+#pragma unroll
+                for (int i = 0; i < B_ITERS; ++i) vb[i] = ldg_pred(pb[i]);
+                if (any_slow) {  // ragged edges, unaligned rows, chunks that straddle filter taps: element by element
+#pragma unroll
+                    for (int i = 0; i < A_ITERS; ++i) {
+                        if (pa[i] != kFetchSlow) continue;
+                        int r = (i * 4 + lw) * 4 + sub;
+                        int g = Cfg::A_MN ? k0 + (r % BK) : it.m0 + r;
+                        int col = Cfg::A_MN ? it.m0 + (r / BK) * CE + j * Cfg::VEC : k0 + j * Cfg::VEC;
+                        ColCtx kc = {};
+                        if (p.a.kind == 1) kc = col_ctx<Cfg::VEC>(p.a, col);
+                        va[i] = fetch16<InT, Cfg::VEC>(p.a, g, col, boff_a, kc);
+                    }
+#pragma unroll
+                    for (int i = 0; i < B_ITERS; ++i) {
+                        if (pb[i] != kFetchSlow) continue;
+                        int r = (i * 4 + lw) * 4 + sub;
+                        int g = Cfg::B_MN ? k0 + (r % BK) : it.n0 + r;
+                        int col = Cfg::B_MN ? it.n0 + (r / BK) * CE + j * Cfg::VEC : k0 + j * Cfg::VEC;
+                        ColCtx kc = {};
+                        if (p.b.kind == 1) kc = col_ctx<Cfg::VEC>(p.b, col);
+                        vb[i] = fetch16<InT, Cfg::VEC>(p.b, g, col, boff_b, kc);
+                    }
                 }
 #pragma unroll
                 for (int i = 0; i < A_ITERS; ++i) {

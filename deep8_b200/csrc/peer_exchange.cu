@@ -1,0 +1,274 @@
+// extern "C" layer, part two (include/d8k.h, "Exchange of replicated-operand gradients"): memory that the other
+// processes of the box map through CUDA IPC, stream-ordered flags between processes, copy-engine transfers and the
+// fixed-order sum of partial gradients.  The transfers use no SM, and the three small kernels here (signal, wait, sum)
+// need no shared memory and few registers, so they share SMs with a running contraction kernel instead of waiting for
+// one to drain - which is what a library all-reduce kernel, with its large register footprint, has to do.
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <cstdint>
+#include <cstring>
+#include <string>
+
+#include "../../include/d8k.h"
+#include "gemm_host.h"
+
+struct d8k_ctx : public d8k::Ctx {};
+
+namespace d8k {
+namespace {
+
+constexpr int kMaxPeers = 16;
+constexpr int kRoleExchange = 5;  // role field of the status word for a wait that expired here
+
+#define D8K_CUDA(call)                                                                                          \
+    do {                                                                                                        \
+        cudaError_t e__ = (call);                                                                               \
+        if (e__ != cudaSuccess) return fail(D8K_ERR_CUDA, std::string(#call) + ": " + cudaGetErrorString(e__)); \
+    } while (0)
+
+struct FlagList {
+    unsigned* p[kMaxPeers];
+};
+struct SrcList {
+    const void* p[kMaxPeers];
+};
+
+__device__ __forceinline__ unsigned long long global_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+
+// One warp; lane i publishes to flag i.  The fence orders every earlier write of this GPU (kernels and copies that
+// completed before this kernel started, in stream order) before the flag for an observer on any GPU.
+__global__ void peer_signal_kernel(FlagList flags, int n, unsigned value) {
+    int i = threadIdx.x;
+    if (i < n) {
+        __threadfence_system();
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(flags.p[i]), "r"(value) : "memory");
+    }
+}
+
+// One warp; lane i polls flag i until it reaches `value` or the time limit passes.  The first lane that gives up
+// records (role << 8 | i) in the status word; the kernel then ends either way, so the stream always moves on.
+__global__ void peer_wait_kernel(FlagList flags, int n, unsigned value, unsigned long long limit_ns, int* status) {
+    int i = threadIdx.x;
+    if (i >= n) return;
+    const unsigned long long t0 = global_ns();
+    unsigned seen;
+    for (;;) {
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(flags.p[i]) : "memory");
+        if (static_cast<int>(seen - value) >= 0) break;  // counters wrap: compare as a signed distance
+        if (global_ns() - t0 > limit_ns) {
+            atomicCAS(status, 0, (kRoleExchange << 8) | i);
+            break;
+        }
+        __nanosleep(256);
+    }
+}
+
+template <typename T>
+__device__ __forceinline__ void accumulate16(float* acc, const uint4& v);
+template <>
+__device__ __forceinline__ void accumulate16<float>(float* acc, const uint4& v) {
+    acc[0] += __uint_as_float(v.x);
+    acc[1] += __uint_as_float(v.y);
+    acc[2] += __uint_as_float(v.z);
+    acc[3] += __uint_as_float(v.w);
+}
+template <>
+__device__ __forceinline__ void accumulate16<__half>(float* acc, const uint4& v) {
+    const __half2* h = reinterpret_cast<const __half2*>(&v);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        float2 f = __half22float2(h[k]);
+        acc[2 * k] += f.x;
+        acc[2 * k + 1] += f.y;
+    }
+}
+template <typename T>
+__device__ __forceinline__ uint4 round16(const float* acc);
+template <>
+__device__ __forceinline__ uint4 round16<float>(const float* acc) {
+    return make_uint4(__float_as_uint(acc[0]), __float_as_uint(acc[1]), __float_as_uint(acc[2]), __float_as_uint(acc[3]));
+}
+template <>
+__device__ __forceinline__ uint4 round16<__half>(const float* acc) {
+    uint4 o;
+    __half2* h = reinterpret_cast<__half2*>(&o);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) h[k] = __floats2half2_rn(acc[2 * k], acc[2 * k + 1]);
+    return o;
+}
+
+// out = srcs[0] + srcs[1] + ... in that order, fp32 accumulation, 16 bytes per thread per step; NSRC > 0 unrolls the
+// source loop so that all loads of a step are in flight together.
+template <typename T, int NSRC>
+__global__ void __launch_bounds__(256) sum_shards_kernel(T* out, SrcList srcs, int nsrc, size_t count, bool vec) {
+    constexpr int V = 16 / sizeof(T);
+    const size_t tid = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x;
+    const size_t stride = gridDim.x * static_cast<size_t>(blockDim.x);
+    const size_t nv = vec ? count / V : 0;
+    for (size_t i = tid; i < nv; i += stride) {
+        float acc[V];
+#pragma unroll
+        for (int k = 0; k < V; ++k) acc[k] = 0.f;
+        if constexpr (NSRC > 0) {
+            uint4 v[NSRC];
+#pragma unroll
+            for (int s = 0; s < NSRC; ++s) v[s] = __ldcs(reinterpret_cast<const uint4*>(srcs.p[s]) + i);
+#pragma unroll
+            for (int s = 0; s < NSRC; ++s) accumulate16<T>(acc, v[s]);
+        } else {
+            for (int s = 0; s < nsrc; ++s) accumulate16<T>(acc, __ldcs(reinterpret_cast<const uint4*>(srcs.p[s]) + i));
+        }
+        reinterpret_cast<uint4*>(out)[i] = round16<T>(acc);
+    }
+    for (size_t i = nv * V + tid; i < count; i += stride) {
+        float a = 0.f;
+        for (int s = 0; s < nsrc; ++s) {
+            if constexpr (sizeof(T) == 4) a += reinterpret_cast<const float*>(srcs.p[s])[i];
+            else a += __half2float(reinterpret_cast<const __half*>(srcs.p[s])[i]);
+        }
+        if constexpr (sizeof(T) == 4) reinterpret_cast<float*>(out)[i] = a;
+        else reinterpret_cast<__half*>(out)[i] = __float2half_rn(a);
+    }
+}
+
+template <typename T>
+void launch_sum(const Ctx* ctx, void* out, const SrcList& srcs, int nsrc, size_t count, bool vec) {
+    constexpr int V = 16 / sizeof(T);
+    size_t blocks = (count / V + 255) / 256;
+    size_t cap = static_cast<size_t>(ctx->num_sms) * 4;
+    if (blocks > cap) blocks = cap;
+    if (blocks < 1) blocks = 1;
+    dim3 grid(static_cast<unsigned>(blocks));
+    T* o = static_cast<T*>(out);
+    switch (nsrc) {
+        case 2: sum_shards_kernel<T, 2><<<grid, 256, 0, ctx->stream>>>(o, srcs, nsrc, count, vec); break;
+        case 4: sum_shards_kernel<T, 4><<<grid, 256, 0, ctx->stream>>>(o, srcs, nsrc, count, vec); break;
+        case 8: sum_shards_kernel<T, 8><<<grid, 256, 0, ctx->stream>>>(o, srcs, nsrc, count, vec); break;
+        default: sum_shards_kernel<T, 0><<<grid, 256, 0, ctx->stream>>>(o, srcs, nsrc, count, vec); break;
+    }
+}
+
+int check_ctx(const d8k_ctx* ctx) {
+    if (!ctx) return fail(D8K_ERR_ARGUMENT, "null context");
+    return 0;
+}
+
+}  // namespace
+}  // namespace d8k
+
+using namespace d8k;
+
+extern "C" {
+
+int d8k_peer_alloc(d8k_ctx* ctx, size_t bytes, void** ptr, unsigned char handle[D8K_IPC_HANDLE_BYTES]) {
+    static_assert(sizeof(cudaIpcMemHandle_t) == D8K_IPC_HANDLE_BYTES, "IPC handle size");
+    if (int rc = check_ctx(ctx)) return rc;
+    if (!ptr || !handle || bytes == 0) return fail(D8K_ERR_ARGUMENT, "peer_alloc: null pointer or zero size");
+    D8K_CUDA(cudaSetDevice(ctx->device));
+    void* p = nullptr;
+    D8K_CUDA(cudaMalloc(&p, bytes));
+    cudaError_t e = cudaMemset(p, 0, bytes);
+    cudaIpcMemHandle_t h;
+    if (e == cudaSuccess) e = cudaIpcGetMemHandle(&h, p);
+    if (e != cudaSuccess) {
+        cudaFree(p);
+        return fail(D8K_ERR_CUDA, std::string("peer_alloc: ") + cudaGetErrorString(e));
+    }
+    memcpy(handle, &h, sizeof(h));
+    *ptr = p;
+    return 0;
+}
+
+int d8k_peer_free(d8k_ctx* ctx, void* ptr) {
+    if (int rc = check_ctx(ctx)) return rc;
+    if (!ptr) return 0;
+    D8K_CUDA(cudaSetDevice(ctx->device));
+    D8K_CUDA(cudaFree(ptr));
+    return 0;
+}
+
+int d8k_peer_open(d8k_ctx* ctx, const unsigned char handle[D8K_IPC_HANDLE_BYTES], void** ptr) {
+    if (int rc = check_ctx(ctx)) return rc;
+    if (!ptr || !handle) return fail(D8K_ERR_ARGUMENT, "peer_open: null pointer");
+    D8K_CUDA(cudaSetDevice(ctx->device));
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle, sizeof(h));
+    void* p = nullptr;
+    D8K_CUDA(cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess));
+    *ptr = p;
+    return 0;
+}
+
+int d8k_peer_close(d8k_ctx* ctx, void* ptr) {
+    if (int rc = check_ctx(ctx)) return rc;
+    if (!ptr) return 0;
+    D8K_CUDA(cudaSetDevice(ctx->device));
+    D8K_CUDA(cudaIpcCloseMemHandle(ptr));
+    return 0;
+}
+
+int d8k_peer_signal(d8k_ctx* ctx, void* const* flags, int n, unsigned value) {
+    if (int rc = check_ctx(ctx)) return rc;
+    if (n == 0) return 0;
+    if (!flags || n < 0 || n > kMaxPeers) return fail(D8K_ERR_ARGUMENT, "peer_signal: 1 to 16 flags");
+    FlagList f = {};
+    for (int i = 0; i < n; ++i) {
+        if (!flags[i] || (reinterpret_cast<uintptr_t>(flags[i]) & 3)) return fail(D8K_ERR_ARGUMENT, "peer_signal: null or unaligned flag");
+        f.p[i] = static_cast<unsigned*>(flags[i]);
+    }
+    peer_signal_kernel<<<1, 32, 0, ctx->stream>>>(f, n, value);
+    D8K_CUDA(cudaGetLastError());
+    count_launch();
+    return 0;
+}
+
+int d8k_peer_wait(d8k_ctx* ctx, const void* const* flags, int n, unsigned value, double timeout_ms) {
+    if (int rc = check_ctx(ctx)) return rc;
+    if (n == 0) return 0;
+    if (!flags || n < 0 || n > kMaxPeers) return fail(D8K_ERR_ARGUMENT, "peer_wait: 1 to 16 flags");
+    if (!(timeout_ms > 0.0) || timeout_ms > 60000.0) return fail(D8K_ERR_ARGUMENT, "peer_wait: the time limit must be in (0, 60000] ms");
+    FlagList f = {};
+    for (int i = 0; i < n; ++i) {
+        if (!flags[i] || (reinterpret_cast<uintptr_t>(flags[i]) & 3)) return fail(D8K_ERR_ARGUMENT, "peer_wait: null or unaligned flag");
+        f.p[i] = const_cast<unsigned*>(static_cast<const unsigned*>(flags[i]));
+    }
+    peer_wait_kernel<<<1, 32, 0, ctx->stream>>>(f, n, value, static_cast<unsigned long long>(timeout_ms * 1e6), ctx->status);
+    D8K_CUDA(cudaGetLastError());
+    count_launch();
+    return 0;
+}
+
+int d8k_peer_copy(d8k_ctx* ctx, void* dst, const void* src, size_t bytes) {
+    if (int rc = check_ctx(ctx)) return rc;
+    if (bytes == 0) return 0;
+    if (!dst || !src) return fail(D8K_ERR_ARGUMENT, "peer_copy: null pointer");
+    D8K_CUDA(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDefault, ctx->stream));
+    return 0;
+}
+
+int d8k_sum_shards(d8k_ctx* ctx, int dtype, void* out, const void* const* srcs, int nsrc, size_t count) {
+    if (int rc = check_ctx(ctx)) return rc;
+    if (dtype != D8K_F16 && dtype != D8K_F32) return fail(D8K_ERR_ARGUMENT, "type is not support: dtype must be D8K_F16 or D8K_F32");
+    if (count == 0) return 0;
+    if (!out || !srcs || nsrc < 1 || nsrc > kMaxPeers) return fail(D8K_ERR_ARGUMENT, "sum_shards: 1 to 16 sources");
+    SrcList s = {};
+    uintptr_t bits = reinterpret_cast<uintptr_t>(out);
+    for (int i = 0; i < nsrc; ++i) {
+        if (!srcs[i]) return fail(D8K_ERR_ARGUMENT, "sum_shards: null source");
+        s.p[i] = srcs[i];
+        bits |= reinterpret_cast<uintptr_t>(srcs[i]);
+    }
+    bool vec = (bits & 15) == 0;
+    if (dtype == D8K_F32) launch_sum<float>(ctx, out, s, nsrc, count, vec);
+    else launch_sum<__half>(ctx, out, s, nsrc, count, vec);
+    D8K_CUDA(cudaGetLastError());
+    count_launch();
+    return 0;
+}
+
+}  // extern "C"

@@ -35,3 +35,137 @@ class GradientSync:
         for w in self.pending:
             w.wait()
         self.pending = []
+
+
+# ---------------------------------------------------------------------------------------------- exchange over peer memory
+def gradient_shards(numel, world, align=128):
+    """[lo, hi) element ranges, one per rank, that partition a gradient of `numel` elements; every boundary but the last
+    is a multiple of `align` elements so that each shard starts on a 16-byte boundary for any element type."""
+    per = -(-numel // world)
+    per = -(-per // align) * align
+    return [(min(k * per, numel), min((k + 1) * per, numel)) for k in range(world)]
+
+
+def peer_rotation(world, rank):
+    """Order in which `rank` visits its peers: rank+1, rank+2, ...  At visit k every rank talks to a different peer, so
+    the transfers of one round never meet at one GPU."""
+    return [(rank + k) % world for k in range(1, world)]
+
+
+class PeerAllReduce:
+    """Sum of one replicated-operand gradient over the GPUs of a box without a collective kernel.
+
+    Each rank's contraction writes its partial gradient into `partial` (memory the peers map).  Then, on a side stream:
+    the rank tells its peers the partial is ready, pulls its own shard of every peer's partial with the copy engines, adds
+    the shards in rank order (fp32, one rounding - every rank would get the same bits for the same shard), pushes the
+    finished shard into every peer's `result`, and waits until the other shards have arrived.  No SM moves data between
+    GPUs and the three small kernels involved share SMs with whatever contraction is running, so the exchange hides
+    behind the rest of the backward pass instead of competing with it.
+
+    Waits between ranks are kernels with a time limit: a peer that never arrives sets the context's status word (read it
+    with Context.status()) and the stream carries on.
+
+        ar = PeerAllReduce(ctx_main, ctx_side, side_stream, numel, torch.float16, device)
+        ar.before_write()                 # main stream: peers are done reading the previous partial
+        ...contraction writes ar.partial...
+        ar.start()                        # exchange runs on the side stream
+        ...more work on the main stream...
+        ar.finish()                       # main stream waits; ar.result holds the sum
+    """
+
+    FLAG_WORDS = 64  # per kind: one word per peer, padded
+
+    def __init__(self, ctx_main, ctx_side, side_stream, numel, dtype, device, group=None, timeout_ms=2000.0):
+        import torch
+        from .ops import tensor_view
+        self.torch, self.ctx_main, self.ctx_side, self.side = torch, ctx_main, ctx_side, side_stream
+        self.numel, self.dtype, self.device, self.group, self.timeout_ms = numel, dtype, device, group, timeout_ms
+        self.world = dist.get_world_size(group) if dist.is_available() and dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if self.world > 1 else 0
+        if self.world > 16:
+            raise ValueError("at most 16 GPUs exchange through peer memory")
+        self.esize = torch.empty((), dtype=dtype).element_size()
+        self.shards = gradient_shards(numel, self.world)
+        self.step = 0
+        lo, hi = self.shards[self.rank]
+        self.shard_elems = self.shards[0][1] - self.shards[0][0]
+        grad_bytes = -(-numel * self.esize // 256) * 256
+        stage_bytes = -(-self.shard_elems * self.esize // 256) * 256
+        # one allocation: partial | result | staging slot per rank | flags (ready, pulled, gathered)
+        self.off_partial, self.off_result = 0, grad_bytes
+        self.off_stage = 2 * grad_bytes
+        self.off_flags = self.off_stage + self.world * stage_bytes
+        self.stage_bytes = stage_bytes
+        total = self.off_flags + 3 * self.FLAG_WORDS * 4
+        self.base, handle = ctx_main.peer_alloc(total)
+        self.peers = [None] * self.world
+        self.peers[self.rank] = self.base
+        if self.world > 1:
+            handles = [None] * self.world
+            dist.all_gather_object(handles, handle, group=group)
+            for q in range(self.world):
+                if q != self.rank:
+                    self.peers[q] = ctx_main.peer_open(handles[q])
+        self.partial = tensor_view(self.base + self.off_partial, (numel,), dtype, device)
+        self.result = tensor_view(self.base + self.off_result, (numel,), dtype, device) if self.world > 1 else self.partial
+        self.order = peer_rotation(self.world, self.rank)
+        self.e_written = torch.cuda.Event()
+        self.e_done = torch.cuda.Event()
+        if self.world > 1:
+            dist.barrier(group=group)  # every rank has mapped every buffer before the first signal
+
+    def _flag(self, owner, kind, writer):
+        return self.peers[owner] + self.off_flags + (kind * self.FLAG_WORDS + writer) * 4
+
+    def before_write(self):
+        """Main stream: hold the next write of `partial` until every peer has pulled its shard of the previous one."""
+        if self.world > 1 and self.step > 0:
+            self.ctx_main.peer_wait([self._flag(self.rank, 1, q) for q in self.order], self.step, self.timeout_ms)
+
+    def start(self):
+        """Call after the contraction that writes `partial` has been enqueued on the main stream."""
+        if self.world == 1:
+            return
+        torch, c, r = self.torch, self.ctx_side, self.rank
+        self.step += 1
+        s = self.step
+        self.e_written.record(torch.cuda.current_stream())
+        self.side.wait_event(self.e_written)
+        lo, hi = self.shards[r]
+        n = hi - lo
+        c.peer_signal([self._flag(q, 0, r) for q in self.order], s)                       # my partial is ready
+        c.peer_wait([self._flag(r, 0, q) for q in self.order], s, self.timeout_ms)        # so are theirs
+        if n > 0:
+            for q in self.order:                                                           # reduce-scatter: pull my shard
+                c.peer_copy(self.base + self.off_stage + q * self.stage_bytes,
+                            self.peers[q] + self.off_partial + lo * self.esize, n * self.esize)
+        c.peer_signal([self._flag(q, 1, r) for q in self.order], s)                       # their partials may be rewritten
+        if n > 0:
+            srcs = [self.base + self.off_partial + lo * self.esize if q == r else self.base + self.off_stage + q * self.stage_bytes
+                    for q in range(self.world)]
+            mine = self.base + self.off_result + lo * self.esize
+            c.sum_shards(self.dtype, mine, srcs, n)
+            for q in self.order:                                                           # all-gather: push the finished shard
+                c.peer_copy(self.peers[q] + self.off_result + lo * self.esize, mine, n * self.esize)
+        c.peer_signal([self._flag(q, 2, r) for q in self.order], s)                       # my shard has been delivered
+        c.peer_wait([self._flag(r, 2, q) for q in self.order], s, self.timeout_ms)        # and so have theirs
+        self.e_done.record(self.side)
+
+    def finish(self):
+        """Main stream waits for the exchange; `result` then holds the sum on every rank."""
+        if self.world > 1:
+            self.torch.cuda.current_stream().wait_event(self.e_done)
+
+    def close(self):
+        if getattr(self, "base", None) is None:
+            return
+        self.torch.cuda.synchronize()
+        if self.world > 1:
+            dist.barrier(group=self.group)  # nobody unmaps or frees while a peer may still copy
+        for q, p in enumerate(self.peers):
+            if q != self.rank and p is not None:
+                self.ctx_main.peer_close(p)
+        if self.world > 1:
+            dist.barrier(group=self.group)
+        self.ctx_main.peer_free(self.base)
+        self.base = None

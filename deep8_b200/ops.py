@@ -238,3 +238,56 @@ class Context:
     def zero(self, t):
         check(self.lib.d8k_zero(self.h, _p(t), t.numel() * t.element_size()))
         return t
+
+    # ------------------------------------------------------------------------------------------------ exchange between GPUs
+    # Raw device addresses (ints): the memory belongs to the library (d8k_peer_alloc) or to a peer process.
+    def peer_alloc(self, nbytes):
+        """(address, handle): zero-filled device memory that peer processes can map; `handle` is 64 bytes to send them."""
+        ptr = ctypes.c_void_p()
+        handle = ctypes.create_string_buffer(_lib.IPC_HANDLE_BYTES)
+        check(self.lib.d8k_peer_alloc(self.h, nbytes, ctypes.byref(ptr), handle))
+        return ptr.value, handle.raw
+
+    def peer_free(self, ptr):
+        check(self.lib.d8k_peer_free(self.h, ctypes.c_void_p(ptr)))
+
+    def peer_open(self, handle):
+        ptr = ctypes.c_void_p()
+        check(self.lib.d8k_peer_open(self.h, ctypes.create_string_buffer(bytes(handle), _lib.IPC_HANDLE_BYTES), ctypes.byref(ptr)))
+        return ptr.value
+
+    def peer_close(self, ptr):
+        check(self.lib.d8k_peer_close(self.h, ctypes.c_void_p(ptr)))
+
+    @staticmethod
+    def _ptr_array(ptrs):
+        return (ctypes.c_void_p * len(ptrs))(*ptrs)
+
+    def peer_signal(self, flags, value):
+        check(self.lib.d8k_peer_signal(self.h, self._ptr_array(flags), len(flags), value & 0xFFFFFFFF))
+
+    def peer_wait(self, flags, value, timeout_ms=2000.0):
+        check(self.lib.d8k_peer_wait(self.h, self._ptr_array(flags), len(flags), value & 0xFFFFFFFF, float(timeout_ms)))
+
+    def peer_copy(self, dst, src, nbytes):
+        check(self.lib.d8k_peer_copy(self.h, ctypes.c_void_p(dst), ctypes.c_void_p(src), nbytes))
+
+    def sum_shards(self, dtype, out, srcs, count):
+        """out[i] = srcs[0][i] + ... + srcs[-1][i] in that order (fp32 accumulation); dtype is a torch dtype."""
+        code = F16 if dtype == torch.float16 else F32 if dtype == torch.float32 else None
+        if code is None:
+            raise TypeError("type %s is not support" % dtype)
+        check(self.lib.d8k_sum_shards(self.h, code, ctypes.c_void_p(out), self._ptr_array(srcs), len(srcs), count))
+
+
+class _RawCuda:
+    """Array-interface shim so that torch can view device memory it did not allocate."""
+
+    def __init__(self, ptr, shape, typestr):
+        self.__cuda_array_interface__ = {"data": (ptr, False), "shape": tuple(shape), "typestr": typestr, "version": 2, "strides": None}
+
+
+def tensor_view(ptr, shape, dtype, device):
+    """A torch tensor over `ptr` (library or peer memory); the caller keeps the memory alive."""
+    typestr = {torch.float16: "<f2", torch.float32: "<f4", torch.int32: "<i4", torch.uint8: "|u1"}[dtype]
+    return torch.as_tensor(_RawCuda(ptr, shape, typestr), device=device)

@@ -145,6 +145,34 @@ D8K_API int d8k_relu_backward(d8k_ctx* ctx, int dtype, const void* x, void* dx, 
 /* Math::Constant with scalar 0 as used by Variable::zeroGradient (deep8/src/nodes/Variable.cpp:119-123). */
 D8K_API int d8k_zero(d8k_ctx* ctx, void* ptr, size_t bytes);
 
+/* ---- Exchange of replicated-operand gradients between the GPUs of one box (one process per GPU).
+ * No counterpart in the reference, whose Executor pins device 0 (deep8/src/model/Executor.cu:6-8).  The gradient of an
+ * operand every sample shares (a batch-1 MatrixMultiply operand, a Conv2d/DeConv2d filter) is a sum over the batch; with
+ * the batch sharded over GPUs each GPU holds a partial sum and the full gradient is their sum.  These entry points are
+ * the pieces of a reduce-scatter + all-gather that uses no SM for the transfers: buffers that peers map (CUDA IPC), copy
+ * engine transfers, a fixed-order sum kernel, and stream-ordered flags between processes.  Everything is enqueued on the
+ * context's stream; a context per stream lets the exchange run beside the contractions. */
+#define D8K_IPC_HANDLE_BYTES 64
+/* Device memory other processes of this box can map: zero-filled; `handle` receives the bytes to send to the peers. */
+D8K_API int d8k_peer_alloc(d8k_ctx* ctx, size_t bytes, void** ptr, unsigned char handle[D8K_IPC_HANDLE_BYTES]);
+D8K_API int d8k_peer_free(d8k_ctx* ctx, void* ptr);
+/* Maps a peer's d8k_peer_alloc memory into this process; *ptr is valid on the context's device until d8k_peer_close. */
+D8K_API int d8k_peer_open(d8k_ctx* ctx, const unsigned char handle[D8K_IPC_HANDLE_BYTES], void** ptr);
+D8K_API int d8k_peer_close(d8k_ctx* ctx, void* ptr);
+/* After all work enqueued so far: *flags[i] = value for i < n (n <= 16), visible to every GPU; flags are 4-byte words in
+ * d8k_peer_alloc memory of this or a peer process. */
+D8K_API int d8k_peer_signal(d8k_ctx* ctx, void* const* flags, int n, unsigned value);
+/* Holds the stream until flags[i] >= value for every i < n (n <= 16; words in this GPU's own memory that peers signal),
+ * for at most timeout_ms; after that the status word is set ((5 << 8) | index of the first flag still behind, see
+ * d8k_ctx_status) and the stream continues, so a peer that never arrives costs a bounded delay, not a hung GPU. */
+D8K_API int d8k_peer_wait(d8k_ctx* ctx, const void* const* flags, int n, unsigned value, double timeout_ms);
+/* Stream-ordered copy between any two device pointers this process can address (own or peer memory): the copy engines
+ * move the bytes. */
+D8K_API int d8k_peer_copy(d8k_ctx* ctx, void* dst, const void* src, size_t bytes);
+/* out[i] = srcs[0][i] + srcs[1][i] + ... + srcs[nsrc-1][i], i < count, added in that order in fp32 and rounded once to
+ * dtype: every GPU that sums the same partials in the same order gets the same bits.  nsrc <= 16; out may be srcs[k]. */
+D8K_API int d8k_sum_shards(d8k_ctx* ctx, int dtype, void* out, const void* const* srcs, int nsrc, size_t count);
+
 #ifdef __cplusplus
 }
 #endif

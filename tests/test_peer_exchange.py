@@ -1,0 +1,210 @@
+"""The gradient exchange over peer memory (include/d8k.h d8k_peer_* / d8k_sum_shards, deep8_b200.dp.PeerAllReduce).
+
+CPU: the shard and rotation plans.  GPU, one device: the fixed-order sum kernel against numpy, flags (a signal that
+arrives, and a wait on a flag nothing sets, which must end by itself with the status word set), copies.  GPU, two
+devices (skipped on a one-GPU box): two processes exchange a gradient and each compares the result with the sum
+computed from both partials on the host.
+"""
+import os
+import socket
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+# ------------------------------------------------------------------------------------------------ CPU: plans
+def test_gradient_shards_partition_and_alignment():
+    from deep8_b200.dp import gradient_shards
+    for numel in (1, 100, 1000, 4096 * 16384, 12345679):
+        for world in (1, 2, 3, 8, 16):
+            spans = gradient_shards(numel, world)
+            assert len(spans) == world and spans[0][0] == 0 and spans[-1][1] == numel
+            assert all(a[1] == b[0] for a, b in zip(spans, spans[1:]))
+            assert all(lo % 128 == 0 or lo == numel for lo, _ in spans)
+            assert all(hi - lo <= spans[0][1] - spans[0][0] for lo, hi in spans)  # slot 0 is the largest: staging size
+
+
+def test_peer_rotation_is_a_permutation_every_round():
+    from deep8_b200.dp import peer_rotation
+    for world in (2, 3, 4, 8):
+        orders = [peer_rotation(world, r) for r in range(world)]
+        for r, o in enumerate(orders):
+            assert sorted(o) == [q for q in range(world) if q != r]
+        for k in range(world - 1):
+            assert sorted(o[k] for o in orders) == list(range(world))  # no GPU is visited twice in one round
+
+
+# ------------------------------------------------------------------------------------------------ GPU: one device
+def _sum_reference(parts, dtype):
+    acc = np.zeros(parts[0].shape, dtype=np.float32)
+    for p in parts:  # same order, fp32 accumulation, one rounding
+        acc = acc + p.astype(np.float32)
+    return acc.astype(dtype)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [torch.float16, torch.float32])
+@pytest.mark.parametrize("nsrc,count", [(1, 1000), (2, 4096 * 33), (3, 77), (8, 1 << 20), (5, 8 * 1024 + 3)])
+def test_sum_shards_matches_ordered_fp32_sum(ctx, dtype, nsrc, count):
+    g = torch.Generator(device="cuda").manual_seed(nsrc * 1000 + count % 997)
+    parts = [(torch.randn(count, device="cuda", generator=g) * (1 + i)).to(dtype) for i in range(nsrc)]
+    out = torch.empty(count, device="cuda", dtype=dtype)
+    ctx.sum_shards(dtype, out.data_ptr(), [p.data_ptr() for p in parts], count)
+    torch.cuda.synchronize()
+    want = _sum_reference([p.cpu().numpy() for p in parts], out.cpu().numpy().dtype)
+    assert np.array_equal(out.cpu().numpy(), want)  # bit-exact: the order and the rounding are part of the contract
+    assert ctx.status() == 0
+
+
+@pytest.mark.gpu
+def test_sum_shards_unaligned_and_in_place(ctx):
+    a = torch.arange(0, 1001, device="cuda", dtype=torch.float32)
+    b = torch.ones(1001, device="cuda", dtype=torch.float32)
+    ctx.sum_shards(torch.float32, a[1:].data_ptr(), [a[1:].data_ptr(), b[1:].data_ptr()], 1000)  # 4-byte aligned only; out is a source
+    torch.cuda.synchronize()
+    assert torch.equal(a[1:], torch.arange(1, 1001, device="cuda", dtype=torch.float32) + 1)
+    assert a[0].item() == 0
+
+
+@pytest.mark.gpu
+def test_signal_wait_copy_on_one_device(ctx):
+    from deep8_b200.ops import tensor_view
+    ptr, handle = ctx.peer_alloc(4096)
+    assert len(handle) == 64
+    try:
+        words = tensor_view(ptr, (1024,), torch.int32, torch.device("cuda", 0))
+        assert int(words.abs().sum().item()) == 0  # zero-filled
+        ctx.peer_signal([ptr, ptr + 4, ptr + 8], 7)
+        ctx.peer_wait([ptr, ptr + 4, ptr + 8], 7, 500.0)
+        ctx.peer_wait([ptr], 5, 500.0)  # a flag already past the value
+        assert ctx.status() == 0
+        assert words[:4].tolist() == [7, 7, 7, 0]
+        src = torch.arange(256, device="cuda", dtype=torch.int32)
+        ctx.peer_copy(ptr + 1024, src.data_ptr(), 1024)
+        torch.cuda.synchronize()
+        assert torch.equal(words[256:512], src)
+    finally:
+        ctx.peer_free(ptr)
+
+
+@pytest.mark.gpu
+def test_wait_on_a_flag_nothing_sets_gives_up_and_reports(ctx):
+    """The failure path without a fault: the wait runs out after its limit, the kernel returns, the status word says
+    which flag was behind, the context keeps working."""
+    import time
+    ptr, _ = ctx.peer_alloc(256)
+    try:
+        ctx.peer_signal([ptr], 1)
+        t0 = time.perf_counter()
+        ctx.peer_wait([ptr, ptr + 4], 1, 30.0)  # flag 1 is never written
+        with pytest.raises(Exception) as info:
+            ctx.status()
+        waited = time.perf_counter() - t0
+        assert "status %d" % ((5 << 8) | 1) in str(info.value)
+        assert 0.02 < waited < 5.0
+        assert ctx.status() == 0  # reading the status cleared it
+        x = torch.ones(64, device="cuda")
+        ctx.sum_shards(torch.float32, x.data_ptr(), [x.data_ptr(), x.data_ptr()], 64)
+        torch.cuda.synchronize()
+        assert x.sum().item() == 128
+    finally:
+        ctx.peer_free(ptr)
+
+
+@pytest.mark.gpu
+def test_exchange_arguments_are_checked(ctx):
+    from deep8_b200 import D8kError
+    with pytest.raises(D8kError):
+        ctx.peer_wait([0], 1, 10.0)
+    ptr, _ = ctx.peer_alloc(256)
+    try:
+        with pytest.raises(D8kError):
+            ctx.peer_wait([ptr], 1, 0.0)
+        with pytest.raises(D8kError):
+            ctx.peer_signal([ptr + 2], 1)
+        with pytest.raises(D8kError):
+            ctx.peer_signal([ptr] * 17, 1)
+        with pytest.raises(TypeError):
+            ctx.sum_shards(torch.int32, ptr, [ptr], 4)
+    finally:
+        ctx.peer_free(ptr)
+
+
+@pytest.mark.gpu
+def test_single_rank_exchange_is_the_identity(ctx):
+    from deep8_b200.dp import PeerAllReduce
+    side = torch.cuda.Stream()
+    ar = PeerAllReduce(ctx, ctx, side, 1000, torch.float16, torch.device("cuda", 0))
+    ar.before_write()
+    ar.partial.copy_(torch.arange(1000, device="cuda").to(torch.float16))
+    ar.start()
+    ar.finish()
+    torch.cuda.synchronize()
+    assert ar.result.data_ptr() == ar.partial.data_ptr()
+    assert ar.result[999].item() == 999
+    ar.close()
+
+
+# ------------------------------------------------------------------------------------------------ GPU: two devices
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    return port
+
+
+def _exchange_worker(rank, world, port, numel, steps, out_dir):
+    sys.path.insert(0, ROOT)
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    import torch.distributed as dist
+    import deep8_b200
+    from deep8_b200.dp import PeerAllReduce
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("gloo", rank=rank, world_size=world)  # host plumbing only: handles and barriers
+    main = torch.cuda.Stream(device=dev)
+    side = torch.cuda.Stream(device=dev)
+    c_main, c_side = deep8_b200.Context(rank, 1 << 20), deep8_b200.Context(rank, 1 << 20)
+    c_main.use_stream(main)
+    c_side.use_stream(side)
+    ar = PeerAllReduce(c_main, c_side, side, numel, torch.float16, dev)
+    ok = True
+    with torch.cuda.stream(main):
+        for s in range(steps):
+            g = torch.Generator(device=dev).manual_seed(100 * s + rank)
+            mine = torch.randn(numel, device=dev, generator=g).to(torch.float16)
+            ar.before_write()
+            ar.partial.copy_(mine)
+            ar.start()
+            ar.finish()
+            got = ar.result.clone()
+            main.synchronize()
+            acc = np.zeros(numel, dtype=np.float32)
+            for q in range(world):  # rebuild every rank's partial from its seed, sum in rank order
+                gq = torch.Generator(device=dev).manual_seed(100 * s + q)
+                acc = acc + torch.randn(numel, device=dev, generator=gq).to(torch.float16).cpu().numpy().astype(np.float32)
+            ok = ok and np.array_equal(got.cpu().numpy(), acc.astype(np.float16))
+    status = (c_main.status(), c_side.status())
+    ar.close()
+    with open(os.path.join(out_dir, "rank%d.txt" % rank), "w") as f:
+        f.write("%d %d %d" % (int(ok), status[0], status[1]))
+    dist.destroy_process_group()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("numel", [1 << 20, 100003])
+def test_two_gpu_exchange_sums_partials_bit_exactly(tmp_path, numel):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    world = 2
+    mp.spawn(_exchange_worker, args=(world, _free_port(), numel, 3, str(tmp_path)), nprocs=world, join=True)
+    for r in range(world):
+        assert open(os.path.join(str(tmp_path), "rank%d.txt" % r)).read() == "1 0 0"
