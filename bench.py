@@ -166,8 +166,10 @@ def run_reference_arm(args):
 def exchange_name(n):
     if n == 1:
         return "single GPU: nothing to exchange"
-    mode = os.environ.get("D8_BENCH_ALLREDUCE", "peer")
-    return {"peer": "peer memory: copy-engine reduce-scatter/all-gather + fixed-order sum kernel on a side stream",
+    mode = os.environ.get("D8_BENCH_ALLREDUCE", "fused")
+    return {"fused": "peer memory: the contraction's epilogue stores each row block in its owner's GPU (reduce-scatter inside the "
+                     "kernel), fixed-order sum kernel, copy-engine all-gather on a side stream",
+            "peer": "peer memory: copy-engine reduce-scatter/all-gather + fixed-order sum kernel on a side stream",
             "end": "NCCL all-reduce after the last contraction"}.get(mode, "NCCL all-reduce started as each gradient completes")
 
 
@@ -183,8 +185,8 @@ class MlpStep:
     """The MLP step on one GPU through the d8k C ABI; buffers allocated once, as an executor would keep them.
     X, dY and Y are double-buffered so that the end-to-end loop can copy step i+1 in and step i-1 out while step i runs."""
 
-    def __init__(self, ctx, torch, device, rank, fused=True, exchange=None):
-        self.ctx, self.torch, self.fused = ctx, torch, fused
+    def __init__(self, ctx, torch, device, rank, fused=True, exchange=None, scatter=False):
+        self.ctx, self.torch, self.fused, self.scatter = ctx, torch, fused, scatter
         self.ar1 = self.ar2 = None
         g = torch.Generator(device=device)
         g.manual_seed(10)
@@ -203,7 +205,7 @@ class MlpStep:
         self.dX, self.dW1, self.dW2 = torch.empty_like(self.X[0]), torch.empty_like(self.W1), torch.empty_like(self.W2)
         if exchange is not None:
             # weight gradients live in memory the peers map; the sums arrive in ar.result
-            self.ar1, self.ar2 = exchange(self.W1.numel()), exchange(self.W2.numel())
+            self.ar1, self.ar2 = exchange(self.W1.numel(), D_IN), exchange(self.W2.numel(), D_HID)
             self.dW1, self.dW2 = self.ar1.partial.view(self.W1.shape), self.ar2.partial.view(self.W2.shape)
         self.gemm_events = []
         self.tail_events = []  # (after the last contraction, after the exchange has been waited for)
@@ -228,7 +230,7 @@ class MlpStep:
     def step(self, dist=None, timed=False, buf=0):
         c = self.ctx
         X, dY, Y = self.X[buf], self.dY[buf], self.Y[buf]
-        overlap = os.environ.get("D8_BENCH_ALLREDUCE", "peer") != "end"
+        overlap = os.environ.get("D8_BENCH_ALLREDUCE", "fused") != "end"
         work = []
         if self.ar1 is not None:
             self.ar2.before_write()
@@ -238,10 +240,16 @@ class MlpStep:
             # still to run behind it: dW2 needs only A and dY, dW1 needs dH, and dX (no exchange) goes last.
             self._gemm(lambda: c.matmul_forward_relu(X, self.W1, self.H, self.A), timed)
             self._gemm(lambda: c.matmul_forward(self.A, self.W2, out=Y), timed)
-            self._gemm(lambda: c.matmul_grad_y(self.A, self.W2, self.dW2, dY, accumulate=False), timed)
+            if self.scatter:  # the contraction's epilogue stores each row block in its owner's memory
+                self._gemm(lambda: self.ar2.scatter_grad_y(self.A, dY), timed)
+            else:
+                self._gemm(lambda: c.matmul_grad_y(self.A, self.W2, self.dW2, dY, accumulate=False), timed)
             self._reduce(2, dist, work, overlap)
             self._gemm(lambda: c.matmul_grad_x_relu(self.A, self.dA, self.W2, dY, self.H, self.dH, False, False), timed)
-            self._gemm(lambda: c.matmul_grad_y(X, self.W1, self.dW1, self.dH, accumulate=False), timed)
+            if self.scatter:
+                self._gemm(lambda: self.ar1.scatter_grad_y(X, self.dH), timed)
+            else:
+                self._gemm(lambda: c.matmul_grad_y(X, self.W1, self.dW1, self.dH, accumulate=False), timed)
             self._reduce(1, dist, work, overlap)
             self._gemm(lambda: c.matmul_grad_x(X, self.dX, self.W1, self.dH, accumulate=False), timed)
         else:
@@ -293,16 +301,17 @@ def run_gpu_arm(args):
     stream = torch.cuda.current_stream()
     ctx.use_stream(stream if stream.cuda_stream != 0 else None)
     exchange = None
-    mode = os.environ.get("D8_BENCH_ALLREDUCE", "peer")
-    if world > 1 and mode == "peer":
+    mode = os.environ.get("D8_BENCH_ALLREDUCE", "fused")
+    if world > 1 and mode in ("peer", "fused"):
         # gradient exchange through peer memory on a side stream (deep8_b200.dp.PeerAllReduce); D8_BENCH_ALLREDUCE=overlap
         # or =end selects NCCL all-reduce instead, started as each gradient completes or after the last contraction
         from deep8_b200.dp import PeerAllReduce
         side = torch.cuda.Stream(device=device)
         ctx_side = deep8_b200.Context(local_rank, scratch_bytes=1 << 20)
         ctx_side.use_stream(side)
-        exchange = lambda numel: PeerAllReduce(ctx, ctx_side, side, numel, torch.float16, device)
-    mlp = MlpStep(ctx, torch, device, rank, fused=not args.unfused, exchange=exchange)
+        exchange = lambda numel, rows: PeerAllReduce(ctx, ctx_side, side, numel, torch.float16, device, rows=rows)
+    mlp = MlpStep(ctx, torch, device, rank, fused=not args.unfused, exchange=exchange,
+                  scatter=exchange is not None and mode == "fused" and not args.unfused)
 
     def barrier():
         if dist is not None:

@@ -52,6 +52,7 @@ SIGNATURES = {
     "d8k_peer_signal": (_i, [_vp, ctypes.POINTER(_vp), _i, ctypes.c_uint]),
     "d8k_peer_wait": (_i, [_vp, ctypes.POINTER(_vp), _i, ctypes.c_uint, ctypes.c_double]),
     "d8k_peer_copy": (_i, [_vp, _vp, _vp, _sz]),
+    "d8k_matmul_grad_y_scatter": (_i, [_vp, _i, _vp, _i, _i, _i, _i, _vp, ctypes.POINTER(_vp), _i, _i]),
     "d8k_sum_shards": (_i, [_vp, _i, _vp, ctypes.POINTER(_vp), _i, _sz]),
 }
 

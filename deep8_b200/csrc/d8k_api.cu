@@ -288,7 +288,8 @@ int d8k_ctx_status(d8k_ctx* ctx, int* status) {
 
 static int gemm_call(d8k_ctx* ctx, int dtype, int transA, int transB, int M, int N, int K, const void* A, long long lda, int batchA,
                      long long strideA, const void* B, long long ldb, int batchB, long long strideB, void* C, long long ldc, long long strideC,
-                     int batch, int beta, int reduce_batch, int epi = 0, void* E1 = nullptr, void* E2 = nullptr, int beta2 = 0) {
+                     int batch, int beta, int reduce_batch, int epi = 0, void* E1 = nullptr, void* E2 = nullptr, int beta2 = 0,
+                     void* const* row_blocks = nullptr, int num_blocks = 0, int block_rows = 0) {
     if (int rc = check_ctx(ctx)) return rc;
     if (int rc = check_dtype(dtype)) return rc;
     if (batchA < 1 || batchB < 1 || batch < 0) return fail(D8K_ERR_ARGUMENT, "d8k_gemm: batch counts must be positive");
@@ -307,6 +308,12 @@ static int gemm_call(d8k_ctx* ctx, int dtype, int transA, int transB, int M, int
     if (reduce_batch && batch == 0) g.K = 0;
     g.beta = beta;
     g.epi = epi; g.E1 = E1; g.E2 = E2; g.beta2 = beta2;
+    if (row_blocks) {
+        if (num_blocks < 1 || num_blocks > kMaxScatter) return fail(D8K_ERR_ARGUMENT, "1 to 16 row blocks");
+        g.scatter_rows = block_rows;
+        g.scatter_count = num_blocks;
+        for (int k = 0; k < num_blocks; ++k) g.scatter_base[k] = row_blocks[k];
+    }
     return run_gemm(ctx, g);
 }
 
@@ -380,6 +387,16 @@ int d8k_matmul_grad_x_into(d8k_ctx* ctx, int dtype, void* dx, int xb, int xr, in
 int d8k_matmul_grad_y_into(d8k_ctx* ctx, int dtype, const void* x, int xb, int xr, int xc, void* dy, int yb, int yc, const void* dz,
                            int accumulate) {
     return matmul_grad_y_impl(ctx, dtype, x, xb, xr, xc, dy, yb, yc, dz, accumulate);
+}
+int d8k_matmul_grad_y_scatter(d8k_ctx* ctx, int dtype, const void* x, int xb, int xr, int xc, int yc, const void* dz, void* const* row_blocks,
+                              int num_blocks, int block_rows) {
+    if (int rc = check_ctx(ctx)) return rc;
+    if (int rc = check_dtype(dtype)) return rc;
+    if (int rc = check_matmul(xb, xr, xc, 1, yc)) return rc;
+    if (!row_blocks) return fail(D8K_ERR_ARGUMENT, "d8k_matmul_grad_y_scatter: null pointer");
+    // the yb == 1 case of matmul_grad_y_impl with the output rows sent to their blocks
+    return gemm_call(ctx, dtype, 1, 0, xc, yc, xb * xr, x, xc, 1, 0, dz, yc, 1, 0, nullptr, yc, 0, 1, 0, 0, 0, nullptr, nullptr, 0, row_blocks,
+                     num_blocks, block_rows);
 }
 int d8k_matmul_forward_relu(d8k_ctx* ctx, int dtype, const void* x, int xb, int xr, int xc, const void* y, int yb, int yc, void* z, void* a) {
     if (!a) return fail(D8K_ERR_ARGUMENT, "d8k_matmul_forward_relu: null pointer");

@@ -308,7 +308,7 @@ d8k_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
         for (int w = pair; ok && w < p.total_work; w += num_pairs) {
             PairWork it = decode_pair_work(p, w);
             const int row = it.m0 + 128 * static_cast<int>(rank) + row_in_tile;
-            const long long crow = static_cast<long long>(it.batch) * p.c_batch_stride + static_cast<long long>(row) * p.ldc;
+            const long long crow = static_cast<long long>(it.batch) * p.c_batch_stride + static_cast<long long>(row) * p.ldc + scatter_offset(p, row);
             const long long tw = p.prof ? clock64() : 0;
             ok = wait_bar(tfull_bar(acc), acc_phase, &s_abort, p.status, (kRoleEpilogue << 8) | 3);
             if (!ok) break;
@@ -316,7 +316,8 @@ d8k_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
             ptx::tc_fence_after_sync();
             const uint32_t taddr = tmem_base + acc * 256 + (static_cast<uint32_t>(quarter * 32) << 16);
             const int warp_row0 = it.m0 + 128 * static_cast<int>(rank) + quarter * 32;  // first row of this warp
-            const long long warp_off = static_cast<long long>(it.batch) * p.c_batch_stride + static_cast<long long>(warp_row0) * p.ldc;
+            const long long warp_off = static_cast<long long>(it.batch) * p.c_batch_stride + static_cast<long long>(warp_row0) * p.ldc +
+                                       scatter_offset(p, warp_row0);
 #pragma unroll 1
             for (int c = 0; c < 256 / 32; ++c) {
                 uint32_t r[32];
@@ -401,6 +402,8 @@ d8k_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
             ptx::mbar_arrive_cluster(acc == 0 ? tempty_leader0 : tempty_leader1);
             if (++acc == 2) { acc = 0; acc_phase ^= 1; }
         }
+        // scattered rows may sit in a peer GPU's memory: order this thread's stores before whatever the host enqueues next
+        if (p.scatter_rows) __threadfence_system();
         if (p.prof && threadIdx.x == 0) {
             p.prof[blockIdx.x * 8 + 5] = clock64() - t_begin;
             p.prof[blockIdx.x * 8 + 6] = waited;

@@ -47,6 +47,10 @@ struct GemmProblem {
     void* E2 = nullptr;
     void* ws = nullptr;  // optional caller scratch for split-K
     size_t ws_bytes = 0;
+    // scatter_rows > 0: C is not used; output rows [k * scatter_rows, (k + 1) * scatter_rows) go to scatter_base[k], a
+    // matrix of scatter_rows rows with pitch ldc (GemmParams::scatter_rows)
+    int scatter_rows = 0, scatter_count = 0;
+    void* scatter_base[kMaxScatter] = {};
 };
 
 // error reporting shared by the API layer

@@ -85,6 +85,8 @@ struct GatherSrc {
     ConvRule cr;
 };
 
+constexpr int kMaxScatter = 16;
+
 struct GemmParams {
     int M, N, K;
     int batch;         // output batches (independent problems)
@@ -105,8 +107,19 @@ struct GemmParams {
     int a_batch_mod, b_batch_mod;  // TMA: batch coordinate = b % mod
     int a_chunked, b_chunked;      // single-CTA TMA kernel: the MN-major operand comes through a 4-D {64, k, chunk, batch} map, one box per stage
     long long* prof;   // optional, normally null: per CTA 8 counters of cycles each role spent waiting (paired kernel only)
+    // Row-block scatter of the output (scatter_rows > 0): rows [k * scatter_rows, (k + 1) * scatter_rows) are stored at
+    // C + scatter_off[k] (elements) instead of at C - each block may live in another allocation, on this GPU or a peer
+    // mapped into this process.  scatter_rows is a multiple of 128, so no epilogue warp straddles two blocks.
+    int scatter_rows;
+    long long scatter_off[kMaxScatter];
     GatherSrc a, b;
 };
+
+__device__ __forceinline__ long long scatter_offset(const GemmParams& p, int row) {
+    if (p.scatter_rows == 0) return 0;
+    int k = row / p.scatter_rows;
+    return p.scatter_off[k < kMaxScatter ? k : kMaxScatter - 1];
+}
 
 template <bool F32_, bool A_MN_, bool B_MN_, int BN_, int STAGES_, bool GATHER_>
 struct GemmCfg {
@@ -652,7 +665,7 @@ d8k_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         for (int w = blockIdx.x; ok && w < p.total_work; w += gridDim.x) {
             WorkItem it = decode_work(p, w, BN);
             const int row = it.m0 + row_in_tile;
-            const long long crow = static_cast<long long>(it.batch) * p.c_batch_stride + static_cast<long long>(row) * p.ldc;
+            const long long crow = static_cast<long long>(it.batch) * p.c_batch_stride + static_cast<long long>(row) * p.ldc + scatter_offset(p, row);
             float* part = p.ws + (static_cast<size_t>(w) * kBM + row_in_tile) * BN;
             if constexpr (Cfg::CHUNK_KB == 0) {
                 ok = wait_bar(tfull_bar(acc), acc_phase, &s_abort, p.status, (kRoleEpilogue << 8) | 3);
@@ -752,6 +765,8 @@ d8k_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                 }
             }
         }
+        // scattered rows may sit in a peer GPU's memory: order this thread's stores before whatever the host enqueues next
+        if (p.scatter_rows) __threadfence_system();
     } else if (Cfg::GATHER && warp >= Cfg::LOADER_WARP0) {
         // ============================================================================ gather loaders
         const int lw = (warp - Cfg::LOADER_WARP0) % Cfg::LOADER_WARPS;

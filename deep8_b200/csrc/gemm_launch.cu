@@ -153,11 +153,19 @@ size_t gemm_scratch_need(const Ctx* ctx, const GemmProblem& g) {
 int run_gemm(Ctx* ctx, const GemmProblem& g) {
     if (g.M < 0 || g.N < 0 || g.K < 0 || g.batch < 0 || g.kbatch < 1) return fail(1, "gemm: negative extent");
     if (g.M == 0 || g.N == 0 || g.batch == 0) return 0;
-    if (!g.C || (g.K > 0 && (!g.a.ptr || !g.b.ptr))) return fail(1, "gemm: null pointer");
+    if ((!g.C && g.scatter_rows == 0) || (g.K > 0 && (!g.a.ptr || !g.b.ptr))) return fail(1, "gemm: null pointer");
     if (g.dtype != 0 && g.dtype != 1) return fail(1, "gemm: dtype must be D8K_F16 or D8K_F32");
     if (g.beta != 0 && g.beta != 1) return fail(1, "gemm: beta must be 0 or 1");
     if (g.epi < 0 || g.epi > 2 || (g.epi >= 1 && !g.E1) || (g.epi == 2 && !g.E2)) return fail(1, "gemm: bad fused epilogue arguments");
     const int esize = g.dtype == 1 ? 4 : 2;
+    if (g.scatter_rows != 0) {
+        if (g.scatter_rows < 0 || g.scatter_rows % 128 != 0) return fail(1, "gemm: scattered row blocks must be multiples of 128 rows");
+        if (g.scatter_count < 1 || g.scatter_count > kMaxScatter || static_cast<long long>(g.scatter_count) * g.scatter_rows < g.M)
+            return fail(1, "gemm: 1 to 16 row blocks that cover every output row");
+        if (g.beta != 0 || g.epi != 0 || g.batch != 1 || g.K == 0) return fail(1, "gemm: a scattered output is overwritten, unbatched, without a fused tail");
+        for (int k = 0; k < g.scatter_count; ++k)
+            if (!g.scatter_base[k] || (reinterpret_cast<uintptr_t>(g.scatter_base[k]) & 15)) return fail(1, "gemm: null or unaligned row block");
+    }
     if (g.K == 0) {  // an empty contraction is a zero matrix
         if (g.beta == 0) {
             for (int b = 0; b < g.batch; ++b) {
@@ -194,6 +202,15 @@ int run_gemm(Ctx* ctx, const GemmProblem& g) {
     p.E1 = g.E1;
     p.E2 = g.E2;
     p.C = g.C;
+    if (g.scatter_rows > 0) {  // offsets are relative to block 0, which stands in for C
+        p.C = g.scatter_base[0];
+        p.scatter_rows = g.scatter_rows;
+        for (int k = 0; k < kMaxScatter; ++k) {
+            const int kk = k < g.scatter_count ? k : g.scatter_count - 1;
+            const long long bytes = static_cast<const char*>(g.scatter_base[kk]) - static_cast<const char*>(g.scatter_base[0]);
+            p.scatter_off[k] = bytes / esize - static_cast<long long>(kk) * g.scatter_rows * g.ldc;
+        }
+    }
     p.ldc = g.ldc;
     p.c_batch_stride = g.c_batch_stride;
     p.ws = scratch;

@@ -46,6 +46,16 @@ def gradient_shards(numel, world, align=128):
     return [(min(k * per, numel), min((k + 1) * per, numel)) for k in range(world)]
 
 
+def row_block_shards(rows, cols, world, align_rows=128):
+    """(block_rows, shards): the gradient as a rows x cols matrix cut into `world` blocks of block_rows rows (a multiple of
+    `align_rows`, which is what the contraction's scattered epilogue needs); shards are the blocks' [lo, hi) element
+    ranges, empty for trailing ranks when there are fewer blocks than ranks."""
+    per = -(-rows // world)
+    block_rows = -(-per // align_rows) * align_rows
+    shards = [(min(k * block_rows, rows) * cols, min((k + 1) * block_rows, rows) * cols) for k in range(world)]
+    return block_rows, shards
+
+
 def peer_rotation(world, rank):
     """Order in which `rank` visits its peers: rank+1, rank+2, ...  At visit k every rank talks to a different peer, so
     the transfers of one round never meet at one GPU."""
@@ -75,7 +85,9 @@ class PeerAllReduce:
 
     FLAG_WORDS = 64  # per kind: one word per peer, padded
 
-    def __init__(self, ctx_main, ctx_side, side_stream, numel, dtype, device, group=None, timeout_ms=2000.0):
+    def __init__(self, ctx_main, ctx_side, side_stream, numel, dtype, device, group=None, timeout_ms=2000.0, rows=None):
+        """rows: the gradient is a rows x (numel / rows) matrix to be cut into row blocks - needed for scatter_grad_y,
+        where the contraction's epilogue stores each block straight into its owner's staging memory."""
         import torch
         from .ops import tensor_view
         self.torch, self.ctx_main, self.ctx_side, self.side = torch, ctx_main, ctx_side, side_stream
@@ -85,10 +97,17 @@ class PeerAllReduce:
         if self.world > 16:
             raise ValueError("at most 16 GPUs exchange through peer memory")
         self.esize = torch.empty((), dtype=dtype).element_size()
-        self.shards = gradient_shards(numel, self.world)
+        self.rows, self.cols, self.block_rows = rows, None, None
+        if rows is None:
+            self.shards = gradient_shards(numel, self.world)
+        else:
+            if numel % rows:
+                raise ValueError("numel is not a multiple of rows")
+            self.cols = numel // rows
+            self.block_rows, self.shards = row_block_shards(rows, self.cols, self.world)
         self.step = 0
         lo, hi = self.shards[self.rank]
-        self.shard_elems = self.shards[0][1] - self.shards[0][0]
+        self.shard_elems = self.shards[0][1] - self.shards[0][0] if rows is None else self.block_rows * self.cols
         grad_bytes = -(-numel * self.esize // 256) * 256
         stage_bytes = -(-self.shard_elems * self.esize // 256) * 256
         # one allocation: partial | result | staging slot per rank | flags (ready, pulled, gathered)
@@ -117,8 +136,26 @@ class PeerAllReduce:
     def _flag(self, owner, kind, writer):
         return self.peers[owner] + self.off_flags + (kind * self.FLAG_WORDS + writer) * 4
 
+    def scatter_grad_y(self, x, dz):
+        """The contraction and the reduce-scatter's transfer in one kernel: dy = x^T * dz (replicated y, x [b, r, rows],
+        dz [b, r, cols]) with every row block stored by the epilogue into its owner's staging slot for this rank, over
+        NVLink where the owner is a peer.  Replaces `contraction writes partial` + the pull phase; call before_write()
+        first and start() after, as usual.  `partial` is not written in this mode."""
+        if self.rows is None:
+            raise ValueError("PeerAllReduce was built without rows")
+        if x.shape[2] != self.rows or dz.shape[2] != self.cols:
+            raise ValueError("the shape is error")
+        nblocks = -(-self.rows // self.block_rows)
+        if self.world == 1:
+            bases = [self.base + self.off_partial]  # one block, nobody to exchange with: the result in place
+        else:
+            bases = [self.peers[k] + self.off_stage + self.rank * self.stage_bytes for k in range(nblocks)]
+        self.ctx_main.matmul_grad_y_scatter(x, self.cols, dz, bases, self.block_rows)
+        self.scattered = True
+
     def before_write(self):
-        """Main stream: hold the next write of `partial` until every peer has pulled its shard of the previous one."""
+        """Main stream: hold the next write of `partial` (or of the peers' staging slots) until every peer has consumed
+        the previous step's data."""
         if self.world > 1 and self.step > 0:
             self.ctx_main.peer_wait([self._flag(self.rank, 1, q) for q in self.order], self.step, self.timeout_ms)
 
@@ -135,16 +172,24 @@ class PeerAllReduce:
         n = hi - lo
         c.peer_signal([self._flag(q, 0, r) for q in self.order], s)                       # my partial is ready
         c.peer_wait([self._flag(r, 0, q) for q in self.order], s, self.timeout_ms)        # so are theirs
+        scattered, self.scattered = getattr(self, "scattered", False), False
+        mine = self.base + self.off_result + lo * self.esize
+        if scattered:
+            # every rank's epilogue has already put its block of partial sums into my staging slots
+            if n > 0:
+                c.sum_shards(self.dtype, mine, [self.base + self.off_stage + q * self.stage_bytes for q in range(self.world)], n)
+            c.peer_signal([self._flag(q, 1, r) for q in self.order], s)                   # my staging slots may be rewritten
+        else:
+            if n > 0:
+                for q in self.order:                                                       # reduce-scatter: pull my shard
+                    c.peer_copy(self.base + self.off_stage + q * self.stage_bytes,
+                                self.peers[q] + self.off_partial + lo * self.esize, n * self.esize)
+            c.peer_signal([self._flag(q, 1, r) for q in self.order], s)                   # their partials may be rewritten
+            if n > 0:
+                srcs = [self.base + self.off_partial + lo * self.esize if q == r else self.base + self.off_stage + q * self.stage_bytes
+                        for q in range(self.world)]
+                c.sum_shards(self.dtype, mine, srcs, n)
         if n > 0:
-            for q in self.order:                                                           # reduce-scatter: pull my shard
-                c.peer_copy(self.base + self.off_stage + q * self.stage_bytes,
-                            self.peers[q] + self.off_partial + lo * self.esize, n * self.esize)
-        c.peer_signal([self._flag(q, 1, r) for q in self.order], s)                       # their partials may be rewritten
-        if n > 0:
-            srcs = [self.base + self.off_partial + lo * self.esize if q == r else self.base + self.off_stage + q * self.stage_bytes
-                    for q in range(self.world)]
-            mine = self.base + self.off_result + lo * self.esize
-            c.sum_shards(self.dtype, mine, srcs, n)
             for q in self.order:                                                           # all-gather: push the finished shard
                 c.peer_copy(self.peers[q] + self.off_result + lo * self.esize, mine, n * self.esize)
         c.peer_signal([self._flag(q, 2, r) for q in self.order], s)                       # my shard has been delivered

@@ -272,6 +272,13 @@ class Context:
     def peer_copy(self, dst, src, nbytes):
         check(self.lib.d8k_peer_copy(self.h, ctypes.c_void_p(dst), ctypes.c_void_p(src), nbytes))
 
+    def matmul_grad_y_scatter(self, x, yc, dz, row_blocks, block_rows):
+        """dy = x^T * dz for a replicated y ([1, xc, yc]), rows [k * block_rows, ...) written to address row_blocks[k]."""
+        dt = _same(x, dz)
+        xb, xr, xc = x.shape
+        check(self.lib.d8k_matmul_grad_y_scatter(self.h, dt, _p(x), xb, xr, xc, yc, _p(dz), self._ptr_array(row_blocks),
+                                                 len(row_blocks), block_rows))
+
     def sum_shards(self, dtype, out, srcs, count):
         """out[i] = srcs[0][i] + ... + srcs[-1][i] in that order (fp32 accumulation); dtype is a torch dtype."""
         code = F16 if dtype == torch.float16 else F32 if dtype == torch.float32 else None

@@ -169,6 +169,15 @@ D8K_API int d8k_peer_wait(d8k_ctx* ctx, const void* const* flags, int n, unsigne
 /* Stream-ordered copy between any two device pointers this process can address (own or peer memory): the copy engines
  * move the bytes. */
 D8K_API int d8k_peer_copy(d8k_ctx* ctx, void* dst, const void* src, size_t bytes);
+/* MatrixMultiplyGradYGPU for a replicated y (yb == 1; MatrixMultiply.cu:508-551 with the batch folded into the
+ * contraction) whose result leaves the kernel already scattered for the sum over GPUs: dy = x^T * dz is not stored as
+ * one matrix; rows [k * block_rows, (k + 1) * block_rows) of it are written (overwritten, not accumulated) to
+ * row_blocks[k], a block_rows x yc matrix that may live in a peer's d8k_peer_alloc memory - the epilogue stores straight
+ * over NVLink, so the reduce-scatter's transfer happens tile by tile while the contraction runs.  block_rows is a
+ * multiple of 128; num_blocks <= 16 blocks cover the xc rows.  The stores are complete, for every GPU, when the kernel
+ * is: signal the peers after it (d8k_peer_signal on the same stream). */
+D8K_API int d8k_matmul_grad_y_scatter(d8k_ctx* ctx, int dtype, const void* x, int xb, int xr, int xc, int yc, const void* dz,
+                                      void* const* row_blocks, int num_blocks, int block_rows);
 /* out[i] = srcs[0][i] + srcs[1][i] + ... + srcs[nsrc-1][i], i < count, added in that order in fp32 and rounded once to
  * dtype: every GPU that sums the same partials in the same order gets the same bits.  nsrc <= 16; out may be srcs[k]. */
 D8K_API int d8k_sum_shards(d8k_ctx* ctx, int dtype, void* out, const void* const* srcs, int nsrc, size_t count);

@@ -149,6 +149,47 @@ def test_single_rank_exchange_is_the_identity(ctx):
     ar.close()
 
 
+@pytest.mark.gpu
+@pytest.mark.parametrize("r,rows,cols", [(256, 512, 384), (1024, 4096, 4096), (64, 200, 72)])
+def test_scattered_grad_y_equals_grad_y(ctx, r, rows, cols):
+    """One GPU: the scattered epilogue with the row blocks laid end to end (or shuffled) gives matmul_grad_y's bits."""
+    g = torch.Generator(device="cuda").manual_seed(rows + cols)
+    x = torch.randn((1, r, rows), device="cuda", generator=g).to(torch.float16)
+    dz = torch.randn((1, r, cols), device="cuda", generator=g).to(torch.float16)
+    want = torch.zeros((1, rows, cols), device="cuda", dtype=torch.float16)
+    ctx.matmul_grad_y(x, want, want, dz, accumulate=False)
+    block = 128
+    n = -(-rows // block)
+    if n > 16:
+        block = -(-rows // 16 // 128) * 128
+        n = -(-rows // block)
+    pool = torch.full((n, block, cols), 7.0, device="cuda", dtype=torch.float16)
+    perm = list(reversed(range(n)))  # block k lands in slot perm[k]
+    ctx.matmul_grad_y_scatter(x, cols, dz, [pool[perm[k]].data_ptr() for k in range(n)], block)
+    torch.cuda.synchronize()
+    assert ctx.status() == 0
+    for k in range(n):
+        lo, hi = k * block, min(rows, (k + 1) * block)
+        assert torch.equal(pool[perm[k]][: hi - lo], want[0, lo:hi])
+        assert bool((pool[perm[k]][hi - lo:] == 7.0).all())  # rows past the matrix are left alone
+
+
+@pytest.mark.gpu
+def test_scattered_grad_y_arguments_are_checked(ctx):
+    from deep8_b200 import D8kError
+    x = torch.zeros((1, 64, 256), device="cuda", dtype=torch.float16)
+    dz = torch.zeros((1, 64, 128), device="cuda", dtype=torch.float16)
+    out = torch.zeros((256, 128), device="cuda", dtype=torch.float16)
+    with pytest.raises(D8kError):
+        ctx.matmul_grad_y_scatter(x, 128, dz, [out.data_ptr()], 100)       # not a multiple of 128
+    with pytest.raises(D8kError):
+        ctx.matmul_grad_y_scatter(x, 128, dz, [out.data_ptr()], 128)       # one block of 128 rows does not cover 256
+    with pytest.raises(D8kError):
+        ctx.matmul_grad_y_scatter(x, 128, dz, [out.data_ptr(), 0], 128)    # null block
+    ctx.matmul_grad_y_scatter(x, 128, dz, [out.data_ptr(), out[128:].data_ptr()], 128)
+    torch.cuda.synchronize()
+
+
 # ------------------------------------------------------------------------------------------------ GPU: two devices
 def _free_port():
     s = socket.socket()
@@ -196,6 +237,67 @@ def _exchange_worker(rank, world, port, numel, steps, out_dir):
     with open(os.path.join(out_dir, "rank%d.txt" % rank), "w") as f:
         f.write("%d %d %d" % (int(ok), status[0], status[1]))
     dist.destroy_process_group()
+
+
+def _fused_worker(rank, world, port, r, rows, cols, steps, out_dir):
+    sys.path.insert(0, ROOT)
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    import torch.distributed as dist
+    import deep8_b200
+    from deep8_b200.dp import PeerAllReduce
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    main = torch.cuda.Stream(device=dev)
+    side = torch.cuda.Stream(device=dev)
+    c_main, c_side = deep8_b200.Context(rank), deep8_b200.Context(rank, 1 << 20)
+    c_main.use_stream(main)
+    c_side.use_stream(side)
+    ar = PeerAllReduce(c_main, c_side, side, rows * cols, torch.float16, dev, rows=rows)
+    ok = True
+
+    def inputs(s, q):
+        g = torch.Generator(device=dev).manual_seed(1000 * s + q)
+        return (torch.randn((1, r, rows), device=dev, generator=g).to(torch.float16),
+                torch.randn((1, r, cols), device=dev, generator=g).to(torch.float16))
+
+    with torch.cuda.stream(main):
+        for s in range(steps):
+            x, dz = inputs(s, rank)
+            ar.before_write()
+            ar.scatter_grad_y(x, dz)
+            ar.start()
+            ar.finish()
+            got = ar.result.clone().view(rows, cols)
+            main.synchronize()
+            acc = np.zeros((rows, cols), dtype=np.float32)
+            part = torch.empty((1, rows, cols), device=dev, dtype=torch.float16)
+            for q in range(world):  # every rank's partial, by the same kernel on the same inputs, summed in rank order
+                xq, dzq = inputs(s, q)
+                c_main.matmul_grad_y(xq, part, part, dzq, accumulate=False)
+                main.synchronize()
+                acc = acc + part[0].cpu().numpy().astype(np.float32)
+            ok = ok and np.array_equal(got.cpu().numpy(), acc.astype(np.float16))
+    status = (c_main.status(), c_side.status())
+    ar.close()
+    with open(os.path.join(out_dir, "rank%d.txt" % rank), "w") as f:
+        f.write("%d %d %d" % (int(ok), status[0], status[1]))
+    dist.destroy_process_group()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("r,rows,cols", [(512, 4096, 4096), (96, 200, 72)])
+def test_two_gpu_fused_scatter_exchange_is_bit_exact(tmp_path, r, rows, cols):
+    """The contraction whose epilogue stores each row block into its owner's memory, then sum + all-gather: equal, bit
+    for bit, to summing the ranks' ordinary matmul_grad_y results in rank order."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    world = 2
+    mp.spawn(_fused_worker, args=(world, _free_port(), r, rows, cols, 3, str(tmp_path)), nprocs=world, join=True)
+    for q in range(world):
+        assert open(os.path.join(str(tmp_path), "rank%d.txt" % q)).read() == "1 0 0"
 
 
 @pytest.mark.gpu
