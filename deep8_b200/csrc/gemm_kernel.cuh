@@ -60,6 +60,7 @@ struct ConvRule {
     int RH, RW, SH, SW, C, FW;
     int mul_y, mul_x, e_y, e_x, off_y, off_x, div_y, div_x;
     FastDiv f_plane, f_rw, f_c, f_fw, f_divy, f_divx;  // RH*RW, RW, C, FW, div_y, div_x
+    int unit_div;                                      // div_y == div_x == 1: no divisibility test
 };
 inline void finish_rule(ConvRule& r) {
     r.f_plane = make_fastdiv(r.RH * r.RW);
@@ -68,6 +69,7 @@ inline void finish_rule(ConvRule& r) {
     r.f_fw = make_fastdiv(r.FW);
     r.f_divy = make_fastdiv(r.div_y);
     r.f_divx = make_fastdiv(r.div_x);
+    r.unit_div = (r.div_y == 1 && r.div_x == 1) ? 1 : 0;
 }
 
 // Where the loader warps find one operand.  Logical view: `rows` x `cols` elements, 128-byte windows of a row are
@@ -82,6 +84,7 @@ struct GatherSrc {
     long long ld, ld2;
     long long batch_stride;
     int batch_count;
+    int vec_ok;  // base, pitches, batch stride (and channel count) keep every chunk 16-byte aligned and inside one tap
     ConvRule cr;
 };
 
@@ -295,42 +298,94 @@ __device__ __forceinline__ uint4 fetch16(const GatherSrc& s, int g, int col, lon
     return *reinterpret_cast<uint4*>(tmp);
 }
 
-// The common case of fetch16 split in two so that the loader can issue all of a k-block's loads back to back:
-// plan16 only computes where the 16 bytes are - kFetchZero (padding or outside the matrix), kFetchSlow (needs the
-// element-wise path of fetch16) or the address of an aligned 16-byte load - and ldg_pred performs the load as ONE
-// predicated instruction.  Loading inside fetch16's branches made the compiler merge each loaded value at a branch
-// join, which serialised the loads: about one global-memory latency per chunk.
-constexpr uintptr_t kFetchZero = 0, kFetchSlow = 1;
-template <typename T, int VEC>
-__device__ __forceinline__ uintptr_t plan16(const GatherSrc& s, int g, int col, long long boff, const ColCtx& k) {
-    if (g >= s.rows || col >= s.cols) return kFetchZero;
-    const T* base = reinterpret_cast<const T*>(s.base);
-    const T* p;
+// ---- the fast path of the loaders.  An address is (row part) + (column part); for a K-major operand a thread keeps its
+// rows for a whole tile and moves along the columns k-block by k-block, for an MN-major operand the other way round, so
+// the part that does not change is worked out once per tile (RowState / ColState below) and a chunk's address costs a
+// few additions.  Decoding pixel and tap for every chunk took about 145 instructions per 16 bytes.
+struct RowState {  // kind 0: lo | hi = element offset of the row, ok = the row exists
+    int lo, hi, ok;  // kind 1: lo = index of pixel (n, 0, 0), hi = py * mul_y, ok = px * mul_x; a missing row has hi far below zero
+};
+struct ColState {  // kind 0: c = the column; kind 1: channel and the tap's part of the pixel numerators
+    int c, ty, tx;
+    int how;       // kChunkZero: outside the matrix; kChunkFast: one aligned 16-byte load; kChunkSlow: element by element
+};
+enum : int { kChunkZero = 0, kChunkFast = 1, kChunkSlow = 2 };
+
+__device__ __forceinline__ RowState row_state(const GatherSrc& s, int g) {
+    RowState r;
     if (s.kind == 0) {
-        p = base + boff + col;
+        long long off;
         if (s.rmod > 0) {
             int q = fdiv(g, s.f_rmod);
-            p += static_cast<long long>(g - q * s.rmod) * s.ld + static_cast<long long>(q) * s.ld2;
+            off = static_cast<long long>(g - q * s.rmod) * s.ld + static_cast<long long>(q) * s.ld2;
         } else {
-            p += static_cast<long long>(g) * s.ld;
+            off = static_cast<long long>(g) * s.ld;
         }
-        if (col + VEC > s.cols) return kFetchSlow;
+        r.lo = static_cast<int>(static_cast<unsigned long long>(off) & 0xffffffffull);
+        r.hi = static_cast<int>(off >> 32);
+        r.ok = g < s.rows;
     } else {
-        if (!k.inside) return kFetchSlow;
-        long long off;
-        if (!locate(s.cr, g, k, off)) return kFetchZero;
-        p = base + off;
+        const ConvRule& cr = s.cr;
+        int n = fdiv(g, cr.f_plane);
+        int rem = g - n * (cr.RH * cr.RW);
+        int py = fdiv(rem, cr.f_rw);
+        int px = rem - py * cr.RW;
+        r.lo = n * (cr.SH * cr.SW);
+        r.hi = g < s.rows ? py * cr.mul_y : -(1 << 30);
+        r.ok = px * cr.mul_x;
     }
-    uintptr_t a = reinterpret_cast<uintptr_t>(p);
-    return (a & 15) ? kFetchSlow : a;
+    return r;
 }
 
+template <int VEC>
+__device__ __forceinline__ ColState col_state(const GatherSrc& s, int col) {
+    ColState k;
+    if (s.kind == 0) {
+        k.c = col;
+        k.ty = k.tx = 0;
+        k.how = col >= s.cols ? kChunkZero : (col + VEC <= s.cols && s.vec_ok) ? kChunkFast : kChunkSlow;
+    } else {
+        ColCtx x = col_ctx<VEC>(s, col);
+        k.c = x.c;
+        k.ty = x.ty;
+        k.tx = x.tx;
+        k.how = col >= s.cols ? kChunkZero : (x.inside && s.vec_ok) ? kChunkFast : kChunkSlow;
+    }
+    return k;
+}
+
+// Address of a kChunkFast chunk, or 0 where the row is missing or the tap falls on padding.  `base` already includes
+// the batch offset.
+template <typename T>
+__device__ __forceinline__ uintptr_t chunk_addr(const GatherSrc& s, const T* base, const RowState& r, const ColState& k) {
+    if (s.kind == 0) {
+        long long off = (static_cast<long long>(r.hi) << 32 | static_cast<unsigned>(r.lo)) + k.c;
+        return r.ok ? reinterpret_cast<uintptr_t>(base + off) : 0;
+    }
+    const ConvRule& cr = s.cr;
+    int ny = r.hi + k.ty, nx = r.ok + k.tx;
+    int sy = ny, sx = nx;
+    bool ok;
+    if (cr.unit_div) {
+        ok = static_cast<unsigned>(ny) < static_cast<unsigned>(cr.SH) && static_cast<unsigned>(nx) < static_cast<unsigned>(cr.SW);
+    } else {
+        ok = (ny | nx) >= 0;
+        sy = fdiv(ny, cr.f_divy);
+        sx = fdiv(nx, cr.f_divx);
+        ok = ok && sy * cr.div_y == ny && sx * cr.div_x == nx && sy < cr.SH && sx < cr.SW;
+    }
+    long long off = static_cast<long long>(r.lo + sy * cr.SW + sx) * cr.C + k.c;
+    return ok ? reinterpret_cast<uintptr_t>(base + off) : 0;
+}
+
+// One predicated 16-byte load.  A load inside an if/else made the compiler merge the loaded value at the join, which
+// serialised the loads of a k-block: about one global-memory latency per chunk.
 __device__ __forceinline__ uint4 ldg_pred(uintptr_t addr) {  // zeros unless addr is a real address
     uint4 v;
     asm volatile(
         "{\n\t"
         ".reg .pred q;\n\t"
-        "setp.gt.u64 q, %4, 1;\n\t"
+        "setp.ne.u64 q, %4, 0;\n\t"
         "mov.b32 %0, 0;\n\t"
         "mov.b32 %1, 0;\n\t"
         "mov.b32 %2, 0;\n\t"
@@ -774,10 +829,39 @@ d8k_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         const int sub = lane >> 3;  // row inside a group of four
         const int j = lane & 7;     // 16-byte chunk of the row
         constexpr int A_ITERS = kBM / 16, B_ITERS = BN / 16;
+        // Chunk i of this thread sits in tile row r_i = 16 i + r0.  K-major: r_i is the operand row, the column is the
+        // k-block's.  MN-major: r_i = (chunk of 128 bytes along M or N) * BK + (k row), so i % NPIX picks one of the
+        // thread's NPIX k rows and i / NPIX the 128-byte chunk.
+        constexpr int NPIX = BK / 16;
+        constexpr int A_NROW = Cfg::A_MN ? NPIX : A_ITERS, A_NCOL = Cfg::A_MN ? A_ITERS / NPIX : 1;
+        constexpr int B_NROW = Cfg::B_MN ? NPIX : B_ITERS, B_NCOL = Cfg::B_MN ? B_ITERS / NPIX : 1;
+        static_assert(A_ITERS % NPIX == 0 && B_ITERS % NPIX == 0, "an MN-major tile is whole 128-byte chunks");
+        const int r0 = lw * 4 + sub;
+        // 16 i + r0 keeps its low three bits, so the swizzled position is that of row r0 plus 2048 i
+        const uint32_t sw_a = swz<Cfg::A_B32>(r0, j), sw_b = swz<Cfg::B_B32>(r0, j);
+        const InT* const base_a0 = reinterpret_cast<const InT*>(p.a.base);
+        const InT* const base_b0 = reinterpret_cast<const InT*>(p.b.base);
         int t = 0;                  // running k-block count of this CTA: k-block t uses stage t % STAGES
         bool ok = true;
         for (int w = blockIdx.x; ok && w < p.total_work; w += gridDim.x) {
             WorkItem it = decode_work(p, w, BN);
+            RowState ra[A_NROW], rb[B_NROW];
+            ColState ca[A_NCOL], cb[B_NCOL];
+            // the half of each address that stays put for the whole tile
+            if constexpr (!Cfg::A_MN) {
+#pragma unroll
+                for (int i = 0; i < A_ITERS; ++i) ra[i] = row_state(p.a, it.m0 + 16 * i + r0);
+            } else {
+#pragma unroll
+                for (int q = 0; q < A_NCOL; ++q) ca[q] = col_state<Cfg::VEC>(p.a, it.m0 + q * CE + j * Cfg::VEC);
+            }
+            if constexpr (!Cfg::B_MN) {
+#pragma unroll
+                for (int i = 0; i < B_ITERS; ++i) rb[i] = row_state(p.b, it.n0 + 16 * i + r0);
+            } else {
+#pragma unroll
+                for (int q = 0; q < B_NCOL; ++q) cb[q] = col_state<Cfg::VEC>(p.b, it.n0 + q * CE + j * Cfg::VEC);
+            }
             for (int kk = it.kb_begin; kk < it.kb_end; ++kk, ++t) {
                 if (t % Cfg::LOADER_GROUPS != group) continue;
                 const int stage = t % STAGES;
@@ -792,52 +876,44 @@ d8k_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                 const int k0 = kb * BK;
                 const long long boff_a = p.a.batch_count > 1 ? static_cast<long long>(b % p.a.batch_count) * p.a.batch_stride : 0;
                 const long long boff_b = p.b.batch_count > 1 ? static_cast<long long>(b % p.b.batch_count) * p.b.batch_stride : 0;
-                // K-major operands: every row of this thread reads the same columns, one column context per k-block
-                ColCtx ka = {}, kbx = {};
-                if (!Cfg::A_MN && p.a.kind == 1) ka = col_ctx<Cfg::VEC>(p.a, k0 + j * Cfg::VEC);
-                if (!Cfg::B_MN && p.b.kind == 1) kbx = col_ctx<Cfg::VEC>(p.b, k0 + j * Cfg::VEC);
+                // the half that moves with the k-block
+                if constexpr (!Cfg::A_MN) {
+                    ca[0] = col_state<Cfg::VEC>(p.a, k0 + j * Cfg::VEC);
+                } else {
+#pragma unroll
+                    for (int h = 0; h < NPIX; ++h) ra[h] = row_state(p.a, k0 + 16 * h + r0);
+                }
+                if constexpr (!Cfg::B_MN) {
+                    cb[0] = col_state<Cfg::VEC>(p.b, k0 + j * Cfg::VEC);
+                } else {
+#pragma unroll
+                    for (int h = 0; h < NPIX; ++h) rb[h] = row_state(p.b, k0 + 16 * h + r0);
+                }
+                const InT* const base_a = base_a0 + (p.a.kind == 0 ? boff_a : 0);
+                const InT* const base_b = base_b0 + (p.b.kind == 0 ? boff_b : 0);
                 uint4 va[A_ITERS], vb[B_ITERS];
-                uintptr_t pa[A_ITERS], pb[B_ITERS];
-                bool any_slow = false;
+                unsigned slow = 0;  // bit i: chunk i of A, bit 16 + i: chunk i of B
 #pragma unroll
                 for (int i = 0; i < A_ITERS; ++i) {
-                    int r = (i * 4 + lw) * 4 + sub;
-                    int g, col;
-                    if constexpr (!Cfg::A_MN) {
-                        g = it.m0 + r;
-                        col = k0 + j * Cfg::VEC;
-                    } else {
-                        g = k0 + (r % BK);
-                        col = it.m0 + (r / BK) * CE + j * Cfg::VEC;
-                        if (p.a.kind == 1) ka = col_ctx<Cfg::VEC>(p.a, col);
-                    }
-                    pa[i] = plan16<InT, Cfg::VEC>(p.a, g, col, boff_a, ka);
-                    any_slow |= pa[i] == kFetchSlow;
+                    const RowState& r = ra[Cfg::A_MN ? i % NPIX : i];
+                    const ColState& k = ca[Cfg::A_MN ? i / NPIX : 0];
+                    uintptr_t addr = chunk_addr<InT>(p.a, base_a, r, k);
+                    if (k.how == kChunkSlow) slow |= 1u << i;
+                    va[i] = ldg_pred(k.how == kChunkFast ? addr : 0);
                 }
 #pragma unroll
                 for (int i = 0; i < B_ITERS; ++i) {
-                    int r = (i * 4 + lw) * 4 + sub;
-                    int g, col;
-                    if constexpr (!Cfg::B_MN) {
-                        g = it.n0 + r;
-                        col = k0 + j * Cfg::VEC;
-                    } else {
-                        g = k0 + (r % BK);
-                        col = it.n0 + (r / BK) * CE + j * Cfg::VEC;
-                        if (p.b.kind == 1) kbx = col_ctx<Cfg::VEC>(p.b, col);
-                    }
-                    pb[i] = plan16<InT, Cfg::VEC>(p.b, g, col, boff_b, kbx);
-                    any_slow |= pb[i] == kFetchSlow;
+                    const RowState& r = rb[Cfg::B_MN ? i % NPIX : i];
+                    const ColState& k = cb[Cfg::B_MN ? i / NPIX : 0];
+                    uintptr_t addr = chunk_addr<InT>(p.b, base_b, r, k);
+                    if (k.how == kChunkSlow) slow |= 1u << (16 + i);
+                    vb[i] = ldg_pred(k.how == kChunkFast ? addr : 0);
                 }
-#pragma unroll
-                for (int i = 0; i < A_ITERS; ++i) va[i] = ldg_pred(pa[i]);
-#pragma unroll
-                for (int i = 0; i < B_ITERS; ++i) vb[i] = ldg_pred(pb[i]);
-                if (any_slow) {  // ragged edges, unaligned rows, chunks that straddle filter taps: element by element
+                if (slow) {  // ragged edges, unaligned rows, chunks that straddle filter taps: element by element
 #pragma unroll
                     for (int i = 0; i < A_ITERS; ++i) {
-                        if (pa[i] != kFetchSlow) continue;
-                        int r = (i * 4 + lw) * 4 + sub;
+                        if (!(slow >> i & 1u)) continue;
+                        int r = 16 * i + r0;
                         int g = Cfg::A_MN ? k0 + (r % BK) : it.m0 + r;
                         int col = Cfg::A_MN ? it.m0 + (r / BK) * CE + j * Cfg::VEC : k0 + j * Cfg::VEC;
                         ColCtx kc = {};
@@ -846,8 +922,8 @@ d8k_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                     }
 #pragma unroll
                     for (int i = 0; i < B_ITERS; ++i) {
-                        if (pb[i] != kFetchSlow) continue;
-                        int r = (i * 4 + lw) * 4 + sub;
+                        if (!(slow >> (16 + i) & 1u)) continue;
+                        int r = 16 * i + r0;
                         int g = Cfg::B_MN ? k0 + (r % BK) : it.n0 + r;
                         int col = Cfg::B_MN ? it.n0 + (r / BK) * CE + j * Cfg::VEC : k0 + j * Cfg::VEC;
                         ColCtx kc = {};
@@ -856,15 +932,9 @@ d8k_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                     }
                 }
 #pragma unroll
-                for (int i = 0; i < A_ITERS; ++i) {
-                    int r = (i * 4 + lw) * 4 + sub;
-                    store_chunk_smem<Cfg::F32>(stage_a(stage) + swz<Cfg::A_B32>(r, j), Cfg::A_BYTES, va[i]);
-                }
+                for (int i = 0; i < A_ITERS; ++i) store_chunk_smem<Cfg::F32>(stage_a(stage) + sw_a + 2048u * i, Cfg::A_BYTES, va[i]);
 #pragma unroll
-                for (int i = 0; i < B_ITERS; ++i) {
-                    int r = (i * 4 + lw) * 4 + sub;
-                    store_chunk_smem<Cfg::F32>(stage_b(stage) + swz<Cfg::B_B32>(r, j), Cfg::B_BYTES, vb[i]);
-                }
+                for (int i = 0; i < B_ITERS; ++i) store_chunk_smem<Cfg::F32>(stage_b(stage) + sw_b + 2048u * i, Cfg::B_BYTES, vb[i]);
                 ptx::fence_proxy_async_smem();
                 ptx::mbar_arrive(full_bar(stage));
             }

@@ -76,7 +76,7 @@ bool make_pair_map(CUtensorMap* map, const HostOperand& o, long long extent, lon
     return r == CUDA_SUCCESS;
 }
 
-GatherSrc to_gather(const HostOperand& o, int rows, int cols) {
+GatherSrc to_gather(const HostOperand& o, int rows, int cols, int esize) {
     GatherSrc s;
     std::memset(&s, 0, sizeof(s));
     s.base = o.ptr;
@@ -90,6 +90,9 @@ GatherSrc to_gather(const HostOperand& o, int rows, int cols) {
     s.batch_stride = o.batch_stride;
     s.batch_count = o.batch_count > 0 ? o.batch_count : 1;
     s.cr = o.cr;
+    const long long vec = 16 / esize;
+    s.vec_ok = (reinterpret_cast<uintptr_t>(o.ptr) & 15) == 0 && o.ld % vec == 0 && o.ld2 % vec == 0 && o.batch_stride % vec == 0 &&
+               (!o.is_virtual || o.cr.C % vec == 0);
     return s;
 }
 
@@ -238,8 +241,8 @@ int run_gemm(Ctx* ctx, const GemmProblem& g) {
         if (!oka || !okb) return fail(2, "gemm: cuTensorMapEncodeTiled failed");
         fn = lookup_f16_tma(g.a.mn, g.b.mn, pl.bn);
     } else {
-        p.a = g.a.mn ? to_gather(g.a, g.K, g.M) : to_gather(g.a, g.M, g.K);
-        p.b = g.b.mn ? to_gather(g.b, g.K, g.N) : to_gather(g.b, g.N, g.K);
+        p.a = g.a.mn ? to_gather(g.a, g.K, g.M, esize) : to_gather(g.a, g.M, g.K, esize);
+        p.b = g.b.mn ? to_gather(g.b, g.K, g.N, esize) : to_gather(g.b, g.N, g.K, esize);
         fn = pl.f32 ? lookup_f32_gather(g.a.mn, g.b.mn, pl.bn) : lookup_f16_gather(g.a.mn, g.b.mn, pl.bn);
     }
     if (!fn) return fail(2, "gemm: no kernel for this configuration");
