@@ -106,11 +106,6 @@ __device__ __forceinline__ void tc_commit_pair(uint32_t bar, uint16_t mask) {
                  : "memory");
 }
 
-__device__ __forceinline__ uint4 ld_shared_v4(uint32_t addr) {
-    uint4 v;
-    asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr) : "memory");
-    return v;
-}
 
 }  // namespace ptx
 

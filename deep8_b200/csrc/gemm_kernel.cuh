@@ -152,12 +152,16 @@ struct GemmCfg {
     static constexpr int PRODUCER_WARP = 4, MMA_WARP = 5, LOADER_WARP0 = 6, LOADER_WARPS = 4;
     // fp32 with 128 columns keeps 128 accumulators per epilogue thread in registers: no room for a second group there
     static constexpr int LOADER_GROUPS = (F32 && BN_ > 64) ? 1 : 2;
-    static constexpr int THREADS = GATHER ? 32 * (LOADER_WARP0 + LOADER_WARPS * LOADER_GROUPS) : 32 * 6;
+    // fp32 without GATHER: TMA brings the operands as stored.  The tensor core reads a raw fp32 word as tf32 by dropping
+    // its low 13 mantissa bits, so the copy TMA made IS the hi image; the same warps that would gather only have to
+    // write the lo image, tf32(v - trunc(v)), beside it - shared memory to shared memory, no global-load latency.
+    static constexpr bool CONVERT = F32 && !GATHER;
+    static constexpr bool HELPERS = GATHER || CONVERT;  // warps beyond the MMA warp exist
+    static constexpr int THREADS = HELPERS ? 32 * (LOADER_WARP0 + LOADER_WARPS * LOADER_GROUPS) : 32 * 6;
     static constexpr int BAR_BYTES = 256;
     static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + BAR_BYTES + 1024;  // + slack to align the ring to 1024
     static_assert(BN % 16 == 0 && BN >= 16 && BN <= 256, "UMMA N");
     static_assert(BN % CE == 0, "an MN-major B tile is whole 128-byte chunks");
-    static_assert(!F32 || GATHER, "the fp32 path needs the loader warps for the hi/lo split");
     static_assert(SMEM_BYTES <= 227 * 1024, "shared memory");
     static_assert(SMEM_BYTES > 114 * 1024, "one CTA per SM: two would compete for tensor memory");
 };
@@ -411,6 +415,18 @@ __device__ __forceinline__ void st_shared_v4(uint32_t addr, uint4 v) {
     asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
 }
 
+// What the tensor core misses when it reads the fp32 word v as tf32 (it drops the low 13 bits): v - trunc(v), exact
+// in fp32, rounded to tf32.
+__device__ __forceinline__ uint4 tf32_low_part(const uint4& v) {
+    uint4 o;
+    const uint32_t* in = &v.x;
+    uint32_t* out = &o.x;
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+        out[i] = __float_as_uint(ptx::to_tf32(__uint_as_float(in[i]) - __uint_as_float(in[i] & 0xffffe000u)));
+    return o;
+}
+
 // Write one fetched chunk: fp16 as is; fp32 as a tf32 hi image and a tf32 lo image `lo_offset` bytes further.
 template <bool F32>
 __device__ __forceinline__ void store_chunk_smem(uint32_t addr, uint32_t lo_offset, uint4 v) {
@@ -570,7 +586,8 @@ d8k_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + a); };
     auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + 2 + a); };
     const uint32_t tmem_slot = bar_base + 8u * (2 * STAGES + 4);
-    static_assert(8 * (2 * Cfg::STAGES + 4) + 8 <= Cfg::BAR_BYTES, "barrier block");
+    auto raw_bar = [&](int s) { return bar_base + 8u * (2 * STAGES + 5 + s); };  // CONVERT: TMA's bytes have landed
+    static_assert(8 * (3 * Cfg::STAGES + 5) <= Cfg::BAR_BYTES, "barrier block");
 
     __shared__ volatile int s_abort;
     __shared__ int s_last;
@@ -581,8 +598,9 @@ d8k_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     if (threadIdx.x == 0) {
         s_abort = 0;
         for (int s = 0; s < STAGES; ++s) {
-            ptx::mbar_init(full_bar(s), Cfg::GATHER ? 32 * Cfg::LOADER_WARPS : 1);
+            ptx::mbar_init(full_bar(s), Cfg::HELPERS ? 32 * Cfg::LOADER_WARPS : 1);
             ptx::mbar_init(empty_bar(s), 1);
+            ptx::mbar_init(raw_bar(s), 1);
         }
         for (int a = 0; a < 2; ++a) {
             ptx::mbar_init(tfull_bar(a), 1);
@@ -624,27 +642,29 @@ d8k_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                         kb = kk - b * p.num_kb;
                     }
                     int k0 = kb * BK;
-                    ptx::mbar_arrive_expect_tx(full_bar(stage), Cfg::STAGE_BYTES);
+                    // CONVERT: the boxes fill the hi halves of the stage and complete on the raw barrier
+                    const uint32_t bar = Cfg::CONVERT ? raw_bar(stage) : full_bar(stage);
+                    ptx::mbar_arrive_expect_tx(bar, Cfg::CONVERT ? Cfg::A_BYTES + Cfg::B_BYTES : Cfg::STAGE_BYTES);
                     if constexpr (!Cfg::A_MN) {
-                        ptx::tma_load_3d(stage_a(stage), &tmA, full_bar(stage), k0, it.m0, b % p.a_batch_mod);
+                        ptx::tma_load_3d(stage_a(stage), &tmA, bar, k0, it.m0, b % p.a_batch_mod);
                     } else {
-                        if (p.a_chunked) {  // one box for all 64-wide chunks of the tile: the TMA unit is bound by box count
-                            ptx::tma_load_4d(stage_a(stage), &tmA, full_bar(stage), 0, k0, it.m0 / CE, b % p.a_batch_mod);
+                        if (p.a_chunked) {  // one box for all 128-byte chunks of the tile: the TMA unit is bound by box count
+                            ptx::tma_load_4d(stage_a(stage), &tmA, bar, 0, k0, it.m0 / CE, b % p.a_batch_mod);
                         } else {
 #pragma unroll
                             for (int c = 0; c < kBM / CE; ++c)
-                                ptx::tma_load_3d(stage_a(stage) + c * BK * 128, &tmA, full_bar(stage), it.m0 + c * CE, k0, b % p.a_batch_mod);
+                                ptx::tma_load_3d(stage_a(stage) + c * BK * 128, &tmA, bar, it.m0 + c * CE, k0, b % p.a_batch_mod);
                         }
                     }
                     if constexpr (!Cfg::B_MN) {
-                        ptx::tma_load_3d(stage_b(stage), &tmB, full_bar(stage), k0, it.n0, b % p.b_batch_mod);
+                        ptx::tma_load_3d(stage_b(stage), &tmB, bar, k0, it.n0, b % p.b_batch_mod);
                     } else {
                         if (p.b_chunked) {
-                            ptx::tma_load_4d(stage_b(stage), &tmB, full_bar(stage), 0, k0, it.n0 / CE, b % p.b_batch_mod);
+                            ptx::tma_load_4d(stage_b(stage), &tmB, bar, 0, k0, it.n0 / CE, b % p.b_batch_mod);
                         } else {
 #pragma unroll
                             for (int c = 0; c < BN / CE; ++c)
-                                ptx::tma_load_3d(stage_b(stage) + c * BK * 128, &tmB, full_bar(stage), it.n0 + c * CE, k0, b % p.b_batch_mod);
+                                ptx::tma_load_3d(stage_b(stage) + c * BK * 128, &tmB, bar, it.n0 + c * CE, k0, b % p.b_batch_mod);
                         }
                     }
                 }
@@ -822,6 +842,37 @@ d8k_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         }
         // scattered rows may sit in a peer GPU's memory: order this thread's stores before whatever the host enqueues next
         if (p.scatter_rows) __threadfence_system();
+    } else if (Cfg::CONVERT && warp >= Cfg::LOADER_WARP0) {
+        // ============================================================================ converters (fp32 behind TMA)
+        // The stage's hi halves hold the operands as TMA wrote them, already in the swizzled layout; the lo image has
+        // the same layout A_BYTES (B_BYTES) further on, so this is a linear pass over 16-byte chunks.
+        const int group = (warp - Cfg::LOADER_WARP0) / Cfg::LOADER_WARPS;
+        const int tid = threadIdx.x - 32 * (Cfg::LOADER_WARP0 + Cfg::LOADER_WARPS * group);  // 0..127 inside the group
+        constexpr int A_CHUNKS = Cfg::A_BYTES / 16 / 128, B_CHUNKS = Cfg::B_BYTES / 16 / 128;
+        int t = 0;
+        bool ok = true;
+        for (int w = blockIdx.x; ok && w < p.total_work; w += gridDim.x) {
+            WorkItem it = decode_work(p, w, BN);
+            for (int kk = it.kb_begin; kk < it.kb_end; ++kk, ++t) {
+                if (t % Cfg::LOADER_GROUPS != group) continue;
+                const int stage = t % STAGES;
+                const uint32_t phase = (t / STAGES) & 1;
+                ok = wait_bar(raw_bar(stage), phase, &s_abort, p.status, (kRoleLoader << 8) | 2);  // every reader observes the phase itself
+                if (!ok) break;
+                uint4 va[A_CHUNKS], vb[B_CHUNKS];
+                const uint32_t a0 = stage_a(stage) + 16u * tid, b0 = stage_b(stage) + 16u * tid;
+#pragma unroll
+                for (int i = 0; i < A_CHUNKS; ++i) va[i] = ptx::ld_shared_v4(a0 + 2048u * i);
+#pragma unroll
+                for (int i = 0; i < B_CHUNKS; ++i) vb[i] = ptx::ld_shared_v4(b0 + 2048u * i);
+#pragma unroll
+                for (int i = 0; i < A_CHUNKS; ++i) st_shared_v4(a0 + 2048u * i + Cfg::A_BYTES, tf32_low_part(va[i]));
+#pragma unroll
+                for (int i = 0; i < B_CHUNKS; ++i) st_shared_v4(b0 + 2048u * i + Cfg::B_BYTES, tf32_low_part(vb[i]));
+                ptx::fence_proxy_async_smem();
+                ptx::mbar_arrive(full_bar(stage));
+            }
+        }
     } else if (Cfg::GATHER && warp >= Cfg::LOADER_WARP0) {
         // ============================================================================ gather loaders
         const int lw = (warp - Cfg::LOADER_WARP0) % Cfg::LOADER_WARPS;

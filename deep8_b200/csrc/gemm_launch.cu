@@ -41,37 +41,43 @@ bool tma_ok(const HostOperand& o, int esize) {
 }
 
 // 3-D map {inner, rows, batch} over a row-major fp16 matrix stack, 128-byte swizzle, zero fill outside.
-bool make_map(CUtensorMap* map, const HostOperand& o, long long inner, long long rows, int box_rows) {
+bool make_map(CUtensorMap* map, const HostOperand& o, long long inner, long long rows, int box_rows, int esize = 2, bool atom32 = false) {
     EncodeTiledFn enc = encode_tiled();
     if (!enc) return false;
     cuuint64_t dims[3] = {static_cast<cuuint64_t>(inner), static_cast<cuuint64_t>(rows), static_cast<cuuint64_t>(o.batch_count)};
     long long bstride = o.batch_count > 1 ? o.batch_stride : rows * o.ld;
-    cuuint64_t strides[2] = {static_cast<cuuint64_t>(o.ld * 2), static_cast<cuuint64_t>(bstride * 2)};
-    cuuint32_t box[3] = {64u, static_cast<cuuint32_t>(box_rows), 1u};
+    cuuint64_t strides[2] = {static_cast<cuuint64_t>(o.ld * esize), static_cast<cuuint64_t>(bstride * esize)};
+    cuuint32_t box[3] = {static_cast<cuuint32_t>(128 / esize), static_cast<cuuint32_t>(box_rows), 1u};
     cuuint32_t estr[3] = {1u, 1u, 1u};
-    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<void*>(o.ptr), dims, strides, box, estr,
-                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+    CUresult r = enc(map, esize == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<void*>(o.ptr), dims,
+                     strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                     atom32 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS;
 }
 
-// 4-D map for the paired kernel, one 32 KB box per operand and stage (two k-blocks of 64).
-//   K-major  (mn == false): {64 k, rows, K / 64, batch},  box {64, 128, 2, 1}   - needs K % 64 == 0
-//   MN-major (mn == true) : {64 m/n, K, extent / 64, batch}, box {64, 128, 2, 1} - needs extent % 64 == 0
+// 4-D map that delivers several 128-byte-wide pieces of an operand as ONE box (the TMA unit is bound by box count).
+// With ce = 128 / esize elements per piece:
+//   K-major  (mn == false): {ce k, rows, K / ce, batch},      box {ce, box_k rows, box_groups k-pieces, 1} - needs K % ce == 0
+//   MN-major (mn == true) : {ce m/n, K, extent / ce, batch},  box {ce, box_k k rows, box_groups chunks, 1} - needs extent % ce == 0
 // The second and third strides are not in increasing order (the 128-byte step comes after the row pitch); TMA only
-// computes addresses from them.
-bool make_pair_map(CUtensorMap* map, const HostOperand& o, long long extent, long long K, int box_k = 128, int box_groups = 2) {
+// computes addresses from them.  atom32: the 128-byte swizzle with 32-byte atoms that MN-major tf32 operands need.
+bool make_pair_map(CUtensorMap* map, const HostOperand& o, long long extent, long long K, int box_k = 128, int box_groups = 2,
+                   int esize = 2, bool atom32 = false) {
     EncodeTiledFn enc = encode_tiled();
     if (!enc) return false;
+    const long long ce = 128 / esize;
     long long rows = o.mn ? K : extent;           // stored rows
-    long long groups = (o.mn ? extent : K) / 64;  // 64-element groups along the stored row
-    cuuint64_t dims[4] = {64u, static_cast<cuuint64_t>(rows), static_cast<cuuint64_t>(groups), static_cast<cuuint64_t>(o.batch_count)};
+    long long groups = (o.mn ? extent : K) / ce;  // 128-byte groups along the stored row
+    cuuint64_t dims[4] = {static_cast<cuuint64_t>(ce), static_cast<cuuint64_t>(rows), static_cast<cuuint64_t>(groups),
+                          static_cast<cuuint64_t>(o.batch_count)};
     long long bstride = o.batch_count > 1 ? o.batch_stride : rows * o.ld;
-    cuuint64_t strides[3] = {static_cast<cuuint64_t>(o.ld * 2), 128u, static_cast<cuuint64_t>(bstride * 2)};
-    cuuint32_t box[4] = {64u, static_cast<cuuint32_t>(box_k), static_cast<cuuint32_t>(box_groups), 1u};  // MN-major: {64, k rows, chunks}
+    cuuint64_t strides[3] = {static_cast<cuuint64_t>(o.ld * esize), 128u, static_cast<cuuint64_t>(bstride * esize)};
+    cuuint32_t box[4] = {static_cast<cuuint32_t>(ce), static_cast<cuuint32_t>(box_k), static_cast<cuuint32_t>(box_groups), 1u};
     cuuint32_t estr[4] = {1u, 1u, 1u, 1u};
-    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, const_cast<void*>(o.ptr), dims, strides, box, estr,
-                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+    CUresult r = enc(map, esize == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, const_cast<void*>(o.ptr), dims,
+                     strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                     atom32 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS;
 }
@@ -106,13 +112,15 @@ Plan make_plan(const Ctx* ctx, const GemmProblem& g, size_t scratch_limit) {
     Plan pl;
     pl.f32 = g.dtype == 1;
     int esize = pl.f32 ? 4 : 2;
-    pl.tma = !pl.f32 && tma_ok(g.a, esize) && tma_ok(g.b, esize) && encode_tiled() != nullptr && !env_int("D8K_FORCE_GATHER", 0);
-    if (pl.tma) pl.bn = g.N > 128 ? 256 : 128;
-    else if (pl.f32) pl.bn = 64;  // the 64-column fp32 kernel runs two loader groups (see GemmCfg::LOADER_GROUPS)
+    pl.tma = tma_ok(g.a, esize) && tma_ok(g.b, esize) && encode_tiled() != nullptr && !env_int("D8K_FORCE_GATHER", 0);
+    // fp32 behind TMA: an MN-major operand arrives as one box of whole 32-element chunks
+    if (pl.f32 && ((g.a.mn && g.M % 32 != 0) || (g.b.mn && g.N % 32 != 0) || !env_int("D8K_F32_TMA", 1))) pl.tma = false;
+    if (pl.f32) pl.bn = 64;  // the 64-column fp32 kernels run two groups of helper warps (see GemmCfg::LOADER_GROUPS)
+    else if (pl.tma) pl.bn = g.N > 128 ? 256 : 128;
     else pl.bn = g.N > 64 ? 128 : 64;
     int forced_bn = env_int("D8K_BN", 0);
     if (forced_bn == 64 && !pl.tma) pl.bn = 64;
-    if (forced_bn == 128) pl.bn = 128;
+    if (forced_bn == 128 && !(pl.f32 && pl.tma)) pl.bn = 128;
     if (forced_bn == 256 && pl.tma) pl.bn = 256;
     pl.bk = 128 / esize;
     pl.tiles_m = (g.M + kBM - 1) / kBM;
@@ -229,6 +237,14 @@ int run_gemm(Ctx* ctx, const GemmProblem& g) {
     if (pl.pair) {
         if (!make_pair_map(&ta, g.a, g.M, g.K) || !make_pair_map(&tb, g.b, g.N, g.K)) return fail(2, "gemm: cuTensorMapEncodeTiled (4-D) failed");
         fn = lookup_f16_pair(g.a.mn, g.b.mn);
+    } else if (pl.tma && pl.f32) {
+        // raw fp32 through TMA, lo images by the converter warps; MN-major operands use the 32-byte-atom swizzle
+        p.a_chunked = g.a.mn;
+        p.b_chunked = g.b.mn;
+        bool oka = g.a.mn ? make_pair_map(&ta, g.a, g.M, g.K, 32, kBM / 32, 4, true) : make_map(&ta, g.a, g.K, g.M, kBM, 4);
+        bool okb = g.b.mn ? make_pair_map(&tb, g.b, g.N, g.K, 32, pl.bn / 32, 4, true) : make_map(&tb, g.b, g.K, g.N, pl.bn, 4);
+        if (!oka || !okb) return fail(2, "gemm: cuTensorMapEncodeTiled (fp32) failed");
+        fn = lookup_f32_tma(g.a.mn, g.b.mn, pl.bn);
     } else if (pl.tma) {
         // K-major: {K, rows}; MN-major: {rows(M or N), K}
         // an MN-major operand whose extent is a multiple of 64 arrives as one 4-D box {64, 64 k-rows, chunks of 64, 1}
