@@ -23,6 +23,7 @@ SIGNATURES = {
     "d8k_ctx_num_sms": (_i, [_vp]),
     "d8k_last_error": (ctypes.c_char_p, []),
     "d8k_launch_count": (ctypes.c_ulonglong, []),
+    "d8k_last_kernel": (ctypes.c_char_p, []),
     "d8k_gemm": (_i, [_vp, _i, _i, _i, _i, _i, _i, _vp, _ll, _i, _ll, _vp, _ll, _i, _ll, _vp, _ll, _ll, _i, _i, _i]),
     "d8k_gemm_static": (_i, [_i, _i, _i, _i, _i, _i, _vp, _ll, _vp, _ll, _vp, _ll, _i, _vp]),
     "d8k_matmul_forward": (_i, [_vp, _i, _vp, _i, _i, _i, _vp, _i, _i, _vp]),

@@ -21,6 +21,8 @@ int fail(int code, const std::string& msg) {
     return code;
 }
 void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
+static thread_local std::string g_last_kernel;
+void set_last_kernel(const std::string& text) { g_last_kernel = text; }
 
 namespace {
 
@@ -64,10 +66,10 @@ int check_conv(const ConvDims& d, int sy, int sx, int dy, int dx) {
     return 0;
 }
 
-ConvRule rule(int RH, int RW, int SH, int SW, int C, int FW, int mul_y, int mul_x, int e_y, int e_x, int off_y, int off_x, int div_y,
+ConvRule rule(int RH, int RW, int SH, int SW, int C, int FH, int FW, int mul_y, int mul_x, int e_y, int e_x, int off_y, int off_x, int div_y,
               int div_x) {
     ConvRule r;
-    r.RH = RH; r.RW = RW; r.SH = SH; r.SW = SW; r.C = C; r.FW = FW;
+    r.RH = RH; r.RW = RW; r.SH = SH; r.SW = SW; r.C = C; r.FW = FW; r.FH = FH;
     r.mul_y = mul_y; r.mul_x = mul_x; r.e_y = e_y; r.e_x = e_x; r.off_y = off_y; r.off_x = off_x; r.div_y = div_y; r.div_x = div_x;
     finish_rule(r);
     return r;
@@ -139,17 +141,17 @@ int conv_like(d8k_ctx* ctx, int which, int dtype, const ConvDims& d, const ConvR
 void conv_rules(const ConvDims& d, int sy, int sx, int dly, int dlx, ConvRule* fwd, ConvRule* bwd) {
     int pt = conv_pad_before(d.ih, d.oh, d.fh, sy, dly), pl = conv_pad_before(d.iw, d.ow, d.fw, sx, dlx);
     // deep8/src/math/Conv2d.cu:44-45: inY = padTop + oy*strideY + fy*dilationY
-    *fwd = rule(d.oh, d.ow, d.ih, d.iw, d.ic, d.fw, sy, sx, dly, dlx, pt, pl, 1, 1);
+    *fwd = rule(d.oh, d.ow, d.ih, d.iw, d.ic, d.fh, d.fw, sy, sx, dly, dlx, pt, pl, 1, 1);
     // deep8/src/math/Conv2d.cu:99-113: oy = (iy - padTop - fy*dilationY) / strideY when divisible and inside
-    *bwd = rule(d.ih, d.iw, d.oh, d.ow, d.oc, d.fw, 1, 1, -dly, -dlx, -pt, -pl, sy, sx);
+    *bwd = rule(d.ih, d.iw, d.oh, d.ow, d.oc, d.fh, d.fw, 1, 1, -dly, -dlx, -pt, -pl, sy, sx);
 }
 
 void deconv_rules(const ConvDims& d, int sy, int sx, ConvRule* fwd, ConvRule* bwd) {
     int pt = deconv_pad_before(d.ih, d.oh, d.fh, sy), pl = deconv_pad_before(d.iw, d.ow, d.fw, sx);
     // deep8/src/math/DeConv2d.cu:41-48: iy = (oy + padTop + fy) / strideY when divisible and inside
-    *fwd = rule(d.oh, d.ow, d.ih, d.iw, d.ic, d.fw, 1, 1, 1, 1, pt, pl, sy, sx);
+    *fwd = rule(d.oh, d.ow, d.ih, d.iw, d.ic, d.fh, d.fw, 1, 1, 1, 1, pt, pl, sy, sx);
     // deep8/src/math/DeConv2d.cu:342-343: oy = iy*strideY - padTop - fy
-    *bwd = rule(d.ih, d.iw, d.oh, d.ow, d.oc, d.fw, sy, sx, -1, -1, -pt, -pl, 1, 1);
+    *bwd = rule(d.ih, d.iw, d.oh, d.ow, d.oc, d.fh, d.fw, sy, sx, -1, -1, -pt, -pl, 1, 1);
 }
 
 // ------------------------------------------------------------------------------------------------ element-wise
@@ -226,6 +228,7 @@ extern "C" {
 
 const char* d8k_last_error(void) { return g_error.c_str(); }
 unsigned long long d8k_launch_count(void) { return g_launches.load(); }
+const char* d8k_last_kernel(void) { return g_last_kernel.c_str(); }
 
 int d8k_ctx_create(int device, size_t scratch_bytes, d8k_ctx** out) {
     if (!out) return fail(D8K_ERR_ARGUMENT, "d8k_ctx_create: null output pointer");

@@ -57,6 +57,7 @@ struct GemmProblem {
 void set_error(const std::string& msg);
 int fail(int code, const std::string& msg);
 void count_launch();
+void set_last_kernel(const std::string& text);
 
 int run_gemm(Ctx* ctx, const GemmProblem& g);
 // scratch bytes run_gemm would use for this problem with its default split choice (0 when it runs unsplit)

@@ -57,11 +57,14 @@ __device__ __forceinline__ int fdiv(int n, const FastDiv& f) {
 // tap = fy * FW + fx.  The source pixel is ((py*mul_y + fy*e_y + off_y) / div_y, likewise x) in an SH x SW image with
 // C channels; the element is zero unless the numerators are >= 0, divisible, and the quotients are inside the image.
 struct ConvRule {
-    int RH, RW, SH, SW, C, FW;
+    int RH, RW, SH, SW, C, FW, FH;
     int mul_y, mul_x, e_y, e_x, off_y, off_x, div_y, div_x;
     FastDiv f_plane, f_rw, f_c, f_fw, f_divy, f_divx;  // RH*RW, RW, C, FW, div_y, div_x
     int unit_div;                                      // div_y == div_x == 1: no divisibility test
+    int low_y, low_x;  // unit_div: source pixel = anchor + tap offset with anchor = (py*mul_y + low_y, ...), tap offset >= 0
 };
+// tap offset along one axis for filter index f of F: the rule's e may be negative (taps walk backwards)
+__host__ __device__ __forceinline__ int tap_offset(int f, int F, int e) { return e >= 0 ? f * e : (F - 1 - f) * (-e); }
 inline void finish_rule(ConvRule& r) {
     r.f_plane = make_fastdiv(r.RH * r.RW);
     r.f_rw = make_fastdiv(r.RW);
@@ -70,6 +73,8 @@ inline void finish_rule(ConvRule& r) {
     r.f_divy = make_fastdiv(r.div_y);
     r.f_divx = make_fastdiv(r.div_x);
     r.unit_div = (r.div_y == 1 && r.div_x == 1) ? 1 : 0;
+    r.low_y = r.off_y + (r.e_y < 0 ? (r.FH - 1) * r.e_y : 0);
+    r.low_x = r.off_x + (r.e_x < 0 ? (r.FW - 1) * r.e_x : 0);
 }
 
 // Where the loader warps find one operand.  Logical view: `rows` x `cols` elements, 128-byte windows of a row are
@@ -89,6 +94,13 @@ struct GatherSrc {
 };
 
 constexpr int kMaxScatter = 16;
+// producer modes per operand (GemmParams::a_tma, b_tma)
+enum : int {
+    kTmaTiled = 0,      // K-major rows or MN-major chunks of a stored matrix (3-D map, or 4-D when *_chunked)
+    kTmaIm2col = 1,     // virtual im2col matrix, K-major: one im2col box of 128 (or BN) pixels x one 128-byte channel slice of one tap
+    kTmaIm2colMN = 2,   // virtual im2col matrix, MN-major: per 128-byte chunk one im2col box of BK pixels
+    kTmaFilterTap = 3,  // filter [oc, taps, ic] as W'[(tap, co)][ci], MN-major: 4-D map {ce ci, oc, taps, ic / ce}
+};
 
 struct GemmParams {
     int M, N, K;
@@ -109,6 +121,7 @@ struct GemmParams {
     int* status;
     int a_batch_mod, b_batch_mod;  // TMA: batch coordinate = b % mod
     int a_chunked, b_chunked;      // single-CTA TMA kernel: the MN-major operand comes through a 4-D {64, k, chunk, batch} map, one box per stage
+    int a_tma, b_tma;              // single-CTA TMA kernels: how the producer fetches the operand (kTma*); a.cr / b.cr describe images
     long long* prof;   // optional, normally null: per CTA 8 counters of cycles each role spent waiting (paired kernel only)
     // Row-block scatter of the output (scatter_rows > 0): rows [k * scatter_rows, (k + 1) * scatter_rows) are stored at
     // C + scatter_off[k] (elements) instead of at C - each block may live in another allocation, on this GPU or a peer
@@ -570,6 +583,61 @@ __device__ __forceinline__ void store_row_chunk(const GemmParams& p, long long o
 }
 
 // ------------------------------------------------------------------------------------------------ the kernel
+// Producer side of one operand for one stage (one elected lane).  ROWS: tile rows of the operand (kBM or BN); mn0: first
+// row (M or N index) of the tile; k0: first contraction index of the k-block.  Every mode delivers ROWS * 128 bytes.
+template <class Cfg, bool MN, int ROWS>
+__device__ __forceinline__ void produce_operand(int mode, int chunked, const GatherSrc& src, const void* map, uint32_t dst, uint32_t bar,
+                                                int k0, int mn0, int batch) {
+    constexpr int BK = Cfg::BK, CE = Cfg::CE;
+    if (mode == kTmaTiled) {
+        if constexpr (!MN) {
+            ptx::tma_load_3d(dst, map, bar, k0, mn0, batch);
+        } else {
+            if (chunked) {  // one box for all 128-byte chunks of the tile: the TMA unit is bound by box count
+                ptx::tma_load_4d(dst, map, bar, 0, k0, mn0 / CE, batch);
+            } else {
+#pragma unroll
+                for (int c = 0; c < ROWS / CE; ++c) ptx::tma_load_3d(dst + c * BK * 128, map, bar, mn0 + c * CE, k0, batch);
+            }
+        }
+        return;
+    }
+    const ConvRule& r = src.cr;
+    if (mode == kTmaFilterTap) {  // k = tap * oc + co: the k-block is BK filters co of one tap
+        int t = fdiv(k0, src.f_rmod);
+        ptx::tma_load_4d(dst, map, bar, 0, k0 - t * src.rmod, t, mn0 / CE);
+        return;
+    }
+    // the im2col modes start from one pixel index: the tile's first row (K-major) or the k-block's first row (MN-major)
+    const int g = mode == kTmaIm2col ? mn0 : k0;
+    const int n = fdiv(g, r.f_plane);
+    const int rem = g - n * (r.RH * r.RW);
+    const int py = fdiv(rem, r.f_rw);
+    const int px = rem - py * r.RW;
+    const int w = px * r.mul_x + r.low_x, h = py * r.mul_y + r.low_y;
+    if (mode == kTmaIm2col) {  // columns k0 .. k0 + BK: channels c0.. of one tap
+        int tap = fdiv(k0, r.f_c);
+        int c0 = k0 - tap * r.C;
+        int fy = fdiv(tap, r.f_fw);
+        int fx = tap - fy * r.FW;
+        ptx::tma_load_im2col_4d(dst, map, bar, c0, w, h, n, tap_offset(fx, r.FW, r.e_x), tap_offset(fy, r.FH, r.e_y));
+    } else {  // kTmaIm2colMN: each 128-byte chunk of columns is a channel slice of one tap
+#pragma unroll
+        for (int c = 0; c < ROWS / CE; ++c) {
+            int col = mn0 + c * CE;
+            int tap = fdiv(col, r.f_c);
+            int c0 = col - tap * r.C;
+            int fy = fdiv(tap, r.f_fw);
+            int fx = tap - fy * r.FW;
+            if (col >= src.cols) {  // past the matrix: a channel coordinate outside the image makes the box all zeros
+                c0 = r.C;
+                fy = fx = 0;
+            }
+            ptx::tma_load_im2col_4d(dst + c * BK * 128, map, bar, c0, w, h, n, tap_offset(fx, r.FW, r.e_x), tap_offset(fy, r.FH, r.e_y));
+        }
+    }
+}
+
 template <class Cfg>
 __global__ void __launch_bounds__(Cfg::THREADS, 1)
 d8k_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmParams p) {
@@ -645,28 +713,8 @@ d8k_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                     // CONVERT: the boxes fill the hi halves of the stage and complete on the raw barrier
                     const uint32_t bar = Cfg::CONVERT ? raw_bar(stage) : full_bar(stage);
                     ptx::mbar_arrive_expect_tx(bar, Cfg::CONVERT ? Cfg::A_BYTES + Cfg::B_BYTES : Cfg::STAGE_BYTES);
-                    if constexpr (!Cfg::A_MN) {
-                        ptx::tma_load_3d(stage_a(stage), &tmA, bar, k0, it.m0, b % p.a_batch_mod);
-                    } else {
-                        if (p.a_chunked) {  // one box for all 128-byte chunks of the tile: the TMA unit is bound by box count
-                            ptx::tma_load_4d(stage_a(stage), &tmA, bar, 0, k0, it.m0 / CE, b % p.a_batch_mod);
-                        } else {
-#pragma unroll
-                            for (int c = 0; c < kBM / CE; ++c)
-                                ptx::tma_load_3d(stage_a(stage) + c * BK * 128, &tmA, bar, it.m0 + c * CE, k0, b % p.a_batch_mod);
-                        }
-                    }
-                    if constexpr (!Cfg::B_MN) {
-                        ptx::tma_load_3d(stage_b(stage), &tmB, bar, k0, it.n0, b % p.b_batch_mod);
-                    } else {
-                        if (p.b_chunked) {
-                            ptx::tma_load_4d(stage_b(stage), &tmB, bar, 0, k0, it.n0 / CE, b % p.b_batch_mod);
-                        } else {
-#pragma unroll
-                            for (int c = 0; c < BN / CE; ++c)
-                                ptx::tma_load_3d(stage_b(stage) + c * BK * 128, &tmB, bar, it.n0 + c * CE, k0, b % p.b_batch_mod);
-                        }
-                    }
+                    produce_operand<Cfg, Cfg::A_MN, kBM>(p.a_tma, p.a_chunked, p.a, &tmA, stage_a(stage), bar, k0, it.m0, b % p.a_batch_mod);
+                    produce_operand<Cfg, Cfg::B_MN, BN>(p.b_tma, p.b_chunked, p.b, &tmB, stage_b(stage), bar, k0, it.n0, b % p.b_batch_mod);
                 }
                 __syncwarp();
                 if (++stage == STAGES) { stage = 0; phase ^= 1; }

@@ -27,6 +27,23 @@ EncodeTiledFn encode_tiled() {
     return fn;
 }
 
+typedef CUresult (*EncodeIm2colFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const int*,
+                                   const int*, cuuint32_t, cuuint32_t, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeIm2colFn encode_im2col() {
+    static EncodeIm2colFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* sym = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeIm2col", &sym, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeIm2colFn>(sym);
+    });
+    return fn;
+}
+
 int env_int(const char* name, int fallback) {
     const char* v = std::getenv(name);
     return v ? std::atoi(v) : fallback;
@@ -82,6 +99,65 @@ bool make_pair_map(CUtensorMap* map, const HostOperand& o, long long extent, lon
     return r == CUDA_SUCCESS;
 }
 
+// How the TMA producer can fetch an operand (kTma*), or -1 when only the loader warps can.  extent: M or N.
+int tma_mode(const HostOperand& o, int esize, long long extent, long long K) {
+    const long long ce = 128 / esize;  // elements per 128-byte row; also the k-block
+    if (reinterpret_cast<uintptr_t>(o.ptr) & 15) return -1;
+    if (!o.is_virtual && o.rmod == 0) return tma_ok(o, esize) ? kTmaTiled : -1;
+    if (!o.is_virtual) {  // filter [oc, taps, ic] read as W'[(tap, co)][ci]: ld = taps * ic, ld2 = ic, rmod = oc
+        if (!o.mn || o.batch_count > 1 || o.ld2 % ce != 0 || o.rmod % ce != 0 || extent != o.ld2 || encode_tiled() == nullptr) return -1;
+        return kTmaFilterTap;
+    }
+    const ConvRule& r = o.cr;
+    if (!r.unit_div || r.C % ce != 0 || r.mul_y > 8 || r.mul_x > 8 || encode_im2col() == nullptr || o.batch_count > 1) return -1;
+    const int up_y = r.low_y + (r.RH - 1) * r.mul_y - (r.SH - 1), up_x = r.low_x + (r.RW - 1) * r.mul_x - (r.SW - 1);
+    auto corner_ok = [](int v) { return v >= -128 && v <= 127; };
+    if (!corner_ok(r.low_y) || !corner_ok(r.low_x) || !corner_ok(up_y) || !corner_ok(up_x)) return -1;
+    const int span_y = (r.FH - 1) * (r.e_y < 0 ? -r.e_y : r.e_y), span_x = (r.FW - 1) * (r.e_x < 0 ? -r.e_x : r.e_x);
+    if (span_y > 255 || span_x > 255) return -1;
+    (void)K;
+    return o.mn ? kTmaIm2colMN : kTmaIm2col;
+}
+
+// im2col map over the NHWC image of a virtual operand: `pixels` anchor pixels per box, one 128-byte channel slice.
+// rows: logical pixel rows of the virtual matrix (images * RH * RW).
+bool make_im2col_map(CUtensorMap* map, const HostOperand& o, long long rows, int pixels, int esize, bool atom32) {
+    EncodeIm2colFn enc = encode_im2col();
+    if (!enc) return false;
+    const ConvRule& r = o.cr;
+    const long long images = rows / (static_cast<long long>(r.RH) * r.RW);
+    cuuint64_t dims[4] = {static_cast<cuuint64_t>(r.C), static_cast<cuuint64_t>(r.SW), static_cast<cuuint64_t>(r.SH),
+                          static_cast<cuuint64_t>(images)};
+    cuuint64_t strides[3] = {static_cast<cuuint64_t>(r.C) * esize, static_cast<cuuint64_t>(r.SW) * r.C * esize,
+                             static_cast<cuuint64_t>(r.SH) * r.SW * r.C * esize};
+    // anchors run over [low, low + (R - 1) * mul] in each axis: the box's far corner, relative to the image's
+    int lower[2] = {r.low_x, r.low_y};
+    int upper[2] = {r.low_x + (r.RW - 1) * r.mul_x - (r.SW - 1), r.low_y + (r.RH - 1) * r.mul_y - (r.SH - 1)};
+    cuuint32_t estr[4] = {1u, static_cast<cuuint32_t>(r.mul_x), static_cast<cuuint32_t>(r.mul_y), 1u};
+    CUresult rc = enc(map, esize == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, const_cast<void*>(o.ptr), dims,
+                      strides, lower, upper, static_cast<cuuint32_t>(128 / esize), static_cast<cuuint32_t>(pixels), estr,
+                      CU_TENSOR_MAP_INTERLEAVE_NONE, atom32 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
+                      CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return rc == CUDA_SUCCESS;
+}
+
+// 4-D map {ce ci, oc, taps, ic / ce} over a filter [oc, taps, ic]: one box = box_k filters of one tap x `chunks` 128-byte
+// slices of input channels, laid out chunk by chunk as an MN-major operand wants.
+bool make_filter_tap_map(CUtensorMap* map, const HostOperand& o, int box_k, int chunks, int esize, bool atom32) {
+    EncodeTiledFn enc = encode_tiled();
+    if (!enc) return false;
+    const long long ce = 128 / esize, ic = o.ld2, taps = o.ld / o.ld2, oc = o.rmod;
+    cuuint64_t dims[4] = {static_cast<cuuint64_t>(ce), static_cast<cuuint64_t>(oc), static_cast<cuuint64_t>(taps), static_cast<cuuint64_t>(ic / ce)};
+    cuuint64_t strides[3] = {static_cast<cuuint64_t>(o.ld) * esize, static_cast<cuuint64_t>(ic) * esize, 128u};
+    cuuint32_t box[4] = {static_cast<cuuint32_t>(ce), static_cast<cuuint32_t>(box_k), 1u, static_cast<cuuint32_t>(chunks)};
+    cuuint32_t estr[4] = {1u, 1u, 1u, 1u};
+    CUresult rc = enc(map, esize == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, const_cast<void*>(o.ptr), dims,
+                      strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                      atom32 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return rc == CUDA_SUCCESS;
+}
+
 GatherSrc to_gather(const HostOperand& o, int rows, int cols, int esize) {
     GatherSrc s;
     std::memset(&s, 0, sizeof(s));
@@ -104,6 +180,7 @@ GatherSrc to_gather(const HostOperand& o, int rows, int cols, int esize) {
 
 struct Plan {
     bool f32, tma, pair;
+    int a_tma, b_tma;  // kTma* of each operand when tma
     int bn, bk, tiles_m, tiles_n, tiles, num_kb, total_kb, splits, kb_per_split;
     size_t scratch;
 };
@@ -112,9 +189,14 @@ Plan make_plan(const Ctx* ctx, const GemmProblem& g, size_t scratch_limit) {
     Plan pl;
     pl.f32 = g.dtype == 1;
     int esize = pl.f32 ? 4 : 2;
-    pl.tma = tma_ok(g.a, esize) && tma_ok(g.b, esize) && encode_tiled() != nullptr && !env_int("D8K_FORCE_GATHER", 0);
-    // fp32 behind TMA: an MN-major operand arrives as one box of whole 32-element chunks
-    if (pl.f32 && ((g.a.mn && g.M % 32 != 0) || (g.b.mn && g.N % 32 != 0) || !env_int("D8K_F32_TMA", 1))) pl.tma = false;
+    pl.a_tma = tma_mode(g.a, esize, g.M, g.K);
+    pl.b_tma = tma_mode(g.b, esize, g.N, g.K);
+    pl.tma = pl.a_tma >= 0 && pl.b_tma >= 0 && encode_tiled() != nullptr && !env_int("D8K_FORCE_GATHER", 0);
+    if ((pl.a_tma > kTmaTiled || pl.b_tma > kTmaTiled) && !env_int("D8K_IM2COL", 1)) pl.tma = false;
+    // fp32 behind TMA: an MN-major stored matrix arrives as one box of whole 32-element chunks
+    if (pl.f32 && ((pl.a_tma == kTmaTiled && g.a.mn && g.M % 32 != 0) || (pl.b_tma == kTmaTiled && g.b.mn && g.N % 32 != 0) ||
+                   !env_int("D8K_F32_TMA", 1)))
+        pl.tma = false;
     if (pl.f32) pl.bn = 64;  // the 64-column fp32 kernels run two groups of helper warps (see GemmCfg::LOADER_GROUPS)
     else if (pl.tma) pl.bn = g.N > 128 ? 256 : 128;
     else pl.bn = g.N > 64 ? 128 : 64;
@@ -144,7 +226,7 @@ Plan make_plan(const Ctx* ctx, const GemmProblem& g, size_t scratch_limit) {
     pl.scratch = pl.splits > 1 ? per_split * pl.splits : 0;
     // CTA pairs on 256 x 256 tiles once the output alone fills the machine (74 pairs) and nothing is split
     int tiles256 = g.batch * ((g.M + 255) / 256) * ((g.N + 255) / 256);
-    pl.pair = pl.tma && pl.bn == 256 && pl.splits == 1 && tiles256 * 2 >= ctx->num_sms && env_int("D8K_PAIR", 1) != 0 &&
+    pl.pair = pl.tma && pl.a_tma == kTmaTiled && pl.b_tma == kTmaTiled && pl.bn == 256 && pl.splits == 1 && tiles256 * 2 >= ctx->num_sms && env_int("D8K_PAIR", 1) != 0 &&
               g.K % 64 == 0 && (!g.a.mn || g.M % 64 == 0) && (!g.b.mn || g.N % 64 == 0);
     if (pl.pair) {
         pl.tiles_m = (g.M + 255) / 256;
@@ -237,25 +319,27 @@ int run_gemm(Ctx* ctx, const GemmProblem& g) {
     if (pl.pair) {
         if (!make_pair_map(&ta, g.a, g.M, g.K) || !make_pair_map(&tb, g.b, g.N, g.K)) return fail(2, "gemm: cuTensorMapEncodeTiled (4-D) failed");
         fn = lookup_f16_pair(g.a.mn, g.b.mn);
-    } else if (pl.tma && pl.f32) {
-        // raw fp32 through TMA, lo images by the converter warps; MN-major operands use the 32-byte-atom swizzle
-        p.a_chunked = g.a.mn;
-        p.b_chunked = g.b.mn;
-        bool oka = g.a.mn ? make_pair_map(&ta, g.a, g.M, g.K, 32, kBM / 32, 4, true) : make_map(&ta, g.a, g.K, g.M, kBM, 4);
-        bool okb = g.b.mn ? make_pair_map(&tb, g.b, g.N, g.K, 32, pl.bn / 32, 4, true) : make_map(&tb, g.b, g.K, g.N, pl.bn, 4);
-        if (!oka || !okb) return fail(2, "gemm: cuTensorMapEncodeTiled (fp32) failed");
-        fn = lookup_f32_tma(g.a.mn, g.b.mn, pl.bn);
     } else if (pl.tma) {
-        // K-major: {K, rows}; MN-major: {rows(M or N), K}
-        // an MN-major operand whose extent is a multiple of 64 arrives as one 4-D box {64, 64 k-rows, chunks of 64, 1}
-        p.a_chunked = g.a.mn && g.M % 64 == 0 && env_int("D8K_CHUNKED", 1);
-        p.b_chunked = g.b.mn && g.N % 64 == 0 && env_int("D8K_CHUNKED", 1);
-        bool oka = p.a_chunked ? make_pair_map(&ta, g.a, g.M, g.K, 64, kBM / 64)
-                               : (g.a.mn ? make_map(&ta, g.a, g.M, g.K, 64) : make_map(&ta, g.a, g.K, g.M, kBM));
-        bool okb = p.b_chunked ? make_pair_map(&tb, g.b, g.N, g.K, 64, pl.bn / 64)
-                               : (g.b.mn ? make_map(&tb, g.b, g.N, g.K, 64) : make_map(&tb, g.b, g.K, g.N, pl.bn));
-        if (!oka || !okb) return fail(2, "gemm: cuTensorMapEncodeTiled failed");
-        fn = lookup_f16_tma(g.a.mn, g.b.mn, pl.bn);
+        // one map per operand, by producer mode; fp32 MN-major operands use the 32-byte-atom swizzle; the raw fp32 tiles
+        // are the hi images and converter warps add the lo images
+        const int ce = 128 / esize;
+        p.a_tma = pl.a_tma;
+        p.b_tma = pl.b_tma;
+        p.a = g.a.mn ? to_gather(g.a, g.K, g.M, esize) : to_gather(g.a, g.M, g.K, esize);
+        p.b = g.b.mn ? to_gather(g.b, g.K, g.N, esize) : to_gather(g.b, g.N, g.K, esize);
+        auto build = [&](CUtensorMap* map, const HostOperand& o, int mode, long long extent, int rows_tile, int* chunked) -> bool {
+            const bool atom32 = pl.f32 && o.mn;
+            if (mode == kTmaIm2col) return make_im2col_map(map, o, extent, rows_tile, esize, atom32);
+            if (mode == kTmaIm2colMN) return make_im2col_map(map, o, g.K, ce, esize, atom32);
+            if (mode == kTmaFilterTap) return make_filter_tap_map(map, o, ce, rows_tile / ce, esize, atom32);
+            if (!o.mn) return make_map(map, o, g.K, extent, rows_tile, esize);
+            *chunked = (pl.f32 || extent % ce == 0) && env_int("D8K_CHUNKED", 1);
+            if (pl.f32 && !*chunked) return false;
+            return *chunked ? make_pair_map(map, o, extent, g.K, ce, rows_tile / ce, esize, atom32) : make_map(map, o, extent, g.K, ce, esize);
+        };
+        if (!build(&ta, g.a, pl.a_tma, g.M, kBM, &p.a_chunked) || !build(&tb, g.b, pl.b_tma, g.N, pl.bn, &p.b_chunked))
+            return fail(2, "gemm: cuTensorMapEncode failed");
+        fn = pl.f32 ? lookup_f32_tma(g.a.mn, g.b.mn, pl.bn) : lookup_f16_tma(g.a.mn, g.b.mn, pl.bn);
     } else {
         p.a = g.a.mn ? to_gather(g.a, g.K, g.M, esize) : to_gather(g.a, g.M, g.K, esize);
         p.b = g.b.mn ? to_gather(g.b, g.K, g.N, esize) : to_gather(g.b, g.N, g.K, esize);
@@ -267,6 +351,14 @@ int run_gemm(Ctx* ctx, const GemmProblem& g) {
     cudaError_t e = fn(grid, ctx->stream, ta, tb, p);
     if (e != cudaSuccess) return fail(2, std::string("gemm: launch failed: ") + cudaGetErrorString(e));
     count_launch();
+    {
+        static const char* const kModes[] = {"tiled", "im2col", "im2col-mn", "filter-tap"};
+        std::ostringstream os;
+        os << (pl.f32 ? "f32 " : "f16 ") << (pl.pair ? "pair" : pl.tma ? "tma" : "gather");
+        if (pl.tma && !pl.pair) os << " a=" << kModes[pl.a_tma] << " b=" << kModes[pl.b_tma];
+        os << " bn=" << (pl.pair ? 256 : pl.bn) << " splits=" << pl.splits << " grid=" << grid;
+        set_last_kernel(os.str());
+    }
     return 0;
 }
 

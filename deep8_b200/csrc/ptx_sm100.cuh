@@ -63,6 +63,17 @@ __device__ __forceinline__ void tma_load_4d(uint32_t dst, const void* tmap, uint
         ::"r"(dst), "l"(tmap), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
         : "memory");
 }
+// im2col load over an NHWC image: `pixels per column` consecutive anchor pixels starting at (w, h, n) - the traversal
+// wraps at the bounding box's right edge to the next row and at its bottom to the next image - each displaced by the
+// filter-tap offset (off_w, off_h); channels [c, c + channels per pixel).  Pixels outside the image read as zeros.
+__device__ __forceinline__ void tma_load_im2col_4d(uint32_t dst, const void* tmap, uint32_t bar, int c, int w, int h, int n, int off_w,
+                                                   int off_h) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.im2col.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2], {%7, %8};"
+        ::"r"(dst), "l"(tmap), "r"(bar), "r"(c), "r"(w), "r"(h), "r"(n), "h"(static_cast<unsigned short>(off_w)),
+        "h"(static_cast<unsigned short>(off_h))
+        : "memory");
+}
 // bring one box of a tensor map into L2 without touching shared memory
 __device__ __forceinline__ void tma_prefetch_l2_3d(const void* tmap, int x, int y, int z) {
     asm volatile("cp.async.bulk.prefetch.tensor.3d.L2.global [%0, {%1, %2, %3}];" ::"l"(tmap), "r"(x), "r"(y), "r"(z) : "memory");

@@ -71,6 +71,10 @@ class Context:
     def launch_count(self):
         return int(self.lib.d8k_launch_count())
 
+    def last_kernel(self):
+        """Text describing the contraction kernel of this thread's last launch (d8k_last_kernel)."""
+        return self.lib.d8k_last_kernel().decode()
+
     # ------------------------------------------------------------------------------------------------ gemm
     def gemm(self, A, B, C, transA=False, transB=False, beta=0, reduce_batch=False):
         """C[b] (+)= op(A[b % batchA]) op(B[b % batchB]); A, B, C are [batch, rows, cols] tensors."""

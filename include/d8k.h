@@ -54,6 +54,9 @@ D8K_API const char* d8k_last_error(void);
 
 /* Number of kernels this library has launched from the calling process since it was loaded. */
 D8K_API unsigned long long d8k_launch_count(void);
+/* Which contraction kernel the calling thread's last launch used, as text: dtype, "pair" / "tma" / "gather", how the TMA
+ * producer fetched each operand, tile width, split count, grid.  For tests and profiles; not a stable format. */
+D8K_API const char* d8k_last_kernel(void);
 
 /* General contraction, row-major:  C[b] (+)= op(A[b % batchA]) * op(B[b % batchB]),  b < batch.
  *   transA == 0: A[b] is M x K with pitch lda;  transA != 0: A[b] is K x M with pitch lda (its transpose is used)
