@@ -50,6 +50,10 @@ CONV_EDGE = [
     ((2, 7, 10, 8), (4, 3, 2, 8), False, (1, 2), (1, 1)),       # non-square everything, not covered
     ((1, 1, 1, 16), (8, 1, 1, 16), True, (1, 1), (1, 1)),       # one pixel, 1x1 filter
     ((3, 11, 11, 20), (70, 3, 3, 20), True, (2, 2), (1, 1)),    # 70 output channels: ragged N
+    # channel counts the TMA im2col producer takes (multiples of 32 / 64), with nothing square or symmetric
+    ((2, 9, 13, 32), (32, 3, 2, 32), False, (1, 2), (2, 1)),
+    ((1, 10, 7, 64), (64, 2, 3, 64), True, (2, 1), (1, 2)),
+    ((3, 6, 5, 64), (96, 3, 3, 64), True, (1, 1), (1, 1)),      # 96 filters: the last tile of N is half empty
 ]
 CONV_CFG3 = ((32, 56, 56, 64), (64, 3, 3, 64), True, (1, 1), (1, 1))
 
@@ -63,6 +67,8 @@ DECONV_EDGE = [
     ((2, 7, 7, 16), (8, 3, 3, 16), False, (2, 2)),
     ((2, 7, 7, 16), (8, 3, 3, 16), True, (1, 1)),
     ((1, 5, 6, 3), (2, 2, 3, 3), False, (2, 1)),
+    ((2, 6, 9, 64), (64, 3, 2, 64), False, (1, 1)),             # stride 1: every contraction goes through TMA im2col
+    ((2, 5, 8, 32), (32, 2, 3, 32), True, (2, 3)),              # unequal strides
 ]
 DECONV_CFG4 = ((16, 14, 14, 256), (128, 4, 4, 256), True, (2, 2))   # output 27x27, what the reference's shape rule yields
 

@@ -354,3 +354,28 @@ def test_cpp_host_interface():
     print(r.stdout)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-2000:]
     assert "0 failed" in r.stdout
+
+
+@pytest.mark.gpu
+def test_conv_contractions_take_the_tma_paths(ctx):
+    """Channel counts that are multiples of 32: the virtual im2col operand arrives through im2col tensor maps and the
+    filter-by-tap operand through its 4-D map, not through the loader warps."""
+    x = torch.zeros((2, 8, 8, 64), device="cuda")
+    w = torch.zeros((64, 3, 3, 64), device="cuda")
+    dz = torch.zeros((2, 8, 8, 64), device="cuda")
+    ctx.conv2d_forward(x, w, True, (1, 1), (1, 1))
+    assert "tma a=im2col b=tiled" in ctx.last_kernel()
+    ctx.conv2d_grad_x(x, torch.zeros_like(x), w, dz, True, (1, 1), (1, 1))
+    assert "tma a=im2col b=filter-tap" in ctx.last_kernel()
+    ctx.conv2d_grad_y(x, w, torch.zeros_like(w), dz, True, (1, 1), (1, 1))
+    assert "tma a=tiled b=im2col-mn" in ctx.last_kernel()
+    ctx.conv2d_forward(x.half(), w.half(), True, (1, 1), (1, 1))
+    assert "f16 tma a=im2col" in ctx.last_kernel()
+    x3 = torch.zeros((1, 9, 9, 3), device="cuda")
+    ctx.conv2d_forward(x3, torch.zeros((5, 3, 3, 3), device="cuda"), True, (1, 1), (1, 1))
+    assert "gather" in ctx.last_kernel()  # 3 channels: no 128-byte channel slices
+    a = torch.zeros((1, 256, 512), device="cuda")
+    ctx.matmul_forward(a, torch.zeros((1, 512, 128), device="cuda"))
+    assert "f32 tma a=tiled b=tiled" in ctx.last_kernel()
+    torch.cuda.synchronize()
+    assert ctx.status() == 0
