@@ -4,6 +4,7 @@
 #include <cstdint>
 #include <cstring>
 #include <string>
+#include <vector>
 
 #include "../../include/d8k.h"
 #include "gemm_host.h"
@@ -103,6 +104,104 @@ HostOperand filter_by_tap(const void* ptr, int oc, int taps, int ic) {
     return o;
 }
 
+// ---- rules with a divisor, one residue class at a time
+// A rule whose source pixel is (py*mul + fy*e + off) / div only touches the image where the numerator is divisible.  For
+// the rows py = r (mod div) that holds for the taps fy = f0 + step*j alone, and there the quotient is
+// py'*mul + off' + j*e' with py = r + div*py': a divisor-free rule over a sub-grid of rows and a sub-grid of taps, which
+// the im2col tensor maps can describe.  The div_y*div_x classes are independent contractions: they write disjoint output
+// pixels (forward, x-gradient) or disjoint filter taps (filter gradient), and none of them multiplies by the zeros that
+// the undivided rule would gather (3/4 of the taps at stride 2).
+struct AxisClass {
+    int rows, f0, step, nf, e2, off2;
+};
+int gcd_int(int a, int b) {
+    while (b) {
+        int t = a % b;
+        a = b;
+        b = t;
+    }
+    return a < 0 ? -a : a;
+}
+AxisClass axis_class(int R, int F, int mul, int e, int off, int div, int r) {
+    AxisClass c = {};
+    c.rows = r < R ? (R - r + div - 1) / div : 0;
+    c.step = div / gcd_int(e, div);
+    c.f0 = -1;
+    for (int f = 0; f < c.step; ++f)
+        if ((((r * mul + off + f * e) % div) + div) % div == 0) {
+            c.f0 = f;
+            break;
+        }
+    if (c.f0 < 0 || c.f0 >= F) return c;  // nf == 0: these rows see no tap
+    c.nf = (F - c.f0 + c.step - 1) / c.step;
+    c.e2 = e * c.step / div;
+    c.off2 = (r * mul + off + c.f0 * e) / div;
+    return c;
+}
+
+// Runs contraction `which` of a convolution-like operator as one launch per residue class of `R` (the rule that has the
+// divisor).  *done stays false - and nothing is launched - unless every class can go through the TMA producer; the
+// caller then runs the undivided rule on the loader warps.
+int conv_by_residue_class(d8k_ctx* ctx, int which, const GemmProblem& whole, const ConvDims& d, const ConvRule& R, const void* x,
+                          const void* y, const void* dz, bool* done) {
+    *done = false;
+    const int taps = d.fh * d.fw;
+    std::vector<GemmProblem> parts;
+    bool uncovered = false;  // some output rows receive no tap at all
+    for (int ry = 0; ry < R.div_y; ++ry) {
+        for (int rx = 0; rx < R.div_x; ++rx) {
+            AxisClass cy = axis_class(R.RH, R.FH, R.mul_y, R.e_y, R.off_y, R.div_y, ry);
+            AxisClass cx = axis_class(R.RW, R.FW, R.mul_x, R.e_x, R.off_x, R.div_x, rx);
+            if (cy.rows == 0 || cx.rows == 0) continue;
+            if (cy.nf == 0 || cx.nf == 0) {
+                uncovered = true;
+                continue;
+            }
+            ConvRule sub = rule(cy.rows, cx.rows, R.SH, R.SW, R.C, cy.nf, cx.nf, R.mul_y, R.mul_x, cy.e2, cx.e2, cy.off2, cx.off2, 1, 1);
+            GemmProblem g = whole;
+            HostOperand::TapSubset t;
+            t.on = 1; t.f0y = cy.f0; t.f0x = cx.f0; t.ty = cy.step; t.tx = cx.step; t.nfy = cy.nf; t.nfx = cx.nf;
+            t.FH = d.fh; t.FW = d.fw; t.ic = d.ic; t.oc = d.oc;
+            const int pixels = d.batch * cy.rows * cx.rows;
+            if (which == 0) {
+                g.M = pixels; g.N = d.oc; g.K = cy.nf * cx.nf * d.ic;
+                g.a = virt(x, false, sub);
+                g.b = plain(y, false, 1LL * taps * d.ic);
+                g.b.sub = t;
+            } else if (which == 1) {
+                g.M = pixels; g.N = d.ic; g.K = cy.nf * cx.nf * d.oc;
+                g.a = virt(dz, false, sub);
+                g.b = filter_by_tap(y, d.oc, taps, d.ic);
+                g.b.sub = t;
+            } else {
+                // the class's pixels of dz: an im2col walk with one tap, stride div, starting at (ry, rx)
+                ConvRule pick = rule(cy.rows, cx.rows, R.RH, R.RW, d.oc, 1, 1, R.div_y, R.div_x, 1, 1, ry, rx, 1, 1);
+                g.M = d.oc; g.N = cy.nf * cx.nf * d.ic; g.K = pixels;
+                g.a = virt(dz, true, pick);
+                g.b = virt(x, true, sub);
+                g.out.cols_on = 1;
+                g.out.C = d.ic; g.out.NFX = cx.nf; g.out.FW = d.fw;
+                g.out.f0y = cy.f0; g.out.f0x = cx.f0; g.out.ty = cy.step; g.out.tx = cx.step;
+            }
+            if (which != 2) {
+                g.out.rows_on = 1;
+                g.out.RH = cy.rows; g.out.RW = cx.rows; g.out.OH = R.RH; g.out.OW = R.RW;
+                g.out.sy = R.div_y; g.out.sx = R.div_x; g.out.ry = ry; g.out.rx = rx;
+            }
+            if (!gemm_goes_through_tma(ctx, g)) return 0;
+            parts.push_back(g);
+        }
+    }
+    if (which == 0 && uncovered) {  // forward overwrites: rows that no tap reaches are zeros
+        size_t bytes = static_cast<size_t>(d.batch) * d.oh * d.ow * d.oc * (whole.dtype == D8K_F32 ? 4 : 2);
+        if (cudaMemsetAsync(whole.C, 0, bytes, ctx->stream) != cudaSuccess) return fail(D8K_ERR_CUDA, "cudaMemsetAsync failed");
+    }
+    *done = true;
+    for (const GemmProblem& g : parts)
+        if (int rc = run_gemm(ctx, g)) return rc;
+    return 0;
+}
+
 // The three contractions of a convolution-like operator over virtual im2col matrices.
 //   forward : z[Mout x oc]      = V(x)[Mout x T*ic] * y^T
 //   grad x  : dx[Min x ic]     += V'(dz)[Min x T*oc] * W'
@@ -134,6 +233,12 @@ int conv_like(d8k_ctx* ctx, int which, int dtype, const ConvDims& d, const ConvR
     if (plan_only) {
         *need = gemm_scratch_need(ctx, g);
         return 0;
+    }
+    const ConvRule& divided = which == 1 ? bwd : fwd;
+    if (!divided.unit_div) {
+        bool done = false;
+        int rc = conv_by_residue_class(ctx, which, g, d, divided, x, y, dz, &done);
+        if (done || rc != 0) return rc;
     }
     return run_gemm(ctx, g);
 }

@@ -31,6 +31,12 @@ struct HostOperand {
     long long batch_stride = 0;
     int batch_count = 1;
     ConvRule cr = {};
+    // A filter [oc, FH, FW, ic] restricted to the taps (f0y + ty*j, f0x + tx*i), j < nfy, i < nfx - one residue class of a
+    // strided convolution.  With rmod == 0 the operand is K-major rows of filters, columns (j, i, c); with rmod > 0 it is
+    // the filter read by tap, W'[((j, i), co)][ci].  TMA only.
+    struct TapSubset {
+        int on = 0, f0y = 0, f0x = 0, ty = 1, tx = 1, nfy = 0, nfx = 0, FH = 0, FW = 0, ic = 0, oc = 0;
+    } sub;
 };
 
 struct GemmProblem {
@@ -51,6 +57,7 @@ struct GemmProblem {
     // matrix of scatter_rows rows with pitch ldc (GemmParams::scatter_rows)
     int scatter_rows = 0, scatter_count = 0;
     void* scatter_base[kMaxScatter] = {};
+    OutMap out = {};  // strided placement of rows / columns in the output tensor (GemmParams::out); FastDivs filled by run_gemm
 };
 
 // error reporting shared by the API layer
@@ -62,6 +69,8 @@ void set_last_kernel(const std::string& text);
 int run_gemm(Ctx* ctx, const GemmProblem& g);
 // scratch bytes run_gemm would use for this problem with its default split choice (0 when it runs unsplit)
 size_t gemm_scratch_need(const Ctx* ctx, const GemmProblem& g);
+// true when run_gemm would fetch both operands with the TMA producer (no loader warps)
+bool gemm_goes_through_tma(const Ctx* ctx, const GemmProblem& g);
 
 typedef cudaError_t (*GemmLaunchFn)(int grid, cudaStream_t stream, const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p);
 // one table per translation unit of instantiations; index [a_mn][b_mn][bn slot]

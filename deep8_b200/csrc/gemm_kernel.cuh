@@ -100,6 +100,18 @@ enum : int {
     kTmaIm2col = 1,     // virtual im2col matrix, K-major: one im2col box of 128 (or BN) pixels x one 128-byte channel slice of one tap
     kTmaIm2colMN = 2,   // virtual im2col matrix, MN-major: per 128-byte chunk one im2col box of BK pixels
     kTmaFilterTap = 3,  // filter [oc, taps, ic] as W'[(tap, co)][ci], MN-major: 4-D map {ce ci, oc, taps, ic / ce}
+    kTmaFilterSub = 4,     // filter [oc, FH, FW, ic] restricted to a grid of taps, K-major: 4-D map {ic, taps x, taps y, oc}
+    kTmaFilterTapSub = 5,  // the same subset read as W'[(tap, co)][ci], MN-major: 5-D map {ce ci, oc, taps x, taps y, ic / ce}
+};
+
+// Where the result goes when it is a strided part of a larger tensor (one residue class of a strided convolution).
+struct OutMap {
+    int rows_on;  // row m = pixel (n, py, px) of an RH x RW sub-grid; it is stored at pixel (n, ry + sy*py, rx + sx*px) of an OH x OW image
+    int RH, RW, OH, OW, sy, sx, ry, rx;
+    FastDiv f_plane, f_rw;  // RH * RW, RW
+    int cols_on;  // column = (j, i, c) over a sub-grid of taps; it is stored at ((f0y + ty*j) * FW + f0x + tx*i) * C + c
+    int C, NFX, FW, f0y, f0x, ty, tx;
+    FastDiv f_c, f_nfx;     // C, NFX
 };
 
 struct GemmParams {
@@ -128,8 +140,30 @@ struct GemmParams {
     // mapped into this process.  scatter_rows is a multiple of 128, so no epilogue warp straddles two blocks.
     int scatter_rows;
     long long scatter_off[kMaxScatter];
+    OutMap out;
     GatherSrc a, b;
 };
+
+// element offset of output row `row` (without the batch term)
+__device__ __forceinline__ long long out_row_offset(const GemmParams& p, int row) {
+    if (!p.out.rows_on) return static_cast<long long>(row) * p.ldc;
+    const OutMap& o = p.out;
+    int n = fdiv(row, o.f_plane);
+    int rem = row - n * (o.RH * o.RW);
+    int py = fdiv(rem, o.f_rw);
+    int px = rem - py * o.RW;
+    return ((static_cast<long long>(n) * o.OH + o.ry + o.sy * py) * o.OW + o.rx + o.sx * px) * p.ldc;
+}
+// stored column of logical column `col` (a multiple of 32; C is a multiple of 32 when the map is on, so 32 columns stay together)
+__device__ __forceinline__ int out_col(const GemmParams& p, int col) {
+    if (!p.out.cols_on) return col;
+    const OutMap& o = p.out;
+    int tap = fdiv(col, o.f_c);
+    int c = col - tap * o.C;
+    int j = fdiv(tap, o.f_nfx);
+    int i = tap - j * o.NFX;
+    return ((o.f0y + o.ty * j) * o.FW + o.f0x + o.tx * i) * o.C + c;
+}
 
 __device__ __forceinline__ long long scatter_offset(const GemmParams& p, int row) {
     if (p.scatter_rows == 0) return 0;
@@ -515,9 +549,10 @@ template <typename OutT, int EPI>
 __device__ __forceinline__ void store_row_chunk_epi(const GemmParams& p, long long off, int col0, const float* acc) {
     using V = EpiVec<OutT>;
     constexpr int VEC = V::N;
-    OutT* dst = reinterpret_cast<OutT*>(p.C) + off + col0;
-    OutT* e1 = reinterpret_cast<OutT*>(p.E1) + off + col0;
-    OutT* e2 = reinterpret_cast<OutT*>(p.E2) + off + col0;
+    const int colm = out_col(p, col0);
+    OutT* dst = reinterpret_cast<OutT*>(p.C) + off + colm;
+    OutT* e1 = reinterpret_cast<OutT*>(p.E1) + off + colm;
+    OutT* e2 = reinterpret_cast<OutT*>(p.E2) + off + colm;
     bool vec_ok = (col0 + 32 <= p.N) && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0);
     if (EPI >= 1) vec_ok = vec_ok && ((reinterpret_cast<uintptr_t>(e1) & 15) == 0);
     if (EPI == 2) vec_ok = vec_ok && ((reinterpret_cast<uintptr_t>(e2) & 15) == 0);
@@ -606,6 +641,18 @@ __device__ __forceinline__ void produce_operand(int mode, int chunked, const Gat
     if (mode == kTmaFilterTap) {  // k = tap * oc + co: the k-block is BK filters co of one tap
         int t = fdiv(k0, src.f_rmod);
         ptx::tma_load_4d(dst, map, bar, 0, k0 - t * src.rmod, t, mn0 / CE);
+        return;
+    }
+    if (mode == kTmaFilterSub) {  // k = (j * NFX + i) * C + c over the tap sub-grid; rows = filters
+        int tap = fdiv(k0, r.f_c);
+        int j = fdiv(tap, r.f_fw);
+        ptx::tma_load_4d(dst, map, bar, k0 - tap * r.C, tap - j * r.FW, j, mn0);
+        return;
+    }
+    if (mode == kTmaFilterTapSub) {  // k = (j * NFX + i) * oc + co
+        int tap = fdiv(k0, src.f_rmod);
+        int j = fdiv(tap, r.f_fw);
+        ptx::tma_load_5d(dst, map, bar, 0, k0 - tap * src.rmod, tap - j * r.FW, j, mn0 / CE);
         return;
     }
     // the im2col modes start from one pixel index: the tile's first row (K-major) or the k-block's first row (MN-major)
@@ -788,7 +835,7 @@ d8k_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         for (int w = blockIdx.x; ok && w < p.total_work; w += gridDim.x) {
             WorkItem it = decode_work(p, w, BN);
             const int row = it.m0 + row_in_tile;
-            const long long crow = static_cast<long long>(it.batch) * p.c_batch_stride + static_cast<long long>(row) * p.ldc + scatter_offset(p, row);
+            const long long crow = static_cast<long long>(it.batch) * p.c_batch_stride + out_row_offset(p, row) + scatter_offset(p, row);
             float* part = p.ws + (static_cast<size_t>(w) * kBM + row_in_tile) * BN;
             if constexpr (Cfg::CHUNK_KB == 0) {
                 ok = wait_bar(tfull_bar(acc), acc_phase, &s_abort, p.status, (kRoleEpilogue << 8) | 3);

@@ -103,6 +103,11 @@ bool make_pair_map(CUtensorMap* map, const HostOperand& o, long long extent, lon
 int tma_mode(const HostOperand& o, int esize, long long extent, long long K) {
     const long long ce = 128 / esize;  // elements per 128-byte row; also the k-block
     if (reinterpret_cast<uintptr_t>(o.ptr) & 15) return -1;
+    if (o.sub.on) {  // a grid of taps of a filter [oc, FH, FW, ic]
+        if (o.is_virtual || o.batch_count > 1 || o.sub.ic % ce != 0 || encode_tiled() == nullptr) return -1;
+        if (o.rmod == 0) return o.mn ? -1 : kTmaFilterSub;
+        return (o.mn && o.sub.oc % ce == 0) ? kTmaFilterTapSub : -1;
+    }
     if (!o.is_virtual && o.rmod == 0) return tma_ok(o, esize) ? kTmaTiled : -1;
     if (!o.is_virtual) {  // filter [oc, taps, ic] read as W'[(tap, co)][ci]: ld = taps * ic, ld2 = ic, rmod = oc
         if (!o.mn || o.batch_count > 1 || o.ld2 % ce != 0 || o.rmod % ce != 0 || extent != o.ld2 || encode_tiled() == nullptr) return -1;
@@ -158,6 +163,38 @@ bool make_filter_tap_map(CUtensorMap* map, const HostOperand& o, int box_k, int 
     return rc == CUDA_SUCCESS;
 }
 
+// Maps over a tap sub-grid of a filter [oc, FH, FW, ic] (HostOperand::TapSubset), all strides in bytes.
+//   K-major : {ic, nfx, nfy, oc}, box {ce, 1, 1, rows_tile}: rows_tile filters x one 128-byte channel slice of one tap
+//   by tap  : {ce ci, oc, nfx, nfy, ic / ce}, box {ce, ce filters, 1, 1, chunks}
+bool make_filter_sub_map(CUtensorMap* map, const HostOperand& o, int rows_tile, int esize, bool by_tap, bool atom32) {
+    EncodeTiledFn enc = encode_tiled();
+    if (!enc) return false;
+    const HostOperand::TapSubset& t = o.sub;
+    const cuuint64_t es = esize, ce = 128 / esize, ic = t.ic, oc = t.oc;
+    const char* base = static_cast<const char*>(o.ptr) + (static_cast<size_t>(t.f0y) * t.FW + t.f0x) * ic * es;
+    const cuuint64_t step_x = static_cast<cuuint64_t>(t.tx) * ic * es, step_y = static_cast<cuuint64_t>(t.ty) * t.FW * ic * es,
+                     step_f = static_cast<cuuint64_t>(t.FH) * t.FW * ic * es;
+    CUresult rc;
+    const CUtensorMapDataType dt = esize == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    const CUtensorMapSwizzle sw = atom32 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B;
+    if (!by_tap) {
+        cuuint64_t dims[4] = {ic, static_cast<cuuint64_t>(t.nfx), static_cast<cuuint64_t>(t.nfy), oc};
+        cuuint64_t strides[3] = {step_x, step_y, step_f};
+        cuuint32_t box[4] = {static_cast<cuuint32_t>(ce), 1u, 1u, static_cast<cuuint32_t>(rows_tile)};
+        cuuint32_t estr[4] = {1u, 1u, 1u, 1u};
+        rc = enc(map, dt, 4, const_cast<char*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
+                 CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    } else {
+        cuuint64_t dims[5] = {ce, oc, static_cast<cuuint64_t>(t.nfx), static_cast<cuuint64_t>(t.nfy), ic / ce};
+        cuuint64_t strides[4] = {step_f, step_x, step_y, 128u};
+        cuuint32_t box[5] = {static_cast<cuuint32_t>(ce), static_cast<cuuint32_t>(ce), 1u, 1u, static_cast<cuuint32_t>(rows_tile / ce)};
+        cuuint32_t estr[5] = {1u, 1u, 1u, 1u, 1u};
+        rc = enc(map, dt, 5, const_cast<char*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
+                 CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    }
+    return rc == CUDA_SUCCESS;
+}
+
 GatherSrc to_gather(const HostOperand& o, int rows, int cols, int esize) {
     GatherSrc s;
     std::memset(&s, 0, sizeof(s));
@@ -175,6 +212,14 @@ GatherSrc to_gather(const HostOperand& o, int rows, int cols, int esize) {
     const long long vec = 16 / esize;
     s.vec_ok = (reinterpret_cast<uintptr_t>(o.ptr) & 15) == 0 && o.ld % vec == 0 && o.ld2 % vec == 0 && o.batch_stride % vec == 0 &&
                (!o.is_virtual || o.cr.C % vec == 0);
+    if (o.sub.on) {  // the producer decodes k = (j * nfx + i) * C + c (or * oc + co) with these
+        s.cr.C = o.sub.ic;
+        s.cr.FW = o.sub.nfx;
+        s.cr.f_c = make_fastdiv(o.sub.ic);
+        s.cr.f_fw = make_fastdiv(o.sub.nfx);
+        s.rmod = o.rmod > 0 ? o.sub.oc : 0;
+        s.f_rmod = make_fastdiv(o.sub.oc > 0 ? o.sub.oc : 1);
+    }
     return s;
 }
 
@@ -243,6 +288,11 @@ size_t gemm_scratch_need(const Ctx* ctx, const GemmProblem& g) {
     return make_plan(ctx, g, ~static_cast<size_t>(0)).scratch;
 }
 
+bool gemm_goes_through_tma(const Ctx* ctx, const GemmProblem& g) {
+    Plan pl = make_plan(ctx, g, ~static_cast<size_t>(0));
+    return pl.tma;
+}
+
 int run_gemm(Ctx* ctx, const GemmProblem& g) {
     if (g.M < 0 || g.N < 0 || g.K < 0 || g.batch < 0 || g.kbatch < 1) return fail(1, "gemm: negative extent");
     if (g.M == 0 || g.N == 0 || g.batch == 0) return 0;
@@ -275,6 +325,7 @@ int run_gemm(Ctx* ctx, const GemmProblem& g) {
     size_t scratch_limit = own_scratch ? ctx->scratch_bytes : g.ws_bytes;
     if (reinterpret_cast<uintptr_t>(scratch) & 15) return fail(1, "gemm: scratch memory must be 16-byte aligned");
     Plan pl = make_plan(ctx, g, scratch_limit);
+    if ((g.a.sub.on || g.b.sub.on) && !pl.tma) return fail(1, "gemm: a tap subset of a filter is only read through TMA");
 
     GemmParams p;
     std::memset(&p, 0, sizeof(p));
@@ -304,6 +355,15 @@ int run_gemm(Ctx* ctx, const GemmProblem& g) {
             p.scatter_off[k] = bytes / esize - static_cast<long long>(kk) * g.scatter_rows * g.ldc;
         }
     }
+    p.out = g.out;
+    if (p.out.rows_on) {
+        p.out.f_plane = make_fastdiv(p.out.RH * p.out.RW);
+        p.out.f_rw = make_fastdiv(p.out.RW);
+    }
+    if (p.out.cols_on) {
+        p.out.f_c = make_fastdiv(p.out.C);
+        p.out.f_nfx = make_fastdiv(p.out.NFX);
+    }
     p.ldc = g.ldc;
     p.c_batch_stride = g.c_batch_stride;
     p.ws = scratch;
@@ -332,6 +392,8 @@ int run_gemm(Ctx* ctx, const GemmProblem& g) {
             if (mode == kTmaIm2col) return make_im2col_map(map, o, extent, rows_tile, esize, atom32);
             if (mode == kTmaIm2colMN) return make_im2col_map(map, o, g.K, ce, esize, atom32);
             if (mode == kTmaFilterTap) return make_filter_tap_map(map, o, ce, rows_tile / ce, esize, atom32);
+            if (mode == kTmaFilterSub) return make_filter_sub_map(map, o, rows_tile, esize, false, atom32);
+            if (mode == kTmaFilterTapSub) return make_filter_sub_map(map, o, rows_tile, esize, true, atom32);
             if (!o.mn) return make_map(map, o, g.K, extent, rows_tile, esize);
             *chunked = (pl.f32 || extent % ce == 0) && env_int("D8K_CHUNKED", 1);
             if (pl.f32 && !*chunked) return false;
@@ -352,7 +414,7 @@ int run_gemm(Ctx* ctx, const GemmProblem& g) {
     if (e != cudaSuccess) return fail(2, std::string("gemm: launch failed: ") + cudaGetErrorString(e));
     count_launch();
     {
-        static const char* const kModes[] = {"tiled", "im2col", "im2col-mn", "filter-tap"};
+        static const char* const kModes[] = {"tiled", "im2col", "im2col-mn", "filter-tap", "filter-sub", "filter-tap-sub"};
         std::ostringstream os;
         os << (pl.f32 ? "f32 " : "f16 ") << (pl.pair ? "pair" : pl.tma ? "tma" : "gather");
         if (pl.tma && !pl.pair) os << " a=" << kModes[pl.a_tma] << " b=" << kModes[pl.b_tma];

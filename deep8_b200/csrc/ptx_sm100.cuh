@@ -63,6 +63,12 @@ __device__ __forceinline__ void tma_load_4d(uint32_t dst, const void* tmap, uint
         ::"r"(dst), "l"(tmap), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
         : "memory");
 }
+__device__ __forceinline__ void tma_load_5d(uint32_t dst, const void* tmap, uint32_t bar, int c0, int c1, int c2, int c3, int c4) {
+    asm volatile(
+        "cp.async.bulk.tensor.5d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
+        ::"r"(dst), "l"(tmap), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4)
+        : "memory");
+}
 // im2col load over an NHWC image: `pixels per column` consecutive anchor pixels starting at (w, h, n) - the traversal
 // wraps at the bounding box's right edge to the next row and at its bottom to the next image - each displaced by the
 // filter-tap offset (off_w, off_h); channels [c, c + channels per pixel).  Pixels outside the image read as zeros.

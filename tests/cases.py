@@ -69,6 +69,8 @@ DECONV_EDGE = [
     ((1, 5, 6, 3), (2, 2, 3, 3), False, (2, 1)),
     ((2, 6, 9, 64), (64, 3, 2, 64), False, (1, 1)),             # stride 1: every contraction goes through TMA im2col
     ((2, 5, 8, 32), (32, 2, 3, 32), True, (2, 3)),              # unequal strides
+    ((1, 4, 4, 32), (32, 2, 2, 32), False, (3, 3)),             # stride beyond the filter: every third output row and column is zero
+    ((2, 6, 6, 64), (64, 5, 5, 64), True, (2, 2)),              # 3 + 2 taps per axis in the two residue classes
 ]
 DECONV_CFG4 = ((16, 14, 14, 256), (128, 4, 4, 256), True, (2, 2))   # output 27x27, what the reference's shape rule yields
 

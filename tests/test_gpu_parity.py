@@ -374,6 +374,14 @@ def test_conv_contractions_take_the_tma_paths(ctx):
     x3 = torch.zeros((1, 9, 9, 3), device="cuda")
     ctx.conv2d_forward(x3, torch.zeros((5, 3, 3, 3), device="cuda"), True, (1, 1), (1, 1))
     assert "gather" in ctx.last_kernel()  # 3 channels: no 128-byte channel slices
+    # stride 2: one launch per residue class of output pixels, each over its own sub-grid of taps
+    xd, wd = torch.zeros((2, 6, 6, 64), device="cuda"), torch.zeros((64, 4, 4, 64), device="cuda")
+    zd = ctx.deconv2d_forward(xd, wd, True, (2, 2))
+    assert "tma a=im2col b=filter-sub" in ctx.last_kernel()
+    ctx.deconv2d_grad_y(xd, wd, torch.zeros_like(wd), torch.zeros_like(zd), True, (2, 2))
+    assert "tma a=im2col-mn b=im2col-mn" in ctx.last_kernel()
+    ctx.conv2d_grad_x(x, torch.zeros_like(x), w, torch.zeros((2, 4, 4, 64), device="cuda"), True, (2, 2), (1, 1))
+    assert "tma a=im2col b=filter-tap-sub" in ctx.last_kernel()
     a = torch.zeros((1, 256, 512), device="cuda")
     ctx.matmul_forward(a, torch.zeros((1, 512, 128), device="cuda"))
     assert "f32 tma a=tiled b=tiled" in ctx.last_kernel()
