@@ -463,14 +463,17 @@ __device__ __forceinline__ void st_shared_v4(uint32_t addr, uint4 v) {
 }
 
 // What the tensor core misses when it reads the fp32 word v as tf32 (it drops the low 13 bits): v - trunc(v), exact
-// in fp32, rounded to tf32.
+// in fp32, rounded to tf32 (nearest, ties away from zero) with integer arithmetic - the conversion instruction runs at
+// a quarter of the rate of the logic and add pipes, and this loop is the converter warps' whole job.
 __device__ __forceinline__ uint4 tf32_low_part(const uint4& v) {
     uint4 o;
     const uint32_t* in = &v.x;
     uint32_t* out = &o.x;
 #pragma unroll
-    for (int i = 0; i < 4; ++i)
-        out[i] = __float_as_uint(ptx::to_tf32(__uint_as_float(in[i]) - __uint_as_float(in[i] & 0xffffe000u)));
+    for (int i = 0; i < 4; ++i) {
+        float d = __uint_as_float(in[i]) - __uint_as_float(in[i] & 0xffffe000u);
+        out[i] = (__float_as_uint(d) + 0x1000u) & 0xffffe000u;
+    }
     return o;
 }
 
