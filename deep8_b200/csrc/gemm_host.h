@@ -77,7 +77,7 @@ typedef cudaError_t (*GemmLaunchFn)(int grid, cudaStream_t stream, const CUtenso
 GemmLaunchFn lookup_f16_tma(bool a_mn, bool b_mn, int bn);
 GemmLaunchFn lookup_f16_gather(bool a_mn, bool b_mn, int bn);
 GemmLaunchFn lookup_f32_gather(bool a_mn, bool b_mn, int bn);
-GemmLaunchFn lookup_f32_tma(bool a_mn, bool b_mn, int bn);
+GemmLaunchFn lookup_f32_tma(bool a_mn, bool b_mn, int bn, bool a_in_tmem);
 // paired-CTA kernel: the first argument of the launch function is the number of CTA pairs
 GemmLaunchFn lookup_f16_pair(bool a_mn, bool b_mn);
 

@@ -171,7 +171,7 @@ __device__ __forceinline__ long long scatter_offset(const GemmParams& p, int row
     return p.scatter_off[k < kMaxScatter ? k : kMaxScatter - 1];
 }
 
-template <bool F32_, bool A_MN_, bool B_MN_, int BN_, int STAGES_, bool GATHER_>
+template <bool F32_, bool A_MN_, bool B_MN_, int BN_, int STAGES_, bool GATHER_, bool ATMEM_ = false>
 struct GemmCfg {
     static constexpr bool F32 = F32_, A_MN = A_MN_, B_MN = B_MN_, GATHER = GATHER_;
     static constexpr int BN = BN_, STAGES = STAGES_;
@@ -186,8 +186,18 @@ struct GemmCfg {
     static constexpr bool A_B32 = F32 && A_MN, B_B32 = F32 && B_MN;
     static constexpr int A_BYTES = kBM * 128;
     static constexpr int B_BYTES = BN * 128;
-    static constexpr int STAGE_BYTES = PARTS * (A_BYTES + B_BYTES);
-    static constexpr int TMEM_COLS = (2 * BN <= 32) ? 32 : (2 * BN <= 64) ? 64 : (2 * BN <= 128) ? 128 : (2 * BN <= 256) ? 256 : 512;
+    // ATMEM (fp32 behind TMA only): the converter warps put A's hi and lo images into tensor memory instead of shared
+    // memory - one row per lane, BK columns each - and the MMAs take A from there.  The stage keeps raw A and B hi/lo;
+    // shared memory then holds six stages instead of four and the three MMA passes read only B from it.
+    static constexpr bool ATMEM = ATMEM_;
+    static constexpr int A_PARTS = ATMEM ? 1 : PARTS;
+    static constexpr int STAGE_BYTES = A_PARTS * A_BYTES + PARTS * B_BYTES;
+    static constexpr int A_TMEM_COL0 = 2 * BN;                  // after the two accumulator buffers
+    static constexpr int A_TMEM_COLS = ATMEM ? 2 * BK * STAGES : 0;  // per stage BK columns of hi, BK of lo
+    static constexpr int TMEM_NEED = 2 * BN + A_TMEM_COLS;
+    static constexpr int TMEM_COLS = (TMEM_NEED <= 32) ? 32 : (TMEM_NEED <= 64) ? 64 : (TMEM_NEED <= 128) ? 128 : (TMEM_NEED <= 256) ? 256 : 512;
+    static_assert(TMEM_NEED <= 512, "tensor memory");
+    static_assert(!ATMEM || (F32 && !GATHER), "A in tensor memory belongs to the fp32 TMA kernels");
     // fp32 only: the tensor core adds into its fp32 accumulator with truncation, so a long chain drifts (about
     // 2e-5 of the result after 1300 accumulations).  Every CHUNK_KB k-blocks the accumulator buffer is handed to the
     // epilogue warps, which add it to register accumulators with round-to-nearest, and a fresh chain starts in the
@@ -741,7 +751,7 @@ d8k_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     asm volatile("ld.shared.b32 %0, [%1];" : "=r"(tmem_base) : "r"(tmem_slot) : "memory");
 
     auto stage_a = [&](int s) { return smem_base + s * Cfg::STAGE_BYTES; };
-    auto stage_b = [&](int s) { return smem_base + s * Cfg::STAGE_BYTES + Cfg::PARTS * Cfg::A_BYTES; };
+    auto stage_b = [&](int s) { return smem_base + s * Cfg::STAGE_BYTES + Cfg::A_PARTS * Cfg::A_BYTES; };
 
     if (!Cfg::GATHER && warp == Cfg::PRODUCER_WARP) {
         // ============================================================================ TMA producer
@@ -772,7 +782,8 @@ d8k_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         }
     } else if (warp == Cfg::MMA_WARP) {
         // ============================================================================ MMA issuer
-        constexpr uint32_t idesc = ptx::make_idesc(Cfg::F32 ? 2u : 0u, Cfg::A_MN, Cfg::B_MN, kBM, BN);
+        // A from tensor memory is always one row per lane, whatever the stored layout was
+        constexpr uint32_t idesc = ptx::make_idesc(Cfg::F32 ? 2u : 0u, Cfg::A_MN && !Cfg::ATMEM, Cfg::B_MN, kBM, BN);
         // descriptor step per UMMA_K: K-major advances 32 bytes inside the swizzled row; MN-major advances UMMA_K rows
         constexpr uint32_t a_step = Cfg::A_MN ? Cfg::UMMA_K * 128 : 32;
         constexpr uint32_t b_step = Cfg::B_MN ? Cfg::UMMA_K * 128 : 32;
@@ -808,7 +819,13 @@ d8k_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                         uint64_t da = ptx::smem_desc(a_hi + s * a_step, a_lbo, a_sbo, a_lay);
                         uint64_t db = ptx::smem_desc(b_hi + s * b_step, b_lbo, b_sbo, b_lay);
                         uint32_t accumulate = (in_chain > 0 || s > 0) ? 1u : 0u;
-                        if constexpr (Cfg::F32) {
+                        if constexpr (Cfg::ATMEM) {
+                            const uint32_t ta_hi = tmem_base + Cfg::A_TMEM_COL0 + stage * (2 * BK) + s * Cfg::UMMA_K;
+                            uint64_t db_lo = ptx::smem_desc(b_hi + Cfg::B_BYTES + s * b_step, b_lbo, b_sbo, b_lay);
+                            ptx::mma_tf32_a_tmem(d_tmem, ta_hi + BK, db, idesc, accumulate);  // small terms first
+                            ptx::mma_tf32_a_tmem(d_tmem, ta_hi, db_lo, idesc, 1u);
+                            ptx::mma_tf32_a_tmem(d_tmem, ta_hi, db, idesc, 1u);
+                        } else if constexpr (Cfg::F32) {
                             uint64_t da_lo = ptx::smem_desc(a_hi + Cfg::A_BYTES + s * a_step, a_lbo, a_sbo, a_lay);
                             uint64_t db_lo = ptx::smem_desc(b_hi + Cfg::B_BYTES + s * b_step, b_lbo, b_sbo, b_lay);
                             ptx::mma_tf32(d_tmem, da_lo, db, idesc, accumulate);  // small terms first
@@ -957,6 +974,42 @@ d8k_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                 const uint32_t phase = (t / STAGES) & 1;
                 ok = wait_bar(raw_bar(stage), phase, &s_abort, p.status, (kRoleLoader << 8) | 2);  // every reader observes the phase itself
                 if (!ok) break;
+                if constexpr (Cfg::ATMEM) {
+                    // A: this thread owns tile row 32 (warp % 4) + lane, the tensor-memory lane its warp may write
+                    const int q = warp & 3;
+                    uint32_t hi[32], lo[32];
+                    if constexpr (!Cfg::A_MN) {
+                        const int row = q * 32 + lane;
+                        const uint32_t base = stage_a(stage) + 128u * row;
+#pragma unroll
+                        for (int c = 0; c < 8; ++c) {  // the row's eight 16-byte chunks, un-swizzled on the way
+                            uint4 v = ptx::ld_shared_v4(base + ((c ^ (row & 7)) << 4));
+                            hi[4 * c] = v.x; hi[4 * c + 1] = v.y; hi[4 * c + 2] = v.z; hi[4 * c + 3] = v.w;
+                        }
+                    } else {
+                        // MN-major: chunk q holds BK k-rows of 32 m's; this thread's m is `lane`, one word per k-row
+                        const uint32_t base = stage_a(stage) + q * (BK * 128) + ((lane & 3) << 2);
+                        const int c16 = lane >> 2;
+#pragma unroll
+                        for (int k = 0; k < 32; ++k) hi[k] = ptx::ld_shared_b32(base + swz<true>(k, c16));
+                    }
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        float d = __uint_as_float(hi[i]) - __uint_as_float(hi[i] & 0xffffe000u);
+                        lo[i] = (__float_as_uint(d) + 0x1000u) & 0xffffe000u;
+                    }
+                    const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + Cfg::A_TMEM_COL0 + stage * (2 * BK);
+                    ptx::tmem_st_32x32(taddr, hi);
+                    ptx::tmem_st_32x32(taddr + BK, lo);
+                    uint4 vb[B_CHUNKS];
+                    const uint32_t b0 = stage_b(stage) + 16u * tid;
+#pragma unroll
+                    for (int i = 0; i < B_CHUNKS; ++i) vb[i] = ptx::ld_shared_v4(b0 + 2048u * i);
+#pragma unroll
+                    for (int i = 0; i < B_CHUNKS; ++i) st_shared_v4(b0 + 2048u * i + Cfg::B_BYTES, tf32_low_part(vb[i]));
+                    ptx::tmem_st_wait();
+                    ptx::tc_fence_before_sync();
+                } else {
                 uint4 va[A_CHUNKS], vb[B_CHUNKS];
                 const uint32_t a0 = stage_a(stage) + 16u * tid, b0 = stage_b(stage) + 16u * tid;
 #pragma unroll
@@ -967,6 +1020,7 @@ d8k_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                 for (int i = 0; i < A_CHUNKS; ++i) st_shared_v4(a0 + 2048u * i + Cfg::A_BYTES, tf32_low_part(va[i]));
 #pragma unroll
                 for (int i = 0; i < B_CHUNKS; ++i) st_shared_v4(b0 + 2048u * i + Cfg::B_BYTES, tf32_low_part(vb[i]));
+                }
                 ptx::fence_proxy_async_smem();
                 ptx::mbar_arrive(full_bar(stage));
             }

@@ -401,7 +401,7 @@ int run_gemm(Ctx* ctx, const GemmProblem& g) {
         };
         if (!build(&ta, g.a, pl.a_tma, g.M, kBM, &p.a_chunked) || !build(&tb, g.b, pl.b_tma, g.N, pl.bn, &p.b_chunked))
             return fail(2, "gemm: cuTensorMapEncode failed");
-        fn = pl.f32 ? lookup_f32_tma(g.a.mn, g.b.mn, pl.bn) : lookup_f16_tma(g.a.mn, g.b.mn, pl.bn);
+        fn = pl.f32 ? lookup_f32_tma(g.a.mn, g.b.mn, pl.bn, env_int("D8K_F32_ATMEM", 1) != 0) : lookup_f16_tma(g.a.mn, g.b.mn, pl.bn);
     } else {
         p.a = g.a.mn ? to_gather(g.a, g.K, g.M, esize) : to_gather(g.a, g.M, g.K, esize);
         p.b = g.b.mn ? to_gather(g.b, g.K, g.N, esize) : to_gather(g.b, g.N, g.K, esize);

@@ -387,3 +387,44 @@ def test_conv_contractions_take_the_tma_paths(ctx):
     assert "f32 tma a=tiled b=tiled" in ctx.last_kernel()
     torch.cuda.synchronize()
     assert ctx.status() == 0
+
+
+def _random_conv_cases(n, seed):
+    """Seeded random geometries with channel counts the TMA producer takes: everything else is drawn freely, so strides,
+    dilations, paddings, filter shapes and residue classes meet in combinations no hand-written list covers."""
+    r = np.random.Generator(np.random.Philox(seed))
+    out = []
+    while len(out) < n:
+        ic, oc = int(r.choice([32, 64, 96])), int(r.choice([32, 64, 96, 128]))
+        fh, fw = int(r.integers(1, 5)), int(r.integers(1, 5))
+        sy, sx = int(r.integers(1, 4)), int(r.integers(1, 4))
+        dy, dx = int(r.integers(1, 3)), int(r.integers(1, 3))
+        h, w = int(r.integers(fh * dy + 1, 13)), int(r.integers(fw * dx + 1, 13))
+        out.append(((int(r.integers(1, 4)), h, w, ic), (oc, fh, fw, ic), bool(r.integers(0, 2)), (sy, sx), (dy, dx)))
+    return out
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("xs,ws,cov,st,dil", _random_conv_cases(16, 2024))
+def test_conv_random_geometries_f32(ctx, restated, xs, ws, cov, st, dil):
+    parity(ctx, restated, "conv", xs, ws, (cov, st, dil), torch.float32, F32_TOL, seed=11)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("xs,ws,cov,st,dil", _random_conv_cases(6, 2025))
+def test_conv_random_geometries_integers_exact_and_f16(ctx, restated, xs, ws, cov, st, dil):
+    parity(ctx, restated, "conv", xs, ws, (cov, st, dil), torch.float32, 0.0, gen="int")
+    parity(ctx, restated, "conv", xs, ws, (cov, st, dil), torch.float16, F16_TOL)  # fp16 outputs round: sums pass 2048
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("xs,ws,cov,st,dil", _random_conv_cases(16, 2026))
+def test_deconv_random_geometries_f32(ctx, restated, xs, ws, cov, st, dil):
+    parity(ctx, restated, "deconv", xs, ws, (cov, st), torch.float32, F32_TOL, seed=12)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("xs,ws,cov,st,dil", _random_conv_cases(6, 2027))
+def test_deconv_random_geometries_integers_exact_and_f16(ctx, restated, xs, ws, cov, st, dil):
+    parity(ctx, restated, "deconv", xs, ws, (cov, st), torch.float32, 0.0, gen="int")
+    parity(ctx, restated, "deconv", xs, ws, (cov, st), torch.float16, F16_TOL)
