@@ -62,6 +62,40 @@ def peer_rotation(world, rank):
     return [(rank + k) % world for k in range(1, world)]
 
 
+class CudaRuntime:
+    """The pieces of torch.cuda that PeerAllReduce needs - events, stream ordering, tensors over raw addresses - behind
+    one small interface, so that the protocol itself can be exercised on host memory by the CPU tests."""
+
+    def __init__(self):
+        import torch
+        self.torch = torch
+
+    def event(self):
+        return self.torch.cuda.Event()
+
+    def record_current(self, event):
+        event.record(self.torch.cuda.current_stream())
+
+    def record(self, event, stream):
+        event.record(stream)
+
+    def stream_wait(self, stream, event):
+        stream.wait_event(event)
+
+    def current_wait(self, event):
+        self.torch.cuda.current_stream().wait_event(event)
+
+    def view(self, ptr, shape, dtype, device):
+        from .ops import tensor_view
+        return tensor_view(ptr, shape, dtype, device)
+
+    def element_size(self, dtype):
+        return self.torch.empty((), dtype=dtype).element_size()
+
+    def synchronize(self):
+        self.torch.cuda.synchronize()
+
+
 class PeerAllReduce:
     """Sum of one replicated-operand gradient over the GPUs of a box without a collective kernel.
 
@@ -85,18 +119,19 @@ class PeerAllReduce:
 
     FLAG_WORDS = 64  # per kind: one word per peer, padded
 
-    def __init__(self, ctx_main, ctx_side, side_stream, numel, dtype, device, group=None, timeout_ms=2000.0, rows=None):
+    def __init__(self, ctx_main, ctx_side, side_stream, numel, dtype, device, group=None, timeout_ms=2000.0, rows=None,
+                 runtime=None):
         """rows: the gradient is a rows x (numel / rows) matrix to be cut into row blocks - needed for scatter_grad_y,
-        where the contraction's epilogue stores each block straight into its owner's staging memory."""
-        import torch
-        from .ops import tensor_view
-        self.torch, self.ctx_main, self.ctx_side, self.side = torch, ctx_main, ctx_side, side_stream
+        where the contraction's epilogue stores each block straight into its owner's staging memory.
+        runtime: CudaRuntime unless a test substitutes host memory."""
+        self.rt = runtime if runtime is not None else CudaRuntime()
+        self.ctx_main, self.ctx_side, self.side = ctx_main, ctx_side, side_stream
         self.numel, self.dtype, self.device, self.group, self.timeout_ms = numel, dtype, device, group, timeout_ms
         self.world = dist.get_world_size(group) if dist.is_available() and dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if self.world > 1 else 0
         if self.world > 16:
             raise ValueError("at most 16 GPUs exchange through peer memory")
-        self.esize = torch.empty((), dtype=dtype).element_size()
+        self.esize = self.rt.element_size(dtype)
         self.rows, self.cols, self.block_rows = rows, None, None
         if rows is None:
             self.shards = gradient_shards(numel, self.world)
@@ -125,11 +160,11 @@ class PeerAllReduce:
             for q in range(self.world):
                 if q != self.rank:
                     self.peers[q] = ctx_main.peer_open(handles[q])
-        self.partial = tensor_view(self.base + self.off_partial, (numel,), dtype, device)
-        self.result = tensor_view(self.base + self.off_result, (numel,), dtype, device) if self.world > 1 else self.partial
+        self.partial = self.rt.view(self.base + self.off_partial, (numel,), dtype, device)
+        self.result = self.rt.view(self.base + self.off_result, (numel,), dtype, device) if self.world > 1 else self.partial
         self.order = peer_rotation(self.world, self.rank)
-        self.e_written = torch.cuda.Event()
-        self.e_done = torch.cuda.Event()
+        self.e_written = self.rt.event()
+        self.e_done = self.rt.event()
         if self.world > 1:
             dist.barrier(group=group)  # every rank has mapped every buffer before the first signal
 
@@ -163,11 +198,11 @@ class PeerAllReduce:
         """Call after the contraction that writes `partial` has been enqueued on the main stream."""
         if self.world == 1:
             return
-        torch, c, r = self.torch, self.ctx_side, self.rank
+        c, r = self.ctx_side, self.rank
         self.step += 1
         s = self.step
-        self.e_written.record(torch.cuda.current_stream())
-        self.side.wait_event(self.e_written)
+        self.rt.record_current(self.e_written)
+        self.rt.stream_wait(self.side, self.e_written)
         lo, hi = self.shards[r]
         n = hi - lo
         c.peer_signal([self._flag(q, 0, r) for q in self.order], s)                       # my partial is ready
@@ -194,17 +229,17 @@ class PeerAllReduce:
                 c.peer_copy(self.peers[q] + self.off_result + lo * self.esize, mine, n * self.esize)
         c.peer_signal([self._flag(q, 2, r) for q in self.order], s)                       # my shard has been delivered
         c.peer_wait([self._flag(r, 2, q) for q in self.order], s, self.timeout_ms)        # and so have theirs
-        self.e_done.record(self.side)
+        self.rt.record(self.e_done, self.side)
 
     def finish(self):
         """Main stream waits for the exchange; `result` then holds the sum on every rank."""
         if self.world > 1:
-            self.torch.cuda.current_stream().wait_event(self.e_done)
+            self.rt.current_wait(self.e_done)
 
     def close(self):
         if getattr(self, "base", None) is None:
             return
-        self.torch.cuda.synchronize()
+        self.rt.synchronize()
         if self.world > 1:
             dist.barrier(group=self.group)  # nobody unmaps or frees while a peer may still copy
         for q, p in enumerate(self.peers):

@@ -16,6 +16,14 @@ import torch
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    return port
+
+
 # ------------------------------------------------------------------------------------------------ CPU: plans
 def test_gradient_shards_partition_and_alignment():
     from deep8_b200.dp import gradient_shards
@@ -36,6 +44,158 @@ def test_peer_rotation_is_a_permutation_every_round():
             assert sorted(o) == [q for q in range(world) if q != r]
         for k in range(world - 1):
             assert sorted(o[k] for o in orders) == list(range(world))  # no GPU is visited twice in one round
+
+
+# ------------------------------------------------------------------------------------------------ CPU: the protocol on host memory
+class _HostContext:
+    """Stands in for deep8_b200.Context in the protocol test: "device memory" is POSIX shared memory that the other
+    rank maps, flags are words in it, and every call runs at once on the calling process - so the order of signals,
+    waits, copies and sums that PeerAllReduce issues is executed for real by two processes, only not on GPUs."""
+
+    def __init__(self):
+        self.blocks = {}
+        self.timeouts = 0
+
+    def peer_alloc(self, nbytes):
+        import ctypes
+        from multiprocessing import shared_memory
+        shm = shared_memory.SharedMemory(create=True, size=nbytes)
+        shm.buf[:nbytes] = bytes(nbytes)
+        addr = ctypes.addressof(ctypes.c_char.from_buffer(shm.buf))
+        self.blocks[addr] = shm
+        return addr, shm.name.encode().ljust(64, b"\0")
+
+    def peer_open(self, handle):
+        import ctypes
+        from multiprocessing import shared_memory
+        shm = shared_memory.SharedMemory(name=handle.rstrip(b"\0").decode())
+        addr = ctypes.addressof(ctypes.c_char.from_buffer(shm.buf))
+        self.blocks[addr] = shm
+        return addr
+
+    def peer_close(self, ptr):
+        self.blocks.pop(ptr)  # the mapping lives until the process exits: ctypes views pin the buffer
+
+    def peer_free(self, ptr):
+        self.blocks.pop(ptr).unlink()
+
+    def peer_signal(self, flags, value):
+        import ctypes
+        for f in flags:
+            ctypes.c_uint32.from_address(f).value = value
+
+    def peer_wait(self, flags, value, timeout_ms):
+        import ctypes
+        import time
+        t0 = time.time()
+        for f in flags:
+            while ctypes.c_int32(ctypes.c_uint32.from_address(f).value - value).value < 0:
+                if (time.time() - t0) * 1e3 > timeout_ms:
+                    self.timeouts += 1
+                    return
+                time.sleep(0.0005)
+
+    def peer_copy(self, dst, src, nbytes):
+        import ctypes
+        ctypes.memmove(dst, src, nbytes)
+
+    @staticmethod
+    def _f16(addr, count):
+        import ctypes
+        return np.ctypeslib.as_array((ctypes.c_uint16 * count).from_address(addr)).view(np.float16)
+
+    def sum_shards(self, dtype, out, srcs, count):
+        acc = np.zeros(count, dtype=np.float32)
+        for a in srcs:
+            acc = acc + self._f16(a, count).astype(np.float32)
+        self._f16(out, count)[:] = acc.astype(np.float16)
+
+    def matmul_grad_y_scatter(self, x, yc, dz, row_blocks, block_rows):
+        dy = (x[0].numpy().astype(np.float32).T @ dz[0].numpy().astype(np.float32)).astype(np.float16)
+        for k, addr in enumerate(row_blocks):
+            rows = dy[k * block_rows:(k + 1) * block_rows]
+            self._f16(addr, rows.size)[:] = rows.reshape(-1)
+
+
+class _HostRuntime:
+    def event(self):
+        return None
+
+    def record_current(self, event):
+        pass
+
+    def record(self, event, stream):
+        pass
+
+    def stream_wait(self, stream, event):
+        pass
+
+    def current_wait(self, event):
+        pass
+
+    def view(self, ptr, shape, dtype, device):
+        n = int(np.prod(shape))
+        return torch.from_numpy(_HostContext._f16(ptr, n)).view(*shape)
+
+    def element_size(self, dtype):
+        return 2
+
+    def synchronize(self):
+        pass
+
+
+def _protocol_worker(rank, world, port, out_dir):
+    sys.path.insert(0, ROOT)
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    import torch.distributed as dist
+    from deep8_b200.dp import PeerAllReduce
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    ctx = _HostContext()
+    ok = True
+    # copy-engine variant: partial -> pull -> sum -> push
+    numel = 5000
+    ar = PeerAllReduce(ctx, ctx, None, numel, torch.float16, "cpu", runtime=_HostRuntime(), timeout_ms=5000.0)
+    for s in range(3):
+        parts = [torch.from_numpy(np.random.default_rng(10 * s + q).standard_normal(numel).astype(np.float16)) for q in range(world)]
+        ar.before_write()
+        ar.partial.copy_(parts[rank])
+        ar.start()
+        ar.finish()
+        acc = np.zeros(numel, dtype=np.float32)
+        for q in range(world):
+            acc = acc + parts[q].numpy().astype(np.float32)
+        ok = ok and np.array_equal(ar.result.numpy(), acc.astype(np.float16))
+    ar.close()
+    # scattered variant: each rank's contraction writes row blocks into the owners' staging slots
+    r, rows, cols = 24, 300, 40
+    ar = PeerAllReduce(ctx, ctx, None, rows * cols, torch.float16, "cpu", runtime=_HostRuntime(), timeout_ms=5000.0, rows=rows)
+    for s in range(3):
+        xs = [torch.from_numpy(np.random.default_rng(100 * s + q).standard_normal((1, r, rows)).astype(np.float16)) for q in range(world)]
+        dzs = [torch.from_numpy(np.random.default_rng(100 * s + 50 + q).standard_normal((1, r, cols)).astype(np.float16)) for q in range(world)]
+        ar.before_write()
+        ar.scatter_grad_y(xs[rank], dzs[rank])
+        ar.start()
+        ar.finish()
+        acc = np.zeros((rows, cols), dtype=np.float32)
+        for q in range(world):
+            acc = acc + (xs[q][0].numpy().astype(np.float32).T @ dzs[q][0].numpy().astype(np.float32)).astype(np.float16).astype(np.float32)
+        ok = ok and np.array_equal(ar.result.numpy().reshape(rows, cols), acc.astype(np.float16))
+    ar.close()
+    with open(os.path.join(out_dir, "rank%d.txt" % rank), "w") as f:
+        f.write("%d %d" % (int(ok), ctx.timeouts))
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 3])
+def test_exchange_protocol_on_host_memory(tmp_path, world):
+    """Two and three gloo ranks run PeerAllReduce's own sequence of signals, bounded waits, copies and sums against shared
+    host memory: every rank ends with the rank-ordered sum, no wait runs out, for both the copy variant and the
+    scattered-contraction variant, three steps each (so the reuse hazards of staging and partial buffers are exercised)."""
+    import torch.multiprocessing as mp
+    mp.spawn(_protocol_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    for r in range(world):
+        assert open(os.path.join(str(tmp_path), "rank%d.txt" % r)).read() == "1 0"
 
 
 # ------------------------------------------------------------------------------------------------ GPU: one device
@@ -191,14 +351,6 @@ def test_scattered_grad_y_arguments_are_checked(ctx):
 
 
 # ------------------------------------------------------------------------------------------------ GPU: two devices
-def _free_port():
-    s = socket.socket()
-    s.bind(("127.0.0.1", 0))
-    port = s.getsockname()[1]
-    s.close()
-    return port
-
-
 def _exchange_worker(rank, world, port, numel, steps, out_dir):
     sys.path.insert(0, ROOT)
     os.environ["MASTER_ADDR"] = "127.0.0.1"
