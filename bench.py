@@ -185,8 +185,10 @@ class MlpStep:
     """The MLP step on one GPU through the d8k C ABI; buffers allocated once, as an executor would keep them.
     X, dY and Y are double-buffered so that the end-to-end loop can copy step i+1 in and step i-1 out while step i runs."""
 
-    def __init__(self, ctx, torch, device, rank, fused=True, exchange=None, scatter=False):
-        self.ctx, self.torch, self.fused, self.scatter = ctx, torch, fused, scatter
+    SGD = (1e-6, 1e-4)  # learning rate, weight decay of the optional trainer step (--sgd); small: the data are random every step
+
+    def __init__(self, ctx, torch, device, rank, fused=True, exchange=None, scatter=False, sgd=False):
+        self.ctx, self.torch, self.fused, self.scatter, self.sgd = ctx, torch, fused, scatter, sgd
         self.ar1 = self.ar2 = None
         g = torch.Generator(device=device)
         g.manual_seed(10)
@@ -207,13 +209,17 @@ class MlpStep:
             # weight gradients live in memory the peers map; the sums arrive in ar.result
             self.ar1, self.ar2 = exchange(self.W1.numel(), D_IN), exchange(self.W2.numel(), D_HID)
             self.dW1, self.dW2 = self.ar1.partial.view(self.W1.shape), self.ar2.partial.view(self.W2.shape)
+            if sgd:  # the weights move into peer memory: each rank updates the shard it sums and receives the rest
+                self.ar1.weights.copy_(self.W1.view(-1))
+                self.ar2.weights.copy_(self.W2.view(-1))
+                self.W1, self.W2 = self.ar1.weights.view(self.W1.shape), self.ar2.weights.view(self.W2.shape)
         self.gemm_events = []
         self.tail_events = []  # (after the last contraction, after the exchange has been waited for)
 
     def _reduce(self, which, dist, work, overlap):
         ar, grad = (self.ar1, self.dW1) if which == 1 else (self.ar2, self.dW2)
         if ar is not None:
-            ar.start()
+            ar.start(sgd=self.SGD if self.sgd else None)
         elif dist is not None and overlap:
             work.append(dist.all_reduce(grad, async_op=True))
 
@@ -279,6 +285,11 @@ class MlpStep:
                 work.append(dist.all_reduce(self.dW1, async_op=True))
             for w in work:
                 w.wait()
+        if self.sgd and self.ar1 is None:  # SGDTrainer::update on the full gradients (one GPU, or after NCCL)
+            from deep8_b200.dp import sgd_coefficients
+            alpha, beta = sgd_coefficients(*self.SGD)
+            c.axpby(self.dW2, alpha, self.W2, beta)
+            c.axpby(self.dW1, alpha, self.W1, beta)
 
 
 def run_gpu_arm(args):
@@ -309,9 +320,9 @@ def run_gpu_arm(args):
         side = torch.cuda.Stream(device=device)
         ctx_side = deep8_b200.Context(local_rank, scratch_bytes=1 << 20)
         ctx_side.use_stream(side)
-        exchange = lambda numel, rows: PeerAllReduce(ctx, ctx_side, side, numel, torch.float16, device, rows=rows)
+        exchange = lambda numel, rows: PeerAllReduce(ctx, ctx_side, side, numel, torch.float16, device, rows=rows, with_weights=args.sgd)
     mlp = MlpStep(ctx, torch, device, rank, fused=not args.unfused, exchange=exchange,
-                  scatter=exchange is not None and mode == "fused" and not args.unfused)
+                  scatter=exchange is not None and mode == "fused" and not args.unfused, sgd=args.sgd)
 
     def barrier():
         if dist is not None:
@@ -429,8 +440,9 @@ def run_gpu_arm(args):
         line = {
             "metric": METRIC, "value": per_gpu * world, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16 (f32 accumulate)",
-            "data": "synthetic", "config": dict(workload_config(world), step="fused epilogues, first-touch gradients" if not args.unfused
-                                                  else "reference call sequence (zero fill, separate ReLU passes)"),
+            "data": "synthetic", "config": dict(workload_config(world), step=("fused epilogues, first-touch gradients" if not args.unfused
+                                                  else "reference call sequence (zero fill, separate ReLU passes)") +
+                                                  (" + SGD step (outside the metric's work)" if args.sgd else "")),
             "per_gpu_tflops": per_gpu, "frac_of_nominal_fp16_peak": per_gpu / NOMINAL_FP16_TFLOPS,
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
                          "traffic": TRAFFIC_BYTES_PER_LAUNCH, "kernel": "d8k_gemm_pair_kernel (TMA-fed fp16, CTA pairs on 256x256 tiles)",
@@ -566,6 +578,9 @@ def main():
     ap.add_argument("--config", type=int, default=5, choices=[1, 2, 3, 4, 5], help="BASELINE configuration; 5 (default) is the benchmark "
                     "line, 1-4 print an auxiliary fp32 report for one operator")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--sgd", action="store_true",
+                    help="add the reference's SGD step on W1, W2 to every step (not part of the metric's forward + backward): "
+                         "after the backward pass on one GPU, inside the gradient exchange's sum kernel on several")
     ap.add_argument("--unfused", action="store_true", help="the reference's call sequence: zero fill, separate ReLU passes, += everywhere")
     ap.add_argument("--profile", action="store_true", help="for runs under a profiler: no clock sampling, no end-to-end or CPU leg, "
                     "warm-up as given; the printed numbers are not benchmark values")

@@ -104,8 +104,23 @@ __device__ __forceinline__ uint4 round16<__half>(const float* acc) {
 
 // out = srcs[0] + srcs[1] + ... in that order, fp32 accumulation, 16 bytes per thread per step; NSRC > 0 unrolls the
 // source loop so that all loads of a step are in flight together.
+// w = g * alpha + w * beta for 16 bytes of weights, g in fp32: two products and one sum, each rounded (no fused
+// multiply-add), then - for fp16 weights - one rounding to T.  For fp32 this is the reference's CPU arithmetic bit for bit.
+template <typename T>
+__device__ __forceinline__ uint4 sgd16(const float* g, const uint4& w_in, float alpha, float beta) {
+    constexpr int V = 16 / sizeof(T);
+    float w[V];
+#pragma unroll
+    for (int k = 0; k < V; ++k) w[k] = 0.f;
+    accumulate16<T>(w, w_in);
+#pragma unroll
+    for (int k = 0; k < V; ++k) w[k] = __fadd_rn(__fmul_rn(g[k], alpha), __fmul_rn(w[k], beta));
+    return round16<T>(w);
+}
+
 template <typename T, int NSRC>
-__global__ void __launch_bounds__(256) sum_shards_kernel(T* out, SrcList srcs, int nsrc, size_t count, bool vec) {
+__global__ void __launch_bounds__(256) sum_shards_kernel(T* out, SrcList srcs, int nsrc, size_t count, bool vec, T* weights, float alpha,
+                                                         float beta) {
     constexpr int V = 16 / sizeof(T);
     const size_t tid = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x;
     const size_t stride = gridDim.x * static_cast<size_t>(blockDim.x);
@@ -123,7 +138,15 @@ __global__ void __launch_bounds__(256) sum_shards_kernel(T* out, SrcList srcs, i
         } else {
             for (int s = 0; s < nsrc; ++s) accumulate16<T>(acc, __ldcs(reinterpret_cast<const uint4*>(srcs.p[s]) + i));
         }
-        reinterpret_cast<uint4*>(out)[i] = round16<T>(acc);
+        const uint4 g = round16<T>(acc);
+        if (out) reinterpret_cast<uint4*>(out)[i] = g;
+        if (weights) {  // the trainer's step on the gradient as stored (rounded to T), like a separate pass would see it
+            float gs[V];
+#pragma unroll
+            for (int k = 0; k < V; ++k) gs[k] = 0.f;
+            accumulate16<T>(gs, g);
+            reinterpret_cast<uint4*>(weights)[i] = sgd16<T>(gs, reinterpret_cast<const uint4*>(weights)[i], alpha, beta);
+        }
     }
     for (size_t i = nv * V + tid; i < count; i += stride) {
         float a = 0.f;
@@ -131,13 +154,23 @@ __global__ void __launch_bounds__(256) sum_shards_kernel(T* out, SrcList srcs, i
             if constexpr (sizeof(T) == 4) a += reinterpret_cast<const float*>(srcs.p[s])[i];
             else a += __half2float(reinterpret_cast<const __half*>(srcs.p[s])[i]);
         }
-        if constexpr (sizeof(T) == 4) reinterpret_cast<float*>(out)[i] = a;
-        else reinterpret_cast<__half*>(out)[i] = __float2half_rn(a);
+        T gt;
+        if constexpr (sizeof(T) == 4) gt = a;
+        else gt = __float2half_rn(a);
+        if (out) out[i] = gt;
+        if (weights) {
+            float gs, ws;
+            if constexpr (sizeof(T) == 4) { gs = gt; ws = weights[i]; }
+            else { gs = __half2float(gt); ws = __half2float(weights[i]); }
+            float r = __fadd_rn(__fmul_rn(gs, alpha), __fmul_rn(ws, beta));
+            if constexpr (sizeof(T) == 4) weights[i] = r;
+            else weights[i] = __float2half_rn(r);
+        }
     }
 }
 
 template <typename T>
-void launch_sum(const Ctx* ctx, void* out, const SrcList& srcs, int nsrc, size_t count, bool vec) {
+void launch_sum(const Ctx* ctx, void* out, const SrcList& srcs, int nsrc, size_t count, bool vec, void* weights, float alpha, float beta) {
     constexpr int V = 16 / sizeof(T);
     size_t blocks = (count / V + 255) / 256;
     size_t cap = static_cast<size_t>(ctx->num_sms) * 4;
@@ -145,11 +178,13 @@ void launch_sum(const Ctx* ctx, void* out, const SrcList& srcs, int nsrc, size_t
     if (blocks < 1) blocks = 1;
     dim3 grid(static_cast<unsigned>(blocks));
     T* o = static_cast<T*>(out);
+    T* w = static_cast<T*>(weights);
     switch (nsrc) {
-        case 2: sum_shards_kernel<T, 2><<<grid, 256, 0, ctx->stream>>>(o, srcs, nsrc, count, vec); break;
-        case 4: sum_shards_kernel<T, 4><<<grid, 256, 0, ctx->stream>>>(o, srcs, nsrc, count, vec); break;
-        case 8: sum_shards_kernel<T, 8><<<grid, 256, 0, ctx->stream>>>(o, srcs, nsrc, count, vec); break;
-        default: sum_shards_kernel<T, 0><<<grid, 256, 0, ctx->stream>>>(o, srcs, nsrc, count, vec); break;
+        case 1: sum_shards_kernel<T, 1><<<grid, 256, 0, ctx->stream>>>(o, srcs, nsrc, count, vec, w, alpha, beta); break;
+        case 2: sum_shards_kernel<T, 2><<<grid, 256, 0, ctx->stream>>>(o, srcs, nsrc, count, vec, w, alpha, beta); break;
+        case 4: sum_shards_kernel<T, 4><<<grid, 256, 0, ctx->stream>>>(o, srcs, nsrc, count, vec, w, alpha, beta); break;
+        case 8: sum_shards_kernel<T, 8><<<grid, 256, 0, ctx->stream>>>(o, srcs, nsrc, count, vec, w, alpha, beta); break;
+        default: sum_shards_kernel<T, 0><<<grid, 256, 0, ctx->stream>>>(o, srcs, nsrc, count, vec, w, alpha, beta); break;
     }
 }
 
@@ -251,24 +286,42 @@ int d8k_peer_copy(d8k_ctx* ctx, void* dst, const void* src, size_t bytes) {
     return 0;
 }
 
-int d8k_sum_shards(d8k_ctx* ctx, int dtype, void* out, const void* const* srcs, int nsrc, size_t count) {
+static int sum_shards_impl(d8k_ctx* ctx, int dtype, void* out, const void* const* srcs, int nsrc, size_t count, void* weights, float alpha,
+                           float beta) {
     if (int rc = check_ctx(ctx)) return rc;
     if (dtype != D8K_F16 && dtype != D8K_F32) return fail(D8K_ERR_ARGUMENT, "type is not support: dtype must be D8K_F16 or D8K_F32");
     if (count == 0) return 0;
-    if (!out || !srcs || nsrc < 1 || nsrc > kMaxPeers) return fail(D8K_ERR_ARGUMENT, "sum_shards: 1 to 16 sources");
+    if ((!out && !weights) || !srcs || nsrc < 1 || nsrc > kMaxPeers) return fail(D8K_ERR_ARGUMENT, "sum_shards: 1 to 16 sources");
     SrcList s = {};
-    uintptr_t bits = reinterpret_cast<uintptr_t>(out);
+    uintptr_t bits = reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(weights);
     for (int i = 0; i < nsrc; ++i) {
         if (!srcs[i]) return fail(D8K_ERR_ARGUMENT, "sum_shards: null source");
         s.p[i] = srcs[i];
         bits |= reinterpret_cast<uintptr_t>(srcs[i]);
     }
     bool vec = (bits & 15) == 0;
-    if (dtype == D8K_F32) launch_sum<float>(ctx, out, s, nsrc, count, vec);
-    else launch_sum<__half>(ctx, out, s, nsrc, count, vec);
+    if (dtype == D8K_F32) launch_sum<float>(ctx, out, s, nsrc, count, vec, weights, alpha, beta);
+    else launch_sum<__half>(ctx, out, s, nsrc, count, vec, weights, alpha, beta);
     D8K_CUDA(cudaGetLastError());
     count_launch();
     return 0;
+}
+
+int d8k_sum_shards(d8k_ctx* ctx, int dtype, void* out, const void* const* srcs, int nsrc, size_t count) {
+    if (!out) return fail(D8K_ERR_ARGUMENT, "sum_shards: null output");
+    return sum_shards_impl(ctx, dtype, out, srcs, nsrc, count, nullptr, 0.f, 0.f);
+}
+
+int d8k_sum_shards_sgd(d8k_ctx* ctx, int dtype, void* grad_out, const void* const* srcs, int nsrc, size_t count, void* weights, float alpha,
+                       float beta) {
+    if (!weights) return fail(D8K_ERR_ARGUMENT, "sum_shards_sgd: null weights");
+    return sum_shards_impl(ctx, dtype, grad_out, srcs, nsrc, count, weights, alpha, beta);
+}
+
+int d8k_axpby(d8k_ctx* ctx, int dtype, const void* x, float alpha, void* y, float beta, size_t n) {
+    if (!x || !y) return n == 0 ? 0 : fail(D8K_ERR_ARGUMENT, "axpby: null pointer");
+    const void* src[1] = {x};
+    return sum_shards_impl(ctx, dtype, nullptr, src, 1, n, y, alpha, beta);
 }
 
 }  // extern "C"

@@ -62,6 +62,18 @@ def peer_rotation(world, rank):
     return [(rank + k) % world for k in range(1, world)]
 
 
+def sgd_coefficients(learning_rate, weight_decay):
+    """(alpha, beta) with which SGDTrainer::update calls Math::AXPBY (deep8/src/trainer/SGDTrainer.cpp:13-14):
+    alpha = -1 * lr and beta = 1.0 - lr * decay, the product in float, the difference in double, both stored as float."""
+    import struct
+
+    def f32(v):
+        return struct.unpack("f", struct.pack("f", v))[0]
+
+    lr, wd = f32(learning_rate), f32(weight_decay)
+    return f32(-1.0 * lr), f32(1.0 - f32(lr * wd))
+
+
 class CudaRuntime:
     """The pieces of torch.cuda that PeerAllReduce needs - events, stream ordering, tensors over raw addresses - behind
     one small interface, so that the protocol itself can be exercised on host memory by the CPU tests."""
@@ -120,10 +132,12 @@ class PeerAllReduce:
     FLAG_WORDS = 64  # per kind: one word per peer, padded
 
     def __init__(self, ctx_main, ctx_side, side_stream, numel, dtype, device, group=None, timeout_ms=2000.0, rows=None,
-                 runtime=None):
+                 runtime=None, with_weights=False):
         """rows: the gradient is a rows x (numel / rows) matrix to be cut into row blocks - needed for scatter_grad_y,
         where the contraction's epilogue stores each block straight into its owner's staging memory.
-        runtime: CudaRuntime unless a test substitutes host memory."""
+        runtime: CudaRuntime unless a test substitutes host memory.
+        with_weights: also keep the operand itself in peer memory (`weights`), so that start(sgd=...) can apply the
+        trainer's step to the shard this rank sums and send updated weights instead of gradients."""
         self.rt = runtime if runtime is not None else CudaRuntime()
         self.ctx_main, self.ctx_side, self.side = ctx_main, ctx_side, side_stream
         self.numel, self.dtype, self.device, self.group, self.timeout_ms = numel, dtype, device, group, timeout_ms
@@ -148,7 +162,8 @@ class PeerAllReduce:
         # one allocation: partial | result | staging slot per rank | flags (ready, pulled, gathered)
         self.off_partial, self.off_result = 0, grad_bytes
         self.off_stage = 2 * grad_bytes
-        self.off_flags = self.off_stage + self.world * stage_bytes
+        self.off_weights = self.off_stage + self.world * stage_bytes
+        self.off_flags = self.off_weights + (grad_bytes if with_weights else 0)
         self.stage_bytes = stage_bytes
         total = self.off_flags + 3 * self.FLAG_WORDS * 4
         self.base, handle = ctx_main.peer_alloc(total)
@@ -162,6 +177,7 @@ class PeerAllReduce:
                     self.peers[q] = ctx_main.peer_open(handles[q])
         self.partial = self.rt.view(self.base + self.off_partial, (numel,), dtype, device)
         self.result = self.rt.view(self.base + self.off_result, (numel,), dtype, device) if self.world > 1 else self.partial
+        self.weights = self.rt.view(self.base + self.off_weights, (numel,), dtype, device) if with_weights else None
         self.order = peer_rotation(self.world, self.rank)
         self.e_written = self.rt.event()
         self.e_done = self.rt.event()
@@ -194,9 +210,21 @@ class PeerAllReduce:
         if self.world > 1 and self.step > 0:
             self.ctx_main.peer_wait([self._flag(self.rank, 1, q) for q in self.order], self.step, self.timeout_ms)
 
-    def start(self):
-        """Call after the contraction that writes `partial` has been enqueued on the main stream."""
+    def start(self, sgd=None):
+        """Call after the contraction that writes `partial` has been enqueued on the main stream.
+        sgd = (learning_rate, weight_decay): the reference's SGD step (SGDTrainer::update) runs inside the sum on the shard
+        this rank owns, and the all-gather carries the updated `weights`; `result` then holds only this rank's shard of
+        the summed gradient.  Every rank must pass the same values; `weights` must hold the same data on every rank."""
+        coeff = None
+        if sgd is not None:
+            if self.weights is None:
+                raise ValueError("PeerAllReduce was built without weights")
+            coeff = sgd_coefficients(*sgd)
         if self.world == 1:
+            self.scattered = False
+            if coeff is not None:
+                self.ctx_main.sum_shards(self.dtype, None, [self.base + self.off_partial], self.numel,
+                                         sgd=(self.base + self.off_weights, coeff[0], coeff[1]))
             return
         c, r = self.ctx_side, self.rank
         self.step += 1
@@ -209,10 +237,11 @@ class PeerAllReduce:
         c.peer_wait([self._flag(r, 0, q) for q in self.order], s, self.timeout_ms)        # so are theirs
         scattered, self.scattered = getattr(self, "scattered", False), False
         mine = self.base + self.off_result + lo * self.esize
+        step = None if coeff is None else (self.base + self.off_weights + lo * self.esize, coeff[0], coeff[1])
         if scattered:
             # every rank's epilogue has already put its block of partial sums into my staging slots
             if n > 0:
-                c.sum_shards(self.dtype, mine, [self.base + self.off_stage + q * self.stage_bytes for q in range(self.world)], n)
+                c.sum_shards(self.dtype, mine, [self.base + self.off_stage + q * self.stage_bytes for q in range(self.world)], n, sgd=step)
             c.peer_signal([self._flag(q, 1, r) for q in self.order], s)                   # my staging slots may be rewritten
         else:
             if n > 0:
@@ -223,10 +252,11 @@ class PeerAllReduce:
             if n > 0:
                 srcs = [self.base + self.off_partial + lo * self.esize if q == r else self.base + self.off_stage + q * self.stage_bytes
                         for q in range(self.world)]
-                c.sum_shards(self.dtype, mine, srcs, n)
+                c.sum_shards(self.dtype, mine, srcs, n, sgd=step)
         if n > 0:
+            off = (self.off_weights if step is not None else self.off_result) + lo * self.esize
             for q in self.order:                                                           # all-gather: push the finished shard
-                c.peer_copy(self.peers[q] + self.off_result + lo * self.esize, mine, n * self.esize)
+                c.peer_copy(self.peers[q] + off, self.base + off, n * self.esize)
         c.peer_signal([self._flag(q, 2, r) for q in self.order], s)                       # my shard has been delivered
         c.peer_wait([self._flag(r, 2, q) for q in self.order], s, self.timeout_ms)        # and so have theirs
         self.rt.record(self.e_done, self.side)

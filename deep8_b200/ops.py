@@ -283,12 +283,29 @@ class Context:
         check(self.lib.d8k_matmul_grad_y_scatter(self.h, dt, _p(x), xb, xr, xc, yc, _p(dz), self._ptr_array(row_blocks),
                                                  len(row_blocks), block_rows))
 
-    def sum_shards(self, dtype, out, srcs, count):
-        """out[i] = srcs[0][i] + ... + srcs[-1][i] in that order (fp32 accumulation); dtype is a torch dtype."""
+    @staticmethod
+    def _code(dtype):
         code = F16 if dtype == torch.float16 else F32 if dtype == torch.float32 else None
         if code is None:
             raise TypeError("type %s is not support" % dtype)
-        check(self.lib.d8k_sum_shards(self.h, code, ctypes.c_void_p(out), self._ptr_array(srcs), len(srcs), count))
+        return code
+
+    def sum_shards(self, dtype, out, srcs, count, sgd=None):
+        """out[i] = srcs[0][i] + ... + srcs[-1][i] in that order (fp32 accumulation); dtype is a torch dtype.
+        sgd = (weights address, alpha, beta): also weights = sum * alpha + weights * beta (out may then be None)."""
+        code = self._code(dtype)
+        if sgd is None:
+            check(self.lib.d8k_sum_shards(self.h, code, ctypes.c_void_p(out), self._ptr_array(srcs), len(srcs), count))
+        else:
+            w, alpha, beta = sgd
+            check(self.lib.d8k_sum_shards_sgd(self.h, code, ctypes.c_void_p(out) if out else None, self._ptr_array(srcs), len(srcs), count,
+                                              ctypes.c_void_p(w), alpha, beta))
+
+    def axpby(self, x, alpha, y, beta):
+        """y = x * alpha + y * beta (Math::AXPBY as the trainers call it); returns y."""
+        dt = _same(x, y)
+        check(self.lib.d8k_axpby(self.h, dt, _p(x), alpha, _p(y), beta, x.numel()))
+        return y
 
 
 class _RawCuda:

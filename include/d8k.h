@@ -184,6 +184,17 @@ D8K_API int d8k_matmul_grad_y_scatter(d8k_ctx* ctx, int dtype, const void* x, in
 /* out[i] = srcs[0][i] + srcs[1][i] + ... + srcs[nsrc-1][i], i < count, added in that order in fp32 and rounded once to
  * dtype: every GPU that sums the same partials in the same order gets the same bits.  nsrc <= 16; out may be srcs[k]. */
 D8K_API int d8k_sum_shards(d8k_ctx* ctx, int dtype, void* out, const void* const* srcs, int nsrc, size_t count);
+/* Math::AXPBY as the trainers use it (deep8/src/math/AXPBY.cu:9-37, SGDTrainer::update deep8/src/trainer/SGDTrainer.cpp:9-17):
+ * y = x * alpha + y * beta over n elements, with alpha = -learningRate and beta = 1 - learningRate * weightDecay for SGD.
+ * Products and sum are rounded separately in fp32 (the reference's CPU arithmetic, bit for bit, for D8K_F32); fp16
+ * operands are widened, and the result rounded once. */
+D8K_API int d8k_axpby(d8k_ctx* ctx, int dtype, const void* x, float alpha, void* y, float beta, size_t n);
+/* d8k_sum_shards and the SGD step in one pass over the shard a GPU owns: g = srcs[0] + ... + srcs[nsrc-1] (stored to
+ * grad_out unless it is NULL), then weights = g * alpha + weights * beta on the same elements, g taken as stored (rounded
+ * to dtype) so that the weights equal those of d8k_sum_shards followed by d8k_axpby.  The gradient is read once and the
+ * updated weights, not the gradient, are what the all-gather then has to carry. */
+D8K_API int d8k_sum_shards_sgd(d8k_ctx* ctx, int dtype, void* grad_out, const void* const* srcs, int nsrc, size_t count, void* weights,
+                               float alpha, float beta);
 
 #ifdef __cplusplus
 }

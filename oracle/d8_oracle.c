@@ -329,4 +329,17 @@ D8O_API void D8O_(d8o_deconv2d_grad_y)(const D8O_T* x, int b, int ih, int iw, in
     }
 }
 
+/* Math::AXPBY (deep8/src/math/AXPBY.cpp:22-31): z = x * alpha + y * beta, each product and the sum rounded in T
+ * (the reference's build has no fused multiply-add: no -m flags, deep8/CMakeLists.txt:86).  z may be x or y.
+ * SGDTrainer::update (deep8/src/trainer/SGDTrainer.cpp:9-17) is this with x = gradient, y = z = value,
+ * alpha = -learningRate, beta = 1 - learningRate * weightDecay. */
+D8O_API void D8O_(d8o_axpby)(const D8O_T* x, D8O_T alpha, const D8O_T* y, D8O_T beta, D8O_T* z, size_t n) {
+#pragma STDC FP_CONTRACT OFF
+    for (size_t i = 0; i < n; ++i) {
+        volatile D8O_T a = x[i] * alpha;
+        volatile D8O_T b = y[i] * beta;
+        z[i] = a + b;
+    }
+}
+
 #endif

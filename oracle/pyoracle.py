@@ -117,6 +117,16 @@ class _Base:
         return dy
 
 
+def sgd_coefficients(learning_rate, weight_decay):
+    """alpha, beta of SGDTrainer::update (deep8/src/trainer/SGDTrainer.cpp:13-14) with its float/double mix:
+    alpha = -1 * lr in float; beta = (1.0 - lr * decay) with the product in float and the difference in double,
+    stored to float."""
+    lr, wd = np.float32(learning_rate), np.float32(weight_decay)
+    alpha = np.float32(-1) * lr
+    beta = np.float32(1.0 - float(np.float32(lr * wd)))
+    return float(alpha), float(beta)
+
+
 class Restated(_Base):
     kind = "port"
 
@@ -127,6 +137,14 @@ class Restated(_Base):
 
     def threads(self):
         return os.cpu_count() or 1
+
+    def axpby(self, x, alpha, y, beta):
+        """x * alpha + y * beta (Math::AXPBY), a new array."""
+        dt = self._check(x, y)
+        z = np.empty_like(x)
+        ct = ctypes.c_float if dt == np.float32 else ctypes.c_double
+        getattr(self.lib, "d8o_axpby_" + _suffix(dt))(_ptr(x), ct(alpha), _ptr(y), ct(beta), _ptr(z), ctypes.c_size_t(x.size))
+        return z
 
     def _matmul(self, which, x, dx, y, dy, z, dz):
         dt = self._check(x, y)
@@ -188,6 +206,13 @@ class Reference(_Base):
     def _ok(self, rc):
         if rc != 0:
             raise RuntimeError(self.lib.d8ref_last_error().decode())
+
+    def axpby(self, x, alpha, y, beta):
+        dt = self._check(x, y)
+        z = np.empty_like(x)
+        self._ok(self.lib.d8ref_axpby(0 if dt == np.float32 else 1, _ptr(x), ctypes.c_float(alpha), _ptr(y), ctypes.c_float(beta),
+                                      _ptr(z), ctypes.c_size_t(x.size)))
+        return z
 
     def _matmul(self, which, x, dx, y, dy, z, dz):
         dt = self._check(x, y)

@@ -23,6 +23,7 @@
 #include "math/MatrixMultiply.h"
 #include "math/Conv2d.h"
 #include "math/DeConv2d.h"
+#include "math/AXPBY.h"
 
 #define D8REF_API extern "C" __attribute__((visibility("default")))
 
@@ -153,5 +154,16 @@ D8REF_API int d8ref_deconv2d(int which, int dtype,
             View vdz(dtype, dz, b, {oh, ow, oc});
             Deep8::Math::DeConv2dGradY(vx.tensor, vy.tensor, vdy.tensor, vz.tensor, vdz.tensor, covered != 0, strideY, strideX, nullptr);
         }
+    });
+}
+
+// Math::AXPBY (deep8/src/math/AXPBY.cpp:6-20): z = x * alpha + y * beta over n elements; z may alias x or y.
+// This is the arithmetic of SGDTrainer::update (deep8/src/trainer/SGDTrainer.cpp:9-17).
+D8REF_API int d8ref_axpby(int dtype, const void* x, float alpha, const void* y, float beta, void* z, size_t n) {
+    return guarded([&] {
+        View vx(dtype, x, 1, {n});
+        View vy(dtype, y, 1, {n});
+        View vz(dtype, z, 1, {n});
+        Deep8::Math::AXPBY(vx.tensor, alpha, vy.tensor, beta, vz.tensor);
     });
 }

@@ -148,3 +148,23 @@ def test_library_exports_every_declared_symbol():
     for name in declared:
         assert hasattr(lib, name), name
     assert declared == set(_lib.SIGNATURES), declared ^ set(_lib.SIGNATURES)
+
+
+@pytest.mark.parametrize("dtype", [np.float32, np.float64])
+def test_axpby_restated_equals_reference_bit_for_bit(restated, reference, dtype):
+    """Math::AXPBY as SGDTrainer::update calls it: the plain-C restatement and the reference's Eigen expression round the two
+    products and the sum the same way, so the results are identical, not merely close."""
+    from oracle import pyoracle
+    rng = np.random.default_rng(3)
+    g, w = rng.standard_normal(100003).astype(dtype), rng.standard_normal(100003).astype(dtype)
+    for lr, decay in ((0.01, 0.0005), (0.5, 0.0), (1e-3, 0.1)):
+        alpha, beta = pyoracle.sgd_coefficients(lr, decay)
+        assert alpha == float(np.float32(-lr)) and abs(beta - (1 - lr * decay)) < 1e-6
+        assert np.array_equal(restated.axpby(g, alpha, w, beta), reference.axpby(g, alpha, w, beta))
+
+
+def test_sgd_coefficients_host_side_agrees_with_the_oracle():
+    from deep8_b200.dp import sgd_coefficients
+    from oracle import pyoracle
+    for lr, decay in ((0.01, 0.0005), (0.5, 0.0), (1e-3, 0.1), (0.3, 0.7)):
+        assert sgd_coefficients(lr, decay) == pyoracle.sgd_coefficients(lr, decay)

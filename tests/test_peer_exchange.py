@@ -104,11 +104,17 @@ class _HostContext:
         import ctypes
         return np.ctypeslib.as_array((ctypes.c_uint16 * count).from_address(addr)).view(np.float16)
 
-    def sum_shards(self, dtype, out, srcs, count):
+    def sum_shards(self, dtype, out, srcs, count, sgd=None):
         acc = np.zeros(count, dtype=np.float32)
         for a in srcs:
             acc = acc + self._f16(a, count).astype(np.float32)
-        self._f16(out, count)[:] = acc.astype(np.float16)
+        g = acc.astype(np.float16)
+        if out:
+            self._f16(out, count)[:] = g
+        if sgd is not None:
+            w, alpha, beta = sgd
+            wv = self._f16(w, count)
+            wv[:] = (g.astype(np.float32) * np.float32(alpha) + wv.astype(np.float32) * np.float32(beta)).astype(np.float16)
 
     def matmul_grad_y_scatter(self, x, yc, dz, row_blocks, block_rows):
         dy = (x[0].numpy().astype(np.float32).T @ dz[0].numpy().astype(np.float32)).astype(np.float16)
@@ -181,6 +187,26 @@ def _protocol_worker(rank, world, port, out_dir):
         for q in range(world):
             acc = acc + (xs[q][0].numpy().astype(np.float32).T @ dzs[q][0].numpy().astype(np.float32)).astype(np.float16).astype(np.float32)
         ok = ok and np.array_equal(ar.result.numpy().reshape(rows, cols), acc.astype(np.float16))
+    ar.close()
+    # the trainer's step inside the sum: every rank ends with the same updated weights
+    ar = PeerAllReduce(ctx, ctx, None, numel, torch.float16, "cpu", runtime=_HostRuntime(), timeout_ms=5000.0, with_weights=True)
+    w0 = np.random.default_rng(7).standard_normal(numel).astype(np.float16)
+    ar.weights.copy_(torch.from_numpy(w0))
+    want = w0.copy()
+    from deep8_b200.dp import sgd_coefficients
+    alpha, beta = sgd_coefficients(0.05, 0.001)
+    for s in range(3):
+        parts = [np.random.default_rng(20 * s + q).standard_normal(numel).astype(np.float16) for q in range(world)]
+        ar.before_write()
+        ar.partial.copy_(torch.from_numpy(parts[rank]))
+        ar.start(sgd=(0.05, 0.001))
+        ar.finish()
+        acc = np.zeros(numel, dtype=np.float32)
+        for q in range(world):
+            acc = acc + parts[q].astype(np.float32)
+        g = acc.astype(np.float16).astype(np.float32)
+        want = (g * np.float32(alpha) + want.astype(np.float32) * np.float32(beta)).astype(np.float16)
+        ok = ok and np.array_equal(ar.weights.numpy(), want)
     ar.close()
     with open(os.path.join(out_dir, "rank%d.txt" % rank), "w") as f:
         f.write("%d %d" % (int(ok), ctx.timeouts))
@@ -350,6 +376,51 @@ def test_scattered_grad_y_arguments_are_checked(ctx):
     torch.cuda.synchronize()
 
 
+@pytest.mark.gpu
+@pytest.mark.parametrize("n", [1000, 4096 * 33 + 5])
+def test_axpby_is_the_reference_sgd_step(ctx, restated, n):
+    """fp32: bit for bit the reference's x * alpha + y * beta (two roundings, no fused multiply-add); fp16 within 2e-2."""
+    from oracle import pyoracle
+    alpha, beta = pyoracle.sgd_coefficients(0.01, 0.0005)
+    from deep8_b200.dp import sgd_coefficients
+    assert sgd_coefficients(0.01, 0.0005) == (alpha, beta)
+    rng = np.random.default_rng(n)
+    g, w = rng.standard_normal(n).astype(np.float32), rng.standard_normal(n).astype(np.float32)
+    want = restated.axpby(g, alpha, w, beta)
+    W = torch.from_numpy(w).cuda()
+    ctx.axpby(torch.from_numpy(g).cuda(), alpha, W, beta)
+    torch.cuda.synchronize()
+    assert np.array_equal(W.cpu().numpy(), want)
+    if pyoracle.Reference.available():
+        assert np.array_equal(pyoracle.Reference().axpby(g, alpha, w, beta), want)
+    gh, wh = g.astype(np.float16), w.astype(np.float16)
+    Wh = torch.from_numpy(wh).cuda()
+    ctx.axpby(torch.from_numpy(gh).cuda(), alpha, Wh, beta)
+    torch.cuda.synchronize()
+    want16 = restated.axpby(gh.astype(np.float32), alpha, wh.astype(np.float32), beta)
+    assert np.abs(Wh.cpu().numpy().astype(np.float32) - want16).max() <= 2e-2 * np.abs(want16).max()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [torch.float16, torch.float32])
+def test_sum_shards_sgd_equals_sum_then_axpby(ctx, dtype):
+    n = 8 * 1024 + 3
+    g = torch.Generator(device="cuda").manual_seed(5)
+    parts = [torch.randn(n, device="cuda", generator=g).to(dtype) for _ in range(4)]
+    w = torch.randn(n, device="cuda", generator=g).to(dtype)
+    grad = torch.empty(n, device="cuda", dtype=dtype)
+    ctx.sum_shards(dtype, grad.data_ptr(), [p.data_ptr() for p in parts], n)
+    w_two = ctx.axpby(grad, -0.05, w.clone(), 0.999)
+    w_one, grad_one = w.clone(), torch.empty_like(grad)
+    ctx.sum_shards(dtype, grad_one.data_ptr(), [p.data_ptr() for p in parts], n, sgd=(w_one.data_ptr(), -0.05, 0.999))
+    torch.cuda.synchronize()
+    assert torch.equal(grad_one, grad) and torch.equal(w_one, w_two)
+    w_none = w.clone()
+    ctx.sum_shards(dtype, None, [p.data_ptr() for p in parts], n, sgd=(w_none.data_ptr(), -0.05, 0.999))
+    torch.cuda.synchronize()
+    assert torch.equal(w_none, w_two)
+
+
 # ------------------------------------------------------------------------------------------------ GPU: two devices
 def _exchange_worker(rank, world, port, numel, steps, out_dir):
     sys.path.insert(0, ROOT)
@@ -384,6 +455,29 @@ def _exchange_worker(rank, world, port, numel, steps, out_dir):
                 gq = torch.Generator(device=dev).manual_seed(100 * s + q)
                 acc = acc + torch.randn(numel, device=dev, generator=gq).to(torch.float16).cpu().numpy().astype(np.float32)
             ok = ok and np.array_equal(got.cpu().numpy(), acc.astype(np.float16))
+    ar.close()
+    # the SGD step inside the sum: both ranks end with the same weights, equal to sum -> round -> axpby on the host
+    from deep8_b200.dp import sgd_coefficients
+    ar = PeerAllReduce(c_main, c_side, side, numel, torch.float16, dev, with_weights=True)
+    alpha, beta = sgd_coefficients(0.05, 0.001)
+    with torch.cuda.stream(main):
+        w0 = torch.randn(numel, device=dev, generator=torch.Generator(device=dev).manual_seed(77)).to(torch.float16)
+        ar.weights.copy_(w0)
+        want = w0.cpu().numpy()
+        for s in range(2):
+            g = torch.Generator(device=dev).manual_seed(300 * s + rank)
+            ar.before_write()
+            ar.partial.copy_(torch.randn(numel, device=dev, generator=g).to(torch.float16))
+            ar.start(sgd=(0.05, 0.001))
+            ar.finish()
+            main.synchronize()
+            acc = np.zeros(numel, dtype=np.float32)
+            for q in range(world):
+                gq = torch.Generator(device=dev).manual_seed(300 * s + q)
+                acc = acc + torch.randn(numel, device=dev, generator=gq).to(torch.float16).cpu().numpy().astype(np.float32)
+            gsum = acc.astype(np.float16).astype(np.float32)
+            want = (gsum * np.float32(alpha) + want.astype(np.float32) * np.float32(beta)).astype(np.float16)
+            ok = ok and np.array_equal(ar.weights.cpu().numpy(), want)
     status = (c_main.status(), c_side.status())
     ar.close()
     with open(os.path.join(out_dir, "rank%d.txt" % rank), "w") as f:
