@@ -33,6 +33,9 @@ SIGNATURES = {
     "d8k_matmul_grad_y_into": (_i, [_vp, _i, _vp, _i, _i, _i, _vp, _i, _i, _vp, _i]),
     "d8k_matmul_forward_relu": (_i, [_vp, _i, _vp, _i, _i, _i, _vp, _i, _i, _vp, _vp]),
     "d8k_matmul_grad_x_relu": (_i, [_vp, _i, _vp, _i, _i, _i, _vp, _i, _i, _vp, _i, _vp, _vp, _i]),
+    "d8k_matmul_forward_bias": (_i, [_vp, _i, _vp, _i, _i, _i, _vp, _i, _i, _vp, _vp]),
+    "d8k_add_bias": (_i, [_vp, _i, _vp, _vp, _vp, _sz, _i]),
+    "d8k_add_bias_grad": (_i, [_vp, _i, _vp, _vp, _sz, _i]),
     "d8k_conv2d_out_dim": (_i, [_i, _i, _i, _i, _i]),
     "d8k_deconv2d_out_dim": (_i, [_i, _i, _i, _i]),
     "d8k_conv2d_interim_size": (_sz, [_vp, _i, _i] + [_i] * 9),

@@ -312,6 +312,60 @@ __global__ void relu_backward_kernel(const T* __restrict__ x, T* __restrict__ dx
         if (to_f(x[i]) > 0.f) dx[i] = from_f<T>(to_f(dx[i]) + to_f(dy[i]));
 }
 
+// z[r][c] = x[r][c] + bias[c]: Math::Add with the bias broadcast over batch and rows (deep8/src/math/Add.cu).
+template <typename T>
+__global__ void add_bias_kernel(const T* __restrict__ x, const T* __restrict__ bias, T* __restrict__ z, size_t rows, int cols, bool vec) {
+    constexpr int V = 16 / sizeof(T);
+    const size_t n = rows * static_cast<size_t>(cols);
+    size_t tid = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x;
+    size_t stride = gridDim.x * static_cast<size_t>(blockDim.x);
+    if (vec) {  // cols is a multiple of V: a 16-byte piece stays inside one row
+        for (size_t i = tid; i < n / V; i += stride) {
+            uint4 a = reinterpret_cast<const uint4*>(x)[i];
+            uint4 b = __ldg(reinterpret_cast<const uint4*>(bias) + (i % (cols / V)));
+            T* ae = reinterpret_cast<T*>(&a);
+            const T* be = reinterpret_cast<const T*>(&b);
+#pragma unroll
+            for (int k = 0; k < V; ++k) ae[k] = from_f<T>(to_f(ae[k]) + to_f(be[k]));
+            reinterpret_cast<uint4*>(z)[i] = a;
+        }
+    } else {
+        for (size_t i = tid; i < n; i += stride) z[i] = from_f<T>(to_f(x[i]) + to_f(bias[i % cols]));
+    }
+}
+
+// Column sums for Math::AddGradY of a bias, in two fixed-order steps: CTA (strip, slice) adds its slice of rows for 32
+// columns into partial[slice][col] (rows in order, fp32), then the last step adds the slices in order and accumulates
+// into dbias.  Every run adds in the same order.
+template <typename T>
+__global__ void bias_grad_partial_kernel(const T* __restrict__ dz, float* __restrict__ partial, size_t rows, int cols, int rows_per_slice) {
+    const int col = blockIdx.x * 32 + (threadIdx.x & 31);
+    const int sub = threadIdx.x >> 5;  // 8 warps share the slice's rows; their sums meet in shared memory in warp order
+    __shared__ float part[8][32];
+    const size_t r0 = static_cast<size_t>(blockIdx.y) * rows_per_slice;
+    size_t r1 = r0 + rows_per_slice;
+    if (r1 > rows) r1 = rows;
+    float acc = 0.f;
+    if (col < cols)
+        for (size_t r = r0 + sub; r < r1; r += 8) acc += to_f(dz[r * cols + col]);
+    part[sub][threadIdx.x & 31] = acc;
+    __syncthreads();
+    if (sub == 0 && col < cols) {
+        float t = 0.f;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) t += part[w][threadIdx.x];
+        partial[static_cast<size_t>(blockIdx.y) * cols + col] = t;
+    }
+}
+template <typename T>
+__global__ void bias_grad_final_kernel(T* __restrict__ dbias, const float* __restrict__ partial, int slices, int cols) {
+    int col = blockIdx.x * blockDim.x + threadIdx.x;
+    if (col >= cols) return;
+    float t = 0.f;
+    for (int s = 0; s < slices; ++s) t += partial[static_cast<size_t>(s) * cols + col];
+    dbias[col] = from_f<T>(to_f(dbias[col]) + t);
+}
+
 bool aligned16(const void* a, const void* b, const void* c) {
     return ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b) | reinterpret_cast<uintptr_t>(c)) & 15) == 0;
 }
@@ -514,6 +568,60 @@ int d8k_matmul_grad_x_relu(d8k_ctx* ctx, int dtype, void* dx, int xb, int xr, in
                            int accumulate_dx, const void* h, void* dh, int accumulate_dh) {
     if (!h || !dh) return fail(D8K_ERR_ARGUMENT, "d8k_matmul_grad_x_relu: null pointer");
     return matmul_grad_x_impl(ctx, dtype, dx, xb, xr, xc, y, yb, yc, dz, accumulate_dx, 2, h, dh, accumulate_dh);
+}
+
+int d8k_matmul_forward_bias(d8k_ctx* ctx, int dtype, const void* x, int xb, int xr, int xc, const void* y, int yb, int yc, const void* bias,
+                            void* z) {
+    if (!bias) return fail(D8K_ERR_ARGUMENT, "d8k_matmul_forward_bias: null pointer");
+    return matmul_forward_impl(ctx, dtype, x, xb, xr, xc, y, yb, yc, z, 3, const_cast<void*>(bias));
+}
+
+int d8k_add_bias(d8k_ctx* ctx, int dtype, const void* x, const void* bias, void* z, size_t rows, int cols) {
+    if (int rc = check_ctx(ctx)) return rc;
+    if (int rc = check_dtype(dtype)) return rc;
+    if (rows == 0 || cols <= 0) return cols < 0 ? fail(D8K_ERR_ARGUMENT, "the shape is error") : 0;
+    if (!x || !bias || !z) return fail(D8K_ERR_ARGUMENT, "add_bias: null pointer");
+    const size_t n = rows * static_cast<size_t>(cols);
+    const int per = dtype == D8K_F32 ? 4 : 8;
+    bool vec = aligned16(x, bias, z) && cols % per == 0;
+    if (dtype == D8K_F32)
+        add_bias_kernel<float><<<elementwise_grid(ctx, n, 4), 256, 0, ctx->stream>>>(static_cast<const float*>(x), static_cast<const float*>(bias),
+                                                                                     static_cast<float*>(z), rows, cols, vec);
+    else
+        add_bias_kernel<__half><<<elementwise_grid(ctx, n, 8), 256, 0, ctx->stream>>>(static_cast<const __half*>(x), static_cast<const __half*>(bias),
+                                                                                      static_cast<__half*>(z), rows, cols, vec);
+    D8K_CUDA(cudaGetLastError());
+    count_launch();
+    return 0;
+}
+
+int d8k_add_bias_grad(d8k_ctx* ctx, int dtype, void* dbias, const void* dz, size_t rows, int cols) {
+    if (int rc = check_ctx(ctx)) return rc;
+    if (int rc = check_dtype(dtype)) return rc;
+    if (rows == 0 || cols <= 0) return cols < 0 ? fail(D8K_ERR_ARGUMENT, "the shape is error") : 0;
+    if (!dbias || !dz) return fail(D8K_ERR_ARGUMENT, "add_bias_grad: null pointer");
+    // enough slices to occupy the GPU, bounded by the context's scratch memory (slices * cols floats)
+    const int strips = (cols + 31) / 32;
+    int slices = (ctx->num_sms * 4 + strips - 1) / strips;
+    const size_t max_slices = ctx->scratch_bytes / (static_cast<size_t>(cols) * sizeof(float));
+    if (max_slices < 1) return fail(D8K_ERR_ARGUMENT, "add_bias_grad: the context's scratch memory is smaller than one row of floats");
+    if (static_cast<size_t>(slices) > max_slices) slices = static_cast<int>(max_slices);
+    if (static_cast<size_t>(slices) > (rows + 63) / 64) slices = static_cast<int>((rows + 63) / 64);
+    if (slices < 1) slices = 1;
+    const int rows_per_slice = static_cast<int>((rows + slices - 1) / slices);
+    slices = static_cast<int>((rows + rows_per_slice - 1) / rows_per_slice);
+    dim3 grid(strips, slices);
+    if (dtype == D8K_F32) {
+        bias_grad_partial_kernel<float><<<grid, 256, 0, ctx->stream>>>(static_cast<const float*>(dz), ctx->scratch, rows, cols, rows_per_slice);
+        bias_grad_final_kernel<float><<<(cols + 255) / 256, 256, 0, ctx->stream>>>(static_cast<float*>(dbias), ctx->scratch, slices, cols);
+    } else {
+        bias_grad_partial_kernel<__half><<<grid, 256, 0, ctx->stream>>>(static_cast<const __half*>(dz), ctx->scratch, rows, cols, rows_per_slice);
+        bias_grad_final_kernel<__half><<<(cols + 255) / 256, 256, 0, ctx->stream>>>(static_cast<__half*>(dbias), ctx->scratch, slices, cols);
+    }
+    D8K_CUDA(cudaGetLastError());
+    count_launch();
+    count_launch();
+    return 0;
 }
 
 int d8k_conv2d_out_dim(int in, int filter, int stride, int dilation, int covered) {

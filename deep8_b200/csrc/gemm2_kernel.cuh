@@ -353,9 +353,17 @@ d8k_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
 #pragma unroll
                             for (int i = 0; i < 8; ++i) cv[i] += old[i];
                         }
-                        const uint4 cw = V::pack(cv);
+                        uint4 cw = V::pack(cv);
+                        if (p.epi == 3) {  // + bias row, after the product's own rounding (MatrixMultiply then Add)
+                            float b[8];
+                            V::unpack(cw, cv);
+                            V::unpack(__ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const OutT*>(p.E1) + col0) + v), b);
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) cv[i] += b[i];
+                            cw = V::pack(cv);
+                        }
                         st_shared_v4(s0 + slot_off(lane, v), cw);
-                        if (p.epi != 0) V::unpack(cw, cv);  // the stored (rounded) values drive the fused tails
+                        if (p.epi == 1 || p.epi == 2) V::unpack(cw, cv);  // the stored (rounded) values drive the fused tails
                         if (p.epi == 1) {
 #pragma unroll
                             for (int i = 0; i < 8; ++i) cv[i] = cv[i] > 0.f ? cv[i] : 0.f;

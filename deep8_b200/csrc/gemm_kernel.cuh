@@ -123,7 +123,7 @@ struct GemmParams {
     int tiles_m, tiles_n, raster_group;
     int total_work;    // batch * tiles_m * tiles_n * splits
     int beta;          // 0: overwrite, 1: accumulate into C
-    int epi, beta2;    // fused element-wise tail, see store_row_chunk
+    int epi, beta2;    // fused element-wise tail, see store_row_chunk: 1 ReLU, 2 ReLU gradient, 3 bias row added (E1 = bias[N])
     void* E1;          // epi 1: relu(C) is written here; epi 2: ReLu's input is read here
     void* E2;          // epi 2: ReLu's input gradient, overwritten (beta2 == 0) or accumulated (beta2 == 1)
     void* C;
@@ -564,7 +564,8 @@ __device__ __forceinline__ void store_row_chunk_epi(const GemmParams& p, long lo
     constexpr int VEC = V::N;
     const int colm = out_col(p, col0);
     OutT* dst = reinterpret_cast<OutT*>(p.C) + off + colm;
-    OutT* e1 = reinterpret_cast<OutT*>(p.E1) + off + colm;
+    // EPI 3: E1 is a bias row of N elements, indexed by the logical column alone
+    OutT* e1 = EPI == 3 ? reinterpret_cast<OutT*>(p.E1) + col0 : reinterpret_cast<OutT*>(p.E1) + off + colm;
     OutT* e2 = reinterpret_cast<OutT*>(p.E2) + off + colm;
     bool vec_ok = (col0 + 32 <= p.N) && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0);
     if (EPI >= 1) vec_ok = vec_ok && ((reinterpret_cast<uintptr_t>(e1) & 15) == 0);
@@ -581,9 +582,17 @@ __device__ __forceinline__ void store_row_chunk_epi(const GemmParams& p, long lo
 #pragma unroll
                 for (int i = 0; i < VEC; ++i) c[i] += old[i];
             }
-            const uint4 cw = V::pack(c);
+            uint4 cw = V::pack(c);
+            if (EPI == 3) {  // z = round(round(x * y) + bias): the two roundings of MatrixMultiply followed by Add
+                float b[VEC];
+                V::unpack(cw, c);
+                V::unpack(reinterpret_cast<const uint4*>(e1)[v], b);
+#pragma unroll
+                for (int i = 0; i < VEC; ++i) c[i] += b[i];
+                cw = V::pack(c);
+            }
             reinterpret_cast<uint4*>(dst)[v] = cw;
-            if (EPI != 0) V::unpack(cw, c);  // the stored (rounded) values drive the fused tails
+            if (EPI == 1 || EPI == 2) V::unpack(cw, c);  // the stored (rounded) values drive the fused tails
             if (EPI == 1) {
 #pragma unroll
                 for (int i = 0; i < VEC; ++i) c[i] = c[i] > 0.f ? c[i] : 0.f;
@@ -610,6 +619,7 @@ __device__ __forceinline__ void store_row_chunk_epi(const GemmParams& p, long lo
                 float v = acc[i];
                 if (p.beta) v += epi_to_float(dst[i]);
                 OutT c = epi_from_float<OutT>(v);
+                if (EPI == 3) c = epi_from_float<OutT>(epi_to_float(c) + epi_to_float(e1[i]));
                 dst[i] = c;
                 if (EPI == 1) {
                     e1[i] = epi_to_float(c) > 0.f ? c : epi_from_float<OutT>(0.f);
@@ -627,7 +637,8 @@ template <typename OutT>
 __device__ __forceinline__ void store_row_chunk(const GemmParams& p, long long off, int col0, const float* acc) {
     if (p.epi == 0) store_row_chunk_epi<OutT, 0>(p, off, col0, acc);
     else if (p.epi == 1) store_row_chunk_epi<OutT, 1>(p, off, col0, acc);
-    else store_row_chunk_epi<OutT, 2>(p, off, col0, acc);
+    else if (p.epi == 2) store_row_chunk_epi<OutT, 2>(p, off, col0, acc);
+    else store_row_chunk_epi<OutT, 3>(p, off, col0, acc);
 }
 
 // ------------------------------------------------------------------------------------------------ the kernel

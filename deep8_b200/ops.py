@@ -136,6 +136,35 @@ class Context:
         check(self.lib.d8k_matmul_forward_relu(self.h, dt, _p(x), xb, xr, xc, _p(y), yb, yc, _p(z), _p(a)))
         return z, a
 
+    def matmul_forward_bias(self, x, y, bias, out=None):
+        """z = x * y + bias, bias [1, yc] added to every row (MatrixMultiply followed by Add, one launch)."""
+        dt = _same(x, y, bias)
+        xb, xr, xc, yb, yc = self._mm_dims(x, y)
+        if bias.numel() != yc:
+            raise ValueError("the shape is error")
+        z = out if out is not None else torch.empty((max(xb, yb), xr, yc), device=x.device, dtype=x.dtype)
+        check(self.lib.d8k_matmul_forward_bias(self.h, dt, _p(x), xb, xr, xc, _p(y), yb, yc, _p(bias), _p(z)))
+        return z
+
+    def add_bias(self, x, bias, out=None):
+        """x [..., cols] + bias [cols] broadcast over the leading dimensions (Math::Add for a bias)."""
+        dt = _same(x, bias)
+        cols = x.shape[-1]
+        if bias.numel() != cols:
+            raise ValueError("the shape is error")
+        z = out if out is not None else torch.empty_like(x)
+        check(self.lib.d8k_add_bias(self.h, dt, _p(x), _p(bias), _p(z), x.numel() // cols, cols))
+        return z
+
+    def add_bias_grad(self, dbias, dz):
+        """dbias [cols] += sum of dz [..., cols] over the leading dimensions (Math::AddGradY for a bias)."""
+        dt = _same(dbias, dz)
+        cols = dz.shape[-1]
+        if dbias.numel() != cols:
+            raise ValueError("the shape is error")
+        check(self.lib.d8k_add_bias_grad(self.h, dt, _p(dbias), _p(dz), dz.numel() // cols, cols))
+        return dbias
+
     def matmul_grad_x_relu(self, x, dx, y, dz, h, dh, accumulate_dx=True, accumulate_dh=True):
         """For x = relu(h): dx (+)= dz y^T, then dh (+)= (h > 0 ? dx : 0), in one launch."""
         dt = _same(x, dx, y, dz, h, dh)

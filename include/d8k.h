@@ -105,6 +105,18 @@ D8K_API int d8k_matmul_forward_relu(d8k_ctx* ctx, int dtype, const void* x, int 
 D8K_API int d8k_matmul_grad_x_relu(d8k_ctx* ctx, int dtype, void* dx, int xb, int xr, int xc, const void* y, int yb, int yc, const void* dz,
                            int accumulate_dx, const void* h, void* dh, int accumulate_dh);
 
+/* MatrixMultiplyGPU followed by AddGPU with a bias (deep8/src/math/Add.cu; shapes broadcast from the tail,
+ * deep8/include/utils/ShapeUtils.h:40-55) in one launch: z = x * y + bias, bias one row of yc elements added to every
+ * row of every batch entry, from the accumulator in the epilogue.  Rounded as the two calls would: the product to dtype,
+ * then the sum. */
+D8K_API int d8k_matmul_forward_bias(d8k_ctx* ctx, int dtype, const void* x, int xb, int xr, int xc, const void* y, int yb, int yc,
+                                    const void* bias, void* z);
+/* AddGPU for that bias alone: z[r][c] = x[r][c] + bias[c], r < rows (batch * rows of the operand); z may be x. */
+D8K_API int d8k_add_bias(d8k_ctx* ctx, int dtype, const void* x, const void* bias, void* z, size_t rows, int cols);
+/* AddGradYGPU for that bias (deep8/src/math/Add.cu, the broadcast dimensions are summed): dbias[c] += sum over r < rows of
+ * dz[r][c], added in a fixed order (same bits every run) with fp32 accumulation; uses the context's scratch memory. */
+D8K_API int d8k_add_bias_grad(d8k_ctx* ctx, int dtype, void* dbias, const void* dz, size_t rows, int cols);
+
 /* Conv2d shape helpers: output extent (deep8/src/nodes/Conv2d.cpp:47-63) and DeConv2d's (deep8/src/nodes/DeConv2d.cpp:36-52). */
 D8K_API int d8k_conv2d_out_dim(int in, int filter, int stride, int dilation, int covered);
 D8K_API int d8k_deconv2d_out_dim(int in, int filter, int stride, int covered);

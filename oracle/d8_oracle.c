@@ -342,4 +342,21 @@ D8O_API void D8O_(d8o_axpby)(const D8O_T* x, D8O_T alpha, const D8O_T* y, D8O_T 
     }
 }
 
+/* Math::Add for a bias: x (batch, {rows, cols}) + y (1, {cols}) broadcast over batch and rows
+ * (deep8/src/math/Add.cpp:7-31, 112-146; shapes aligned from the tail, deep8/include/utils/ShapeUtils.h:40-55). */
+D8O_API void D8O_(d8o_add_bias)(const D8O_T* x, const D8O_T* bias, D8O_T* z, size_t rows, size_t cols) {
+    for (size_t r = 0; r < rows; ++r)
+        for (size_t c = 0; c < cols; ++c) z[r * cols + c] = x[r * cols + c] + bias[c];
+}
+
+/* Math::AddGradY for that bias: dbias[c] += sum over batch and rows of dz (deep8/src/math/Add.cpp:165-187, the
+ * broadcast dimensions are summed). */
+D8O_API void D8O_(d8o_add_bias_grad)(D8O_T* dbias, const D8O_T* dz, size_t rows, size_t cols) {
+    for (size_t c = 0; c < cols; ++c) {
+        double acc = 0;
+        for (size_t r = 0; r < rows; ++r) acc += (double)dz[r * cols + c];
+        dbias[c] = (D8O_T)((double)dbias[c] + acc);
+    }
+}
+
 #endif

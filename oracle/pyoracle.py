@@ -138,6 +138,22 @@ class Restated(_Base):
     def threads(self):
         return os.cpu_count() or 1
 
+    def add_bias(self, x, bias):
+        """x [batch, rows, cols] + bias [1, cols] (Math::Add with the bias broadcast), a new array."""
+        dt = self._check(x, bias)
+        z = np.empty_like(x)
+        rows, cols = x.shape[0] * x.shape[1], x.shape[2]
+        getattr(self.lib, "d8o_add_bias_" + _suffix(dt))(_ptr(x), _ptr(bias), _ptr(z), ctypes.c_size_t(rows), ctypes.c_size_t(cols))
+        return z
+
+    def add_bias_grad(self, dz, d0):
+        """d0 [1, cols] + sum of dz [batch, rows, cols] over batch and rows (Math::AddGradY), a new array."""
+        dt = self._check(dz, d0)
+        out = d0.copy()
+        rows, cols = dz.shape[0] * dz.shape[1], dz.shape[2]
+        getattr(self.lib, "d8o_add_bias_grad_" + _suffix(dt))(_ptr(out), _ptr(dz), ctypes.c_size_t(rows), ctypes.c_size_t(cols))
+        return out
+
     def axpby(self, x, alpha, y, beta):
         """x * alpha + y * beta (Math::AXPBY), a new array."""
         dt = self._check(x, y)
@@ -206,6 +222,24 @@ class Reference(_Base):
     def _ok(self, rc):
         if rc != 0:
             raise RuntimeError(self.lib.d8ref_last_error().decode())
+
+    def add_bias(self, x, bias):
+        dt = self._check(x, bias)
+        z = np.empty_like(x)
+        b, r, c = x.shape
+        sz = ctypes.c_size_t
+        self._ok(self.lib.d8ref_add_bias(0, 0 if dt == np.float32 else 1, _ptr(x), sz(b), sz(r), sz(c), _ptr(bias), None, _ptr(z), None))
+        return z
+
+    def add_bias_grad(self, dz, d0):
+        dt = self._check(dz, d0)
+        out = d0.copy()
+        b, r, c = dz.shape
+        sz = ctypes.c_size_t
+        x = np.zeros_like(dz)
+        self._ok(self.lib.d8ref_add_bias(2, 0 if dt == np.float32 else 1, _ptr(x), sz(b), sz(r), sz(c), _ptr(d0), _ptr(out), _ptr(x),
+                                         _ptr(dz)))
+        return out
 
     def axpby(self, x, alpha, y, beta):
         dt = self._check(x, y)

@@ -24,6 +24,7 @@
 #include "math/Conv2d.h"
 #include "math/DeConv2d.h"
 #include "math/AXPBY.h"
+#include "math/Add.h"
 
 #define D8REF_API extern "C" __attribute__((visibility("default")))
 
@@ -165,5 +166,23 @@ D8REF_API int d8ref_axpby(int dtype, const void* x, float alpha, const void* y, 
         View vy(dtype, y, 1, {n});
         View vz(dtype, z, 1, {n});
         Deep8::Math::AXPBY(vx.tensor, alpha, vy.tensor, beta, vz.tensor);
+    });
+}
+
+// Math::Add / Math::AddGradY (deep8/src/math/Add.cpp:7-31, 71-110) for x (batch, {rows, cols}) and a bias y (1, {cols}).
+// which: 0 = z = x + y; 2 = dy += sum of dz over batch and rows.
+D8REF_API int d8ref_add_bias(int which, int dtype, const void* x, size_t batch, size_t rows, size_t cols, const void* y, void* dy, void* z,
+                             const void* dz) {
+    return guarded([&] {
+        View vx(dtype, x, batch, {rows, cols});
+        View vy(dtype, y, 1, {cols});
+        View vz(dtype, z, batch, {rows, cols});
+        if (which == 0) {
+            Deep8::Math::Add(vx.tensor, vy.tensor, vz.tensor);
+        } else {
+            View vdy(dtype, dy, 1, {cols});
+            View vdz(dtype, dz, batch, {rows, cols});
+            Deep8::Math::AddGradY(vx.tensor, vy.tensor, vdy.tensor, vz.tensor, vdz.tensor);
+        }
     });
 }

@@ -428,3 +428,44 @@ def test_deconv_random_geometries_f32(ctx, restated, xs, ws, cov, st, dil):
 def test_deconv_random_geometries_integers_exact_and_f16(ctx, restated, xs, ws, cov, st, dil):
     parity(ctx, restated, "deconv", xs, ws, (cov, st), torch.float32, 0.0, gen="int")
     parity(ctx, restated, "deconv", xs, ws, (cov, st), torch.float16, F16_TOL)
+
+
+# ------------------------------------------------------------------------------------------------ bias (Add after MatrixMultiply)
+@pytest.mark.gpu
+@pytest.mark.parametrize("tdtype", [torch.float32, torch.float16])
+@pytest.mark.parametrize("xs,ys", [((2, 129, 65), (1, 65, 33)), ((1, 512, 256), (1, 256, 384)), ((3, 40, 24), (3, 24, 56)),
+                                   ((1, 2048, 512), (1, 512, 1024))])
+def test_matmul_forward_bias(ctx, restated, tdtype, xs, ys):
+    """One launch equals MatrixMultiply followed by Add bit for bit, and both follow the oracle."""
+    x, y, b = cases.uniform(21, xs), cases.normal(22, ys, 0.25), cases.uniform(23, (1, ys[2]))
+    if tdtype == torch.float16:
+        x, y, b = (a.astype(np.float16).astype(np.float32) for a in (x, y, b))
+    X, Y, B = dev(x, tdtype), dev(y, tdtype), dev(b, tdtype)
+    fused = ctx.matmul_forward_bias(X, Y, B)
+    two = ctx.add_bias(ctx.matmul_forward(X, Y), B)
+    torch.cuda.synchronize()
+    assert torch.equal(fused, two)
+    want = restated.add_bias(restated.matmul_forward(x, y), b)
+    check(ctx, fused, want, F32_TOL if tdtype == torch.float32 else F16_TOL, "z")
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("shape", [(3, 50, 33), (1, 8192, 4096), (2, 1, 7), (1, 100, 1)])
+def test_bias_gradient(ctx, restated, shape):
+    dz, d0 = cases.normal(31, shape), cases.normal(32, (1, shape[2]))
+    want = restated.add_bias_grad(dz, d0)
+    DB = dev(d0)
+    ctx.add_bias_grad(DB, dev(dz))
+    check(ctx, DB, want, F32_TOL, "dbias")
+    DB2 = dev(d0)
+    ctx.add_bias_grad(DB2, dev(dz))
+    torch.cuda.synchronize()
+    assert torch.equal(DB, DB2)  # fixed order of addition: the same bits every run
+    dzi, d0i = cases.small_ints(33, shape), cases.small_ints(34, (1, shape[2]))
+    DBi = dev(d0i)
+    ctx.add_bias_grad(DBi, dev(dzi))
+    check(ctx, DBi, restated.add_bias_grad(dzi, d0i), 0.0, "dbias on integers")
+    dzh = dz.astype(np.float16).astype(np.float32)
+    DBh = dev(d0, torch.float16)
+    ctx.add_bias_grad(DBh, dev(dzh, torch.float16))
+    check(ctx, DBh, restated.add_bias_grad(dzh, d0.astype(np.float16).astype(np.float32)), F16_TOL, "dbias f16")

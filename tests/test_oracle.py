@@ -168,3 +168,16 @@ def test_sgd_coefficients_host_side_agrees_with_the_oracle():
     from oracle import pyoracle
     for lr, decay in ((0.01, 0.0005), (0.5, 0.0), (1e-3, 0.1), (0.3, 0.7)):
         assert sgd_coefficients(lr, decay) == pyoracle.sgd_coefficients(lr, decay)
+
+
+def test_bias_add_and_its_gradient_restated_equal_reference(restated, reference):
+    """Math::Add / Math::AddGradY with a bias (1, {cols}) broadcast over batch and rows."""
+    rng = np.random.default_rng(5)
+    for shape in ((3, 50, 33), (1, 7, 128), (2, 1, 1)):
+        x = rng.standard_normal(shape).astype(np.float32)
+        b = rng.standard_normal((1, shape[2])).astype(np.float32)
+        assert np.array_equal(restated.add_bias(x, b), reference.add_bias(x, b))
+        xi = rng.integers(0, 50, shape).astype(np.float32)  # integer data: any summation order gives the same bits
+        assert np.array_equal(restated.add_bias_grad(xi, b * 0 + 3), reference.add_bias_grad(xi, b * 0 + 3))
+        got, want = restated.add_bias_grad(x, b), reference.add_bias_grad(x, b)
+        assert np.abs(got - want).max() <= 1e-5 * max(np.abs(want).max(), 1e-30)
