@@ -500,27 +500,40 @@ def run_small_config(args):
         x, w = cases.uniform(7, (16, 14, 14, 256)), cases.normal(8, (128, 4, 4, 256), 1.0 / 64)
         dz = cases.normal(9, (16, 27, 27, 128))
         kind, meta, flop = "deconv", (True, (2, 2)), 3 * 2.0 * 3136 * 256 * 2048
-    X, W, DZ = (torch.from_numpy(a).to(dev) for a in (x, w, dz))
+    tdtype, tol, label = torch.float32, 1e-5, "f32 (3xTF32)"
+    if args.half:  # the same operator on fp16 storage (fp32 accumulation); the oracle sees the rounded inputs
+        tdtype, tol, label = torch.float16, 2e-2, "f16 (f32 accumulate)"
+        x, w, dz = (a.astype("float16").astype("float32") for a in (x, w, dz))
+    X, W, DZ = (torch.from_numpy(a).to(dev).to(tdtype) for a in (x, w, dz))
     DX, DW = torch.zeros_like(X), torch.zeros_like(W)
+
+    paths = {}  # which kernel variant each contraction took (d8k_last_kernel)
 
     def step():
         ctx.zero(DX)
         ctx.zero(DW)
         if kind == "matmul":
             z = ctx.matmul_forward(X, W, out=Z)
+            paths["forward"] = ctx.last_kernel()
             ctx.matmul_grad_x(X, DX, W, DZ)
+            paths["grad_x"] = ctx.last_kernel()
             ctx.matmul_grad_y(X, W, DW, DZ)
         elif kind == "conv":
             z = ctx.conv2d_forward(X, W, *meta, out=Z)
+            paths["forward"] = ctx.last_kernel()
             ctx.conv2d_grad_x(X, DX, W, DZ, *meta)
+            paths["grad_x"] = ctx.last_kernel()
             ctx.conv2d_grad_y(X, W, DW, DZ, *meta)
         else:
             z = ctx.deconv2d_forward(X, W, *meta, out=Z)
+            paths["forward"] = ctx.last_kernel()
             ctx.deconv2d_grad_x(X, DX, W, DZ, *meta)
+            paths["grad_x"] = ctx.last_kernel()
             ctx.deconv2d_grad_y(X, W, DW, DZ, *meta)
+        paths["grad_y"] = ctx.last_kernel()
         return z
 
-    Z = torch.empty(tuple(dz.shape), device=dev)
+    Z = torch.empty(tuple(dz.shape), device=dev, dtype=tdtype)
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)  # larger than the 126 MB L2
     for _ in range(max(args.warmup, 3)):
         step()
@@ -548,11 +561,11 @@ def run_small_config(args):
         return impl.deconv2d_forward(x, w, *meta), impl.deconv2d_grad_x(x, w, dz, *meta), impl.deconv2d_grad_y(x, w, dz, *meta)
 
     if args.no_cpu:
-        print(json.dumps({"report": "config %d" % n, "workload": name, "ms_per_step": ms, "tflops": flop / ms / 1e9,
-                          "steps": args.steps, "cpu": None}), flush=True)
+        print(json.dumps({"report": "config %d" % n, "workload": name, "dtype": label, "ms_per_step": ms, "tflops": flop / ms / 1e9,
+                          "steps": args.steps, "kernels": paths, "cpu": None}), flush=True)
         return
     want = cpu(oracle)
-    got = (Z.cpu().numpy(), DX.cpu().numpy(), DW.cpu().numpy())
+    got = (Z.float().cpu().numpy(), DX.float().cpu().numpy(), DW.float().cpu().numpy())
     err = max(cases.rel_max(g, r) for g, r in zip(got, want))
     cpu(ref)
     cpu_times = []
@@ -561,9 +574,11 @@ def run_small_config(args):
         cpu(ref)
         cpu_times.append(time.perf_counter() - t0)
     cpu_ms = min(cpu_times) * 1e3
-    line = {"report": "config %d" % n, "workload": name, "dtype": "f32 (3xTF32)", "ms_per_step": ms, "tflops": flop / ms / 1e9,
-            "frac_of_tf32_peak_over_3": flop / ms / 1e9 / (1100.0 / 3), "max_rel_err_vs_oracle": err, "tolerance": 1e-5,
-            "l2": "flushed between iterations (256 MiB write)", "steps": args.steps,
+    line = {"report": "config %d" % n, "workload": name.replace("fp32", "fp16") if args.half else name, "dtype": label, "ms_per_step": ms,
+            "tflops": flop / ms / 1e9,
+            ("frac_of_fp16_peak" if args.half else "frac_of_tf32_peak_over_3"): flop / ms / 1e9 / (2250.0 if args.half else 1100.0 / 3),
+            "max_rel_err_vs_oracle": err, "tolerance": tol,
+            "l2": "flushed between iterations (256 MiB write)", "steps": args.steps, "kernels": paths,
             "cpu": {"ms": cpu_ms, "kind": ref.kind, "threads": 1 if kind == "matmul" else ref.threads(),
                     "gflops": flop / cpu_ms / 1e6}}
     print(json.dumps(line), flush=True)
@@ -578,6 +593,7 @@ def main():
     ap.add_argument("--config", type=int, default=5, choices=[1, 2, 3, 4, 5], help="BASELINE configuration; 5 (default) is the benchmark "
                     "line, 1-4 print an auxiliary fp32 report for one operator")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--half", action="store_true", help="with --config: run the configuration's operator on fp16 storage")
     ap.add_argument("--sgd", action="store_true",
                     help="add the reference's SGD step on W1, W2 to every step (not part of the metric's forward + backward): "
                          "after the backward pass on one GPU, inside the gradient exchange's sum kernel on several")
