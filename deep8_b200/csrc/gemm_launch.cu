@@ -243,7 +243,12 @@ Plan make_plan(const Ctx* ctx, const GemmProblem& g, size_t scratch_limit) {
                    !env_int("D8K_F32_TMA", 1)))
         pl.tma = false;
     if (pl.f32) pl.bn = 64;  // the 64-column fp32 kernels run two groups of helper warps (see GemmCfg::LOADER_GROUPS)
-    else if (pl.tma) pl.bn = g.N > 128 ? 256 : 128;
+    else if (pl.tma) {
+        pl.bn = g.N > 128 ? 256 : 128;
+        // 256 columns only when such tiles alone give every SM one: a small problem prefers twice as many narrower tiles
+        const long long tiles256 = static_cast<long long>(g.batch) * ((g.M + kBM - 1) / kBM) * ((g.N + 255) / 256);
+        if (pl.bn == 256 && tiles256 < ctx->num_sms) pl.bn = 128;
+    }
     else pl.bn = g.N > 64 ? 128 : 64;
     int forced_bn = env_int("D8K_BN", 0);
     if (forced_bn == 64 && !pl.tma) pl.bn = 64;
@@ -271,7 +276,7 @@ Plan make_plan(const Ctx* ctx, const GemmProblem& g, size_t scratch_limit) {
     pl.scratch = pl.splits > 1 ? per_split * pl.splits : 0;
     // CTA pairs on 256 x 256 tiles once the output alone fills the machine (74 pairs) and nothing is split
     int tiles256 = g.batch * ((g.M + 255) / 256) * ((g.N + 255) / 256);
-    pl.pair = pl.tma && pl.a_tma == kTmaTiled && pl.b_tma == kTmaTiled && pl.bn == 256 && pl.splits == 1 && tiles256 * 2 >= ctx->num_sms && env_int("D8K_PAIR", 1) != 0 &&
+    pl.pair = pl.tma && pl.a_tma == kTmaTiled && pl.b_tma == kTmaTiled && !g.out.rows_on && !g.out.cols_on && pl.bn == 256 && pl.splits == 1 && tiles256 * 2 >= ctx->num_sms && env_int("D8K_PAIR", 1) != 0 &&
               g.K % 64 == 0 && (!g.a.mn || g.M % 64 == 0) && (!g.b.mn || g.N % 64 == 0);
     if (pl.pair) {
         pl.tiles_m = (g.M + 255) / 256;

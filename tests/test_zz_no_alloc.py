@@ -48,13 +48,20 @@ def test_static_scratch_matches_context_entry_point(ctx, dtype, tol):
         assert cases.rel_max(got.float().cpu().numpy(), exact) <= tol
 
 
-def test_static_scratch_rejects_oversize():
+def test_static_scratch_rejects_oversize(monkeypatch):
     from deep8_b200 import _lib
     lib = _lib.load()
-    M, N, K = 1152, 2048, 8192   # 72 tiles of 128x256 in two splits: 18 MiB of partial tiles, over the 16 MiB array
+    # The launcher's own split choice never needs more than 148 partial tiles (9.25 MiB).  D8K_SPLITS asks for more:
+    # 144 tiles of 128x128 in 4 splits are 36 MiB of partial tiles, over the 16 MiB array.
+    monkeypatch.setenv("D8K_SPLITS", "4")
+    M, N, K = 1152, 2048, 8192
     A = torch.zeros(M, K, device=DEV, dtype=torch.float16)
     B = torch.zeros(N, K, device=DEV, dtype=torch.float16)
     C = torch.zeros(M, N, device=DEV, dtype=torch.float16)
     rc = lib.d8k_gemm_static(_lib.F16, 0, 1, M, N, K, _ptr(A), K, _ptr(B), K, _ptr(C), N, 0, None)
     assert rc == 1
     assert "static maximum" in lib.d8k_last_error().decode()
+    monkeypatch.delenv("D8K_SPLITS")
+    rc = lib.d8k_gemm_static(_lib.F16, 0, 1, M, N, K, _ptr(A), K, _ptr(B), K, _ptr(C), N, 0, None)  # unsplit: fits
+    assert rc == 0, lib.d8k_last_error().decode()
+    torch.cuda.synchronize()
