@@ -292,6 +292,29 @@ class MlpStep:
             c.axpby(self.dW1, alpha, self.W1, beta)
 
 
+def bind_to_gpu_numa_node(torch, index):
+    """Run this process (and place the pinned host buffers it allocates later) on the NUMA node the GPU hangs off: with
+    several ranks feeding their GPUs from host memory every step, buffers on the wrong socket halve the copy rate.
+    Returns the node, or None when the topology is not visible (then nothing changes)."""
+    try:
+        prop = torch.cuda.get_device_properties(index)
+        bdf = "%04x:%02x:%02x.0" % (prop.pci_domain_id, prop.pci_bus_id, prop.pci_device_id)
+        node = int(open("/sys/bus/pci/devices/%s/numa_node" % bdf).read())
+        if node < 0:
+            return None
+        cpus = set()
+        for part in open("/sys/devices/system/node/node%d/cpulist" % node).read().strip().split(","):
+            lo, _, hi = part.partition("-")
+            cpus.update(range(int(lo), int(hi or lo) + 1))
+        cpus &= os.sched_getaffinity(0)
+        if not cpus:
+            return None
+        os.sched_setaffinity(0, cpus)
+        return node
+    except (OSError, ValueError, AttributeError):
+        return None
+
+
 def run_gpu_arm(args):
     import torch
     import deep8_b200
@@ -303,6 +326,7 @@ def run_gpu_arm(args):
         raise SystemExit("--gpus %d but WORLD_SIZE=%d: launch with torch.distributed.run --nproc-per-node %d" % (args.gpus, world, args.gpus))
     torch.cuda.set_device(local_rank)
     device = torch.device("cuda", local_rank)
+    numa_node = bind_to_gpu_numa_node(torch, local_rank) if world > 1 else None
     dist = None
     if world > 1:
         import torch.distributed as dist
@@ -450,7 +474,7 @@ def run_gpu_arm(args):
                          "gemm_share_of_step": sum(gemm_ms) / (ms_step * args.steps)},
             "e2e": {"value": FLOP_PER_STEP * world / (e2e_ms * 1e-3) / 1e12, "unit": UNIT, "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms, "steps": e2e_steps,
-                    "overlap": "copies on side streams, double-buffered inputs and outputs"},
+                    "overlap": "copies on side streams, double-buffered inputs and outputs", "host_numa_node_rank0": numa_node},
             "gpu_launches": launches, "clocks": clocks,
         }
         if world == 1 and not args.no_cpu:
