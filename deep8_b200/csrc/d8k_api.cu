@@ -334,27 +334,45 @@ __global__ void add_bias_kernel(const T* __restrict__ x, const T* __restrict__ b
     }
 }
 
-// Column sums for Math::AddGradY of a bias, in two fixed-order steps: CTA (strip, slice) adds its slice of rows for 32
-// columns into partial[slice][col] (rows in order, fp32), then the last step adds the slices in order and accumulates
-// into dbias.  Every run adds in the same order.
-template <typename T>
+// Column sums for Math::AddGradY of a bias, in two fixed-order steps: CTA (strip, slice) adds its slice of rows for one
+// strip of columns into partial[slice][col] (rows in order, fp32), then the last step adds the slices in order and
+// accumulates into dbias.  Every run adds in the same order.  W columns per thread: 16-byte loads (W = 16 / sizeof(T))
+// when rows and pitch allow, else one column per thread.
+template <typename T, int W>
 __global__ void bias_grad_partial_kernel(const T* __restrict__ dz, float* __restrict__ partial, size_t rows, int cols, int rows_per_slice) {
-    const int col = blockIdx.x * 32 + (threadIdx.x & 31);
+    const int lane = threadIdx.x & 31;
+    const int col = (blockIdx.x * 32 + lane) * W;
     const int sub = threadIdx.x >> 5;  // 8 warps share the slice's rows; their sums meet in shared memory in warp order
-    __shared__ float part[8][32];
+    __shared__ float part[8][32 * W];
     const size_t r0 = static_cast<size_t>(blockIdx.y) * rows_per_slice;
     size_t r1 = r0 + rows_per_slice;
     if (r1 > rows) r1 = rows;
-    float acc = 0.f;
-    if (col < cols)
-        for (size_t r = r0 + sub; r < r1; r += 8) acc += to_f(dz[r * cols + col]);
-    part[sub][threadIdx.x & 31] = acc;
+    float acc[W];
+#pragma unroll
+    for (int k = 0; k < W; ++k) acc[k] = 0.f;
+    if (col < cols) {
+        for (size_t r = r0 + sub; r < r1; r += 8) {
+            if constexpr (W == 1) {
+                acc[0] += to_f(dz[r * cols + col]);
+            } else {
+                const uint4 v = __ldcs(reinterpret_cast<const uint4*>(dz + r * cols + col));
+                const T* e = reinterpret_cast<const T*>(&v);
+#pragma unroll
+                for (int k = 0; k < W; ++k) acc[k] += to_f(e[k]);
+            }
+        }
+    }
+#pragma unroll
+    for (int k = 0; k < W; ++k) part[sub][lane * W + k] = acc[k];
     __syncthreads();
     if (sub == 0 && col < cols) {
-        float t = 0.f;
 #pragma unroll
-        for (int w = 0; w < 8; ++w) t += part[w][threadIdx.x];
-        partial[static_cast<size_t>(blockIdx.y) * cols + col] = t;
+        for (int k = 0; k < W; ++k) {
+            float t = 0.f;
+#pragma unroll
+            for (int w = 0; w < 8; ++w) t += part[w][lane * W + k];
+            partial[static_cast<size_t>(blockIdx.y) * cols + col + k] = t;
+        }
     }
 }
 template <typename T>
@@ -600,8 +618,12 @@ int d8k_add_bias_grad(d8k_ctx* ctx, int dtype, void* dbias, const void* dz, size
     if (int rc = check_dtype(dtype)) return rc;
     if (rows == 0 || cols <= 0) return cols < 0 ? fail(D8K_ERR_ARGUMENT, "the shape is error") : 0;
     if (!dbias || !dz) return fail(D8K_ERR_ARGUMENT, "add_bias_grad: null pointer");
+    // 16-byte loads when every row starts on a 16-byte boundary and holds whole pieces
+    const int per = dtype == D8K_F32 ? 4 : 8;
+    const bool wide = (reinterpret_cast<uintptr_t>(dz) & 15) == 0 && cols % per == 0;
+    const int strip_cols = 32 * (wide ? per : 1);
     // enough slices to occupy the GPU, bounded by the context's scratch memory (slices * cols floats)
-    const int strips = (cols + 31) / 32;
+    const int strips = (cols + strip_cols - 1) / strip_cols;
     int slices = (ctx->num_sms * 4 + strips - 1) / strips;
     const size_t max_slices = ctx->scratch_bytes / (static_cast<size_t>(cols) * sizeof(float));
     if (max_slices < 1) return fail(D8K_ERR_ARGUMENT, "add_bias_grad: the context's scratch memory is smaller than one row of floats");
@@ -612,10 +634,14 @@ int d8k_add_bias_grad(d8k_ctx* ctx, int dtype, void* dbias, const void* dz, size
     slices = static_cast<int>((rows + rows_per_slice - 1) / rows_per_slice);
     dim3 grid(strips, slices);
     if (dtype == D8K_F32) {
-        bias_grad_partial_kernel<float><<<grid, 256, 0, ctx->stream>>>(static_cast<const float*>(dz), ctx->scratch, rows, cols, rows_per_slice);
+        const float* src = static_cast<const float*>(dz);
+        if (wide) bias_grad_partial_kernel<float, 4><<<grid, 256, 0, ctx->stream>>>(src, ctx->scratch, rows, cols, rows_per_slice);
+        else bias_grad_partial_kernel<float, 1><<<grid, 256, 0, ctx->stream>>>(src, ctx->scratch, rows, cols, rows_per_slice);
         bias_grad_final_kernel<float><<<(cols + 255) / 256, 256, 0, ctx->stream>>>(static_cast<float*>(dbias), ctx->scratch, slices, cols);
     } else {
-        bias_grad_partial_kernel<__half><<<grid, 256, 0, ctx->stream>>>(static_cast<const __half*>(dz), ctx->scratch, rows, cols, rows_per_slice);
+        const __half* src = static_cast<const __half*>(dz);
+        if (wide) bias_grad_partial_kernel<__half, 8><<<grid, 256, 0, ctx->stream>>>(src, ctx->scratch, rows, cols, rows_per_slice);
+        else bias_grad_partial_kernel<__half, 1><<<grid, 256, 0, ctx->stream>>>(src, ctx->scratch, rows, cols, rows_per_slice);
         bias_grad_final_kernel<__half><<<(cols + 255) / 256, 256, 0, ctx->stream>>>(static_cast<__half*>(dbias), ctx->scratch, slices, cols);
     }
     D8K_CUDA(cudaGetLastError());
