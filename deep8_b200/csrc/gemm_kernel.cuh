@@ -270,14 +270,6 @@ __device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity, volatile
     return true;
 }
 
-// One lane waits, the warp learns the outcome: 32 lanes polling the same barrier buy nothing.
-__device__ __forceinline__ bool warp_wait_bar(int lane, uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code,
-                                              unsigned backoff_ns = 0) {
-    int ok = 1;
-    if (lane == 0) ok = wait_bar(bar, parity, abort_flag, status, code, backoff_ns) ? 1 : 0;
-    return __shfl_sync(0xffffffffu, ok, 0) != 0;
-}
-
 // ------------------------------------------------------------------------------------------------ gather loaders
 // Column part of a virtual-matrix address: which tap and channel, and the tap's contribution to the pixel numerators.
 struct ColCtx {

@@ -80,10 +80,6 @@ __device__ __forceinline__ void tma_load_im2col_4d(uint32_t dst, const void* tma
         "h"(static_cast<unsigned short>(off_h))
         : "memory");
 }
-// bring one box of a tensor map into L2 without touching shared memory
-__device__ __forceinline__ void tma_prefetch_l2_3d(const void* tmap, int x, int y, int z) {
-    asm volatile("cp.async.bulk.prefetch.tensor.3d.L2.global [%0, {%1, %2, %3}];" ::"l"(tmap), "r"(x), "r"(y), "r"(z) : "memory");
-}
 __device__ __forceinline__ void tma_prefetch_desc(const void* tmap) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(tmap) : "memory");
 }
