@@ -344,7 +344,9 @@ def run_gpu_arm(args):
         side = torch.cuda.Stream(device=device)
         ctx_side = deep8_b200.Context(local_rank, scratch_bytes=1 << 20)
         ctx_side.use_stream(side)
-        exchange = lambda numel, rows: PeerAllReduce(ctx, ctx_side, side, numel, torch.float16, device, rows=rows, with_weights=args.sgd)
+        # waits between ranks give up after 20 s here (first steps include module loading on every rank); the default is 2 s
+        exchange = lambda numel, rows: PeerAllReduce(ctx, ctx_side, side, numel, torch.float16, device, rows=rows, with_weights=args.sgd,
+                                                     timeout_ms=20000.0)
     mlp = MlpStep(ctx, torch, device, rank, fused=not args.unfused, exchange=exchange,
                   scatter=exchange is not None and mode == "fused" and not args.unfused, sgd=args.sgd)
 
