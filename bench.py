@@ -487,9 +487,9 @@ def run_gpu_arm(args):
         dist.destroy_process_group()
 
 
-# DRAM bytes (read + write) of one contraction launch of this workload: mean of the three launches captured with ncu
+# DRAM bytes (read + write) of one contraction launch of this workload: mean of the three launches of the default step captured with ncu
 # (profiles/d8k_gemm_pair_kernel_f16_mlp_config5.md); algorithmic bytes are 0.47e9.
-TRAFFIC_BYTES_PER_LAUNCH = 1.10e9
+TRAFFIC_BYTES_PER_LAUNCH = 1.28e9
 
 
 # ------------------------------------------------------------------------------------------------ configs 1-4 (fp32)

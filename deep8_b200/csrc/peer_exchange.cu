@@ -173,7 +173,8 @@ template <typename T>
 void launch_sum(const Ctx* ctx, void* out, const SrcList& srcs, int nsrc, size_t count, bool vec, void* weights, float alpha, float beta) {
     constexpr int V = 16 / sizeof(T);
     size_t blocks = (count / V + 255) / 256;
-    size_t cap = static_cast<size_t>(ctx->num_sms) * 4;
+    // enough 16-byte loads in flight to cover HBM latency: each thread has nsrc (+1 with weights) per step
+    size_t cap = static_cast<size_t>(ctx->num_sms) * (nsrc <= 2 ? 8 : 4);
     if (blocks > cap) blocks = cap;
     if (blocks < 1) blocks = 1;
     dim3 grid(static_cast<unsigned>(blocks));
