@@ -517,6 +517,48 @@ void ReLuGrad(const Tensor& x, Tensor& dx, const Tensor& y, const Tensor& dy) {
                          "the shape or type is error");
     d8kCheck(d8k_relu_backward(gpuOf(x)->kernels, d8kType(x), x.raw(), dx.raw(), dy.raw(), dx.size()));
 }
+namespace {
+// the two shapes this path adds: 0 = equal shapes, 1 = y is a bias (1, {cols}) over x's last dimension
+int addKind(const Tensor& x, const Tensor& y) {
+    if (x.shape == y.shape) return 0;
+    if (1 == y.batch() && 1 == y.nDims() && x.nDims() >= 1 && x.dim(x.nDims() - 1) == y.dim(0)) return 1;
+    DEEP8_RUNTIME_ERROR("only equal shapes or a bias over the last dimension can be added on this path");
+}
+}  // namespace
+
+void Add(const Tensor& x, const Tensor& y, Tensor& z) {
+    DEEP8_ARGUMENT_CHECK(x.elementType == y.elementType && x.elementType == z.elementType, "the param data type must be same");
+    DEEP8_ARGUMENT_CHECK(x.shape == z.shape, "the shape is error");
+    if (0 == addKind(x, y)) {
+        const void* src[2] = {x.raw(), y.raw()};
+        d8kCheck(d8k_sum_shards(gpuOf(x)->kernels, d8kType(x), z.raw(), src, 2, x.size()));
+    } else {
+        d8kCheck(d8k_add_bias(gpuOf(x)->kernels, d8kType(x), x.raw(), y.raw(), z.raw(), x.size() / y.size(), (int)y.size()));
+    }
+}
+void AddGradX(const Tensor& x, Tensor& dx, const Tensor& y, const Tensor& z, const Tensor& dz) {
+    DEEP8_ARGUMENT_CHECK(x.shape == dx.shape && z.shape == dz.shape && x.shape == z.shape, "the shape is error");
+    DEEP8_ARGUMENT_CHECK(x.elementType == dx.elementType && x.elementType == dz.elementType, "the param data type must be same");
+    addKind(x, y);
+    const void* src[2] = {dx.raw(), dz.raw()};  // dx += dz
+    d8kCheck(d8k_sum_shards(gpuOf(x)->kernels, d8kType(x), dx.raw(), src, 2, dx.size()));
+}
+void AddGradY(const Tensor& x, const Tensor& y, Tensor& dy, const Tensor& z, const Tensor& dz) {
+    DEEP8_ARGUMENT_CHECK(y.shape == dy.shape && z.shape == dz.shape && x.shape == z.shape, "the shape is error");
+    DEEP8_ARGUMENT_CHECK(x.elementType == dy.elementType && x.elementType == dz.elementType, "the param data type must be same");
+    if (0 == addKind(x, y)) {
+        const void* src[2] = {dy.raw(), dz.raw()};
+        d8kCheck(d8k_sum_shards(gpuOf(x)->kernels, d8kType(x), dy.raw(), src, 2, dy.size()));
+    } else {
+        d8kCheck(d8k_add_bias_grad(gpuOf(x)->kernels, d8kType(x), dy.raw(), dz.raw(), dz.size() / dy.size(), (int)dy.size()));
+    }
+}
+void AXPBY(const Tensor& x, float alpha, const Tensor& y, float beta, Tensor& z) {
+    DEEP8_ARGUMENT_CHECK(x.elementType == y.elementType && x.elementType == z.elementType, "the param data type must be same");
+    DEEP8_ARGUMENT_CHECK(x.shape.size() == y.shape.size() && x.shape.size() == z.shape.size(), "the param shape size must be same");
+    DEEP8_ARGUMENT_CHECK(y.raw() == z.raw(), "on this path AXPBY updates y in place (z must be y), as the trainers call it");
+    d8kCheck(d8k_axpby(gpuOf(x)->kernels, d8kType(x), x.raw(), alpha, z.raw(), beta, x.size()));
+}
 void Constant(Tensor& x, float scalar) {
     DEEP8_ARGUMENT_CHECK(0.f == scalar, "only the constant 0 is supported on this path");
     d8kCheck(d8k_zero(gpuOf(x)->kernels, x.raw(), x.byteCount()));
@@ -746,6 +788,22 @@ void DeConv2d::backward(const std::vector<const Tensor*>& in, const Tensor* out,
     }
 }
 
+// ---- Add (deep8/src/nodes/Add.cpp): output shape = x's; y equal to it or a bias over the last dimension
+Add::Add(std::vector<Node*>& in) : Function(in) {}
+Shape Add::checkShape(std::vector<Shape>& s) {
+    DEEP8_ARGUMENT_CHECK(2 == s.size(), "the input count must be 2");
+    const Shape &x = s[0], &y = s[1];
+    bool bias = 1 == y.batch && 1 == y.nDims && x.nDims >= 1 && x.dim(x.nDims - 1) == y.dim(0);
+    DEEP8_ARGUMENT_CHECK(x == y || bias, "the Shape can not Broadcast");
+    return x;
+}
+void Add::forward(const std::vector<const Tensor*>& in, Tensor* out) { Math::Add(*in[0], *in[1], *out); }
+void Add::backward(const std::vector<const Tensor*>& in, const Tensor* out, const Tensor* dOut, size_t index, Tensor* dIn) {
+    if (0 == index) Math::AddGradX(*in[0], *dIn, *in[1], *out, *dOut);
+    else if (1 == index) Math::AddGradY(*in[0], *in[1], *dIn, *out, *dOut);
+    else DEEP8_RUNTIME_ERROR("the index is error");
+}
+
 // ---- ReLu (deep8/src/nodes/ReLu.cpp)
 ReLu::ReLu(std::vector<Node*>& in) : Function(in) {}
 Shape ReLu::checkShape(std::vector<Shape>& s) {
@@ -941,6 +999,39 @@ Variable& Variable::deConv2d(Variable& filter, bool covered, int sY, int sX) {
 Variable& Variable::relu() {
     std::vector<Node*> in = {this};
     return *executor->addFunction(new ReLu(in));
+}
+
+Variable& Variable::add(Variable& y) {
+    std::vector<Node*> in = {this, &y};
+    return *executor->addFunction(new Add(in));
+}
+Variable& operator+(Variable& x, Variable& y) { return x.add(y); }
+Variable& add(Variable& x, Variable& y) { return x.add(y); }
+
+// ================================================================================================ trainer
+// deep8/src/trainer/{LearningRateIterator,ConstantLearningRateIterator,Trainer,SGDTrainer}.cpp
+float LearningRateIterator::next(int64_t) { DEEP8_RUNTIME_ERROR("can not call this function in LearningRateIterator"); }
+ConstantLearningRateIterator::ConstantLearningRateIterator(float lr) : learningRate(lr) {}
+float ConstantLearningRateIterator::next(int64_t) { return learningRate; }
+
+Trainer::Trainer(LearningRateIterator* lr, float decay) : steps(0), learningRate(lr), weightDecay(decay) {}
+void Trainer::update(Executor*, Variable*, float, float, int64_t) { DEEP8_RUNTIME_ERROR("can not call this function in trainer"); }
+void Trainer::train(Executor* executor, std::vector<Variable*> parameters) {
+    if (parameters.empty()) return;
+    float lr = learningRate->next(steps);
+    for (auto parameter : parameters) {
+        if (!parameter->updateGradient) continue;
+        this->update(executor, parameter, lr, this->weightDecay, steps);
+    }
+    steps++;
+}
+void Trainer::train(Executor* executor) { train(executor, executor->trainableParameters()); }
+
+SGDTrainer::SGDTrainer(LearningRateIterator* lr, float decay) : Trainer(lr, decay) {}
+void SGDTrainer::update(Executor*, Variable* parameter, float learningRate, float weightDecay, int64_t) {
+    float alpha = -1 * learningRate;
+    float beta = (1.0 - learningRate * weightDecay);  // the reference's mix: float product, double difference (SGDTrainer.cpp:13-14)
+    Math::AXPBY(parameter->gradient, alpha, parameter->value, beta, parameter->value);
 }
 
 Variable& operator*(Variable& x, Variable& y) { return x.matrixMultiply(y); }

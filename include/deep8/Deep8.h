@@ -293,6 +293,14 @@ DEEP8_API void DeConv2dGradYGPU(const Tensor& x, const Tensor& y, Tensor& dy, co
 DEEP8_API void ReLu(const Tensor& x, Tensor& y);
 DEEP8_API void ReLuGrad(const Tensor& x, Tensor& dx, const Tensor& y, const Tensor& dy);
 DEEP8_API void Constant(Tensor& x, float scalar);  // only 0 is supported: what zeroGradient needs
+
+// Math::Add (deep8/src/math/Add.cpp:7-110) for the two cases of the path: equal shapes, and y a bias of shape (1, {cols})
+// added to every row of x (any batch, last dimension cols); other broadcasts throw std::runtime_error.
+DEEP8_API void Add(const Tensor& x, const Tensor& y, Tensor& z);
+DEEP8_API void AddGradX(const Tensor& x, Tensor& dx, const Tensor& y, const Tensor& z, const Tensor& dz);
+DEEP8_API void AddGradY(const Tensor& x, const Tensor& y, Tensor& dy, const Tensor& z, const Tensor& dz);
+// Math::AXPBY (deep8/src/math/AXPBY.cpp:6-20) with z == y, which is how every trainer calls it: y = x * alpha + y * beta
+DEEP8_API void AXPBY(const Tensor& x, float alpha, const Tensor& y, float beta, Tensor& z);
 }  // namespace Math
 
 // ------------------------------------------------------------------------------------------------ graph nodes
@@ -364,9 +372,10 @@ public:
     Variable& conv2d(Variable& filter, bool covered = true, int strideY = 1, int strideX = 1, int dilationY = 1, int dilationX = 1);
     Variable& deConv2d(Variable& filter, bool covered = false, int strideY = 1, int strideX = 1);
     Variable& relu();
+    Variable& add(Variable& y);
 };
 
-enum class FunctionType { Unkown = 0, Conv2d, DeConv2d, MatrixMultiply, ReLu };
+enum class FunctionType { Unkown = 0, Add, Conv2d, DeConv2d, MatrixMultiply, ReLu };
 
 class DEEP8_API Function : public Node {
 protected:
@@ -417,6 +426,16 @@ public:
 class DEEP8_API ReLu : public Function {
 public:
     explicit ReLu(std::vector<Node*>& inputs);
+    Shape checkShape(std::vector<Shape>& inputShapes) override;
+    void forward(const std::vector<const Tensor*>& inputs, Tensor* output) override;
+    void backward(const std::vector<const Tensor*>& inputs, const Tensor* output, const Tensor* outputGradient, size_t index,
+                  Tensor* iGradient) override;
+};
+
+// deep8/include/nodes/Add.h, deep8/src/nodes/Add.cpp: z = x + y with the shapes Math::Add accepts here
+class DEEP8_API Add : public Function {
+public:
+    explicit Add(std::vector<Node*>& inputs);
     Shape checkShape(std::vector<Shape>& inputShapes) override;
     void forward(const std::vector<const Tensor*>& inputs, Tensor* output) override;
     void backward(const std::vector<const Tensor*>& inputs, const Tensor* output, const Tensor* outputGradient, size_t index,
@@ -478,6 +497,40 @@ DEEP8_API Variable& matrixMultiply(Variable& x, Variable& y);
 DEEP8_API Variable& conv2d(Variable& x, Variable& filter, bool covered = true, int strideY = 1, int strideX = 1, int dilationY = 1, int dilationX = 1);
 DEEP8_API Variable& deConv2d(Variable& x, Variable& filter, bool covered = false, int strideY = 1, int strideX = 1);
 DEEP8_API Variable& relu(Variable& x);
+DEEP8_API Variable& operator+(Variable& x, Variable& y);
+DEEP8_API Variable& add(Variable& x, Variable& y);
+
+// ------------------------------------------------------------------------------------------------ trainer (SGD)
+// deep8/include/trainer/{LearningRateIterator,ConstantLearningRateIterator,Trainer,SGDTrainer}.h
+class DEEP8_API LearningRateIterator {
+public:
+    virtual ~LearningRateIterator() = default;
+    virtual float next(int64_t steps);
+};
+class DEEP8_API ConstantLearningRateIterator : public LearningRateIterator {
+public:
+    float learningRate;
+    explicit ConstantLearningRateIterator(float lr = 0.01);
+    float next(int64_t steps) override;
+};
+class DEEP8_API Trainer {
+protected:
+    int64_t steps;
+    LearningRateIterator* learningRate;
+    float weightDecay;
+    explicit Trainer(LearningRateIterator* lr, float decay = 0);
+
+public:
+    virtual ~Trainer() = default;
+    virtual void update(Executor* executor, Variable* parameter, float learningRate, float weightDecay, int64_t steps);
+    void train(Executor* executor, std::vector<Variable*> parameters);
+    void train(Executor* executor);
+};
+class DEEP8_API SGDTrainer : public Trainer {
+public:
+    explicit SGDTrainer(LearningRateIterator* lr, float decay = 0);
+    void update(Executor* executor, Variable* parameter, float learningRate, float weightDecay, int64_t steps) override;
+};
 
 }  // namespace Deep8
 

@@ -27,6 +27,9 @@ void d8o_deconv2d_grad_x_f32(float* dx, int b, int ih, int iw, int ic, const flo
                              int sy, int sx);
 void d8o_deconv2d_grad_y_f32(const float* x, int b, int ih, int iw, int ic, float* dy, int oc, int fh, int fw, const float* dz, int oh, int ow,
                              int sy, int sx);
+void d8o_add_bias_f32(const float* x, const float* bias, float* z, size_t rows, size_t cols);
+void d8o_add_bias_grad_f32(float* dbias, const float* dz, size_t rows, size_t cols);
+void d8o_axpby_f32(const float* x, float alpha, const float* y, float beta, float* z, size_t n);
 }
 
 using namespace Deep8;
@@ -127,6 +130,62 @@ static void mlpGraph() {
     EXPECT(same(gdw1, rdw1));
     EXPECT(same(gdw2, rdw2));
     EXPECT(executor.trainableParameters().size() == 3);
+    executor.clearInterimNodes();
+}
+
+template <typename E>
+static bool throws(const std::function<void()>& f);
+
+// ---- z = x * w + b through the nodes, backward, then one SGDTrainer step: every tensor equal to the oracle's
+static void linearWithBiasAndSgd() {
+    EagerExecutor executor(DeviceType::GPU);
+    const size_t batch = 3, rows = 40, din = 24, dout = 56;
+    auto hx = ints(batch * rows * din, 5), hw = ints(din * dout, 5), hb = ints(dout, 5), hdz = ints(batch * rows * dout, 5);
+    Variable& x = parameter(&executor, batch, {rows, din}, false);
+    Variable& w = parameter(&executor, {din, dout});
+    Variable& b = parameter(&executor, {dout});
+    x.feed(hx.data());
+    w.feed(hw.data());
+    b.feed(hb.data());
+    Variable& z = x * w + b;
+    std::vector<float> gz(batch * rows * dout), rz(gz.size()), rmm(gz.size());
+    z.fetch(gz.data());
+    d8o_matmul_forward_f32(hx.data(), batch, rows, din, hw.data(), 1, dout, rmm.data());
+    d8o_add_bias_f32(rmm.data(), hb.data(), rz.data(), batch * rows, dout);
+    EXPECT(same(gz, rz));
+    executor.backward(&z, hdz.data(), false);
+    std::vector<float> rdw(din * dout, 0.f), rdb(dout, 0.f), gdw(din * dout), gdb(dout);
+    d8o_matmul_grad_y_f32(hx.data(), batch, rows, din, rdw.data(), 1, dout, hdz.data());
+    d8o_add_bias_grad_f32(rdb.data(), hdz.data(), batch * rows, dout);
+    w.fetchGradient(gdw.data());
+    b.fetchGradient(gdb.data());
+    EXPECT(same(gdw, rdw));
+    EXPECT(same(gdb, rdb));
+    EXPECT(executor.trainableParameters().size() == 2);
+    // SGDTrainer::update: value = gradient * (-lr) + value * (1 - lr * decay)
+    ConstantLearningRateIterator lr(0.125f);
+    SGDTrainer trainer(&lr, 0.5f);
+    trainer.train(&executor);
+    float alpha = -1 * 0.125f, beta = (1.0 - 0.125f * 0.5f);
+    std::vector<float> rw(hw.size()), rb(hb.size()), gw(hw.size()), gb(hb.size());
+    d8o_axpby_f32(rdw.data(), alpha, hw.data(), beta, rw.data(), rw.size());
+    d8o_axpby_f32(rdb.data(), alpha, hb.data(), beta, rb.data(), rb.size());
+    w.fetch(gw.data());
+    b.fetch(gb.data());
+    EXPECT(same(gw, rw));
+    EXPECT(same(gb, rb));
+    // equal shapes add too
+    Variable& p = parameter(&executor, {7, 9});
+    Variable& q = parameter(&executor, {7, 9});
+    auto hp = ints(63, 9), hq = ints(63, 9);
+    p.feed(hp.data());
+    q.feed(hq.data());
+    Variable& r = p + q;
+    std::vector<float> gr(63);
+    r.fetch(gr.data());
+    for (size_t i = 0; i < 63; ++i) EXPECT(gr[i] == hp[i] + hq[i]);
+    Variable& bad = parameter(&executor, {9, 7});
+    EXPECT(throws<std::invalid_argument>([&] { p + bad; }));
     executor.clearInterimNodes();
 }
 
@@ -269,6 +328,7 @@ int main() {
         {"matmul Math:: x[1,300,100] * y[10,100,1] (GPU2_float)", [] { matmulMath(1, 300, 100, 10, 1); }},
         {"matmul Math:: x[3,17,5] * y[3,5,9] (per-batch branch)", [] { matmulMath(3, 17, 5, 3, 9); }},
         {"graph: parameter, feed, x*w1, relu, *w2, backward(host gradient), fetch", mlpGraph},
+        {"graph: x*w + b, backward, SGDTrainer step (Add, AddGradY, AXPBY)", linearWithBiasAndSgd},
         {"Conv2d node 2x32x32x64, 4x4x64->32, covered, stride 2, dilation 2 (test/Conv2dTest.h)", [] { convNode(2, 32, 32, 64, 32, 4, 4, true, 2, 2); }},
         {"Conv2d node 2x32x32x64, 5x5, covered, stride 1", [] { convNode(2, 32, 32, 64, 32, 5, 5, true, 1, 1); }},
         {"Conv2d node not covered, stride 2, dilation 2", [] { convNode(2, 32, 32, 64, 32, 4, 4, false, 2, 2); }},
