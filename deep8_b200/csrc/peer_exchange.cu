@@ -102,8 +102,6 @@ __device__ __forceinline__ uint4 round16<__half>(const float* acc) {
     return o;
 }
 
-// out = srcs[0] + srcs[1] + ... in that order, fp32 accumulation, 16 bytes per thread per step; NSRC > 0 unrolls the
-// source loop so that all loads of a step are in flight together.
 // w = g * alpha + w * beta for 16 bytes of weights, g in fp32: two products and one sum, each rounded (no fused
 // multiply-add), then - for fp16 weights - one rounding to T.  For fp32 this is the reference's CPU arithmetic bit for bit.
 template <typename T>
@@ -118,6 +116,9 @@ __device__ __forceinline__ uint4 sgd16(const float* g, const uint4& w_in, float 
     return round16<T>(w);
 }
 
+// out = srcs[0] + srcs[1] + ... in that order, fp32 accumulation, 16 bytes per thread per step; NSRC > 0 unrolls the
+// source loop so that all loads of a step are in flight together.
+// With `weights` the trainer's step follows on the same elements (sgd16).
 template <typename T, int NSRC>
 __global__ void __launch_bounds__(256) sum_shards_kernel(T* out, SrcList srcs, int nsrc, size_t count, bool vec, T* weights, float alpha,
                                                          float beta) {
