@@ -293,26 +293,40 @@ class MlpStep:
 
 
 def bind_to_gpu_numa_node(torch, index):
-    """Run this process (and place the pinned host buffers it allocates later) on the NUMA node the GPU hangs off: with
-    several ranks feeding their GPUs from host memory every step, buffers on the wrong socket halve the copy rate.
-    Returns the node, or None when the topology is not visible (then nothing changes)."""
+    """Run this process (and place the pinned host buffers it allocates later) on the CPUs next to the GPU: with several
+    ranks feeding their GPUs from host memory every step, buffers on the wrong socket halve the copy rate.  The GPU's
+    NUMA node comes from sysfs; where a container hides it, from NVML's ideal-CPU mask (read only).  Returns what was
+    used ("node 1", "nvml 48 cpus"), or None when neither is visible (then nothing changes)."""
+    allowed = os.sched_getaffinity(0)
     try:
         prop = torch.cuda.get_device_properties(index)
         bdf = "%04x:%02x:%02x.0" % (prop.pci_domain_id, prop.pci_bus_id, prop.pci_device_id)
         node = int(open("/sys/bus/pci/devices/%s/numa_node" % bdf).read())
-        if node < 0:
-            return None
-        cpus = set()
-        for part in open("/sys/devices/system/node/node%d/cpulist" % node).read().strip().split(","):
-            lo, _, hi = part.partition("-")
-            cpus.update(range(int(lo), int(hi or lo) + 1))
-        cpus &= os.sched_getaffinity(0)
-        if not cpus:
-            return None
-        os.sched_setaffinity(0, cpus)
-        return node
+        if node >= 0:
+            cpus = set()
+            for part in open("/sys/devices/system/node/node%d/cpulist" % node).read().strip().split(","):
+                lo, _, hi = part.partition("-")
+                cpus.update(range(int(lo), int(hi or lo) + 1))
+            cpus &= allowed
+            if cpus:
+                os.sched_setaffinity(0, cpus)
+                return "node %d" % node
     except (OSError, ValueError, AttributeError):
-        return None
+        pass
+    try:
+        import pynvml
+        pynvml.nvmlInit()
+        uuid = str(torch.cuda.get_device_properties(index).uuid)
+        handle = pynvml.nvmlDeviceGetHandleByUUID(("GPU-" + uuid) if not uuid.startswith("GPU-") else uuid)
+        words = (max(allowed) + 64) // 64
+        mask = pynvml.nvmlDeviceGetCpuAffinity(handle, words)
+        cpus = {64 * w + b for w, word in enumerate(mask) for b in range(64) if (word >> b) & 1} & allowed
+        if cpus and cpus != allowed:
+            os.sched_setaffinity(0, cpus)
+            return "nvml %d cpus" % len(cpus)
+    except Exception:
+        pass
+    return None
 
 
 def run_gpu_arm(args):
