@@ -360,7 +360,7 @@ def run_gpu_arm(args):
         ctx_side.use_stream(side)
         # waits between ranks give up after 20 s here (first steps include module loading on every rank); the default is 2 s
         exchange = lambda numel, rows: PeerAllReduce(ctx, ctx_side, side, numel, torch.float16, device, rows=rows, with_weights=args.sgd,
-                                                     timeout_ms=20000.0)
+                                                     timeout_ms=20000.0, gather=os.environ.get("D8_BENCH_GATHER", "copy"))
     mlp = MlpStep(ctx, torch, device, rank, fused=not args.unfused, exchange=exchange,
                   scatter=exchange is not None and mode == "fused" and not args.unfused, sgd=args.sgd)
 

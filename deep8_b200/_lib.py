@@ -58,6 +58,7 @@ SIGNATURES = {
     "d8k_peer_copy": (_i, [_vp, _vp, _vp, _sz]),
     "d8k_matmul_grad_y_scatter": (_i, [_vp, _i, _vp, _i, _i, _i, _i, _vp, ctypes.POINTER(_vp), _i, _i]),
     "d8k_sum_shards": (_i, [_vp, _i, _vp, ctypes.POINTER(_vp), _i, _sz]),
+    "d8k_sum_shards_gather": (_i, [_vp, _i, _vp, ctypes.POINTER(_vp), _i, _sz, _vp, ctypes.c_float, ctypes.c_float, ctypes.POINTER(_vp), _i]),
     "d8k_axpby": (_i, [_vp, _i, _vp, ctypes.c_float, _vp, ctypes.c_float, _sz]),
     "d8k_sum_shards_sgd": (_i, [_vp, _i, _vp, ctypes.POINTER(_vp), _i, _sz, _vp, ctypes.c_float, ctypes.c_float]),
 }

@@ -121,7 +121,7 @@ __device__ __forceinline__ uint4 sgd16(const float* g, const uint4& w_in, float 
 // With `weights` the trainer's step follows on the same elements (sgd16).
 template <typename T, int NSRC>
 __global__ void __launch_bounds__(256) sum_shards_kernel(T* out, SrcList srcs, int nsrc, size_t count, bool vec, T* weights, float alpha,
-                                                         float beta) {
+                                                         float beta, FlagList copies, int ncopies) {
     constexpr int V = 16 / sizeof(T);
     const size_t tid = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x;
     const size_t stride = gridDim.x * static_cast<size_t>(blockDim.x);
@@ -146,7 +146,11 @@ __global__ void __launch_bounds__(256) sum_shards_kernel(T* out, SrcList srcs, i
 #pragma unroll
             for (int k = 0; k < V; ++k) gs[k] = 0.f;
             accumulate16<T>(gs, g);
-            reinterpret_cast<uint4*>(weights)[i] = sgd16<T>(gs, reinterpret_cast<const uint4*>(weights)[i], alpha, beta);
+            const uint4 w = sgd16<T>(gs, reinterpret_cast<const uint4*>(weights)[i], alpha, beta);
+            reinterpret_cast<uint4*>(weights)[i] = w;
+            for (int c = 0; c < ncopies; ++c) reinterpret_cast<uint4*>(copies.p[c])[i] = w;  // the all-gather: peers' copies of the weights
+        } else {
+            for (int c = 0; c < ncopies; ++c) reinterpret_cast<uint4*>(copies.p[c])[i] = g;  // the all-gather: peers' copies of the sum
         }
     }
     for (size_t i = nv * V + tid; i < count; i += stride) {
@@ -164,14 +168,19 @@ __global__ void __launch_bounds__(256) sum_shards_kernel(T* out, SrcList srcs, i
             if constexpr (sizeof(T) == 4) { gs = gt; ws = weights[i]; }
             else { gs = __half2float(gt); ws = __half2float(weights[i]); }
             float r = __fadd_rn(__fmul_rn(gs, alpha), __fmul_rn(ws, beta));
-            if constexpr (sizeof(T) == 4) weights[i] = r;
-            else weights[i] = __float2half_rn(r);
+            if constexpr (sizeof(T) == 4) gt = r;
+            else gt = __float2half_rn(r);
+            weights[i] = gt;
         }
+        for (int c = 0; c < ncopies; ++c) reinterpret_cast<T*>(copies.p[c])[i] = gt;
     }
+    // the copies may sit in peers' memory: order this thread's stores before whatever the host enqueues next
+    if (ncopies) __threadfence_system();
 }
 
 template <typename T>
-void launch_sum(const Ctx* ctx, void* out, const SrcList& srcs, int nsrc, size_t count, bool vec, void* weights, float alpha, float beta) {
+void launch_sum(const Ctx* ctx, void* out, const SrcList& srcs, int nsrc, size_t count, bool vec, void* weights, float alpha, float beta,
+                const FlagList& copies, int ncopies) {
     constexpr int V = 16 / sizeof(T);
     size_t blocks = (count / V + 255) / 256;
     // enough 16-byte loads in flight to cover HBM latency: each thread has nsrc (+1 with weights) per step
@@ -182,11 +191,11 @@ void launch_sum(const Ctx* ctx, void* out, const SrcList& srcs, int nsrc, size_t
     T* o = static_cast<T*>(out);
     T* w = static_cast<T*>(weights);
     switch (nsrc) {
-        case 1: sum_shards_kernel<T, 1><<<grid, 256, 0, ctx->stream>>>(o, srcs, nsrc, count, vec, w, alpha, beta); break;
-        case 2: sum_shards_kernel<T, 2><<<grid, 256, 0, ctx->stream>>>(o, srcs, nsrc, count, vec, w, alpha, beta); break;
-        case 4: sum_shards_kernel<T, 4><<<grid, 256, 0, ctx->stream>>>(o, srcs, nsrc, count, vec, w, alpha, beta); break;
-        case 8: sum_shards_kernel<T, 8><<<grid, 256, 0, ctx->stream>>>(o, srcs, nsrc, count, vec, w, alpha, beta); break;
-        default: sum_shards_kernel<T, 0><<<grid, 256, 0, ctx->stream>>>(o, srcs, nsrc, count, vec, w, alpha, beta); break;
+        case 1: sum_shards_kernel<T, 1><<<grid, 256, 0, ctx->stream>>>(o, srcs, nsrc, count, vec, w, alpha, beta, copies, ncopies); break;
+        case 2: sum_shards_kernel<T, 2><<<grid, 256, 0, ctx->stream>>>(o, srcs, nsrc, count, vec, w, alpha, beta, copies, ncopies); break;
+        case 4: sum_shards_kernel<T, 4><<<grid, 256, 0, ctx->stream>>>(o, srcs, nsrc, count, vec, w, alpha, beta, copies, ncopies); break;
+        case 8: sum_shards_kernel<T, 8><<<grid, 256, 0, ctx->stream>>>(o, srcs, nsrc, count, vec, w, alpha, beta, copies, ncopies); break;
+        default: sum_shards_kernel<T, 0><<<grid, 256, 0, ctx->stream>>>(o, srcs, nsrc, count, vec, w, alpha, beta, copies, ncopies); break;
     }
 }
 
@@ -289,7 +298,7 @@ int d8k_peer_copy(d8k_ctx* ctx, void* dst, const void* src, size_t bytes) {
 }
 
 static int sum_shards_impl(d8k_ctx* ctx, int dtype, void* out, const void* const* srcs, int nsrc, size_t count, void* weights, float alpha,
-                           float beta) {
+                           float beta, void* const* copies = nullptr, int ncopies = 0) {
     if (int rc = check_ctx(ctx)) return rc;
     if (dtype != D8K_F16 && dtype != D8K_F32) return fail(D8K_ERR_ARGUMENT, "type is not support: dtype must be D8K_F16 or D8K_F32");
     if (count == 0) return 0;
@@ -301,9 +310,16 @@ static int sum_shards_impl(d8k_ctx* ctx, int dtype, void* out, const void* const
         s.p[i] = srcs[i];
         bits |= reinterpret_cast<uintptr_t>(srcs[i]);
     }
+    FlagList cp = {};
+    if (ncopies < 0 || ncopies > kMaxPeers || (ncopies > 0 && !copies)) return fail(D8K_ERR_ARGUMENT, "sum_shards: 0 to 16 copies");
+    for (int i = 0; i < ncopies; ++i) {
+        if (!copies[i]) return fail(D8K_ERR_ARGUMENT, "sum_shards: null copy");
+        cp.p[i] = static_cast<unsigned*>(copies[i]);
+        bits |= reinterpret_cast<uintptr_t>(copies[i]);
+    }
     bool vec = (bits & 15) == 0;
-    if (dtype == D8K_F32) launch_sum<float>(ctx, out, s, nsrc, count, vec, weights, alpha, beta);
-    else launch_sum<__half>(ctx, out, s, nsrc, count, vec, weights, alpha, beta);
+    if (dtype == D8K_F32) launch_sum<float>(ctx, out, s, nsrc, count, vec, weights, alpha, beta, cp, ncopies);
+    else launch_sum<__half>(ctx, out, s, nsrc, count, vec, weights, alpha, beta, cp, ncopies);
     D8K_CUDA(cudaGetLastError());
     count_launch();
     return 0;
@@ -318,6 +334,12 @@ int d8k_sum_shards_sgd(d8k_ctx* ctx, int dtype, void* grad_out, const void* cons
                        float beta) {
     if (!weights) return fail(D8K_ERR_ARGUMENT, "sum_shards_sgd: null weights");
     return sum_shards_impl(ctx, dtype, grad_out, srcs, nsrc, count, weights, alpha, beta);
+}
+
+int d8k_sum_shards_gather(d8k_ctx* ctx, int dtype, void* out, const void* const* srcs, int nsrc, size_t count, void* weights, float alpha,
+                          float beta, void* const* copies, int ncopies) {
+    if (!out && !weights) return fail(D8K_ERR_ARGUMENT, "sum_shards_gather: null output");
+    return sum_shards_impl(ctx, dtype, out, srcs, nsrc, count, weights, alpha, beta, copies, ncopies);
 }
 
 int d8k_axpby(d8k_ctx* ctx, int dtype, const void* x, float alpha, void* y, float beta, size_t n) {

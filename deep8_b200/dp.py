@@ -132,12 +132,17 @@ class PeerAllReduce:
     FLAG_WORDS = 64  # per kind: one word per peer, padded
 
     def __init__(self, ctx_main, ctx_side, side_stream, numel, dtype, device, group=None, timeout_ms=2000.0, rows=None,
-                 runtime=None, with_weights=False):
+                 runtime=None, with_weights=False, gather="copy"):
         """rows: the gradient is a rows x (numel / rows) matrix to be cut into row blocks - needed for scatter_grad_y,
         where the contraction's epilogue stores each block straight into its owner's staging memory.
         runtime: CudaRuntime unless a test substitutes host memory.
         with_weights: also keep the operand itself in peer memory (`weights`), so that start(sgd=...) can apply the
-        trainer's step to the shard this rank sums and send updated weights instead of gradients."""
+        trainer's step to the shard this rank sums and send updated weights instead of gradients.
+        gather: "copy" - the finished shard reaches the peers by copy-engine transfers; "kernel" - the sum kernel itself
+        stores every finished 16 bytes into the peers' buffers (sum and all-gather in one kernel, no copy engine)."""
+        if gather not in ("copy", "kernel"):
+            raise ValueError("gather is 'copy' or 'kernel'")
+        self.gather = gather
         self.rt = runtime if runtime is not None else CudaRuntime()
         self.ctx_main, self.ctx_side, self.side = ctx_main, ctx_side, side_stream
         self.numel, self.dtype, self.device, self.group, self.timeout_ms = numel, dtype, device, group, timeout_ms
@@ -238,10 +243,13 @@ class PeerAllReduce:
         scattered, self.scattered = getattr(self, "scattered", False), False
         mine = self.base + self.off_result + lo * self.esize
         step = None if coeff is None else (self.base + self.off_weights + lo * self.esize, coeff[0], coeff[1])
+        off = (self.off_weights if step is not None else self.off_result) + lo * self.esize  # what the all-gather carries
+        copies = [self.peers[q] + off for q in self.order] if self.gather == "kernel" else None
         if scattered:
             # every rank's epilogue has already put its block of partial sums into my staging slots
             if n > 0:
-                c.sum_shards(self.dtype, mine, [self.base + self.off_stage + q * self.stage_bytes for q in range(self.world)], n, sgd=step)
+                c.sum_shards(self.dtype, mine, [self.base + self.off_stage + q * self.stage_bytes for q in range(self.world)], n, sgd=step,
+                             copies=copies)
             c.peer_signal([self._flag(q, 1, r) for q in self.order], s)                   # my staging slots may be rewritten
         else:
             if n > 0:
@@ -252,9 +260,8 @@ class PeerAllReduce:
             if n > 0:
                 srcs = [self.base + self.off_partial + lo * self.esize if q == r else self.base + self.off_stage + q * self.stage_bytes
                         for q in range(self.world)]
-                c.sum_shards(self.dtype, mine, srcs, n, sgd=step)
-        if n > 0:
-            off = (self.off_weights if step is not None else self.off_result) + lo * self.esize
+                c.sum_shards(self.dtype, mine, srcs, n, sgd=step, copies=copies)
+        if n > 0 and copies is None:
             for q in self.order:                                                           # all-gather: push the finished shard
                 c.peer_copy(self.peers[q] + off, self.base + off, n * self.esize)
         c.peer_signal([self._flag(q, 2, r) for q in self.order], s)                       # my shard has been delivered

@@ -319,11 +319,16 @@ class Context:
             raise TypeError("type %s is not support" % dtype)
         return code
 
-    def sum_shards(self, dtype, out, srcs, count, sgd=None):
+    def sum_shards(self, dtype, out, srcs, count, sgd=None, copies=None):
         """out[i] = srcs[0][i] + ... + srcs[-1][i] in that order (fp32 accumulation); dtype is a torch dtype.
-        sgd = (weights address, alpha, beta): also weights = sum * alpha + weights * beta (out may then be None)."""
+        sgd = (weights address, alpha, beta): also weights = sum * alpha + weights * beta (out may then be None).
+        copies: addresses (peers' buffers) that also receive the result - the updated weights with sgd, else the sum."""
         code = self._code(dtype)
-        if sgd is None:
+        if copies:
+            w, alpha, beta = sgd if sgd is not None else (None, 0.0, 0.0)
+            check(self.lib.d8k_sum_shards_gather(self.h, code, ctypes.c_void_p(out) if out else None, self._ptr_array(srcs), len(srcs),
+                                                 count, ctypes.c_void_p(w) if w else None, alpha, beta, self._ptr_array(copies), len(copies)))
+        elif sgd is None:
             check(self.lib.d8k_sum_shards(self.h, code, ctypes.c_void_p(out), self._ptr_array(srcs), len(srcs), count))
         else:
             w, alpha, beta = sgd

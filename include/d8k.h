@@ -105,6 +105,13 @@ D8K_API int d8k_matmul_forward_relu(d8k_ctx* ctx, int dtype, const void* x, int 
 D8K_API int d8k_matmul_grad_x_relu(d8k_ctx* ctx, int dtype, void* dx, int xb, int xr, int xc, const void* y, int yb, int yc, const void* dz,
                            int accumulate_dx, const void* h, void* dh, int accumulate_dh);
 
+/* The sum and the all-gather in one kernel: as d8k_sum_shards (weights == NULL) or d8k_sum_shards_sgd (weights != NULL),
+ * and every finished 16 bytes - of the sum, or of the updated weights - are also stored to copies[0..ncopies), the same
+ * shard in each peer's buffer (d8k_peer_open addresses), over NVLink from the threads that computed them.  No copy
+ * engine call and no second pass over the shard; signal the peers after it (d8k_peer_signal on the same stream). */
+D8K_API int d8k_sum_shards_gather(d8k_ctx* ctx, int dtype, void* out, const void* const* srcs, int nsrc, size_t count, void* weights,
+                                  float alpha, float beta, void* const* copies, int ncopies);
+
 /* MatrixMultiplyGPU followed by AddGPU with a bias (deep8/src/math/Add.cu; shapes broadcast from the tail,
  * deep8/include/utils/ShapeUtils.h:40-55) in one launch: z = x * y + bias, bias one row of yc elements added to every
  * row of every batch entry, from the accumulator in the epilogue.  Rounded as the two calls would: the product to dtype,

@@ -104,7 +104,7 @@ class _HostContext:
         import ctypes
         return np.ctypeslib.as_array((ctypes.c_uint16 * count).from_address(addr)).view(np.float16)
 
-    def sum_shards(self, dtype, out, srcs, count, sgd=None):
+    def sum_shards(self, dtype, out, srcs, count, sgd=None, copies=None):
         acc = np.zeros(count, dtype=np.float32)
         for a in srcs:
             acc = acc + self._f16(a, count).astype(np.float32)
@@ -115,6 +115,9 @@ class _HostContext:
             w, alpha, beta = sgd
             wv = self._f16(w, count)
             wv[:] = (g.astype(np.float32) * np.float32(alpha) + wv.astype(np.float32) * np.float32(beta)).astype(np.float16)
+            g = wv.copy()
+        for a in copies or []:
+            self._f16(a, count)[:] = g
 
     def matmul_grad_y_scatter(self, x, yc, dz, row_blocks, block_rows):
         dy = (x[0].numpy().astype(np.float32).T @ dz[0].numpy().astype(np.float32)).astype(np.float16)
@@ -150,7 +153,7 @@ class _HostRuntime:
         pass
 
 
-def _protocol_worker(rank, world, port, out_dir):
+def _protocol_worker(rank, world, port, out_dir, gather="copy"):
     sys.path.insert(0, ROOT)
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
@@ -161,7 +164,7 @@ def _protocol_worker(rank, world, port, out_dir):
     ok = True
     # copy-engine variant: partial -> pull -> sum -> push
     numel = 5000
-    ar = PeerAllReduce(ctx, ctx, None, numel, torch.float16, "cpu", runtime=_HostRuntime(), timeout_ms=5000.0)
+    ar = PeerAllReduce(ctx, ctx, None, numel, torch.float16, "cpu", runtime=_HostRuntime(), timeout_ms=5000.0, gather=gather)
     for s in range(3):
         parts = [torch.from_numpy(np.random.default_rng(10 * s + q).standard_normal(numel).astype(np.float16)) for q in range(world)]
         ar.before_write()
@@ -175,7 +178,7 @@ def _protocol_worker(rank, world, port, out_dir):
     ar.close()
     # scattered variant: each rank's contraction writes row blocks into the owners' staging slots
     r, rows, cols = 24, 300, 40
-    ar = PeerAllReduce(ctx, ctx, None, rows * cols, torch.float16, "cpu", runtime=_HostRuntime(), timeout_ms=5000.0, rows=rows)
+    ar = PeerAllReduce(ctx, ctx, None, rows * cols, torch.float16, "cpu", runtime=_HostRuntime(), timeout_ms=5000.0, rows=rows, gather=gather)
     for s in range(3):
         xs = [torch.from_numpy(np.random.default_rng(100 * s + q).standard_normal((1, r, rows)).astype(np.float16)) for q in range(world)]
         dzs = [torch.from_numpy(np.random.default_rng(100 * s + 50 + q).standard_normal((1, r, cols)).astype(np.float16)) for q in range(world)]
@@ -189,7 +192,8 @@ def _protocol_worker(rank, world, port, out_dir):
         ok = ok and np.array_equal(ar.result.numpy().reshape(rows, cols), acc.astype(np.float16))
     ar.close()
     # the trainer's step inside the sum: every rank ends with the same updated weights
-    ar = PeerAllReduce(ctx, ctx, None, numel, torch.float16, "cpu", runtime=_HostRuntime(), timeout_ms=5000.0, with_weights=True)
+    ar = PeerAllReduce(ctx, ctx, None, numel, torch.float16, "cpu", runtime=_HostRuntime(), timeout_ms=5000.0, with_weights=True,
+                       gather=gather)
     w0 = np.random.default_rng(7).standard_normal(numel).astype(np.float16)
     ar.weights.copy_(torch.from_numpy(w0))
     want = w0.copy()
@@ -213,13 +217,13 @@ def _protocol_worker(rank, world, port, out_dir):
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("world", [2, 3])
-def test_exchange_protocol_on_host_memory(tmp_path, world):
+@pytest.mark.parametrize("world,gather", [(2, "copy"), (3, "copy"), (2, "kernel"), (3, "kernel")])
+def test_exchange_protocol_on_host_memory(tmp_path, world, gather):
     """Two and three gloo ranks run PeerAllReduce's own sequence of signals, bounded waits, copies and sums against shared
     host memory: every rank ends with the rank-ordered sum, no wait runs out, for both the copy variant and the
     scattered-contraction variant, three steps each (so the reuse hazards of staging and partial buffers are exercised)."""
     import torch.multiprocessing as mp
-    mp.spawn(_protocol_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    mp.spawn(_protocol_worker, args=(world, _free_port(), str(tmp_path), gather), nprocs=world, join=True)
     for r in range(world):
         assert open(os.path.join(str(tmp_path), "rank%d.txt" % r)).read() == "1 0"
 
@@ -421,8 +425,32 @@ def test_sum_shards_sgd_equals_sum_then_axpby(ctx, dtype):
     assert torch.equal(w_none, w_two)
 
 
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [torch.float16, torch.float32])
+def test_sum_shards_gather_writes_every_copy(ctx, dtype):
+    """Sum and all-gather in one kernel: the copies (here on the same GPU) receive the sum, or the updated weights."""
+    n = 8 * 1024 + 5
+    g = torch.Generator(device="cuda").manual_seed(9)
+    parts = [torch.randn(n, device="cuda", generator=g).to(dtype) for _ in range(3)]
+    want = torch.empty(n, device="cuda", dtype=dtype)
+    ctx.sum_shards(dtype, want.data_ptr(), [p.data_ptr() for p in parts], n)
+    out = torch.empty_like(want)
+    copies = [torch.zeros_like(want) for _ in range(3)]
+    ctx.sum_shards(dtype, out.data_ptr(), [p.data_ptr() for p in parts], n, copies=[c.data_ptr() for c in copies])
+    torch.cuda.synchronize()
+    assert torch.equal(out, want) and all(torch.equal(c, want) for c in copies)
+    w = torch.randn(n, device="cuda", generator=g).to(dtype)
+    w_want = ctx.axpby(want, -0.05, w.clone(), 0.999)
+    w_got = w.clone()
+    ctx.sum_shards(dtype, out.data_ptr(), [p.data_ptr() for p in parts], n, sgd=(w_got.data_ptr(), -0.05, 0.999),
+                   copies=[c.data_ptr() for c in copies])
+    torch.cuda.synchronize()
+    assert torch.equal(w_got, w_want) and all(torch.equal(c, w_want) for c in copies)
+    assert ctx.status() == 0
+
+
 # ------------------------------------------------------------------------------------------------ GPU: two devices
-def _exchange_worker(rank, world, port, numel, steps, out_dir):
+def _exchange_worker(rank, world, port, numel, steps, out_dir, gather="copy"):
     sys.path.insert(0, ROOT)
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
@@ -438,7 +466,7 @@ def _exchange_worker(rank, world, port, numel, steps, out_dir):
     c_main, c_side = deep8_b200.Context(rank, 1 << 20), deep8_b200.Context(rank, 1 << 20)
     c_main.use_stream(main)
     c_side.use_stream(side)
-    ar = PeerAllReduce(c_main, c_side, side, numel, torch.float16, dev)
+    ar = PeerAllReduce(c_main, c_side, side, numel, torch.float16, dev, gather=gather)
     ok = True
     with torch.cuda.stream(main):
         for s in range(steps):
@@ -458,7 +486,7 @@ def _exchange_worker(rank, world, port, numel, steps, out_dir):
     ar.close()
     # the SGD step inside the sum: both ranks end with the same weights, equal to sum -> round -> axpby on the host
     from deep8_b200.dp import sgd_coefficients
-    ar = PeerAllReduce(c_main, c_side, side, numel, torch.float16, dev, with_weights=True)
+    ar = PeerAllReduce(c_main, c_side, side, numel, torch.float16, dev, with_weights=True, gather=gather)
     alpha, beta = sgd_coefficients(0.05, 0.001)
     with torch.cuda.stream(main):
         w0 = torch.randn(numel, device=dev, generator=torch.Generator(device=dev).manual_seed(77)).to(torch.float16)
@@ -485,7 +513,7 @@ def _exchange_worker(rank, world, port, numel, steps, out_dir):
     dist.destroy_process_group()
 
 
-def _fused_worker(rank, world, port, r, rows, cols, steps, out_dir):
+def _fused_worker(rank, world, port, r, rows, cols, steps, out_dir, gather="copy"):
     sys.path.insert(0, ROOT)
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
@@ -500,7 +528,7 @@ def _fused_worker(rank, world, port, r, rows, cols, steps, out_dir):
     c_main, c_side = deep8_b200.Context(rank), deep8_b200.Context(rank, 1 << 20)
     c_main.use_stream(main)
     c_side.use_stream(side)
-    ar = PeerAllReduce(c_main, c_side, side, rows * cols, torch.float16, dev, rows=rows)
+    ar = PeerAllReduce(c_main, c_side, side, rows * cols, torch.float16, dev, rows=rows, gather=gather)
     ok = True
 
     def inputs(s, q):
@@ -533,26 +561,28 @@ def _fused_worker(rank, world, port, r, rows, cols, steps, out_dir):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("gather", ["copy", "kernel"])
 @pytest.mark.parametrize("r,rows,cols", [(512, 4096, 4096), (96, 200, 72)])
-def test_two_gpu_fused_scatter_exchange_is_bit_exact(tmp_path, r, rows, cols):
+def test_two_gpu_fused_scatter_exchange_is_bit_exact(tmp_path, r, rows, cols, gather):
     """The contraction whose epilogue stores each row block into its owner's memory, then sum + all-gather: equal, bit
     for bit, to summing the ranks' ordinary matmul_grad_y results in rank order."""
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     import torch.multiprocessing as mp
     world = 2
-    mp.spawn(_fused_worker, args=(world, _free_port(), r, rows, cols, 3, str(tmp_path)), nprocs=world, join=True)
+    mp.spawn(_fused_worker, args=(world, _free_port(), r, rows, cols, 3, str(tmp_path), gather), nprocs=world, join=True)
     for q in range(world):
         assert open(os.path.join(str(tmp_path), "rank%d.txt" % q)).read() == "1 0 0"
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("gather", ["copy", "kernel"])
 @pytest.mark.parametrize("numel", [1 << 20, 100003])
-def test_two_gpu_exchange_sums_partials_bit_exactly(tmp_path, numel):
+def test_two_gpu_exchange_sums_partials_bit_exactly(tmp_path, numel, gather):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     import torch.multiprocessing as mp
     world = 2
-    mp.spawn(_exchange_worker, args=(world, _free_port(), numel, 3, str(tmp_path)), nprocs=world, join=True)
+    mp.spawn(_exchange_worker, args=(world, _free_port(), numel, 3, str(tmp_path), gather), nprocs=world, join=True)
     for r in range(world):
         assert open(os.path.join(str(tmp_path), "rank%d.txt" % r)).read() == "1 0 0"
