@@ -18,6 +18,7 @@ own CPU code on a row slice of the same workload.  `--impl reference` times only
 """
 import argparse
 import json
+import math
 import os
 import statistics
 import subprocess
@@ -50,8 +51,68 @@ def measured_peaks():
 
 
 # ------------------------------------------------------------------------------------------------ clocks
-class ClockSampler:
-    """Samples nvidia-smi while the timed region runs: SM clock, its maximum and the active throttle reasons."""
+class NvmlSampler:
+    """Reads SM clock, board power and the active clock-event reasons of one GPU through NVML (queries only) from a thread
+    of this process every `period_s`; report(t0, t1) summarises the samples whose host time lies inside [t0, t1] - the
+    timed region, bracketed by synchronisations on both sides - so the clock figure describes the region itself."""
+
+    REASONS = (("hw_slowdown", 0x8), ("hw_thermal_slowdown", 0x40), ("sw_thermal_slowdown", 0x20), ("sw_power_cap", 0x4))
+
+    def __init__(self, torch, index, period_s=0.002):
+        self.period_s, self.samples, self.stop_flag, self.thread, self.handle, self.nvml = period_s, [], False, None, None, None
+        self.max_mhz = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            uuid = str(torch.cuda.get_device_properties(index).uuid)
+            self.handle = pynvml.nvmlDeviceGetHandleByUUID(uuid if uuid.startswith("GPU-") else "GPU-" + uuid)
+            self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(self.handle, pynvml.NVML_CLOCK_SM))
+            self.nvml = pynvml
+        except Exception:
+            self.handle = None
+
+    def available(self):
+        return self.handle is not None
+
+    def _loop(self):
+        n, h = self.nvml, self.handle
+        reasons_fn = getattr(n, "nvmlDeviceGetCurrentClocksEventReasons", None) or n.nvmlDeviceGetCurrentClocksThrottleReasons
+        while not self.stop_flag:
+            try:
+                mhz = n.nvmlDeviceGetClockInfo(h, n.NVML_CLOCK_SM)
+                mask = reasons_fn(h)
+                watts = n.nvmlDeviceGetPowerUsage(h) / 1000.0
+                self.samples.append((time.perf_counter(), float(mhz), int(mask), watts))
+            except Exception:
+                pass
+            time.sleep(self.period_s)
+
+    def start(self):
+        if self.handle is not None:
+            self.thread = threading.Thread(target=self._loop, daemon=True)
+            self.thread.start()
+
+    def stop(self):
+        self.stop_flag = True
+        if self.thread is not None:
+            self.thread.join(timeout=2)
+
+    def report(self, t0, t1):
+        inside = [s for s in self.samples if t0 <= s[0] <= t1]
+        if not inside:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": ["no NVML sample inside the timed region"], "samples": 0}
+        mhz = [s[1] for s in inside]
+        mask = 0
+        for s in inside:
+            mask |= s[2]
+        return {"sm_mhz": statistics.median(mhz), "sm_mhz_min": min(mhz), "sm_mhz_max": max(mhz), "sm_max_mhz": self.max_mhz,
+                "reasons": [name for name, bit in self.REASONS if mask & bit], "samples": len(inside),
+                "power_w_median": statistics.median(s[3] for s in inside),
+                "source": "NVML queries from this process every %g ms; only samples inside the timed region are counted" % (self.period_s * 1e3)}
+
+
+class SmiSampler:
+    """Fallback when NVML cannot be loaded: nvidia-smi polled every 100 ms (too coarse to resolve a short region)."""
 
     FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
@@ -69,21 +130,24 @@ class ClockSampler:
 
     def _read(self):
         for line in self.proc.stdout:
-            self.lines.append(line.strip())
+            self.lines.append((time.perf_counter(), line.strip()))
 
     def stop(self):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def report(self, t0, t1):
         if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        self.proc.terminate()
-        try:
-            self.proc.wait(timeout=5)
-        except subprocess.TimeoutExpired:
-            self.proc.kill()
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"], "samples": 0}
         sm, mx, reasons = [], [], set()
         names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
-        for line in self.lines:
+        for t, line in self.lines:
             parts = [p.strip() for p in line.split(",")]
-            if len(parts) < 6:
+            if len(parts) < 6 or not (t0 <= t <= t1 + 0.1):
                 continue
             try:
                 sm.append(float(parts[0]))
@@ -94,7 +158,7 @@ class ClockSampler:
                 if v.lower().startswith("active"):
                     reasons.add(name)
         return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "reasons": sorted(reasons), "samples": len(sm)}
+                "reasons": sorted(reasons), "samples": len(sm), "source": "nvidia-smi -lms 100 (NVML could not be loaded)"}
 
 
 # ------------------------------------------------------------------------------------------------ CPU reference arm
@@ -155,9 +219,12 @@ def run_reference_arm(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    base, dt = cpu_arm(max(1, min(args.steps, 3)), 1 if args.warmup > 0 else 0)
-    line = {"impl": "reference", "metric": METRIC, "value": base["value"], "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+    steps = max(1, min(args.steps, 3))       # a step of the 256-row sample takes about 7 s on one core
+    warmup = 1 if args.warmup > 0 else 0
+    base, dt = cpu_arm(steps, warmup)
+    line = {"impl": "reference", "metric": METRIC, "value": base["value"], "unit": UNIT, "n_gpus": args.gpus, "steps": steps,
+            "warmup": warmup, "steps_requested": args.steps, "warmup_requested": args.warmup,
+            "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "f32", "data": "synthetic", "config": workload_config(args.gpus), "cpu_baseline": base,
             "e2e": {"value": base["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line), flush=True)
@@ -170,6 +237,7 @@ def exchange_name(n):
     return {"fused": "peer memory: the contraction's epilogue stores each row block in its owner's GPU (reduce-scatter inside the "
                      "kernel), fixed-order sum kernel, copy-engine all-gather on a side stream",
             "peer": "peer memory: copy-engine reduce-scatter/all-gather + fixed-order sum kernel on a side stream",
+            "none": "NO exchange (diagnostic: independent replicas, gradients are not summed)",
             "end": "NCCL all-reduce after the last contraction"}.get(mode, "NCCL all-reduce started as each gradient completes")
 
 
@@ -181,15 +249,25 @@ def workload_config(n):
 
 
 # ------------------------------------------------------------------------------------------------ GPU arm
+# the six contractions of one step, in the order the fused step launches them
+CONTRACTIONS = ("H = X*W1 (+ReLU)", "Y = A*W2", "dW2 = A^T*dY", "dA = dY*W2^T (+ReLU grad)", "dW1 = X^T*dH", "dX = dH*W1^T")
+
+
 class MlpStep:
     """The MLP step on one GPU through the d8k C ABI; buffers allocated once, as an executor would keep them.
-    X, dY and Y are double-buffered so that the end-to-end loop can copy step i+1 in and step i-1 out while step i runs."""
+    X, dY and Y are double-buffered so that the end-to-end loop can copy step i+1 in and step i-1 out while step i runs.
+
+    With several GPUs the sums of dW1 and dW2 run on a side stream.  A step does not wait for its own exchange: the wait
+    moves to the first point of the NEXT step that needs it - before the staging memory is rewritten (after the two
+    forward contractions), or, with the trainer's step inside the exchange (sgd), before the first contraction, which reads
+    the updated weights.  drain() waits for whatever is still pending; the timed regions end with it."""
 
     SGD = (1e-6, 1e-4)  # learning rate, weight decay of the optional trainer step (--sgd); small: the data are random every step
 
     def __init__(self, ctx, torch, device, rank, fused=True, exchange=None, scatter=False, sgd=False):
         self.ctx, self.torch, self.fused, self.scatter, self.sgd = ctx, torch, fused, scatter, sgd
         self.ar1 = self.ar2 = None
+        self.pending = False
         g = torch.Generator(device=device)
         g.manual_seed(10)
         h = torch.float16
@@ -214,7 +292,7 @@ class MlpStep:
                 self.ar2.weights.copy_(self.W2.view(-1))
                 self.W1, self.W2 = self.ar1.weights.view(self.W1.shape), self.ar2.weights.view(self.W2.shape)
         self.gemm_events = []
-        self.tail_events = []  # (after the last contraction, after the exchange has been waited for)
+        self.tail_events = []  # around each wait of the main stream for the exchange
 
     def _reduce(self, which, dist, work, overlap):
         ar, grad = (self.ar1, self.dW1) if which == 1 else (self.ar2, self.dW2)
@@ -233,52 +311,82 @@ class MlpStep:
         else:
             fn()
 
+    def drain(self, timed=False):
+        """Main stream waits for the exchanges started by the last step (no-op when nothing is pending)."""
+        if self.ar1 is None or not self.pending:
+            return
+        if timed:
+            ev = (self.torch.cuda.Event(enable_timing=True), self.torch.cuda.Event(enable_timing=True))
+            ev[0].record()
+        self.ar2.finish()
+        self.ar1.finish()
+        if timed:
+            ev[1].record()
+            self.tail_events.append(ev)
+        self.pending = False
+
     def step(self, dist=None, timed=False, buf=0):
         c = self.ctx
         X, dY, Y = self.X[buf], self.dY[buf], self.Y[buf]
         overlap = os.environ.get("D8_BENCH_ALLREDUCE", "fused") != "end"
         work = []
-        if self.ar1 is not None:
-            self.ar2.before_write()
-            self.ar1.before_write()
+        if self.sgd:
+            self.drain(timed)  # the forward pass reads the weights the previous step's exchange updates
         if self.fused:
             # Weight gradients are produced as early as their inputs allow, so that each exchange has contractions
             # still to run behind it: dW2 needs only A and dY, dW1 needs dH, and dX (no exchange) goes last.
             self._gemm(lambda: c.matmul_forward_relu(X, self.W1, self.H, self.A), timed)
             self._gemm(lambda: c.matmul_forward(self.A, self.W2, out=Y), timed)
+            self.drain(timed)
+            if self.ar1 is not None:
+                self.ar2.before_write()
             if self.scatter:  # the contraction's epilogue stores each row block in its owner's memory
                 self._gemm(lambda: self.ar2.scatter_grad_y(self.A, dY), timed)
             else:
                 self._gemm(lambda: c.matmul_grad_y(self.A, self.W2, self.dW2, dY, accumulate=False), timed)
-            self._reduce(2, dist, work, overlap)
+            if not self.sgd:
+                self._reduce(2, dist, work, overlap)
             self._gemm(lambda: c.matmul_grad_x_relu(self.A, self.dA, self.W2, dY, self.H, self.dH, False, False), timed)
+            if self.sgd:  # the trainer's step rewrites W2: only after its last reader of this step (dA) is enqueued
+                self._reduce(2, dist, work, overlap)
+            if self.ar1 is not None:
+                self.ar1.before_write()
             if self.scatter:
                 self._gemm(lambda: self.ar1.scatter_grad_y(X, self.dH), timed)
             else:
                 self._gemm(lambda: c.matmul_grad_y(X, self.W1, self.dW1, self.dH, accumulate=False), timed)
-            self._reduce(1, dist, work, overlap)
+            if not self.sgd:
+                self._reduce(1, dist, work, overlap)
             self._gemm(lambda: c.matmul_grad_x(X, self.dX, self.W1, self.dH, accumulate=False), timed)
+            if self.sgd:  # likewise W1 and dX
+                self._reduce(1, dist, work, overlap)
         else:
-            for t in (self.dA, self.dH, self.dX, self.dW1, self.dW2):
+            for t in (self.dA, self.dH, self.dX):
                 c.zero(t)
             self._gemm(lambda: c.matmul_forward(X, self.W1, out=self.H), timed)
             c.relu_forward(self.H, out=self.A)
             self._gemm(lambda: c.matmul_forward(self.A, self.W2, out=Y), timed)
+            self.drain(timed)
+            if self.ar1 is not None:
+                self.ar2.before_write()
+                self.ar1.before_write()
+            c.zero(self.dW2)
+            c.zero(self.dW1)
             self._gemm(lambda: c.matmul_grad_y(self.A, self.W2, self.dW2, dY), timed)
-            self._reduce(2, dist, work, overlap)
+            if not self.sgd:
+                self._reduce(2, dist, work, overlap)
             self._gemm(lambda: c.matmul_grad_x(self.A, self.dA, self.W2, dY), timed)
+            if self.sgd:
+                self._reduce(2, dist, work, overlap)
             c.relu_backward(self.H, self.dH, self.dA)
             self._gemm(lambda: c.matmul_grad_y(X, self.W1, self.dW1, self.dH), timed)
-            self._reduce(1, dist, work, overlap)
+            if not self.sgd:
+                self._reduce(1, dist, work, overlap)
             self._gemm(lambda: c.matmul_grad_x(X, self.dX, self.W1, self.dH), timed)
+            if self.sgd:
+                self._reduce(1, dist, work, overlap)
         if self.ar1 is not None:
-            if timed:
-                self.tail_events.append((self.torch.cuda.Event(enable_timing=True), self.torch.cuda.Event(enable_timing=True)))
-                self.tail_events[-1][0].record()
-            self.ar2.finish()
-            self.ar1.finish()
-            if timed:
-                self.tail_events[-1][1].record()
+            self.pending = True
         elif dist is not None:
             if not overlap:
                 work.append(dist.all_reduce(self.dW2, async_op=True))
@@ -329,6 +437,109 @@ def bind_to_gpu_numa_node(torch, index):
     return None
 
 
+def exchange_check(mlp, ctx, torch, dist, device, world, rank):
+    """After the timed steps: is what the exchange delivered the sum of the ranks' partial gradients?  Each rank recomputes
+    its partial dW2 and dW1 with the plain gradient entry point, a few 128-row slabs of them (the first and last of every
+    owner's row block) travel over NCCL to every rank, are added there in rank order in fp32 and rounded once - the
+    arithmetic of the sum kernel - and must equal the exchanged result bit for bit.  With the trainer's step inside the
+    exchange a rank holds only the summed shard it owns, so it checks that one (and that the weights agree everywhere)."""
+    part = torch.empty_like(mlp.W2)
+    bad = 0
+    slabs_checked = 0
+    for ar, x, dz, rows, cols in ((mlp.ar2, mlp.A, mlp.dY[0], D_HID, D_IN), (mlp.ar1, mlp.X[0], mlp.dH, D_IN, D_HID)):
+        w = part.view(1, rows, cols)
+        ctx.matmul_grad_y(x, w, w, dz, accumulate=False)
+        torch.cuda.synchronize()
+        got_all = ar.result.view(rows, cols)
+        br = ar.block_rows
+        for owner in range(world):
+            lo, hi = owner * br, min((owner + 1) * br, rows)
+            if lo >= hi:
+                continue
+            for r0 in sorted({lo, max(lo, hi - 128)}):
+                mine = w[0, r0:r0 + 128].contiguous()
+                parts = [torch.empty_like(mine) for _ in range(world)]
+                dist.all_gather(parts, mine)
+                acc = parts[0].float()
+                for q in range(1, world):
+                    acc += parts[q].float()
+                want = acc.to(torch.float16)
+                if mlp.sgd and owner != rank:
+                    continue
+                slabs_checked += 1
+                if not torch.equal(got_all[r0:r0 + 128], want):
+                    bad += 1
+    if mlp.sgd:  # every rank must hold the same updated weights
+        for wt in (mlp.W1, mlp.W2):
+            probe = wt.view(-1)[:: max(1, wt.numel() // 65536)].contiguous()
+            parts = [torch.empty_like(probe) for _ in range(world)]
+            dist.all_gather(parts, probe)
+            slabs_checked += 1
+            if any(not torch.equal(parts[0], p) for p in parts[1:]):
+                bad += 1
+    t = torch.tensor([bad, slabs_checked], device=device, dtype=torch.int64)
+    dist.all_reduce(t)
+    return int(t[0].item()), int(t[1].item())
+
+
+def filter_gradient_exchange(n_cfg, ctx, ctx_side, side, torch, dist, device, world, rank):
+    """BASELINE configuration 3 (Conv2d) or 4 (DeConv2d) with the images sharded over the GPUs: each rank computes the
+    filter gradient of its images, the partial gradients are summed through PeerAllReduce (copy-engine reduce-scatter,
+    fixed-order sum kernel, copy-engine all-gather - the filter is far too small for row blocks per owner), and rank 0
+    compares the result with the CPU oracle on the whole batch.  Returns (ms per gradient + exchange, max rel error)."""
+    from deep8_b200.dp import PeerAllReduce, shard_range
+    name, x, w, dz, kind, meta, _ = small_config_case(n_cfg)
+    lo, hi = shard_range(x.shape[0], world, rank)
+    X = torch.from_numpy(np.ascontiguousarray(x[lo:hi])).to(device)
+    DZ = torch.from_numpy(np.ascontiguousarray(dz[lo:hi])).to(device)
+    W = torch.from_numpy(w).to(device)
+    ar = PeerAllReduce(ctx, ctx_side, side, W.numel(), torch.float32, device, timeout_ms=20000.0)
+    DW = ar.partial.view(W.shape)
+    grad = ctx.conv2d_grad_y if kind == "conv" else ctx.deconv2d_grad_y
+
+    def one():
+        ar.before_write()
+        ctx.zero(DW)
+        if hi > lo:
+            grad(X, W, DW, DZ, *meta)
+        ar.start()
+        ar.finish()
+
+    for _ in range(3):
+        one()
+    dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    iters = 10
+    e0.record()
+    for _ in range(iters):
+        one()
+    e1.record()
+    torch.cuda.synchronize()
+    t = torch.tensor([e0.elapsed_time(e1) / iters], device=device, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    got = ar.result.view(W.shape).cpu().numpy()
+    # every rank must hold the same bits
+    probe = ar.result.clone()
+    parts = [torch.empty_like(probe) for _ in range(world)]
+    dist.all_gather(parts, probe)
+    same = all(torch.equal(parts[0], p) for p in parts[1:])
+    err = None
+    if rank == 0:
+        from oracle import pyoracle
+        oracle = pyoracle.Restated()
+        want = oracle.conv2d_grad_y(x, w, dz, *meta) if kind == "conv" else oracle.deconv2d_grad_y(x, w, dz, *meta)
+        sys.path.insert(0, os.path.join(ROOT, "tests"))
+        import cases
+        err = cases.rel_max(got, want)
+    dist.barrier()
+    ar.close()
+    return {"workload": name, "images_per_gpu": hi - lo, "filter_gradient_bytes": W.numel() * 4, "ms_gradient_plus_exchange": float(t.item()),
+            "max_rel_err_vs_oracle_whole_batch": err, "same_bits_on_every_rank": bool(same),
+            "path": "PeerAllReduce: partial gradient in peer-mapped memory, copy-engine pull of the owned shard, fixed-order sum kernel, "
+                    "copy-engine push to every peer"}
+
+
 def run_gpu_arm(args):
     import torch
     import deep8_b200
@@ -350,6 +561,7 @@ def run_gpu_arm(args):
     stream = torch.cuda.current_stream()
     ctx.use_stream(stream if stream.cuda_stream != 0 else None)
     exchange = None
+    ctx_side = side = None
     mode = os.environ.get("D8_BENCH_ALLREDUCE", "fused")
     if world > 1 and mode in ("peer", "fused"):
         # gradient exchange through peer memory on a side stream (deep8_b200.dp.PeerAllReduce); D8_BENCH_ALLREDUCE=overlap
@@ -361,6 +573,7 @@ def run_gpu_arm(args):
         # waits between ranks give up after 20 s here (first steps include module loading on every rank); the default is 2 s
         exchange = lambda numel, rows: PeerAllReduce(ctx, ctx_side, side, numel, torch.float16, device, rows=rows, with_weights=args.sgd,
                                                      timeout_ms=20000.0, gather=os.environ.get("D8_BENCH_GATHER", "copy"))
+    step_dist = None if mode == "none" else dist  # "none": the ranks run side by side and nothing is summed (diagnostic)
     mlp = MlpStep(ctx, torch, device, rank, fused=not args.unfused, exchange=exchange,
                   scatter=exchange is not None and mode == "fused" and not args.unfused, sgd=args.sgd)
 
@@ -376,37 +589,75 @@ def run_gpu_arm(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
-    for _ in range(args.warmup):
-        mlp.step(dist)
+    def status_ok():
+        return ctx.status() == 0 and (ctx_side is None or ctx_side.status() == 0)
+
     barrier()
-    if ctx.status() != 0 or (exchange is not None and ctx_side.status() != 0):
+    w0, w1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    w0.record()
+    for _ in range(args.warmup):
+        mlp.step(step_dist)
+    mlp.drain()
+    w1.record()
+    barrier()
+    if not status_ok():
         raise SystemExit("kernel status non-zero after warm-up")
+    # Pre-heat: the same step, untimed, for about `--preheat` seconds, so that the timed region runs at the clock the power
+    # limit settles on rather than at the boost clock of a cold start.  Every rank runs the same number of steps.
+    preheat_steps, preheat_s = 0, 0.0
+    if args.preheat > 0 and not args.profile:
+        warm_ms = max_over_ranks(w0.elapsed_time(w1) / max(1, args.warmup))
+        preheat_steps = max(1, int(math.ceil(args.preheat * 1e3 / max(warm_ms, 0.1))))
+        th = time.perf_counter()
+        for _ in range(preheat_steps):
+            mlp.step(step_dist)
+        mlp.drain()
+        barrier()
+        preheat_s = time.perf_counter() - th
 
     # ---- device-resident timed region
-    sampler = ClockSampler(local_rank)
+    sampler = None
     if rank == 0 and not args.profile:
+        sampler = NvmlSampler(torch, local_rank)
+        if not sampler.available():
+            sampler = SmiSampler(local_rank)
         sampler.start()
-        time.sleep(0.3)
     launches0 = ctx.launch_count()
     barrier()
+    host_t0 = time.perf_counter()
     t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     t0.record()
     for _ in range(args.steps):
-        mlp.step(dist, timed=True)
+        mlp.step(step_dist, timed=True)
+    mlp.drain(timed=True)
     t1.record()
+    torch.cuda.synchronize()
+    host_t1 = time.perf_counter()
     barrier()
     launches = ctx.launch_count() - launches0
-    clocks = sampler.stop() if (rank == 0 and not args.profile) else None
-    ms_total = max_over_ranks(t0.elapsed_time(t1))
-    ms_step = ms_total / args.steps
+    clocks = None
+    if sampler is not None:
+        sampler.stop()
+        clocks = sampler.report(host_t0, host_t1)
+    my_ms = t0.elapsed_time(t1) / args.steps
+    ms_step = max_over_ranks(t0.elapsed_time(t1)) / args.steps
     gemm_ms = [a.elapsed_time(b) for a, b in mlp.gemm_events]
     mlp.gemm_events = []
-    if os.environ.get("D8_BENCH_DIAG"):  # per rank: where the step's time went
-        tail = [a.elapsed_time(b) for a, b in mlp.tail_events]
-        print("rank %d: step %.3f ms, contractions %.3f ms, exchange left after the last contraction %.3f ms" %
-              (rank, t0.elapsed_time(t1) / args.steps, sum(gemm_ms) / args.steps, sum(tail) / max(1, args.steps)), file=sys.stderr, flush=True)
+    per_gemm = [sum(gemm_ms[i::6]) / max(1, len(gemm_ms[i::6])) for i in range(6)]   # mean of each of the six contractions
+    tail_ms = sum(a.elapsed_time(b) for a, b in mlp.tail_events) / args.steps
     mlp.tail_events = []
-    if ctx.status() != 0 or (exchange is not None and ctx_side.status() != 0):
+    # every rank's step, contraction and exchange-wait times, so that the line shows the spread between GPUs
+    mine = torch.tensor([my_ms, sum(gemm_ms) / args.steps, tail_ms] + per_gemm, device=device, dtype=torch.float64)
+    if dist is not None:
+        allr = [torch.empty_like(mine) for _ in range(world)]
+        dist.all_gather(allr, mine)
+        table = torch.stack(allr).cpu().numpy()
+    else:
+        table = mine.cpu().numpy()[None, :]
+    if os.environ.get("D8_BENCH_DIAG"):  # per rank: where the step's time went
+        print("rank %d: step %.3f ms, contractions %.3f ms (%s), waiting for the exchange %.3f ms" %
+              (rank, my_ms, sum(gemm_ms) / args.steps, " ".join("%.3f" % v for v in per_gemm), tail_ms), file=sys.stderr, flush=True)
+    if not status_ok():
         raise SystemExit("kernel status non-zero after the timed region")
 
     if args.profile:
@@ -416,6 +667,21 @@ def run_gpu_arm(args):
             dist.barrier()
             dist.destroy_process_group()
         return
+
+    # ---- correctness of the exchange, outside the timed region
+    xcheck = None
+    filt = None
+    if dist is not None and exchange is not None:
+        bad, slabs = exchange_check(mlp, ctx, torch, dist, device, world, rank)
+        xcheck = {"result": "bit-exact" if bad == 0 else "MISMATCH", "slabs_compared": slabs, "mismatching": bad,
+                  "what": "dW1 and dW2 after the last timed step against the rank-ordered fp32 sum of every rank's recomputed partial "
+                          "gradient (first and last 128 rows of each owner's block, gathered over NCCL)"}
+        if not args.no_aux:
+            filt = {"config 3": filter_gradient_exchange(3, ctx, ctx_side, side, torch, dist, device, world, rank),
+                    "config 4": filter_gradient_exchange(4, ctx, ctx_side, side, torch, dist, device, world, rank)}
+        if not status_ok():
+            raise SystemExit("kernel status non-zero after the exchange checks")
+
     # ---- end-to-end: X and dY from pinned host memory every step, Y back to the host.  Copies run on their own
     # streams into the other half of the double buffers, so step i computes while step i+1 arrives and step i-1 leaves.
     hX = torch.empty(mlp.X[0].shape, dtype=torch.float16).pin_memory()
@@ -427,7 +693,7 @@ def run_gpu_arm(args):
     s_in, s_out = torch.cuda.Stream(device=device), torch.cuda.Stream(device=device)
     main = torch.cuda.current_stream()
 
-    def e2e_loop(n):
+    def e2e_loop(n, compute=True):
         in_ready = [None, None]    # event: inputs of buffer b have arrived
         out_done = [None, None]    # event: Y of buffer b has left
         comp_done = [None, None]   # event: the step that used buffer b has finished
@@ -450,7 +716,8 @@ def run_gpu_arm(args):
             main.wait_event(in_ready[b])
             if out_done[b] is not None:
                 main.wait_event(out_done[b])            # Y[b] of two steps ago has been read
-            mlp.step(dist, buf=b)
+            if compute:
+                mlp.step(step_dist, buf=b)
             comp_done[b] = torch.cuda.Event()
             comp_done[b].record(main)
             with torch.cuda.stream(s_out):
@@ -458,17 +725,24 @@ def run_gpu_arm(args):
                 hY[b].copy_(mlp.Y[b], non_blocking=True)
                 out_done[b] = torch.cuda.Event()
                 out_done[b].record(s_out)
+        if compute:
+            mlp.drain()
         main.wait_stream(s_out)
         main.wait_stream(s_in)
 
-    e2e_loop(2)
-    barrier()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    e2e_loop(e2e_steps)
-    e1.record()
-    barrier()
-    e2e_ms = max_over_ranks(e0.elapsed_time(e1)) / e2e_steps
+    def timed_loop(compute):
+        e2e_loop(2, compute)
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        e2e_loop(e2e_steps, compute)
+        e1.record()
+        barrier()
+        return max_over_ranks(e0.elapsed_time(e1)) / e2e_steps
+
+    e2e_ms = timed_loop(True)
+    # the same copies on the same buffers and streams with no kernel in between: the host-link ceiling of this box at this N
+    copy_ms = timed_loop(False)
     h2d = hX.numel() * 2 + hdY.numel() * 2
     d2h = hY[0].numel() * 2
 
@@ -477,6 +751,9 @@ def run_gpu_arm(args):
         avg_gemm_ms = sum(gemm_ms) / len(gemm_ms)
         achieved = FLOP_PER_GEMM / (avg_gemm_ms * 1e-3) / 1e12
         per_gpu = FLOP_PER_STEP / (ms_step * 1e-3) / 1e12
+        sm_mhz = clocks.get("sm_mhz") if clocks else None
+        contractions = [{"name": CONTRACTIONS[i] if not args.unfused else CONTRACTIONS[i].split(" (")[0], "ms_rank0": float(table[0, 3 + i]),
+                         "ms_min_over_ranks": float(table[:, 3 + i].min()), "ms_max_over_ranks": float(table[:, 3 + i].max())} for i in range(6)]
         line = {
             "metric": METRIC, "value": per_gpu * world, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16 (f32 accumulate)",
@@ -484,102 +761,117 @@ def run_gpu_arm(args):
                                                   else "reference call sequence (zero fill, separate ReLU passes)") +
                                                   (" + SGD step (outside the metric's work)" if args.sgd else "")),
             "per_gpu_tflops": per_gpu, "frac_of_nominal_fp16_peak": per_gpu / NOMINAL_FP16_TFLOPS,
+            "preheat_s": preheat_s, "preheat_steps": preheat_steps,
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
                          "traffic": TRAFFIC_BYTES_PER_LAUNCH, "kernel": "d8k_gemm_pair_kernel (TMA-fed fp16, CTA pairs on 256x256 tiles)",
                          "peak_source": peak_src, "flop_per_launch": FLOP_PER_GEMM, "avg_launch_ms": avg_gemm_ms,
-                         "gemm_share_of_step": sum(gemm_ms) / (ms_step * args.steps)},
+                         "mcycles_per_launch": (avg_gemm_ms * 1e-3 * sm_mhz) if sm_mhz else None,
+                         "gemm_share_of_step": sum(gemm_ms) / (my_ms * args.steps)},
+            "contractions": contractions,
+            "ranks": {"step_ms": [float(table[:, 0].min()), float(table[:, 0].max())],
+                      "contractions_ms": [float(table[:, 1].min()), float(table[:, 1].max())],
+                      "waiting_for_exchange_ms": [float(table[:, 2].min()), float(table[:, 2].max())],
+                      "note": "[min, max] over ranks of each rank's own per-step means; a step's exchange is waited for inside the next step"},
             "e2e": {"value": FLOP_PER_STEP * world / (e2e_ms * 1e-3) / 1e12, "unit": UNIT, "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms, "steps": e2e_steps,
-                    "overlap": "copies on side streams, double-buffered inputs and outputs", "host_numa_node_rank0": numa_node},
+                    "overlap": "copies on side streams, double-buffered inputs and outputs", "host_numa_node_rank0": numa_node,
+                    "copy_only_ms": copy_ms, "copy_only_gbs_per_gpu": (h2d + d2h) / (copy_ms * 1e-3) / 1e9,
+                    "copy_only_gbs_aggregate": world * (h2d + d2h) / (copy_ms * 1e-3) / 1e9,
+                    "e2e_over_max_of_copy_and_compute": e2e_ms / max(copy_ms, ms_step)},
             "gpu_launches": launches, "clocks": clocks,
         }
+        if xcheck is not None:
+            line["exchange_check"] = xcheck["result"]
+            line["exchange_check_detail"] = xcheck
+        if filt is not None:
+            line["filter_gradient_exchange"] = filt
         if world == 1 and not args.no_cpu:
             line["cpu_baseline"], _ = cpu_arm(1, 0)
+        if world == 1 and not args.no_aux:
+            # BASELINE configurations 1-4 with their own inputs: an auxiliary report, outside the headline's timed region
+            line["aux"] = [run_small(ctx, torch, device, n, steps=20, warmup=3, half=False, with_cpu=not args.no_cpu) for n in (1, 2, 3, 4)]
         print(json.dumps(line), flush=True)
     if dist is not None:
         dist.barrier()
+        if xcheck is not None and xcheck["mismatching"]:
+            dist.destroy_process_group()
+            raise SystemExit("the exchanged gradients differ from the sum of the partial gradients")
         dist.destroy_process_group()
 
 
-# DRAM bytes (read + write) of one contraction launch of this workload: mean of the three launches of the default step captured with ncu
-# (profiles/d8k_gemm_pair_kernel_f16_mlp_config5.md); algorithmic bytes are 0.47e9.
+# DRAM bytes (read + write) of one contraction launch of this workload: mean over the launches of one step captured with ncu;
+# the algorithmic bytes are 0.47e9.
 TRAFFIC_BYTES_PER_LAUNCH = 1.28e9
 
 
 # ------------------------------------------------------------------------------------------------ configs 1-4 (fp32)
-def run_small_config(args):
-    """BASELINE configurations 1-4 (fp32, 3xTF32): forward + gradient of x + gradient of y of ONE operator on one GPU,
+def small_config_case(n):
+    """(name, x, w, dz, kind, meta, flop) of BASELINE configuration n in 1..4, inputs drawn as the configuration states
+    (numpy Philox streams named by the configuration's seeds; the second operand of configurations 1 and 2 uses seed + 10)."""
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import cases
+    if n == 1:
+        return ("fp32 MatrixMultiply 256x512 * 512x128", cases.uniform(0, (1, 256, 512)), cases.uniform(10, (1, 512, 128)),
+                cases.uniform(1, (1, 256, 128)), "matmul", None, 3 * 2.0 * 256 * 512 * 128)
+    if n == 2:
+        return ("fp32 MatrixMultiply batch 64 of 128x256 * batch 1 of 256x256", cases.normal(2, (64, 128, 256), 0.05),
+                cases.normal(12, (1, 256, 256), 0.05), cases.normal(3, (64, 128, 256)), "matmul", None, 3 * 2.0 * 8192 * 256 * 256)
+    if n == 3:
+        return ("fp32 Conv2d 32x56x56x64, 3x3x64 -> 64, stride 1, covered", cases.uniform(4, (32, 56, 56, 64)),
+                cases.normal(5, (64, 3, 3, 64), (2.0 / 576) ** 0.5), cases.normal(6, (32, 56, 56, 64)), "conv", (True, (1, 1), (1, 1)),
+                3 * 2.0 * 100352 * 576 * 64)
+    return ("fp32 DeConv2d 16x14x14x256, 4x4x256 -> 128, stride 2, covered (output 27x27)", cases.uniform(7, (16, 14, 14, 256)),
+            cases.normal(8, (128, 4, 4, 256), 1.0 / 64), cases.normal(9, (16, 27, 27, 128)), "deconv", (True, (2, 2)),
+            3 * 2.0 * 3136 * 256 * 2048)
+
+
+def run_small(ctx, torch, dev, n, steps, warmup, half, with_cpu):
+    """BASELINE configuration n in 1..4 (fp32, 3xTF32): forward + gradient of x + gradient of y of ONE operator on one GPU,
     timed with CUDA events with an L2 flush between iterations, checked against the oracle, with the reference's CPU
-    code timed beside it.  An auxiliary report (one JSON line), not the benchmark line of the default run."""
-    import torch
-    import deep8_b200
+    code timed beside it.  Returns the report as a dict."""
     from oracle import pyoracle
     sys.path.insert(0, os.path.join(ROOT, "tests"))
     import cases
 
-    n = args.config
-    dev = torch.device("cuda", 0)
-    ctx = deep8_b200.Context(0)
-    if n == 1:
-        name = "fp32 MatrixMultiply 256x512 * 512x128"
-        x, w = cases.uniform(0, (1, 256, 512)), cases.uniform(10, (1, 512, 128))
-        dz = cases.uniform(1, (1, 256, 128))
-        kind, meta, flop = "matmul", None, 3 * 2.0 * 256 * 512 * 128
-    elif n == 2:
-        name = "fp32 MatrixMultiply batch 64 of 128x256 * batch 1 of 256x256"
-        x, w = cases.normal(2, (64, 128, 256), 0.05), cases.normal(12, (1, 256, 256), 0.05)
-        dz = cases.normal(3, (64, 128, 256))
-        kind, meta, flop = "matmul", None, 3 * 2.0 * 8192 * 256 * 256
-    elif n == 3:
-        name = "fp32 Conv2d 32x56x56x64, 3x3x64 -> 64, stride 1, covered"
-        x, w = cases.uniform(4, (32, 56, 56, 64)), cases.normal(5, (64, 3, 3, 64), (2.0 / 576) ** 0.5)
-        dz = cases.normal(6, (32, 56, 56, 64))
-        kind, meta, flop = "conv", (True, (1, 1), (1, 1)), 3 * 2.0 * 100352 * 576 * 64
-    else:
-        name = "fp32 DeConv2d 16x14x14x256, 4x4x256 -> 128, stride 2, covered (output 27x27)"
-        x, w = cases.uniform(7, (16, 14, 14, 256)), cases.normal(8, (128, 4, 4, 256), 1.0 / 64)
-        dz = cases.normal(9, (16, 27, 27, 128))
-        kind, meta, flop = "deconv", (True, (2, 2)), 3 * 2.0 * 3136 * 256 * 2048
+    name, x, w, dz, kind, meta, flop = small_config_case(n)
     tdtype, tol, label = torch.float32, 1e-5, "f32 (3xTF32)"
-    if args.half:  # the same operator on fp16 storage (fp32 accumulation); the oracle sees the rounded inputs
+    if half:  # the same operator on fp16 storage (fp32 accumulation); the oracle sees the rounded inputs
         tdtype, tol, label = torch.float16, 2e-2, "f16 (f32 accumulate)"
         x, w, dz = (a.astype("float16").astype("float32") for a in (x, w, dz))
     X, W, DZ = (torch.from_numpy(a).to(dev).to(tdtype) for a in (x, w, dz))
     DX, DW = torch.zeros_like(X), torch.zeros_like(W)
-
+    Z = torch.empty(tuple(dz.shape), device=dev, dtype=tdtype)
     paths = {}  # which kernel variant each contraction took (d8k_last_kernel)
 
     def step():
         ctx.zero(DX)
         ctx.zero(DW)
         if kind == "matmul":
-            z = ctx.matmul_forward(X, W, out=Z)
+            ctx.matmul_forward(X, W, out=Z)
             paths["forward"] = ctx.last_kernel()
             ctx.matmul_grad_x(X, DX, W, DZ)
             paths["grad_x"] = ctx.last_kernel()
             ctx.matmul_grad_y(X, W, DW, DZ)
         elif kind == "conv":
-            z = ctx.conv2d_forward(X, W, *meta, out=Z)
+            ctx.conv2d_forward(X, W, *meta, out=Z)
             paths["forward"] = ctx.last_kernel()
             ctx.conv2d_grad_x(X, DX, W, DZ, *meta)
             paths["grad_x"] = ctx.last_kernel()
             ctx.conv2d_grad_y(X, W, DW, DZ, *meta)
         else:
-            z = ctx.deconv2d_forward(X, W, *meta, out=Z)
+            ctx.deconv2d_forward(X, W, *meta, out=Z)
             paths["forward"] = ctx.last_kernel()
             ctx.deconv2d_grad_x(X, DX, W, DZ, *meta)
             paths["grad_x"] = ctx.last_kernel()
             ctx.deconv2d_grad_y(X, W, DW, DZ, *meta)
         paths["grad_y"] = ctx.last_kernel()
-        return z
 
-    Z = torch.empty(tuple(dz.shape), device=dev, dtype=tdtype)
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)  # larger than the 126 MB L2
-    for _ in range(max(args.warmup, 3)):
+    for _ in range(max(warmup, 3)):
         step()
     torch.cuda.synchronize()
     times = []
-    for _ in range(args.steps):
+    for _ in range(steps):
         flush.zero_()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
@@ -587,8 +879,15 @@ def run_small_config(args):
         e1.record()
         torch.cuda.synchronize()
         times.append(e0.elapsed_time(e1))
-    assert ctx.status() == 0
+    if ctx.status() != 0:
+        raise SystemExit("kernel status non-zero in configuration %d" % n)
     ms = statistics.median(times)
+    line = {"report": "config %d" % n, "workload": name.replace("fp32", "fp16") if half else name, "dtype": label, "ms_per_step": ms,
+            "tflops": flop / ms / 1e9,
+            ("frac_of_fp16_peak" if half else "frac_of_tf32_peak_over_3"): flop / ms / 1e9 / (2250.0 if half else 1100.0 / 3),
+            "l2": "flushed between iterations (256 MiB write)", "steps": steps, "kernels": dict(paths), "cpu": None}
+    if not with_cpu:
+        return line
     # parity against the oracle and the reference's CPU time
     oracle = pyoracle.Restated()
     ref = pyoracle.Reference() if pyoracle.Reference.available() else oracle
@@ -600,13 +899,10 @@ def run_small_config(args):
             return impl.conv2d_forward(x, w, *meta), impl.conv2d_grad_x(x, w, dz, *meta), impl.conv2d_grad_y(x, w, dz, *meta)
         return impl.deconv2d_forward(x, w, *meta), impl.deconv2d_grad_x(x, w, dz, *meta), impl.deconv2d_grad_y(x, w, dz, *meta)
 
-    if args.no_cpu:
-        print(json.dumps({"report": "config %d" % n, "workload": name, "dtype": label, "ms_per_step": ms, "tflops": flop / ms / 1e9,
-                          "steps": args.steps, "kernels": paths, "cpu": None}), flush=True)
-        return
     want = cpu(oracle)
     got = (Z.float().cpu().numpy(), DX.float().cpu().numpy(), DW.float().cpu().numpy())
-    err = max(cases.rel_max(g, r) for g, r in zip(got, want))
+    line["max_rel_err_vs_oracle"] = max(cases.rel_max(g, r) for g, r in zip(got, want))
+    line["tolerance"] = tol
     cpu(ref)
     cpu_times = []
     for _ in range(3):
@@ -614,14 +910,16 @@ def run_small_config(args):
         cpu(ref)
         cpu_times.append(time.perf_counter() - t0)
     cpu_ms = min(cpu_times) * 1e3
-    line = {"report": "config %d" % n, "workload": name.replace("fp32", "fp16") if args.half else name, "dtype": label, "ms_per_step": ms,
-            "tflops": flop / ms / 1e9,
-            ("frac_of_fp16_peak" if args.half else "frac_of_tf32_peak_over_3"): flop / ms / 1e9 / (2250.0 if args.half else 1100.0 / 3),
-            "max_rel_err_vs_oracle": err, "tolerance": tol,
-            "l2": "flushed between iterations (256 MiB write)", "steps": args.steps, "kernels": paths,
-            "cpu": {"ms": cpu_ms, "kind": ref.kind, "threads": 1 if kind == "matmul" else ref.threads(),
-                    "gflops": flop / cpu_ms / 1e6}}
-    print(json.dumps(line), flush=True)
+    line["cpu"] = {"ms": cpu_ms, "kind": ref.kind, "threads": 1 if kind == "matmul" else ref.threads(), "gflops": flop / cpu_ms / 1e6}
+    return line
+
+
+def run_small_config(args):
+    """`--config N` with N in 1..4: the auxiliary report of one configuration as its own JSON line."""
+    import torch
+    import deep8_b200
+    ctx = deep8_b200.Context(0)
+    print(json.dumps(run_small(ctx, torch, torch.device("cuda", 0), args.config, args.steps, args.warmup, args.half, not args.no_cpu)), flush=True)
 
 
 def main():
@@ -633,6 +931,9 @@ def main():
     ap.add_argument("--config", type=int, default=5, choices=[1, 2, 3, 4, 5], help="BASELINE configuration; 5 (default) is the benchmark "
                     "line, 1-4 print an auxiliary fp32 report for one operator")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-aux", action="store_true", help="skip the auxiliary reports (configurations 1-4 on one GPU; the Conv2d/DeConv2d "
+                    "filter-gradient exchange on several)")
+    ap.add_argument("--preheat", type=float, default=2.0, help="seconds of untimed steps before the timed region (0 = none)")
     ap.add_argument("--half", action="store_true", help="with --config: run the configuration's operator on fp16 storage")
     ap.add_argument("--sgd", action="store_true",
                     help="add the reference's SGD step on W1, W2 to every step (not part of the metric's forward + backward): "

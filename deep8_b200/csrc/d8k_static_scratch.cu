@@ -11,8 +11,8 @@
 // once per device with that device current (the first call on a device does it: make that call before any stream
 // capture).  The entry point calls no cudaMalloc, cudaFree or allocating library routine.
 //
-// All calls on a device share the array and it keeps the previous call's contents: the tile tickets are cleared on the
-// stream at the start of every call, partial tiles are always written before they are read, and two calls whose kernels
+// All calls on a device share the array and it keeps the previous call's contents: the tile tickets a split launch uses are cleared on
+// the stream before it, partial tiles are always written before they are read, and two calls whose kernels
 // overlap on the GPU (different streams, or different host threads) race on it - serialise them.
 #include <mutex>
 #include <string>
@@ -92,9 +92,6 @@ extern "C" int d8k_gemm_static(int dtype, int transA, int transB, int M, int N, 
         return fail(D8K_ERR_ARGUMENT, "d8k_gemm_static: this contraction needs " + std::to_string(need) +
                                           " bytes of split-K scratch, the static maximum is " + std::to_string(kStaticScratchBytes) +
                                           "; use d8k_gemm with a context");
-    if (need > 0) {  // tickets must start at zero whatever an earlier call left behind
-        cudaError_t e = cudaMemsetAsync(ctx.counters, 0, kMaxCounters * sizeof(int), ctx.stream);
-        if (e != cudaSuccess) return fail(D8K_ERR_CUDA, std::string("d8k_gemm_static: cudaMemsetAsync: ") + cudaGetErrorString(e));
-    }
+    // tickets must start at zero whatever an earlier call left behind: run_gemm clears the ones a split launch uses, on the stream
     return run_gemm(&ctx, g);
 }

@@ -81,6 +81,22 @@ __device__ __forceinline__ void tma_load_4d_pair(uint32_t dst, const void* tmap,
         ::"r"(dst), "l"(tmap), "r"(bar_cluster_addr), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
         : "memory");
 }
+// the same load with an L2 eviction priority (createpolicy value)
+__device__ __forceinline__ void tma_load_4d_pair_hint(uint32_t dst, const void* tmap, uint32_t bar_cluster_addr, int c0, int c1, int c2, int c3,
+                                                      uint64_t policy) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%3, %4, %5, %6}], [%2], %7;"
+        ::"r"(dst), "l"(tmap), "r"(bar_cluster_addr), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "l"(policy)
+        : "memory");
+}
+// L2 eviction priority for loads: 0 normal, 1 evict first, 2 evict last
+__device__ __forceinline__ uint64_t l2_policy(int kind) {
+    uint64_t pol;
+    if (kind == 2) asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(pol));
+    else if (kind == 1) asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+    else asm volatile("createpolicy.fractional.L2::evict_normal.b64 %0, 1.0;" : "=l"(pol));
+    return pol;
+}
 __device__ __forceinline__ void tmem_alloc_pair(uint32_t smem_dst, uint32_t ncols) {
     asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(ncols) : "memory");
 }
@@ -123,15 +139,17 @@ __device__ __forceinline__ PairWork decode_pair_work(const GemmParams& p, int w)
     int tpb = p.tiles_m * p.tiles_n;
     it.batch = w / tpb;
     int t = w - it.batch * tpb;
-    int group_size = p.raster_group * p.tiles_n;
+    // groups of `raster_group` tiles along one axis sweep the whole other axis, fastest along the grouped axis
+    const int along = p.raster_n ? p.tiles_n : p.tiles_m, across = p.raster_n ? p.tiles_m : p.tiles_n;
+    int group_size = p.raster_group * across;
     int gid = t / group_size;
-    int first_m = gid * p.raster_group;
-    int gm = min(p.tiles_m - first_m, p.raster_group);
+    int first = gid * p.raster_group;
+    int g = min(along - first, p.raster_group);
     int in_group = t - gid * group_size;
-    int nt = in_group / gm;
-    int mt = first_m + (in_group - nt * gm);
-    it.m0 = mt * 256;
-    it.n0 = nt * 256;
+    int sweep = in_group / g;
+    int pos = first + (in_group - sweep * g);
+    it.m0 = (p.raster_n ? sweep : pos) * 256;
+    it.n0 = (p.raster_n ? pos : sweep) * 256;
     return it;
 }
 
@@ -200,6 +218,8 @@ d8k_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
         bool ok = true;
         long long waited = 0;
         const long long t_begin = p.prof ? clock64() : 0;
+        const bool hinted = (p.l2_a | p.l2_b) != 0;
+        const uint64_t pol_a = ptx::l2_policy(p.l2_a), pol_b = ptx::l2_policy(p.l2_b);
         for (int w = pair; ok && w < p.total_work; w += num_pairs) {
             PairWork it = decode_pair_work(p, w);
             const int my_m0 = it.m0 + 128 * static_cast<int>(rank);
@@ -219,10 +239,15 @@ d8k_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
                     const uint32_t bar = ptx::map_to_rank(full_bar(stage), 0);
                     if (leader) ptx::mbar_arrive_expect_tx(full_bar(stage), 2 * Cfg::STAGE_BYTES);
                     // K-major: {k in block, row, k-block, batch}; MN-major: {m/n in chunk, k, chunk of 64, batch}
-                    if constexpr (!Cfg::A_MN) ptx::tma_load_4d_pair(stage_a(stage), &tmA, bar, 0, my_m0, kb0, b % p.a_batch_mod);
-                    else ptx::tma_load_4d_pair(stage_a(stage), &tmA, bar, 0, kb0 * 64, my_m0 / 64, b % p.a_batch_mod);
-                    if constexpr (!Cfg::B_MN) ptx::tma_load_4d_pair(stage_b(stage), &tmB, bar, 0, my_n0, kb0, b % p.b_batch_mod);
-                    else ptx::tma_load_4d_pair(stage_b(stage), &tmB, bar, 0, kb0 * 64, my_n0 / 64, b % p.b_batch_mod);
+                    const int a1 = Cfg::A_MN ? kb0 * 64 : my_m0, a2 = Cfg::A_MN ? my_m0 / 64 : kb0;
+                    const int b1 = Cfg::B_MN ? kb0 * 64 : my_n0, b2 = Cfg::B_MN ? my_n0 / 64 : kb0;
+                    if (hinted) {
+                        ptx::tma_load_4d_pair_hint(stage_a(stage), &tmA, bar, 0, a1, a2, b % p.a_batch_mod, pol_a);
+                        ptx::tma_load_4d_pair_hint(stage_b(stage), &tmB, bar, 0, b1, b2, b % p.b_batch_mod, pol_b);
+                    } else {
+                        ptx::tma_load_4d_pair(stage_a(stage), &tmA, bar, 0, a1, a2, b % p.a_batch_mod);
+                        ptx::tma_load_4d_pair(stage_b(stage), &tmB, bar, 0, b1, b2, b % p.b_batch_mod);
+                    }
                 }
                 __syncwarp();
                 if (++stage == STAGES) { stage = 0; phase ^= 1; }
@@ -304,15 +329,34 @@ d8k_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
             PairWork it = decode_pair_work(p, w);
             const int row = it.m0 + 128 * static_cast<int>(rank) + row_in_tile;
             const long long crow = static_cast<long long>(it.batch) * p.c_batch_stride + static_cast<long long>(row) * p.ldc + scatter_offset(p, row);
+            const int warp_row0 = it.m0 + 128 * static_cast<int>(rank) + quarter * 32;  // first row of this warp
+            const long long warp_off = static_cast<long long>(it.batch) * p.c_batch_stride + static_cast<long long>(warp_row0) * p.ldc +
+                                       scatter_offset(p, warp_row0);
+            const int lr = lane >> 2, lc = lane & 3;  // coalesced pattern: row 8 i + lr, 16-byte chunk lc
+            // ReLu's input for the fused gradient tail is read once, from DRAM: the loads of a 32-column chunk are issued
+            // one chunk ahead (the first before the accumulator is even finished), so their latency overlaps the previous
+            // chunk's work instead of adding to every chunk - with four epilogue warps per CTA that latency, serialised,
+            // made the epilogue longer than a short-K tile's main loop.
+            uint4 pre[4] = {};
+            const bool prefetch = coalesced && p.epi == 2;
+            auto issue_e1 = [&](int c) {
+                const int pc0 = it.n0 + c * 32;
+                if (!prefetch || pc0 + 32 > p.N) return;
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const int rr = 8 * i + lr;
+                    if (warp_row0 + rr < p.M)
+                        pre[i] = __ldcs(reinterpret_cast<const uint4*>(reinterpret_cast<const OutT*>(p.E1) + warp_off + static_cast<long long>(rr) * p.ldc +
+                                                                       pc0 + lc * 8));
+                }
+            };
+            issue_e1(0);
             const long long tw = p.prof ? clock64() : 0;
-            ok = wait_bar(tfull_bar(acc), acc_phase, &s_abort, p.status, (kRoleEpilogue << 8) | 3);
+            ok = wait_bar(tfull_bar(acc), acc_phase, &s_abort, p.status, (kRoleEpilogue << 8) | 3, static_cast<unsigned>(p.epi_backoff_ns));
             if (!ok) break;
             if (p.prof) waited += clock64() - tw;
             ptx::tc_fence_after_sync();
             const uint32_t taddr = tmem_base + acc * 256 + (static_cast<uint32_t>(quarter * 32) << 16);
-            const int warp_row0 = it.m0 + 128 * static_cast<int>(rank) + quarter * 32;  // first row of this warp
-            const long long warp_off = static_cast<long long>(it.batch) * p.c_batch_stride + static_cast<long long>(warp_row0) * p.ldc +
-                                       scatter_offset(p, warp_row0);
 #pragma unroll 1
             for (int c = 0; c < 256 / 32; ++c) {
                 uint32_t r[32];
@@ -325,7 +369,6 @@ d8k_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
                     // Rows leave as whole 64-byte segments: the values cross from "one thread per row" (the tensor
                     // memory layout) to "four threads per row" through this warp's private staging slots.
                     const uint32_t s0 = staging + 0 * Cfg::SLOT_BYTES, s1 = staging + 1 * Cfg::SLOT_BYTES, s2 = staging + 2 * Cfg::SLOT_BYTES;
-                    const int lr = lane >> 2, lc = lane & 3;  // coalesced pattern: row 8 i + lr, 16-byte chunk lc
                     if (p.beta || p.epi == 2) {
 #pragma unroll
                         for (int i = 0; i < 4; ++i) {
@@ -334,11 +377,12 @@ d8k_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
                                 const long long e = warp_off + static_cast<long long>(rr) * p.ldc + col0 + lc * 8;
                                 if (p.beta) st_shared_v4(s0 + slot_off(rr, lc), *reinterpret_cast<const uint4*>(reinterpret_cast<const OutT*>(p.C) + e));
                                 if (p.epi == 2) {
-                                    st_shared_v4(s1 + slot_off(rr, lc), *reinterpret_cast<const uint4*>(reinterpret_cast<const OutT*>(p.E1) + e));
+                                    st_shared_v4(s1 + slot_off(rr, lc), pre[i]);
                                     if (p.beta2) st_shared_v4(s2 + slot_off(rr, lc), *reinterpret_cast<const uint4*>(reinterpret_cast<const OutT*>(p.E2) + e));
                                 }
                             }
                         }
+                        if (c + 1 < 256 / 32) issue_e1(c + 1);
                         __syncwarp();
                     }
                     using V = EpiVec<OutT>;

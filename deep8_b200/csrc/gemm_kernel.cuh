@@ -121,6 +121,12 @@ struct GemmParams {
     int num_kb;        // k-blocks per batch = ceil(K / BK)
     int splits, kb_per_split;
     int tiles_m, tiles_n, raster_group;
+    // Paired kernel only.  raster_n == 0: tiles are visited in groups of raster_group rows of tiles, each group sweeping all
+    // columns (the group's A strips are what successive waves share); raster_n == 1: groups of raster_group columns sweeping
+    // all rows (B strips shared).  l2_a / l2_b: L2 eviction priority of each operand's loads - 0 normal, 1 evict first
+    // (a strip that streams through once per group), 2 evict last (the strips successive waves come back to).
+    int raster_n, l2_a, l2_b;
+    int epi_backoff_ns;  // paired kernel: sleep between the epilogue warps' polls for a finished accumulator (0 = poll back to back)
     int total_work;    // batch * tiles_m * tiles_n * splits
     int beta;          // 0: overwrite, 1: accumulate into C
     int epi, beta2;    // fused element-wise tail, see store_row_chunk: 1 ReLU, 2 ReLU gradient, 3 bias row added (E1 = bias[N])

@@ -286,6 +286,55 @@ Plan make_plan(const Ctx* ctx, const GemmProblem& g, size_t scratch_limit) {
     return pl;
 }
 
+// Tile order of the paired kernel, chosen to keep DRAM traffic down when the operands exceed the L2.
+// A wave is the `pairs` tiles in flight together; all of them walk along K in step, so within a wave every distinct operand
+// strip (256 rows x K) is fetched from DRAM once.  With groups of g tiles along one axis sweeping the other axis a wave
+// touches about g + pairs / g strips.  If in addition the g strips of a group are small enough to stay in L2 while the
+// group's sweeps stream past (loads marked evict-last), later waves of the group find them there, and the traffic drops to
+// (resident operand once) + (number of groups) x (streamed operand).  The model below picks axis, g and residency by the
+// bytes each choice would read.
+struct Raster {
+    int group, along_n, l2_a, l2_b;
+};
+Raster pick_raster(long long M, long long N, long long K, int tiles_m, int tiles_n, int pairs) {
+    const double strip = 256.0 * static_cast<double>(K) * 2.0;
+    const double a_total = static_cast<double>(M) * K * 2.0, b_total = static_cast<double>(N) * K * 2.0;
+    const double budget = static_cast<double>(env_int("D8K_L2_RESIDENT_MB", 40)) * 1048576.0;
+    Raster best = {16, 0, 0, 0};
+    double best_cost = -1.0;
+    for (int along_n = 0; along_n < 2; ++along_n) {
+        const int along = along_n ? tiles_n : tiles_m;
+        const double res_total = along_n ? b_total : a_total, str_total = along_n ? a_total : b_total;
+        for (int g = 1; g <= along && g <= 32; ++g) {
+            const int groups = (along + g - 1) / g;
+            // strips of the group resident in L2 across its waves
+            if (g * strip <= budget && env_int("D8K_L2_HINTS", 0)) {
+                const double cost = res_total + groups * str_total;
+                if (best_cost < 0 || cost < best_cost * 0.999) {
+                    best_cost = cost;
+                    best = {g, along_n, along_n ? 1 : 2, along_n ? 2 : 1};
+                }
+            }
+            // no residency: every wave fetches the strips it touches (the last group may be narrower)
+            const int across = along_n ? tiles_m : tiles_n;
+            double cost = 0.0;
+            for (int first = 0; first < along; first += g) {
+                const int gi = along - first < g ? along - first : g;
+                cost += static_cast<double>(gi) * across / pairs * (gi + static_cast<double>(pairs) / gi) * strip;
+            }
+            if (best_cost < 0 || cost < best_cost * 0.999) {
+                best_cost = cost;
+                best = {g, along_n, 0, 0};
+            }
+        }
+    }
+    if (!env_int("D8K_L2_STREAM_FIRST", 1)) {  // the streamed operand at normal priority instead of evict-first
+        if (best.l2_a == 1) best.l2_a = 0;
+        if (best.l2_b == 1) best.l2_b = 0;
+    }
+    return best;
+}
+
 }  // namespace
 
 size_t gemm_scratch_need(const Ctx* ctx, const GemmProblem& g) {
@@ -326,7 +375,10 @@ int run_gemm(Ctx* ctx, const GemmProblem& g) {
         return 0;
     }
 
-    const bool own_scratch = g.ws == nullptr;
+    // The caller's scratch (a node's interim buffer) is used when it holds everything the split plan wants; a buffer that is
+    // missing, empty or smaller than that would silently cost splits, so the context's own scratch serves instead.
+    bool own_scratch = g.ws == nullptr || g.ws_bytes == 0;
+    if (!own_scratch && g.ws_bytes < ctx->scratch_bytes && make_plan(ctx, g, ctx->scratch_bytes).scratch > g.ws_bytes) own_scratch = true;
     float* scratch = own_scratch ? ctx->scratch : static_cast<float*>(g.ws);
     size_t scratch_limit = own_scratch ? ctx->scratch_bytes : g.ws_bytes;
     if (reinterpret_cast<uintptr_t>(scratch) & 15) return fail(1, "gemm: scratch memory must be 16-byte aligned");
@@ -343,7 +395,19 @@ int run_gemm(Ctx* ctx, const GemmProblem& g) {
     p.kb_per_split = pl.kb_per_split;
     p.tiles_m = pl.tiles_m;
     p.tiles_n = pl.tiles_n;
-    p.raster_group = env_int("D8K_RASTER", 16);  // rows of tiles per column sweep; 8 to 16 measure alike on config 5 (16 ahead by under 1 %), 2 and 32 are 5-7 % slower
+    p.raster_group = 16;
+    if (pl.pair && g.batch == 1) {
+        const Raster r = pick_raster(g.M, g.N, static_cast<long long>(g.K) * g.kbatch, pl.tiles_m, pl.tiles_n, ctx->num_sms / 2);
+        p.raster_group = r.group;
+        p.raster_n = r.along_n;
+        p.l2_a = r.l2_a;
+        p.l2_b = r.l2_b;
+    }
+    p.epi_backoff_ns = env_int("D8K_EPI_BACKOFF", 0);
+    if (env_int("D8K_RASTER", 0) > 0) p.raster_group = env_int("D8K_RASTER", 0);
+    if (env_int("D8K_RASTER_N", -1) >= 0) p.raster_n = env_int("D8K_RASTER_N", 0) ? 1 : 0;
+    if (env_int("D8K_L2_A", -1) >= 0) p.l2_a = env_int("D8K_L2_A", 0);
+    if (env_int("D8K_L2_B", -1) >= 0) p.l2_b = env_int("D8K_L2_B", 0);
     if (p.raster_group < 1) p.raster_group = 1;
     p.total_work = pl.tiles * pl.splits;
     p.beta = g.beta;
@@ -375,6 +439,8 @@ int run_gemm(Ctx* ctx, const GemmProblem& g) {
     p.ws = scratch;
     p.counters = ctx->counters;
     p.status = ctx->status;
+    if (const char* pp = std::getenv("D8K_PROF_PTR"))  // diagnostics: device address of 8 cycle counters per CTA (paired kernel)
+        p.prof = reinterpret_cast<long long*>(static_cast<uintptr_t>(std::strtoull(pp, nullptr, 0)));
     p.a_batch_mod = g.a.batch_count > 0 ? g.a.batch_count : 1;
     p.b_batch_mod = g.b.batch_count > 0 ? g.b.batch_count : 1;
 
@@ -414,6 +480,12 @@ int run_gemm(Ctx* ctx, const GemmProblem& g) {
         fn = pl.f32 ? lookup_f32_gather(g.a.mn, g.b.mn, pl.bn) : lookup_f16_gather(g.a.mn, g.b.mn, pl.bn);
     }
     if (!fn) return fail(2, "gemm: no kernel for this configuration");
+    if (pl.splits > 1) {
+        // Tile tickets must start at zero.  A kernel that gave up on a bounded wait leaves them half-counted, and the status
+        // word that says so may not have been read yet: clear the tickets this launch uses on the stream, every time.
+        cudaError_t ce = cudaMemsetAsync(ctx->counters, 0, static_cast<size_t>(pl.tiles) * sizeof(int), ctx->stream);
+        if (ce != cudaSuccess) return fail(2, std::string("gemm: cudaMemsetAsync: ") + cudaGetErrorString(ce));
+    }
     int grid = p.total_work < ctx->num_sms ? p.total_work : ctx->num_sms;
     if (pl.pair) grid = p.total_work < ctx->num_sms / 2 ? p.total_work : ctx->num_sms / 2;  // pairs
     cudaError_t e = fn(grid, ctx->stream, ta, tb, p);
@@ -425,6 +497,7 @@ int run_gemm(Ctx* ctx, const GemmProblem& g) {
         os << (pl.f32 ? "f32 " : "f16 ") << (pl.pair ? "pair" : pl.tma ? "tma" : "gather");
         if (pl.tma && !pl.pair) os << " a=" << kModes[pl.a_tma] << " b=" << kModes[pl.b_tma];
         os << " bn=" << (pl.pair ? 256 : pl.bn) << " splits=" << pl.splits << " grid=" << grid;
+        if (pl.pair) os << " raster=" << (p.raster_n ? "n" : "m") << p.raster_group << " l2=" << p.l2_a << p.l2_b;
         set_last_kernel(os.str());
     }
     return 0;

@@ -7,6 +7,7 @@
 #include <cuda_runtime.h>
 
 #include <cstdint>
+#include <cstdlib>
 #include <cstring>
 #include <string>
 
@@ -183,8 +184,12 @@ void launch_sum(const Ctx* ctx, void* out, const SrcList& srcs, int nsrc, size_t
                 const FlagList& copies, int ncopies) {
     constexpr int V = 16 / sizeof(T);
     size_t blocks = (count / V + 255) / 256;
-    // enough 16-byte loads in flight to cover HBM latency: each thread has nsrc (+1 with weights) per step
-    size_t cap = static_cast<size_t>(ctx->num_sms) * (nsrc <= 2 ? 8 : 4);
+    // One CTA of 256 threads per SM.  The sum runs beside a persistent contraction kernel and shares its SMs' issue slots:
+    // with 8 CTAs per SM (2048 extra threads) the contractions of a 2-GPU step took 5.40 ms, with one they took 5.22 ms -
+    // what they take with no exchange at all - and the sum (nsrc + 1 16-byte accesses in flight per thread) still ends
+    // long before the contractions behind it.  D8K_SUM_BLOCKS_PER_SM overrides.
+    static const int forced = [] { const char* v = std::getenv("D8K_SUM_BLOCKS_PER_SM"); return v ? std::atoi(v) : 0; }();
+    size_t cap = static_cast<size_t>(ctx->num_sms) * (forced > 0 ? forced : 1);
     if (blocks > cap) blocks = cap;
     if (blocks < 1) blocks = 1;
     dim3 grid(static_cast<unsigned>(blocks));

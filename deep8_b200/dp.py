@@ -219,7 +219,11 @@ class PeerAllReduce:
         """Call after the contraction that writes `partial` has been enqueued on the main stream.
         sgd = (learning_rate, weight_decay): the reference's SGD step (SGDTrainer::update) runs inside the sum on the shard
         this rank owns, and the all-gather carries the updated `weights`; `result` then holds only this rank's shard of
-        the summed gradient.  Every rank must pass the same values; `weights` must hold the same data on every rank."""
+        the summed gradient.  Every rank must pass the same values; `weights` must hold the same data on every rank.
+        From start(sgd=...) until finish() `weights` is being rewritten - this rank's shard by the sum kernel, the rest by
+        the peers' transfers - so nothing on any stream may read it in between: enqueue start(sgd=...) only after the last
+        contraction of the backward pass that reads the operand (the reference runs the whole backward pass before
+        SGDTrainer::update, deep8/src/trainer/Trainer.cpp:12-32), and finish() before the next forward pass."""
         coeff = None
         if sgd is not None:
             if self.weights is None:

@@ -25,6 +25,17 @@ def _p(t):
     return ctypes.c_void_p(t.data_ptr()) if t is not None else None
 
 
+def _out(out, shape, like):
+    """A caller-supplied output: same device, dtype and layout rules as the inputs and exactly the computed shape - a wrong
+    size here would otherwise become an out-of-bounds device write.  None allocates."""
+    if out is None:
+        return torch.empty(shape, dtype=like.dtype, device=like.device)
+    _same(like, out)
+    if tuple(out.shape) != tuple(shape):
+        raise ValueError("the shape is error")
+    return out
+
+
 def _same(*ts):
     d0 = ts[0]
     for t in ts:
@@ -106,7 +117,7 @@ class Context:
     def matmul_forward(self, x, y, out=None):
         dt = _same(x, y)
         xb, xr, xc, yb, yc = self._mm_dims(x, y)
-        z = out if out is not None else torch.empty((max(xb, yb), xr, yc), dtype=x.dtype, device=x.device)
+        z = _out(out, (max(xb, yb), xr, yc), x)
         check(self.lib.d8k_matmul_forward(self.h, dt, _p(x), xb, xr, xc, _p(y), yb, yc, _p(z)))
         return z
 
@@ -142,7 +153,7 @@ class Context:
         xb, xr, xc, yb, yc = self._mm_dims(x, y)
         if bias.numel() != yc:
             raise ValueError("the shape is error")
-        z = out if out is not None else torch.empty((max(xb, yb), xr, yc), device=x.device, dtype=x.dtype)
+        z = _out(out, (max(xb, yb), xr, yc), x)
         check(self.lib.d8k_matmul_forward_bias(self.h, dt, _p(x), xb, xr, xc, _p(y), yb, yc, _p(bias), _p(z)))
         return z
 
@@ -152,7 +163,7 @@ class Context:
         cols = x.shape[-1]
         if bias.numel() != cols:
             raise ValueError("the shape is error")
-        z = out if out is not None else torch.empty_like(x)
+        z = _out(out, tuple(x.shape), x)
         check(self.lib.d8k_add_bias(self.h, dt, _p(x), _p(bias), _p(z), x.numel() // cols, cols))
         return z
 
@@ -188,7 +199,7 @@ class Context:
     def conv2d_forward(self, x, w, covered=False, stride=(1, 1), dilation=(1, 1), out=None):
         dt = _same(x, w)
         b, oh, ow, oc = self.conv2d_out_shape(x, w, covered, stride, dilation)
-        z = out if out is not None else torch.empty((b, oh, ow, oc), dtype=x.dtype, device=x.device)
+        z = _out(out, (b, oh, ow, oc), x)
         _, ih, iw, ic = x.shape
         _, fh, fw, _ = w.shape
         check(self.lib.d8k_conv2d_forward(self.h, dt, _p(x), b, ih, iw, ic, _p(w), oc, fh, fw, _p(z), oh, ow, stride[0], stride[1],
@@ -230,7 +241,7 @@ class Context:
     def deconv2d_forward(self, x, w, covered=False, stride=(1, 1), out=None):
         dt = _same(x, w)
         b, oh, ow, oc = self.deconv2d_out_shape(x, w, covered, stride)
-        z = out if out is not None else torch.empty((b, oh, ow, oc), dtype=x.dtype, device=x.device)
+        z = _out(out, (b, oh, ow, oc), x)
         _, ih, iw, ic = x.shape
         _, fh, fw, _ = w.shape
         check(self.lib.d8k_deconv2d_forward(self.h, dt, _p(x), b, ih, iw, ic, _p(w), oc, fh, fw, _p(z), oh, ow, stride[0], stride[1], None, 0))
@@ -259,7 +270,7 @@ class Context:
     # ------------------------------------------------------------------------------------------------ neighbours
     def relu_forward(self, x, out=None):
         dt = _same(x)
-        y = out if out is not None else torch.empty_like(x)
+        y = _out(out, tuple(x.shape), x)
         check(self.lib.d8k_relu_forward(self.h, dt, _p(x), _p(y), x.numel()))
         return y
 
@@ -309,6 +320,9 @@ class Context:
         """dy = x^T * dz for a replicated y ([1, xc, yc]), rows [k * block_rows, ...) written to address row_blocks[k]."""
         dt = _same(x, dz)
         xb, xr, xc = x.shape
+        if tuple(dz.shape) != (xb, xr, yc) or block_rows < 128 or block_rows % 128 or not 1 <= len(row_blocks) <= 16 or \
+                len(row_blocks) * block_rows < xc:
+            raise ValueError("the shape is error")
         check(self.lib.d8k_matmul_grad_y_scatter(self.h, dt, _p(x), xb, xr, xc, yc, _p(dz), self._ptr_array(row_blocks),
                                                  len(row_blocks), block_rows))
 

@@ -130,8 +130,11 @@ D8K_API int d8k_deconv2d_out_dim(int in, int filter, int stride, int covered);
 
 /* Conv2dInterimSize / GradXInterimSize / GradYInterimSize and the DeConv2d ones (deep8/src/math/Conv2d.cpp:6-44, 98-137,
  * 195-234; DeConv2d.cpp:6-41, 84-120, 164-200).  The reference returns the byte size of its im2col column buffer; these
- * kernels build the tiles in shared memory, so the answer is 0 unless the call will run split-K and the caller wants to
- * supply the scratch itself (`interim`); with interim == NULL the context's scratch is used.
+ * kernels build the tiles in shared memory, so the answer is 0 unless the contraction would run split-K and the caller
+ * wants to supply the scratch itself (`interim`).  The size is computed for the undivided contraction (stride and dilation
+ * are not arguments of the reference's functions either); a strided call runs one contraction per residue class and may
+ * want less or more.  The operator entry points therefore treat `interim` as an offer: it is used when it holds what the
+ * launch wants, and the context's own scratch serves when interim is NULL, empty or smaller than that.
  * which: 0 forward, 1 gradient of x, 2 gradient of the filter. */
 D8K_API size_t d8k_conv2d_interim_size(const d8k_ctx* ctx, int which, int dtype, int batch, int ih, int iw, int ic, int oc, int fh, int fw,
                                int oh, int ow);

@@ -370,10 +370,17 @@ def test_scattered_grad_y_arguments_are_checked(ctx):
     x = torch.zeros((1, 64, 256), device="cuda", dtype=torch.float16)
     dz = torch.zeros((1, 64, 128), device="cuda", dtype=torch.float16)
     out = torch.zeros((256, 128), device="cuda", dtype=torch.float16)
-    with pytest.raises(D8kError):
+    # the front-end refuses bad block plans before anything is launched; the library has the same checks behind it
+    with pytest.raises(ValueError):
         ctx.matmul_grad_y_scatter(x, 128, dz, [out.data_ptr()], 100)       # not a multiple of 128
-    with pytest.raises(D8kError):
+    with pytest.raises(ValueError):
         ctx.matmul_grad_y_scatter(x, 128, dz, [out.data_ptr()], 128)       # one block of 128 rows does not cover 256
+    import ctypes
+    blocks = (ctypes.c_void_p * 1)(out.data_ptr())
+    rc = ctx.lib.d8k_matmul_grad_y_scatter(ctx.h, 0, ctypes.c_void_p(x.data_ptr()), 1, 64, 256, 128, ctypes.c_void_p(dz.data_ptr()), blocks, 1, 100)
+    assert rc == 1 and b"128" in ctx.lib.d8k_last_error()
+    rc = ctx.lib.d8k_matmul_grad_y_scatter(ctx.h, 0, ctypes.c_void_p(x.data_ptr()), 1, 64, 256, 128, ctypes.c_void_p(dz.data_ptr()), blocks, 1, 128)
+    assert rc == 1
     with pytest.raises(D8kError):
         ctx.matmul_grad_y_scatter(x, 128, dz, [out.data_ptr(), 0], 128)    # null block
     ctx.matmul_grad_y_scatter(x, 128, dz, [out.data_ptr(), out[128:].data_ptr()], 128)
@@ -558,6 +565,80 @@ def _fused_worker(rank, world, port, r, rows, cols, steps, out_dir, gather="copy
     with open(os.path.join(out_dir, "rank%d.txt" % rank), "w") as f:
         f.write("%d %d %d" % (int(ok), status[0], status[1]))
     dist.destroy_process_group()
+
+
+def _sgd_order_worker(rank, world, port, r, rows, cols, steps, out_dir):
+    """A backward pass with the trainer's step inside the exchange, in the order the exchange requires: the gradient of x,
+    which reads the weights, is enqueued BEFORE start(sgd=...).  It must equal the product with the weights as they were,
+    and the weights must end as sum -> round -> x * alpha + y * beta on every rank."""
+    sys.path.insert(0, ROOT)
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    import torch.distributed as dist
+    import deep8_b200
+    from deep8_b200.dp import PeerAllReduce, sgd_coefficients
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    main = torch.cuda.Stream(device=dev)
+    side = torch.cuda.Stream(device=dev)
+    c_main, c_side = deep8_b200.Context(rank), deep8_b200.Context(rank, 1 << 20)
+    c_main.use_stream(main)
+    c_side.use_stream(side)
+    ar = PeerAllReduce(c_main, c_side, side, rows * cols, torch.float16, dev, rows=rows, with_weights=True)
+    lr, wd = 0.05, 0.001
+    alpha, beta = sgd_coefficients(lr, wd)
+    ok = True
+
+    def inputs(s, q):
+        g = torch.Generator(device=dev).manual_seed(1000 * s + q)
+        return (torch.randn((1, r, rows), device=dev, generator=g).to(torch.float16),
+                torch.randn((1, r, cols), device=dev, generator=g).to(torch.float16))
+
+    with torch.cuda.stream(main):
+        w0 = (torch.randn(rows * cols, device=dev, generator=torch.Generator(device=dev).manual_seed(5)) * 0.1).to(torch.float16)
+        ar.weights.copy_(w0)
+        W = ar.weights.view(1, rows, cols)
+        for s in range(steps):
+            x, dz = inputs(s, rank)
+            w_before = W.clone()
+            ar.before_write()
+            ar.scatter_grad_y(x, dz)
+            dx = torch.empty_like(x)
+            c_main.matmul_grad_x(x, dx, W, dz, accumulate=False)   # the last reader of the weights in this backward pass
+            ar.start(sgd=(lr, wd))
+            ar.finish()
+            main.synchronize()
+            dx_want = torch.empty_like(x)
+            c_main.matmul_grad_x(x, dx_want, w_before, dz, accumulate=False)
+            main.synchronize()
+            ok = ok and torch.equal(dx, dx_want)
+            acc = np.zeros((rows, cols), dtype=np.float32)
+            part = torch.empty((1, rows, cols), device=dev, dtype=torch.float16)
+            for q in range(world):
+                xq, dzq = inputs(s, q)
+                c_main.matmul_grad_y(xq, part, part, dzq, accumulate=False)
+                main.synchronize()
+                acc = acc + part[0].cpu().numpy().astype(np.float32)
+            gsum = acc.astype(np.float16).astype(np.float32)
+            want = (gsum * np.float32(alpha) + w_before[0].cpu().numpy().astype(np.float32) * np.float32(beta)).astype(np.float16)
+            ok = ok and np.array_equal(W[0].cpu().numpy(), want)
+    status = (c_main.status(), c_side.status())
+    ar.close()
+    with open(os.path.join(out_dir, "rank%d.txt" % rank), "w") as f:
+        f.write("%d %d %d" % (int(ok), status[0], status[1]))
+    dist.destroy_process_group()
+
+
+@pytest.mark.gpu
+def test_two_gpu_sgd_inside_exchange_after_the_last_reader_of_the_weights(tmp_path):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    world = 2
+    mp.spawn(_sgd_order_worker, args=(world, _free_port(), 256, 512, 384, 3, str(tmp_path)), nprocs=world, join=True)
+    for q in range(world):
+        assert open(os.path.join(str(tmp_path), "rank%d.txt" % q)).read() == "1 0 0"
 
 
 @pytest.mark.gpu
