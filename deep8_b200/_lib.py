@@ -46,6 +46,16 @@ SIGNATURES = {
     "d8k_deconv2d_forward": (_i, [_vp, _i, _vp, _i, _i, _i, _i, _vp, _i, _i, _i, _vp, _i, _i, _i, _i, _vp, _sz]),
     "d8k_deconv2d_grad_x": (_i, [_vp, _i, _vp, _i, _i, _i, _i, _vp, _i, _i, _i, _vp, _i, _i, _i, _i, _vp, _sz]),
     "d8k_deconv2d_grad_y": (_i, [_vp, _i, _vp, _i, _i, _i, _i, _vp, _i, _i, _i, _vp, _i, _i, _i, _i, _vp, _sz]),
+    "d8k_conv2d_grad_x_into": (_i, [_vp, _i, _vp, _i, _i, _i, _i, _vp, _i, _i, _i, _vp, _i, _i, _i, _i, _i, _i, _vp, _sz, _i]),
+    "d8k_conv2d_grad_y_into": (_i, [_vp, _i, _vp, _i, _i, _i, _i, _vp, _i, _i, _i, _vp, _i, _i, _i, _i, _i, _i, _vp, _sz, _i]),
+    "d8k_deconv2d_grad_x_into": (_i, [_vp, _i, _vp, _i, _i, _i, _i, _vp, _i, _i, _i, _vp, _i, _i, _i, _i, _vp, _sz, _i]),
+    "d8k_deconv2d_grad_y_into": (_i, [_vp, _i, _vp, _i, _i, _i, _i, _vp, _i, _i, _i, _vp, _i, _i, _i, _i, _vp, _sz, _i]),
+    "d8k_linear_forward": (_i, [_vp, _i, _vp, ctypes.c_float, ctypes.c_float, _vp, _sz]),
+    "d8k_linear_grad": (_i, [_vp, _i, _vp, ctypes.c_float, _vp, _sz]),
+    "d8k_matmul_forward_linear": (_i, [_vp, _i, _vp, _i, _i, _i, _vp, _i, _i, _vp, ctypes.c_float, ctypes.c_float, _vp]),
+    "d8k_adam_update": (_i, [_vp, _i, _vp, _vp, _vp, _vp] + [ctypes.c_float] * 5 + [_ll, _sz]),
+    "d8k_adam_ratio": (ctypes.c_float, [ctypes.c_float, ctypes.c_float, ctypes.c_float, _ll]),
+    "d8k_sum_shards_adam": (_i, [_vp, _i, _vp, ctypes.POINTER(_vp), _i, _sz, _vp, _vp, _vp] + [ctypes.c_float] * 5 + [_ll, ctypes.POINTER(_vp), _i]),
     "d8k_relu_forward": (_i, [_vp, _i, _vp, _vp, _sz]),
     "d8k_relu_backward": (_i, [_vp, _i, _vp, _vp, _vp, _sz]),
     "d8k_zero": (_i, [_vp, _vp, _sz]),

@@ -147,12 +147,15 @@ int conv_by_residue_class(d8k_ctx* ctx, int which, const GemmProblem& whole, con
     *done = false;
     const int taps = d.fh * d.fw;
     std::vector<GemmProblem> parts;
-    bool uncovered = false;  // some output rows receive no tap at all
+    bool uncovered = false;  // some output rows (or, for the filter gradient, taps) are written by no class
     for (int ry = 0; ry < R.div_y; ++ry) {
         for (int rx = 0; rx < R.div_x; ++rx) {
             AxisClass cy = axis_class(R.RH, R.FH, R.mul_y, R.e_y, R.off_y, R.div_y, ry);
             AxisClass cx = axis_class(R.RW, R.FW, R.mul_x, R.e_x, R.off_x, R.div_x, rx);
-            if (cy.rows == 0 || cx.rows == 0) continue;
+            if (cy.rows == 0 || cx.rows == 0) {
+                if (which == 2) uncovered = true;  // the taps of a class without rows get no contribution
+                continue;
+            }
             if (cy.nf == 0 || cx.nf == 0) {
                 uncovered = true;
                 continue;
@@ -192,9 +195,12 @@ int conv_by_residue_class(d8k_ctx* ctx, int which, const GemmProblem& whole, con
             parts.push_back(g);
         }
     }
-    if (which == 0 && uncovered) {  // forward overwrites: rows that no tap reaches are zeros
-        size_t bytes = static_cast<size_t>(d.batch) * d.oh * d.ow * d.oc * (whole.dtype == D8K_F32 ? 4 : 2);
-        if (cudaMemsetAsync(whole.C, 0, bytes, ctx->stream) != cudaSuccess) return fail(D8K_ERR_CUDA, "cudaMemsetAsync failed");
+    if (whole.beta == 0 && uncovered) {  // an overwriting call: what no class writes is zeros
+        const size_t elems = which == 0   ? static_cast<size_t>(d.batch) * d.oh * d.ow * d.oc
+                             : which == 1 ? static_cast<size_t>(d.batch) * d.ih * d.iw * d.ic
+                                          : static_cast<size_t>(d.oc) * d.fh * d.fw * d.ic;
+        if (cudaMemsetAsync(whole.C, 0, elems * (whole.dtype == D8K_F32 ? 4 : 2), ctx->stream) != cudaSuccess)
+            return fail(D8K_ERR_CUDA, "cudaMemsetAsync failed");
     }
     *done = true;
     for (const GemmProblem& g : parts)
@@ -208,7 +214,8 @@ int conv_by_residue_class(d8k_ctx* ctx, int which, const GemmProblem& whole, con
 //   grad y  : dy[oc x T*ic]    += dz^T[oc x Mout] * V(x)[Mout x T*ic]
 // `fwd` is the rule of V (rows = output pixels, source = x); `bwd` the rule of V' (rows = input pixels, source = dz).
 int conv_like(d8k_ctx* ctx, int which, int dtype, const ConvDims& d, const ConvRule& fwd, const ConvRule& bwd, const void* x, void* dx,
-              const void* y, void* dy, void* z, const void* dz, void* interim, size_t interim_bytes, bool plan_only, size_t* need) {
+              const void* y, void* dy, void* z, const void* dz, void* interim, size_t interim_bytes, bool plan_only, size_t* need,
+              int accumulate = 1) {
     const int taps = d.fh * d.fw;
     GemmProblem g;
     g.dtype = dtype;
@@ -223,12 +230,12 @@ int conv_like(d8k_ctx* ctx, int which, int dtype, const ConvDims& d, const ConvR
         g.M = d.batch * d.ih * d.iw; g.N = d.ic; g.K = taps * d.oc;
         g.a = virt(dz, false, bwd);
         g.b = filter_by_tap(y, d.oc, taps, d.ic);
-        g.C = dx; g.ldc = d.ic; g.beta = 1;
+        g.C = dx; g.ldc = d.ic; g.beta = accumulate ? 1 : 0;
     } else {
         g.M = d.oc; g.N = taps * d.ic; g.K = d.batch * d.oh * d.ow;
         g.a = plain(dz, true, d.oc);
         g.b = virt(x, true, fwd);
-        g.C = dy; g.ldc = g.N; g.beta = 1;
+        g.C = dy; g.ldc = g.N; g.beta = accumulate ? 1 : 0;
     }
     if (plan_only) {
         *need = gemm_scratch_need(ctx, g);
@@ -338,8 +345,11 @@ __global__ void add_bias_kernel(const T* __restrict__ x, const T* __restrict__ b
 // strip of columns into partial[slice][col] (rows in order, fp32), then the last step adds the slices in order and
 // accumulates into dbias.  Every run adds in the same order.  W columns per thread: 16-byte loads (W = 16 / sizeof(T))
 // when rows and pitch allow, else one column per thread.
+// With `scale` the rows are weighted, partial[slice][c] = sum of dz[r][c] * scale[r]: the matrix-vector product dz^T * scale of
+// MatrixMultiply's gradient of y when y is a single column (deep8/src/math/MatrixMultiply.cu:393-398 with n == 1).
 template <typename T, int W>
-__global__ void bias_grad_partial_kernel(const T* __restrict__ dz, float* __restrict__ partial, size_t rows, int cols, int rows_per_slice) {
+__global__ void bias_grad_partial_kernel(const T* __restrict__ dz, float* __restrict__ partial, size_t rows, int cols, int rows_per_slice,
+                                         const T* __restrict__ scale = nullptr) {
     const int lane = threadIdx.x & 31;
     const int col = (blockIdx.x * 32 + lane) * W;
     const int sub = threadIdx.x >> 5;  // 8 warps share the slice's rows; their sums meet in shared memory in warp order
@@ -352,13 +362,14 @@ __global__ void bias_grad_partial_kernel(const T* __restrict__ dz, float* __rest
     for (int k = 0; k < W; ++k) acc[k] = 0.f;
     if (col < cols) {
         for (size_t r = r0 + sub; r < r1; r += 8) {
+            const float s = scale ? to_f(scale[r]) : 1.f;
             if constexpr (W == 1) {
-                acc[0] += to_f(dz[r * cols + col]);
+                acc[0] += to_f(dz[r * cols + col]) * s;
             } else {
                 const uint4 v = __ldcs(reinterpret_cast<const uint4*>(dz + r * cols + col));
                 const T* e = reinterpret_cast<const T*>(&v);
 #pragma unroll
-                for (int k = 0; k < W; ++k) acc[k] += to_f(e[k]);
+                for (int k = 0; k < W; ++k) acc[k] += to_f(e[k]) * s;
             }
         }
     }
@@ -376,12 +387,83 @@ __global__ void bias_grad_partial_kernel(const T* __restrict__ dz, float* __rest
     }
 }
 template <typename T>
-__global__ void bias_grad_final_kernel(T* __restrict__ dbias, const float* __restrict__ partial, int slices, int cols) {
+__global__ void bias_grad_final_kernel(T* __restrict__ dbias, const float* __restrict__ partial, int slices, int cols, int accumulate = 1) {
     int col = blockIdx.x * blockDim.x + threadIdx.x;
     if (col >= cols) return;
     float t = 0.f;
     for (int s = 0; s < slices; ++s) t += partial[static_cast<size_t>(s) * cols + col];
-    dbias[col] = from_f<T>(to_f(dbias[col]) + t);
+    dbias[col] = from_f<T>((accumulate ? to_f(dbias[col]) : 0.f) + t);
+}
+
+// ---- MatrixMultiply with a single-column y (the n == 1 case of the reference's first branch, deep8/src/math/MatrixMultiply.cu:31-36,
+// 205-213, 393-398): a matrix-vector product.  One useful column would waste 63 / 64 of a tensor-core tile and the whole
+// matrix is read exactly once, so these are HBM-bound SIMT kernels: 16-byte loads, fp32 accumulation in a fixed order.
+// z[r] (+)= sum over c of A[r][c] * v[c]; one warp per row, four 16-byte loads in flight per lane.
+template <typename T>
+__global__ void __launch_bounds__(256) matvec_rows_kernel(const T* __restrict__ A, const T* __restrict__ v, T* __restrict__ z, size_t rows,
+                                                          int cols, int accumulate, bool vec) {
+    constexpr int V = 16 / sizeof(T);
+    const int lane = threadIdx.x & 31;
+    const size_t warp = (blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x) >> 5;
+    const size_t nwarps = (gridDim.x * static_cast<size_t>(blockDim.x)) >> 5;
+    for (size_t r = warp; r < rows; r += nwarps) {
+        const T* a = A + r * cols;
+        float acc[4] = {0.f, 0.f, 0.f, 0.f};
+        if (vec) {
+            const int nv = cols / V;
+            const uint4* a4 = reinterpret_cast<const uint4*>(a);
+            const uint4* v4 = reinterpret_cast<const uint4*>(v);
+            for (int i0 = lane; i0 < nv; i0 += 128) {
+                uint4 av[4], vv[4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const int i = i0 + 32 * u;
+                    av[u] = i < nv ? __ldcs(a4 + i) : make_uint4(0u, 0u, 0u, 0u);
+                    vv[u] = i < nv ? __ldg(v4 + i) : make_uint4(0u, 0u, 0u, 0u);
+                }
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const T* ae = reinterpret_cast<const T*>(&av[u]);
+                    const T* ve = reinterpret_cast<const T*>(&vv[u]);
+#pragma unroll
+                    for (int k = 0; k < V; ++k) acc[u] = fmaf(to_f(ae[k]), to_f(ve[k]), acc[u]);
+                }
+            }
+        } else {
+            for (int c = lane; c < cols; c += 32) acc[0] = fmaf(to_f(a[c]), to_f(v[c]), acc[0]);
+        }
+        float t = (acc[0] + acc[1]) + (acc[2] + acc[3]);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+        if (lane == 0) z[r] = from_f<T>((accumulate ? to_f(z[r]) : 0.f) + t);
+    }
+}
+
+// D[r][c] (+)= u[r] * v[c]: the gradient of x for a single-column y.  A thread keeps its 16 bytes of v and walks down the rows.
+template <typename T>
+__global__ void __launch_bounds__(256) outer_product_kernel(T* __restrict__ D, const T* __restrict__ u, const T* __restrict__ v, size_t rows,
+                                                            int cols, int accumulate, bool vec) {
+    constexpr int V = 16 / sizeof(T);
+    const int chunk = blockIdx.x * blockDim.x + threadIdx.x;
+    if (vec) {
+        if (chunk >= cols / V) return;
+        const uint4 v4 = __ldg(reinterpret_cast<const uint4*>(v) + chunk);
+        const T* ve = reinterpret_cast<const T*>(&v4);
+        for (size_t r = blockIdx.y; r < rows; r += gridDim.y) {
+            const float s = to_f(u[r]);
+            uint4* dst = reinterpret_cast<uint4*>(D + r * cols) + chunk;
+            uint4 d4 = accumulate ? *dst : make_uint4(0u, 0u, 0u, 0u);
+            T* de = reinterpret_cast<T*>(&d4);
+#pragma unroll
+            for (int k = 0; k < V; ++k) de[k] = from_f<T>((accumulate ? to_f(de[k]) : 0.f) + s * to_f(ve[k]));
+            *dst = d4;
+        }
+    } else {
+        if (chunk >= cols) return;
+        const float t = to_f(v[chunk]);
+        for (size_t r = blockIdx.y; r < rows; r += gridDim.y)
+            D[r * cols + chunk] = from_f<T>((accumulate ? to_f(D[r * cols + chunk]) : 0.f) + to_f(u[r]) * t);
+    }
 }
 
 bool aligned16(const void* a, const void* b, const void* c) {
@@ -469,7 +551,7 @@ int d8k_ctx_status(d8k_ctx* ctx, int* status) {
 static int gemm_call(d8k_ctx* ctx, int dtype, int transA, int transB, int M, int N, int K, const void* A, long long lda, int batchA,
                      long long strideA, const void* B, long long ldb, int batchB, long long strideB, void* C, long long ldc, long long strideC,
                      int batch, int beta, int reduce_batch, int epi = 0, void* E1 = nullptr, void* E2 = nullptr, int beta2 = 0,
-                     void* const* row_blocks = nullptr, int num_blocks = 0, int block_rows = 0) {
+                     void* const* row_blocks = nullptr, int num_blocks = 0, int block_rows = 0, float epi_a = 0.f, float epi_b = 0.f) {
     if (int rc = check_ctx(ctx)) return rc;
     if (int rc = check_dtype(dtype)) return rc;
     if (batchA < 1 || batchB < 1 || batch < 0) return fail(D8K_ERR_ARGUMENT, "d8k_gemm: batch counts must be positive");
@@ -488,6 +570,7 @@ static int gemm_call(d8k_ctx* ctx, int dtype, int transA, int transB, int M, int
     if (reduce_batch && batch == 0) g.K = 0;
     g.beta = beta;
     g.epi = epi; g.E1 = E1; g.E2 = E2; g.beta2 = beta2;
+    g.epi_a = epi_a; g.epi_b = epi_b;
     if (row_blocks) {
         if (num_blocks < 1 || num_blocks > kMaxScatter) return fail(D8K_ERR_ARGUMENT, "1 to 16 row blocks");
         g.scatter_rows = block_rows;
@@ -511,16 +594,68 @@ static int check_matmul(int xb, int xr, int xc, int yb, int yc) {
     return 0;
 }
 
+static int column_sums(d8k_ctx* ctx, int dtype, void* out, const void* src, size_t rows, int cols, const void* scale, int accumulate);
+
+// z[rows] (+)= A[rows x cols] * v[cols]
+static int matvec_rows(d8k_ctx* ctx, int dtype, const void* A, const void* v, void* z, size_t rows, int cols, int accumulate) {
+    if (!A || !v || !z) return fail(D8K_ERR_ARGUMENT, "gemm: null pointer");
+    const int per = dtype == D8K_F32 ? 4 : 8;
+    const bool vec = aligned16(A, v, nullptr) && cols % per == 0;
+    size_t blocks = (rows + 7) / 8;
+    const size_t cap = static_cast<size_t>(ctx->num_sms) * 8;
+    if (blocks > cap) blocks = cap;
+    if (dtype == D8K_F32)
+        matvec_rows_kernel<float><<<static_cast<unsigned>(blocks), 256, 0, ctx->stream>>>(static_cast<const float*>(A), static_cast<const float*>(v),
+                                                                                        static_cast<float*>(z), rows, cols, accumulate, vec);
+    else
+        matvec_rows_kernel<__half><<<static_cast<unsigned>(blocks), 256, 0, ctx->stream>>>(static_cast<const __half*>(A), static_cast<const __half*>(v),
+                                                                                         static_cast<__half*>(z), rows, cols, accumulate, vec);
+    D8K_CUDA(cudaGetLastError());
+    count_launch();
+    set_last_kernel(std::string(dtype == D8K_F32 ? "f32" : "f16") + " matvec rows");
+    return 0;
+}
+
+// D[rows x cols] (+)= u[rows] (x) v[cols]
+static int outer_product(d8k_ctx* ctx, int dtype, void* D, const void* u, const void* v, size_t rows, int cols, int accumulate) {
+    if (!D || !u || !v) return fail(D8K_ERR_ARGUMENT, "gemm: null pointer");
+    const int per = dtype == D8K_F32 ? 4 : 8;
+    const bool vec = aligned16(D, v, nullptr) && cols % per == 0;
+    const int chunks = vec ? cols / per : cols;
+    const int bx = (chunks + 255) / 256;
+    size_t by = (static_cast<size_t>(ctx->num_sms) * 8 + bx - 1) / bx;
+    if (by > rows) by = rows;
+    if (by > 65535) by = 65535;
+    dim3 grid(bx, static_cast<unsigned>(by));
+    if (dtype == D8K_F32)
+        outer_product_kernel<float><<<grid, 256, 0, ctx->stream>>>(static_cast<float*>(D), static_cast<const float*>(u), static_cast<const float*>(v),
+                                                                 rows, cols, accumulate, vec);
+    else
+        outer_product_kernel<__half><<<grid, 256, 0, ctx->stream>>>(static_cast<__half*>(D), static_cast<const __half*>(u),
+                                                                  static_cast<const __half*>(v), rows, cols, accumulate, vec);
+    D8K_CUDA(cudaGetLastError());
+    count_launch();
+    set_last_kernel(std::string(dtype == D8K_F32 ? "f32" : "f16") + " outer product");
+    return 0;
+}
+
 static int matmul_forward_impl(d8k_ctx* ctx, int dtype, const void* x, int xb, int xr, int xc, const void* y, int yb, int yc, void* z,
-                               int epi, void* relu_out) {
+                               int epi, void* relu_out, float epi_a = 0.f, float epi_b = 0.f) {
     if (int rc = check_ctx(ctx)) return rc;
     if (int rc = check_dtype(dtype)) return rc;
     if (int rc = check_matmul(xb, xr, xc, yb, yc)) return rc;
+    if (yb == 1 && yc == 1 && epi == 0)  // one column: a matrix-vector product over the folded rows
+        return matvec_rows(ctx, dtype, x, y, z, static_cast<size_t>(xb) * xr, xc, 0);
     if (yb == 1)  // deep8/src/math/MatrixMultiply.cu:31-36: the batch folds into M
-        return gemm_call(ctx, dtype, 0, 0, xb * xr, yc, xc, x, xc, 1, 0, y, yc, 1, 0, z, yc, 0, 1, 0, 0, epi, relu_out);
+        return gemm_call(ctx, dtype, 0, 0, xb * xr, yc, xc, x, xc, 1, 0, y, yc, 1, 0, z, yc, 0, 1, 0, 0, epi, relu_out, nullptr, 0, nullptr, 0, 0,
+                         epi_a, epi_b);
+    if (xb == 1 && yc == 1 && (epi == 0 || epi == 1 || epi == 4))
+        // deep8/src/math/MatrixMultiply.cu:37-42: z [yb x xr] = Y [yb x xc] * X^T, the batch of vectors as the rows of one matrix
+        return gemm_call(ctx, dtype, 0, 1, yb, xr, xc, y, xc, 1, 0, x, xc, 1, 0, z, xr, 0, 1, 0, 0, epi, relu_out, nullptr, 0, nullptr, 0, 0,
+                         epi_a, epi_b);
     int zb = xb > yb ? xb : yb;
     return gemm_call(ctx, dtype, 0, 0, xr, yc, xc, x, xc, xb, 1LL * xr * xc, y, yc, yb, 1LL * xc * yc, z, yc, 1LL * xr * yc, zb, 0, 0, epi,
-                     relu_out);
+                     relu_out, nullptr, 0, nullptr, 0, 0, epi_a, epi_b);
 }
 
 static int matmul_grad_x_impl(d8k_ctx* ctx, int dtype, void* dx, int xb, int xr, int xc, const void* y, int yb, int yc, const void* dz,
@@ -530,6 +665,11 @@ static int matmul_grad_x_impl(d8k_ctx* ctx, int dtype, void* dx, int xb, int xr,
     if (int rc = check_matmul(xb, xr, xc, yb, yc)) return rc;
     void* hh = const_cast<void*>(h);
     const int beta = accumulate ? 1 : 0, beta2 = accumulate_dh ? 1 : 0;
+    if (yb == 1 && yc == 1 && epi == 0)  // one column: dx [rows x xc] (+)= dz [rows] (x) y [xc]
+        return outer_product(ctx, dtype, dx, dz, y, static_cast<size_t>(xb) * xr, xc, beta);
+    if (xb == 1 && yc == 1 && yb > 1 && epi == 0)
+        // deep8/src/math/MatrixMultiply.cu:214-219: dx [xr x xc] (+)= dZ^T [xr x yb] * Y [yb x xc]
+        return gemm_call(ctx, dtype, 1, 0, xr, xc, yb, dz, xr, 1, 0, y, xc, 1, 0, dx, xc, 0, 1, beta, 0);
     // dx[M x xc] (+)= dz[M x yc] * y^T ; y is [xc x yc], i.e. already "N x K" for this product
     if (yb == 1) return gemm_call(ctx, dtype, 0, 1, xb * xr, xc, yc, dz, yc, 1, 0, y, yc, 1, 0, dx, xc, 0, 1, beta, 0, epi, hh, dh, beta2);
     int zb = xb > yb ? xb : yb;
@@ -546,6 +686,14 @@ static int matmul_grad_y_impl(d8k_ctx* ctx, int dtype, const void* x, int xb, in
     if (int rc = check_dtype(dtype)) return rc;
     if (int rc = check_matmul(xb, xr, xc, yb, yc)) return rc;
     const int beta = accumulate ? 1 : 0;
+    if (yb == 1 && yc == 1) {  // one column: dy [xc] (+)= x^T [xc x rows] * dz [rows], column sums of x weighted by dz
+        if (!x || !dy || !dz) return fail(D8K_ERR_ARGUMENT, "gemm: null pointer");
+        set_last_kernel(std::string(dtype == D8K_F32 ? "f32" : "f16") + " matvec columns");
+        return column_sums(ctx, dtype, dy, x, static_cast<size_t>(xb) * xr, xc, dz, beta);
+    }
+    if (xb == 1 && yc == 1 && yb > 1)
+        // deep8/src/math/MatrixMultiply.cu:402-407: dy [yb x xc] (+)= dZ [yb x xr] * X [xr x xc]
+        return gemm_call(ctx, dtype, 0, 0, yb, xc, xr, dz, xr, 1, 0, x, xc, 1, 0, dy, xc, 0, 1, beta, 0);
     // dy[xc x yc] (+)= x^T * dz ; with yb == 1 the batch joins the contraction: K = xb * xr (deep8/src/math/MatrixMultiply.cu:393-398)
     if (yb == 1) return gemm_call(ctx, dtype, 1, 0, xc, yc, xb * xr, x, xc, 1, 0, dz, yc, 1, 0, dy, yc, 0, 1, beta, 0);
     return gemm_call(ctx, dtype, 1, 0, xc, yc, xr, x, xc, xb, 1LL * xr * xc, dz, yc, yb, 1LL * xr * yc, dy, yc, 1LL * xc * yc, yb, beta, 0);
@@ -588,6 +736,12 @@ int d8k_matmul_grad_x_relu(d8k_ctx* ctx, int dtype, void* dx, int xb, int xr, in
     return matmul_grad_x_impl(ctx, dtype, dx, xb, xr, xc, y, yb, yc, dz, accumulate_dx, 2, h, dh, accumulate_dh);
 }
 
+int d8k_matmul_forward_linear(d8k_ctx* ctx, int dtype, const void* x, int xb, int xr, int xc, const void* y, int yb, int yc, void* z, float a,
+                              float b, void* l) {
+    if (!l) return fail(D8K_ERR_ARGUMENT, "d8k_matmul_forward_linear: null pointer");
+    return matmul_forward_impl(ctx, dtype, x, xb, xr, xc, y, yb, yc, z, 4, l, a, b);
+}
+
 int d8k_matmul_forward_bias(d8k_ctx* ctx, int dtype, const void* x, int xb, int xr, int xc, const void* y, int yb, int yc, const void* bias,
                             void* z) {
     if (!bias) return fail(D8K_ERR_ARGUMENT, "d8k_matmul_forward_bias: null pointer");
@@ -613,20 +767,17 @@ int d8k_add_bias(d8k_ctx* ctx, int dtype, const void* x, const void* bias, void*
     return 0;
 }
 
-int d8k_add_bias_grad(d8k_ctx* ctx, int dtype, void* dbias, const void* dz, size_t rows, int cols) {
-    if (int rc = check_ctx(ctx)) return rc;
-    if (int rc = check_dtype(dtype)) return rc;
-    if (rows == 0 || cols <= 0) return cols < 0 ? fail(D8K_ERR_ARGUMENT, "the shape is error") : 0;
-    if (!dbias || !dz) return fail(D8K_ERR_ARGUMENT, "add_bias_grad: null pointer");
+// out[c] (+)= sum over r < rows of src[r][c] (* scale[r] when scale is given), two fixed-order steps through the context's scratch
+static int column_sums(d8k_ctx* ctx, int dtype, void* out, const void* src, size_t rows, int cols, const void* scale, int accumulate) {
     // 16-byte loads when every row starts on a 16-byte boundary and holds whole pieces
     const int per = dtype == D8K_F32 ? 4 : 8;
-    const bool wide = (reinterpret_cast<uintptr_t>(dz) & 15) == 0 && cols % per == 0;
+    const bool wide = (reinterpret_cast<uintptr_t>(src) & 15) == 0 && cols % per == 0;
     const int strip_cols = 32 * (wide ? per : 1);
     // enough slices to occupy the GPU, bounded by the context's scratch memory (slices * cols floats)
     const int strips = (cols + strip_cols - 1) / strip_cols;
     int slices = (ctx->num_sms * 4 + strips - 1) / strips;
     const size_t max_slices = ctx->scratch_bytes / (static_cast<size_t>(cols) * sizeof(float));
-    if (max_slices < 1) return fail(D8K_ERR_ARGUMENT, "add_bias_grad: the context's scratch memory is smaller than one row of floats");
+    if (max_slices < 1) return fail(D8K_ERR_ARGUMENT, "the context's scratch memory is smaller than one row of floats");
     if (static_cast<size_t>(slices) > max_slices) slices = static_cast<int>(max_slices);
     if (static_cast<size_t>(slices) > (rows + 63) / 64) slices = static_cast<int>((rows + 63) / 64);
     if (slices < 1) slices = 1;
@@ -634,20 +785,30 @@ int d8k_add_bias_grad(d8k_ctx* ctx, int dtype, void* dbias, const void* dz, size
     slices = static_cast<int>((rows + rows_per_slice - 1) / rows_per_slice);
     dim3 grid(strips, slices);
     if (dtype == D8K_F32) {
-        const float* src = static_cast<const float*>(dz);
-        if (wide) bias_grad_partial_kernel<float, 4><<<grid, 256, 0, ctx->stream>>>(src, ctx->scratch, rows, cols, rows_per_slice);
-        else bias_grad_partial_kernel<float, 1><<<grid, 256, 0, ctx->stream>>>(src, ctx->scratch, rows, cols, rows_per_slice);
-        bias_grad_final_kernel<float><<<(cols + 255) / 256, 256, 0, ctx->stream>>>(static_cast<float*>(dbias), ctx->scratch, slices, cols);
+        const float* in = static_cast<const float*>(src);
+        const float* sc = static_cast<const float*>(scale);
+        if (wide) bias_grad_partial_kernel<float, 4><<<grid, 256, 0, ctx->stream>>>(in, ctx->scratch, rows, cols, rows_per_slice, sc);
+        else bias_grad_partial_kernel<float, 1><<<grid, 256, 0, ctx->stream>>>(in, ctx->scratch, rows, cols, rows_per_slice, sc);
+        bias_grad_final_kernel<float><<<(cols + 255) / 256, 256, 0, ctx->stream>>>(static_cast<float*>(out), ctx->scratch, slices, cols, accumulate);
     } else {
-        const __half* src = static_cast<const __half*>(dz);
-        if (wide) bias_grad_partial_kernel<__half, 8><<<grid, 256, 0, ctx->stream>>>(src, ctx->scratch, rows, cols, rows_per_slice);
-        else bias_grad_partial_kernel<__half, 1><<<grid, 256, 0, ctx->stream>>>(src, ctx->scratch, rows, cols, rows_per_slice);
-        bias_grad_final_kernel<__half><<<(cols + 255) / 256, 256, 0, ctx->stream>>>(static_cast<__half*>(dbias), ctx->scratch, slices, cols);
+        const __half* in = static_cast<const __half*>(src);
+        const __half* sc = static_cast<const __half*>(scale);
+        if (wide) bias_grad_partial_kernel<__half, 8><<<grid, 256, 0, ctx->stream>>>(in, ctx->scratch, rows, cols, rows_per_slice, sc);
+        else bias_grad_partial_kernel<__half, 1><<<grid, 256, 0, ctx->stream>>>(in, ctx->scratch, rows, cols, rows_per_slice, sc);
+        bias_grad_final_kernel<__half><<<(cols + 255) / 256, 256, 0, ctx->stream>>>(static_cast<__half*>(out), ctx->scratch, slices, cols, accumulate);
     }
     D8K_CUDA(cudaGetLastError());
     count_launch();
     count_launch();
     return 0;
+}
+
+int d8k_add_bias_grad(d8k_ctx* ctx, int dtype, void* dbias, const void* dz, size_t rows, int cols) {
+    if (int rc = check_ctx(ctx)) return rc;
+    if (int rc = check_dtype(dtype)) return rc;
+    if (rows == 0 || cols <= 0) return cols < 0 ? fail(D8K_ERR_ARGUMENT, "the shape is error") : 0;
+    if (!dbias || !dz) return fail(D8K_ERR_ARGUMENT, "add_bias_grad: null pointer");
+    return column_sums(ctx, dtype, dbias, dz, rows, cols, nullptr, 1);
 }
 
 int d8k_conv2d_out_dim(int in, int filter, int stride, int dilation, int covered) {
@@ -697,6 +858,33 @@ int d8k_conv2d_grad_y(d8k_ctx* ctx, int dtype, const void* x, int batch, int ih,
     D8K_CONV_PROLOGUE(strideY, strideX, dilationY, dilationX)
     conv_rules(d, strideY, strideX, dilationY, dilationX, &fwd, &bwd);
     return conv_like(ctx, 2, dtype, d, fwd, bwd, x, nullptr, nullptr, dy, nullptr, dz, interim, interim_bytes, false, nullptr);
+}
+
+int d8k_conv2d_grad_x_into(d8k_ctx* ctx, int dtype, void* dx, int batch, int ih, int iw, int ic, const void* y, int oc, int fh, int fw,
+                           const void* dz, int oh, int ow, int strideY, int strideX, int dilationY, int dilationX, void* interim,
+                           size_t interim_bytes, int accumulate) {
+    D8K_CONV_PROLOGUE(strideY, strideX, dilationY, dilationX)
+    conv_rules(d, strideY, strideX, dilationY, dilationX, &fwd, &bwd);
+    return conv_like(ctx, 1, dtype, d, fwd, bwd, nullptr, dx, y, nullptr, nullptr, dz, interim, interim_bytes, false, nullptr, accumulate);
+}
+int d8k_conv2d_grad_y_into(d8k_ctx* ctx, int dtype, const void* x, int batch, int ih, int iw, int ic, void* dy, int oc, int fh, int fw,
+                           const void* dz, int oh, int ow, int strideY, int strideX, int dilationY, int dilationX, void* interim,
+                           size_t interim_bytes, int accumulate) {
+    D8K_CONV_PROLOGUE(strideY, strideX, dilationY, dilationX)
+    conv_rules(d, strideY, strideX, dilationY, dilationX, &fwd, &bwd);
+    return conv_like(ctx, 2, dtype, d, fwd, bwd, x, nullptr, nullptr, dy, nullptr, dz, interim, interim_bytes, false, nullptr, accumulate);
+}
+int d8k_deconv2d_grad_x_into(d8k_ctx* ctx, int dtype, void* dx, int batch, int ih, int iw, int ic, const void* y, int oc, int fh, int fw,
+                             const void* dz, int oh, int ow, int strideY, int strideX, void* interim, size_t interim_bytes, int accumulate) {
+    D8K_CONV_PROLOGUE(strideY, strideX, 1, 1)
+    deconv_rules(d, strideY, strideX, &fwd, &bwd);
+    return conv_like(ctx, 1, dtype, d, fwd, bwd, nullptr, dx, y, nullptr, nullptr, dz, interim, interim_bytes, false, nullptr, accumulate);
+}
+int d8k_deconv2d_grad_y_into(d8k_ctx* ctx, int dtype, const void* x, int batch, int ih, int iw, int ic, void* dy, int oc, int fh, int fw,
+                             const void* dz, int oh, int ow, int strideY, int strideX, void* interim, size_t interim_bytes, int accumulate) {
+    D8K_CONV_PROLOGUE(strideY, strideX, 1, 1)
+    deconv_rules(d, strideY, strideX, &fwd, &bwd);
+    return conv_like(ctx, 2, dtype, d, fwd, bwd, x, nullptr, nullptr, dy, nullptr, dz, interim, interim_bytes, false, nullptr, accumulate);
 }
 
 int d8k_deconv2d_forward(d8k_ctx* ctx, int dtype, const void* x, int batch, int ih, int iw, int ic, const void* y, int oc, int fh, int fw,

@@ -407,10 +407,14 @@ d8k_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
                             cw = V::pack(cv);
                         }
                         st_shared_v4(s0 + slot_off(lane, v), cw);
-                        if (p.epi == 1 || p.epi == 2) V::unpack(cw, cv);  // the stored (rounded) values drive the fused tails
+                        if (p.epi == 1 || p.epi == 2 || p.epi == 4) V::unpack(cw, cv);  // the stored (rounded) values drive the fused tails
                         if (p.epi == 1) {
 #pragma unroll
                             for (int i = 0; i < 8; ++i) cv[i] = cv[i] > 0.f ? cv[i] : 0.f;
+                            st_shared_v4(s1 + slot_off(lane, v), V::pack(cv));
+                        } else if (p.epi == 4) {
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) cv[i] = epi_linear<OutT>(cv[i], p.epi_a, p.epi_b);
                             st_shared_v4(s1 + slot_off(lane, v), V::pack(cv));
                         } else if (p.epi == 2) {
                             float x[8], g[8];
@@ -434,7 +438,7 @@ d8k_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
                         if (warp_row0 + rr < p.M) {
                             const long long e = warp_off + static_cast<long long>(rr) * p.ldc + col0 + lc * 8;
                             *reinterpret_cast<uint4*>(reinterpret_cast<OutT*>(p.C) + e) = ptx::ld_shared_v4(s0 + slot_off(rr, lc));
-                            if (p.epi == 1) *reinterpret_cast<uint4*>(reinterpret_cast<OutT*>(p.E1) + e) = ptx::ld_shared_v4(s1 + slot_off(rr, lc));
+                            if (p.epi == 1 || p.epi == 4) *reinterpret_cast<uint4*>(reinterpret_cast<OutT*>(p.E1) + e) = ptx::ld_shared_v4(s1 + slot_off(rr, lc));
                             if (p.epi == 2) *reinterpret_cast<uint4*>(reinterpret_cast<OutT*>(p.E2) + e) = ptx::ld_shared_v4(s2 + slot_off(rr, lc));
                         }
                     }

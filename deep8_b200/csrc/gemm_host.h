@@ -49,6 +49,7 @@ struct GemmProblem {
     int kbatch = 1;   // batches summed into one output
     int beta = 0;
     int epi = 0, beta2 = 0;  // fused element-wise tail (GemmParams::epi)
+    float epi_a = 0.f, epi_b = 0.f;
     void* E1 = nullptr;
     void* E2 = nullptr;
     void* ws = nullptr;  // optional caller scratch for split-K

@@ -129,7 +129,8 @@ struct GemmParams {
     int epi_backoff_ns;  // paired kernel: sleep between the epilogue warps' polls for a finished accumulator (0 = poll back to back)
     int total_work;    // batch * tiles_m * tiles_n * splits
     int beta;          // 0: overwrite, 1: accumulate into C
-    int epi, beta2;    // fused element-wise tail, see store_row_chunk: 1 ReLU, 2 ReLU gradient, 3 bias row added (E1 = bias[N])
+    int epi, beta2;    // fused element-wise tail, see store_row_chunk: 1 ReLU, 2 ReLU gradient, 3 bias row added (E1 = bias[N]), 4 Linear
+    float epi_a, epi_b;  // epi 4: E1 = C * epi_a + epi_b
     void* E1;          // epi 1: relu(C) is written here; epi 2: ReLu's input is read here
     void* E2;          // epi 2: ReLu's input gradient, overwritten (beta2 == 0) or accumulated (beta2 == 1)
     void* C;
@@ -550,12 +551,25 @@ struct EpiVec<__half> {
     }
 };
 
+// Math::Linear on one stored value (widened): fp32 rounds the product and the sum separately (deep8/src/math/Linear.cpp:46-54);
+// fp16 works in half arithmetic with a and b converted to half, like the reference's half kernel (deep8/src/math/Linear.cu:46-52).
+template <typename OutT>
+__device__ __forceinline__ float epi_linear(float c, float a, float b);
+template <>
+__device__ __forceinline__ float epi_linear<float>(float c, float a, float b) { return __fadd_rn(__fmul_rn(c, a), b); }
+template <>
+__device__ __forceinline__ float epi_linear<__half>(float c, float a, float b) {
+    return __half2float(__hadd(__hmul(__float2half(a), __float2half(c)), __float2half(b)));
+}
+
 // Element-wise tail of the epilogue for one row and 32 columns [col0, col0 + 32), clipped to N.  `off` is the element
 // offset of C(row, 0); E1 and E2 have C's shape and pitch.  With c = OutT(acc + (beta ? C : 0)):
 //   EPI 0: C = c
 //   EPI 1: C = c; E1 = c > 0 ? c : 0                     MatrixMultiply followed by ReLu (deep8/src/math/ReLu.cu:11-15)
 //   EPI 2: C = c; E2 = (beta2 ? E2 : 0) + (E1 > 0 ? c : 0)   gradient of x followed by ReLu's gradient with E1 = ReLu's
 //                                                        input (deep8/src/math/ReLu.cu:58-63); sums are rounded to OutT
+//   EPI 3: C = OutT(c + bias[col])                        MatrixMultiply followed by Add with a bias row E1
+//   EPI 4: C = c; E1 = c * epi_a + epi_b                  MatrixMultiply followed by Linear (deep8/src/math/Linear.cu:11-58)
 template <typename OutT, int EPI>
 __device__ __forceinline__ void store_row_chunk_epi(const GemmParams& p, long long off, int col0, const float* acc) {
     using V = EpiVec<OutT>;
@@ -590,10 +604,14 @@ __device__ __forceinline__ void store_row_chunk_epi(const GemmParams& p, long lo
                 cw = V::pack(c);
             }
             reinterpret_cast<uint4*>(dst)[v] = cw;
-            if (EPI == 1 || EPI == 2) V::unpack(cw, c);  // the stored (rounded) values drive the fused tails
+            if (EPI == 1 || EPI == 2 || EPI == 4) V::unpack(cw, c);  // the stored (rounded) values drive the fused tails
             if (EPI == 1) {
 #pragma unroll
                 for (int i = 0; i < VEC; ++i) c[i] = c[i] > 0.f ? c[i] : 0.f;
+                reinterpret_cast<uint4*>(e1)[v] = V::pack(c);
+            } else if (EPI == 4) {
+#pragma unroll
+                for (int i = 0; i < VEC; ++i) c[i] = epi_linear<OutT>(c[i], p.epi_a, p.epi_b);
                 reinterpret_cast<uint4*>(e1)[v] = V::pack(c);
             } else if (EPI == 2) {
                 float x[VEC], g[VEC];
@@ -621,6 +639,8 @@ __device__ __forceinline__ void store_row_chunk_epi(const GemmParams& p, long lo
                 dst[i] = c;
                 if (EPI == 1) {
                     e1[i] = epi_to_float(c) > 0.f ? c : epi_from_float<OutT>(0.f);
+                } else if (EPI == 4) {
+                    e1[i] = epi_from_float<OutT>(epi_linear<OutT>(epi_to_float(c), p.epi_a, p.epi_b));
                 } else if (EPI == 2) {
                     OutT g = p.beta2 ? e2[i] : epi_from_float<OutT>(0.f);
                     if (epi_to_float(e1[i]) > 0.f) g = epi_from_float<OutT>(epi_to_float(g) + epi_to_float(c));
@@ -636,7 +656,8 @@ __device__ __forceinline__ void store_row_chunk(const GemmParams& p, long long o
     if (p.epi == 0) store_row_chunk_epi<OutT, 0>(p, off, col0, acc);
     else if (p.epi == 1) store_row_chunk_epi<OutT, 1>(p, off, col0, acc);
     else if (p.epi == 2) store_row_chunk_epi<OutT, 2>(p, off, col0, acc);
-    else store_row_chunk_epi<OutT, 3>(p, off, col0, acc);
+    else if (p.epi == 3) store_row_chunk_epi<OutT, 3>(p, off, col0, acc);
+    else store_row_chunk_epi<OutT, 4>(p, off, col0, acc);
 }
 
 // ------------------------------------------------------------------------------------------------ the kernel

@@ -353,7 +353,7 @@ int run_gemm(Ctx* ctx, const GemmProblem& g) {
     if ((!g.C && g.scatter_rows == 0) || (g.K > 0 && (!g.a.ptr || !g.b.ptr))) return fail(1, "gemm: null pointer");
     if (g.dtype != 0 && g.dtype != 1) return fail(1, "gemm: dtype must be D8K_F16 or D8K_F32");
     if (g.beta != 0 && g.beta != 1) return fail(1, "gemm: beta must be 0 or 1");
-    if (g.epi < 0 || g.epi > 3 || (g.epi >= 1 && !g.E1) || (g.epi == 2 && !g.E2)) return fail(1, "gemm: bad fused epilogue arguments");
+    if (g.epi < 0 || g.epi > 4 || (g.epi >= 1 && !g.E1) || (g.epi == 2 && !g.E2)) return fail(1, "gemm: bad fused epilogue arguments");
     if (g.epi == 3 && (g.beta != 0 || g.scatter_rows != 0 || g.out.cols_on)) return fail(1, "gemm: the bias tail belongs to an overwriting forward product");
     const int esize = g.dtype == 1 ? 4 : 2;
     if (g.scatter_rows != 0) {
@@ -412,6 +412,8 @@ int run_gemm(Ctx* ctx, const GemmProblem& g) {
     p.total_work = pl.tiles * pl.splits;
     p.beta = g.beta;
     p.epi = g.epi;
+    p.epi_a = g.epi_a;
+    p.epi_b = g.epi_b;
     p.beta2 = g.beta2;
     p.E1 = g.E1;
     p.E2 = g.E2;

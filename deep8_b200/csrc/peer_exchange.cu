@@ -12,6 +12,7 @@
 #include <string>
 
 #include "../../include/d8k.h"
+#include "elementwise.cuh"
 #include "gemm_host.h"
 
 struct d8k_ctx : public d8k::Ctx {};
@@ -67,40 +68,6 @@ __global__ void peer_wait_kernel(FlagList flags, int n, unsigned value, unsigned
         }
         __nanosleep(256);
     }
-}
-
-template <typename T>
-__device__ __forceinline__ void accumulate16(float* acc, const uint4& v);
-template <>
-__device__ __forceinline__ void accumulate16<float>(float* acc, const uint4& v) {
-    acc[0] += __uint_as_float(v.x);
-    acc[1] += __uint_as_float(v.y);
-    acc[2] += __uint_as_float(v.z);
-    acc[3] += __uint_as_float(v.w);
-}
-template <>
-__device__ __forceinline__ void accumulate16<__half>(float* acc, const uint4& v) {
-    const __half2* h = reinterpret_cast<const __half2*>(&v);
-#pragma unroll
-    for (int k = 0; k < 4; ++k) {
-        float2 f = __half22float2(h[k]);
-        acc[2 * k] += f.x;
-        acc[2 * k + 1] += f.y;
-    }
-}
-template <typename T>
-__device__ __forceinline__ uint4 round16(const float* acc);
-template <>
-__device__ __forceinline__ uint4 round16<float>(const float* acc) {
-    return make_uint4(__float_as_uint(acc[0]), __float_as_uint(acc[1]), __float_as_uint(acc[2]), __float_as_uint(acc[3]));
-}
-template <>
-__device__ __forceinline__ uint4 round16<__half>(const float* acc) {
-    uint4 o;
-    __half2* h = reinterpret_cast<__half2*>(&o);
-#pragma unroll
-    for (int k = 0; k < 4; ++k) h[k] = __floats2half2_rn(acc[2 * k], acc[2 * k + 1]);
-    return o;
 }
 
 // w = g * alpha + w * beta for 16 bytes of weights, g in fp32: two products and one sum, each rounded (no fused
@@ -176,6 +143,54 @@ __global__ void __launch_bounds__(256) sum_shards_kernel(T* out, SrcList srcs, i
         for (int c = 0; c < ncopies; ++c) reinterpret_cast<T*>(copies.p[c])[i] = gt;
     }
     // the copies may sit in peers' memory: order this thread's stores before whatever the host enqueues next
+    if (ncopies) __threadfence_system();
+}
+
+// The sum with Adam behind it (Math::AdamUpdate on the shard a GPU owns): g = srcs[0] + ... rounded to T as the separate
+// sum would store it, then gradient += value * decay, m, v and value are updated on the same elements; the updated
+// weights also go to `copies` (the peers' buffers).  m and v exist only for the owned shard: each GPU keeps 1 / N of
+// the optimiser's state.
+template <typename T>
+__global__ void __launch_bounds__(256) sum_shards_adam_kernel(T* grad_out, SrcList srcs, int nsrc, size_t count, bool vec, T* weights, T* m,
+                                                              T* v, AdamCoeff c, FlagList copies, int ncopies) {
+    constexpr int V = 16 / sizeof(T);
+    const size_t tid = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x;
+    const size_t stride = gridDim.x * static_cast<size_t>(blockDim.x);
+    const size_t nv = vec ? count / V : 0;
+    for (size_t i = tid; i < nv; i += stride) {
+        float acc[V];
+#pragma unroll
+        for (int k = 0; k < V; ++k) acc[k] = 0.f;
+        for (int s = 0; s < nsrc; ++s) accumulate16<T>(acc, __ldcs(reinterpret_cast<const uint4*>(srcs.p[s]) + i));
+        uint4 g4 = round16<T>(acc), w4 = reinterpret_cast<const uint4*>(weights)[i];
+        uint4 m4 = reinterpret_cast<const uint4*>(m)[i], v4 = reinterpret_cast<const uint4*>(v)[i];
+        T* ge = reinterpret_cast<T*>(&g4);
+        T* we = reinterpret_cast<T*>(&w4);
+        T* me = reinterpret_cast<T*>(&m4);
+        T* ve = reinterpret_cast<T*>(&v4);
+#pragma unroll
+        for (int k = 0; k < V; ++k) {
+            float w = widen(we[k]), g = widen(ge[k]), mm = widen(me[k]), vv = widen(ve[k]);
+            adam_element(w, g, mm, vv, c);
+            we[k] = narrow<T>(w); ge[k] = narrow<T>(g); me[k] = narrow<T>(mm); ve[k] = narrow<T>(vv);
+        }
+        if (grad_out) reinterpret_cast<uint4*>(grad_out)[i] = g4;
+        reinterpret_cast<uint4*>(weights)[i] = w4;
+        reinterpret_cast<uint4*>(m)[i] = m4;
+        reinterpret_cast<uint4*>(v)[i] = v4;
+        for (int q = 0; q < ncopies; ++q) reinterpret_cast<uint4*>(copies.p[q])[i] = w4;
+    }
+    for (size_t i = nv * V + tid; i < count; i += stride) {
+        float a = 0.f;
+        for (int s = 0; s < nsrc; ++s) a += widen(reinterpret_cast<const T*>(srcs.p[s])[i]);
+        float g = widen(narrow<T>(a)), w = widen(weights[i]), mm = widen(m[i]), vv = widen(v[i]);
+        adam_element(w, g, mm, vv, c);
+        if (grad_out) grad_out[i] = narrow<T>(g);
+        weights[i] = narrow<T>(w);
+        m[i] = narrow<T>(mm);
+        v[i] = narrow<T>(vv);
+        for (int q = 0; q < ncopies; ++q) reinterpret_cast<T*>(copies.p[q])[i] = narrow<T>(w);
+    }
     if (ncopies) __threadfence_system();
 }
 
@@ -345,6 +360,47 @@ int d8k_sum_shards_gather(d8k_ctx* ctx, int dtype, void* out, const void* const*
                           float beta, void* const* copies, int ncopies) {
     if (!out && !weights) return fail(D8K_ERR_ARGUMENT, "sum_shards_gather: null output");
     return sum_shards_impl(ctx, dtype, out, srcs, nsrc, count, weights, alpha, beta, copies, ncopies);
+}
+
+int d8k_sum_shards_adam(d8k_ctx* ctx, int dtype, void* grad_out, const void* const* srcs, int nsrc, size_t count, void* weights, void* m, void* v,
+                        float beta1, float beta2, float epsilon, float learning_rate, float weight_decay, long long steps, void* const* copies,
+                        int ncopies) {
+    if (int rc = check_ctx(ctx)) return rc;
+    if (dtype != D8K_F16 && dtype != D8K_F32) return fail(D8K_ERR_ARGUMENT, "type is not support: dtype must be D8K_F16 or D8K_F32");
+    if (count == 0) return 0;
+    if (!weights || !m || !v || !srcs || nsrc < 1 || nsrc > kMaxPeers) return fail(D8K_ERR_ARGUMENT, "sum_shards_adam: null pointer, or not 1 to 16 sources");
+    if (ncopies < 0 || ncopies > kMaxPeers || (ncopies > 0 && !copies)) return fail(D8K_ERR_ARGUMENT, "sum_shards_adam: 0 to 16 copies");
+    SrcList sl = {};
+    FlagList cp = {};
+    uintptr_t bits = reinterpret_cast<uintptr_t>(grad_out) | reinterpret_cast<uintptr_t>(weights) | reinterpret_cast<uintptr_t>(m) |
+                     reinterpret_cast<uintptr_t>(v);
+    for (int i = 0; i < nsrc; ++i) {
+        if (!srcs[i]) return fail(D8K_ERR_ARGUMENT, "sum_shards_adam: null source");
+        sl.p[i] = srcs[i];
+        bits |= reinterpret_cast<uintptr_t>(srcs[i]);
+    }
+    for (int i = 0; i < ncopies; ++i) {
+        if (!copies[i]) return fail(D8K_ERR_ARGUMENT, "sum_shards_adam: null copy");
+        cp.p[i] = static_cast<unsigned*>(copies[i]);
+        bits |= reinterpret_cast<uintptr_t>(copies[i]);
+    }
+    const bool vec = (bits & 15) == 0;
+    AdamCoeff c = {beta1, beta2, 1.0f - beta1, 1.0f - beta2, epsilon, weight_decay, d8k_adam_ratio(learning_rate, beta1, beta2, steps)};
+    const int per = dtype == D8K_F32 ? 4 : 8;
+    size_t blocks = (count / per + 255) / 256;
+    if (blocks > static_cast<size_t>(ctx->num_sms)) blocks = ctx->num_sms;  // one CTA per SM, like the plain sum
+    if (blocks < 1) blocks = 1;
+    if (dtype == D8K_F32)
+        sum_shards_adam_kernel<float><<<static_cast<unsigned>(blocks), 256, 0, ctx->stream>>>(
+            static_cast<float*>(grad_out), sl, nsrc, count, vec, static_cast<float*>(weights), static_cast<float*>(m), static_cast<float*>(v), c, cp,
+            ncopies);
+    else
+        sum_shards_adam_kernel<__half><<<static_cast<unsigned>(blocks), 256, 0, ctx->stream>>>(
+            static_cast<__half*>(grad_out), sl, nsrc, count, vec, static_cast<__half*>(weights), static_cast<__half*>(m), static_cast<__half*>(v), c,
+            cp, ncopies);
+    D8K_CUDA(cudaGetLastError());
+    count_launch();
+    return 0;
 }
 
 int d8k_axpby(d8k_ctx* ctx, int dtype, const void* x, float alpha, void* y, float beta, size_t n) {

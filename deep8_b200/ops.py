@@ -147,6 +147,15 @@ class Context:
         check(self.lib.d8k_matmul_forward_relu(self.h, dt, _p(x), xb, xr, xc, _p(y), yb, yc, _p(z), _p(a)))
         return z, a
 
+    def matmul_forward_linear(self, x, y, z, l, a, b):
+        """z = x y and l = z * a + b in one launch (MatrixMultiply node followed by Linear node)."""
+        dt = _same(x, y, z, l)
+        xb, xr, xc, yb, yc = self._mm_dims(x, y)
+        if tuple(z.shape) != (max(xb, yb), xr, yc) or l.shape != z.shape:
+            raise ValueError("the shape is error")
+        check(self.lib.d8k_matmul_forward_linear(self.h, dt, _p(x), xb, xr, xc, _p(y), yb, yc, _p(z), float(a), float(b), _p(l)))
+        return z, l
+
     def matmul_forward_bias(self, x, y, bias, out=None):
         """z = x * y + bias, bias [1, yc] added to every row (MatrixMultiply followed by Add, one launch)."""
         dt = _same(x, y, bias)
@@ -206,26 +215,26 @@ class Context:
                                           dilation[0], dilation[1], None, 0))
         return z
 
-    def conv2d_grad_x(self, x, dx, w, dz, covered=False, stride=(1, 1), dilation=(1, 1)):
+    def conv2d_grad_x(self, x, dx, w, dz, covered=False, stride=(1, 1), dilation=(1, 1), accumulate=True):
         dt = _same(x, dx, w, dz)
         b, oh, ow, oc = self.conv2d_out_shape(x, w, covered, stride, dilation)
         if tuple(dz.shape) != (b, oh, ow, oc) or dx.shape != x.shape:
             raise ValueError("the shape is error")
         _, ih, iw, ic = x.shape
         _, fh, fw, _ = w.shape
-        check(self.lib.d8k_conv2d_grad_x(self.h, dt, _p(dx), b, ih, iw, ic, _p(w), oc, fh, fw, _p(dz), oh, ow, stride[0], stride[1],
-                                         dilation[0], dilation[1], None, 0))
+        check(self.lib.d8k_conv2d_grad_x_into(self.h, dt, _p(dx), b, ih, iw, ic, _p(w), oc, fh, fw, _p(dz), oh, ow, stride[0], stride[1],
+                                              dilation[0], dilation[1], None, 0, int(accumulate)))
         return dx
 
-    def conv2d_grad_y(self, x, w, dw, dz, covered=False, stride=(1, 1), dilation=(1, 1)):
+    def conv2d_grad_y(self, x, w, dw, dz, covered=False, stride=(1, 1), dilation=(1, 1), accumulate=True):
         dt = _same(x, w, dw, dz)
         b, oh, ow, oc = self.conv2d_out_shape(x, w, covered, stride, dilation)
         if tuple(dz.shape) != (b, oh, ow, oc) or dw.shape != w.shape:
             raise ValueError("the shape is error")
         _, ih, iw, ic = x.shape
         _, fh, fw, _ = w.shape
-        check(self.lib.d8k_conv2d_grad_y(self.h, dt, _p(x), b, ih, iw, ic, _p(dw), oc, fh, fw, _p(dz), oh, ow, stride[0], stride[1],
-                                         dilation[0], dilation[1], None, 0))
+        check(self.lib.d8k_conv2d_grad_y_into(self.h, dt, _p(x), b, ih, iw, ic, _p(dw), oc, fh, fw, _p(dz), oh, ow, stride[0], stride[1],
+                                              dilation[0], dilation[1], None, 0, int(accumulate)))
         return dw
 
     # ------------------------------------------------------------------------------------------------ DeConv2d
@@ -247,24 +256,26 @@ class Context:
         check(self.lib.d8k_deconv2d_forward(self.h, dt, _p(x), b, ih, iw, ic, _p(w), oc, fh, fw, _p(z), oh, ow, stride[0], stride[1], None, 0))
         return z
 
-    def deconv2d_grad_x(self, x, dx, w, dz, covered=False, stride=(1, 1)):
+    def deconv2d_grad_x(self, x, dx, w, dz, covered=False, stride=(1, 1), accumulate=True):
         dt = _same(x, dx, w, dz)
         b, oh, ow, oc = self.deconv2d_out_shape(x, w, covered, stride)
         if tuple(dz.shape) != (b, oh, ow, oc) or dx.shape != x.shape:
             raise ValueError("the shape is error")
         _, ih, iw, ic = x.shape
         _, fh, fw, _ = w.shape
-        check(self.lib.d8k_deconv2d_grad_x(self.h, dt, _p(dx), b, ih, iw, ic, _p(w), oc, fh, fw, _p(dz), oh, ow, stride[0], stride[1], None, 0))
+        check(self.lib.d8k_deconv2d_grad_x_into(self.h, dt, _p(dx), b, ih, iw, ic, _p(w), oc, fh, fw, _p(dz), oh, ow, stride[0], stride[1], None, 0,
+                                                int(accumulate)))
         return dx
 
-    def deconv2d_grad_y(self, x, w, dw, dz, covered=False, stride=(1, 1)):
+    def deconv2d_grad_y(self, x, w, dw, dz, covered=False, stride=(1, 1), accumulate=True):
         dt = _same(x, w, dw, dz)
         b, oh, ow, oc = self.deconv2d_out_shape(x, w, covered, stride)
         if tuple(dz.shape) != (b, oh, ow, oc) or dw.shape != w.shape:
             raise ValueError("the shape is error")
         _, ih, iw, ic = x.shape
         _, fh, fw, _ = w.shape
-        check(self.lib.d8k_deconv2d_grad_y(self.h, dt, _p(x), b, ih, iw, ic, _p(dw), oc, fh, fw, _p(dz), oh, ow, stride[0], stride[1], None, 0))
+        check(self.lib.d8k_deconv2d_grad_y_into(self.h, dt, _p(x), b, ih, iw, ic, _p(dw), oc, fh, fw, _p(dz), oh, ow, stride[0], stride[1], None, 0,
+                                                int(accumulate)))
         return dw
 
     # ------------------------------------------------------------------------------------------------ neighbours
@@ -278,6 +289,30 @@ class Context:
         dt = _same(x, dx, dy)
         check(self.lib.d8k_relu_backward(self.h, dt, _p(x), _p(dx), _p(dy), x.numel()))
         return dx
+
+    def linear_forward(self, x, a, b, out=None):
+        """x * a + b (Math::Linear)."""
+        dt = _same(x)
+        y = _out(out, tuple(x.shape), x)
+        check(self.lib.d8k_linear_forward(self.h, dt, _p(x), float(a), float(b), _p(y), x.numel()))
+        return y
+
+    def linear_grad(self, dx, a, dy):
+        """dx += dy * a (Math::LinearGrad)."""
+        dt = _same(dx, dy)
+        if dx.shape != dy.shape:
+            raise ValueError("the shape is error")
+        check(self.lib.d8k_linear_grad(self.h, dt, _p(dx), float(a), _p(dy), dx.numel()))
+        return dx
+
+    def adam_update(self, value, gradient, m, v, beta1, beta2, epsilon, learning_rate, weight_decay, steps):
+        """Math::AdamUpdate on all four tensors in place (AdamTrainer::update)."""
+        dt = _same(value, gradient, m, v)
+        if not (value.numel() == gradient.numel() == m.numel() == v.numel()):
+            raise ValueError("the param shape size must be same")
+        check(self.lib.d8k_adam_update(self.h, dt, _p(value), _p(gradient), _p(m), _p(v), float(beta1), float(beta2), float(epsilon),
+                                       float(learning_rate), float(weight_decay), int(steps), value.numel()))
+        return value
 
     def zero(self, t):
         check(self.lib.d8k_zero(self.h, _p(t), t.numel() * t.element_size()))
@@ -333,11 +368,20 @@ class Context:
             raise TypeError("type %s is not support" % dtype)
         return code
 
-    def sum_shards(self, dtype, out, srcs, count, sgd=None, copies=None):
+    def sum_shards(self, dtype, out, srcs, count, sgd=None, copies=None, adam=None):
         """out[i] = srcs[0][i] + ... + srcs[-1][i] in that order (fp32 accumulation); dtype is a torch dtype.
         sgd = (weights address, alpha, beta): also weights = sum * alpha + weights * beta (out may then be None).
-        copies: addresses (peers' buffers) that also receive the result - the updated weights with sgd, else the sum."""
+        adam = (weights, m, v addresses, beta1, beta2, epsilon, learning_rate, weight_decay, steps): Math::AdamUpdate on the summed
+        shard instead; out (may be None) receives the gradient after the decay term.
+        copies: addresses (peers' buffers) that also receive the result - the updated weights with sgd or adam, else the sum."""
         code = self._code(dtype)
+        if adam is not None:
+            w, m, v, b1, b2, eps, lr, wd, steps = adam
+            cp = self._ptr_array(copies) if copies else None
+            check(self.lib.d8k_sum_shards_adam(self.h, code, ctypes.c_void_p(out) if out else None, self._ptr_array(srcs), len(srcs), count,
+                                               ctypes.c_void_p(w), ctypes.c_void_p(m), ctypes.c_void_p(v), b1, b2, eps, lr, wd, int(steps), cp,
+                                               len(copies) if copies else 0))
+            return
         if copies:
             w, alpha, beta = sgd if sgd is not None else (None, 0.0, 0.0)
             check(self.lib.d8k_sum_shards_gather(self.h, code, ctypes.c_void_p(out) if out else None, self._ptr_array(srcs), len(srcs),

@@ -82,7 +82,10 @@ D8K_API int d8k_gemm_static(int dtype, int transA, int transB, int M, int N, int
                             const void* B, long long ldb, void* C, long long ldc, int beta, void* stream);
 
 /* MatrixMultiplyGPU (deep8/src/math/MatrixMultiply.cu:139-176): z[b] = x[b % xb] * y[b % yb];
- * x is xb matrices xr x xc, y is yb matrices xc x yc, z is max(xb, yb) matrices xr x yc; xb, yb equal or 1. */
+ * x is xb matrices xr x xc, y is yb matrices xc x yc, z is max(xb, yb) matrices xr x yc; xb, yb equal or 1.
+ * The three branches of the reference (MatrixMultiply.cu:31-56) map to: yb == 1 - one contraction with the batch folded into
+ * the rows (a matrix-vector kernel when yc == 1); xb == 1 and yc == 1 - one contraction Z [yb x xr] = Y [yb x xc] * X^T;
+ * otherwise one batched launch.  The gradients follow the same three cases (MatrixMultiply.cu:205-231, 393-419). */
 D8K_API int d8k_matmul_forward(d8k_ctx* ctx, int dtype, const void* x, int xb, int xr, int xc, const void* y, int yb, int yc, void* z);
 /* MatrixMultiplyGradXGPU (MatrixMultiply.cu:320-363): dx[b % xb] += dz[b] * y[b % yb]^T (summed over b when xb == 1). */
 D8K_API int d8k_matmul_grad_x(d8k_ctx* ctx, int dtype, void* dx, int xb, int xr, int xc, const void* y, int yb, int yc, const void* dz);
@@ -154,6 +157,23 @@ D8K_API int d8k_conv2d_grad_y(d8k_ctx* ctx, int dtype, const void* x, int batch,
                       const void* dz, int oh, int ow, int strideY, int strideX, int dilationY, int dilationX, void* interim,
                       size_t interim_bytes);
 
+/* The four convolution gradients with the accumulation made explicit, like d8k_matmul_grad_{x,y}_into: accumulate != 0 is the
+ * reference's += (Conv2d.cu:799, DeConv2d.cu:426, 697); accumulate == 0 overwrites - the first contribution to a gradient
+ * needs no zero fill (Variable::zeroGradient, deep8/src/model/EagerExecutor.cpp:51-65).  Elements no filter tap reaches
+ * (stride beyond the filter) are written as zeros. */
+D8K_API int d8k_conv2d_grad_x_into(d8k_ctx* ctx, int dtype, void* dx, int batch, int ih, int iw, int ic, const void* y, int oc, int fh, int fw,
+                                   const void* dz, int oh, int ow, int strideY, int strideX, int dilationY, int dilationX, void* interim,
+                                   size_t interim_bytes, int accumulate);
+D8K_API int d8k_conv2d_grad_y_into(d8k_ctx* ctx, int dtype, const void* x, int batch, int ih, int iw, int ic, void* dy, int oc, int fh, int fw,
+                                   const void* dz, int oh, int ow, int strideY, int strideX, int dilationY, int dilationX, void* interim,
+                                   size_t interim_bytes, int accumulate);
+D8K_API int d8k_deconv2d_grad_x_into(d8k_ctx* ctx, int dtype, void* dx, int batch, int ih, int iw, int ic, const void* y, int oc, int fh, int fw,
+                                     const void* dz, int oh, int ow, int strideY, int strideX, void* interim, size_t interim_bytes,
+                                     int accumulate);
+D8K_API int d8k_deconv2d_grad_y_into(d8k_ctx* ctx, int dtype, const void* x, int batch, int ih, int iw, int ic, void* dy, int oc, int fh, int fw,
+                                     const void* dz, int oh, int ow, int strideY, int strideX, void* interim, size_t interim_bytes,
+                                     int accumulate);
+
 /* DeConv2dGPU (deep8/src/math/DeConv2d.cu:251-308).  x [batch, ih, iw, ic], y [oc, fh, fw, ic], z [batch, oh, ow, oc]. */
 D8K_API int d8k_deconv2d_forward(d8k_ctx* ctx, int dtype, const void* x, int batch, int ih, int iw, int ic, const void* y, int oc, int fh, int fw,
                          void* z, int oh, int ow, int strideY, int strideX, void* interim, size_t interim_bytes);
@@ -217,6 +237,35 @@ D8K_API int d8k_axpby(d8k_ctx* ctx, int dtype, const void* x, float alpha, void*
  * updated weights, not the gradient, are what the all-gather then has to carry. */
 D8K_API int d8k_sum_shards_sgd(d8k_ctx* ctx, int dtype, void* grad_out, const void* const* srcs, int nsrc, size_t count, void* weights,
                                float alpha, float beta);
+
+/* LinearGPU (deep8/src/math/Linear.cu:25-58): y = x * a + b over n elements; y may be x.  fp32: the product and the sum
+ * are rounded separately, which is the reference's CPU arithmetic bit for bit (deep8/src/math/Linear.cpp:46-54); fp16: in
+ * half arithmetic with a and b converted to half, as the reference's half kernel does (Linear.cu:46-52). */
+D8K_API int d8k_linear_forward(d8k_ctx* ctx, int dtype, const void* x, float a, float b, void* y, size_t n);
+/* LinearGradGPU (Linear.cu:74-110): dx += dy * a. */
+D8K_API int d8k_linear_grad(d8k_ctx* ctx, int dtype, void* dx, float a, const void* dy, size_t n);
+/* MatrixMultiplyGPU followed by LinearGPU in one launch: z = x * y and l = z * a + b, both written from the accumulator in
+ * the epilogue; the results are those of the two separate calls (l is computed from z as stored). */
+D8K_API int d8k_matmul_forward_linear(d8k_ctx* ctx, int dtype, const void* x, int xb, int xr, int xc, const void* y, int yb, int yc, void* z,
+                                      float a, float b, void* l);
+
+/* AdamUpdateGPU (deep8/src/math/AdamUpdate.cu:9-58, called by AdamTrainer::update, deep8/src/trainer/AdamTrainer.cpp:9-31):
+ *   gradient += value * weight_decay;  m = m * beta1 + gradient * (1 - beta1);  v = v * beta2 + gradient^2 * (1 - beta2);
+ *   value -= m / (sqrt(v) + epsilon) * ratio,  ratio = d8k_adam_ratio(learning_rate, beta1, beta2, steps).
+ * All four arrays are updated in place.  fp32: every operation rounded separately, IEEE sqrt and division - the
+ * reference's CPU statements (deep8/src/math/AdamUpdate.cpp:24-41) with an exact square root; fp16 arrays are widened,
+ * updated in fp32 and rounded once each. */
+D8K_API int d8k_adam_update(d8k_ctx* ctx, int dtype, void* value, void* gradient, void* m, void* v, float beta1, float beta2, float epsilon,
+                            float learning_rate, float weight_decay, long long steps, size_t n);
+/* learning_rate * sqrt(1 - beta2^steps) / (1 - beta1^steps) in float, steps <= 0 taken as 1 (AdamUpdate.cpp:11-14, 38). */
+D8K_API float d8k_adam_ratio(float learning_rate, float beta1, float beta2, long long steps);
+/* d8k_sum_shards and Adam in one pass over the shard a GPU owns (the counterpart of d8k_sum_shards_sgd): g = srcs[0] + ...
+ * + srcs[nsrc-1] rounded to dtype, then d8k_adam_update's statements on (weights, g, m, v) for the same elements; g after
+ * the decay term is stored to grad_out unless it is NULL, and the updated weights are also stored to copies[0..ncopies) -
+ * the same shard in each peer's buffer.  m and v cover the owned shard only: each GPU keeps 1 / N of the optimiser's state. */
+D8K_API int d8k_sum_shards_adam(d8k_ctx* ctx, int dtype, void* grad_out, const void* const* srcs, int nsrc, size_t count, void* weights, void* m,
+                                void* v, float beta1, float beta2, float epsilon, float learning_rate, float weight_decay, long long steps,
+                                void* const* copies, int ncopies);
 
 #ifdef __cplusplus
 }

@@ -17,6 +17,7 @@
  */
 #ifndef D8O_T /* ---------------------------------------------------------------- first pass: shared part */
 
+#include <math.h>
 #include <stddef.h>
 #include <stdint.h>
 
@@ -356,6 +357,63 @@ D8O_API void D8O_(d8o_add_bias_grad)(D8O_T* dbias, const D8O_T* dz, size_t rows,
         double acc = 0;
         for (size_t r = 0; r < rows; ++r) acc += (double)dz[r * cols + c];
         dbias[c] = (D8O_T)((double)dbias[c] + acc);
+    }
+}
+
+/* Math::ReLu (deep8/src/math/ReLu.cpp:39-47): y = max(x, 0). */
+D8O_API void D8O_(d8o_relu)(const D8O_T* x, D8O_T* y, size_t n) {
+    for (size_t i = 0; i < n; ++i) y[i] = x[i] > (D8O_T)0 ? x[i] : (D8O_T)0;
+}
+
+/* Math::ReLuGrad (deep8/src/math/ReLu.cpp:64-80): dx += (x > 0 ? dy : 0). */
+D8O_API void D8O_(d8o_relu_grad)(const D8O_T* x, D8O_T* dx, const D8O_T* dy, size_t n) {
+    for (size_t i = 0; i < n; ++i) dx[i] = dx[i] + (x[i] > (D8O_T)0 ? dy[i] : (D8O_T)0);
+}
+
+/* Math::Linear (deep8/src/math/Linear.cpp:46-54): y = x * a + b, product and sum rounded separately in T. */
+D8O_API void D8O_(d8o_linear)(const D8O_T* x, D8O_T a, D8O_T b, D8O_T* y, size_t n) {
+#pragma STDC FP_CONTRACT OFF
+    for (size_t i = 0; i < n; ++i) {
+        volatile D8O_T t = x[i] * a;
+        y[i] = t + b;
+    }
+}
+
+/* Math::LinearGrad (deep8/src/math/Linear.cpp:72-80): dx += dy * a. */
+D8O_API void D8O_(d8o_linear_grad)(D8O_T* dx, D8O_T a, const D8O_T* dy, size_t n) {
+#pragma STDC FP_CONTRACT OFF
+    for (size_t i = 0; i < n; ++i) {
+        volatile D8O_T t = dy[i] * a;
+        dx[i] = dx[i] + t;
+    }
+}
+
+/* Math::AdamUpdate (deep8/src/math/AdamUpdate.cpp:24-41), statement by statement, every operation rounded in T:
+ *   gradient += value * weightDecay
+ *   m = m * beta1 + gradient * (1 - beta1)
+ *   v = v * beta2 + gradient^2 * (1 - beta2)
+ *   value -= m / (sqrt(v) + epsilon) * ratio
+ * `ratio` = learningRate * sqrt(1 - beta2^steps) / (1 - beta1^steps) is computed by the caller. */
+D8O_API void D8O_(d8o_adam_update)(D8O_T* value, D8O_T* gradient, D8O_T* m, D8O_T* v, D8O_T beta1, D8O_T beta2, D8O_T epsilon,
+                                   D8O_T weight_decay, D8O_T ratio, size_t n) {
+#pragma STDC FP_CONTRACT OFF
+    volatile D8O_T c1 = (D8O_T)1 - beta1, c2 = (D8O_T)1 - beta2;
+    for (size_t i = 0; i < n; ++i) {
+        volatile D8O_T t = value[i] * weight_decay;
+        volatile D8O_T g = gradient[i] + t;
+        gradient[i] = g;
+        volatile D8O_T m1 = m[i] * beta1, m2 = g * c1;
+        volatile D8O_T mm = m1 + m2;
+        m[i] = mm;
+        volatile D8O_T gg = g * g;
+        volatile D8O_T v1 = v[i] * beta2, v2 = gg * c2;
+        volatile D8O_T vv = v1 + v2;
+        v[i] = vv;
+        volatile D8O_T root = sizeof(D8O_T) == 4 ? (D8O_T)sqrtf((float)vv) : (D8O_T)sqrt((double)vv);
+        volatile D8O_T den = root + epsilon;
+        volatile D8O_T q = mm / den;
+        volatile D8O_T step = q * ratio;
+        value[i] = value[i] - step;
     }
 }
 

@@ -21,10 +21,20 @@ RESTATED_LIB = os.path.join(_HERE, "libd8oracle.so")
 REFERENCE_LIB = os.path.join(_HERE, "_ref", "libd8ref.so")
 
 
+def reference_root():
+    """Where the reference project's source tree is: $DEEP8_REFERENCE, else a directory named `reference` beside this
+    repository.  None when neither exists (then a prebuilt oracle/_ref is used as it is)."""
+    for cand in (os.environ.get("DEEP8_REFERENCE"), os.path.join(os.path.dirname(os.path.dirname(_HERE)), "reference")):
+        if cand and os.path.exists(os.path.join(cand, "deep8", "src", "math", "MatrixMultiply.cpp")):
+            return cand
+    return None
+
+
 def build(ref=True):
     """Run oracle/Makefile (the restatement always; the reference library when its source tree is present)."""
     targets = ["oracle"] + (["ref"] if ref else [])
-    subprocess.run(["make", "-s", "-C", _HERE] + targets, check=True)
+    root = reference_root()
+    subprocess.run(["make", "-s", "-C", _HERE] + (["REF=" + root] if root else []) + targets, check=True)
 
 
 def _ptr(a):
@@ -127,6 +137,15 @@ def sgd_coefficients(learning_rate, weight_decay):
     return float(alpha), float(beta)
 
 
+def adam_ratio(learning_rate, beta1, beta2, steps, dtype=np.float32):
+    """learningRate * sqrt(1 - beta2^steps) / (1 - beta1^steps) in the tensor's element type, steps <= 0 taken as 1
+    (deep8/src/math/AdamUpdate.cpp:11-14, 38)."""
+    t = np.float32 if dtype == np.float32 else np.float64
+    steps = max(int(steps), 1)
+    lr, b1, b2 = t(learning_rate), t(beta1), t(beta2)
+    return float(t(t(lr * np.sqrt(t(t(1) - np.power(b2, t(steps))))) / t(t(1) - np.power(b1, t(steps)))))
+
+
 class Restated(_Base):
     kind = "port"
 
@@ -161,6 +180,46 @@ class Restated(_Base):
         ct = ctypes.c_float if dt == np.float32 else ctypes.c_double
         getattr(self.lib, "d8o_axpby_" + _suffix(dt))(_ptr(x), ct(alpha), _ptr(y), ct(beta), _ptr(z), ctypes.c_size_t(x.size))
         return z
+
+    def relu(self, x):
+        """max(x, 0) (Math::ReLu), a new array."""
+        dt = self._check(x)
+        y = np.empty_like(x)
+        getattr(self.lib, "d8o_relu_" + _suffix(dt))(_ptr(x), _ptr(y), ctypes.c_size_t(x.size))
+        return y
+
+    def relu_grad(self, x, dy, d0=None):
+        """d0 + (x > 0 ? dy : 0) (Math::ReLuGrad), a new array."""
+        dt = self._check(x, dy)
+        dx = self._grad0(d0, x.shape, dt)
+        getattr(self.lib, "d8o_relu_grad_" + _suffix(dt))(_ptr(x), _ptr(dx), _ptr(dy), ctypes.c_size_t(x.size))
+        return dx
+
+    def linear(self, x, a, b):
+        """x * a + b (Math::Linear), a new array."""
+        dt = self._check(x)
+        y = np.empty_like(x)
+        ct = ctypes.c_float if dt == np.float32 else ctypes.c_double
+        getattr(self.lib, "d8o_linear_" + _suffix(dt))(_ptr(x), ct(a), ct(b), _ptr(y), ctypes.c_size_t(x.size))
+        return y
+
+    def linear_grad(self, dy, a, d0=None):
+        """d0 + dy * a (Math::LinearGrad), a new array."""
+        dt = self._check(dy)
+        dx = self._grad0(d0, dy.shape, dt)
+        ct = ctypes.c_float if dt == np.float32 else ctypes.c_double
+        getattr(self.lib, "d8o_linear_grad_" + _suffix(dt))(_ptr(dx), ct(a), _ptr(dy), ctypes.c_size_t(dy.size))
+        return dx
+
+    def adam_update(self, value, gradient, m, v, beta1, beta2, epsilon, learning_rate, weight_decay, steps):
+        """Math::AdamUpdate: returns new (value, gradient, m, v); the inputs are left alone."""
+        dt = self._check(value, gradient, m, v)
+        out = [np.array(a, copy=True, order="C") for a in (value, gradient, m, v)]
+        ratio = adam_ratio(learning_rate, beta1, beta2, steps, dt)
+        ct = ctypes.c_float if dt == np.float32 else ctypes.c_double
+        getattr(self.lib, "d8o_adam_update_" + _suffix(dt))(_ptr(out[0]), _ptr(out[1]), _ptr(out[2]), _ptr(out[3]), ct(beta1), ct(beta2),
+                                                            ct(epsilon), ct(weight_decay), ct(ratio), ctypes.c_size_t(value.size))
+        return tuple(out)
 
     def _matmul(self, which, x, dx, y, dy, z, dz):
         dt = self._check(x, y)
@@ -247,6 +306,43 @@ class Reference(_Base):
         self._ok(self.lib.d8ref_axpby(0 if dt == np.float32 else 1, _ptr(x), ctypes.c_float(alpha), _ptr(y), ctypes.c_float(beta),
                                       _ptr(z), ctypes.c_size_t(x.size)))
         return z
+
+    def relu(self, x):
+        dt = self._check(x)
+        y = np.empty_like(x)
+        self._ok(self.lib.d8ref_relu(0, 0 if dt == np.float32 else 1, _ptr(x), None, _ptr(y), None, ctypes.c_size_t(x.size)))
+        return y
+
+    def relu_grad(self, x, dy, d0=None):
+        dt = self._check(x, dy)
+        dx = self._grad0(d0, x.shape, dt)
+        y = np.zeros_like(x)
+        self._ok(self.lib.d8ref_relu(1, 0 if dt == np.float32 else 1, _ptr(x), _ptr(dx), _ptr(y), _ptr(dy), ctypes.c_size_t(x.size)))
+        return dx
+
+    def linear(self, x, a, b):
+        dt = self._check(x)
+        y = np.empty_like(x)
+        self._ok(self.lib.d8ref_linear(0, 0 if dt == np.float32 else 1, _ptr(x), None, ctypes.c_float(a), ctypes.c_float(b), _ptr(y), None,
+                                       ctypes.c_size_t(x.size)))
+        return y
+
+    def linear_grad(self, dy, a, d0=None):
+        dt = self._check(dy)
+        dx = self._grad0(d0, dy.shape, dt)
+        x = np.zeros_like(dy)
+        self._ok(self.lib.d8ref_linear(1, 0 if dt == np.float32 else 1, _ptr(x), _ptr(dx), ctypes.c_float(a), ctypes.c_float(0.0), _ptr(x),
+                                       _ptr(dy), ctypes.c_size_t(dy.size)))
+        return dx
+
+    def adam_update(self, value, gradient, m, v, beta1, beta2, epsilon, learning_rate, weight_decay, steps):
+        dt = self._check(value, gradient, m, v)
+        out = [np.array(a, copy=True, order="C") for a in (value, gradient, m, v)]
+        f = ctypes.c_float
+        self._ok(self.lib.d8ref_adam_update(0 if dt == np.float32 else 1, _ptr(out[0]), _ptr(out[1]), _ptr(out[2]), _ptr(out[3]), f(beta1),
+                                            f(beta2), f(epsilon), f(learning_rate), f(weight_decay), ctypes.c_longlong(steps),
+                                            ctypes.c_size_t(value.size)))
+        return tuple(out)
 
     def _matmul(self, which, x, dx, y, dy, z, dz):
         dt = self._check(x, y)

@@ -25,6 +25,9 @@
 #include "math/DeConv2d.h"
 #include "math/AXPBY.h"
 #include "math/Add.h"
+#include "math/ReLu.h"
+#include "math/Linear.h"
+#include "math/AdamUpdate.h"
 
 #define D8REF_API extern "C" __attribute__((visibility("default")))
 
@@ -184,5 +187,47 @@ D8REF_API int d8ref_add_bias(int which, int dtype, const void* x, size_t batch, 
             View vdz(dtype, dz, batch, {rows, cols});
             Deep8::Math::AddGradY(vx.tensor, vy.tensor, vdy.tensor, vz.tensor, vdz.tensor);
         }
+    });
+}
+
+// Math::ReLu / Math::ReLuGrad (deep8/src/math/ReLu.cpp:6-37).  which: 0 = y = max(x, 0); 1 = dx += (x > 0 ? dy : 0).
+D8REF_API int d8ref_relu(int which, int dtype, const void* x, void* dx, void* y, const void* dy, size_t n) {
+    return guarded([&] {
+        View vx(dtype, x, 1, {n});
+        View vy(dtype, y, 1, {n});
+        if (which == 0) {
+            Deep8::Math::ReLu(vx.tensor, vy.tensor);
+        } else {
+            View vdx(dtype, dx, 1, {n});
+            View vdy(dtype, dy, 1, {n});
+            Deep8::Math::ReLuGrad(vx.tensor, vdx.tensor, vy.tensor, vdy.tensor);
+        }
+    });
+}
+
+// Math::Linear / Math::LinearGrad (deep8/src/math/Linear.cpp:9-44).  which: 0 = y = x * a + b; 1 = dx += dy * a.
+D8REF_API int d8ref_linear(int which, int dtype, const void* x, void* dx, float a, float b, void* y, const void* dy, size_t n) {
+    return guarded([&] {
+        View vx(dtype, x, 1, {n});
+        View vy(dtype, y, 1, {n});
+        if (which == 0) {
+            Deep8::Math::Linear(vx.tensor, a, b, vy.tensor);
+        } else {
+            View vdx(dtype, dx, 1, {n});
+            View vdy(dtype, dy, 1, {n});
+            Deep8::Math::LinearGrad(vx.tensor, vdx.tensor, a, b, vy.tensor, vdy.tensor);
+        }
+    });
+}
+
+// Math::AdamUpdate (deep8/src/math/AdamUpdate.cpp:6-22): value, gradient, m and v are all updated in place.
+D8REF_API int d8ref_adam_update(int dtype, void* value, void* gradient, void* m, void* v, float beta1, float beta2, float epsilon,
+                                float learningRate, float weightDecay, long long steps, size_t n) {
+    return guarded([&] {
+        View vv(dtype, value, 1, {n});
+        View vg(dtype, gradient, 1, {n});
+        View vm(dtype, m, 1, {n});
+        View vs(dtype, v, 1, {n});
+        Deep8::Math::AdamUpdate(vv.tensor, vg.tensor, vm.tensor, vs.tensor, beta1, beta2, epsilon, learningRate, weightDecay, steps);
     });
 }

@@ -163,7 +163,7 @@ def test_deconv_f32(ctx, restated, xs, ws, cov, st):
     parity(ctx, restated, "deconv", xs, ws, (cov, st), torch.float32, F32_TOL)
 
 
-@pytest.mark.parametrize("xs,ws,cov,st", cases.DECONV_EDGE)
+@pytest.mark.parametrize("xs,ws,cov,st", cases.DECONV_REFERENCE_TESTS + cases.DECONV_EDGE)
 def test_deconv_f16(ctx, restated, xs, ws, cov, st):
     parity(ctx, restated, "deconv", xs, ws, (cov, st), torch.float16, F16_TOL)
 
@@ -469,3 +469,211 @@ def test_bias_gradient(ctx, restated, shape):
     DBh = dev(d0, torch.float16)
     ctx.add_bias_grad(DBh, dev(dzh, torch.float16))
     check(ctx, DBh, restated.add_bias_grad(dzh, d0.astype(np.float16).astype(np.float32)), F16_TOL, "dbias f16")
+
+
+# ------------------------------------------------------------------------------------------------ the benchmark configurations as stated
+def _config_inputs(n):
+    """Inputs of benchmark configuration n exactly as it words them (distributions, scales, seeds; the second operand of
+    configurations 1 and 2 takes seed + 10)."""
+    if n == 1:
+        return "matmul", None, cases.uniform(0, (1, 256, 512)), cases.uniform(10, (1, 512, 128)), cases.uniform(1, (1, 256, 128))
+    if n == 2:
+        return "matmul", None, cases.normal(2, (64, 128, 256), 0.05), cases.normal(12, (1, 256, 256), 0.05), cases.normal(3, (64, 128, 256))
+    if n == 3:
+        return ("conv", (True, (1, 1), (1, 1)), cases.uniform(4, (32, 56, 56, 64)), cases.normal(5, (64, 3, 3, 64), (2.0 / 576) ** 0.5),
+                cases.normal(6, (32, 56, 56, 64)))
+    return ("deconv", (True, (2, 2)), cases.uniform(7, (16, 14, 14, 256)), cases.normal(8, (128, 4, 4, 256), 1.0 / 64),
+            cases.normal(9, (16, 27, 27, 128)))
+
+
+@pytest.mark.parametrize("n", [1, 2, 3, 4])
+def test_benchmark_configuration_with_its_own_inputs(ctx, restated, n):
+    """Configurations 1-4 at full size with the value distributions and seeds they name (He-normal filter for 3, N(0, 1/64) for 4,
+    the 0.05 scale for 2), gradients from zero: fp32 within 1e-5 of the oracle."""
+    kind, meta, x, w, dz = _config_inputs(n)
+    r = Runner(ctx, restated, kind, meta)
+    got = r.gpu(x, w, dz, np.zeros_like(x), np.zeros_like(w), torch.float32)
+    want = r.cpu(x, w, dz, None, None)
+    for name, g, wnt in zip(("z", "dx", "dy"), got, want):
+        check(ctx, g, wnt, F32_TOL, "config %d %s" % (n, name))
+
+
+@pytest.mark.parametrize("n", [3, 4])
+def test_benchmark_configuration_on_fp16_storage(ctx, restated, n):
+    kind, meta, x, w, dz = _config_inputs(n)
+    x, w, dz = (a.astype(np.float16).astype(np.float32) for a in (x, w, dz))
+    r = Runner(ctx, restated, kind, meta)
+    got = r.gpu(x, w, dz, np.zeros_like(x), np.zeros_like(w), torch.float16)
+    want = r.cpu(x, w, dz, None, None)
+    for name, g, wnt in zip(("z", "dx", "dy"), got, want):
+        check(ctx, g, wnt, F16_TOL, "config %d %s" % (n, name))
+
+
+def test_cfg5_second_layer_and_fused_tails_sampled(ctx, restated):
+    """Config 5 at full size, the half of the step the first-layer test leaves out: Y = A W2 (K = 16384), dA = dY W2^T,
+    dW2 = A^T dY, and the fused calls - forward + ReLU, gradient of x + ReLU gradient - over 8192 x 16384, on sampled rows and
+    columns against the oracle."""
+    torch.manual_seed(10)
+    M, K, N = 8192, 16384, 4096    # second layer: A [M x K], W2 [K x N]
+    g = torch.Generator(device=DEV).manual_seed(10)
+    X = torch.randn(1, M, N, device=DEV, generator=g).to(torch.float16)
+    W1 = (torch.randn(1, N, K, device=DEV, generator=g) * 0.02).to(torch.float16)
+    W2 = (torch.randn(1, K, N, device=DEV, generator=g) * 0.02).to(torch.float16)
+    dY = (torch.randn(1, M, N, device=DEV, generator=g) * 0.01).to(torch.float16)
+    H, A = torch.empty(1, M, K, device=DEV, dtype=torch.float16), torch.empty(1, M, K, device=DEV, dtype=torch.float16)
+    ctx.matmul_forward_relu(X, W1, H, A)            # fused forward + ReLU at 8192 x 16384
+    rows = [0, 127, 128, 4097, 8191]
+    h_want = restated.matmul_forward(np.ascontiguousarray(host(X[:, rows, :])), host(W1))
+    assert cases.rel_max(host(H[:, rows, :]), h_want) <= F16_TOL
+    assert np.array_equal(host(A[:, rows, :]), restated.relu(host(H[:, rows, :])))      # ReLU of the stored H, exactly
+    Y = ctx.matmul_forward(A, W2)
+    want = restated.matmul_forward(np.ascontiguousarray(host(A[:, rows, :])), host(W2))
+    assert cases.rel_max(host(Y[:, rows, :]), want) <= F16_TOL
+    dA, dH = torch.empty_like(A), torch.empty_like(H)
+    ctx.matmul_grad_x_relu(A, dA, W2, dY, H, dH, accumulate_dx=False, accumulate_dh=False)   # fused at 8192 x 16384
+    want = restated.matmul_grad_x(np.zeros((1, len(rows), K), np.float32), host(W2), np.ascontiguousarray(host(dY[:, rows, :])))
+    assert cases.rel_max(host(dA[:, rows, :]), want) <= F16_TOL
+    dh_want = restated.relu_grad(host(H[:, rows, :]), host(dA[:, rows, :]))                   # from the stored dA, exactly
+    assert np.array_equal(host(dH[:, rows, :]), dh_want)
+    dW2 = torch.empty_like(W2)
+    ctx.matmul_grad_y(A, W2, dW2, dY, accumulate=False)
+    cols = [0, 255, 256, 4095]
+    want = restated.matmul_grad_y(host(A), np.zeros((1, K, len(cols)), np.float32), np.ascontiguousarray(host(dY[:, :, cols])))
+    assert cases.rel_max(host(dW2[:, :, cols]), want) <= F16_TOL
+    assert ctx.status() == 0
+
+
+# ------------------------------------------------------------------------------------------------ element-wise neighbours
+@pytest.mark.parametrize("n", [1000, 4096 * 33 + 5])
+def test_relu_against_the_oracles(ctx, restated, n):
+    """ReLu / ReLuGrad against the oracle (pinned to deep8/src/math/ReLu.cpp): identical in fp32 and in fp16."""
+    rng = np.random.default_rng(n)
+    x, dy, d0 = (rng.standard_normal(n).astype(np.float32) for _ in range(3))
+    x[::13] = 0
+    for tdtype in (torch.float32, torch.float16):
+        xs, dys, d0s = (a.astype(np.float16).astype(np.float32) for a in (x, dy, d0)) if tdtype == torch.float16 else (x, dy, d0)
+        X, DY, DX = dev(xs, tdtype), dev(dys, tdtype), dev(d0s, tdtype)
+        assert np.array_equal(host(ctx.relu_forward(X)), restated.relu(xs))
+        ctx.relu_backward(X, DX, DY)
+        want = restated.relu_grad(xs, dys, d0s)
+        if tdtype == torch.float16:
+            want = want.astype(np.float16).astype(np.float32)   # one fp32 sum of two fp16 values, rounded to fp16
+        assert np.array_equal(host(DX), want)
+
+
+@pytest.mark.parametrize("n", [1000, 4096 * 33 + 5])
+def test_linear_against_the_oracles(ctx, restated, n):
+    """Linear / LinearGrad: fp32 bit for bit the reference's CPU arithmetic; fp16 (half arithmetic, as the reference's half
+    kernel) within 2e-2 of it."""
+    rng = np.random.default_rng(n + 1)
+    x, dy, d0 = (rng.standard_normal(n).astype(np.float32) for _ in range(3))
+    a, b = 0.375, -1.25
+    X, DY, DX = dev(x), dev(dy), dev(d0)
+    assert np.array_equal(host(ctx.linear_forward(X, a, b)), restated.linear(x, a, b))
+    ctx.linear_grad(DX, a, DY)
+    assert np.array_equal(host(DX), restated.linear_grad(dy, a, d0))
+    xh, dyh, d0h = (v.astype(np.float16).astype(np.float32) for v in (x, dy, d0))
+    Xh, DYh, DXh = dev(xh, torch.float16), dev(dyh, torch.float16), dev(d0h, torch.float16)
+    check(ctx, ctx.linear_forward(Xh, a, b), restated.linear(xh, a, b), F16_TOL)
+    ctx.linear_grad(DXh, a, DYh)
+    check(ctx, DXh, restated.linear_grad(dyh, a, d0h), F16_TOL)
+
+
+@pytest.mark.parametrize("tdtype,xs,ys", [(torch.float32, (2, 70, 40), (1, 40, 96)), (torch.float16, (1, 2304, 256), (1, 256, 2304)),
+                                          (torch.float16, (1, 130, 33), (1, 33, 50))])
+def test_matmul_forward_linear_equals_the_two_calls(ctx, tdtype, xs, ys):
+    """The Linear tail of the epilogue (paired kernel, single-CTA kernels, ragged path) stores what MatrixMultiply followed by
+    Linear stores."""
+    X, Y = dev(cases.normal(31, xs), tdtype), dev(cases.normal(32, ys, 0.1), tdtype)
+    Z = ctx.matmul_forward(X, Y)
+    L = ctx.linear_forward(Z, 0.375, -1.25)
+    Z2, L2 = torch.full_like(Z, 3.0), torch.full_like(Z, 3.0)
+    ctx.matmul_forward_linear(X, Y, Z2, L2, 0.375, -1.25)
+    assert ctx.status() == 0
+    assert torch.equal(Z, Z2) and torch.equal(L, L2)
+
+
+@pytest.mark.parametrize("steps", [0, 1, 25])
+def test_adam_update_against_the_oracle(ctx, restated, steps):
+    """AdamUpdate: fp32 equal to the restated reference arithmetic bit for bit (gradient, m, v and value); fp16 within 2e-2."""
+    rng = np.random.default_rng(40 + steps)
+    n = 4096 * 9 + 3
+    w, g = rng.standard_normal(n).astype(np.float32), rng.standard_normal(n).astype(np.float32)
+    m, v = (rng.standard_normal(n) * 0.1).astype(np.float32), (rng.random(n) * 0.01).astype(np.float32)
+    args = (0.875, 0.9990234375, 2.0 ** -20, 0.0078125, 0.00048828125, steps)
+    want = restated.adam_update(w, g, m, v, *args)
+    W, G, M, V = dev(w), dev(g), dev(m), dev(v)
+    ctx.adam_update(W, G, M, V, *args)
+    assert ctx.status() == 0
+    for name, got, wnt in zip(("value", "gradient", "m", "v"), (W, G, M, V), want):
+        assert np.array_equal(host(got), wnt), name
+    h = lambda a: a.astype(np.float16).astype(np.float32)
+    wh, gh, mh, vh = h(w), h(g), h(m), h(v)
+    want = restated.adam_update(wh, gh, mh, vh, *args)
+    Wh, Gh, Mh, Vh = (dev(a, torch.float16) for a in (wh, gh, mh, vh))
+    ctx.adam_update(Wh, Gh, Mh, Vh, *args)
+    for got, wnt in zip((Wh, Gh, Mh, Vh), want):
+        check(ctx, got, wnt, F16_TOL)
+
+
+def test_sum_shards_adam_equals_sum_then_adam(ctx):
+    for dtype in (torch.float16, torch.float32):
+        n = 8 * 1024 + 3
+        gen = torch.Generator(device="cuda").manual_seed(6)
+        parts = [torch.randn(n, device="cuda", generator=gen).to(dtype) for _ in range(3)]
+        w = torch.randn(n, device="cuda", generator=gen).to(dtype)
+        m = (torch.randn(n, device="cuda", generator=gen) * 0.1).to(dtype)
+        v = (torch.rand(n, device="cuda", generator=gen) * 0.01).to(dtype)
+        args = (0.875, 0.9990234375, 2.0 ** -20, 0.0078125, 0.00048828125, 3)
+        grad = torch.empty(n, device="cuda", dtype=dtype)
+        ctx.sum_shards(dtype, grad.data_ptr(), [p.data_ptr() for p in parts], n)
+        w2, m2, v2 = w.clone(), m.clone(), v.clone()
+        ctx.adam_update(w2, grad, m2, v2, *args)
+        w1, m1, v1, g1 = w.clone(), m.clone(), v.clone(), torch.empty_like(grad)
+        copies = [torch.zeros_like(w) for _ in range(2)]
+        ctx.sum_shards(dtype, g1.data_ptr(), [p.data_ptr() for p in parts], n, adam=(w1.data_ptr(), m1.data_ptr(), v1.data_ptr()) + args,
+                       copies=[c.data_ptr() for c in copies])
+        torch.cuda.synchronize()
+        assert torch.equal(w1, w2) and torch.equal(m1, m2) and torch.equal(v1, v2) and torch.equal(g1, grad)
+        assert all(torch.equal(c, w2) for c in copies)
+    assert ctx.status() == 0
+
+
+# ------------------------------------------------------------------------------------------------ first-touch convolution gradients
+@pytest.mark.parametrize("case", [("conv",) + cases.CONV_REFERENCE_TESTS[0], ("conv",) + cases.CONV_EDGE[3], ("conv",) + cases.CONV_EDGE[6],
+                                  ("deconv",) + cases.DECONV_REFERENCE_TESTS[1], ("deconv",) + cases.DECONV_EDGE[6], ("deconv",) + cases.DECONV_EDGE[3]])
+def test_convolution_gradients_overwrite_without_zero_fill(ctx, case):
+    """accumulate=False into buffers full of garbage gives the bits of zero fill followed by +=, stride beyond the filter and
+    residue classes included."""
+    kind, xs, ws, cov, st = case[:5]
+    meta = (cov, st) + ((case[5],) if kind == "conv" else ())
+    X, W = dev(cases.uniform(51, xs)), dev(cases.normal(52, ws, 0.25))
+    fwd = ctx.conv2d_forward if kind == "conv" else ctx.deconv2d_forward
+    gx = ctx.conv2d_grad_x if kind == "conv" else ctx.deconv2d_grad_x
+    gy = ctx.conv2d_grad_y if kind == "conv" else ctx.deconv2d_grad_y
+    Z = fwd(X, W, *meta)
+    DZ = dev(cases.normal(53, tuple(Z.shape)))
+    dx_ref, dw_ref = torch.zeros_like(X), torch.zeros_like(W)
+    gx(X, dx_ref, W, DZ, *meta)
+    gy(X, W, dw_ref, DZ, *meta)
+    dx, dw = torch.full_like(X, 7.0), torch.full_like(W, 7.0)
+    gx(X, dx, W, DZ, *meta, accumulate=False)
+    gy(X, W, dw, DZ, *meta, accumulate=False)
+    assert ctx.status() == 0
+    assert torch.equal(dx, dx_ref) and torch.equal(dw, dw_ref)
+
+
+def test_matrix_vector_kernels_take_the_single_column_case(ctx):
+    X, Y = dev(cases.uniform(61, (2, 64, 256))), dev(cases.uniform(62, (1, 256, 1)))
+    ctx.matmul_forward(X, Y)
+    assert "matvec rows" in ctx.last_kernel()
+    dz, dx, dy = dev(cases.uniform(63, (2, 64, 1))), torch.zeros_like(X), torch.zeros_like(Y)
+    ctx.matmul_grad_x(X, dx, Y, dz)
+    assert "outer product" in ctx.last_kernel()
+    ctx.matmul_grad_y(X, Y, dy, dz)
+    assert "matvec columns" in ctx.last_kernel()
+    Yb = dev(cases.uniform(64, (6, 256, 1)))
+    Xb = dev(cases.uniform(65, (1, 64, 256)))
+    ctx.matmul_forward(Xb, Yb)
+    assert "tma" in ctx.last_kernel()       # the batch of vectors as one contraction through the TMA producer
+    assert ctx.status() == 0

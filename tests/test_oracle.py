@@ -181,3 +181,36 @@ def test_bias_add_and_its_gradient_restated_equal_reference(restated, reference)
         assert np.array_equal(restated.add_bias_grad(xi, b * 0 + 3), reference.add_bias_grad(xi, b * 0 + 3))
         got, want = restated.add_bias_grad(x, b), reference.add_bias_grad(x, b)
         assert np.abs(got - want).max() <= 1e-5 * max(np.abs(want).max(), 1e-30)
+
+
+@pytest.mark.parametrize("dtype", [np.float32, np.float64])
+def test_relu_and_linear_restated_equal_reference_bit_for_bit(restated, reference, dtype):
+    """Math::ReLu / ReLuGrad (deep8/src/math/ReLu.cpp) and Math::Linear / LinearGrad (deep8/src/math/Linear.cpp): the
+    restatement rounds where the reference's Eigen expressions round, so the arrays are identical.  a and b are floats in
+    the reference's interface: values a float holds exactly make the float64 case comparable too."""
+    rng = np.random.default_rng(11)
+    n = 100003
+    x, dy, d0 = (rng.standard_normal(n).astype(dtype) for _ in range(3))
+    x[::17] = 0  # the boundary of x > 0
+    assert np.array_equal(restated.relu(x), reference.relu(x))
+    assert np.array_equal(restated.relu_grad(x, dy, d0), reference.relu_grad(x, dy, d0))
+    for a, b in ((0.375, -1.25), (-3.0, 0.0), (1.0, 2.0 ** -10)):
+        assert np.array_equal(restated.linear(x, a, b), reference.linear(x, a, b))
+        assert np.array_equal(restated.linear_grad(dy, a, d0), reference.linear_grad(dy, a, d0))
+
+
+@pytest.mark.parametrize("steps", [0, 1, 7, 1000])
+def test_adam_update_restated_against_reference(restated, reference, steps):
+    """Math::AdamUpdate (deep8/src/math/AdamUpdate.cpp:24-41): gradient, m and v come out identical; value goes through the
+    reference's sqrt, which under EIGEN_FAST_MATH is Eigen's reciprocal-square-root approximation with one Newton step,
+    so it is compared to a few units in the last place instead."""
+    rng = np.random.default_rng(13)
+    n = 50001
+    w, g = rng.standard_normal(n).astype(np.float32), rng.standard_normal(n).astype(np.float32)
+    m, v = (rng.standard_normal(n) * 0.1).astype(np.float32), (rng.random(n) * 0.01).astype(np.float32)
+    args = (0.875, 0.9990234375, 2.0 ** -20, 0.0078125, 0.00048828125, steps)   # exactly representable floats
+    got, want = restated.adam_update(w, g, m, v, *args), reference.adam_update(w, g, m, v, *args)
+    for k in (1, 2, 3):
+        assert np.array_equal(got[k], want[k])
+    assert np.abs(got[0] - want[0]).max() <= 4 * np.finfo(np.float32).eps * np.abs(want[0]).max()
+    assert not np.array_equal(got[0], w)
