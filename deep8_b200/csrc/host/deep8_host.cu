@@ -333,6 +333,14 @@ void Tensor::zero() { Math::Constant(*this, 0); }
 namespace Math {
 
 namespace {
+thread_local bool g_overwriteGradient = false;
+int accumulateFlag() { return g_overwriteGradient ? 0 : 1; }
+}  // namespace
+OverwriteGradient::OverwriteGradient(bool on) : previous(g_overwriteGradient) { g_overwriteGradient = on; }
+OverwriteGradient::~OverwriteGradient() { g_overwriteGradient = previous; }
+bool OverwriteGradient::active() { return g_overwriteGradient; }
+
+namespace {
 void checkMatMul(const Tensor& x, const Tensor& y, const Tensor& z) {
     DEEP8_ARGUMENT_CHECK(x.deviceType() == y.deviceType() && x.deviceType() == z.deviceType(), "the device type must be same");
     DEEP8_ARGUMENT_CHECK(x.elementType == y.elementType && x.elementType == z.elementType, "the data type must be same");
@@ -361,8 +369,8 @@ void MatrixMultiplyGradX(const Tensor& x, Tensor& dx, const Tensor& y, const Ten
     MatrixMultiplyGradXGPU(x, dx, y, z, dz);
 }
 void MatrixMultiplyGradXGPU(const Tensor& x, Tensor& dx, const Tensor& y, const Tensor&, const Tensor& dz) {
-    d8kCheck(d8k_matmul_grad_x(gpuOf(x)->kernels, d8kType(x), dx.raw(), (int)x.batch(), (int)x.row(), (int)x.col(), y.raw(), (int)y.batch(),
-                               (int)y.col(), dz.raw()));
+    d8kCheck(d8k_matmul_grad_x_into(gpuOf(x)->kernels, d8kType(x), dx.raw(), (int)x.batch(), (int)x.row(), (int)x.col(), y.raw(),
+                                    (int)y.batch(), (int)y.col(), dz.raw(), accumulateFlag()));
 }
 void MatrixMultiplyGradY(const Tensor& x, const Tensor& y, Tensor& dy, const Tensor& z, const Tensor& dz) {
     checkMatMul(x, y, z);
@@ -371,8 +379,8 @@ void MatrixMultiplyGradY(const Tensor& x, const Tensor& y, Tensor& dy, const Ten
     MatrixMultiplyGradYGPU(x, y, dy, z, dz);
 }
 void MatrixMultiplyGradYGPU(const Tensor& x, const Tensor& y, Tensor& dy, const Tensor&, const Tensor& dz) {
-    d8kCheck(d8k_matmul_grad_y(gpuOf(x)->kernels, d8kType(x), x.raw(), (int)x.batch(), (int)x.row(), (int)x.col(), dy.raw(), (int)y.batch(),
-                               (int)y.col(), dz.raw()));
+    d8kCheck(d8k_matmul_grad_y_into(gpuOf(x)->kernels, d8kType(x), x.raw(), (int)x.batch(), (int)x.row(), (int)x.col(), dy.raw(),
+                                    (int)y.batch(), (int)y.col(), dz.raw(), accumulateFlag()));
 }
 
 namespace {
@@ -446,8 +454,8 @@ void Conv2dGradX(const Tensor& x, Tensor& dx, const Tensor& y, const Tensor& z, 
 void Conv2dGradXGPU(const Tensor& x, Tensor& dx, const Tensor& y, const Tensor& z, const Tensor& dz, bool covered, int sY, int sX, int dY,
                     int dX, void* dxcol) {
     ConvGeom g = convGeom(x, y, z, covered, sY, sX, dY, dX);
-    d8kCheck(d8k_conv2d_grad_x(gpuOf(x)->kernels, d8kType(x), dx.raw(), g.batch, g.ih, g.iw, g.ic, y.raw(), g.oc, g.fh, g.fw, dz.raw(), g.oh,
-                               g.ow, sY, sX, dY, dX, dxcol, dxcol ? interim(x, g, 1, false) : 0));
+    d8kCheck(d8k_conv2d_grad_x_into(gpuOf(x)->kernels, d8kType(x), dx.raw(), g.batch, g.ih, g.iw, g.ic, y.raw(), g.oc, g.fh, g.fw, dz.raw(),
+                                    g.oh, g.ow, sY, sX, dY, dX, dxcol, dxcol ? interim(x, g, 1, false) : 0, accumulateFlag()));
 }
 void Conv2dGradY(const Tensor& x, const Tensor& y, Tensor& dy, const Tensor& z, const Tensor& dz, bool covered, int sY, int sX, int dY, int dX,
                  void* interimPtr) {
@@ -459,8 +467,8 @@ void Conv2dGradY(const Tensor& x, const Tensor& y, Tensor& dy, const Tensor& z, 
 void Conv2dGradYGPU(const Tensor& x, const Tensor& y, Tensor& dy, const Tensor& z, const Tensor& dz, bool covered, int sY, int sX, int dY,
                     int dX, void* xcol) {
     ConvGeom g = convGeom(x, y, z, covered, sY, sX, dY, dX);
-    d8kCheck(d8k_conv2d_grad_y(gpuOf(x)->kernels, d8kType(x), x.raw(), g.batch, g.ih, g.iw, g.ic, dy.raw(), g.oc, g.fh, g.fw, dz.raw(), g.oh,
-                               g.ow, sY, sX, dY, dX, xcol, xcol ? interim(x, g, 2, false) : 0));
+    d8kCheck(d8k_conv2d_grad_y_into(gpuOf(x)->kernels, d8kType(x), x.raw(), g.batch, g.ih, g.iw, g.ic, dy.raw(), g.oc, g.fh, g.fw, dz.raw(),
+                                    g.oh, g.ow, sY, sX, dY, dX, xcol, xcol ? interim(x, g, 2, false) : 0, accumulateFlag()));
 }
 
 size_t DeConv2dInterimSize(const Tensor& x, const Tensor& y, Tensor& z, bool covered, int sY, int sX) {
@@ -491,8 +499,8 @@ void DeConv2dGradX(const Tensor& x, Tensor& dx, const Tensor& y, const Tensor& z
 void DeConv2dGradXGPU(const Tensor& x, Tensor& dx, const Tensor& y, const Tensor& z, const Tensor& dz, bool covered, int sY, int sX,
                       void* interimPtr) {
     ConvGeom g = deconvGeom(x, y, z, covered, sY, sX);
-    d8kCheck(d8k_deconv2d_grad_x(gpuOf(x)->kernels, d8kType(x), dx.raw(), g.batch, g.ih, g.iw, g.ic, y.raw(), g.oc, g.fh, g.fw, dz.raw(), g.oh,
-                                 g.ow, sY, sX, interimPtr, interimPtr ? interim(x, g, 1, true) : 0));
+    d8kCheck(d8k_deconv2d_grad_x_into(gpuOf(x)->kernels, d8kType(x), dx.raw(), g.batch, g.ih, g.iw, g.ic, y.raw(), g.oc, g.fh, g.fw, dz.raw(),
+                                      g.oh, g.ow, sY, sX, interimPtr, interimPtr ? interim(x, g, 1, true) : 0, accumulateFlag()));
 }
 void DeConv2dGradY(const Tensor& x, const Tensor& y, Tensor& dy, const Tensor& z, const Tensor& dz, bool covered, int sY, int sX,
                    void* interimPtr) {
@@ -504,8 +512,8 @@ void DeConv2dGradY(const Tensor& x, const Tensor& y, Tensor& dy, const Tensor& z
 void DeConv2dGradYGPU(const Tensor& x, const Tensor& y, Tensor& dy, const Tensor& z, const Tensor& dz, bool covered, int sY, int sX,
                       void* interimPtr) {
     ConvGeom g = deconvGeom(x, y, z, covered, sY, sX);
-    d8kCheck(d8k_deconv2d_grad_y(gpuOf(x)->kernels, d8kType(x), x.raw(), g.batch, g.ih, g.iw, g.ic, dy.raw(), g.oc, g.fh, g.fw, dz.raw(), g.oh,
-                                 g.ow, sY, sX, interimPtr, interimPtr ? interim(x, g, 2, true) : 0));
+    d8kCheck(d8k_deconv2d_grad_y_into(gpuOf(x)->kernels, d8kType(x), x.raw(), g.batch, g.ih, g.iw, g.ic, dy.raw(), g.oc, g.fh, g.fw, dz.raw(),
+                                      g.oh, g.ow, sY, sX, interimPtr, interimPtr ? interim(x, g, 2, true) : 0, accumulateFlag()));
 }
 
 void ReLu(const Tensor& x, Tensor& y) {
@@ -540,19 +548,76 @@ void AddGradX(const Tensor& x, Tensor& dx, const Tensor& y, const Tensor& z, con
     DEEP8_ARGUMENT_CHECK(x.shape == dx.shape && z.shape == dz.shape && x.shape == z.shape, "the shape is error");
     DEEP8_ARGUMENT_CHECK(x.elementType == dx.elementType && x.elementType == dz.elementType, "the param data type must be same");
     addKind(x, y);
-    const void* src[2] = {dx.raw(), dz.raw()};  // dx += dz
-    d8kCheck(d8k_sum_shards(gpuOf(x)->kernels, d8kType(x), dx.raw(), src, 2, dx.size()));
+    const void* src[2] = {dz.raw(), dx.raw()};  // dx += dz, or dx = dz for a first contribution
+    d8kCheck(d8k_sum_shards(gpuOf(x)->kernels, d8kType(x), dx.raw(), src, OverwriteGradient::active() ? 1 : 2, dx.size()));
 }
 void AddGradY(const Tensor& x, const Tensor& y, Tensor& dy, const Tensor& z, const Tensor& dz) {
     DEEP8_ARGUMENT_CHECK(y.shape == dy.shape && z.shape == dz.shape && x.shape == z.shape, "the shape is error");
     DEEP8_ARGUMENT_CHECK(x.elementType == dy.elementType && x.elementType == dz.elementType, "the param data type must be same");
     if (0 == addKind(x, y)) {
-        const void* src[2] = {dy.raw(), dz.raw()};
-        d8kCheck(d8k_sum_shards(gpuOf(x)->kernels, d8kType(x), dy.raw(), src, 2, dy.size()));
+        const void* src[2] = {dz.raw(), dy.raw()};
+        d8kCheck(d8k_sum_shards(gpuOf(x)->kernels, d8kType(x), dy.raw(), src, OverwriteGradient::active() ? 1 : 2, dy.size()));
     } else {
+        if (OverwriteGradient::active()) dy.zero();  // the column sums add into dy: a small vector, zeroed here for a first contribution
         d8kCheck(d8k_add_bias_grad(gpuOf(x)->kernels, d8kType(x), dy.raw(), dz.raw(), dz.size() / dy.size(), (int)dy.size()));
     }
 }
+// deep8/src/math/Linear.cpp:9-44
+void Linear(const Tensor& x, const float a, const float b, Tensor& y) {
+    DEEP8_ARGUMENT_CHECK(x.deviceType() == y.deviceType(), "the param device type must be same");
+    DEEP8_ARGUMENT_CHECK(x.elementType == y.elementType, "the param data type must be same");
+    DEEP8_ARGUMENT_CHECK(x.shape == y.shape, "the param shape must be same");
+    d8kCheck(d8k_linear_forward(gpuOf(x)->kernels, d8kType(x), x.raw(), a, b, y.raw(), x.size()));
+}
+void LinearGrad(const Tensor& x, Tensor& dx, const float a, const float, const Tensor& y, const Tensor& dy) {
+    DEEP8_ARGUMENT_CHECK(x.elementType == dx.elementType && x.elementType == y.elementType && x.elementType == dy.elementType,
+                         "the param data type must be same");
+    DEEP8_ARGUMENT_CHECK(x.shape == dx.shape && x.shape == y.shape && x.shape == dy.shape, "the param shape must be same");
+    d8kCheck(d8k_linear_grad(gpuOf(x)->kernels, d8kType(x), dx.raw(), a, dy.raw(), dx.size()));
+}
+// deep8/src/math/AdamUpdate.cpp:6-22
+void AdamUpdate(Tensor& value, Tensor& gradient, Tensor& m, Tensor& v, float beta1, float beta2, float epsilon, float learningRate,
+                float weightDecay, int64_t steps) {
+    DEEP8_ARGUMENT_CHECK(value.elementType == gradient.elementType && value.elementType == m.elementType && value.elementType == v.elementType,
+                         "the param data type must be same");
+    DEEP8_ARGUMENT_CHECK(value.shape.size() == gradient.shape.size() && value.shape.size() == m.shape.size() &&
+                             value.shape.size() == v.shape.size(),
+                         "the param shape size must be same");
+    d8kCheck(d8k_adam_update(gpuOf(value)->kernels, d8kType(value), value.raw(), gradient.raw(), m.raw(), v.raw(), beta1, beta2, epsilon,
+                             learningRate, weightDecay, steps, value.size()));
+}
+
+void MatrixMultiplyReLu(const Tensor& x, const Tensor& y, Tensor& z, Tensor& a) {
+    checkMatMul(x, y, z);
+    DEEP8_ARGUMENT_CHECK(z.shape == a.shape && z.elementType == a.elementType, "the shape or type is error");
+    d8kCheck(d8k_matmul_forward_relu(gpuOf(x)->kernels, d8kType(x), x.raw(), (int)x.batch(), (int)x.row(), (int)x.col(), y.raw(), (int)y.batch(),
+                                     (int)y.col(), z.raw(), a.raw()));
+}
+void MatrixMultiplyLinear(const Tensor& x, const Tensor& y, Tensor& z, float a, float b, Tensor& l) {
+    checkMatMul(x, y, z);
+    DEEP8_ARGUMENT_CHECK(z.shape == l.shape && z.elementType == l.elementType, "the shape or type is error");
+    d8kCheck(d8k_matmul_forward_linear(gpuOf(x)->kernels, d8kType(x), x.raw(), (int)x.batch(), (int)x.row(), (int)x.col(), y.raw(),
+                                       (int)y.batch(), (int)y.col(), z.raw(), a, b, l.raw()));
+}
+void MatrixMultiplyAddBias(const Tensor& x, const Tensor& y, const Tensor& bias, Tensor& z) {
+    checkMatMul(x, y, z);
+    DEEP8_ARGUMENT_CHECK(bias.elementType == z.elementType && 1 == bias.batch() && 1 == bias.nDims() && bias.dim(0) == y.col() && y.col() > 1,
+                         "the bias must be one row of y.col() elements");
+    d8kCheck(d8k_matmul_forward_bias(gpuOf(x)->kernels, d8kType(x), x.raw(), (int)x.batch(), (int)x.row(), (int)x.col(), y.raw(), (int)y.batch(),
+                                     (int)y.col(), bias.raw(), z.raw()));
+}
+void MatrixMultiplyGradXReLuGrad(const Tensor& x, Tensor& dx, const Tensor& y, const Tensor& z, const Tensor& dz, const Tensor& h, Tensor& dh,
+                                 bool accumulateDx, bool accumulateDh) {
+    checkMatMul(x, y, z);
+    DEEP8_ARGUMENT_CHECK(x.shape == dx.shape && z.shape == dz.shape && h.shape.size() == x.shape.size() && dh.shape.size() == x.shape.size(),
+                         "the shape is error");
+    DEEP8_ARGUMENT_CHECK(x.elementType == dx.elementType && x.elementType == dz.elementType && x.elementType == h.elementType &&
+                             x.elementType == dh.elementType,
+                         "the data type must be same");
+    d8kCheck(d8k_matmul_grad_x_relu(gpuOf(x)->kernels, d8kType(x), dx.raw(), (int)x.batch(), (int)x.row(), (int)x.col(), y.raw(), (int)y.batch(),
+                                    (int)y.col(), dz.raw(), accumulateDx ? 1 : 0, h.raw(), dh.raw(), accumulateDh ? 1 : 0));
+}
+
 void AXPBY(const Tensor& x, float alpha, const Tensor& y, float beta, Tensor& z) {
     DEEP8_ARGUMENT_CHECK(x.elementType == y.elementType && x.elementType == z.elementType, "the param data type must be same");
     DEEP8_ARGUMENT_CHECK(x.shape.size() == y.shape.size() && x.shape.size() == z.shape.size(), "the param shape size must be same");
@@ -616,11 +681,17 @@ void Variable::removeGradient() {
 }
 Variable& Variable::feed(const void* cpuPtr) {
     DEEP8_ARGUMENT_CHECK(nullptr != cpuPtr, "the pointer can not be null");
+    if (executor) executor->flush();  // a held product was defined with the values of the moment it was added
+    valueStale = false;
     value.device()->copyFromCPUToGPU(cpuPtr, value.raw(), value.byteCount());
     return *this;
 }
 Variable& Variable::fetch(void* cpuPtr) {
     DEEP8_ARGUMENT_CHECK(nullptr != cpuPtr, "the pointer can not be null");
+    if (executor) {
+        executor->flush();
+        executor->materialise(this);
+    }
     static_cast<GPUDevice*>(value.device())->synchronize();
     value.device()->copyFromGPUToCPU(value.raw(), cpuPtr, value.byteCount());
     return *this;
@@ -628,6 +699,7 @@ Variable& Variable::fetch(void* cpuPtr) {
 Variable& Variable::feedGradient(const void* cpuPtr) {
     DEEP8_ARGUMENT_CHECK(updateGradient && nullptr != cpuPtr, "the Variable has no gradient");
     gradient.device()->copyFromCPUToGPU(cpuPtr, gradient.raw(), gradient.byteCount());
+    gradientTouched = true;
     return *this;
 }
 Variable& Variable::fetchGradient(void* cpuPtr) {
@@ -637,6 +709,8 @@ Variable& Variable::fetchGradient(void* cpuPtr) {
     return *this;
 }
 Variable& Variable::zero() {
+    if (executor) executor->flush();
+    valueStale = false;
     value.zero();
     return *this;
 }
@@ -675,16 +749,30 @@ void Function::backward() {
     DEEP8_ARGUMENT_CHECK(1 == outputs.size(), "the output size must be 1");
     DEEP8_ARGUMENT_CHECK(NodeType::Variable == outputs.first()->type, "the output must be Variable type");
     auto out = static_cast<Variable*>(outputs.first());
+    if (out->updateGradient && !out->gradientTouched) {  // nothing has contributed to it: the zeros the reference's zero fill leaves
+        out->zeroGradient();
+        out->gradientTouched = true;
+    }
     std::vector<const Tensor*> values;
     for (auto item : inputs) values.push_back(&static_cast<Variable*>(item)->value);
     for (size_t i = 0; i < inputs.size(); ++i) {
         auto in = static_cast<Variable*>(inputs[i]);
-        if (in->updateGradient) backward(values, &out->value, &out->gradient, i, &in->gradient);
+        if (!in->updateGradient) continue;
+        bool first = !in->gradientTouched;
+        if (first && !canOverwriteGradient(i)) {  // this node can only add: give it zeros to add to
+            in->zeroGradient();
+            first = false;
+        }
+        {
+            Math::OverwriteGradient guard(first);
+            backward(values, &out->value, &out->gradient, i, &in->gradient);
+        }
+        in->gradientTouched = true;
     }
 }
 
 // ---- MatrixMultiply (deep8/src/nodes/MatrixMultiply.cpp)
-MatrixMultiply::MatrixMultiply(std::vector<Node*>& in) : Function(in) {}
+MatrixMultiply::MatrixMultiply(std::vector<Node*>& in) : Function(in) { functionType = FunctionType::MatrixMultiply; }
 
 Shape MatrixMultiply::checkShape(std::vector<Shape>& s) {
     DEEP8_ARGUMENT_CHECK(2 == s.size(), "the input count must be 2");
@@ -706,6 +794,7 @@ void MatrixMultiply::backward(const std::vector<const Tensor*>& in, const Tensor
 // ---- Conv2d (deep8/src/nodes/Conv2d.cpp)
 Conv2d::Conv2d(std::vector<Node*>& in, bool c, int sY, int sX, int dY, int dX)
     : Function(in), covered(c), strideY(sY), strideX(sX), dilationY(dY), dilationX(dX) {
+    functionType = FunctionType::Conv2d;
     DEEP8_ARGUMENT_CHECK(strideY >= 1 && strideX >= 1 && dilationY >= 1 && dilationX >= 1, "the stride and dilation must >= 1");
 }
 
@@ -758,6 +847,7 @@ void Conv2d::backward(const std::vector<const Tensor*>& in, const Tensor* out, c
 
 // ---- DeConv2d (deep8/src/nodes/DeConv2d.cpp)
 DeConv2d::DeConv2d(std::vector<Node*>& in, bool c, int sY, int sX) : Function(in), forwardCovered(c), forwardStrideY(sY), forwardStrideX(sX) {
+    functionType = FunctionType::DeConv2d;
     DEEP8_ARGUMENT_CHECK(forwardStrideY >= 1 && forwardStrideX >= 1, "the stride must >= 1");
 }
 
@@ -789,7 +879,7 @@ void DeConv2d::backward(const std::vector<const Tensor*>& in, const Tensor* out,
 }
 
 // ---- Add (deep8/src/nodes/Add.cpp): output shape = x's; y equal to it or a bias over the last dimension
-Add::Add(std::vector<Node*>& in) : Function(in) {}
+Add::Add(std::vector<Node*>& in) : Function(in) { functionType = FunctionType::Add; }
 Shape Add::checkShape(std::vector<Shape>& s) {
     DEEP8_ARGUMENT_CHECK(2 == s.size(), "the input count must be 2");
     const Shape &x = s[0], &y = s[1];
@@ -805,7 +895,7 @@ void Add::backward(const std::vector<const Tensor*>& in, const Tensor* out, cons
 }
 
 // ---- ReLu (deep8/src/nodes/ReLu.cpp)
-ReLu::ReLu(std::vector<Node*>& in) : Function(in) {}
+ReLu::ReLu(std::vector<Node*>& in) : Function(in) { functionType = FunctionType::ReLu; }
 Shape ReLu::checkShape(std::vector<Shape>& s) {
     DEEP8_ARGUMENT_CHECK(1 == s.size(), "the input count must be 1");
     return s[0];
@@ -814,6 +904,25 @@ void ReLu::forward(const std::vector<const Tensor*>& in, Tensor* out) { Math::Re
 void ReLu::backward(const std::vector<const Tensor*>& in, const Tensor* out, const Tensor* dOut, size_t index, Tensor* dIn) {
     DEEP8_ARGUMENT_CHECK(0 == index, "the index is error");
     Math::ReLuGrad(*in[0], *dIn, *out, *dOut);
+}
+
+// ---- Linear (deep8/src/nodes/Linear.cpp)
+Linear::Linear(std::vector<Node*>& in, float aa, float bb) : Function(in), a(aa), b(bb) {
+    functionType = FunctionType::Linear;
+    DEEP8_ARGUMENT_CHECK(1 == this->inputs.size(), "the Linear Function needs 1 input");
+}
+Shape Linear::checkShape(std::vector<Shape>& s) {
+    DEEP8_ARGUMENT_CHECK(1 == s.size(), "the input count must be 1");
+    return s[0];
+}
+ElementType Linear::checkElementType(std::vector<ElementType>& t) {
+    DEEP8_ARGUMENT_CHECK(1 == t.size(), "the input count must be 1");
+    return Function::checkElementType(t);
+}
+void Linear::forward(const std::vector<const Tensor*>& in, Tensor* out) { Math::Linear(*in[0], a, b, *out); }
+void Linear::backward(const std::vector<const Tensor*>& in, const Tensor* out, const Tensor* dOut, size_t index, Tensor* dIn) {
+    DEEP8_ARGUMENT_CHECK(0 == index, "the index is error");
+    Math::LinearGrad(*in[0], *dIn, a, b, *out, *dOut);
 }
 
 // ================================================================================================ executors
@@ -892,6 +1001,7 @@ Variable* Executor::createVariableByFunction(Function* func) {
 }
 
 void Executor::clearInterimNodes() {
+    flush();  // a held product belongs to the nodes about to be deleted
     for (auto& item : allNodes) {
         item.second->inputs.clear();
         item.second->outputs.clear();
@@ -918,6 +1028,32 @@ std::vector<Variable*> Executor::trainableParameters() {
 
 EagerExecutor::EagerExecutor(DeviceType deviceType, int deviceId) : Executor(deviceType, deviceId) {}
 
+void EagerExecutor::setFusion(bool on) {
+    flush();
+    fuse = on;
+}
+void EagerExecutor::setFirstTouch(bool on) { touch = on; }
+
+void EagerExecutor::flush() {
+    if (nullptr == pending) return;
+    Function* f = pending;
+    pending = nullptr;
+    f->forward();
+}
+
+void EagerExecutor::materialise(Variable* v) {
+    if (nullptr == v || !v->valueStale) return;
+    DEEP8_ARGUMENT_CHECK(1 == v->inputs.size() && NodeType::Function == v->inputs[0]->type, "a stale value needs the function that produces it");
+    v->valueStale = false;
+    static_cast<Function*>(v->inputs[0])->forward();
+}
+
+namespace {
+bool isBias(const Variable* b, const Variable* of) {
+    return 1 == b->value.batch() && 1 == b->value.nDims() && of->value.nDims() == 2 && b->value.dim(0) == of->value.col();
+}
+}  // namespace
+
 Variable* EagerExecutor::addFunction(Function* function) {
     function->id = generateUniqueId();
     function->name = generateUniqueName("Function");
@@ -927,7 +1063,41 @@ Variable* EagerExecutor::addFunction(Function* function) {
     allNodes[variable->name] = variable;
     interimNodes[function->name] = function;
     interimNodes[variable->name] = variable;
-    function->forward();  // eager: the output is computed as the graph is built
+    // eager: the output is computed as the graph is built - except that a MatrixMultiply waits for the next node, so that a
+    // ReLu, a Linear or a bias Add of its product can run inside its launch
+    if (nullptr != pending) {
+        Function* prod = pending;
+        auto z = static_cast<Variable*>(prod->outputs.first());
+        auto x = static_cast<Variable*>(prod->inputs[0]);
+        auto y = static_cast<Variable*>(prod->inputs[1]);
+        const bool consumesProduct = !function->inputs.empty() && function->inputs[0] == z;
+        if (consumesProduct && FunctionType::ReLu == function->functionType) {
+            pending = nullptr;
+            Math::MatrixMultiplyReLu(x->value, y->value, z->value, variable->value);
+            return variable;
+        }
+        if (consumesProduct && FunctionType::Linear == function->functionType) {
+            pending = nullptr;
+            auto lin = static_cast<Linear*>(function);
+            Math::MatrixMultiplyLinear(x->value, y->value, z->value, lin->a, lin->b, variable->value);
+            return variable;
+        }
+        if (consumesProduct && FunctionType::Add == function->functionType && 2 == function->inputs.size() && function->inputs[1] != z &&
+            isBias(static_cast<Variable*>(function->inputs[1]), z)) {
+            pending = nullptr;
+            Math::MatrixMultiplyAddBias(x->value, y->value, static_cast<Variable*>(function->inputs[1])->value, variable->value);
+            z->valueStale = true;  // the product itself was never stored: computed if anybody asks for it
+            return variable;
+        }
+        flush();
+    }
+    for (auto in : function->inputs) materialise(static_cast<Variable*>(in));
+    if (fuse && FunctionType::MatrixMultiply == function->functionType) {
+        (void)d8kType(variable->value);  // an unsupported element type is reported now, when the node is added, not when it runs
+        pending = function;
+        return variable;
+    }
+    function->forward();
     return variable;
 }
 
@@ -961,13 +1131,60 @@ void EagerExecutor::backward(Node* last, bool clearInterim) {
     backward(v, v->elementType().id == DType::Float16 ? static_cast<const void*>(&one16) : static_cast<const void*>(&one32), clearInterim);
 }
 
+// One node of the backward walk.  A MatrixMultiply z = a * w whose first operand is a = ReLu(h), consumed by nothing else, runs
+// its gradient of a together with ReLu's gradient (one launch); the ReLu node is then done.
+void EagerExecutor::backwardNode(Node* n, std::unordered_set<Node*>& done) {
+    if (done.count(n)) return;
+    if (fuse && NodeType::Function == n->type && FunctionType::MatrixMultiply == static_cast<Function*>(n)->functionType && 2 == n->inputs.size() &&
+        1 == n->outputs.size()) {
+        auto f = static_cast<Function*>(n);
+        auto z = static_cast<Variable*>(f->outputs.first());
+        auto a = static_cast<Variable*>(f->inputs[0]);
+        auto w = static_cast<Variable*>(f->inputs[1]);
+        Function* r = (1 == a->inputs.size() && NodeType::Function == a->inputs[0]->type) ? static_cast<Function*>(a->inputs[0]) : nullptr;
+        if (a->updateGradient && a != w && 1 == a->outputs.size() && nullptr != r && FunctionType::ReLu == r->functionType && !done.count(r) &&
+            1 == r->inputs.size()) {
+            auto h = static_cast<Variable*>(r->inputs[0]);
+            if (h->updateGradient && h != a && h != w && h != z) {
+                if (z->updateGradient && !z->gradientTouched) {
+                    z->zeroGradient();
+                    z->gradientTouched = true;
+                }
+                Math::MatrixMultiplyGradXReLuGrad(a->value, a->gradient, w->value, z->value, z->gradient, h->value, h->gradient, a->gradientTouched,
+                                                  h->gradientTouched);
+                a->gradientTouched = h->gradientTouched = true;
+                done.insert(r);
+                if (w->updateGradient) {
+                    Math::OverwriteGradient guard(!w->gradientTouched);
+                    Math::MatrixMultiplyGradY(a->value, w->value, w->gradient, z->value, z->gradient);
+                    w->gradientTouched = true;
+                }
+                return;
+            }
+        }
+    }
+    n->backward();
+}
+
 void EagerExecutor::backward(Variable* last, const void* hostGradient, bool clearInterim) {
     DEEP8_ARGUMENT_CHECK(nullptr != last && last->updateGradient && nullptr != hostGradient, "the last Variable needs a gradient");
-    bfs(last, [](Node* n) {
-        if (NodeType::Variable == n->type) static_cast<Variable*>(n)->zeroGradient();
+    flush();
+    bfs(last, [this](Node* n) {
+        if (NodeType::Variable != n->type) return;
+        auto v = static_cast<Variable*>(n);
+        if (touch) v->gradientTouched = false;  // the first contribution will overwrite
+        else v->zeroGradient();                 // the reference's walk: zero everything, then add
     });
     last->feedGradient(hostGradient);
-    bfs(last, [](Node* n) { n->backward(); });
+    std::unordered_set<Node*> done;
+    bfs(last, [this, &done](Node* n) { backwardNode(n, done); });
+    if (touch)
+        bfs(last, [](Node* n) {  // a gradient nothing contributed to reads as zeros, as after the reference's zero fill
+            if (NodeType::Variable != n->type) return;
+            auto v = static_cast<Variable*>(n);
+            if (v->updateGradient && !v->gradientTouched) v->zeroGradient();
+            v->gradientTouched = true;
+        });
     if (clearInterim) clearInterimNodes();
 }
 
@@ -1001,6 +1218,12 @@ Variable& Variable::relu() {
     return *executor->addFunction(new ReLu(in));
 }
 
+Variable& Variable::linear(float a, float b) {
+    std::vector<Node*> in = {this};
+    return *executor->addFunction(new Linear(in, a, b));
+}
+Variable& linear(Variable& x, float a, float b) { return x.linear(a, b); }
+
 Variable& Variable::add(Variable& y) {
     std::vector<Node*> in = {this, &y};
     return *executor->addFunction(new Add(in));
@@ -1018,6 +1241,7 @@ Trainer::Trainer(LearningRateIterator* lr, float decay) : steps(0), learningRate
 void Trainer::update(Executor*, Variable*, float, float, int64_t) { DEEP8_RUNTIME_ERROR("can not call this function in trainer"); }
 void Trainer::train(Executor* executor, std::vector<Variable*> parameters) {
     if (parameters.empty()) return;
+    executor->flush();  // a held product must read the weights as they are now
     float lr = learningRate->next(steps);
     for (auto parameter : parameters) {
         if (!parameter->updateGradient) continue;
@@ -1032,6 +1256,26 @@ void SGDTrainer::update(Executor*, Variable* parameter, float learningRate, floa
     float alpha = -1 * learningRate;
     float beta = (1.0 - learningRate * weightDecay);  // the reference's mix: float product, double difference (SGDTrainer.cpp:13-14)
     Math::AXPBY(parameter->gradient, alpha, parameter->value, beta, parameter->value);
+}
+
+// deep8/src/trainer/AdamTrainer.cpp
+AdamTrainer::AdamTrainer(LearningRateIterator* lr, float b1, float b2, float e, float decay) : Trainer(lr, decay), beta1(b1), beta2(b2), epsilon(e) {}
+void AdamTrainer::update(Executor* executor, Variable* parameter, float learningRate, float weightDecay, int64_t steps) {
+    auto value = parameter->value;
+    auto gradient = parameter->gradient;
+    if (m.find(parameter) == m.end()) {
+        auto mt = executor->addVariable(value.shape, value.elementType, false);
+        mt->value.zero();
+        m[parameter] = mt;
+    }
+    if (v.find(parameter) == v.end()) {
+        auto vt = executor->addVariable(value.shape, value.elementType, false);
+        vt->value.zero();
+        v[parameter] = vt;
+    }
+    auto mt = m[parameter]->value;
+    auto vt = v[parameter]->value;
+    Math::AdamUpdate(value, gradient, mt, vt, beta1, beta2, this->epsilon, learningRate, weightDecay, steps);
 }
 
 Variable& operator*(Variable& x, Variable& y) { return x.matrixMultiply(y); }

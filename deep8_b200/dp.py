@@ -184,6 +184,7 @@ class PeerAllReduce:
         self.result = self.rt.view(self.base + self.off_result, (numel,), dtype, device) if self.world > 1 else self.partial
         self.weights = self.rt.view(self.base + self.off_weights, (numel,), dtype, device) if with_weights else None
         self.order = peer_rotation(self.world, self.rank)
+        self.adam_m = self.adam_v = None  # optimiser state of the owned shard, created by the first start(adam=...)
         self.e_written = self.rt.event()
         self.e_done = self.rt.event()
         if self.world > 1:
@@ -215,8 +216,12 @@ class PeerAllReduce:
         if self.world > 1 and self.step > 0:
             self.ctx_main.peer_wait([self._flag(self.rank, 1, q) for q in self.order], self.step, self.timeout_ms)
 
-    def start(self, sgd=None):
+    def start(self, sgd=None, adam=None):
         """Call after the contraction that writes `partial` has been enqueued on the main stream.
+        adam = (beta1, beta2, epsilon, learning_rate, weight_decay, steps): Math::AdamUpdate (AdamTrainer::update,
+        deep8/src/trainer/AdamTrainer.cpp:9-31) runs inside the sum on the shard this rank owns, with this rank's m and v for
+        that shard (`adam_m`, `adam_v`, zero at first: 1 / world of the optimiser's state per GPU), and the all-gather
+        carries the updated `weights`.  Same rules as sgd.
         sgd = (learning_rate, weight_decay): the reference's SGD step (SGDTrainer::update) runs inside the sum on the shard
         this rank owns, and the all-gather carries the updated `weights`; `result` then holds only this rank's shard of
         the summed gradient.  Every rank must pass the same values; `weights` must hold the same data on every rank.
@@ -225,15 +230,30 @@ class PeerAllReduce:
         contraction of the backward pass that reads the operand (the reference runs the whole backward pass before
         SGDTrainer::update, deep8/src/trainer/Trainer.cpp:12-32), and finish() before the next forward pass."""
         coeff = None
-        if sgd is not None:
+        if sgd is not None and adam is not None:
+            raise ValueError("one trainer step per exchange: sgd or adam")
+        if sgd is not None or adam is not None:
             if self.weights is None:
                 raise ValueError("PeerAllReduce was built without weights")
+        if sgd is not None:
             coeff = sgd_coefficients(*sgd)
+        lo, hi = self.shards[self.rank]
+        if adam is not None and self.adam_m is None:
+            import torch
+            n_own = max(hi - lo, 1)
+            self.adam_m = torch.zeros(n_own, dtype=self.dtype, device=self.device)
+            self.adam_v = torch.zeros(n_own, dtype=self.dtype, device=self.device)
+
+        def adam_args(weights_addr):
+            return (weights_addr, self.adam_m.data_ptr(), self.adam_v.data_ptr()) + tuple(adam)
+
         if self.world == 1:
             self.scattered = False
             if coeff is not None:
                 self.ctx_main.sum_shards(self.dtype, None, [self.base + self.off_partial], self.numel,
                                          sgd=(self.base + self.off_weights, coeff[0], coeff[1]))
+            elif adam is not None:
+                self.ctx_main.sum_shards(self.dtype, None, [self.base + self.off_partial], self.numel, adam=adam_args(self.base + self.off_weights))
             return
         c, r = self.ctx_side, self.rank
         self.step += 1
@@ -247,13 +267,15 @@ class PeerAllReduce:
         scattered, self.scattered = getattr(self, "scattered", False), False
         mine = self.base + self.off_result + lo * self.esize
         step = None if coeff is None else (self.base + self.off_weights + lo * self.esize, coeff[0], coeff[1])
-        off = (self.off_weights if step is not None else self.off_result) + lo * self.esize  # what the all-gather carries
+        astep = None if adam is None else adam_args(self.base + self.off_weights + lo * self.esize)
+        trained = step is not None or astep is not None
+        off = (self.off_weights if trained else self.off_result) + lo * self.esize  # what the all-gather carries
         copies = [self.peers[q] + off for q in self.order] if self.gather == "kernel" else None
         if scattered:
             # every rank's epilogue has already put its block of partial sums into my staging slots
             if n > 0:
                 c.sum_shards(self.dtype, mine, [self.base + self.off_stage + q * self.stage_bytes for q in range(self.world)], n, sgd=step,
-                             copies=copies)
+                             copies=copies, adam=astep)
             c.peer_signal([self._flag(q, 1, r) for q in self.order], s)                   # my staging slots may be rewritten
         else:
             if n > 0:
@@ -264,7 +286,7 @@ class PeerAllReduce:
             if n > 0:
                 srcs = [self.base + self.off_partial + lo * self.esize if q == r else self.base + self.off_stage + q * self.stage_bytes
                         for q in range(self.world)]
-                c.sum_shards(self.dtype, mine, srcs, n, sgd=step, copies=copies)
+                c.sum_shards(self.dtype, mine, srcs, n, sgd=step, copies=copies, adam=astep)
         if n > 0 and copies is None:
             for q in self.order:                                                           # all-gather: push the finished shard
                 c.peer_copy(self.peers[q] + off, self.base + off, n * self.esize)

@@ -6,7 +6,7 @@
 //   Device, GPUDevice, GPUMemoryPool deep8/include/model/Device.h, GPUDevice.h, GPUMemoryPool.h
 //   TensorStorage, Tensor           deep8/include/model/TensorStorage.h, Tensor.h
 //   Node, Variable, Function        deep8/include/nodes/Node.h, Variable.h, Function.h
-//   MatrixMultiply, Conv2d, DeConv2d, ReLu   deep8/include/nodes/*.h
+//   MatrixMultiply, Conv2d, DeConv2d, ReLu, Add, Linear   deep8/include/nodes/*.h
 //   Executor, EagerExecutor         deep8/include/model/Executor.h, EagerExecutor.h
 //   Math::*                          deep8/include/math/{MatrixMultiply,Conv2d,DeConv2d,ReLu}.h
 //   parameter(), operator*, conv2d(), deConv2d(), relu(), backward()   deep8/include/model/Net.h
@@ -292,6 +292,36 @@ DEEP8_API void DeConv2dGradYGPU(const Tensor& x, const Tensor& y, Tensor& dy, co
 
 DEEP8_API void ReLu(const Tensor& x, Tensor& y);
 DEEP8_API void ReLuGrad(const Tensor& x, Tensor& dx, const Tensor& y, const Tensor& dy);
+// deep8/include/math/Linear.h: y = x * a + b;  dx += dy * a
+DEEP8_API void Linear(const Tensor& x, const float a, const float b, Tensor& y);
+DEEP8_API void LinearGrad(const Tensor& x, Tensor& dx, const float a, const float b, const Tensor& y, const Tensor& dy);
+// deep8/include/math/AdamUpdate.h: value, gradient, m and v are all updated in place
+DEEP8_API void AdamUpdate(Tensor& value, Tensor& gradient, Tensor& m, Tensor& v, float beta1, float beta2, float epsilon, float learningRate,
+                          float weightDecay, int64_t steps);
+
+// ---- additions (no counterpart in the reference's Math namespace)
+// While a guard constructed with `on == true` is alive on this thread, the GradX / GradY functions of MatrixMultiply,
+// Conv2d, DeConv2d and Add OVERWRITE their gradient argument instead of adding to it: the executor uses it for the first
+// contribution to a gradient tensor, which then needs no zero fill (deep8/src/model/EagerExecutor.cpp:51-65 zero-fills
+// every gradient before the backward walk).  Other gradient functions ignore it.
+class DEEP8_API OverwriteGradient {
+public:
+    explicit OverwriteGradient(bool on);
+    ~OverwriteGradient();
+    OverwriteGradient(const OverwriteGradient&) = delete;
+    OverwriteGradient& operator=(const OverwriteGradient&) = delete;
+    static bool active();
+
+private:
+    bool previous;
+};
+// One-launch forms of a MatrixMultiply followed by an element-wise node; each stores exactly what the two separate calls store.
+DEEP8_API void MatrixMultiplyReLu(const Tensor& x, const Tensor& y, Tensor& z, Tensor& a);                              // a = ReLu(z)
+DEEP8_API void MatrixMultiplyLinear(const Tensor& x, const Tensor& y, Tensor& z, float a, float b, Tensor& l);          // l = Linear(z)
+DEEP8_API void MatrixMultiplyAddBias(const Tensor& x, const Tensor& y, const Tensor& bias, Tensor& z);                  // z = x * y + bias
+// MatrixMultiplyGradX for x = ReLu(h) followed by ReLuGrad: dx (+)= dz * y^T, then dh (+)= (h > 0 ? dx : 0)
+DEEP8_API void MatrixMultiplyGradXReLuGrad(const Tensor& x, Tensor& dx, const Tensor& y, const Tensor& z, const Tensor& dz, const Tensor& h,
+                                           Tensor& dh, bool accumulateDx, bool accumulateDh);
 DEEP8_API void Constant(Tensor& x, float scalar);  // only 0 is supported: what zeroGradient needs
 
 // Math::Add (deep8/src/math/Add.cpp:7-110) for the two cases of the path: equal shapes, and y a bias of shape (1, {cols})
@@ -347,6 +377,11 @@ public:
     Tensor value;
     Tensor gradient;
     bool updateGradient;
+    // Executor bookkeeping (additions).  gradientTouched: a contribution has been written to `gradient` in the running
+    // backward pass, so the next one adds.  valueStale: `value` has not been computed because its producing MatrixMultiply
+    // ran fused with the Add that consumes it; it is computed when somebody asks for it (fetch, a second consumer).
+    bool gradientTouched = true;
+    bool valueStale = false;
 
     Variable(int64_t id, std::string name, Executor* exe, Tensor& v);
     Variable(int64_t id, std::string name, Executor* exe, Tensor& v, Tensor& g);
@@ -373,16 +408,21 @@ public:
     Variable& deConv2d(Variable& filter, bool covered = false, int strideY = 1, int strideX = 1);
     Variable& relu();
     Variable& add(Variable& y);
+    Variable& linear(float a = 1, float b = 0);
 };
 
-enum class FunctionType { Unkown = 0, Add, Conv2d, DeConv2d, MatrixMultiply, ReLu };
+enum class FunctionType { Unkown = 0, Add, Conv2d, DeConv2d, Linear, MatrixMultiply, ReLu };
 
 class DEEP8_API Function : public Node {
 protected:
     explicit Function(std::vector<Node*>& inputs);
 
 public:
+    FunctionType functionType = FunctionType::Unkown;  // addition: lets the executor recognise the chains it can run in one launch
     virtual bool isShared() { return false; }
+    // addition: true when backward(..., index, ...) honours Math::OverwriteGradient for that input, i.e. can write the first
+    // contribution to the gradient without a zero fill
+    virtual bool canOverwriteGradient(size_t /*index*/) { return false; }
     virtual Shape checkShape(std::vector<Shape>& inputShapes);
     virtual ElementType checkElementType(std::vector<ElementType>& inputTypes);
     virtual void forward(const std::vector<const Tensor*>& inputs, Tensor* output);
@@ -394,6 +434,7 @@ public:
 
 class DEEP8_API MatrixMultiply : public Function {
 public:
+    bool canOverwriteGradient(size_t) override { return true; }
     explicit MatrixMultiply(std::vector<Node*>& inputs);
     Shape checkShape(std::vector<Shape>& inputShapes) override;
     void forward(const std::vector<const Tensor*>& inputs, Tensor* output) override;
@@ -403,6 +444,7 @@ public:
 
 class DEEP8_API Conv2d : public Function {
 public:
+    bool canOverwriteGradient(size_t) override { return true; }
     bool covered;
     int strideY, strideX, dilationY, dilationX;
     explicit Conv2d(std::vector<Node*>& inputs, bool covered = false, int strideY = 1, int strideX = 1, int dilationY = 1, int dilationX = 1);
@@ -414,6 +456,7 @@ public:
 
 class DEEP8_API DeConv2d : public Function {
 public:
+    bool canOverwriteGradient(size_t) override { return true; }
     bool forwardCovered;
     int forwardStrideY, forwardStrideX;
     explicit DeConv2d(std::vector<Node*>& inputs, bool covered = false, int strideY = 1, int strideX = 1);
@@ -435,8 +478,22 @@ public:
 // deep8/include/nodes/Add.h, deep8/src/nodes/Add.cpp: z = x + y with the shapes Math::Add accepts here
 class DEEP8_API Add : public Function {
 public:
+    bool canOverwriteGradient(size_t) override { return true; }
     explicit Add(std::vector<Node*>& inputs);
     Shape checkShape(std::vector<Shape>& inputShapes) override;
+    void forward(const std::vector<const Tensor*>& inputs, Tensor* output) override;
+    void backward(const std::vector<const Tensor*>& inputs, const Tensor* output, const Tensor* outputGradient, size_t index,
+                  Tensor* iGradient) override;
+};
+
+// deep8/include/nodes/Linear.h: y = a * x + b
+class DEEP8_API Linear : public Function {
+public:
+    float a;
+    float b;
+    explicit Linear(std::vector<Node*>& inputs, float a, float b);
+    Shape checkShape(std::vector<Shape>& inputShapes) override;
+    ElementType checkElementType(std::vector<ElementType>& inputTypes) override;
     void forward(const std::vector<const Tensor*>& inputs, Tensor* output) override;
     void backward(const std::vector<const Tensor*>& inputs, const Tensor* output, const Tensor* outputGradient, size_t index,
                   Tensor* iGradient) override;
@@ -473,6 +530,9 @@ public:
     virtual Variable* addFunction(Function* func) = 0;
     virtual void forward(Node* last) = 0;
     virtual void backward(Node* last, bool clearInterim = true) = 0;
+    // additions: run whatever an eager executor has put off (see EagerExecutor), and make a stale value real
+    virtual void flush() {}
+    virtual void materialise(Variable*) {}
 };
 
 class DEEP8_API EagerExecutor : public Executor {
@@ -485,6 +545,26 @@ public:
     void backward(Node* last, bool clearInterim = true) override;
     // addition: start from `last` with an upstream gradient given on the host (the benchmark configurations supply one)
     void backward(Variable* last, const void* hostGradient, bool clearInterim = true);
+
+    // ---- additions: fewer launches and less memory traffic for the same tensors, on by default
+    // Fusion: a MatrixMultiply is not launched at once but held until the next node is added.  If that node is a ReLu or a
+    // Linear of the product, or an Add of the product and a bias, both run as ONE launch (the element-wise node inside the
+    // contraction's epilogue); anything else - another node, feed, fetch, backward - launches the held product first.  In the
+    // backward walk the gradient of x of z = ReLu(h) * w runs with ReLu's gradient in its epilogue when ReLu's output feeds
+    // only that product.  Every tensor a caller can observe holds the bits the node-by-node sequence produces.
+    // First touch: the backward walk zero-fills no gradient; the first contribution to each gradient tensor overwrites it
+    // (Function::canOverwriteGradient) and later ones add, as the reference's zero fill + "+=" would.
+    void setFusion(bool on);
+    void setFirstTouch(bool on);
+    bool fusion() const { return fuse; }
+    bool firstTouch() const { return touch; }
+    void flush() override;
+    void materialise(Variable* v) override;
+
+private:
+    bool fuse = true, touch = true;
+    Function* pending = nullptr;  // a MatrixMultiply whose launch is held
+    void backwardNode(Node* n, std::unordered_set<Node*>& done);
 };
 
 // ------------------------------------------------------------------------------------------------ Net.h sugar for the path
@@ -497,11 +577,12 @@ DEEP8_API Variable& matrixMultiply(Variable& x, Variable& y);
 DEEP8_API Variable& conv2d(Variable& x, Variable& filter, bool covered = true, int strideY = 1, int strideX = 1, int dilationY = 1, int dilationX = 1);
 DEEP8_API Variable& deConv2d(Variable& x, Variable& filter, bool covered = false, int strideY = 1, int strideX = 1);
 DEEP8_API Variable& relu(Variable& x);
+DEEP8_API Variable& linear(Variable& x, float a = 1, float b = 0);
 DEEP8_API Variable& operator+(Variable& x, Variable& y);
 DEEP8_API Variable& add(Variable& x, Variable& y);
 
-// ------------------------------------------------------------------------------------------------ trainer (SGD)
-// deep8/include/trainer/{LearningRateIterator,ConstantLearningRateIterator,Trainer,SGDTrainer}.h
+// ------------------------------------------------------------------------------------------------ trainers (SGD, Adam)
+// deep8/include/trainer/{LearningRateIterator,ConstantLearningRateIterator,Trainer,SGDTrainer,AdamTrainer}.h
 class DEEP8_API LearningRateIterator {
 public:
     virtual ~LearningRateIterator() = default;
@@ -529,6 +610,18 @@ public:
 class DEEP8_API SGDTrainer : public Trainer {
 public:
     explicit SGDTrainer(LearningRateIterator* lr, float decay = 0);
+    void update(Executor* executor, Variable* parameter, float learningRate, float weightDecay, int64_t steps) override;
+};
+
+// deep8/include/trainer/AdamTrainer.h
+class DEEP8_API AdamTrainer : public Trainer {
+public:
+    float beta1;
+    float beta2;
+    float epsilon;
+    std::unordered_map<Variable*, Variable*> m;
+    std::unordered_map<Variable*, Variable*> v;
+    explicit AdamTrainer(LearningRateIterator* lr, float beta1 = 0.9, float beta2 = 0.999, float epsilon = 1e-7, float decay = 0);
     void update(Executor* executor, Variable* parameter, float learningRate, float weightDecay, int64_t steps) override;
 };
 

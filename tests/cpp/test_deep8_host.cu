@@ -30,6 +30,10 @@ void d8o_deconv2d_grad_y_f32(const float* x, int b, int ih, int iw, int ic, floa
 void d8o_add_bias_f32(const float* x, const float* bias, float* z, size_t rows, size_t cols);
 void d8o_add_bias_grad_f32(float* dbias, const float* dz, size_t rows, size_t cols);
 void d8o_axpby_f32(const float* x, float alpha, const float* y, float beta, float* z, size_t n);
+void d8o_linear_f32(const float* x, float a, float b, float* y, size_t n);
+void d8o_linear_grad_f32(float* dx, float a, const float* dy, size_t n);
+void d8o_adam_update_f32(float* value, float* gradient, float* m, float* v, float beta1, float beta2, float epsilon, float weight_decay,
+                         float ratio, size_t n);
 }
 
 using namespace Deep8;
@@ -135,6 +139,138 @@ static void mlpGraph() {
 
 template <typename E>
 static bool throws(const std::function<void()>& f);
+
+// ---- the same MLP step with the executor's fusion and first-touch gradients on and off: every fetched tensor identical, and
+// the fused step launches exactly its six contractions
+struct MlpRun {
+    std::vector<float> h, a, y, dx, dw1, dw2;
+    unsigned long long forwardLaunches, backwardLaunches;
+};
+static MlpRun runMlp(bool fusion, bool firstTouch, const std::vector<float>& hx, const std::vector<float>& hw1, const std::vector<float>& hw2,
+                     const std::vector<float>& hdy, size_t rows, size_t din, size_t dhid) {
+    EagerExecutor executor(DeviceType::GPU);
+    executor.setFusion(fusion);
+    executor.setFirstTouch(firstTouch);
+    Variable& x = parameter(&executor, {rows, din});
+    Variable& w1 = parameter(&executor, {din, dhid});
+    Variable& w2 = parameter(&executor, {dhid, din});
+    x.feed(hx.data());
+    w1.feed(hw1.data());
+    w2.feed(hw2.data());
+    MlpRun r;
+    unsigned long long l0 = d8k_launch_count();
+    Variable& h = x * w1;
+    Variable& a = relu(h);
+    Variable& yv = matrixMultiply(a, w2);
+    executor.flush();
+    r.forwardLaunches = d8k_launch_count() - l0;
+    l0 = d8k_launch_count();
+    executor.backward(&yv, hdy.data(), false);
+    r.backwardLaunches = d8k_launch_count() - l0;
+    r.h.resize(rows * dhid); r.a.resize(rows * dhid); r.y.resize(rows * din);
+    r.dx.resize(rows * din); r.dw1.resize(din * dhid); r.dw2.resize(dhid * din);
+    h.fetch(r.h.data());
+    a.fetch(r.a.data());
+    yv.fetch(r.y.data());
+    x.fetchGradient(r.dx.data());
+    w1.fetchGradient(r.dw1.data());
+    w2.fetchGradient(r.dw2.data());
+    executor.clearInterimNodes();
+    return r;
+}
+static void fusedExecutorEqualsNodeByNode() {
+    const size_t rows = 200, din = 72, dhid = 136;
+    std::vector<float> hx(rows * din), hw1(din * dhid), hw2(dhid * din), hdy(rows * din);
+    for (auto& v : hx) v = (std::rand() % 2001 - 1000) / 1000.f;     // real-valued data: the roundings must agree too
+    for (auto& v : hw1) v = (std::rand() % 2001 - 1000) / 4000.f;
+    for (auto& v : hw2) v = (std::rand() % 2001 - 1000) / 4000.f;
+    for (auto& v : hdy) v = (std::rand() % 2001 - 1000) / 1000.f;
+    MlpRun plain = runMlp(false, false, hx, hw1, hw2, hdy, rows, din, dhid);
+    MlpRun fused = runMlp(true, true, hx, hw1, hw2, hdy, rows, din, dhid);
+    EXPECT(same(plain.h, fused.h));
+    EXPECT(same(plain.a, fused.a));
+    EXPECT(same(plain.y, fused.y));
+    EXPECT(same(plain.dx, fused.dx));
+    EXPECT(same(plain.dw1, fused.dw1));
+    EXPECT(same(plain.dw2, fused.dw2));
+    EXPECT(plain.forwardLaunches == 3);                 // product, ReLu, product
+    EXPECT(fused.forwardLaunches == 2);                 // product with ReLu inside, product
+    EXPECT(fused.backwardLaunches == 4);                // dA (+ ReLu gradient), dW2, dX, dW1: no zero fill, no ReLuGrad launch
+    EXPECT(plain.backwardLaunches == 5);                // + ReLuGrad (the zero fills are memsets, not kernels)
+    MlpRun touchOnly = runMlp(false, true, hx, hw1, hw2, hdy, rows, din, dhid);
+    EXPECT(same(plain.dx, touchOnly.dx) && same(plain.dw1, touchOnly.dw1) && same(plain.dw2, touchOnly.dw2));
+}
+
+// ---- Linear node after a product (one launch), its gradient, and AdamTrainer on the weights: equal to the oracle
+static void linearNodeAndAdam() {
+    EagerExecutor executor(DeviceType::GPU);
+    const size_t rows = 40, din = 24, dout = 56;
+    auto hx = ints(rows * din, 5), hw = ints(din * dout, 5), hdz = ints(rows * dout, 5);
+    Variable& x = parameter(&executor, {rows, din}, false);
+    Variable& w = parameter(&executor, {din, dout});
+    x.feed(hx.data());
+    w.feed(hw.data());
+    unsigned long long l0 = d8k_launch_count();
+    Variable& p = x * w;
+    Variable& l = linear(p, 0.5f, -3.f);
+    EXPECT(d8k_launch_count() - l0 == 1);               // the product ran with Linear in its epilogue
+    std::vector<float> gp(rows * dout), gl(rows * dout), rp(rows * dout), rl(rows * dout);
+    p.fetch(gp.data());
+    l.fetch(gl.data());
+    d8o_matmul_forward_f32(hx.data(), 1, rows, din, hw.data(), 1, dout, rp.data());
+    d8o_linear_f32(rp.data(), 0.5f, -3.f, rl.data(), rl.size());
+    EXPECT(same(gp, rp));
+    EXPECT(same(gl, rl));
+    executor.backward(&l, hdz.data(), false);
+    std::vector<float> rdp(rows * dout, 0.f), rdw(din * dout, 0.f), gdw(din * dout);
+    d8o_linear_grad_f32(rdp.data(), 0.5f, hdz.data(), rdp.size());
+    d8o_matmul_grad_y_f32(hx.data(), 1, rows, din, rdw.data(), 1, dout, rdp.data());
+    w.fetchGradient(gdw.data());
+    EXPECT(same(gdw, rdw));
+    // two AdamTrainer steps on w with the same gradient
+    ConstantLearningRateIterator lr(0.0078125f);
+    AdamTrainer trainer(&lr, 0.875f, 0.9990234375f, 1.f / 1048576.f, 0.00048828125f);
+    std::vector<float> rw = hw, rg = rdw, rm(hw.size(), 0.f), rv(hw.size(), 0.f), gw(hw.size());
+    for (int step = 0; step < 2; ++step) {
+        trainer.train(&executor);
+        d8o_adam_update_f32(rw.data(), rg.data(), rm.data(), rv.data(), 0.875f, 0.9990234375f, 1.f / 1048576.f, 0.00048828125f,
+                            d8k_adam_ratio(0.0078125f, 0.875f, 0.9990234375f, step), rw.size());
+        w.fetch(gw.data());
+        EXPECT(same(gw, rw));
+    }
+    EXPECT(trainer.m.size() == 1 && trainer.v.size() == 1);
+    executor.clearInterimNodes();
+}
+
+// ---- x * w + b in one launch leaves the product unstored; asking for it, or using it again, computes it
+static void fusedBiasKeepsTheProductAvailable() {
+    EagerExecutor executor(DeviceType::GPU);
+    const size_t rows = 33, din = 20, dout = 48;
+    auto hx = ints(rows * din, 5), hw = ints(din * dout, 5), hb = ints(dout, 5);
+    Variable& x = parameter(&executor, {rows, din}, false);
+    Variable& w = parameter(&executor, {din, dout});
+    Variable& b = parameter(&executor, {dout});
+    x.feed(hx.data());
+    w.feed(hw.data());
+    b.feed(hb.data());
+    unsigned long long l0 = d8k_launch_count();
+    Variable& p = x * w;
+    Variable& z = p + b;
+    EXPECT(d8k_launch_count() - l0 == 1);
+    EXPECT(p.valueStale);
+    std::vector<float> rp(rows * dout), rz(rows * dout), gz(rows * dout), gp(rows * dout), gq(rows * dout);
+    d8o_matmul_forward_f32(hx.data(), 1, rows, din, hw.data(), 1, dout, rp.data());
+    d8o_add_bias_f32(rp.data(), hb.data(), rz.data(), rows, dout);
+    z.fetch(gz.data());
+    EXPECT(same(gz, rz));
+    Variable& q = relu(p);          // a second consumer of the product: it is computed now
+    EXPECT(!p.valueStale);
+    p.fetch(gp.data());
+    q.fetch(gq.data());
+    EXPECT(same(gp, rp));
+    for (size_t i = 0; i < gq.size(); ++i) EXPECT(gq[i] == (rp[i] > 0 ? rp[i] : 0));
+    executor.clearInterimNodes();
+}
 
 // ---- z = x * w + b through the nodes, backward, then one SGDTrainer step: every tensor equal to the oracle's
 static void linearWithBiasAndSgd() {
@@ -329,6 +465,9 @@ int main() {
         {"matmul Math:: x[3,17,5] * y[3,5,9] (per-batch branch)", [] { matmulMath(3, 17, 5, 3, 9); }},
         {"graph: parameter, feed, x*w1, relu, *w2, backward(host gradient), fetch", mlpGraph},
         {"graph: x*w + b, backward, SGDTrainer step (Add, AddGradY, AXPBY)", linearWithBiasAndSgd},
+        {"executor: fused launches + first-touch gradients equal the node-by-node walk bit for bit; launch counts", fusedExecutorEqualsNodeByNode},
+        {"graph: linear(x*w) in one launch, LinearGrad, AdamTrainer steps", linearNodeAndAdam},
+        {"graph: x*w + b in one launch, the unstored product computed on demand", fusedBiasKeepsTheProductAvailable},
         {"Conv2d node 2x32x32x64, 4x4x64->32, covered, stride 2, dilation 2 (test/Conv2dTest.h)", [] { convNode(2, 32, 32, 64, 32, 4, 4, true, 2, 2); }},
         {"Conv2d node 2x32x32x64, 5x5, covered, stride 1", [] { convNode(2, 32, 32, 64, 32, 5, 5, true, 1, 1); }},
         {"Conv2d node not covered, stride 2, dilation 2", [] { convNode(2, 32, 32, 64, 32, 4, 4, false, 2, 2); }},

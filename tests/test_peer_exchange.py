@@ -104,7 +104,8 @@ class _HostContext:
         import ctypes
         return np.ctypeslib.as_array((ctypes.c_uint16 * count).from_address(addr)).view(np.float16)
 
-    def sum_shards(self, dtype, out, srcs, count, sgd=None, copies=None):
+    def sum_shards(self, dtype, out, srcs, count, sgd=None, copies=None, adam=None):
+        assert adam is None, "the host stand-in covers the plain sum and the SGD step"
         acc = np.zeros(count, dtype=np.float32)
         for a in srcs:
             acc = acc + self._f16(a, count).astype(np.float32)
@@ -514,6 +515,28 @@ def _exchange_worker(rank, world, port, numel, steps, out_dir, gather="copy"):
             want = (gsum * np.float32(alpha) + want.astype(np.float32) * np.float32(beta)).astype(np.float16)
             ok = ok and np.array_equal(ar.weights.cpu().numpy(), want)
     status = (c_main.status(), c_side.status())
+    ar.close()
+    # Adam inside the sum: every rank ends with the same weights, equal to sum -> round -> AdamUpdate on one GPU
+    ar = PeerAllReduce(c_main, c_side, side, numel, torch.float16, dev, with_weights=True, gather=gather)
+    args = (0.875, 0.9990234375, 2.0 ** -20, 0.0078125, 0.00048828125)
+    with torch.cuda.stream(main):
+        ar.weights.copy_(w0)
+        w_ref, m_ref, v_ref = w0.clone(), torch.zeros_like(w0), torch.zeros_like(w0)
+        for s in range(2):
+            g = torch.Generator(device=dev).manual_seed(500 * s + rank)
+            ar.before_write()
+            ar.partial.copy_(torch.randn(numel, device=dev, generator=g).to(torch.float16))
+            ar.start(adam=args + (s,))
+            ar.finish()
+            main.synchronize()
+            parts = [torch.randn(numel, device=dev, generator=torch.Generator(device=dev).manual_seed(500 * s + q)).to(torch.float16)
+                     for q in range(world)]
+            gsum = torch.empty_like(w0)
+            c_main.sum_shards(torch.float16, gsum.data_ptr(), [p.data_ptr() for p in parts], numel)
+            c_main.adam_update(w_ref, gsum, m_ref, v_ref, *args, s)
+            main.synchronize()
+            ok = ok and torch.equal(ar.weights, w_ref)
+    status = (c_main.status() | status[0], c_side.status() | status[1])
     ar.close()
     with open(os.path.join(out_dir, "rank%d.txt" % rank), "w") as f:
         f.write("%d %d %d" % (int(ok), status[0], status[1]))
