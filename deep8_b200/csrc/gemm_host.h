@@ -31,6 +31,8 @@ struct HostOperand {
     long long batch_stride = 0;
     int batch_count = 1;
     ConvRule cr = {};
+    // halo != 0 (set by run_gemm, fp32 only): the virtual matrix is fetched as per-tile patches of halo_rows x halo_wp pixels
+    int halo = 0, halo_wp = 0, halo_rows = 0;
     // A filter [oc, FH, FW, ic] restricted to the taps (f0y + ty*j, f0x + tx*i), j < nfy, i < nfx - one residue class of a
     // strided convolution.  With rmod == 0 the operand is K-major rows of filters, columns (j, i, c); with rmod > 0 it is
     // the filter read by tap, W'[((j, i), co)][ci].  TMA only.
@@ -79,6 +81,7 @@ GemmLaunchFn lookup_f16_tma(bool a_mn, bool b_mn, int bn);
 GemmLaunchFn lookup_f16_gather(bool a_mn, bool b_mn, int bn);
 GemmLaunchFn lookup_f32_gather(bool a_mn, bool b_mn, int bn);
 GemmLaunchFn lookup_f32_tma(bool a_mn, bool b_mn, int bn, bool a_in_tmem);
+GemmLaunchFn lookup_f32_halo(bool b_mn);  // K-major virtual A through patches, 64 columns
 // paired-CTA kernel: the first argument of the launch function is the number of CTA pairs
 GemmLaunchFn lookup_f16_pair(bool a_mn, bool b_mn);
 

@@ -7,9 +7,16 @@ namespace d8k {
 template <bool A_MN, bool B_MN>
 static GemmLaunchFn pick(int bn, bool a_in_tmem) {
     if (bn != 64) return nullptr;
-    // six 32 KB stages with A's hi/lo images in tensor memory, or four 48 KB stages with everything in shared memory
-    if (a_in_tmem) return launch_cfg<GemmCfg<true, A_MN, B_MN, 64, 6, false, true>>;
+    // four 32 KB stages with A's hi/lo images in tensor memory (2 x 128 accumulator columns + 4 x 64 of A fill the 512),
+    // or four 48 KB stages with everything in shared memory
+    if (a_in_tmem) return launch_cfg<GemmCfg<true, A_MN, B_MN, 64, 4, false, true>>;
     return launch_cfg<GemmCfg<true, A_MN, B_MN, 64, 4, false>>;
+}
+
+// four 16 KB stages of B hi/lo, three 44 KB patch slots, A's hi/lo images in tensor memory
+GemmLaunchFn lookup_f32_halo(bool b_mn) {
+    if (b_mn) return launch_cfg<GemmCfg<true, false, true, 64, 4, false, true, true>>;
+    return launch_cfg<GemmCfg<true, false, false, 64, 4, false, true, true>>;
 }
 
 GemmLaunchFn lookup_f32_tma(bool a_mn, bool b_mn, int bn, bool a_in_tmem) {

@@ -102,12 +102,14 @@ enum : int {
     kTmaFilterTap = 3,  // filter [oc, taps, ic] as W'[(tap, co)][ci], MN-major: 4-D map {ce ci, oc, taps, ic / ce}
     kTmaFilterSub = 4,     // filter [oc, FH, FW, ic] restricted to a grid of taps, K-major: 4-D map {ic, taps x, taps y, oc}
     kTmaFilterTapSub = 5,  // the same subset read as W'[(tap, co)][ci], MN-major: 5-D map {ce ci, oc, taps x, taps y, ic / ce}
+    kTmaHalo = 6,          // virtual im2col matrix of a stride-1 rule through per-tile patches (GemmCfg::HALO): 4-D tiled map {c, x, y, image}
 };
 
 // Where the result goes when it is a strided part of a larger tensor (one residue class of a strided convolution).
 struct OutMap {
     int rows_on;  // row m = pixel (n, py, px) of an RH x RW sub-grid; it is stored at pixel (n, ry + sy*py, rx + sx*px) of an OH x OW image
     int RH, RW, OH, OW, sy, sx, ry, rx;
+    int valid_w;  // > 0: only px < valid_w exist; the other columns of the RW-wide raster are padding whose rows are not stored
     FastDiv f_plane, f_rw;  // RH * RW, RW
     int cols_on;  // column = (j, i, c) over a sub-grid of taps; it is stored at ((f0y + ty*j) * FW + f0x + tx*i) * C + c
     int C, NFX, FW, f0y, f0x, ty, tx;
@@ -127,6 +129,11 @@ struct GemmParams {
     // (a strip that streams through once per group), 2 evict last (the strips successive waves come back to).
     int raster_n, l2_a, l2_b;
     int epi_backoff_ns;  // paired kernel: sleep between the epilogue warps' polls for a finished accumulator (0 = poll back to back)
+    // Halo kernels (GemmCfg::HALO): the A operand is a virtual im2col matrix of a stride-1 rule, and the rows of a tile are 128
+    // consecutive pixels of one image's PADDED raster (halo_wp = RW + tap span columns per row).  One TMA box per (tile, 32-channel
+    // slice) brings the tile's source pixels - its rows plus the taps' reach, halo_wp columns wide - into shared memory once; tap
+    // (fy, fx) of the tile is then the same patch shifted by ty * halo_wp + tx rows.  k-blocks run slice-major: kk = slice * taps + tap.
+    int halo_wp, halo_taps, halo_slices, halo_bytes;
     int total_work;    // batch * tiles_m * tiles_n * splits
     int beta;          // 0: overwrite, 1: accumulate into C
     int epi, beta2;    // fused element-wise tail, see store_row_chunk: 1 ReLU, 2 ReLU gradient, 3 bias row added (E1 = bias[N]), 4 Linear
@@ -151,6 +158,16 @@ struct GemmParams {
     GatherSrc a, b;
 };
 
+// false for a row of the padded raster that stands for no output pixel (OutMap::valid_w)
+__device__ __forceinline__ bool out_row_exists(const GemmParams& p, int row) {
+    if (row >= p.M) return false;
+    if (!p.out.rows_on || p.out.valid_w <= 0) return true;
+    const OutMap& o = p.out;
+    int n = fdiv(row, o.f_plane);
+    int rem = row - n * (o.RH * o.RW);
+    int py = fdiv(rem, o.f_rw);
+    return rem - py * o.RW < o.valid_w;
+}
 // element offset of output row `row` (without the batch term)
 __device__ __forceinline__ long long out_row_offset(const GemmParams& p, int row) {
     if (!p.out.rows_on) return static_cast<long long>(row) * p.ldc;
@@ -178,7 +195,7 @@ __device__ __forceinline__ long long scatter_offset(const GemmParams& p, int row
     return p.scatter_off[k < kMaxScatter ? k : kMaxScatter - 1];
 }
 
-template <bool F32_, bool A_MN_, bool B_MN_, int BN_, int STAGES_, bool GATHER_, bool ATMEM_ = false>
+template <bool F32_, bool A_MN_, bool B_MN_, int BN_, int STAGES_, bool GATHER_, bool ATMEM_ = false, bool HALO_ = false>
 struct GemmCfg {
     static constexpr bool F32 = F32_, A_MN = A_MN_, B_MN = B_MN_, GATHER = GATHER_;
     static constexpr int BN = BN_, STAGES = STAGES_;
@@ -197,14 +214,28 @@ struct GemmCfg {
     // memory - one row per lane, BK columns each - and the MMAs take A from there.  The stage keeps raw A and B hi/lo;
     // shared memory then holds six stages instead of four and the three MMA passes read only B from it.
     static constexpr bool ATMEM = ATMEM_;
-    static constexpr int A_PARTS = ATMEM ? 1 : PARTS;
+    // HALO (with ATMEM, K-major A): A does not travel through the stages at all.  PATCH_SLOTS patch buffers of PATCH_BYTES hold
+    // the source pixels of a tile's 32-channel slices (GemmParams::halo_*); the converter warps read each tap's rows from
+    // the patch and write hi/lo to tensor memory.  A pixel is fetched once per tile and slice instead of once per tap.
+    static constexpr bool HALO = HALO_;
+    static constexpr int PATCH_SLOTS = HALO ? 3 : 0;
+    static constexpr int PATCH_BYTES = 44 * 1024;
+    static constexpr int A_PARTS = HALO ? 0 : (ATMEM ? 1 : PARTS);
     static constexpr int STAGE_BYTES = A_PARTS * A_BYTES + PARTS * B_BYTES;
-    static constexpr int A_TMEM_COL0 = 2 * BN;                  // after the two accumulator buffers
+    // STACK (fp32, 64 columns): B's hi and lo images lie one after the other in a stage, so ONE MMA of 2 BN columns multiplies
+    // A_hi by both - columns [0, BN) of the accumulator receive A_hi B_hi, columns [BN, 2 BN) receive A_hi B_lo - and a second
+    // MMA adds A_lo B_hi into the first half; the epilogue adds the halves.  Two instructions per k-step instead of three, and
+    // the wide one runs at the tensor core's full rate (measured: a 128 x 64 x 8 tf32 MMA takes 48 clocks, not 32; a
+    // 128 x 128 x 8 one takes its nominal 64).
+    static constexpr bool STACK = F32 && BN == 64;
+    static constexpr int ACC_COLS = STACK ? 2 * BN : BN;         // accumulator columns per buffer
+    static constexpr int A_TMEM_COL0 = 2 * ACC_COLS;            // after the two accumulator buffers
     static constexpr int A_TMEM_COLS = ATMEM ? 2 * BK * STAGES : 0;  // per stage BK columns of hi, BK of lo
-    static constexpr int TMEM_NEED = 2 * BN + A_TMEM_COLS;
+    static constexpr int TMEM_NEED = 2 * ACC_COLS + A_TMEM_COLS;
     static constexpr int TMEM_COLS = (TMEM_NEED <= 32) ? 32 : (TMEM_NEED <= 64) ? 64 : (TMEM_NEED <= 128) ? 128 : (TMEM_NEED <= 256) ? 256 : 512;
     static_assert(TMEM_NEED <= 512, "tensor memory");
     static_assert(!ATMEM || (F32 && !GATHER), "A in tensor memory belongs to the fp32 TMA kernels");
+    static_assert(!HALO || (ATMEM && !A_MN_), "the halo kernels read a K-major A from patches and keep it in tensor memory");
     // fp32 only: the tensor core adds into its fp32 accumulator with truncation, so a long chain drifts (about
     // 2e-5 of the result after 1300 accumulations).  Every CHUNK_KB k-blocks the accumulator buffer is handed to the
     // epilogue warps, which add it to register accumulators with round-to-nearest, and a fresh chain starts in the
@@ -223,7 +254,7 @@ struct GemmCfg {
     static constexpr bool HELPERS = GATHER || CONVERT;  // warps beyond the MMA warp exist
     static constexpr int THREADS = HELPERS ? 32 * (LOADER_WARP0 + LOADER_WARPS * LOADER_GROUPS) : 32 * 6;
     static constexpr int BAR_BYTES = 256;
-    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + BAR_BYTES + 1024;  // + slack to align the ring to 1024
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + PATCH_SLOTS * PATCH_BYTES + BAR_BYTES + 1024;  // + slack to align the ring to 1024
     static_assert(BN % 16 == 0 && BN >= 16 && BN <= 256, "UMMA N");
     static_assert(BN % CE == 0, "an MN-major B tile is whole 128-byte chunks");
     static_assert(SMEM_BYTES <= 227 * 1024, "shared memory");
@@ -275,6 +306,16 @@ __device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity, volatile
         }
     }
     return true;
+}
+
+// wait_bar that also adds the cycles spent waiting to *acc when the diagnostics buffer is on (GemmParams::prof)
+__device__ __forceinline__ bool wait_bar_timed(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code, bool timed,
+                                               long long* acc, unsigned backoff_ns = 0) {
+    if (!timed) return wait_bar(bar, parity, abort_flag, status, code, backoff_ns);
+    const long long t0 = clock64();
+    const bool ok = wait_bar(bar, parity, abort_flag, status, code, backoff_ns);
+    *acc += clock64() - t0;
+    return ok;
 }
 
 // ------------------------------------------------------------------------------------------------ gather loaders
@@ -737,7 +778,8 @@ d8k_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
 
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;  // ring of stages, 1024-byte aligned
-    const uint32_t bar_base = smem_base + STAGES * Cfg::STAGE_BYTES;
+    const uint32_t patch_base = smem_base + STAGES * Cfg::STAGE_BYTES;  // HALO: PATCH_SLOTS buffers, each 1024-byte aligned
+    const uint32_t bar_base = patch_base + Cfg::PATCH_SLOTS * Cfg::PATCH_BYTES;
     // barrier block: full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2], then the TMEM base address word
     auto full_bar = [&](int s) { return bar_base + 8u * s; };
     auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
@@ -745,7 +787,10 @@ d8k_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + 2 + a); };
     const uint32_t tmem_slot = bar_base + 8u * (2 * STAGES + 4);
     auto raw_bar = [&](int s) { return bar_base + 8u * (2 * STAGES + 5 + s); };  // CONVERT: TMA's bytes have landed
-    static_assert(8 * (3 * Cfg::STAGES + 5) <= Cfg::BAR_BYTES, "barrier block");
+    auto patch_full = [&](int i) { return bar_base + 8u * (3 * STAGES + 5 + i); };                     // HALO: the box has landed
+    auto patch_empty = [&](int i) { return bar_base + 8u * (3 * STAGES + 5 + Cfg::PATCH_SLOTS + i); };  // HALO: every converter is done with it
+    auto patch_addr = [&](int i) { return patch_base + static_cast<uint32_t>(i) * Cfg::PATCH_BYTES; };
+    static_assert(8 * (3 * Cfg::STAGES + 5 + 2 * Cfg::PATCH_SLOTS) <= Cfg::BAR_BYTES, "barrier block");
 
     __shared__ volatile int s_abort;
     __shared__ int s_last;
@@ -759,6 +804,10 @@ d8k_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             ptx::mbar_init(full_bar(s), Cfg::HELPERS ? 32 * Cfg::LOADER_WARPS : 1);
             ptx::mbar_init(empty_bar(s), 1);
             ptx::mbar_init(raw_bar(s), 1);
+        }
+        for (int i = 0; i < Cfg::PATCH_SLOTS; ++i) {
+            ptx::mbar_init(patch_full(i), 1);
+            ptx::mbar_init(patch_empty(i), 32 * Cfg::LOADER_WARPS * Cfg::LOADER_GROUPS);
         }
         for (int a = 0; a < 2; ++a) {
             ptx::mbar_init(tfull_bar(a), 1);
@@ -788,10 +837,50 @@ d8k_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         int stage = 0;
         uint32_t phase = 0;
         bool ok = true;
-        for (int w = blockIdx.x; ok && w < p.total_work; w += gridDim.x) {
+        // HALO: patch q of this CTA belongs to its (q / slices)-th work item and that item's slice q % slices; it lands in slot
+        // q % PATCH_SLOTS.  Patches are requested PATCH_SLOTS - 1 slices ahead of the k-blocks that read them.
+        int q_issued = 0, item_seq = 0;
+        const bool timed = p.prof != nullptr;
+        long long w_empty = 0, w_patch = 0;
+        const long long t_begin = timed ? clock64() : 0;
+        auto issue_patches_before = [&](int q_end) {
+            if constexpr (Cfg::HALO) {
+                while (ok && q_issued < q_end) {
+                    const int seq = q_issued / p.halo_slices, slice = q_issued - seq * p.halo_slices;
+                    const long long w2 = static_cast<long long>(blockIdx.x) + static_cast<long long>(seq) * gridDim.x;
+                    if (w2 >= p.total_work) {
+                        q_issued = q_end;  // nothing left to fetch
+                        break;
+                    }
+                    const WorkItem it2 = decode_work(p, static_cast<int>(w2), BN);
+                    const int slot = q_issued % Cfg::PATCH_SLOTS;
+                    ok = wait_bar_timed(patch_empty(slot), ((q_issued / Cfg::PATCH_SLOTS) & 1) ^ 1, &s_abort, p.status, (kRoleProducer << 8) | 4, timed,
+                                        &w_patch);
+                    if (!ok) break;
+                    if (lane == 0) {
+                        const ConvRule& r = p.a.cr;
+                        ptx::mbar_arrive_expect_tx(patch_full(slot), static_cast<uint32_t>(p.halo_bytes));
+                        // box {32 channels, halo_wp columns, rows, 1 image} whose corner is the tile's first source pixel; what
+                        // lies outside the image arrives as zeros
+                        ptx::tma_load_4d(patch_addr(slot), &tmA, patch_full(slot), slice * CE, r.low_x, it2.m0 / p.halo_wp + r.low_y,
+                                         it2.batch % p.a_batch_mod);
+                    }
+                    __syncwarp();
+                    ++q_issued;
+                }
+            }
+        };
+        for (int w = blockIdx.x; ok && w < p.total_work; w += gridDim.x, ++item_seq) {
             WorkItem it = decode_work(p, w, BN);
             for (int kk = it.kb_begin; kk < it.kb_end; ++kk) {
-                ok = wait_bar(empty_bar(stage), phase ^ 1, &s_abort, p.status, (kRoleProducer << 8) | 1);
+                int k0_halo = 0;
+                if constexpr (Cfg::HALO) {
+                    const int slice = kk / p.halo_taps, tap = kk - slice * p.halo_taps;
+                    if (tap == 0) issue_patches_before(item_seq * p.halo_slices + slice + Cfg::PATCH_SLOTS);
+                    if (!ok) break;
+                    k0_halo = tap * p.a.cr.C + slice * CE;
+                }
+                ok = wait_bar_timed(empty_bar(stage), phase ^ 1, &s_abort, p.status, (kRoleProducer << 8) | 1, timed, &w_empty);
                 if (!ok) break;
                 if (lane == 0) {
                     int b = it.batch, kb = kk;
@@ -799,21 +888,28 @@ d8k_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                         b = kk / p.num_kb;
                         kb = kk - b * p.num_kb;
                     }
-                    int k0 = kb * BK;
+                    int k0 = Cfg::HALO ? k0_halo : kb * BK;
                     // CONVERT: the boxes fill the hi halves of the stage and complete on the raw barrier
                     const uint32_t bar = Cfg::CONVERT ? raw_bar(stage) : full_bar(stage);
-                    ptx::mbar_arrive_expect_tx(bar, Cfg::CONVERT ? Cfg::A_BYTES + Cfg::B_BYTES : Cfg::STAGE_BYTES);
-                    produce_operand<Cfg, Cfg::A_MN, kBM>(p.a_tma, p.a_chunked, p.a, &tmA, stage_a(stage), bar, k0, it.m0, b % p.a_batch_mod);
+                    ptx::mbar_arrive_expect_tx(bar, Cfg::HALO ? Cfg::B_BYTES : Cfg::CONVERT ? Cfg::A_BYTES + Cfg::B_BYTES : Cfg::STAGE_BYTES);
+                    if constexpr (!Cfg::HALO)
+                        produce_operand<Cfg, Cfg::A_MN, kBM>(p.a_tma, p.a_chunked, p.a, &tmA, stage_a(stage), bar, k0, it.m0, b % p.a_batch_mod);
                     produce_operand<Cfg, Cfg::B_MN, BN>(p.b_tma, p.b_chunked, p.b, &tmB, stage_b(stage), bar, k0, it.n0, b % p.b_batch_mod);
                 }
                 __syncwarp();
                 if (++stage == STAGES) { stage = 0; phase ^= 1; }
             }
         }
+        if (timed && lane == 0) {
+            p.prof[blockIdx.x * 16 + 0] = clock64() - t_begin;
+            p.prof[blockIdx.x * 16 + 1] = w_empty;
+            p.prof[blockIdx.x * 16 + 2] = w_patch;
+        }
     } else if (warp == Cfg::MMA_WARP) {
         // ============================================================================ MMA issuer
         // A from tensor memory is always one row per lane, whatever the stored layout was
         constexpr uint32_t idesc = ptx::make_idesc(Cfg::F32 ? 2u : 0u, Cfg::A_MN && !Cfg::ATMEM, Cfg::B_MN, kBM, BN);
+        constexpr uint32_t idesc_wide = ptx::make_idesc(Cfg::F32 ? 2u : 0u, Cfg::A_MN && !Cfg::ATMEM, Cfg::B_MN, kBM, Cfg::STACK ? 2 * BN : BN);
         // descriptor step per UMMA_K: K-major advances 32 bytes inside the swizzled row; MN-major advances UMMA_K rows
         constexpr uint32_t a_step = Cfg::A_MN ? Cfg::UMMA_K * 128 : 32;
         constexpr uint32_t b_step = Cfg::B_MN ? Cfg::UMMA_K * 128 : 32;
@@ -822,58 +918,91 @@ d8k_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         constexpr uint32_t a_sbo = Cfg::A_B32 ? 512 : 1024, b_sbo = Cfg::B_B32 ? 512 : 1024;
         constexpr uint32_t a_lay = Cfg::A_B32 ? ptx::kLayoutSw128Base32 : ptx::kLayoutSw128;
         constexpr uint32_t b_lay = Cfg::B_B32 ? ptx::kLayoutSw128Base32 : ptx::kLayoutSw128;
+        // The tensor pipe holds only a couple of MMAs ahead of the one it runs (measured: issuing costs what executing
+        // costs), so whatever this warp does between two k-blocks is time the pipe idles: a 128 x 64 x 8 tf32 MMA is 48 clocks
+        // and the bookkeeping of a k-block used to cost over 600.  Everything that moves with the stage - barrier addresses,
+        // descriptors, the tensor-memory column of A - is therefore a running value stepped once per k-block, not recomputed.
+        constexpr uint64_t kStageStep = static_cast<uint64_t>(Cfg::STAGE_BYTES >> 4);  // a stage further on, in descriptor units
+        const uint64_t da_first = ptx::smem_desc(stage_a(0), a_lbo, a_sbo, a_lay), db_first = ptx::smem_desc(stage_b(0), b_lbo, b_sbo, b_lay);
+        const uint32_t ta_first = tmem_base + Cfg::A_TMEM_COL0;
         int stage = 0;
         uint32_t phase = 0;
+        uint64_t da_run = da_first, db_run = db_first;
+        uint32_t ta_run = ta_first, full_run = full_bar(0), empty_run = empty_bar(0);
         int acc = 0;
         uint32_t acc_phase = 0;
         bool ok = true;
+        const bool timed = p.prof != nullptr;
+        long long w_full = 0, w_tmem = 0;
+        const long long t_begin = timed ? clock64() : 0;
         for (int w = blockIdx.x; ok && w < p.total_work; w += gridDim.x) {
             WorkItem it = decode_work(p, w, BN);
             uint32_t d_tmem = 0;
+            int in_chain = 0;
             for (int kk = it.kb_begin; kk < it.kb_end; ++kk) {
-                const int in_chain = Cfg::CHUNK_KB > 0 ? (kk - it.kb_begin) % (Cfg::CHUNK_KB > 0 ? Cfg::CHUNK_KB : 1) : kk - it.kb_begin;
                 if (in_chain == 0) {  // a new accumulation chain needs a drained accumulator buffer
-                    ok = wait_bar(tempty_bar(acc), acc_phase ^ 1, &s_abort, p.status, (kRoleMma << 8) | 2);
+                    ok = wait_bar_timed(tempty_bar(acc), acc_phase ^ 1, &s_abort, p.status, (kRoleMma << 8) | 2, timed, &w_tmem);
                     if (!ok) break;
                     ptx::tc_fence_after_sync();
-                    d_tmem = tmem_base + acc * BN;
+                    d_tmem = tmem_base + acc * Cfg::ACC_COLS;
                 }
-                ok = wait_bar(full_bar(stage), phase, &s_abort, p.status, (kRoleMma << 8) | 1);
+                ok = wait_bar_timed(full_run, phase, &s_abort, p.status, (kRoleMma << 8) | 1, timed, &w_full);
                 if (!ok) break;
                 ptx::tc_fence_after_sync();
                 const bool chain_ends = (kk + 1 == it.kb_end) || (Cfg::CHUNK_KB > 0 && in_chain + 1 == Cfg::CHUNK_KB);
                 if (lane == 0) {
-                    const uint32_t a_hi = stage_a(stage), b_hi = stage_b(stage);
 #pragma unroll
                     for (int s = 0; s < Cfg::KSTEPS; ++s) {
-                        uint64_t da = ptx::smem_desc(a_hi + s * a_step, a_lbo, a_sbo, a_lay);
-                        uint64_t db = ptx::smem_desc(b_hi + s * b_step, b_lbo, b_sbo, b_lay);
-                        uint32_t accumulate = (in_chain > 0 || s > 0) ? 1u : 0u;
+                        // a k-step moves the start address by a few 16-byte units, far below the 14-bit field's range: a plain add
+                        const uint64_t da = da_run + ((s * a_step) >> 4), db = db_run + ((s * b_step) >> 4);
+                        const uint32_t accumulate = (in_chain > 0 || s > 0) ? 1u : 0u;
                         if constexpr (Cfg::ATMEM) {
-                            const uint32_t ta_hi = tmem_base + Cfg::A_TMEM_COL0 + stage * (2 * BK) + s * Cfg::UMMA_K;
-                            uint64_t db_lo = ptx::smem_desc(b_hi + Cfg::B_BYTES + s * b_step, b_lbo, b_sbo, b_lay);
-                            ptx::mma_tf32_a_tmem(d_tmem, ta_hi + BK, db, idesc, accumulate);  // small terms first
-                            ptx::mma_tf32_a_tmem(d_tmem, ta_hi, db_lo, idesc, 1u);
-                            ptx::mma_tf32_a_tmem(d_tmem, ta_hi, db, idesc, 1u);
+                            const uint32_t ta_hi = ta_run + s * Cfg::UMMA_K;
+                            if constexpr (Cfg::STACK) {
+                                ptx::mma_tf32_a_tmem(d_tmem, ta_hi, db, idesc_wide, accumulate);  // A_hi [B_hi ; B_lo]
+                                ptx::mma_tf32_a_tmem(d_tmem, ta_hi + BK, db, idesc, 1u);          // A_lo B_hi
+                            } else {
+                                ptx::mma_tf32_a_tmem(d_tmem, ta_hi + BK, db, idesc, accumulate);  // small terms first
+                                ptx::mma_tf32_a_tmem(d_tmem, ta_hi, db + (Cfg::B_BYTES >> 4), idesc, 1u);
+                                ptx::mma_tf32_a_tmem(d_tmem, ta_hi, db, idesc, 1u);
+                            }
                         } else if constexpr (Cfg::F32) {
-                            uint64_t da_lo = ptx::smem_desc(a_hi + Cfg::A_BYTES + s * a_step, a_lbo, a_sbo, a_lay);
-                            uint64_t db_lo = ptx::smem_desc(b_hi + Cfg::B_BYTES + s * b_step, b_lbo, b_sbo, b_lay);
-                            ptx::mma_tf32(d_tmem, da_lo, db, idesc, accumulate);  // small terms first
-                            ptx::mma_tf32(d_tmem, da, db_lo, idesc, 1u);
-                            ptx::mma_tf32(d_tmem, da, db, idesc, 1u);
+                            const uint64_t da_lo = da + (Cfg::A_BYTES >> 4), db_lo = db + (Cfg::B_BYTES >> 4);
+                            if constexpr (Cfg::STACK) {
+                                ptx::mma_tf32(d_tmem, da, db, idesc_wide, accumulate);  // A_hi [B_hi ; B_lo]
+                                ptx::mma_tf32(d_tmem, da_lo, db, idesc, 1u);           // A_lo B_hi
+                            } else {
+                                ptx::mma_tf32(d_tmem, da_lo, db, idesc, accumulate);  // small terms first
+                                ptx::mma_tf32(d_tmem, da, db_lo, idesc, 1u);
+                                ptx::mma_tf32(d_tmem, da, db, idesc, 1u);
+                            }
                         } else {
                             ptx::mma_f16(d_tmem, da, db, idesc, accumulate);
                         }
                     }
-                    ptx::tc_commit(empty_bar(stage));  // the stage may be refilled once these MMAs have read it
+                    ptx::tc_commit(empty_run);  // the stage may be refilled once these MMAs have read it
                     if (chain_ends) ptx::tc_commit(tfull_bar(acc));
                 }
                 __syncwarp();
-                if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                if (++stage == STAGES) {
+                    stage = 0;
+                    phase ^= 1;
+                    da_run = da_first; db_run = db_first; ta_run = ta_first; full_run = full_bar(0); empty_run = empty_bar(0);
+                } else {
+                    da_run += kStageStep; db_run += kStageStep; ta_run += 2 * BK; full_run += 8; empty_run += 8;
+                }
                 if (chain_ends) {
+                    in_chain = 0;
                     if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+                } else {
+                    ++in_chain;
                 }
             }
+        }
+        if (timed && lane == 0) {
+            p.prof[blockIdx.x * 16 + 3] = clock64() - t_begin;
+            p.prof[blockIdx.x * 16 + 4] = w_full;
+            p.prof[blockIdx.x * 16 + 5] = w_tmem;
         }
     } else if (warp < Cfg::EPI_WARPS) {
         // ============================================================================ epilogue (TMEM -> C)
@@ -882,16 +1011,21 @@ d8k_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         int acc = 0;
         uint32_t acc_phase = 0;
         bool ok = true;
+        const bool timed = p.prof != nullptr;
+        long long w_tfull = 0;
+        const long long t_begin = timed ? clock64() : 0;
         for (int w = blockIdx.x; ok && w < p.total_work; w += gridDim.x) {
             WorkItem it = decode_work(p, w, BN);
             const int row = it.m0 + row_in_tile;
+            const bool row_ok = out_row_exists(p, row);
             const long long crow = static_cast<long long>(it.batch) * p.c_batch_stride + out_row_offset(p, row) + scatter_offset(p, row);
             float* part = p.ws + (static_cast<size_t>(w) * kBM + row_in_tile) * BN;
             if constexpr (Cfg::CHUNK_KB == 0) {
-                ok = wait_bar(tfull_bar(acc), acc_phase, &s_abort, p.status, (kRoleEpilogue << 8) | 3);
+                ok = wait_bar_timed(tfull_bar(acc), acc_phase, &s_abort, p.status, (kRoleEpilogue << 8) | 3, timed, &w_tfull,
+                                    static_cast<unsigned>(p.epi_backoff_ns));
                 if (!ok) break;
                 ptx::tc_fence_after_sync();
-                const uint32_t taddr = tmem_base + acc * BN + (static_cast<uint32_t>(quarter * 32) << 16);
+                const uint32_t taddr = tmem_base + acc * Cfg::ACC_COLS + (static_cast<uint32_t>(quarter * 32) << 16);
 #pragma unroll 1
                 for (int c = 0; c < BN / 32; ++c) {
                     uint32_t r[32];
@@ -899,7 +1033,7 @@ d8k_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                     ptx::tmem_ld_32x32(taddr + c * 32, r);
                     ptx::tmem_ld_wait();
                     if (p.splits == 1) {
-                        if (row < p.M && it.n0 + c * 32 < p.N) {
+                        if (row_ok && it.n0 + c * 32 < p.N) {
                             float accv[32];
 #pragma unroll
                             for (int i = 0; i < 32; ++i) accv[i] = __uint_as_float(r[i]);
@@ -921,18 +1055,19 @@ d8k_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                 for (int i = 0; i < BN; ++i) accv[i] = 0.f;
                 const int chains = (it.kb_end - it.kb_begin + Cfg::CHUNK_KB - 1) / Cfg::CHUNK_KB;
                 for (int ch = 0; ch < chains; ++ch) {
-                    ok = wait_bar(tfull_bar(acc), acc_phase, &s_abort, p.status, (kRoleEpilogue << 8) | 3);
+                    ok = wait_bar_timed(tfull_bar(acc), acc_phase, &s_abort, p.status, (kRoleEpilogue << 8) | 3, timed, &w_tfull,
+                                        static_cast<unsigned>(p.epi_backoff_ns));
                     if (!ok) break;
                     ptx::tc_fence_after_sync();
-                    const uint32_t taddr = tmem_base + acc * BN + (static_cast<uint32_t>(quarter * 32) << 16);
+                    const uint32_t taddr = tmem_base + acc * Cfg::ACC_COLS + (static_cast<uint32_t>(quarter * 32) << 16);
 #pragma unroll
-                    for (int c = 0; c < BN / 32; ++c) {
+                    for (int c = 0; c < Cfg::ACC_COLS / 32; ++c) {  // STACK: the second half of the columns holds the A_hi B_lo terms
                         uint32_t r[32];
                         __syncwarp();
                         ptx::tmem_ld_32x32(taddr + c * 32, r);
                         ptx::tmem_ld_wait();
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) accv[c * 32 + i] += __uint_as_float(r[i]);
+                        for (int i = 0; i < 32; ++i) accv[(c % (BN / 32)) * 32 + i] += __uint_as_float(r[i]);
                     }
                     ptx::tc_fence_before_sync();
                     ptx::mbar_arrive(tempty_bar(acc));
@@ -942,7 +1077,7 @@ d8k_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
 #pragma unroll
                 for (int c = 0; c < BN / 32; ++c) {
                     if (p.splits == 1) {
-                        if (row < p.M && it.n0 + c * 32 < p.N) store_row_chunk<OutT>(p, crow, it.n0 + c * 32, &accv[c * 32]);
+                        if (row_ok && it.n0 + c * 32 < p.N) store_row_chunk<OutT>(p, crow, it.n0 + c * 32, &accv[c * 32]);
                     } else {
 #pragma unroll
                         for (int v = 0; v < 8; ++v)
@@ -963,7 +1098,7 @@ d8k_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                 asm volatile("bar.sync 1, 128;" ::: "memory");
                 if (s_last) {
                     __threadfence();
-                    if (row < p.M) {
+                    if (row_ok) {
                         const float* first = p.ws + (static_cast<size_t>(it.tile) * p.splits * kBM + row_in_tile) * BN;
 #pragma unroll 1
                         for (int c = 0; c < BN / 32; ++c) {
@@ -987,6 +1122,10 @@ d8k_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         }
         // scattered rows may sit in a peer GPU's memory: order this thread's stores before whatever the host enqueues next
         if (p.scatter_rows) __threadfence_system();
+        if (timed && threadIdx.x == 0) {
+            p.prof[blockIdx.x * 16 + 6] = clock64() - t_begin;
+            p.prof[blockIdx.x * 16 + 7] = w_tfull;
+        }
     } else if (Cfg::CONVERT && warp >= Cfg::LOADER_WARP0) {
         // ============================================================================ converters (fp32 behind TMA)
         // The stage's hi halves hold the operands as TMA wrote them, already in the swizzled layout; the lo image has
@@ -996,25 +1135,54 @@ d8k_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         constexpr int A_CHUNKS = Cfg::A_BYTES / 16 / 128, B_CHUNKS = Cfg::B_BYTES / 16 / 128;
         int t = 0;
         bool ok = true;
-        for (int w = blockIdx.x; ok && w < p.total_work; w += gridDim.x) {
+        int item_seq = 0;
+        const bool timed = p.prof != nullptr;
+        long long w_raw = 0, w_pfull = 0;
+        const long long t_begin = timed ? clock64() : 0;
+        for (int w = blockIdx.x; ok && w < p.total_work; w += gridDim.x, ++item_seq) {
             WorkItem it = decode_work(p, w, BN);
+            const int tile_col0 = Cfg::HALO ? it.m0 % p.halo_wp : 0;  // HALO: raster position of the tile's first pixel inside its first patch row
             for (int kk = it.kb_begin; kk < it.kb_end; ++kk, ++t) {
-                if (t % Cfg::LOADER_GROUPS != group) continue;
+                // HALO: which patch this k-block reads, and where its tap starts inside it
+                int pslot = 0, prow0 = 0;
+                bool last_tap = false;
+                if constexpr (Cfg::HALO) {
+                    const int slice = kk / p.halo_taps, tap = kk - slice * p.halo_taps;
+                    const int pq = item_seq * p.halo_slices + slice;
+                    pslot = pq % Cfg::PATCH_SLOTS;
+                    last_tap = tap + 1 == p.halo_taps;
+                    if (t % Cfg::LOADER_GROUPS != group) {
+                        // not this group's k-block; its earlier reads of the patch are over, so the slot is done with on the last tap
+                        if (last_tap) ptx::mbar_arrive(patch_empty(pslot));
+                        continue;
+                    }
+                    ok = wait_bar_timed(patch_full(pslot), (pq / Cfg::PATCH_SLOTS) & 1, &s_abort, p.status, (kRoleLoader << 8) | 4, timed, &w_pfull);
+                    if (!ok) break;
+                    const ConvRule& r = p.a.cr;
+                    const int fy = fdiv(tap, r.f_fw), fx = tap - fy * r.FW;
+                    prow0 = tile_col0 + tap_offset(fy, r.FH, r.e_y) * p.halo_wp + tap_offset(fx, r.FW, r.e_x);
+                } else {
+                    if (t % Cfg::LOADER_GROUPS != group) continue;
+                }
                 const int stage = t % STAGES;
                 const uint32_t phase = (t / STAGES) & 1;
-                ok = wait_bar(raw_bar(stage), phase, &s_abort, p.status, (kRoleLoader << 8) | 2);  // every reader observes the phase itself
+                ok = wait_bar_timed(raw_bar(stage), phase, &s_abort, p.status, (kRoleLoader << 8) | 2, timed, &w_raw);  // every reader observes the phase itself
                 if (!ok) break;
                 if constexpr (Cfg::ATMEM) {
                     // A: this thread owns tile row 32 (warp % 4) + lane, the tensor-memory lane its warp may write
                     const int q = warp & 3;
                     uint32_t hi[32], lo[32];
                     if constexpr (!Cfg::A_MN) {
-                        const int row = q * 32 + lane;
-                        const uint32_t base = stage_a(stage) + 128u * row;
+                        // HALO: the row sits in the patch at its pixel's raster position shifted by the tap; else in the stage
+                        const int row = Cfg::HALO ? prow0 + q * 32 + lane : q * 32 + lane;
+                        const uint32_t base = (Cfg::HALO ? patch_addr(pslot) : stage_a(stage)) + 128u * row;
 #pragma unroll
                         for (int c = 0; c < 8; ++c) {  // the row's eight 16-byte chunks, un-swizzled on the way
                             uint4 v = ptx::ld_shared_v4(base + ((c ^ (row & 7)) << 4));
                             hi[4 * c] = v.x; hi[4 * c + 1] = v.y; hi[4 * c + 2] = v.z; hi[4 * c + 3] = v.w;
+                        }
+                        if constexpr (Cfg::HALO) {
+                            if (last_tap) ptx::mbar_arrive(patch_empty(pslot));  // the values are in registers: the slot may be refilled
                         }
                     } else {
                         // MN-major: chunk q holds BK k-rows of 32 m's; this thread's m is `lane`, one word per k-row
@@ -1054,6 +1222,11 @@ d8k_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                 ptx::fence_proxy_async_smem();
                 ptx::mbar_arrive(full_bar(stage));
             }
+        }
+        if (timed && tid == 0) {
+            p.prof[blockIdx.x * 16 + 8 + 3 * group] = clock64() - t_begin;
+            p.prof[blockIdx.x * 16 + 9 + 3 * group] = w_raw;
+            p.prof[blockIdx.x * 16 + 10 + 3 * group] = w_pfull;
         }
     } else if (Cfg::GATHER && warp >= Cfg::LOADER_WARP0) {
         // ============================================================================ gather loaders

@@ -103,6 +103,7 @@ bool make_pair_map(CUtensorMap* map, const HostOperand& o, long long extent, lon
 int tma_mode(const HostOperand& o, int esize, long long extent, long long K) {
     const long long ce = 128 / esize;  // elements per 128-byte row; also the k-block
     if (reinterpret_cast<uintptr_t>(o.ptr) & 15) return -1;
+    if (o.halo) return encode_tiled() != nullptr ? kTmaHalo : -1;
     if (o.sub.on) {  // a grid of taps of a filter [oc, FH, FW, ic]
         if (o.is_virtual || o.batch_count > 1 || o.sub.ic % ce != 0 || encode_tiled() == nullptr) return -1;
         if (o.rmod == 0) return o.mn ? -1 : kTmaFilterSub;
@@ -193,6 +194,65 @@ bool make_filter_sub_map(CUtensorMap* map, const HostOperand& o, int rows_tile, 
                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     }
     return rc == CUDA_SUCCESS;
+}
+
+// Patch map of a halo operand: the NHWC image as {C, W, H, images}, box {32 channels, halo_wp columns, halo_rows rows, 1}.
+bool make_halo_map(CUtensorMap* map, const HostOperand& o, long long images, int esize) {
+    EncodeTiledFn enc = encode_tiled();
+    if (!enc) return false;
+    const ConvRule& r = o.cr;
+    cuuint64_t dims[4] = {static_cast<cuuint64_t>(r.C), static_cast<cuuint64_t>(r.SW), static_cast<cuuint64_t>(r.SH), static_cast<cuuint64_t>(images)};
+    cuuint64_t strides[3] = {static_cast<cuuint64_t>(r.C) * esize, static_cast<cuuint64_t>(r.SW) * r.C * esize,
+                             static_cast<cuuint64_t>(r.SH) * r.SW * r.C * esize};
+    cuuint32_t box[4] = {static_cast<cuuint32_t>(128 / esize), static_cast<cuuint32_t>(o.halo_wp), static_cast<cuuint32_t>(o.halo_rows), 1u};
+    cuuint32_t estr[4] = {1u, 1u, 1u, 1u};
+    CUresult rc = enc(map, esize == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, const_cast<void*>(o.ptr), dims, strides,
+                      box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return rc == CUDA_SUCCESS;
+}
+
+// The halo form of a convolution-like contraction whose A operand is a virtual im2col matrix with unit stride between
+// neighbouring rows (Conv2d forward and gradient of x at stride 1, the residue classes of a strided DeConv2d, ...), or false
+// when it does not apply.  The rows of one image become its PADDED raster - halo_wp = RW + (tap span in x) columns per output
+// row, so that a tap is a constant row shift - and the images become the batch; rows that stand for padding columns are
+// computed and not stored (OutMap::valid_w).  fp32 only: the converter warps rebuild each tap's A rows from the patch.
+constexpr int kHaloPatchBytes = 44 * 1024;  // GemmCfg::PATCH_BYTES
+bool to_halo(const GemmProblem& g, GemmProblem* out) {
+    if (g.a.halo || g.dtype != 1 || !g.a.is_virtual || g.a.mn || g.batch != 1 || g.kbatch != 1 || g.scatter_rows != 0 || g.out.cols_on || g.a.sub.on) return false;
+    if (!env_int("D8K_HALO", 0)) return false;
+    const ConvRule& r = g.a.cr;
+    if (!r.unit_div || r.mul_y != 1 || r.mul_x != 1 || r.C % 32 != 0) return false;
+    const long long plane = static_cast<long long>(r.RH) * r.RW;
+    if (plane <= 0 || g.M % plane != 0) return false;
+    const long long images = g.M / plane;
+    const int span_x = (r.FW - 1) * (r.e_x < 0 ? -r.e_x : r.e_x), span_y = (r.FH - 1) * (r.e_y < 0 ? -r.e_y : r.e_y);
+    const int wp = r.RW + span_x;
+    // patch rows a tile can read: its 128 raster positions starting anywhere in a row, shifted by the farthest tap
+    const long long reach = static_cast<long long>(wp - 1) + 127 + static_cast<long long>(span_y) * wp + span_x + 1;
+    const long long rows = (reach + wp - 1) / wp;
+    if (wp > 256 || rows > 256 || 128LL * wp * rows > kHaloPatchBytes) return false;
+    if (g.out.rows_on && (g.out.RH != r.RH || g.out.RW != r.RW)) return false;
+    if (static_cast<long long>(r.RH) * wp >= (1LL << 31) || images >= (1LL << 31)) return false;
+    if (g.K != static_cast<long long>(r.FH) * r.FW * r.C) return false;
+    GemmProblem h = g;
+    h.batch = static_cast<int>(images);
+    h.M = r.RH * wp;
+    h.a.halo = 1;
+    h.a.halo_wp = wp;
+    h.a.halo_rows = static_cast<int>(rows);
+    h.a.batch_count = static_cast<int>(images);
+    OutMap& o = h.out;
+    if (!o.rows_on) {  // rows are the pixels of the output itself
+        o.rows_on = 1;
+        o.OH = r.RH; o.OW = r.RW; o.sy = 1; o.sx = 1; o.ry = 0; o.rx = 0;
+    }
+    o.RH = r.RH;
+    o.RW = wp;
+    o.valid_w = r.RW;
+    h.c_batch_stride = static_cast<long long>(o.OH) * o.OW * g.ldc;
+    *out = h;
+    return true;
 }
 
 GatherSrc to_gather(const HostOperand& o, int rows, int cols, int esize) {
@@ -375,6 +435,12 @@ int run_gemm(Ctx* ctx, const GemmProblem& g) {
         return 0;
     }
 
+    // a stride-1 virtual operand in fp32: per-tile patches instead of one fetch per filter tap, when the plan stays unsplit
+    GemmProblem halo_problem;
+    if (to_halo(g, &halo_problem)) {
+        const Plan hp = make_plan(ctx, halo_problem, 0);
+        if (hp.tma && hp.splits == 1 && hp.bn == 64 && hp.tiles * 2 > ctx->num_sms) return run_gemm(ctx, halo_problem);
+    }
     // The caller's scratch (a node's interim buffer) is used when it holds everything the split plan wants; a buffer that is
     // missing, empty or smaller than that would silently cost splits, so the context's own scratch serves instead.
     bool own_scratch = g.ws == nullptr || g.ws_bytes == 0;
@@ -384,6 +450,7 @@ int run_gemm(Ctx* ctx, const GemmProblem& g) {
     if (reinterpret_cast<uintptr_t>(scratch) & 15) return fail(1, "gemm: scratch memory must be 16-byte aligned");
     Plan pl = make_plan(ctx, g, scratch_limit);
     if ((g.a.sub.on || g.b.sub.on) && !pl.tma) return fail(1, "gemm: a tap subset of a filter is only read through TMA");
+    if (g.a.halo && (!pl.tma || pl.splits != 1 || pl.bn != 64)) return fail(2, "gemm: the halo form needs the unsplit fp32 TMA kernel");
 
     GemmParams p;
     std::memset(&p, 0, sizeof(p));
@@ -463,6 +530,7 @@ int run_gemm(Ctx* ctx, const GemmProblem& g) {
         p.b = g.b.mn ? to_gather(g.b, g.K, g.N, esize) : to_gather(g.b, g.N, g.K, esize);
         auto build = [&](CUtensorMap* map, const HostOperand& o, int mode, long long extent, int rows_tile, int* chunked) -> bool {
             const bool atom32 = pl.f32 && o.mn;
+            if (mode == kTmaHalo) return make_halo_map(map, o, g.batch, esize);
             if (mode == kTmaIm2col) return make_im2col_map(map, o, extent, rows_tile, esize, atom32);
             if (mode == kTmaIm2colMN) return make_im2col_map(map, o, g.K, ce, esize, atom32);
             if (mode == kTmaFilterTap) return make_filter_tap_map(map, o, ce, rows_tile / ce, esize, atom32);
@@ -476,6 +544,13 @@ int run_gemm(Ctx* ctx, const GemmProblem& g) {
         if (!build(&ta, g.a, pl.a_tma, g.M, kBM, &p.a_chunked) || !build(&tb, g.b, pl.b_tma, g.N, pl.bn, &p.b_chunked))
             return fail(2, "gemm: cuTensorMapEncode failed");
         fn = pl.f32 ? lookup_f32_tma(g.a.mn, g.b.mn, pl.bn, env_int("D8K_F32_ATMEM", 1) != 0) : lookup_f16_tma(g.a.mn, g.b.mn, pl.bn);
+        if (g.a.halo) {
+            fn = lookup_f32_halo(g.b.mn);
+            p.halo_wp = g.a.halo_wp;
+            p.halo_taps = g.a.cr.FH * g.a.cr.FW;
+            p.halo_slices = g.a.cr.C / ce;
+            p.halo_bytes = 128 * g.a.halo_wp * g.a.halo_rows;
+        }
     } else {
         p.a = g.a.mn ? to_gather(g.a, g.K, g.M, esize) : to_gather(g.a, g.M, g.K, esize);
         p.b = g.b.mn ? to_gather(g.b, g.K, g.N, esize) : to_gather(g.b, g.N, g.K, esize);
@@ -494,7 +569,7 @@ int run_gemm(Ctx* ctx, const GemmProblem& g) {
     if (e != cudaSuccess) return fail(2, std::string("gemm: launch failed: ") + cudaGetErrorString(e));
     count_launch();
     {
-        static const char* const kModes[] = {"tiled", "im2col", "im2col-mn", "filter-tap", "filter-sub", "filter-tap-sub"};
+        static const char* const kModes[] = {"tiled", "im2col", "im2col-mn", "filter-tap", "filter-sub", "filter-tap-sub", "halo"};
         std::ostringstream os;
         os << (pl.f32 ? "f32 " : "f16 ") << (pl.pair ? "pair" : pl.tma ? "tma" : "gather");
         if (pl.tma && !pl.pair) os << " a=" << kModes[pl.a_tma] << " b=" << kModes[pl.b_tma];

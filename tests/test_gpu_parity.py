@@ -677,3 +677,30 @@ def test_matrix_vector_kernels_take_the_single_column_case(ctx):
     ctx.matmul_forward(Xb, Yb)
     assert "tma" in ctx.last_kernel()       # the batch of vectors as one contraction through the TMA producer
     assert ctx.status() == 0
+
+
+# ------------------------------------------------------------------------------------------------ the halo form (off by default)
+@pytest.mark.parametrize("case", [("conv", (16, 28, 28, 32), (64, 3, 3, 32), True, (1, 1), (1, 1)), ("conv",) + cases.CONV_REFERENCE_TESTS[1],
+                                  ("conv", (3, 6, 5, 64), (96, 3, 3, 64), True, (1, 1), (1, 1)),
+                                  ("conv", (2, 20, 17, 32), (64, 3, 2, 32), False, (1, 1), (2, 1)),
+                                  ("deconv", (2, 6, 9, 64), (64, 3, 2, 64), False, (1, 1)), ("deconv", (2, 6, 6, 64), (64, 5, 5, 64), True, (2, 2))])
+def test_halo_patches_give_the_same_results(ctx, restated, monkeypatch, case):
+    """D8K_HALO=1: a stride-1 fp32 image operand is fetched once per tile and 32-channel slice as a patch (rows of the padded
+    raster, taps as row shifts) instead of once per filter tap.  Same tolerance against the oracle as the default path."""
+    monkeypatch.setenv("D8K_HALO", "1")
+    kind, xs, ws, cov, st = case[:5]
+    meta = (cov, st) + ((case[5],) if kind == "conv" else ())
+    x, w = cases.uniform(71, xs), cases.normal(72, ws, 0.25)
+    r = Runner(ctx, restated, kind, meta)
+    dz = cases.normal(73, r.zshape(x, w))
+    dx0, dw0 = cases.normal(74, xs), cases.normal(75, ws)
+    X, W = dev(x), dev(w)
+    fwd = ctx.conv2d_forward if kind == "conv" else ctx.deconv2d_forward
+    fwd(X, W, *meta)
+    used = ctx.last_kernel()
+    got = r.gpu(x, w, dz, dx0, dw0, torch.float32)
+    want = r.cpu(x, w, dz, dx0, dw0)
+    for name, g, wnt in zip(("z", "dx", "dy"), got, want):
+        check(ctx, g, wnt, F32_TOL, name)
+    if xs[0] == 16:  # enough tiles for every SM: the halo form is what ran (smaller problems keep the split contraction)
+        assert "halo" in used, used
