@@ -788,6 +788,17 @@ def run_gpu_arm(args):
         if world == 1 and not args.no_cpu:
             line["cpu_baseline"], _ = cpu_arm(1, 0)
         if world == 1 and not args.no_aux:
+            # the same step through the C++ interface (Deep8::Variable::feed -> EagerExecutor -> fetch), in its own process
+            exe = os.path.join(ROOT, "tests", "cpp", "bin", "bench_mlp_e2e")
+            if os.path.exists(exe):
+                del mlp
+                torch.cuda.empty_cache()
+                try:
+                    r = subprocess.run([exe, "10", str(M_PER_GPU)], capture_output=True, text=True, timeout=300)
+                    line["e2e"]["cpp_api"] = json.loads(r.stdout.strip().splitlines()[-1])
+                except Exception as exc:  # the figure is auxiliary: its absence must not cost the line
+                    line["e2e"]["cpp_api"] = {"error": str(exc)[:200]}
+        if world == 1 and not args.no_aux:
             # BASELINE configurations 1-4 with their own inputs: an auxiliary report, outside the headline's timed region
             line["aux"] = [run_small(ctx, torch, device, n, steps=20, warmup=3, half=False, with_cpu=not args.no_cpu) for n in (1, 2, 3, 4)]
         print(json.dumps(line), flush=True)

@@ -625,6 +625,69 @@ public:
     void update(Executor* executor, Variable* parameter, float learningRate, float weightDecay, int64_t steps) override;
 };
 
+// ------------------------------------------------------------------------------------------------ several GPUs (additions)
+// The reference runs on one device (deep8/src/model/Executor.cu:6-8).  With the batch sharded over the GPUs of a box - one
+// process and one EagerExecutor(DeviceType::GPU, rank) per GPU - the gradients of the parameters every rank holds a copy of
+// must be summed over the ranks after backward() and before Trainer::train (deep8/src/trainer/Trainer.cpp:12-32).
+
+// How the processes find each other on the host: handles and barriers only, no tensor data.
+class DEEP8_API Rendezvous {
+public:
+    virtual ~Rendezvous() = default;
+    virtual int rank() const = 0;
+    virtual int world() const = 0;
+    // every rank contributes `bytes` bytes; `all` receives world * bytes, rank r's at offset r * bytes
+    virtual void allGather(const void* mine, size_t bytes, void* all) = 0;
+    virtual void barrier() = 0;
+};
+
+// Rendezvous through a directory every rank can see (a tmpfs path on one box): each allGather writes one small file per rank
+// (written under a temporary name, then renamed) and polls for the others', giving up with std::runtime_error after the timeout.
+class DEEP8_API FileRendezvous : public Rendezvous {
+public:
+    FileRendezvous(std::string directory, int rank, int world, double timeoutSeconds = 60.0);
+    int rank() const override { return myRank; }
+    int world() const override { return worldSize; }
+    void allGather(const void* mine, size_t bytes, void* all) override;
+    void barrier() override;
+
+private:
+    std::string dir;
+    int myRank, worldSize;
+    double timeout;
+    long round = 0;
+};
+
+// Sum of the listed parameters' gradients over the ranks, through GPU memory the peers map (d8k_peer_*): every rank owns a
+// contiguous shard of the concatenated gradients, pulls that shard of every peer's copy with the copy engines, adds the
+// shards in rank order in fp32 (every rank gets the same bits), and pushes the result to the peers.  Everything is enqueued
+// on the executor's stream; a peer that does not arrive within the timeout raises std::runtime_error at the next
+// synchronisation instead of hanging the GPU.  All parameters must share one element type (fp32 or fp16).
+class DEEP8_API PeerGradientSum {
+public:
+    PeerGradientSum(Executor* executor, Rendezvous* rendezvous, std::vector<Variable*> parameters, double timeoutMs = 2000.0);
+    ~PeerGradientSum();
+    PeerGradientSum(const PeerGradientSum&) = delete;
+    PeerGradientSum& operator=(const PeerGradientSum&) = delete;
+    void sum();          // call after backward(); returns with the work enqueued
+    void synchronize();  // waits for it and throws if a wait between the ranks expired
+    size_t elements() const { return total; }
+
+private:
+    Rendezvous* rv;
+    GPUDevice* device;
+    std::vector<Variable*> params;
+    std::vector<size_t> offsets;  // element offset of each gradient in the concatenation
+    size_t total = 0, esize = 0, shardElems = 0;
+    int dtype = 0, world = 1, rank = 0;
+    unsigned step = 0;
+    double timeout;
+    char* base = nullptr;           // partial | result | one staging slot per rank | flags
+    std::vector<char*> peers;       // the same allocation in every rank, as mapped here
+    size_t offPartial = 0, offResult = 0, offStage = 0, offFlags = 0, stageBytes = 0;
+    void* flag(int owner, int kind, int writer) const;
+};
+
 }  // namespace Deep8
 
 #endif  // DEEP8_B200_DEEP8_H

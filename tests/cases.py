@@ -37,6 +37,7 @@ MATMUL_EDGE = [
     ((1, 128, 64), (1, 64, 128)),      # exactly one tile
     ((3, 50, 72), (1, 72, 1)),         # y is one column, batch 1: the matrix-vector kernels (16-byte rows)
     ((1, 257, 1001), (1, 1001, 1)),    # the same with rows that are not 16-byte multiples
+    ((2, 37, 4096), (1, 4096, 1)),     # rows of 8 KB and more take a CTA each
     ((1, 64, 128), (6, 128, 1)),       # x broadcast, y a batch of columns: one contraction Y * X^T through TMA
 ]
 MATMUL_CFG1 = ((1, 256, 512), (1, 512, 128))

@@ -690,3 +690,28 @@ def test_two_gpu_exchange_sums_partials_bit_exactly(tmp_path, numel, gather):
     mp.spawn(_exchange_worker, args=(world, _free_port(), numel, 3, str(tmp_path), gather), nprocs=world, join=True)
     for r in range(world):
         assert open(os.path.join(str(tmp_path), "rank%d.txt" % r)).read() == "1 0 0"
+
+
+@pytest.mark.gpu
+def test_two_gpu_cpp_host_sums_gradients_and_trains(tmp_path):
+    """The C++ host side of the multi-GPU path (Deep8::FileRendezvous, Deep8::PeerGradientSum, SGDTrainer): two processes, one
+    GPU each, run tests/cpp/test_deep8_dp and compare with the CPU oracle for equality."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import subprocess
+    exe = os.path.join(ROOT, "tests", "cpp", "bin", "test_deep8_dp")
+    assert os.path.exists(exe), "tests/cpp/bin/test_deep8_dp is missing: run __graft_entry__.build()"
+    procs = [subprocess.Popen([exe, str(tmp_path), str(r), "2"], stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True) for r in range(2)]
+    outs = [p.communicate(timeout=180)[0] for p in procs]
+    for r, (p, out) in enumerate(zip(procs, outs)):
+        assert p.returncode == 0 and ("rank %d: OK" % r) in out, out
+
+
+@pytest.mark.gpu
+def test_cpp_host_gradient_sum_with_one_rank(tmp_path):
+    """The same program with a world of one: rendezvous, the trainer step and the oracle comparison without a peer."""
+    import subprocess
+    exe = os.path.join(ROOT, "tests", "cpp", "bin", "test_deep8_dp")
+    assert os.path.exists(exe), "tests/cpp/bin/test_deep8_dp is missing: run __graft_entry__.build()"
+    r = subprocess.run([exe, str(tmp_path), "0", "1"], capture_output=True, text=True, timeout=180)
+    assert r.returncode == 0 and "rank 0: OK" in r.stdout, r.stdout + r.stderr
