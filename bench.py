@@ -2,19 +2,24 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
 
-Workload (per GPU, weak scaling): X 8192x4096, W1 4096x16384, ReLU, W2 16384x4096, upstream gradient dY 8192x4096;
-fp16 storage, fp32 accumulation.  One step = H = X W1, A = relu(H), Y = A W2, then dA = dY W2^T, dW2 = A^T dY,
-dH = relu'(H) dA, dX = dH W1^T, dW1 = X^T dH (six contractions of 2*8192*4096*16384 FLOP each), and for N > 1 the NCCL
-all-reduce (sum) of dW1 and dW2.  By default the two ReLU passes run inside the epilogues of the contractions that
-produce their inputs and every gradient is written by its first (here: only) contribution, so no zero fill is needed;
-`--unfused` runs the reference's call sequence instead (zero every gradient, eight separate operator calls, += everywhere).
-Both give bit-identical tensors (tests/test_gpu_parity.py::test_fused_step_equals_unfused).  Inputs are seeded synthetic
-data (X N(0,1), weights N(0,0.02), dY N(0,1)*0.01, seed 10, rank-offset for X and dY).
+Workload (weak scaling, 8192 rows per GPU in the global batch): X rows x 4096, W1 4096x16384, ReLU, W2 16384x4096, upstream
+gradient dY rows x 4096; fp16 storage, fp32 accumulation.  One step = H = X W1, A = relu(H), Y = A W2, then dA = dY W2^T,
+dW2 = A^T dY, dH = relu'(H) dA, dX = dH W1^T, dW1 = X^T dH (six contractions of 2*8192*4096*16384 FLOP each on 8192 rows),
+and for N > 1 the sum of dW1 and dW2 over the GPUs (peer-memory exchange, deep8_b200.dp.PeerAllReduce).  By default the two
+ReLU passes run inside the epilogues of the contractions that produce their inputs and every gradient is written by its
+first (here: only) contribution, so no zero fill is needed; `--unfused` runs the reference's call sequence instead (zero
+every gradient, eight separate operator calls, += everywhere).  Both give bit-identical tensors
+(tests/test_gpu_parity.py::test_fused_step_equals_unfused).  Inputs are seeded synthetic data (X N(0,1), weights N(0,0.02),
+dY N(0,1)*0.01, seed 10, rank-offset for X and dY).  With several GPUs the global batch of N x 8192 rows is split by the
+ranks' measured speeds (`--no-balance`: 8192 rows each).
 
-Prints ONE JSON line.  `value` is the aggregate TFLOP/s over all GPUs with inputs resident in HBM; `e2e` is the same
-metric with X and dY copied from pinned host memory and Y copied back inside every step; `roofline` is for the
-contraction kernel (tensor bound) against the measured cuBLAS bf16 peak of this pool; `cpu_baseline` is the reference's
-own CPU code on a row slice of the same workload.  `--impl reference` times only that CPU code.
+Prints ONE JSON line.  `value` is the aggregate TFLOP/s over all GPUs with inputs resident in HBM, after `--preheat` seconds
+of the same step, with NVML clock samples taken inside the timed region; `e2e` is the same metric with X and dY copied from
+pinned host memory and Y copied back inside every step (plus the same copies without kernels, and the step through the C++
+interface); `roofline` is for the contraction kernel (tensor bound) against the measured cuBLAS bf16 peak of this pool;
+`contractions` and `ranks` say where the step's time went on every rank; `exchange_check` compares the exchanged gradients
+with the sum of the ranks' partial gradients; `cpu_baseline` is the reference's own CPU code on a row slice of the same
+workload; `aux` reports BASELINE configurations 1-4.  `--impl reference` times only that CPU code.
 """
 import argparse
 import json
@@ -264,8 +269,9 @@ class MlpStep:
 
     SGD = (1e-6, 1e-4)  # learning rate, weight decay of the optional trainer step (--sgd); small: the data are random every step
 
-    def __init__(self, ctx, torch, device, rank, fused=True, exchange=None, scatter=False, sgd=False):
+    def __init__(self, ctx, torch, device, rank, fused=True, exchange=None, scatter=False, sgd=False, rows=None):
         self.ctx, self.torch, self.fused, self.scatter, self.sgd = ctx, torch, fused, scatter, sgd
+        M_PER_GPU = self.rows = rows if rows is not None else globals()["M_PER_GPU"]  # this rank's share of the batch
         self.ar1 = self.ar2 = None
         self.pending = False
         g = torch.Generator(device=device)
@@ -540,6 +546,48 @@ def filter_gradient_exchange(n_cfg, ctx, ctx_side, side, torch, dist, device, wo
                     "copy-engine push to every peer"}
 
 
+def step_cost(rows, pairs=74):
+    """Relative time of one step on `rows` rows: the paired kernel works in waves of `pairs` 256 x 256 tiles, each tile costing
+    its contraction length.  Used to predict what moving rows between ranks does, wave quantisation included."""
+    mt = -(-rows // 256)
+    wide = -(-mt * (D_HID // 256) // pairs) * D_IN          # H = X W1 and dA = dY W2^T: rows x 16384 outputs, K = 4096
+    narrow = -(-mt * (D_IN // 256) // pairs) * D_HID         # Y = A W2 and dX = dH W1^T: rows x 4096 outputs, K = 16384
+    grads = -(-(D_HID // 256) * (D_IN // 256) // pairs) * rows  # dW1, dW2: fixed outputs, K = rows
+    return 2.0 * (wide + narrow + grads)
+
+
+def balance_rows(step_ms, total_rows, quantum=256):
+    """Rows per rank (multiples of `quantum`, summing to total_rows) that minimise the slowest rank's predicted step, given
+    each rank's measured step time on an equal share.  GPUs of one box differ by 5-20 % under the power limit, and a step
+    that exchanges gradients runs at the pace of the slowest rank: the faster GPUs take more of the batch."""
+    world = len(step_ms)
+    equal = total_rows // world
+    speed = [1.0 / t for t in step_ms]
+    rows = [max(quantum, int(round(total_rows * sp / sum(speed) / quantum)) * quantum) for sp in speed]
+    while sum(rows) > total_rows:
+        rows[rows.index(max(rows))] -= quantum
+    while sum(rows) < total_rows:
+        rows[rows.index(min(rows))] += quantum
+    predict = lambda r, k: step_ms[k] * step_cost(r) / step_cost(equal)
+    for _ in range(4 * world * (equal // quantum)):  # move one quantum from the slowest predicted rank to the one that stays fastest
+        times = [predict(rows[k], k) for k in range(world)]
+        slow = times.index(max(times))
+        if rows[slow] <= quantum:
+            break
+        best, best_t = None, times[slow]
+        for k in range(world):
+            if k == slow:
+                continue
+            t = max(predict(rows[k] + quantum, k), predict(rows[slow] - quantum, slow))
+            if t < best_t - 1e-9:
+                best, best_t = k, t
+        if best is None:
+            break
+        rows[slow] -= quantum
+        rows[best] += quantum
+    return rows
+
+
 def run_gpu_arm(args):
     import torch
     import deep8_b200
@@ -574,8 +622,33 @@ def run_gpu_arm(args):
         exchange = lambda numel, rows: PeerAllReduce(ctx, ctx_side, side, numel, torch.float16, device, rows=rows, with_weights=args.sgd,
                                                      timeout_ms=20000.0, gather=os.environ.get("D8_BENCH_GATHER", "copy"))
     step_dist = None if mode == "none" else dist  # "none": the ranks run side by side and nothing is summed (diagnostic)
+    # Shares of the batch.  The global batch is world x 8192 rows; each rank first times the step alone on an equal share
+    # (no exchange, about a second, so that the GPUs are at their power-limited clocks), then the rows are split so that every
+    # rank is predicted to need the same time.  --no-balance keeps 8192 rows everywhere.
+    my_rows, balance = M_PER_GPU, None
+    if dist is not None and not args.no_balance and not args.profile:
+        cal = MlpStep(ctx, torch, device, rank, fused=not args.unfused)
+        for _ in range(160):
+            cal.step()
+        torch.cuda.synchronize()
+        c0, c1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        c0.record()
+        for _ in range(40):
+            cal.step()
+        c1.record()
+        torch.cuda.synchronize()
+        mine = torch.tensor([c0.elapsed_time(c1) / 40], device=device, dtype=torch.float64)
+        every = [torch.empty_like(mine) for _ in range(world)]
+        dist.all_gather(every, mine)
+        alone_ms = [float(t.item()) for t in every]
+        shares = balance_rows(alone_ms, M_PER_GPU * world)
+        my_rows = shares[rank]
+        balance = {"rows_per_gpu": shares, "step_ms_alone_on_equal_shares": alone_ms,
+                   "rule": "rows in multiples of 256, chosen so that every rank's predicted step time (measured time x tile-wave count) is equal"}
+        del cal
+        torch.cuda.empty_cache()
     mlp = MlpStep(ctx, torch, device, rank, fused=not args.unfused, exchange=exchange,
-                  scatter=exchange is not None and mode == "fused" and not args.unfused, sgd=args.sgd)
+                  scatter=exchange is not None and mode == "fused" and not args.unfused, sgd=args.sgd, rows=my_rows)
 
     def barrier():
         if dist is not None:
@@ -749,7 +822,8 @@ def run_gpu_arm(args):
     if rank == 0:
         peak, peak_src = measured_peaks()
         avg_gemm_ms = sum(gemm_ms) / len(gemm_ms)
-        achieved = FLOP_PER_GEMM / (avg_gemm_ms * 1e-3) / 1e12
+        flop_per_launch = FLOP_PER_GEMM * my_rows / M_PER_GPU  # rank 0's contractions, on rank 0's share of the rows
+        achieved = flop_per_launch / (avg_gemm_ms * 1e-3) / 1e12
         per_gpu = FLOP_PER_STEP / (ms_step * 1e-3) / 1e12
         sm_mhz = clocks.get("sm_mhz") if clocks else None
         contractions = [{"name": CONTRACTIONS[i] if not args.unfused else CONTRACTIONS[i].split(" (")[0], "ms_rank0": float(table[0, 3 + i]),
@@ -764,7 +838,7 @@ def run_gpu_arm(args):
             "preheat_s": preheat_s, "preheat_steps": preheat_steps,
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
                          "traffic": TRAFFIC_BYTES_PER_LAUNCH, "kernel": "d8k_gemm_pair_kernel (TMA-fed fp16, CTA pairs on 256x256 tiles)",
-                         "peak_source": peak_src, "flop_per_launch": FLOP_PER_GEMM, "avg_launch_ms": avg_gemm_ms,
+                         "peak_source": peak_src, "flop_per_launch": flop_per_launch, "avg_launch_ms": avg_gemm_ms,
                          "mcycles_per_launch": (avg_gemm_ms * 1e-3 * sm_mhz) if sm_mhz else None,
                          "gemm_share_of_step": sum(gemm_ms) / (my_ms * args.steps)},
             "contractions": contractions,
@@ -780,6 +854,9 @@ def run_gpu_arm(args):
                     "e2e_over_max_of_copy_and_compute": e2e_ms / max(copy_ms, ms_step)},
             "gpu_launches": launches, "clocks": clocks,
         }
+        if balance is not None:
+            line["config"]["rows_per_gpu"] = balance["rows_per_gpu"]
+            line["config"]["batch_shares"] = balance
         if xcheck is not None:
             line["exchange_check"] = xcheck["result"]
             line["exchange_check_detail"] = xcheck
@@ -810,9 +887,9 @@ def run_gpu_arm(args):
         dist.destroy_process_group()
 
 
-# DRAM bytes (read + write) of one contraction launch of this workload: mean over the launches of one step captured with ncu;
-# the algorithmic bytes are 0.47e9.
-TRAFFIC_BYTES_PER_LAUNCH = 1.28e9
+# DRAM bytes (read + write) of one contraction launch of this workload: mean over the six launches of one step captured with ncu
+# (dram__bytes_read.sum + dram__bytes_write.sum); the algorithmic bytes are 0.45e9 to 0.96e9 depending on the fused epilogue.
+TRAFFIC_BYTES_PER_LAUNCH = 1.31e9
 
 
 # ------------------------------------------------------------------------------------------------ configs 1-4 (fp32)
@@ -944,6 +1021,8 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-aux", action="store_true", help="skip the auxiliary reports (configurations 1-4 on one GPU; the Conv2d/DeConv2d "
                     "filter-gradient exchange on several)")
+    ap.add_argument("--no-balance", action="store_true", help="several GPUs: keep 8192 rows on every rank instead of giving the faster GPUs "
+                    "a larger share of the global batch")
     ap.add_argument("--preheat", type=float, default=2.0, help="seconds of untimed steps before the timed region (0 = none)")
     ap.add_argument("--half", action="store_true", help="with --config: run the configuration's operator on fp16 storage")
     ap.add_argument("--sgd", action="store_true",

@@ -4,15 +4,19 @@
 //
 // Operands are staged in shared memory as 128-byte rows under the 128-byte swizzle and multiplied by
 // tcgen05.mma (cta_group::1, UMMA 128 x BN x {16 | 8}) into fp32 accumulators in tensor memory; two accumulator
-// buffers let the epilogue of one tile overlap the main loop of the next.  Two ways of filling a stage:
+// buffers let the epilogue of one tile overlap the main loop of the next.  Three ways of filling a stage:
 //
-//   TMA    (fp16 only)  one thread issues cp.async.bulk.tensor loads; needs 16-byte aligned pitches.
-//   GATHER (fp16/fp32)  four loader warps read global memory with plain 16-byte loads and write the swizzled rows
-//                       themselves.  An operand is either a strided matrix or a *virtual im2col matrix* whose
-//                       rows are pixels and whose columns are (filter tap, channel): the column buffer of the
-//                       reference's Conv2d/DeConv2d (deep8/src/math/Conv2d.cu:10-61, DeConv2d.cu:311-351) is never
-//                       written to memory.  For fp32 the loaders split every value into a tf32 "hi" and a tf32 "lo"
-//                       part (3xTF32): D += A_lo*B_hi + A_hi*B_lo + A_hi*B_hi, accumulated in fp32.
+//   TMA            (fp16)  one thread issues cp.async.bulk.tensor loads: tiled boxes of stored matrices, im2col boxes of
+//                          NHWC images (a *virtual im2col matrix* whose rows are pixels and whose columns are (filter tap,
+//                          channel): the column buffer of the reference's Conv2d/DeConv2d, deep8/src/math/Conv2d.cu:10-61,
+//                          DeConv2d.cu:311-351, is never written to memory), boxes over a filter's taps.
+//   TMA + CONVERT  (fp32)  the same loads deliver raw fp32 tiles, which the tensor core reads as the tf32 "hi" image (it
+//                          drops the low 13 mantissa bits); converter warps write the "lo" image beside them - and, with
+//                          ATMEM, A's hi and lo images into tensor memory (3xTF32: D += A_hi [B_hi ; B_lo] + A_lo B_hi).
+//                          HALO additionally fetches a stride-1 image operand as per-tile patches (GemmCfg::HALO).
+//   GATHER         (both)  helper warps read global memory with plain 16-byte loads and write the swizzled rows
+//                          themselves, for whatever TMA cannot describe (unaligned pitches, odd channel counts, rules
+//                          with a divisor); fp32 is split into tf32 hi and lo on the way.
 //
 // Split-K: when the output has few tiles and K is long, `splits` CTAs share one tile.  Each writes its fp32 partial
 // tile to scratch memory, takes a ticket with atomicAdd, and the CTA that draws the last ticket sums the partials

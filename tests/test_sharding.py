@@ -84,3 +84,21 @@ def test_sharded_step_equals_whole_batch(tmp_path, restated):
     for p in parts:                                                          # every rank holds the full sums
         assert cases.rel_max(p["dy"], dy) < 1e-6
         assert cases.rel_max(p["cdw"], cdw) < 1e-6
+
+
+def test_batch_shares_follow_the_measured_speeds():
+    """bench.py's split of the global batch over GPUs of unequal speed: shares sum to the batch, are multiples of 256 rows,
+    give a faster rank at least as many rows as a slower one, and never predict a slower step than the equal split."""
+    sys.path.insert(0, ROOT)
+    import bench
+    for ms in ([5.0, 5.0], [4.46, 5.48], [4.7, 4.9, 5.0, 5.1], [4.7, 4.9, 5.0, 5.1, 5.2, 4.8, 5.3, 4.95], [5.0] * 8):
+        world = len(ms)
+        rows = bench.balance_rows(ms, 8192 * world)
+        assert sum(rows) == 8192 * world and all(r % 256 == 0 and r > 0 for r in rows)
+        for a in range(world):
+            for b in range(world):
+                if ms[a] < ms[b]:
+                    assert rows[a] >= rows[b]
+        predict = lambda r, k: ms[k] * bench.step_cost(r) / bench.step_cost(8192)
+        assert max(predict(rows[k], k) for k in range(world)) <= max(ms) + 1e-9
+    assert bench.balance_rows([5.0, 5.0, 5.0], 8192 * 3) == [8192] * 3
