@@ -878,6 +878,7 @@ def run_gpu_arm(args):
         if world == 1 and not args.no_aux:
             # BASELINE configurations 1-4 with their own inputs: an auxiliary report, outside the headline's timed region
             line["aux"] = [run_small(ctx, torch, device, n, steps=20, warmup=3, half=False, with_cpu=not args.no_cpu) for n in (1, 2, 3, 4)]
+            line["hbm_kernels"] = run_hbm_kernels(ctx, torch, device)
         print(json.dumps(line), flush=True)
     if dist is not None:
         dist.barrier()
@@ -890,6 +891,58 @@ def run_gpu_arm(args):
 # DRAM bytes (read + write) of one contraction launch of this workload: mean over the six launches of one step captured with ncu
 # (dram__bytes_read.sum + dram__bytes_write.sum); the algorithmic bytes are 0.45e9 to 0.96e9 depending on the fused epilogue.
 TRAFFIC_BYTES_PER_LAUNCH = 1.31e9
+
+
+# ------------------------------------------------------------------------------------------------ HBM-bound neighbours
+def run_hbm_kernels(ctx, torch, dev, rows=16384, cols=16384):
+    """The path's HBM-bound kernels on operands far larger than L2: MatrixMultiply with a single-column y (forward = matrix-vector
+    product over rows, gradient of y = over columns, gradient of x = outer product) on a rows x cols matrix, and Linear /
+    AdamUpdate on 2^27 elements.  Median of 10 launches (CUDA events), algorithmic bytes / time, and that as a fraction of the
+    measured copy bandwidth."""
+    import statistics
+    peak, label = 6650.0, "of fallback copy bandwidth (an earlier measurement on this pool)"
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            peak, label = float(json.load(f)["hbm_gbs"]), "of measured copy bandwidth"
+
+    def gbs(fn, nbytes):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        ts = []
+        for _ in range(10):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            fn()
+            b.record()
+            torch.cuda.synchronize()
+            ts.append(a.elapsed_time(b) * 1e-3)
+        v = nbytes / statistics.median(ts) / 1e9
+        return {"gbs": round(v, 1), "frac": round(v / peak, 3)}
+
+    out = {"peak_gbs": peak, "frac_is": label, "matrix": [rows, cols]}
+    for dt, es, name in ((torch.float32, 4, "f32"), (torch.float16, 2, "f16")):
+        X = torch.randn(1, rows, cols, device=dev, dtype=dt)
+        y = torch.randn(1, cols, 1, device=dev, dtype=dt)
+        z = torch.empty(1, rows, 1, device=dev, dtype=dt)
+        dz = torch.randn(1, rows, 1, device=dev, dtype=dt)
+        dX, dy = torch.zeros_like(X), torch.zeros_like(y)
+        r = {}
+        r["matvec_rows"] = gbs(lambda: ctx.matmul_forward(X, y, out=z), rows * cols * es)
+        r["matvec_columns"] = gbs(lambda: ctx.matmul_grad_y(X, y, dy, dz), rows * cols * es)
+        r["outer_product"] = gbs(lambda: ctx.matmul_grad_x(X, dX, y, dz), 2 * rows * cols * es)
+        del X, dX
+        n = 1 << 27
+        a, b = torch.randn(n, device=dev, dtype=dt), torch.randn(n, device=dev, dtype=dt)
+        m, v = torch.zeros(n, device=dev, dtype=dt), torch.zeros(n, device=dev, dtype=dt)
+        r["linear_forward"] = gbs(lambda: ctx.linear_forward(a, 0.5, 1.0, out=b), 2 * n * es)
+        r["linear_grad"] = gbs(lambda: ctx.linear_grad(b, 0.5, a), 3 * n * es)
+        r["adam_update"] = gbs(lambda: ctx.adam_update(a, b, m, v, 0.9, 0.999, 1e-7, 1e-3, 0.0, 1), 8 * n * es)
+        del a, b, m, v
+        torch.cuda.empty_cache()
+        out[name] = r
+    return out
 
 
 # ------------------------------------------------------------------------------------------------ configs 1-4 (fp32)

@@ -81,6 +81,7 @@ GemmLaunchFn lookup_f16_tma(bool a_mn, bool b_mn, int bn);
 GemmLaunchFn lookup_f16_gather(bool a_mn, bool b_mn, int bn);
 GemmLaunchFn lookup_f32_gather(bool a_mn, bool b_mn, int bn);
 GemmLaunchFn lookup_f32_tma(bool a_mn, bool b_mn, int bn, bool a_in_tmem);
+GemmLaunchFn lookup_f32_dual(bool a_mn, bool b_mn, int mode);  // two CTAs per SM (GemmCfg::DUAL, mode 1 or 2); launch 2 x SMs CTAs
 GemmLaunchFn lookup_f32_halo(bool b_mn);  // K-major virtual A through patches, 64 columns
 // paired-CTA kernel: the first argument of the launch function is the number of CTA pairs
 GemmLaunchFn lookup_f16_pair(bool a_mn, bool b_mn);

@@ -19,6 +19,17 @@ GemmLaunchFn lookup_f32_halo(bool b_mn) {
     return launch_cfg<GemmCfg<true, false, false, 64, 4, false, true, true>>;
 }
 
+// two CTAs per SM, each with one accumulator buffer and one converter group.  mode 1: A's hi and lo images in tensor
+// memory, two 32 KB stages; mode 2: only the lo image there (the raw tile is the hi image), three stages
+template <int MODE, int STAGES>
+static GemmLaunchFn pick_dual(bool a_mn, bool b_mn) {
+    if (!a_mn && !b_mn) return launch_cfg<GemmCfg<true, false, false, 64, STAGES, false, true, false, MODE>>;
+    if (!a_mn && b_mn) return launch_cfg<GemmCfg<true, false, true, 64, STAGES, false, true, false, MODE>>;
+    if (a_mn && !b_mn) return launch_cfg<GemmCfg<true, true, false, 64, STAGES, false, true, false, MODE>>;
+    return launch_cfg<GemmCfg<true, true, true, 64, STAGES, false, true, false, MODE>>;
+}
+GemmLaunchFn lookup_f32_dual(bool a_mn, bool b_mn, int mode) { return mode == 2 ? pick_dual<2, 3>(a_mn, b_mn) : pick_dual<1, 2>(a_mn, b_mn); }
+
 GemmLaunchFn lookup_f32_tma(bool a_mn, bool b_mn, int bn, bool a_in_tmem) {
     if (!a_mn && !b_mn) return pick<false, false>(bn, a_in_tmem);
     if (!a_mn && b_mn) return pick<false, true>(bn, a_in_tmem);

@@ -199,7 +199,7 @@ __device__ __forceinline__ long long scatter_offset(const GemmParams& p, int row
     return p.scatter_off[k < kMaxScatter ? k : kMaxScatter - 1];
 }
 
-template <bool F32_, bool A_MN_, bool B_MN_, int BN_, int STAGES_, bool GATHER_, bool ATMEM_ = false, bool HALO_ = false>
+template <bool F32_, bool A_MN_, bool B_MN_, int BN_, int STAGES_, bool GATHER_, bool ATMEM_ = false, bool HALO_ = false, int DUAL_ = 0>
 struct GemmCfg {
     static constexpr bool F32 = F32_, A_MN = A_MN_, B_MN = B_MN_, GATHER = GATHER_;
     static constexpr int BN = BN_, STAGES = STAGES_;
@@ -233,9 +233,21 @@ struct GemmCfg {
     // 128 x 128 x 8 one takes its nominal 64).
     static constexpr bool STACK = F32 && BN == 64;
     static constexpr int ACC_COLS = STACK ? 2 * BN : BN;         // accumulator columns per buffer
-    static constexpr int A_TMEM_COL0 = 2 * ACC_COLS;            // after the two accumulator buffers
-    static constexpr int A_TMEM_COLS = ATMEM ? 2 * BK * STAGES : 0;  // per stage BK columns of hi, BK of lo
-    static constexpr int TMEM_NEED = 2 * ACC_COLS + A_TMEM_COLS;
+    // DUAL (fp32 with ATMEM): TWO CTAs share an SM, each with half of everything - one accumulator buffer instead of two, half
+    // the stages, one converter group, half of tensor memory.  The k-block period of one CTA is set by the latencies of its
+    // single-thread roles (barrier round trips, commits), during which the tensor pipe idles; a second CTA's MMAs fill
+    // those gaps, and its main loop runs while the first CTA's epilogue drains the one accumulator buffer.
+    // DUAL_ == 2 (ALO): only A's lo image goes to tensor memory; the raw tile in shared memory serves as the hi image, read
+    // by the wide MMA through a descriptor.  Half the tensor-memory columns per stage, so each CTA holds three stages.
+    static constexpr bool DUAL = DUAL_ != 0;
+    static constexpr bool ALO = DUAL_ == 2;
+    static constexpr int A_TMEM_STRIDE = ALO ? BK : 2 * BK;     // tensor-memory columns of A per stage
+    static constexpr int ACC_BUFS = DUAL ? 1 : 2;
+    static constexpr int CTAS_PER_SM = DUAL ? 2 : 1;
+    static constexpr int A_TMEM_COL0 = ACC_BUFS * ACC_COLS;     // after the accumulator buffers
+    static constexpr int A_TMEM_COLS = ATMEM ? A_TMEM_STRIDE * STAGES : 0;  // per stage BK columns of hi (unless ALO), BK of lo
+    static constexpr int TMEM_NEED = ACC_BUFS * ACC_COLS + A_TMEM_COLS;
+    static_assert(!DUAL || (ATMEM && !HALO_ && STACK && TMEM_NEED <= 256), "two CTAs per SM share 512 columns of tensor memory");
     static constexpr int TMEM_COLS = (TMEM_NEED <= 32) ? 32 : (TMEM_NEED <= 64) ? 64 : (TMEM_NEED <= 128) ? 128 : (TMEM_NEED <= 256) ? 256 : 512;
     static_assert(TMEM_NEED <= 512, "tensor memory");
     static_assert(!ATMEM || (F32 && !GATHER), "A in tensor memory belongs to the fp32 TMA kernels");
@@ -250,7 +262,7 @@ struct GemmCfg {
     // conversions overlap the other group's global-load latency (a lone group spent 4-8 us per k-block).
     static constexpr int PRODUCER_WARP = 4, MMA_WARP = 5, LOADER_WARP0 = 6, LOADER_WARPS = 4;
     // fp32 with 128 columns keeps 128 accumulators per epilogue thread in registers: no room for a second group there
-    static constexpr int LOADER_GROUPS = (F32 && BN_ > 64) ? 1 : 2;
+    static constexpr int LOADER_GROUPS = ((F32 && BN_ > 64) || DUAL) ? 1 : 2;
     // fp32 without GATHER: TMA brings the operands as stored.  The tensor core reads a raw fp32 word as tf32 by dropping
     // its low 13 mantissa bits, so the copy TMA made IS the hi image; the same warps that would gather only have to
     // write the lo image, tf32(v - trunc(v)), beside it - shared memory to shared memory, no global-load latency.
@@ -262,7 +274,7 @@ struct GemmCfg {
     static_assert(BN % 16 == 0 && BN >= 16 && BN <= 256, "UMMA N");
     static_assert(BN % CE == 0, "an MN-major B tile is whole 128-byte chunks");
     static_assert(SMEM_BYTES <= 227 * 1024, "shared memory");
-    static_assert(SMEM_BYTES > 114 * 1024, "one CTA per SM: two would compete for tensor memory");
+    static_assert(DUAL ? SMEM_BYTES <= 112 * 1024 : SMEM_BYTES > 114 * 1024, "one CTA per SM unless DUAL: more would compete for tensor memory");
 };
 
 struct WorkItem {
@@ -774,7 +786,7 @@ __device__ __forceinline__ void produce_operand(int mode, int chunked, const Gat
 }
 
 template <class Cfg>
-__global__ void __launch_bounds__(Cfg::THREADS, 1)
+__global__ void __launch_bounds__(Cfg::THREADS, Cfg::CTAS_PER_SM)
 d8k_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmParams p) {
     using OutT = typename std::conditional<Cfg::F32, float, __half>::type;
     using InT = OutT;
@@ -913,7 +925,8 @@ d8k_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         // ============================================================================ MMA issuer
         // A from tensor memory is always one row per lane, whatever the stored layout was
         constexpr uint32_t idesc = ptx::make_idesc(Cfg::F32 ? 2u : 0u, Cfg::A_MN && !Cfg::ATMEM, Cfg::B_MN, kBM, BN);
-        constexpr uint32_t idesc_wide = ptx::make_idesc(Cfg::F32 ? 2u : 0u, Cfg::A_MN && !Cfg::ATMEM, Cfg::B_MN, kBM, Cfg::STACK ? 2 * BN : BN);
+        constexpr uint32_t idesc_wide =
+            ptx::make_idesc(Cfg::F32 ? 2u : 0u, Cfg::A_MN && (!Cfg::ATMEM || Cfg::ALO), Cfg::B_MN, kBM, Cfg::STACK ? 2 * BN : BN);
         // descriptor step per UMMA_K: K-major advances 32 bytes inside the swizzled row; MN-major advances UMMA_K rows
         constexpr uint32_t a_step = Cfg::A_MN ? Cfg::UMMA_K * 128 : 32;
         constexpr uint32_t b_step = Cfg::B_MN ? Cfg::UMMA_K * 128 : 32;
@@ -962,7 +975,10 @@ d8k_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                         const uint32_t accumulate = (in_chain > 0 || s > 0) ? 1u : 0u;
                         if constexpr (Cfg::ATMEM) {
                             const uint32_t ta_hi = ta_run + s * Cfg::UMMA_K;
-                            if constexpr (Cfg::STACK) {
+                            if constexpr (Cfg::ALO) {
+                                ptx::mma_tf32(d_tmem, da, db, idesc_wide, accumulate);    // A_hi (shared memory) [B_hi ; B_lo]
+                                ptx::mma_tf32_a_tmem(d_tmem, ta_hi, db, idesc, 1u);      // A_lo (tensor memory) B_hi
+                            } else if constexpr (Cfg::STACK) {
                                 ptx::mma_tf32_a_tmem(d_tmem, ta_hi, db, idesc_wide, accumulate);  // A_hi [B_hi ; B_lo]
                                 ptx::mma_tf32_a_tmem(d_tmem, ta_hi + BK, db, idesc, 1u);          // A_lo B_hi
                             } else {
@@ -993,11 +1009,11 @@ d8k_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                     phase ^= 1;
                     da_run = da_first; db_run = db_first; ta_run = ta_first; full_run = full_bar(0); empty_run = empty_bar(0);
                 } else {
-                    da_run += kStageStep; db_run += kStageStep; ta_run += 2 * BK; full_run += 8; empty_run += 8;
+                    da_run += kStageStep; db_run += kStageStep; ta_run += Cfg::A_TMEM_STRIDE; full_run += 8; empty_run += 8;
                 }
                 if (chain_ends) {
                     in_chain = 0;
-                    if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+                    if (++acc == Cfg::ACC_BUFS) { acc = 0; acc_phase ^= 1; }
                 } else {
                     ++in_chain;
                 }
@@ -1051,7 +1067,7 @@ d8k_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                 }
                 ptx::tc_fence_before_sync();
                 ptx::mbar_arrive(tempty_bar(acc));  // accumulator buffer free for the tile after next
-                if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+                if (++acc == Cfg::ACC_BUFS) { acc = 0; acc_phase ^= 1; }
             } else {
                 // one accumulation chain per CHUNK_KB k-blocks: add each finished chain into registers (round to nearest)
                 float accv[BN];
@@ -1064,18 +1080,30 @@ d8k_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                     if (!ok) break;
                     ptx::tc_fence_after_sync();
                     const uint32_t taddr = tmem_base + acc * Cfg::ACC_COLS + (static_cast<uint32_t>(quarter * 32) << 16);
+                    if constexpr (Cfg::DUAL) {  // 16 columns at a time: two CTAs per SM leave 96 registers per thread
 #pragma unroll
-                    for (int c = 0; c < Cfg::ACC_COLS / 32; ++c) {  // STACK: the second half of the columns holds the A_hi B_lo terms
-                        uint32_t r[32];
-                        __syncwarp();
-                        ptx::tmem_ld_32x32(taddr + c * 32, r);
-                        ptx::tmem_ld_wait();
+                        for (int c = 0; c < Cfg::ACC_COLS / 16; ++c) {
+                            uint32_t r[16];
+                            __syncwarp();
+                            ptx::tmem_ld_32x16(taddr + c * 16, r);
+                            ptx::tmem_ld_wait();
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) accv[(c % (BN / 32)) * 32 + i] += __uint_as_float(r[i]);
+                            for (int i = 0; i < 16; ++i) accv[(c % (BN / 16)) * 16 + i] += __uint_as_float(r[i]);
+                        }
+                    } else {
+#pragma unroll
+                        for (int c = 0; c < Cfg::ACC_COLS / 32; ++c) {  // STACK: the second half of the columns holds the A_hi B_lo terms
+                            uint32_t r[32];
+                            __syncwarp();
+                            ptx::tmem_ld_32x32(taddr + c * 32, r);
+                            ptx::tmem_ld_wait();
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) accv[(c % (BN / 32)) * 32 + i] += __uint_as_float(r[i]);
+                        }
                     }
                     ptx::tc_fence_before_sync();
                     ptx::mbar_arrive(tempty_bar(acc));
-                    if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+                    if (++acc == Cfg::ACC_BUFS) { acc = 0; acc_phase ^= 1; }
                 }
                 if (!ok) break;
 #pragma unroll
@@ -1175,7 +1203,7 @@ d8k_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                 if constexpr (Cfg::ATMEM) {
                     // A: this thread owns tile row 32 (warp % 4) + lane, the tensor-memory lane its warp may write
                     const int q = warp & 3;
-                    uint32_t hi[32], lo[32];
+                    uint32_t hi[32];
                     if constexpr (!Cfg::A_MN) {
                         // HALO: the row sits in the patch at its pixel's raster position shifted by the tap; else in the stage
                         const int row = Cfg::HALO ? prow0 + q * 32 + lane : q * 32 + lane;
@@ -1195,14 +1223,15 @@ d8k_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
 #pragma unroll
                         for (int k = 0; k < 32; ++k) hi[k] = ptx::ld_shared_b32(base + swz<true>(k, c16));
                     }
+                    const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + Cfg::A_TMEM_COL0 + stage * Cfg::A_TMEM_STRIDE;
+                    // the store takes its operands when it issues: the registers are reused for lo
+                    if constexpr (!Cfg::ALO) ptx::tmem_st_32x32(taddr, hi);
 #pragma unroll
                     for (int i = 0; i < 32; ++i) {
                         float d = __uint_as_float(hi[i]) - __uint_as_float(hi[i] & 0xffffe000u);
-                        lo[i] = (__float_as_uint(d) + 0x1000u) & 0xffffe000u;
+                        hi[i] = (__float_as_uint(d) + 0x1000u) & 0xffffe000u;
                     }
-                    const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + Cfg::A_TMEM_COL0 + stage * (2 * BK);
-                    ptx::tmem_st_32x32(taddr, hi);
-                    ptx::tmem_st_32x32(taddr + BK, lo);
+                    ptx::tmem_st_32x32(taddr + (Cfg::ALO ? 0 : BK), hi);
                     uint4 vb[B_CHUNKS];
                     const uint32_t b0 = stage_b(stage) + 16u * tid;
 #pragma unroll

@@ -517,6 +517,7 @@ int run_gemm(Ctx* ctx, const GemmProblem& g) {
     std::memset(&ta, 0, sizeof(ta));
     std::memset(&tb, 0, sizeof(tb));
     GemmLaunchFn fn = nullptr;
+    bool dual = false;  // two CTAs per SM (fp32, A in tensor memory)
     if (pl.pair) {
         if (!make_pair_map(&ta, g.a, g.M, g.K) || !make_pair_map(&tb, g.b, g.N, g.K)) return fail(2, "gemm: cuTensorMapEncodeTiled (4-D) failed");
         fn = lookup_f16_pair(g.a.mn, g.b.mn);
@@ -544,6 +545,19 @@ int run_gemm(Ctx* ctx, const GemmProblem& g) {
         if (!build(&ta, g.a, pl.a_tma, g.M, kBM, &p.a_chunked) || !build(&tb, g.b, pl.b_tma, g.N, pl.bn, &p.b_chunked))
             return fail(2, "gemm: cuTensorMapEncode failed");
         fn = pl.f32 ? lookup_f32_tma(g.a.mn, g.b.mn, pl.bn, env_int("D8K_F32_ATMEM", 1) != 0) : lookup_f16_tma(g.a.mn, g.b.mn, pl.bn);
+        if (pl.f32 && pl.bn == 64 && !g.a.halo && env_int("D8K_F32_ATMEM", 1)) {
+            // Two CTAs per SM (GemmCfg::DUAL) when there is more than one tile per SM and no split: the second CTA's MMAs fill
+            // the tensor pipe while the first one's single-thread roles go round their barriers.  With a split, or with
+            // fewer work items than SMs, a CTA is alone on its SM anyway and the deeper single-CTA pipeline is faster
+            // (measured on twenty-seven shapes).  Mode 2 (three stages, A's hi image read from shared memory) wins on long
+            // accumulation loops, mode 1 (A entirely in tensor memory) on short ones.  D8K_F32_DUAL = 0 / 1 / 2 overrides.
+            int mode = env_int("D8K_F32_DUAL", -1);
+            if (mode < 0) mode = (pl.splits == 1 && p.total_work > ctx->num_sms) ? (pl.total_kb > 8 ? 2 : 1) : 0;
+            if (mode == 1 || mode == 2) {
+                fn = lookup_f32_dual(g.a.mn, g.b.mn, mode);
+                dual = true;
+            }
+        }
         if (g.a.halo) {
             fn = lookup_f32_halo(g.b.mn);
             p.halo_wp = g.a.halo_wp;
@@ -564,6 +578,7 @@ int run_gemm(Ctx* ctx, const GemmProblem& g) {
         if (ce != cudaSuccess) return fail(2, std::string("gemm: cudaMemsetAsync: ") + cudaGetErrorString(ce));
     }
     int grid = p.total_work < ctx->num_sms ? p.total_work : ctx->num_sms;
+    if (dual) grid = p.total_work < 2 * ctx->num_sms ? p.total_work : 2 * ctx->num_sms;
     if (pl.pair) grid = p.total_work < ctx->num_sms / 2 ? p.total_work : ctx->num_sms / 2;  // pairs
     cudaError_t e = fn(grid, ctx->stream, ta, tb, p);
     if (e != cudaSuccess) return fail(2, std::string("gemm: launch failed: ") + cudaGetErrorString(e));
@@ -574,6 +589,7 @@ int run_gemm(Ctx* ctx, const GemmProblem& g) {
         os << (pl.f32 ? "f32 " : "f16 ") << (pl.pair ? "pair" : pl.tma ? "tma" : "gather");
         if (pl.tma && !pl.pair) os << " a=" << kModes[pl.a_tma] << " b=" << kModes[pl.b_tma];
         os << " bn=" << (pl.pair ? 256 : pl.bn) << " splits=" << pl.splits << " grid=" << grid;
+        if (dual) os << " dual";
         if (pl.pair) os << " raster=" << (p.raster_n ? "n" : "m") << p.raster_group << " l2=" << p.l2_a << p.l2_b;
         set_last_kernel(os.str());
     }

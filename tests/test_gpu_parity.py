@@ -704,3 +704,61 @@ def test_halo_patches_give_the_same_results(ctx, restated, monkeypatch, case):
         check(ctx, g, wnt, F32_TOL, name)
     if xs[0] == 16:  # enough tiles for every SM: the halo form is what ran (smaller problems keep the split contraction)
         assert "halo" in used, used
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("case", [("conv", (8, 56, 56, 64), (64, 3, 3, 64), True, (1, 1), (1, 1)), ("conv", (16, 40, 40, 32), (128, 1, 1, 32), True, (1, 1), (1, 1)),
+                                  ("matmul", (1, 4096, 512), (1, 512, 512)), ("matmul", (48, 256, 96), (1, 96, 128))])
+def test_two_ctas_per_sm_give_the_same_bits(ctx, restated, monkeypatch, case):
+    """fp32 launches with more tiles than SMs and no split run two CTAs per SM (half the stages, one accumulator buffer and one
+    converter group each).  The accumulation order does not change, so every result equals the single-CTA kernel's bit for bit -
+    both forms of the paired kernel (A entirely in tensor memory; only its lo image there) - and the oracle within the fp32 bar."""
+    kind = case[0]
+    if kind == "matmul":
+        x, y = cases.normal(81, case[1], 0.5), cases.normal(82, case[2], 0.5)
+        X, Y = dev(x), dev(y)
+        dz = cases.normal(83, (max(case[1][0], case[2][0]), case[1][1], case[2][2]))
+        DZ = dev(dz)
+
+        def run():
+            DX, DY = torch.zeros_like(X), torch.zeros_like(Y)
+            Z = ctx.matmul_forward(X, Y)
+            used = ctx.last_kernel()
+            ctx.matmul_grad_x(X, DX, Y, DZ)
+            ctx.matmul_grad_y(X, Y, DY, DZ)
+            return used, (Z, DX, DY)
+        oracle_args, runner = (x, y, dz, np.zeros(case[1], np.float32), np.zeros(case[2], np.float32)), Runner(ctx, restated, "matmul", None)
+    else:
+        xs, ws, cov, st, dil = case[1:]
+        x, w = cases.uniform(84, xs), cases.normal(85, ws, 0.25)
+        X, W = dev(x), dev(w)
+        meta = (cov, st, dil)
+        shp = ctx.conv2d_out_shape(X, W, *meta)
+        dz = cases.normal(86, tuple(shp))
+        DZ = dev(dz)
+
+        def run():
+            DX, DW = torch.zeros_like(X), torch.zeros_like(W)
+            Z = ctx.conv2d_forward(X, W, *meta)
+            used = ctx.last_kernel()
+            ctx.conv2d_grad_x(X, DX, W, DZ, *meta)
+            ctx.conv2d_grad_y(X, W, DW, DZ, *meta)
+            return used, (Z, DX, DW)
+        oracle_args, runner = (x, w, dz, np.zeros(xs, np.float32), np.zeros(ws, np.float32)), Runner(ctx, restated, "conv", meta)
+    monkeypatch.setenv("D8K_F32_DUAL", "0")
+    used0, single = run()
+    assert "dual" not in used0, used0
+    monkeypatch.delenv("D8K_F32_DUAL")
+    used, auto = run()
+    assert "dual" in used, used
+    for mode in ("1", "2"):
+        monkeypatch.setenv("D8K_F32_DUAL", mode)
+        usedm, forced = run()
+        assert "dual" in usedm, usedm
+        for name, a, b in zip(("z", "dx", "dy"), forced, single):
+            assert torch.equal(a, b), (mode, name)
+    for name, a, b in zip(("z", "dx", "dy"), auto, single):
+        assert torch.equal(a, b), name
+    for name, g, wnt in zip(("z", "dx", "dy"), auto, runner.cpu(*oracle_args)):
+        check(ctx, g, wnt, F32_TOL, name)
+    assert ctx.status() == 0
