@@ -65,7 +65,7 @@ class NvmlSampler:
 
     def __init__(self, torch, index, period_s=0.002):
         self.period_s, self.samples, self.stop_flag, self.thread, self.handle, self.nvml = period_s, [], False, None, None, None
-        self.max_mhz = None
+        self.max_mhz, self.error = None, None
         try:
             import pynvml
             pynvml.nvmlInit()
@@ -73,8 +73,8 @@ class NvmlSampler:
             self.handle = pynvml.nvmlDeviceGetHandleByUUID(uuid if uuid.startswith("GPU-") else "GPU-" + uuid)
             self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(self.handle, pynvml.NVML_CLOCK_SM))
             self.nvml = pynvml
-        except Exception:
-            self.handle = None
+        except Exception as exc:
+            self.handle, self.error = None, repr(exc)[:200]
 
     def available(self):
         return self.handle is not None
@@ -85,11 +85,20 @@ class NvmlSampler:
         while not self.stop_flag:
             try:
                 mhz = n.nvmlDeviceGetClockInfo(h, n.NVML_CLOCK_SM)
-                mask = reasons_fn(h)
+            except Exception as exc:  # without the clock there is no sample; keep the reason for the report
+                self.error = repr(exc)[:200]
+                time.sleep(self.period_s)
+                continue
+            mask, watts = 0, None
+            try:
+                mask = int(reasons_fn(h))
+            except Exception as exc:
+                self.error = repr(exc)[:200]
+            try:
                 watts = n.nvmlDeviceGetPowerUsage(h) / 1000.0
-                self.samples.append((time.perf_counter(), float(mhz), int(mask), watts))
-            except Exception:
-                pass
+            except Exception as exc:
+                self.error = repr(exc)[:200]
+            self.samples.append((time.perf_counter(), float(mhz), mask, watts))
             time.sleep(self.period_s)
 
     def start(self):
@@ -105,19 +114,20 @@ class NvmlSampler:
     def report(self, t0, t1):
         inside = [s for s in self.samples if t0 <= s[0] <= t1]
         if not inside:
-            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": ["no NVML sample inside the timed region"], "samples": 0}
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": ["no NVML sample inside the timed region"], "samples": 0,
+                    "samples_outside": len(self.samples), "error": self.error}
         mhz = [s[1] for s in inside]
         mask = 0
         for s in inside:
             mask |= s[2]
         return {"sm_mhz": statistics.median(mhz), "sm_mhz_min": min(mhz), "sm_mhz_max": max(mhz), "sm_max_mhz": self.max_mhz,
                 "reasons": [name for name, bit in self.REASONS if mask & bit], "samples": len(inside),
-                "power_w_median": statistics.median(s[3] for s in inside),
+                "power_w_median": statistics.median([s[3] for s in inside if s[3] is not None] or [0.0]),
                 "source": "NVML queries from this process every %g ms; only samples inside the timed region are counted" % (self.period_s * 1e3)}
 
 
 class SmiSampler:
-    """Fallback when NVML cannot be loaded: nvidia-smi polled every 100 ms (too coarse to resolve a short region)."""
+    """Fallback when NVML cannot be loaded or returns nothing: nvidia-smi asked for a line every 20 ms."""
 
     FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
@@ -128,7 +138,7 @@ class SmiSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.FIELDS,
-                                          "--format=csv,noheader,nounits", "-lms", "100"], stdout=subprocess.PIPE, text=True)
+                                          "--format=csv,noheader,nounits", "-lms", "20"], stdout=subprocess.PIPE, text=True)
             threading.Thread(target=self._read, daemon=True).start()
         except OSError:
             self.proc = None
@@ -163,7 +173,7 @@ class SmiSampler:
                 if v.lower().startswith("active"):
                     reasons.add(name)
         return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "reasons": sorted(reasons), "samples": len(sm), "source": "nvidia-smi -lms 100 (NVML could not be loaded)"}
+                "reasons": sorted(reasons), "samples": len(sm), "source": "nvidia-smi -lms 20 (the in-process NVML queries gave no sample)"}
 
 
 # ------------------------------------------------------------------------------------------------ CPU reference arm
@@ -677,24 +687,37 @@ def run_gpu_arm(args):
         raise SystemExit("kernel status non-zero after warm-up")
     # Pre-heat: the same step, untimed, for about `--preheat` seconds, so that the timed region runs at the clock the power
     # limit settles on rather than at the boost clock of a cold start.  Every rank runs the same number of steps.
+    # The clock sampler starts before the pre-heat, so that it is known to deliver before the timed region begins.
+    sampler = None
+    if rank == 0 and not args.profile:
+        sampler = NvmlSampler(torch, local_rank)
+        sampler.start()
     preheat_steps, preheat_s = 0, 0.0
     if args.preheat > 0 and not args.profile:
-        warm_ms = max_over_ranks(w0.elapsed_time(w1) / max(1, args.warmup))
-        preheat_steps = max(1, int(math.ceil(args.preheat * 1e3 / max(warm_ms, 0.1))))
         th = time.perf_counter()
-        for _ in range(preheat_steps):
+        # a first chunk, timed, tells how many steps fill the rest of the pre-heat (the warm-up steps carry first-call costs)
+        chunk = 20
+        c0, c1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        c0.record()
+        for _ in range(chunk):
+            mlp.step(step_dist)
+        mlp.drain()
+        c1.record()
+        torch.cuda.synchronize()
+        chunk_ms = max_over_ranks(c0.elapsed_time(c1) / chunk)
+        preheat_steps = chunk + max(0, int(math.ceil(args.preheat * 1e3 / max(chunk_ms, 0.1))) - chunk)
+        for _ in range(preheat_steps - chunk):
             mlp.step(step_dist)
         mlp.drain()
         barrier()
         preheat_s = time.perf_counter() - th
+    fallback_sampler = None
+    if sampler is not None and (not sampler.available() or (args.preheat > 0 and not sampler.samples)):
+        fallback_sampler = SmiSampler(local_rank)  # NVML absent, or it delivered nothing during the pre-heat
+        fallback_sampler.start()
+        time.sleep(0.3)
 
     # ---- device-resident timed region
-    sampler = None
-    if rank == 0 and not args.profile:
-        sampler = NvmlSampler(torch, local_rank)
-        if not sampler.available():
-            sampler = SmiSampler(local_rank)
-        sampler.start()
     launches0 = ctx.launch_count()
     barrier()
     host_t0 = time.perf_counter()
@@ -712,6 +735,12 @@ def run_gpu_arm(args):
     if sampler is not None:
         sampler.stop()
         clocks = sampler.report(host_t0, host_t1)
+        if fallback_sampler is not None:
+            fallback_sampler.stop()
+            if not clocks.get("samples"):
+                nvml_report = clocks
+                clocks = fallback_sampler.report(host_t0, host_t1)
+                clocks["nvml"] = {k: nvml_report.get(k) for k in ("samples_outside", "error")}
     my_ms = t0.elapsed_time(t1) / args.steps
     ms_step = max_over_ranks(t0.elapsed_time(t1)) / args.steps
     gemm_ms = [a.elapsed_time(b) for a, b in mlp.gemm_events]
