@@ -28,7 +28,10 @@ static GemmLaunchFn pick_dual(bool a_mn, bool b_mn) {
     if (a_mn && !b_mn) return launch_cfg<GemmCfg<true, true, false, 64, STAGES, false, true, false, MODE>>;
     return launch_cfg<GemmCfg<true, true, true, 64, STAGES, false, true, false, MODE>>;
 }
-GemmLaunchFn lookup_f32_dual(bool a_mn, bool b_mn, int mode) { return mode == 2 ? pick_dual<2, 3>(a_mn, b_mn) : pick_dual<1, 2>(a_mn, b_mn); }
+GemmLaunchFn lookup_f32_dual(bool a_mn, bool b_mn, int mode) {
+    if (mode == 4) return pick_dual<4, 4>(a_mn, b_mn);  // one CTA per SM with twin TMA and MMA threads (GemmCfg::TWIN)
+    return mode == 2 ? pick_dual<2, 3>(a_mn, b_mn) : pick_dual<1, 2>(a_mn, b_mn);
+}
 
 GemmLaunchFn lookup_f32_tma(bool a_mn, bool b_mn, int bn, bool a_in_tmem) {
     if (!a_mn && !b_mn) return pick<false, false>(bn, a_in_tmem);

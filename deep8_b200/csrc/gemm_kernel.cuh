@@ -239,8 +239,13 @@ struct GemmCfg {
     // those gaps, and its main loop runs while the first CTA's epilogue drains the one accumulator buffer.
     // DUAL_ == 2 (ALO): only A's lo image goes to tensor memory; the raw tile in shared memory serves as the hi image, read
     // by the wide MMA through a descriptor.  Half the tensor-memory columns per stage, so each CTA holds three stages.
-    static constexpr bool DUAL = DUAL_ != 0;
+    static constexpr bool DUAL = DUAL_ == 1 || DUAL_ == 2;
     static constexpr bool ALO = DUAL_ == 2;
+    // DUAL_ == 4 (TWIN): one CTA per SM with a second TMA-issuing thread (one issues A's boxes, the other B's) and a second
+    // MMA-issuing thread (the two take k-blocks in turn, ordered by a token, so the sums are formed in the same order).  A
+    // k-block costs the single MMA thread about as long in barrier traffic and tcgen05.commit as in its eight MMAs, and the
+    // single producer as long again; with two threads each, one thread's bookkeeping runs behind the other's issue.
+    static constexpr bool TWIN = DUAL_ == 4;
     static constexpr int A_TMEM_STRIDE = ALO ? BK : 2 * BK;     // tensor-memory columns of A per stage
     static constexpr int ACC_BUFS = DUAL ? 1 : 2;
     static constexpr int CTAS_PER_SM = DUAL ? 2 : 1;
@@ -268,7 +273,10 @@ struct GemmCfg {
     // write the lo image, tf32(v - trunc(v)), beside it - shared memory to shared memory, no global-load latency.
     static constexpr bool CONVERT = F32 && !GATHER;
     static constexpr bool HELPERS = GATHER || CONVERT;  // warps beyond the MMA warp exist
-    static constexpr int THREADS = HELPERS ? 32 * (LOADER_WARP0 + LOADER_WARPS * LOADER_GROUPS) : 32 * 6;
+    static constexpr int BASE_WARPS = HELPERS ? LOADER_WARP0 + LOADER_WARPS * LOADER_GROUPS : 6;
+    static constexpr int PRODUCER_B_WARP = BASE_WARPS, MMA2_WARP = BASE_WARPS + 1;  // TWIN only
+    static constexpr int THREADS = 32 * (BASE_WARPS + (TWIN ? 2 : 0));
+    static_assert(!TWIN || (CONVERT && !HALO_), "the twin roles belong to the fp32 TMA kernels");
     static constexpr int BAR_BYTES = 256;
     static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + PATCH_SLOTS * PATCH_BYTES + BAR_BYTES + 1024;  // + slack to align the ring to 1024
     static_assert(BN % 16 == 0 && BN >= 16 && BN <= 256, "UMMA N");
@@ -806,7 +814,8 @@ d8k_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     auto patch_full = [&](int i) { return bar_base + 8u * (3 * STAGES + 5 + i); };                     // HALO: the box has landed
     auto patch_empty = [&](int i) { return bar_base + 8u * (3 * STAGES + 5 + Cfg::PATCH_SLOTS + i); };  // HALO: every converter is done with it
     auto patch_addr = [&](int i) { return patch_base + static_cast<uint32_t>(i) * Cfg::PATCH_BYTES; };
-    static_assert(8 * (3 * Cfg::STAGES + 5 + 2 * Cfg::PATCH_SLOTS) <= Cfg::BAR_BYTES, "barrier block");
+    auto turn_bar = [&](int w) { return bar_base + 8u * (3 * STAGES + 5 + 2 * Cfg::PATCH_SLOTS + w); };  // TWIN: MMA thread w may issue
+    static_assert(8 * (3 * Cfg::STAGES + 5 + 2 * Cfg::PATCH_SLOTS + 2) <= Cfg::BAR_BYTES, "barrier block");
 
     __shared__ volatile int s_abort;
     __shared__ int s_last;
@@ -819,8 +828,10 @@ d8k_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         for (int s = 0; s < STAGES; ++s) {
             ptx::mbar_init(full_bar(s), Cfg::HELPERS ? 32 * Cfg::LOADER_WARPS : 1);
             ptx::mbar_init(empty_bar(s), 1);
-            ptx::mbar_init(raw_bar(s), 1);
+            ptx::mbar_init(raw_bar(s), Cfg::TWIN ? 2 : 1);
         }
+        ptx::mbar_init(turn_bar(0), 1);
+        ptx::mbar_init(turn_bar(1), 1);
         for (int i = 0; i < Cfg::PATCH_SLOTS; ++i) {
             ptx::mbar_init(patch_full(i), 1);
             ptx::mbar_init(patch_empty(i), 32 * Cfg::LOADER_WARPS * Cfg::LOADER_GROUPS);
@@ -830,6 +841,7 @@ d8k_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             ptx::mbar_init(tempty_bar(a), 32 * Cfg::EPI_WARPS);
         }
         ptx::fence_mbar_init();
+        if (Cfg::TWIN) ptx::mbar_arrive(turn_bar(0));  // the first k-block has no predecessor: thread 0's first turn is open
     }
     if (warp == Cfg::MMA_WARP) {
         ptx::tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
@@ -848,8 +860,10 @@ d8k_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     auto stage_a = [&](int s) { return smem_base + s * Cfg::STAGE_BYTES; };
     auto stage_b = [&](int s) { return smem_base + s * Cfg::STAGE_BYTES + Cfg::A_PARTS * Cfg::A_BYTES; };
 
-    if (!Cfg::GATHER && warp == Cfg::PRODUCER_WARP) {
+    if (!Cfg::GATHER && (warp == Cfg::PRODUCER_WARP || (Cfg::TWIN && warp == Cfg::PRODUCER_B_WARP))) {
         // ============================================================================ TMA producer
+        // TWIN: this code runs in two warps; the first issues A's boxes, the second B's, each announcing its own bytes
+        const bool do_a = !Cfg::TWIN || warp == Cfg::PRODUCER_WARP, do_b = !Cfg::TWIN || warp != Cfg::PRODUCER_WARP;
         int stage = 0;
         uint32_t phase = 0;
         bool ok = true;
@@ -907,21 +921,22 @@ d8k_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                     int k0 = Cfg::HALO ? k0_halo : kb * BK;
                     // CONVERT: the boxes fill the hi halves of the stage and complete on the raw barrier
                     const uint32_t bar = Cfg::CONVERT ? raw_bar(stage) : full_bar(stage);
-                    ptx::mbar_arrive_expect_tx(bar, Cfg::HALO ? Cfg::B_BYTES : Cfg::CONVERT ? Cfg::A_BYTES + Cfg::B_BYTES : Cfg::STAGE_BYTES);
+                    if constexpr (Cfg::TWIN) ptx::mbar_arrive_expect_tx(bar, do_a ? Cfg::A_BYTES : Cfg::B_BYTES);
+                    else ptx::mbar_arrive_expect_tx(bar, Cfg::HALO ? Cfg::B_BYTES : Cfg::CONVERT ? Cfg::A_BYTES + Cfg::B_BYTES : Cfg::STAGE_BYTES);
                     if constexpr (!Cfg::HALO)
-                        produce_operand<Cfg, Cfg::A_MN, kBM>(p.a_tma, p.a_chunked, p.a, &tmA, stage_a(stage), bar, k0, it.m0, b % p.a_batch_mod);
-                    produce_operand<Cfg, Cfg::B_MN, BN>(p.b_tma, p.b_chunked, p.b, &tmB, stage_b(stage), bar, k0, it.n0, b % p.b_batch_mod);
+                        if (do_a) produce_operand<Cfg, Cfg::A_MN, kBM>(p.a_tma, p.a_chunked, p.a, &tmA, stage_a(stage), bar, k0, it.m0, b % p.a_batch_mod);
+                    if (do_b) produce_operand<Cfg, Cfg::B_MN, BN>(p.b_tma, p.b_chunked, p.b, &tmB, stage_b(stage), bar, k0, it.n0, b % p.b_batch_mod);
                 }
                 __syncwarp();
                 if (++stage == STAGES) { stage = 0; phase ^= 1; }
             }
         }
-        if (timed && lane == 0) {
+        if (timed && lane == 0 && warp == Cfg::PRODUCER_WARP) {
             p.prof[blockIdx.x * 16 + 0] = clock64() - t_begin;
             p.prof[blockIdx.x * 16 + 1] = w_empty;
             p.prof[blockIdx.x * 16 + 2] = w_patch;
         }
-    } else if (warp == Cfg::MMA_WARP) {
+    } else if (warp == Cfg::MMA_WARP || (Cfg::TWIN && warp == Cfg::MMA2_WARP)) {
         // ============================================================================ MMA issuer
         // A from tensor memory is always one row per lane, whatever the stored layout was
         constexpr uint32_t idesc = ptx::make_idesc(Cfg::F32 ? 2u : 0u, Cfg::A_MN && !Cfg::ATMEM, Cfg::B_MN, kBM, BN);
@@ -952,22 +967,34 @@ d8k_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         const bool timed = p.prof != nullptr;
         long long w_full = 0, w_tmem = 0;
         const long long t_begin = timed ? clock64() : 0;
+        // TWIN: both MMA warps walk every k-block to keep the running state; warp `me` issues the k-blocks t with t % 2 == me
+        const int me = (Cfg::TWIN && warp != Cfg::MMA_WARP) ? 1 : 0;
+        int t = 0;
+        uint32_t my_turns = 0;
         for (int w = blockIdx.x; ok && w < p.total_work; w += gridDim.x) {
             WorkItem it = decode_work(p, w, BN);
             uint32_t d_tmem = 0;
             int in_chain = 0;
-            for (int kk = it.kb_begin; kk < it.kb_end; ++kk) {
-                if (in_chain == 0) {  // a new accumulation chain needs a drained accumulator buffer
+            for (int kk = it.kb_begin; kk < it.kb_end; ++kk, ++t) {
+                const bool mine = !Cfg::TWIN || (t & 1) == me;
+                if (in_chain == 0) d_tmem = tmem_base + acc * Cfg::ACC_COLS;
+                if (mine && in_chain == 0) {  // a new accumulation chain needs a drained accumulator buffer
                     ok = wait_bar_timed(tempty_bar(acc), acc_phase ^ 1, &s_abort, p.status, (kRoleMma << 8) | 2, timed, &w_tmem);
                     if (!ok) break;
                     ptx::tc_fence_after_sync();
-                    d_tmem = tmem_base + acc * Cfg::ACC_COLS;
                 }
-                ok = wait_bar_timed(full_run, phase, &s_abort, p.status, (kRoleMma << 8) | 1, timed, &w_full);
-                if (!ok) break;
-                ptx::tc_fence_after_sync();
+                if (mine) {
+                    ok = wait_bar_timed(full_run, phase, &s_abort, p.status, (kRoleMma << 8) | 1, timed, &w_full);
+                    if (!ok) break;
+                    if constexpr (Cfg::TWIN) {  // the other thread has issued the k-block before this one
+                        ok = wait_bar(turn_bar(me), my_turns & 1, &s_abort, p.status, (kRoleMma << 8) | 5);
+                        if (!ok) break;
+                        ++my_turns;
+                    }
+                    ptx::tc_fence_after_sync();
+                }
                 const bool chain_ends = (kk + 1 == it.kb_end) || (Cfg::CHUNK_KB > 0 && in_chain + 1 == Cfg::CHUNK_KB);
-                if (lane == 0) {
+                if (mine && lane == 0) {
 #pragma unroll
                     for (int s = 0; s < Cfg::KSTEPS; ++s) {
                         // a k-step moves the start address by a few 16-byte units, far below the 14-bit field's range: a plain add
@@ -1000,7 +1027,12 @@ d8k_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                             ptx::mma_f16(d_tmem, da, db, idesc, accumulate);
                         }
                     }
+                    if constexpr (Cfg::TWIN) {  // pass the token before this thread's own bookkeeping
+                        ptx::tc_fence_before_sync();
+                        ptx::mbar_arrive(turn_bar(me ^ 1));
+                    }
                     ptx::tc_commit(empty_run);  // the stage may be refilled once these MMAs have read it
+                    // the pipe completes MMAs in issue order: this commit also covers the other thread's earlier k-blocks of the chain
                     if (chain_ends) ptx::tc_commit(tfull_bar(acc));
                 }
                 __syncwarp();
@@ -1019,7 +1051,7 @@ d8k_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                 }
             }
         }
-        if (timed && lane == 0) {
+        if (timed && lane == 0 && warp == Cfg::MMA_WARP) {
             p.prof[blockIdx.x * 16 + 3] = clock64() - t_begin;
             p.prof[blockIdx.x * 16 + 4] = w_full;
             p.prof[blockIdx.x * 16 + 5] = w_tmem;

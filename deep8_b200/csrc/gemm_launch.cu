@@ -518,6 +518,7 @@ int run_gemm(Ctx* ctx, const GemmProblem& g) {
     std::memset(&tb, 0, sizeof(tb));
     GemmLaunchFn fn = nullptr;
     bool dual = false;  // two CTAs per SM (fp32, A in tensor memory)
+    bool twin = false;  // one CTA per SM with twin TMA and MMA threads
     if (pl.pair) {
         if (!make_pair_map(&ta, g.a, g.M, g.K) || !make_pair_map(&tb, g.b, g.N, g.K)) return fail(2, "gemm: cuTensorMapEncodeTiled (4-D) failed");
         fn = lookup_f16_pair(g.a.mn, g.b.mn);
@@ -547,15 +548,19 @@ int run_gemm(Ctx* ctx, const GemmProblem& g) {
         fn = pl.f32 ? lookup_f32_tma(g.a.mn, g.b.mn, pl.bn, env_int("D8K_F32_ATMEM", 1) != 0) : lookup_f16_tma(g.a.mn, g.b.mn, pl.bn);
         if (pl.f32 && pl.bn == 64 && !g.a.halo && env_int("D8K_F32_ATMEM", 1)) {
             // Two CTAs per SM (GemmCfg::DUAL) when there is more than one tile per SM and no split: the second CTA's MMAs fill
-            // the tensor pipe while the first one's single-thread roles go round their barriers.  With a split, or with
-            // fewer work items than SMs, a CTA is alone on its SM anyway and the deeper single-CTA pipeline is faster
-            // (measured on twenty-seven shapes).  Mode 2 (three stages, A's hi image read from shared memory) wins on long
-            // accumulation loops, mode 1 (A entirely in tensor memory) on short ones.  D8K_F32_DUAL = 0 / 1 / 2 overrides.
+            // the tensor pipe while the first one's single-thread roles go round their barriers.  Mode 2 (three stages, A's hi
+            // image read from shared memory) wins on long accumulation loops, mode 1 (A entirely in tensor memory) on short
+            // ones.  With a split, or with fewer work items than SMs, a CTA is alone on its SM anyway: there the one-CTA kernel
+            // with twin TMA and MMA threads runs (mode 4, GemmCfg::TWIN; never slower than the single-thread roles of mode 0
+            // on twenty-seven measured shapes, up to 20 % faster).  D8K_F32_DUAL = 0 / 1 / 2 / 4 overrides.
             int mode = env_int("D8K_F32_DUAL", -1);
-            if (mode < 0) mode = (pl.splits == 1 && p.total_work > ctx->num_sms) ? (pl.total_kb > 8 ? 2 : 1) : 0;
+            if (mode < 0) mode = (pl.splits == 1 && p.total_work > ctx->num_sms) ? (pl.total_kb > 8 ? 2 : 1) : 4;
             if (mode == 1 || mode == 2) {
                 fn = lookup_f32_dual(g.a.mn, g.b.mn, mode);
                 dual = true;
+            } else if (mode == 4) {
+                fn = lookup_f32_dual(g.a.mn, g.b.mn, mode);
+                twin = true;
             }
         }
         if (g.a.halo) {
@@ -590,6 +595,7 @@ int run_gemm(Ctx* ctx, const GemmProblem& g) {
         if (pl.tma && !pl.pair) os << " a=" << kModes[pl.a_tma] << " b=" << kModes[pl.b_tma];
         os << " bn=" << (pl.pair ? 256 : pl.bn) << " splits=" << pl.splits << " grid=" << grid;
         if (dual) os << " dual";
+        if (twin) os << " twin";
         if (pl.pair) os << " raster=" << (p.raster_n ? "n" : "m") << p.raster_group << " l2=" << p.l2_a << p.l2_b;
         set_last_kernel(os.str());
     }

@@ -762,3 +762,33 @@ def test_two_ctas_per_sm_give_the_same_bits(ctx, restated, monkeypatch, case):
     for name, g, wnt in zip(("z", "dx", "dy"), auto, runner.cpu(*oracle_args)):
         check(ctx, g, wnt, F32_TOL, name)
     assert ctx.status() == 0
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("case", [("conv", (2, 20, 17, 64), (64, 3, 3, 64), True, (1, 1), (1, 1)), ("conv", (4, 14, 14, 96), (32, 4, 4, 96), False, (2, 2), (1, 1)),
+                                  ("deconv", (2, 6, 6, 64), (64, 5, 5, 64), True, (2, 2)), ("matmul", (1, 384, 1056), (1, 1056, 192)),
+                                  ("matmul", (3, 130, 64), (3, 64, 70))])
+def test_twin_issuing_threads_give_the_same_bits(ctx, restated, monkeypatch, case):
+    """fp32 launches that keep one CTA per SM (a split contraction, or fewer tiles than SMs) run with two TMA-issuing and two
+    MMA-issuing threads; a token orders the MMA threads, so the sums are formed in the same order as with one thread each and
+    every result equals that kernel's bit for bit."""
+    kind = case[0]
+    meta = None if kind == "matmul" else ((case[3], case[4], case[5]) if kind == "conv" else (case[3], case[4]))
+    x, w = cases.normal(91, case[1], 0.5), cases.normal(92, case[2], 0.25)
+    r = Runner(ctx, restated, kind, meta)
+    dz = cases.normal(93, r.zshape(x, w))
+    dx0, dw0 = cases.normal(94, case[1]), cases.normal(95, case[2])
+    monkeypatch.setenv("D8K_F32_DUAL", "0")
+    single = r.gpu(x, w, dz, dx0, dw0, torch.float32)
+    used0 = ctx.last_kernel()
+    monkeypatch.delenv("D8K_F32_DUAL")
+    auto = r.gpu(x, w, dz, dx0, dw0, torch.float32)
+    used = ctx.last_kernel()
+    assert "twin" not in used0 and "dual" not in used0, used0
+    if "tma" in used:  # shapes TMA cannot describe stay on the loader warps, which have no twin form
+        assert "twin" in used, used
+    for name, a, b in zip(("z", "dx", "dy"), auto, single):
+        assert torch.equal(a, b), name
+    for name, g, wnt in zip(("z", "dx", "dy"), auto, r.cpu(x, w, dz, dx0, dw0)):
+        check(ctx, g, wnt, F32_TOL, name)
+    assert ctx.status() == 0
