@@ -19,7 +19,8 @@ pinned host memory and Y copied back inside every step (plus the same copies wit
 interface); `roofline` is for the contraction kernel (tensor bound) against the measured cuBLAS bf16 peak of this pool;
 `contractions` and `ranks` say where the step's time went on every rank; `exchange_check` compares the exchanged gradients
 with the sum of the ranks' partial gradients; `cpu_baseline` is the reference's own CPU code on a row slice of the same
-workload; `aux` reports BASELINE configurations 1-4.  `--impl reference` times only that CPU code.
+workload; `aux` reports the four fp32 operator configurations (`--config 1..4`) and `hbm_kernels` the HBM-bound neighbours
+(matrix-vector products, Linear, AdamUpdate) against the measured copy bandwidth.  `--impl reference` times only that CPU code.
 """
 import argparse
 import json
@@ -499,7 +500,7 @@ def exchange_check(mlp, ctx, torch, dist, device, world, rank):
 
 
 def filter_gradient_exchange(n_cfg, ctx, ctx_side, side, torch, dist, device, world, rank):
-    """BASELINE configuration 3 (Conv2d) or 4 (DeConv2d) with the images sharded over the GPUs: each rank computes the
+    """Benchmark configuration 3 (Conv2d) or 4 (DeConv2d) with the images sharded over the GPUs: each rank computes the
     filter gradient of its images, the partial gradients are summed through PeerAllReduce (copy-engine reduce-scatter,
     fixed-order sum kernel, copy-engine all-gather - the filter is far too small for row blocks per owner), and rank 0
     compares the result with the CPU oracle on the whole batch.  Returns (ms per gradient + exchange, max rel error)."""
@@ -905,7 +906,7 @@ def run_gpu_arm(args):
                 except Exception as exc:  # the figure is auxiliary: its absence must not cost the line
                     line["e2e"]["cpp_api"] = {"error": str(exc)[:200]}
         if world == 1 and not args.no_aux:
-            # BASELINE configurations 1-4 with their own inputs: an auxiliary report, outside the headline's timed region
+            # benchmark configurations 1-4 with their own inputs: an auxiliary report, outside the headline's timed region
             line["aux"] = [run_small(ctx, torch, device, n, steps=20, warmup=3, half=False, with_cpu=not args.no_cpu) for n in (1, 2, 3, 4)]
             line["hbm_kernels"] = run_hbm_kernels(ctx, torch, device)
         print(json.dumps(line), flush=True)
@@ -976,7 +977,7 @@ def run_hbm_kernels(ctx, torch, dev, rows=16384, cols=16384):
 
 # ------------------------------------------------------------------------------------------------ configs 1-4 (fp32)
 def small_config_case(n):
-    """(name, x, w, dz, kind, meta, flop) of BASELINE configuration n in 1..4, inputs drawn as the configuration states
+    """(name, x, w, dz, kind, meta, flop) of benchmark configuration n in 1..4, inputs drawn as the configuration states
     (numpy Philox streams named by the configuration's seeds; the second operand of configurations 1 and 2 uses seed + 10)."""
     sys.path.insert(0, os.path.join(ROOT, "tests"))
     import cases
@@ -996,7 +997,7 @@ def small_config_case(n):
 
 
 def run_small(ctx, torch, dev, n, steps, warmup, half, with_cpu):
-    """BASELINE configuration n in 1..4 (fp32, 3xTF32): forward + gradient of x + gradient of y of ONE operator on one GPU,
+    """Benchmark configuration n in 1..4 (fp32, 3xTF32): forward + gradient of x + gradient of y of ONE operator on one GPU,
     timed with CUDA events with an L2 flush between iterations, checked against the oracle, with the reference's CPU
     code timed beside it.  Returns the report as a dict."""
     from oracle import pyoracle
@@ -1098,7 +1099,7 @@ def main():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--config", type=int, default=5, choices=[1, 2, 3, 4, 5], help="BASELINE configuration; 5 (default) is the benchmark "
+    ap.add_argument("--config", type=int, default=5, choices=[1, 2, 3, 4, 5], help="benchmark configuration; 5 (default) is the headline "
                     "line, 1-4 print an auxiliary fp32 report for one operator")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-aux", action="store_true", help="skip the auxiliary reports (configurations 1-4 on one GPU; the Conv2d/DeConv2d "

@@ -78,6 +78,7 @@ bool gemm_goes_through_tma(const Ctx* ctx, const GemmProblem& g);
 typedef cudaError_t (*GemmLaunchFn)(int grid, cudaStream_t stream, const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p);
 // one table per translation unit of instantiations; index [a_mn][b_mn][bn slot]
 GemmLaunchFn lookup_f16_tma(bool a_mn, bool b_mn, int bn);
+GemmLaunchFn lookup_f16_twin(bool a_mn, bool b_mn, int bn);  // lookup_f16_tma's tiles with twin issuing threads
 GemmLaunchFn lookup_f16_gather(bool a_mn, bool b_mn, int bn);
 GemmLaunchFn lookup_f32_gather(bool a_mn, bool b_mn, int bn);
 GemmLaunchFn lookup_f32_tma(bool a_mn, bool b_mn, int bn, bool a_in_tmem);

@@ -10,6 +10,21 @@ static GemmLaunchFn pick(int bn) {
     return nullptr;
 }
 
+// the same tiles with twin TMA-issuing and MMA-issuing threads (GemmCfg::TWIN)
+template <bool A_MN, bool B_MN>
+static GemmLaunchFn pick_twin(int bn) {
+    if (bn == 256) return launch_cfg<GemmCfg<false, A_MN, B_MN, 256, 4, false, false, false, 4>>;
+    if (bn == 128) return launch_cfg<GemmCfg<false, A_MN, B_MN, 128, 6, false, false, false, 4>>;
+    return nullptr;
+}
+
+GemmLaunchFn lookup_f16_twin(bool a_mn, bool b_mn, int bn) {
+    if (!a_mn && !b_mn) return pick_twin<false, false>(bn);
+    if (!a_mn && b_mn) return pick_twin<false, true>(bn);
+    if (a_mn && !b_mn) return pick_twin<true, false>(bn);
+    return pick_twin<true, true>(bn);
+}
+
 GemmLaunchFn lookup_f16_tma(bool a_mn, bool b_mn, int bn) {
     if (!a_mn && !b_mn) return pick<false, false>(bn);
     if (!a_mn && b_mn) return pick<false, true>(bn);

@@ -276,7 +276,7 @@ struct GemmCfg {
     static constexpr int BASE_WARPS = HELPERS ? LOADER_WARP0 + LOADER_WARPS * LOADER_GROUPS : 6;
     static constexpr int PRODUCER_B_WARP = BASE_WARPS, MMA2_WARP = BASE_WARPS + 1;  // TWIN only
     static constexpr int THREADS = 32 * (BASE_WARPS + (TWIN ? 2 : 0));
-    static_assert(!TWIN || (CONVERT && !HALO_), "the twin roles belong to the fp32 TMA kernels");
+    static_assert(!TWIN || (!GATHER && !HALO_), "the twin roles belong to the TMA kernels");
     static constexpr int BAR_BYTES = 256;
     static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + PATCH_SLOTS * PATCH_BYTES + BAR_BYTES + 1024;  // + slack to align the ring to 1024
     static_assert(BN % 16 == 0 && BN >= 16 && BN <= 256, "UMMA N");
@@ -826,7 +826,7 @@ d8k_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     if (threadIdx.x == 0) {
         s_abort = 0;
         for (int s = 0; s < STAGES; ++s) {
-            ptx::mbar_init(full_bar(s), Cfg::HELPERS ? 32 * Cfg::LOADER_WARPS : 1);
+            ptx::mbar_init(full_bar(s), Cfg::HELPERS ? 32 * Cfg::LOADER_WARPS : (Cfg::TWIN ? 2 : 1));
             ptx::mbar_init(empty_bar(s), 1);
             ptx::mbar_init(raw_bar(s), Cfg::TWIN ? 2 : 1);
         }

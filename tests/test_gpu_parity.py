@@ -792,3 +792,31 @@ def test_twin_issuing_threads_give_the_same_bits(ctx, restated, monkeypatch, cas
     for name, g, wnt in zip(("z", "dx", "dy"), auto, r.cpu(x, w, dz, dx0, dw0)):
         check(ctx, g, wnt, F32_TOL, name)
     assert ctx.status() == 0
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("case", [("conv", (4, 28, 28, 64), (128, 3, 3, 64), True, (1, 1), (1, 1)), ("matmul", (1, 1024, 512), (1, 512, 384)),
+                                  ("matmul", (5, 128, 192), (1, 192, 256))])
+def test_twin_issuing_threads_fp16_same_bits(ctx, restated, monkeypatch, case):
+    """The fp16 single-CTA kernels run with twin TMA-issuing and MMA-issuing threads too; D8K_F16_TWIN=0 is the form with one
+    thread each, and both give the same bits."""
+    kind = case[0]
+    meta = None if kind == "matmul" else (case[3], case[4], case[5])
+    h = lambda a: a.astype(np.float16).astype(np.float32)
+    x, w = h(cases.normal(96, case[1], 0.5)), h(cases.normal(97, case[2], 0.25))
+    r = Runner(ctx, restated, kind, meta)
+    dz = h(cases.normal(98, r.zshape(x, w)))
+    dx0, dw0 = h(cases.normal(99, case[1])), h(cases.normal(100, case[2]))
+    monkeypatch.setenv("D8K_F16_TWIN", "0")
+    single = r.gpu(x, w, dz, dx0, dw0, torch.float16)
+    assert "twin" not in ctx.last_kernel(), ctx.last_kernel()
+    monkeypatch.delenv("D8K_F16_TWIN")
+    twin = r.gpu(x, w, dz, dx0, dw0, torch.float16)
+    used = ctx.last_kernel()
+    if " tma " in used:
+        assert "twin" in used, used
+    for name, a, b in zip(("z", "dx", "dy"), twin, single):
+        assert torch.equal(a, b), name
+    for name, g, wnt in zip(("z", "dx", "dy"), twin, r.cpu(x, w, dz, dx0, dw0)):
+        check(ctx, g, wnt, F16_TOL, name)
+    assert ctx.status() == 0

@@ -130,7 +130,7 @@ def test_shape_rules(restated):
 
 
 def test_reference_rejects_28x28_deconv(reference):
-    """BASELINE's 16x28x28x128 DeConv2d output is not producible: the reference throws on it (deep8/src/math/DeConv2d.cpp:68)."""
+    """A 16x28x28x128 DeConv2d output (as benchmark configuration 4 was first stated) is not producible: the reference throws on it (deep8/src/math/DeConv2d.cpp:68)."""
     x = np.zeros((1, 14, 14, 4), np.float32)
     w = np.zeros((2, 4, 4, 4), np.float32)
     z = np.zeros((1, 28, 28, 2), np.float32)
