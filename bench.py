@@ -16,7 +16,7 @@ ranks' measured speeds (`--no-balance`: 8192 rows each).
 Prints ONE JSON line.  `value` is the aggregate TFLOP/s over all GPUs with inputs resident in HBM, after `--preheat` seconds
 of the same step, with NVML clock samples taken inside the timed region; `e2e` is the same metric with X and dY copied from
 pinned host memory and Y copied back inside every step (plus the same copies without kernels, and the step through the C++
-interface); `roofline` is for the contraction kernel (tensor bound) against the measured cuBLAS bf16 peak of this pool;
+interface, with synchronous feed / fetch and with its copies on Deep8::CopyStream); `roofline` is for the contraction kernel (tensor bound) against the measured cuBLAS bf16 peak of this pool;
 `contractions` and `ranks` say where the step's time went on every rank; `exchange_check` compares the exchanged gradients
 with the sum of the ranks' partial gradients; `cpu_baseline` is the reference's own CPU code on a row slice of the same
 workload; `aux` reports the four fp32 operator configurations (`--config 1..4`) and `hbm_kernels` the HBM-bound neighbours
@@ -900,11 +900,12 @@ def run_gpu_arm(args):
             if os.path.exists(exe):
                 del mlp
                 torch.cuda.empty_cache()
-                try:
-                    r = subprocess.run([exe, "10", str(M_PER_GPU)], capture_output=True, text=True, timeout=300)
-                    line["e2e"]["cpp_api"] = json.loads(r.stdout.strip().splitlines()[-1])
-                except Exception as exc:  # the figure is auxiliary: its absence must not cost the line
-                    line["e2e"]["cpp_api"] = {"error": str(exc)[:200]}
+                for key, extra in (("cpp_api", []), ("cpp_api_overlapped", ["overlap"])):
+                    try:
+                        r = subprocess.run([exe, "10", str(M_PER_GPU)] + extra, capture_output=True, text=True, timeout=300)
+                        line["e2e"][key] = json.loads(r.stdout.strip().splitlines()[-1])
+                    except Exception as exc:  # the figure is auxiliary: its absence must not cost the line
+                        line["e2e"][key] = {"error": str(exc)[:200]}
         if world == 1 and not args.no_aux:
             # benchmark configurations 1-4 with their own inputs: an auxiliary report, outside the headline's timed region
             line["aux"] = [run_small(ctx, torch, device, n, steps=20, warmup=3, half=False, with_cpu=not args.no_cpu) for n in (1, 2, 3, 4)]

@@ -1167,7 +1167,14 @@ void EagerExecutor::backwardNode(Node* n, std::unordered_set<Node*>& done) {
 }
 
 void EagerExecutor::backward(Variable* last, const void* hostGradient, bool clearInterim) {
-    DEEP8_ARGUMENT_CHECK(nullptr != last && last->updateGradient && nullptr != hostGradient, "the last Variable needs a gradient");
+    backwardFrom(last, hostGradient, nullptr, clearInterim);
+}
+void EagerExecutor::backward(Variable* last, const Tensor& deviceGradient, bool clearInterim) {
+    backwardFrom(last, nullptr, &deviceGradient, clearInterim);
+}
+void EagerExecutor::backwardFrom(Variable* last, const void* hostGradient, const Tensor* deviceGradient, bool clearInterim) {
+    DEEP8_ARGUMENT_CHECK(nullptr != last && last->updateGradient && (nullptr != hostGradient || nullptr != deviceGradient),
+                         "the last Variable needs a gradient");
     flush();
     bfs(last, [this](Node* n) {
         if (NodeType::Variable != n->type) return;
@@ -1175,7 +1182,12 @@ void EagerExecutor::backward(Variable* last, const void* hostGradient, bool clea
         if (touch) v->gradientTouched = false;  // the first contribution will overwrite
         else v->zeroGradient();                 // the reference's walk: zero everything, then add
     });
-    last->feedGradient(hostGradient);
+    if (hostGradient) {
+        last->feedGradient(hostGradient);
+    } else {
+        copyOnExecutorStream(*deviceGradient, last->gradient);
+        last->gradientTouched = true;
+    }
     std::unordered_set<Node*> done;
     bfs(last, [this, &done](Node* n) { backwardNode(n, done); });
     if (touch)
@@ -1186,6 +1198,56 @@ void EagerExecutor::backward(Variable* last, const void* hostGradient, bool clea
             v->gradientTouched = true;
         });
     if (clearInterim) clearInterimNodes();
+}
+
+// ================================================================================================ overlapped copies
+CopyStream::CopyStream(GPUDevice* d) : device(d), stream(nullptr), next(0) {
+    DEEP8_ARGUMENT_CHECK(nullptr != d, "the device can not be null");
+    D8_CUDA_CHECK(cudaSetDevice(d->deviceId));
+    cudaStream_t st;
+    D8_CUDA_CHECK(cudaStreamCreateWithFlags(&st, cudaStreamNonBlocking));
+    stream = st;
+    for (auto& e : events) {
+        cudaEvent_t ev;
+        D8_CUDA_CHECK(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming));
+        e = ev;
+    }
+}
+CopyStream::~CopyStream() {
+    cudaStreamSynchronize(static_cast<cudaStream_t>(stream));
+    for (auto e : events) cudaEventDestroy(static_cast<cudaEvent_t>(e));
+    cudaStreamDestroy(static_cast<cudaStream_t>(stream));
+}
+void* CopyStream::fresh() {
+    void* e = events[next];
+    next = (next + 1) % 16;
+    return e;
+}
+void CopyStream::toDevice(const void* pinned, Tensor& to) {
+    DEEP8_ARGUMENT_CHECK(nullptr != pinned && to.device() == device, "the pointer is null or the tensor is on another device");
+    D8_CUDA_CHECK(cudaMemcpyAsync(to.raw(), pinned, to.byteCount(), cudaMemcpyHostToDevice, static_cast<cudaStream_t>(stream)));
+}
+void CopyStream::toHost(const Tensor& from, void* pinned) {
+    DEEP8_ARGUMENT_CHECK(nullptr != pinned && from.device() == device, "the pointer is null or the tensor is on another device");
+    D8_CUDA_CHECK(cudaMemcpyAsync(pinned, from.raw(), from.byteCount(), cudaMemcpyDeviceToHost, static_cast<cudaStream_t>(stream)));
+}
+void* CopyStream::mark() {
+    void* e = fresh();
+    D8_CUDA_CHECK(cudaEventRecord(static_cast<cudaEvent_t>(e), static_cast<cudaStream_t>(stream)));
+    return e;
+}
+void* CopyStream::markExecutor() {  // the executor enqueues on the legacy default stream (GPUDevice's kernel context)
+    void* e = fresh();
+    D8_CUDA_CHECK(cudaEventRecord(static_cast<cudaEvent_t>(e), cudaStreamLegacy));
+    return e;
+}
+void CopyStream::waitFor(void* m) { D8_CUDA_CHECK(cudaStreamWaitEvent(static_cast<cudaStream_t>(stream), static_cast<cudaEvent_t>(m), 0)); }
+void CopyStream::executorWaitsFor(void* m) { D8_CUDA_CHECK(cudaStreamWaitEvent(cudaStreamLegacy, static_cast<cudaEvent_t>(m), 0)); }
+void CopyStream::synchronize() { D8_CUDA_CHECK(cudaStreamSynchronize(static_cast<cudaStream_t>(stream))); }
+
+void copyOnExecutorStream(const Tensor& from, Tensor& to) {
+    DEEP8_ARGUMENT_CHECK(from.byteCount() == to.byteCount() && from.device() == to.device(), "the tensors differ in size or device");
+    D8_CUDA_CHECK(cudaMemcpyAsync(to.raw(), from.raw(), to.byteCount(), cudaMemcpyDeviceToDevice, cudaStreamLegacy));
 }
 
 // ================================================================================================ Net.h sugar

@@ -545,6 +545,9 @@ public:
     void backward(Node* last, bool clearInterim = true) override;
     // addition: start from `last` with an upstream gradient given on the host (the benchmark configurations supply one)
     void backward(Variable* last, const void* hostGradient, bool clearInterim = true);
+    // addition: the same with the upstream gradient already on the device (copied into last's gradient on the executor's
+    // stream, no host synchronisation) - what a step that overlaps its copies with the previous step's kernels uses
+    void backward(Variable* last, const Tensor& deviceGradient, bool clearInterim = true);
 
     // ---- additions: fewer launches and less memory traffic for the same tensors, on by default
     // Fusion: a MatrixMultiply is not launched at once but held until the next node is added.  If that node is a ReLu or a
@@ -565,7 +568,36 @@ private:
     bool fuse = true, touch = true;
     Function* pending = nullptr;  // a MatrixMultiply whose launch is held
     void backwardNode(Node* n, std::unordered_set<Node*>& done);
+    void backwardFrom(Variable* last, const void* hostGradient, const Tensor* deviceGradient, bool clearInterim);
 };
+
+// ------------------------------------------------------------------------------------------------ overlapped copies (addition)
+// Variable::feed and fetch are synchronous, as in the reference.  A CopyStream is a second CUDA stream (non-blocking) on the
+// executor's GPU for copies between page-locked host memory and tensors that run beside the executor's kernels.  Marks
+// (CUDA events, recycled after 16 further marks) order it against the executor's stream; nothing here blocks the host
+// except synchronize().
+class DEEP8_API CopyStream {
+public:
+    explicit CopyStream(GPUDevice* device);
+    ~CopyStream();
+    CopyStream(const CopyStream&) = delete;
+    CopyStream& operator=(const CopyStream&) = delete;
+    void toDevice(const void* pinned, Tensor& to);    // enqueue host -> device
+    void toHost(const Tensor& from, void* pinned);    // enqueue device -> host
+    void* mark();                        // everything enqueued on this stream so far
+    void* markExecutor();                // everything the executor has enqueued so far
+    void waitFor(void* mark);            // what is enqueued here from now on starts after `mark`
+    void executorWaitsFor(void* mark);   // what the executor enqueues from now on starts after `mark`
+    void synchronize();                  // host waits for this stream
+private:
+    GPUDevice* device;
+    void* stream;
+    void* events[16];
+    int next;
+    void* fresh();
+};
+// device -> device on the executor's stream, without host synchronisation (Tensor::copyFrom's asynchronous form)
+DEEP8_API void copyOnExecutorStream(const Tensor& from, Tensor& to);
 
 // ------------------------------------------------------------------------------------------------ Net.h sugar for the path
 DEEP8_API void backward(Variable& v, bool clearInterim = true);

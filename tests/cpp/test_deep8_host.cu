@@ -242,6 +242,57 @@ static void linearNodeAndAdam() {
     executor.clearInterimNodes();
 }
 
+// ---- inputs through a CopyStream, upstream gradient from a device tensor: the same numbers as feed + backward(host gradient)
+static void copyStreamStepEqualsSynchronousStep() {
+    EagerExecutor executor(DeviceType::GPU);
+    auto dev = static_cast<GPUDevice*>(executor.getDevice());
+    const size_t rows = 96, din = 64, dout = 80;
+    auto hx = ints(rows * din, 5), hw = ints(din * dout, 5), hdz = ints(rows * dout, 5);
+    Variable& x = parameter(&executor, {rows, din});
+    Variable& w = parameter(&executor, {din, dout});
+    Variable& dzv = parameter(&executor, {rows, dout}, false);
+    Variable& zkeep = parameter(&executor, {rows, dout}, false);
+    w.feed(hw.data());
+    // synchronous reference
+    x.feed(hx.data());
+    Variable& z0 = x * w;
+    executor.backward(&z0, hdz.data(), false);
+    std::vector<float> rz(rows * dout), rdx(rows * din), rdw(din * dout);
+    z0.fetch(rz.data());
+    x.fetchGradient(rdx.data());
+    w.fetchGradient(rdw.data());
+    executor.clearInterimNodes();
+    // the same step with the copies on a second stream (page-locked host buffers)
+    float *px, *pdz, *pz;
+    cudaHostAlloc(&px, hx.size() * 4, cudaHostAllocDefault);
+    cudaHostAlloc(&pdz, hdz.size() * 4, cudaHostAllocDefault);
+    cudaHostAlloc(&pz, rz.size() * 4, cudaHostAllocDefault);
+    std::copy(hx.begin(), hx.end(), px);
+    std::copy(hdz.begin(), hdz.end(), pdz);
+    x.zero();
+    CopyStream copies(dev);
+    copies.waitFor(copies.markExecutor());  // x.zero() above was the executor's
+    copies.toDevice(px, x.value);
+    copies.toDevice(pdz, dzv.value);
+    copies.executorWaitsFor(copies.mark());
+    Variable& z1 = x * w;
+    executor.backward(&z1, dzv.value, false);
+    copyOnExecutorStream(z1.value, zkeep.value);
+    executor.clearInterimNodes();
+    copies.waitFor(copies.markExecutor());
+    copies.toHost(zkeep.value, pz);
+    copies.synchronize();
+    std::vector<float> gz(pz, pz + rz.size()), gdx(rows * din), gdw(din * dout);
+    x.fetchGradient(gdx.data());
+    w.fetchGradient(gdw.data());
+    EXPECT(same(gz, rz));
+    EXPECT(same(gdx, rdx));
+    EXPECT(same(gdw, rdw));
+    cudaFreeHost(px);
+    cudaFreeHost(pdz);
+    cudaFreeHost(pz);
+}
+
 // ---- x * w + b in one launch leaves the product unstored; asking for it, or using it again, computes it
 static void fusedBiasKeepsTheProductAvailable() {
     EagerExecutor executor(DeviceType::GPU);
@@ -468,6 +519,7 @@ int main() {
         {"executor: fused launches + first-touch gradients equal the node-by-node walk bit for bit; launch counts", fusedExecutorEqualsNodeByNode},
         {"graph: linear(x*w) in one launch, LinearGrad, AdamTrainer steps", linearNodeAndAdam},
         {"graph: x*w + b in one launch, the unstored product computed on demand", fusedBiasKeepsTheProductAvailable},
+        {"CopyStream: inputs and outputs on a second stream, backward from a device gradient, equal to feed / fetch", copyStreamStepEqualsSynchronousStep},
         {"Conv2d node 2x32x32x64, 4x4x64->32, covered, stride 2, dilation 2 (test/Conv2dTest.h)", [] { convNode(2, 32, 32, 64, 32, 4, 4, true, 2, 2); }},
         {"Conv2d node 2x32x32x64, 5x5, covered, stride 1", [] { convNode(2, 32, 32, 64, 32, 5, 5, true, 1, 1); }},
         {"Conv2d node not covered, stride 2, dilation 2", [] { convNode(2, 32, 32, 64, 32, 4, 4, false, 2, 2); }},
