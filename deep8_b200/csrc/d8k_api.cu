@@ -442,32 +442,41 @@ __global__ void __launch_bounds__(256) matvec_rows_kernel(const T* __restrict__ 
 
 // The same product for long rows: one CTA per row, so that the 256 threads read 4 KB of the row at a time, one after the
 // other (whole DRAM pages) - with a warp per row thousands of 64 KB rows are streamed at once and the matrix arrived at
-// 3.9 TB/s of the 6.4 TB/s a copy reaches.  The eight warps' sums meet in shared memory in warp order.
-template <typename T>
+// 3.9 TB/s of the 6.4 TB/s a copy reaches.  A vector of up to 32 KB is copied to shared memory once per CTA (SMEM_V) instead
+// of being read through L2 for every row.  Eight 16-byte loads of the row are in flight per thread.  The eight warps' sums meet in shared
+// memory in warp order.
+template <typename T, bool SMEM_V>
 __global__ void __launch_bounds__(256) matvec_long_rows_kernel(const T* __restrict__ A, const T* __restrict__ v, T* __restrict__ z, size_t rows,
                                                                int cols, int accumulate) {
     constexpr int V = 16 / sizeof(T);
+    constexpr int U = 8;
+    extern __shared__ uint4 v_smem[];
     __shared__ float part[8];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int nv = cols / V;  // the caller guarantees 16-byte aligned rows of whole 16-byte pieces
     const uint4* v4 = reinterpret_cast<const uint4*>(v);
+    if (SMEM_V) {
+        for (int i = threadIdx.x; i < nv; i += 256) v_smem[i] = __ldg(v4 + i);
+        __syncthreads();
+    }
     for (size_t r = blockIdx.x; r < rows; r += gridDim.x) {
         const uint4* a4 = reinterpret_cast<const uint4*>(A + r * cols);
         float acc[4] = {0.f, 0.f, 0.f, 0.f};
-        for (int i0 = threadIdx.x; i0 < nv; i0 += 1024) {
-            uint4 av[4], vv[4];
+        for (int i0 = threadIdx.x; i0 < nv; i0 += 256 * U) {
+            uint4 av[U];
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {
+            for (int u = 0; u < U; ++u) {
                 const int i = i0 + 256 * u;
                 av[u] = i < nv ? __ldcs(a4 + i) : make_uint4(0u, 0u, 0u, 0u);
-                vv[u] = i < nv ? __ldg(v4 + i) : make_uint4(0u, 0u, 0u, 0u);
             }
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {
+            for (int u = 0; u < U; ++u) {
+                const int i = i0 + 256 * u;
+                const uint4 vv = i < nv ? (SMEM_V ? v_smem[i] : __ldg(v4 + i)) : make_uint4(0u, 0u, 0u, 0u);
                 const T* ae = reinterpret_cast<const T*>(&av[u]);
-                const T* ve = reinterpret_cast<const T*>(&vv[u]);
+                const T* ve = reinterpret_cast<const T*>(&vv);
 #pragma unroll
-                for (int k = 0; k < V; ++k) acc[u] = fmaf(to_f(ae[k]), to_f(ve[k]), acc[u]);
+                for (int k = 0; k < V; ++k) acc[u & 3] = fmaf(to_f(ae[k]), to_f(ve[k]), acc[u & 3]);
             }
         }
         float t = (acc[0] + acc[1]) + (acc[2] + acc[3]);
@@ -483,6 +492,27 @@ __global__ void __launch_bounds__(256) matvec_long_rows_kernel(const T* __restri
         }
         __syncthreads();
     }
+}
+
+template <typename T>
+static cudaError_t launch_matvec_long_rows(const d8k_ctx* ctx, const T* A, const T* v, T* z, size_t rows, int cols, int accumulate) {
+    // the vector in shared memory while six CTAs per SM still fit (32 KB); a longer one would cost more in resident CTAs
+    // than it saves in L2 traffic (measured: 64 KB rows 4.8 TB/s with the vector in shared memory, 128 KB rows 5.5 without)
+    const size_t vbytes = static_cast<size_t>(cols) * sizeof(T);
+    const bool smem_v = vbytes <= 32 * 1024;
+    auto kernel = smem_v ? matvec_long_rows_kernel<T, true> : matvec_long_rows_kernel<T, false>;
+    const size_t dyn = smem_v ? vbytes : 0;
+    if (smem_v) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 32 * 1024);
+        if (e != cudaSuccess) return e;
+    }
+    // as many CTAs as are resident at once, each walking over its share of the rows
+    int per_sm = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, 256, dyn) != cudaSuccess || per_sm < 1) per_sm = smem_v ? 3 : 4;
+    size_t ctas = static_cast<size_t>(ctx->num_sms) * per_sm;
+    if (ctas > rows) ctas = rows;
+    kernel<<<static_cast<unsigned>(ctas), 256, dyn, ctx->stream>>>(A, v, z, rows, cols, accumulate);
+    return cudaGetLastError();
 }
 
 // D[r][c] (+)= u[r] * v[c]: the gradient of x for a single-column y.  A thread keeps its 16 bytes of v and walks down the rows.
@@ -647,20 +677,11 @@ static int matvec_rows(d8k_ctx* ctx, int dtype, const void* A, const void* v, vo
     if (!A || !v || !z) return fail(D8K_ERR_ARGUMENT, "gemm: null pointer");
     const int per = dtype == D8K_F32 ? 4 : 8;
     const bool vec = aligned16(A, v, nullptr) && cols % per == 0;
-    if (vec && static_cast<size_t>(cols) * (dtype == D8K_F32 ? 4 : 2) >= 8192) {  // long rows: a CTA per row
-        // as many CTAs as are resident at once (the register count decides), each walking over its share of the rows
-        int per_sm = 0;
-        cudaError_t oe = dtype == D8K_F32 ? cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, matvec_long_rows_kernel<float>, 256, 0)
-                                          : cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, matvec_long_rows_kernel<__half>, 256, 0);
-        if (oe != cudaSuccess || per_sm < 1) per_sm = 4;
-        size_t ctas = static_cast<size_t>(ctx->num_sms) * per_sm;
-        if (ctas > rows) ctas = rows;
-        if (dtype == D8K_F32)
-            matvec_long_rows_kernel<float><<<static_cast<unsigned>(ctas), 256, 0, ctx->stream>>>(static_cast<const float*>(A), static_cast<const float*>(v),
-                                                                                              static_cast<float*>(z), rows, cols, accumulate);
-        else
-            matvec_long_rows_kernel<__half><<<static_cast<unsigned>(ctas), 256, 0, ctx->stream>>>(static_cast<const __half*>(A), static_cast<const __half*>(v),
-                                                                                               static_cast<__half*>(z), rows, cols, accumulate);
+    // rows of 16 KB and more: a CTA per row (measured on 4 KB .. 128 KB rows: shorter ones run faster with a warp per row)
+    if (vec && static_cast<size_t>(cols) * (dtype == D8K_F32 ? 4 : 2) >= 16384) {
+        D8K_CUDA(dtype == D8K_F32 ? launch_matvec_long_rows(ctx, static_cast<const float*>(A), static_cast<const float*>(v), static_cast<float*>(z), rows, cols, accumulate)
+                                  : launch_matvec_long_rows(ctx, static_cast<const __half*>(A), static_cast<const __half*>(v), static_cast<__half*>(z), rows, cols,
+                                                            accumulate));
         D8K_CUDA(cudaGetLastError());
         count_launch();
         set_last_kernel(std::string(dtype == D8K_F32 ? "f32" : "f16") + " matvec rows (cta per row)");

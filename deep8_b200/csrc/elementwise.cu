@@ -47,14 +47,29 @@ __global__ void linear_forward_kernel(const T* __restrict__ x, T* __restrict__ y
     const size_t tid = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x;
     const size_t stride = gridDim.x * static_cast<size_t>(blockDim.x);
     const size_t nv = vec ? n / V : 0;
-    for (size_t i = tid; i < nv; i += stride) {
+    size_t i = tid;
+    // four independent 16-byte loads in flight per thread before the first store: a lone load per iteration left the
+    // kernel at 5.1 TB/s where the gradient kernel, with two loads per iteration, reached 5.8
+    for (; i + 3 * stride < nv; i += 4 * stride) {
+        uint4 in[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) in[u] = __ldcs(reinterpret_cast<const uint4*>(x) + i + u * stride);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            T* e = reinterpret_cast<T*>(&in[u]);
+#pragma unroll
+            for (int k = 0; k < V; ++k) e[k] = linear_op(e[k], a, b);
+            reinterpret_cast<uint4*>(y)[i + u * stride] = in[u];
+        }
+    }
+    for (; i < nv; i += stride) {
         uint4 in = __ldcs(reinterpret_cast<const uint4*>(x) + i);
         T* e = reinterpret_cast<T*>(&in);
 #pragma unroll
         for (int k = 0; k < V; ++k) e[k] = linear_op(e[k], a, b);
         reinterpret_cast<uint4*>(y)[i] = in;
     }
-    for (size_t i = nv * V + tid; i < n; i += stride) y[i] = linear_op(x[i], a, b);
+    for (size_t j = nv * V + tid; j < n; j += stride) y[j] = linear_op(x[j], a, b);
 }
 
 template <typename T>
