@@ -22,6 +22,11 @@
 // tile to scratch memory, takes a ticket with atomicAdd, and the CTA that draws the last ticket sums the partials
 // in split order (so the result does not depend on arrival order), applies beta and stores.  Nobody waits on another CTA.
 //
+// Two forms beyond one CTA per SM with one thread per role (GemmCfg's last parameter): DUAL - two CTAs per SM, each with
+// half the stages, one accumulator buffer and one converter group, for fp32 launches with more tiles than SMs and no
+// split; TWIN - one CTA per SM with two TMA-issuing threads (A's boxes, B's boxes) and two MMA-issuing threads that take
+// k-blocks in turn under a token, for every other TMA launch.  Both keep the order in which the sums are formed.
+//
 // Every mbarrier wait is bounded: on expiry the CTA records a status code, all roles leave their loops, and the
 // kernel returns through the normal teardown (TMEM freed).
 #pragma once
