@@ -203,8 +203,12 @@ int conv_by_residue_class(d8k_ctx* ctx, int which, const GemmProblem& whole, con
             return fail(D8K_ERR_CUDA, "cudaMemsetAsync failed");
     }
     *done = true;
-    for (const GemmProblem& g : parts)
+    bool first = true;
+    for (GemmProblem& g : parts) {
+        g.tickets = first ? 1 : 2;  // one clearing of the tile tickets serves all the classes (each launch leaves them zero)
+        first = false;
         if (int rc = run_gemm(ctx, g)) return rc;
+    }
     return 0;
 }
 

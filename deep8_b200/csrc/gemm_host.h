@@ -54,6 +54,10 @@ struct GemmProblem {
     float epi_a = 0.f, epi_b = 0.f;
     void* E1 = nullptr;
     void* E2 = nullptr;
+    // Tile tickets of a split launch: 0 - run_gemm clears the ones this launch uses (the default); 1 - it clears ALL of the
+    // context's tickets (the first launch of a series); 2 - the caller vouches that they are zero (a later launch of the
+    // series: each launch leaves them zero unless it gave up on a wait, and then the status word already says so)
+    int tickets = 0;
     void* ws = nullptr;  // optional caller scratch for split-K
     size_t ws_bytes = 0;
     // scatter_rows > 0: C is not used; output rows [k * scatter_rows, (k + 1) * scatter_rows) go to scatter_base[k], a

@@ -582,10 +582,11 @@ int run_gemm(Ctx* ctx, const GemmProblem& g) {
         fn = pl.f32 ? lookup_f32_gather(g.a.mn, g.b.mn, pl.bn) : lookup_f16_gather(g.a.mn, g.b.mn, pl.bn);
     }
     if (!fn) return fail(2, "gemm: no kernel for this configuration");
-    if (pl.splits > 1) {
+    if ((pl.splits > 1 && g.tickets == 0) || g.tickets == 1) {
         // Tile tickets must start at zero.  A kernel that gave up on a bounded wait leaves them half-counted, and the status
         // word that says so may not have been read yet: clear the tickets this launch uses on the stream, every time.
-        cudaError_t ce = cudaMemsetAsync(ctx->counters, 0, static_cast<size_t>(pl.tiles) * sizeof(int), ctx->stream);
+        const size_t count = g.tickets == 1 ? static_cast<size_t>(kMaxCounters) : static_cast<size_t>(pl.tiles);
+        cudaError_t ce = cudaMemsetAsync(ctx->counters, 0, count * sizeof(int), ctx->stream);
         if (ce != cudaSuccess) return fail(2, std::string("gemm: cudaMemsetAsync: ") + cudaGetErrorString(ce));
     }
     int grid = p.total_work < ctx->num_sms ? p.total_work : ctx->num_sms;
