@@ -203,13 +203,7 @@ int conv_by_residue_class(d8k_ctx* ctx, int which, const GemmProblem& whole, con
             return fail(D8K_ERR_CUDA, "cudaMemsetAsync failed");
     }
     *done = true;
-    bool first = true;
-    for (GemmProblem& g : parts) {
-        g.tickets = first ? 1 : 2;  // one clearing of the tile tickets serves all the classes (each launch leaves them zero)
-        first = false;
-        if (int rc = run_gemm(ctx, g)) return rc;
-    }
-    return 0;
+    return run_gemm_group(ctx, parts);
 }
 
 // The three contractions of a convolution-like operator over virtual im2col matrices.
@@ -586,9 +580,11 @@ int d8k_ctx_create(int device, size_t scratch_bytes, d8k_ctx** out) {
     cudaError_t e = cudaMalloc(&ctx->scratch, ctx->scratch_bytes);
     if (e == cudaSuccess) e = cudaMalloc(&ctx->counters, (kMaxCounters + 1) * sizeof(int));
     if (e == cudaSuccess) e = cudaMemset(ctx->counters, 0, (kMaxCounters + 1) * sizeof(int));
+    if (e == cudaSuccess) e = cudaMalloc(&ctx->group_buf, sizeof(GroupEntry) * kMaxGroups);
     if (e != cudaSuccess) {
         cudaFree(ctx->scratch);
         cudaFree(ctx->counters);
+        cudaFree(ctx->group_buf);
         delete ctx;
         return fail(D8K_ERR_CUDA, std::string("d8k_ctx_create: ") + cudaGetErrorString(e));
     }
@@ -602,6 +598,7 @@ int d8k_ctx_destroy(d8k_ctx* ctx) {
     cudaSetDevice(ctx->device);
     cudaFree(ctx->scratch);
     cudaFree(ctx->counters);
+    cudaFree(ctx->group_buf);
     delete ctx;
     return 0;
 }

@@ -4,6 +4,7 @@
 #include <cuda_runtime.h>
 #include <cstddef>
 #include <string>
+#include <vector>
 
 #include "gemm_kernel.cuh"
 
@@ -17,8 +18,10 @@ struct Ctx {
     size_t scratch_bytes = 0;
     int* counters = nullptr;   // kMaxCounters tile tickets, zero between launches
     int* status = nullptr;     // device status word
+    GroupEntry* group_buf = nullptr;  // device memory for kMaxGroups entries of a grouped launch (null: launches are never grouped)
 };
 constexpr int kMaxCounters = 4096;
+constexpr int kMaxGroups = 16;
 
 // One operand as the host sees it.  mn == false: K-major (the contraction index is contiguous); mn == true: MN-major.
 struct HostOperand {
@@ -58,6 +61,8 @@ struct GemmProblem {
     // context's tickets (the first launch of a series); 2 - the caller vouches that they are zero (a later launch of the
     // series: each launch leaves them zero unless it gave up on a wait, and then the status word already says so)
     int tickets = 0;
+    int ticket_base = 0;     // first of the context's tickets this launch uses (grouped launches give every contraction its own range)
+    bool ws_strict = false;  // split within ws / ws_bytes, never in the context's own scratch (run_gemm_group carves that up itself)
     void* ws = nullptr;  // optional caller scratch for split-K
     size_t ws_bytes = 0;
     // scatter_rows > 0: C is not used; output rows [k * scatter_rows, (k + 1) * scatter_rows) go to scatter_base[k], a
@@ -73,16 +78,33 @@ int fail(int code, const std::string& msg);
 void count_launch();
 void set_last_kernel(const std::string& text);
 
-int run_gemm(Ctx* ctx, const GemmProblem& g);
+typedef cudaError_t (*GemmLaunchFn)(int grid, cudaStream_t stream, const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p);
+
+// Everything run_gemm works out for one contraction short of launching it
+struct PreparedGemm {
+    GemmParams p;
+    CUtensorMap ta, tb;
+    GemmLaunchFn fn = nullptr;
+    int grid = 0, tiles = 0, splits = 1;
+    bool pair = false, dual = false, halo = false, twin = false, f32 = false, a_mn = false, b_mn = false;
+    int bn = 0;
+    std::string text;  // what d8k_last_kernel reports
+};
+
+// capture != nullptr: prepare only (no clearing of tickets, no launch) and hand the result back
+int run_gemm(Ctx* ctx, const GemmProblem& g, PreparedGemm* capture = nullptr);
+// The contractions of one operator (the residue classes of a strided convolution): ONE launch whose work items are all of
+// theirs when the context has a group buffer and every part runs the same one-CTA-per-SM kernel, otherwise one launch each.
+int run_gemm_group(Ctx* ctx, std::vector<GemmProblem>& parts);
 // scratch bytes run_gemm would use for this problem with its default split choice (0 when it runs unsplit)
 size_t gemm_scratch_need(const Ctx* ctx, const GemmProblem& g);
 // true when run_gemm would fetch both operands with the TMA producer (no loader warps)
 bool gemm_goes_through_tma(const Ctx* ctx, const GemmProblem& g);
 
-typedef cudaError_t (*GemmLaunchFn)(int grid, cudaStream_t stream, const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p);
 // one table per translation unit of instantiations; index [a_mn][b_mn][bn slot]
 GemmLaunchFn lookup_f16_tma(bool a_mn, bool b_mn, int bn);
 GemmLaunchFn lookup_f16_twin(bool a_mn, bool b_mn, int bn);  // lookup_f16_tma's tiles with twin issuing threads
+GemmLaunchFn lookup_f16_grouped(bool a_mn, bool b_mn, int bn);  // the same for grouped launches
 GemmLaunchFn lookup_f16_gather(bool a_mn, bool b_mn, int bn);
 GemmLaunchFn lookup_f32_gather(bool a_mn, bool b_mn, int bn);
 GemmLaunchFn lookup_f32_tma(bool a_mn, bool b_mn, int bn, bool a_in_tmem);

@@ -25,6 +25,21 @@ GemmLaunchFn lookup_f16_twin(bool a_mn, bool b_mn, int bn) {
     return pick_twin<true, true>(bn);
 }
 
+// twin threads, grouped launches (GemmCfg::GROUPED)
+template <bool A_MN, bool B_MN>
+static GemmLaunchFn pick_grouped(int bn) {
+    if (bn == 256) return launch_cfg<GemmCfg<false, A_MN, B_MN, 256, 4, false, false, false, 5>>;
+    if (bn == 128) return launch_cfg<GemmCfg<false, A_MN, B_MN, 128, 6, false, false, false, 5>>;
+    return nullptr;
+}
+
+GemmLaunchFn lookup_f16_grouped(bool a_mn, bool b_mn, int bn) {
+    if (!a_mn && !b_mn) return pick_grouped<false, false>(bn);
+    if (!a_mn && b_mn) return pick_grouped<false, true>(bn);
+    if (a_mn && !b_mn) return pick_grouped<true, false>(bn);
+    return pick_grouped<true, true>(bn);
+}
+
 GemmLaunchFn lookup_f16_tma(bool a_mn, bool b_mn, int bn) {
     if (!a_mn && !b_mn) return pick<false, false>(bn);
     if (!a_mn && b_mn) return pick<false, true>(bn);

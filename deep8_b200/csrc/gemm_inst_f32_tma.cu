@@ -30,6 +30,7 @@ static GemmLaunchFn pick_dual(bool a_mn, bool b_mn) {
 }
 GemmLaunchFn lookup_f32_dual(bool a_mn, bool b_mn, int mode) {
     if (mode == 4) return pick_dual<4, 4>(a_mn, b_mn);  // one CTA per SM with twin TMA and MMA threads (GemmCfg::TWIN)
+    if (mode == 5) return pick_dual<5, 4>(a_mn, b_mn);  // the same for grouped launches (GemmCfg::GROUPED)
     return mode == 2 ? pick_dual<2, 3>(a_mn, b_mn) : pick_dual<1, 2>(a_mn, b_mn);
 }
 

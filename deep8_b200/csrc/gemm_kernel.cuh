@@ -125,7 +125,15 @@ struct OutMap {
     FastDiv f_c, f_nfx;     // C, NFX
 };
 
+struct GroupEntry;
+
 struct GemmParams {
+    // Grouped launch (group_count > 1): the work items of several contractions of one operator - the residue classes of a strided
+    // convolution - share ONE launch.  `groups` is an array in device memory with each contraction's own parameters and
+    // tensor maps; work item w belongs to the group g with groups[g].first_work <= w < groups[g + 1].first_work and is item
+    // w - first_work of that contraction.  The launch's own copy of the fields below is group 0's, with total_work the sum.
+    int group_count;
+    const GroupEntry* groups;
     int M, N, K;
     int batch;         // output batches (independent problems)
     int kbatch;        // batches folded into the contraction (sum over b of A[b] * B[b]); 1 otherwise
@@ -166,6 +174,33 @@ struct GemmParams {
     OutMap out;
     GatherSrc a, b;
 };
+
+struct alignas(128) GroupEntry {
+    CUtensorMap ta, tb;
+    GemmParams p;
+    int first_work;
+};
+
+// Parameters, tensor maps and local index of work item w (see GemmParams::group_count)
+struct SelectedWork {
+    const GemmParams* p;
+    const CUtensorMap* ta;
+    const CUtensorMap* tb;
+    int w;
+};
+__device__ __forceinline__ SelectedWork select_work(const GemmParams& launch, const CUtensorMap& ta, const CUtensorMap& tb, int w) {
+    SelectedWork s = {&launch, &ta, &tb, w};
+    if (launch.group_count > 1) {
+        int g = 0;
+        while (g + 1 < launch.group_count && w >= launch.groups[g + 1].first_work) ++g;
+        const GroupEntry& e = launch.groups[g];
+        s.p = &e.p;
+        s.ta = &e.ta;
+        s.tb = &e.tb;
+        s.w = w - e.first_work;
+    }
+    return s;
+}
 
 // false for a row of the padded raster that stands for no output pixel (OutMap::valid_w)
 __device__ __forceinline__ bool out_row_exists(const GemmParams& p, int row) {
@@ -250,7 +285,10 @@ struct GemmCfg {
     // MMA-issuing thread (the two take k-blocks in turn, ordered by a token, so the sums are formed in the same order).  A
     // k-block costs the single MMA thread about as long in barrier traffic and tcgen05.commit as in its eight MMAs, and the
     // single producer as long again; with two threads each, one thread's bookkeeping runs behind the other's issue.
-    static constexpr bool TWIN = DUAL_ == 4;
+    static constexpr bool TWIN = DUAL_ == 4 || DUAL_ == 5;
+    // DUAL_ == 5: TWIN whose work items may belong to several contractions (GemmParams::group_count); a kernel of its own,
+    // because per-item parameters read through a pointer cost the ungrouped kernels a fifth of their speed
+    static constexpr bool GROUPED = DUAL_ == 5;
     static constexpr int A_TMEM_STRIDE = ALO ? BK : 2 * BK;     // tensor-memory columns of A per stage
     static constexpr int ACC_BUFS = DUAL ? 1 : 2;
     static constexpr int CTAS_PER_SM = DUAL ? 2 : 1;
@@ -800,7 +838,11 @@ __device__ __forceinline__ void produce_operand(int mode, int chunked, const Gat
 
 template <class Cfg>
 __global__ void __launch_bounds__(Cfg::THREADS, Cfg::CTAS_PER_SM)
-d8k_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmParams p) {
+d8k_gemm_kernel(const __grid_constant__ CUtensorMap tmA_launch, const __grid_constant__ CUtensorMap tmB_launch, const GemmParams p_launch) {
+    // the roles' work loops shadow these three with the ones of the work item's group (select_work)
+    const GemmParams& p = p_launch;
+    const CUtensorMap& tmA = tmA_launch;
+    const CUtensorMap& tmB = tmB_launch;
     using OutT = typename std::conditional<Cfg::F32, float, __half>::type;
     using InT = OutT;
     constexpr int BN = Cfg::BN, STAGES = Cfg::STAGES, BK = Cfg::BK, CE = Cfg::CE;
@@ -905,7 +947,14 @@ d8k_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                 }
             }
         };
-        for (int w = blockIdx.x; ok && w < p.total_work; w += gridDim.x, ++item_seq) {
+        for (int w_all = blockIdx.x; ok && w_all < p_launch.total_work; w_all += gridDim.x, ++item_seq) {
+            SelectedWork sel = {&p_launch, &tmA_launch, &tmB_launch, w_all};
+            if constexpr (Cfg::GROUPED) sel = select_work(p_launch, tmA_launch, tmB_launch, w_all);
+            const GemmParams& p = Cfg::GROUPED ? *sel.p : p_launch;
+            const CUtensorMap& tmA = Cfg::GROUPED ? *sel.ta : tmA_launch;
+            const CUtensorMap& tmB = Cfg::GROUPED ? *sel.tb : tmB_launch;
+            const int w = Cfg::GROUPED ? sel.w : w_all;
+            (void)tmA; (void)tmB; (void)w;
             WorkItem it = decode_work(p, w, BN);
             for (int kk = it.kb_begin; kk < it.kb_end; ++kk) {
                 int k0_halo = 0;
@@ -976,7 +1025,14 @@ d8k_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         const int me = (Cfg::TWIN && warp != Cfg::MMA_WARP) ? 1 : 0;
         int t = 0;
         uint32_t my_turns = 0;
-        for (int w = blockIdx.x; ok && w < p.total_work; w += gridDim.x) {
+        for (int w_all = blockIdx.x; ok && w_all < p_launch.total_work; w_all += gridDim.x) {
+            SelectedWork sel = {&p_launch, &tmA_launch, &tmB_launch, w_all};
+            if constexpr (Cfg::GROUPED) sel = select_work(p_launch, tmA_launch, tmB_launch, w_all);
+            const GemmParams& p = Cfg::GROUPED ? *sel.p : p_launch;
+            const CUtensorMap& tmA = Cfg::GROUPED ? *sel.ta : tmA_launch;
+            const CUtensorMap& tmB = Cfg::GROUPED ? *sel.tb : tmB_launch;
+            const int w = Cfg::GROUPED ? sel.w : w_all;
+            (void)tmA; (void)tmB; (void)w;
             WorkItem it = decode_work(p, w, BN);
             uint32_t d_tmem = 0;
             int in_chain = 0;
@@ -1071,7 +1127,14 @@ d8k_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         const bool timed = p.prof != nullptr;
         long long w_tfull = 0;
         const long long t_begin = timed ? clock64() : 0;
-        for (int w = blockIdx.x; ok && w < p.total_work; w += gridDim.x) {
+        for (int w_all = blockIdx.x; ok && w_all < p_launch.total_work; w_all += gridDim.x) {
+            SelectedWork sel = {&p_launch, &tmA_launch, &tmB_launch, w_all};
+            if constexpr (Cfg::GROUPED) sel = select_work(p_launch, tmA_launch, tmB_launch, w_all);
+            const GemmParams& p = Cfg::GROUPED ? *sel.p : p_launch;
+            const CUtensorMap& tmA = Cfg::GROUPED ? *sel.ta : tmA_launch;
+            const CUtensorMap& tmB = Cfg::GROUPED ? *sel.tb : tmB_launch;
+            const int w = Cfg::GROUPED ? sel.w : w_all;
+            (void)tmA; (void)tmB; (void)w;
             WorkItem it = decode_work(p, w, BN);
             const int row = it.m0 + row_in_tile;
             const bool row_ok = out_row_exists(p, row);
@@ -1208,7 +1271,14 @@ d8k_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         const bool timed = p.prof != nullptr;
         long long w_raw = 0, w_pfull = 0;
         const long long t_begin = timed ? clock64() : 0;
-        for (int w = blockIdx.x; ok && w < p.total_work; w += gridDim.x, ++item_seq) {
+        for (int w_all = blockIdx.x; ok && w_all < p_launch.total_work; w_all += gridDim.x, ++item_seq) {
+            SelectedWork sel = {&p_launch, &tmA_launch, &tmB_launch, w_all};
+            if constexpr (Cfg::GROUPED) sel = select_work(p_launch, tmA_launch, tmB_launch, w_all);
+            const GemmParams& p = Cfg::GROUPED ? *sel.p : p_launch;
+            const CUtensorMap& tmA = Cfg::GROUPED ? *sel.ta : tmA_launch;
+            const CUtensorMap& tmB = Cfg::GROUPED ? *sel.tb : tmB_launch;
+            const int w = Cfg::GROUPED ? sel.w : w_all;
+            (void)tmA; (void)tmB; (void)w;
             WorkItem it = decode_work(p, w, BN);
             const int tile_col0 = Cfg::HALO ? it.m0 % p.halo_wp : 0;  // HALO: raster position of the tile's first pixel inside its first patch row
             for (int kk = it.kb_begin; kk < it.kb_end; ++kk, ++t) {
@@ -1319,7 +1389,14 @@ d8k_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         const InT* const base_b0 = reinterpret_cast<const InT*>(p.b.base);
         int t = 0;                  // running k-block count of this CTA: k-block t uses stage t % STAGES
         bool ok = true;
-        for (int w = blockIdx.x; ok && w < p.total_work; w += gridDim.x) {
+        for (int w_all = blockIdx.x; ok && w_all < p_launch.total_work; w_all += gridDim.x) {
+            SelectedWork sel = {&p_launch, &tmA_launch, &tmB_launch, w_all};
+            if constexpr (Cfg::GROUPED) sel = select_work(p_launch, tmA_launch, tmB_launch, w_all);
+            const GemmParams& p = Cfg::GROUPED ? *sel.p : p_launch;
+            const CUtensorMap& tmA = Cfg::GROUPED ? *sel.ta : tmA_launch;
+            const CUtensorMap& tmB = Cfg::GROUPED ? *sel.tb : tmB_launch;
+            const int w = Cfg::GROUPED ? sel.w : w_all;
+            (void)tmA; (void)tmB; (void)w;
             WorkItem it = decode_work(p, w, BN);
             RowState ra[A_NROW], rb[B_NROW];
             ColState ca[A_NCOL], cb[B_NCOL];

@@ -407,7 +407,7 @@ bool gemm_goes_through_tma(const Ctx* ctx, const GemmProblem& g) {
     return pl.tma;
 }
 
-int run_gemm(Ctx* ctx, const GemmProblem& g) {
+int run_gemm(Ctx* ctx, const GemmProblem& g, PreparedGemm* capture) {
     if (g.M < 0 || g.N < 0 || g.K < 0 || g.batch < 0 || g.kbatch < 1) return fail(1, "gemm: negative extent");
     if (g.M == 0 || g.N == 0 || g.batch == 0) return 0;
     if ((!g.C && g.scatter_rows == 0) || (g.K > 0 && (!g.a.ptr || !g.b.ptr))) return fail(1, "gemm: null pointer");
@@ -437,14 +437,14 @@ int run_gemm(Ctx* ctx, const GemmProblem& g) {
 
     // a stride-1 virtual operand in fp32: per-tile patches instead of one fetch per filter tap, when the plan stays unsplit
     GemmProblem halo_problem;
-    if (to_halo(g, &halo_problem)) {
+    if (!capture && to_halo(g, &halo_problem)) {
         const Plan hp = make_plan(ctx, halo_problem, 0);
         if (hp.tma && hp.splits == 1 && hp.bn == 64 && hp.tiles * 2 > ctx->num_sms) return run_gemm(ctx, halo_problem);
     }
     // The caller's scratch (a node's interim buffer) is used when it holds everything the split plan wants; a buffer that is
     // missing, empty or smaller than that would silently cost splits, so the context's own scratch serves instead.
     bool own_scratch = g.ws == nullptr || g.ws_bytes == 0;
-    if (!own_scratch && g.ws_bytes < ctx->scratch_bytes && make_plan(ctx, g, ctx->scratch_bytes).scratch > g.ws_bytes) own_scratch = true;
+    if (!own_scratch && !g.ws_strict && g.ws_bytes < ctx->scratch_bytes && make_plan(ctx, g, ctx->scratch_bytes).scratch > g.ws_bytes) own_scratch = true;
     float* scratch = own_scratch ? ctx->scratch : static_cast<float*>(g.ws);
     size_t scratch_limit = own_scratch ? ctx->scratch_bytes : g.ws_bytes;
     if (reinterpret_cast<uintptr_t>(scratch) & 15) return fail(1, "gemm: scratch memory must be 16-byte aligned");
@@ -506,7 +506,7 @@ int run_gemm(Ctx* ctx, const GemmProblem& g) {
     p.ldc = g.ldc;
     p.c_batch_stride = g.c_batch_stride;
     p.ws = scratch;
-    p.counters = ctx->counters;
+    p.counters = ctx->counters + g.ticket_base;
     p.status = ctx->status;
     if (const char* pp = std::getenv("D8K_PROF_PTR"))  // diagnostics: device address of 8 cycle counters per CTA (paired kernel)
         p.prof = reinterpret_cast<long long*>(static_cast<uintptr_t>(std::strtoull(pp, nullptr, 0)));
@@ -582,19 +582,10 @@ int run_gemm(Ctx* ctx, const GemmProblem& g) {
         fn = pl.f32 ? lookup_f32_gather(g.a.mn, g.b.mn, pl.bn) : lookup_f16_gather(g.a.mn, g.b.mn, pl.bn);
     }
     if (!fn) return fail(2, "gemm: no kernel for this configuration");
-    if ((pl.splits > 1 && g.tickets == 0) || g.tickets == 1) {
-        // Tile tickets must start at zero.  A kernel that gave up on a bounded wait leaves them half-counted, and the status
-        // word that says so may not have been read yet: clear the tickets this launch uses on the stream, every time.
-        const size_t count = g.tickets == 1 ? static_cast<size_t>(kMaxCounters) : static_cast<size_t>(pl.tiles);
-        cudaError_t ce = cudaMemsetAsync(ctx->counters, 0, count * sizeof(int), ctx->stream);
-        if (ce != cudaSuccess) return fail(2, std::string("gemm: cudaMemsetAsync: ") + cudaGetErrorString(ce));
-    }
     int grid = p.total_work < ctx->num_sms ? p.total_work : ctx->num_sms;
     if (dual) grid = p.total_work < 2 * ctx->num_sms ? p.total_work : 2 * ctx->num_sms;
     if (pl.pair) grid = p.total_work < ctx->num_sms / 2 ? p.total_work : ctx->num_sms / 2;  // pairs
-    cudaError_t e = fn(grid, ctx->stream, ta, tb, p);
-    if (e != cudaSuccess) return fail(2, std::string("gemm: launch failed: ") + cudaGetErrorString(e));
-    count_launch();
+    std::string text;
     {
         static const char* const kModes[] = {"tiled", "im2col", "im2col-mn", "filter-tap", "filter-sub", "filter-tap-sub", "halo"};
         std::ostringstream os;
@@ -604,8 +595,97 @@ int run_gemm(Ctx* ctx, const GemmProblem& g) {
         if (dual) os << " dual";
         if (twin) os << " twin";
         if (pl.pair) os << " raster=" << (p.raster_n ? "n" : "m") << p.raster_group << " l2=" << p.l2_a << p.l2_b;
-        set_last_kernel(os.str());
+        text = os.str();
     }
+    if (capture) {
+        capture->p = p;
+        capture->ta = ta;
+        capture->tb = tb;
+        capture->fn = fn;
+        capture->grid = grid;
+        capture->tiles = pl.tiles;
+        capture->splits = pl.splits;
+        capture->pair = pl.pair;
+        capture->dual = dual;
+        capture->halo = g.a.halo != 0;
+        capture->twin = twin;
+        capture->f32 = pl.f32;
+        capture->a_mn = g.a.mn;
+        capture->b_mn = g.b.mn;
+        capture->bn = pl.bn;
+        capture->text = text;
+        return 0;
+    }
+    if ((pl.splits > 1 && g.tickets == 0) || g.tickets == 1) {
+        // Tile tickets must start at zero.  A kernel that gave up on a bounded wait leaves them half-counted, and the status
+        // word that says so may not have been read yet: clear the tickets this launch uses on the stream, every time.
+        const size_t count = g.tickets == 1 ? static_cast<size_t>(kMaxCounters) : static_cast<size_t>(pl.tiles);
+        cudaError_t ce = cudaMemsetAsync(ctx->counters + (g.tickets == 1 ? 0 : g.ticket_base), 0, count * sizeof(int), ctx->stream);
+        if (ce != cudaSuccess) return fail(2, std::string("gemm: cudaMemsetAsync: ") + cudaGetErrorString(ce));
+    }
+    cudaError_t e = fn(grid, ctx->stream, ta, tb, p);
+    if (e != cudaSuccess) return fail(2, std::string("gemm: launch failed: ") + cudaGetErrorString(e));
+    count_launch();
+    set_last_kernel(text);
+    return 0;
+}
+
+int run_gemm_group(Ctx* ctx, std::vector<GemmProblem>& parts) {
+    const int n = static_cast<int>(parts.size());
+    if (n == 0) return 0;
+    bool grouped = ctx->group_buf != nullptr && n >= 2 && n <= kMaxGroups && env_int("D8K_GROUP", 1);
+    std::vector<PreparedGemm> prep(grouped ? n : 0);
+    int tickets = 0;
+    if (grouped) {
+        // every contraction gets its own part of the context's scratch memory and its own range of tickets
+        const size_t region = (ctx->scratch_bytes / n) & ~static_cast<size_t>(255);
+        for (int i = 0; i < n && grouped; ++i) {
+            GemmProblem g = parts[i];
+            g.ws = reinterpret_cast<char*>(ctx->scratch) + static_cast<size_t>(i) * region;
+            g.ws_bytes = region;
+            g.ws_strict = true;
+            g.ticket_base = tickets;
+            if (g.M <= 0 || g.N <= 0 || g.K <= 0 || g.batch <= 0) grouped = false;  // degenerate parts keep run_gemm's own handling
+            else if (int rc = run_gemm(ctx, g, &prep[i])) return rc;
+            if (!grouped) break;
+            tickets += prep[i].tiles;
+            // one launch needs one kernel: the same instantiation for every part, one CTA per SM
+            if (prep[i].pair || prep[i].dual || prep[i].halo || !prep[i].twin || prep[i].fn != prep[0].fn || tickets > kMaxCounters) grouped = false;
+        }
+    }
+    if (!grouped) {
+        bool first = true;
+        for (GemmProblem& g : parts) {
+            g.tickets = first ? 1 : 2;  // one clearing of the tile tickets serves all the parts (each launch leaves them zero)
+            first = false;
+            if (int rc = run_gemm(ctx, g)) return rc;
+        }
+        return 0;
+    }
+    std::vector<GroupEntry> entries(n);
+    int total = 0;
+    for (int i = 0; i < n; ++i) {
+        std::memset(&entries[i], 0, sizeof(GroupEntry));
+        entries[i].ta = prep[i].ta;
+        entries[i].tb = prep[i].tb;
+        entries[i].p = prep[i].p;
+        entries[i].first_work = total;
+        total += prep[i].p.total_work;
+    }
+    cudaError_t e = cudaMemcpyAsync(ctx->group_buf, entries.data(), sizeof(GroupEntry) * n, cudaMemcpyHostToDevice, ctx->stream);
+    if (e == cudaSuccess) e = cudaMemsetAsync(ctx->counters, 0, static_cast<size_t>(tickets) * sizeof(int), ctx->stream);
+    if (e != cudaSuccess) return fail(2, std::string("gemm: preparing a grouped launch: ") + cudaGetErrorString(e));
+    GemmParams launch = prep[0].p;
+    launch.group_count = n;
+    launch.groups = ctx->group_buf;
+    launch.total_work = total;
+    const int grid = total < ctx->num_sms ? total : ctx->num_sms;
+    const GemmLaunchFn fn = prep[0].f32 ? lookup_f32_dual(prep[0].a_mn, prep[0].b_mn, 5) : lookup_f16_grouped(prep[0].a_mn, prep[0].b_mn, prep[0].bn);
+    if (!fn) return fail(2, "gemm: no grouped kernel for this configuration");
+    e = fn(grid, ctx->stream, prep[0].ta, prep[0].tb, launch);
+    if (e != cudaSuccess) return fail(2, std::string("gemm: launch failed: ") + cudaGetErrorString(e));
+    count_launch();
+    set_last_kernel(prep[0].text + " grouped x" + std::to_string(n) + " grid=" + std::to_string(grid));
     return 0;
 }
 

@@ -820,3 +820,36 @@ def test_twin_issuing_threads_fp16_same_bits(ctx, restated, monkeypatch, case):
     for name, g, wnt in zip(("z", "dx", "dy"), twin, r.cpu(x, w, dz, dx0, dw0)):
         check(ctx, g, wnt, F16_TOL, name)
     assert ctx.status() == 0
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("case", [("deconv", (4, 14, 14, 64), (32, 4, 4, 64), True, (2, 2)), ("deconv", (2, 9, 7, 32), (64, 3, 3, 32), False, (3, 2)),
+                                  ("conv", (2, 33, 29, 64), (64, 3, 3, 64), True, (2, 2), (1, 1)), ("conv", (3, 24, 24, 32), (96, 5, 4, 32), False, (2, 3), (1, 1))])
+@pytest.mark.parametrize("tdtype", [torch.float32, torch.float16])
+def test_residue_classes_in_one_launch_give_the_same_bits(ctx, restated, monkeypatch, case, tdtype):
+    """A strided rule runs one contraction per residue class of pixels (or of taps).  By default their work items share ONE
+    launch (every class with its own parameters, tensor maps, scratch region and tickets in device memory); D8K_GROUP=0
+    launches them one after the other.  Same bits either way, and the oracle within the bar."""
+    kind = case[0]
+    meta = (case[3], case[4], case[5]) if kind == "conv" else (case[3], case[4])
+    h = (lambda a: a.astype(np.float16).astype(np.float32)) if tdtype == torch.float16 else (lambda a: a)
+    x, w = h(cases.uniform(101, case[1])), h(cases.normal(102, case[2], 0.25))
+    r = Runner(ctx, restated, kind, meta)
+    dz = h(cases.normal(103, r.zshape(x, w)))
+    dx0, dw0 = h(cases.normal(104, case[1])), h(cases.normal(105, case[2]))
+    monkeypatch.setenv("D8K_GROUP", "0")
+    before = ctx.launch_count()
+    apart = r.gpu(x, w, dz, dx0, dw0, tdtype)
+    launches_apart = ctx.launch_count() - before
+    assert "grouped" not in ctx.last_kernel(), ctx.last_kernel()
+    monkeypatch.delenv("D8K_GROUP")
+    before = ctx.launch_count()
+    together = r.gpu(x, w, dz, dx0, dw0, tdtype)
+    launches_together = ctx.launch_count() - before
+    if " tma " in ctx.last_kernel():  # which of the three contractions has the divisor depends on the operator: count launches
+        assert launches_together < launches_apart, (launches_together, launches_apart)
+    for name, a, b in zip(("z", "dx", "dy"), together, apart):
+        assert torch.equal(a, b), name
+    for name, g, wnt in zip(("z", "dx", "dy"), together, r.cpu(x, w, dz, dx0, dw0)):
+        check(ctx, g, wnt, F32_TOL if tdtype == torch.float32 else F16_TOL, name)
+    assert ctx.status() == 0
