@@ -956,6 +956,16 @@ d8k_gemm_kernel(const __grid_constant__ CUtensorMap tmA_launch, const __grid_con
             const int w = Cfg::GROUPED ? sel.w : w_all;
             (void)tmA; (void)tmB; (void)w;
             WorkItem it = decode_work(p, w, BN);
+            // GROUPED: what the k-loop reads, copied out of the item's parameters once - read through the pointer every field
+            // would be loaded again after each asm statement with a memory clobber
+            GatherSrc src_copy;
+            int kbatch_l = p.kbatch, num_kb_l = p.num_kb, tma_l = 0, chunked_l = 0, batch_mod_l = 1;
+            if constexpr (Cfg::GROUPED) {
+                src_copy = do_a ? p.a : p.b;
+                tma_l = do_a ? p.a_tma : p.b_tma;
+                chunked_l = do_a ? p.a_chunked : p.b_chunked;
+                batch_mod_l = do_a ? p.a_batch_mod : p.b_batch_mod;
+            }
             for (int kk = it.kb_begin; kk < it.kb_end; ++kk) {
                 int k0_halo = 0;
                 if constexpr (Cfg::HALO) {
@@ -968,18 +978,23 @@ d8k_gemm_kernel(const __grid_constant__ CUtensorMap tmA_launch, const __grid_con
                 if (!ok) break;
                 if (lane == 0) {
                     int b = it.batch, kb = kk;
-                    if (p.kbatch > 1) {
-                        b = kk / p.num_kb;
-                        kb = kk - b * p.num_kb;
+                    if (kbatch_l > 1) {
+                        b = kk / num_kb_l;
+                        kb = kk - b * num_kb_l;
                     }
                     int k0 = Cfg::HALO ? k0_halo : kb * BK;
                     // CONVERT: the boxes fill the hi halves of the stage and complete on the raw barrier
                     const uint32_t bar = Cfg::CONVERT ? raw_bar(stage) : full_bar(stage);
                     if constexpr (Cfg::TWIN) ptx::mbar_arrive_expect_tx(bar, do_a ? Cfg::A_BYTES : Cfg::B_BYTES);
                     else ptx::mbar_arrive_expect_tx(bar, Cfg::HALO ? Cfg::B_BYTES : Cfg::CONVERT ? Cfg::A_BYTES + Cfg::B_BYTES : Cfg::STAGE_BYTES);
-                    if constexpr (!Cfg::HALO)
-                        if (do_a) produce_operand<Cfg, Cfg::A_MN, kBM>(p.a_tma, p.a_chunked, p.a, &tmA, stage_a(stage), bar, k0, it.m0, b % p.a_batch_mod);
-                    if (do_b) produce_operand<Cfg, Cfg::B_MN, BN>(p.b_tma, p.b_chunked, p.b, &tmB, stage_b(stage), bar, k0, it.n0, b % p.b_batch_mod);
+                    if constexpr (Cfg::GROUPED) {  // always TWIN: this thread issues one operand
+                        if (do_a) produce_operand<Cfg, Cfg::A_MN, kBM>(tma_l, chunked_l, src_copy, &tmA, stage_a(stage), bar, k0, it.m0, b % batch_mod_l);
+                        else produce_operand<Cfg, Cfg::B_MN, BN>(tma_l, chunked_l, src_copy, &tmB, stage_b(stage), bar, k0, it.n0, b % batch_mod_l);
+                    } else {
+                        if constexpr (!Cfg::HALO)
+                            if (do_a) produce_operand<Cfg, Cfg::A_MN, kBM>(p.a_tma, p.a_chunked, p.a, &tmA, stage_a(stage), bar, k0, it.m0, b % p.a_batch_mod);
+                        if (do_b) produce_operand<Cfg, Cfg::B_MN, BN>(p.b_tma, p.b_chunked, p.b, &tmB, stage_b(stage), bar, k0, it.n0, b % p.b_batch_mod);
+                    }
                 }
                 __syncwarp();
                 if (++stage == STAGES) { stage = 0; phase ^= 1; }
