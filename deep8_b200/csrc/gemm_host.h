@@ -61,6 +61,7 @@ struct GemmProblem {
     // context's tickets (the first launch of a series); 2 - the caller vouches that they are zero (a later launch of the
     // series: each launch leaves them zero unless it gave up on a wait, and then the status word already says so)
     int tickets = 0;
+    int force_splits = 0;    // > 0: this many splits (bounded by the k-block count and the scratch) instead of the plan's own choice
     int ticket_base = 0;     // first of the context's tickets this launch uses (grouped launches give every contraction its own range)
     bool ws_strict = false;  // split within ws / ws_bytes, never in the context's own scratch (run_gemm_group carves that up itself)
     void* ws = nullptr;  // optional caller scratch for split-K

@@ -327,6 +327,7 @@ Plan make_plan(const Ctx* ctx, const GemmProblem& g, size_t scratch_limit) {
         if (splits > pl.total_kb / 4) splits = pl.total_kb / 4;
     }
     int forced = env_int("D8K_SPLITS", 0);
+    if (forced <= 0) forced = g.force_splits;
     if (forced > 0 && pl.tiles <= kMaxCounters) splits = forced < pl.total_kb ? forced : pl.total_kb;
     size_t per_split = static_cast<size_t>(pl.tiles) * kBM * pl.bn * sizeof(float);
     if (splits > 1 && per_split * splits > scratch_limit) splits = static_cast<int>(scratch_limit / per_split);
@@ -636,6 +637,20 @@ int run_gemm_group(Ctx* ctx, std::vector<GemmProblem>& parts) {
     bool grouped = ctx->group_buf != nullptr && n >= 2 && n <= kMaxGroups && env_int("D8K_GROUP", 1);
     std::vector<PreparedGemm> prep(grouped ? n : 0);
     int tickets = 0;
+    int group_splits = 0;
+    if (grouped) {
+        // Splits are chosen for the group as a whole: the parts' tiles together are what has to fill the SMs.  (Each part
+        // planning for itself split four times too often: configuration 4's filter gradient took 114 us with 9 splits
+        // per class and takes 56 with 2.)
+        long long all_tiles = 0;
+        for (int i = 0; i < n && grouped; ++i) {
+            PreparedGemm probe;
+            if (parts[i].M <= 0 || parts[i].N <= 0 || parts[i].K <= 0 || parts[i].batch <= 0) grouped = false;
+            else if (int rc = run_gemm(ctx, parts[i], &probe)) return rc;
+            else all_tiles += probe.tiles;
+        }
+        group_splits = (all_tiles > 0 && all_tiles * 2 <= ctx->num_sms) ? static_cast<int>(ctx->num_sms / all_tiles) : 1;
+    }
     if (grouped) {
         // every contraction gets its own part of the context's scratch memory and its own range of tickets
         const size_t region = (ctx->scratch_bytes / n) & ~static_cast<size_t>(255);
@@ -645,6 +660,7 @@ int run_gemm_group(Ctx* ctx, std::vector<GemmProblem>& parts) {
             g.ws_bytes = region;
             g.ws_strict = true;
             g.ticket_base = tickets;
+            g.force_splits = group_splits;
             if (g.M <= 0 || g.N <= 0 || g.K <= 0 || g.batch <= 0) grouped = false;  // degenerate parts keep run_gemm's own handling
             else if (int rc = run_gemm(ctx, g, &prep[i])) return rc;
             if (!grouped) break;

@@ -826,10 +826,11 @@ def test_twin_issuing_threads_fp16_same_bits(ctx, restated, monkeypatch, case):
 @pytest.mark.parametrize("case", [("deconv", (4, 14, 14, 64), (32, 4, 4, 64), True, (2, 2)), ("deconv", (2, 9, 7, 32), (64, 3, 3, 32), False, (3, 2)),
                                   ("conv", (2, 33, 29, 64), (64, 3, 3, 64), True, (2, 2), (1, 1)), ("conv", (3, 24, 24, 32), (96, 5, 4, 32), False, (2, 3), (1, 1))])
 @pytest.mark.parametrize("tdtype", [torch.float32, torch.float16])
-def test_residue_classes_in_one_launch_give_the_same_bits(ctx, restated, monkeypatch, case, tdtype):
+def test_residue_classes_in_one_launch(ctx, restated, monkeypatch, case, tdtype):
     """A strided rule runs one contraction per residue class of pixels (or of taps).  By default their work items share ONE
     launch (every class with its own parameters, tensor maps, scratch region and tickets in device memory); D8K_GROUP=0
-    launches them one after the other.  Same bits either way, and the oracle within the bar."""
+    launches them one after the other.  Both within the bar of the oracle and of each other (the grouped launch chooses its
+    split count for all classes together, so the partial sums differ)."""
     kind = case[0]
     meta = (case[3], case[4], case[5]) if kind == "conv" else (case[3], case[4])
     h = (lambda a: a.astype(np.float16).astype(np.float32)) if tdtype == torch.float16 else (lambda a: a)
@@ -848,8 +849,9 @@ def test_residue_classes_in_one_launch_give_the_same_bits(ctx, restated, monkeyp
     launches_together = ctx.launch_count() - before
     if " tma " in ctx.last_kernel():  # which of the three contractions has the divisor depends on the operator: count launches
         assert launches_together < launches_apart, (launches_together, launches_apart)
-    for name, a, b in zip(("z", "dx", "dy"), together, apart):
-        assert torch.equal(a, b), name
+    tol = F32_TOL if tdtype == torch.float32 else F16_TOL
+    for name, a, b in zip(("z", "dx", "dy"), together, apart):  # the group plans its splits as a whole: other partial sums, same values
+        assert cases.rel_max(host(a), host(b)) <= tol, name
     for name, g, wnt in zip(("z", "dx", "dy"), together, r.cpu(x, w, dz, dx0, dw0)):
-        check(ctx, g, wnt, F32_TOL if tdtype == torch.float32 else F16_TOL, name)
+        check(ctx, g, wnt, tol, name)
     assert ctx.status() == 0
