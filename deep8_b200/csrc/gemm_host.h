@@ -86,7 +86,7 @@ struct PreparedGemm {
     GemmParams p;
     CUtensorMap ta, tb;
     GemmLaunchFn fn = nullptr;
-    int grid = 0, tiles = 0, splits = 1;
+    int grid = 0, tiles = 0, splits = 1, total_kb = 0;
     bool pair = false, dual = false, halo = false, twin = false, f32 = false, a_mn = false, b_mn = false;
     int bn = 0;
     std::string text;  // what d8k_last_kernel reports
