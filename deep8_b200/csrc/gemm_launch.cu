@@ -290,6 +290,15 @@ struct Plan {
     size_t scratch;
 };
 
+// An overwriting fp16 product with a long contraction goes to the paired kernel from a third of a wave of 256 x 256 tiles
+// on (measured: 2048^3 forward 33.6 -> 27.4 us, 2048 x 4096 x 2048 57.4 -> 38.9, 1024 x 8192 x 4096 104.9 -> 63.5; accumulating
+// products and shorter contractions of that size are faster on the single-CTA kernel and keep the half-wave threshold)
+bool pair_early(const Ctx* ctx, const GemmProblem& g) {
+    if (g.dtype != 0 || g.beta != 0 || g.epi != 0 || g.K < 2048 || g.kbatch != 1 || !env_int("D8K_PAIR_EARLY", 1)) return false;
+    const long long tiles256 = static_cast<long long>(g.batch) * ((g.M + 255) / 256) * ((g.N + 255) / 256);
+    return tiles256 * 3 >= ctx->num_sms && tiles256 * 2 < ctx->num_sms;
+}
+
 Plan make_plan(const Ctx* ctx, const GemmProblem& g, size_t scratch_limit) {
     Plan pl;
     pl.f32 = g.dtype == 1;
@@ -308,6 +317,8 @@ Plan make_plan(const Ctx* ctx, const GemmProblem& g, size_t scratch_limit) {
         // 256 columns only when such tiles alone give every SM one: a small problem prefers twice as many narrower tiles
         const long long tiles256 = static_cast<long long>(g.batch) * ((g.M + kBM - 1) / kBM) * ((g.N + 255) / 256);
         if (pl.bn == 256 && tiles256 < ctx->num_sms) pl.bn = 128;
+        // ... unless the paired kernel takes the problem at a lower tile count (see below): it needs 256-column tiles
+        if (pair_early(ctx, g)) pl.bn = 256;
     }
     else pl.bn = g.N > 64 ? 128 : 64;
     int forced_bn = env_int("D8K_BN", 0);
@@ -339,7 +350,7 @@ Plan make_plan(const Ctx* ctx, const GemmProblem& g, size_t scratch_limit) {
     pl.scratch = pl.splits > 1 ? per_split * pl.splits : 0;
     // CTA pairs on 256 x 256 tiles once the output alone fills the machine (74 pairs) and nothing is split
     int tiles256 = g.batch * ((g.M + 255) / 256) * ((g.N + 255) / 256);
-    pl.pair = pl.tma && pl.a_tma == kTmaTiled && pl.b_tma == kTmaTiled && !g.out.rows_on && !g.out.cols_on && pl.bn == 256 && pl.splits == 1 && tiles256 * 2 >= ctx->num_sms && env_int("D8K_PAIR", 1) != 0 &&
+    pl.pair = pl.tma && pl.a_tma == kTmaTiled && pl.b_tma == kTmaTiled && !g.out.rows_on && !g.out.cols_on && pl.bn == 256 && pl.splits == 1 && (tiles256 * 2 >= ctx->num_sms || pair_early(ctx, g) || env_int("D8K_PAIR", 1) == 2) && env_int("D8K_PAIR", 1) != 0 &&
               g.K % 64 == 0 && (!g.a.mn || g.M % 64 == 0) && (!g.b.mn || g.N % 64 == 0);
     if (pl.pair) {
         pl.tiles_m = (g.M + 255) / 256;
