@@ -618,8 +618,7 @@ int d8k_ctx_status(d8k_ctx* ctx, int* status) {
     D8K_CUDA(cudaMemcpy(&host, ctx->status, sizeof(int), cudaMemcpyDeviceToHost));
     if (status) *status = host;
     if (host != 0) {
-        // a kernel left early: its tile tickets may be half-counted
-        cudaMemset(ctx->counters, 0, (kMaxCounters + 1) * sizeof(int));
+        cudaMemset(ctx->status, 0, sizeof(int));  // (half-counted tile tickets need no care: the next launch has another epoch)
         return fail(D8K_ERR_KERNEL, "a kernel gave up on a bounded wait, status " + std::to_string(host));
     }
     return 0;

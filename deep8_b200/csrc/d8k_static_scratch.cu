@@ -11,8 +11,8 @@
 // once per device with that device current (the first call on a device does it: make that call before any stream
 // capture).  The entry point calls no cudaMalloc, cudaFree or allocating library routine.
 //
-// All calls on a device share the array and it keeps the previous call's contents: the tile tickets a split launch uses are cleared on
-// the stream before it, partial tiles are always written before they are read, and two calls whose kernels
+// All calls on a device share the array and it keeps the previous call's contents: tile tickets carry the number of the launch
+// that drew them (stale ones count as zero), partial tiles are always written before they are read, and two calls whose kernels
 // overlap on the GPU (different streams, or different host threads) race on it - serialise them.
 #include <mutex>
 #include <string>
@@ -30,6 +30,7 @@ static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBy
 struct DeviceSlot {
     unsigned char* base = nullptr;  // device address of g_static_scratch on this device
     int num_sms = 0;
+    unsigned epoch = 0;             // split launches made on this device's array so far (Ctx::epoch_counter between calls)
 };
 DeviceSlot g_slots[64];
 std::mutex g_slots_mutex;
@@ -92,6 +93,13 @@ extern "C" int d8k_gemm_static(int dtype, int transA, int transB, int M, int N, 
         return fail(D8K_ERR_ARGUMENT, "d8k_gemm_static: this contraction needs " + std::to_string(need) +
                                           " bytes of split-K scratch, the static maximum is " + std::to_string(kStaticScratchBytes) +
                                           "; use d8k_gemm with a context");
-    // tickets must start at zero whatever an earlier call left behind: run_gemm clears the ones a split launch uses, on the stream
-    return run_gemm(&ctx, g);
+    // ticket words carry the epoch of the launch that wrote them, so whatever an earlier call left behind counts as zero; the
+    // epoch lives with the device's slot between calls (calls on one device are serialised by contract)
+    ctx.epoch_counter = slot.epoch;
+    const int rc = run_gemm(&ctx, g);
+    {
+        std::lock_guard<std::mutex> lock(g_slots_mutex);
+        g_slots[ctx.device].epoch = ctx.epoch_counter;
+    }
+    return rc;
 }

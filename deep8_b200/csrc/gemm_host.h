@@ -16,7 +16,8 @@ struct Ctx {
     cudaStream_t stream = nullptr;
     float* scratch = nullptr;  // split-K partial tiles
     size_t scratch_bytes = 0;
-    int* counters = nullptr;   // kMaxCounters tile tickets, zero between launches
+    int* counters = nullptr;   // kMaxCounters tile ticket words (GemmParams::counters)
+    unsigned epoch_counter = 0;  // this context's split launches so far, modulo 2^24 (GemmParams::epoch)
     int* status = nullptr;     // device status word
     GroupEntry* group_buf = nullptr;  // device memory for kMaxGroups entries of a grouped launch (null: launches are never grouped)
 };
@@ -57,10 +58,6 @@ struct GemmProblem {
     float epi_a = 0.f, epi_b = 0.f;
     void* E1 = nullptr;
     void* E2 = nullptr;
-    // Tile tickets of a split launch: 0 - run_gemm clears the ones this launch uses (the default); 1 - it clears ALL of the
-    // context's tickets (the first launch of a series); 2 - the caller vouches that they are zero (a later launch of the
-    // series: each launch leaves them zero unless it gave up on a wait, and then the status word already says so)
-    int tickets = 0;
     int force_splits = 0;    // > 0: this many splits (bounded by the k-block count and the scratch) instead of the plan's own choice
     int ticket_base = 0;     // first of the context's tickets this launch uses (grouped launches give every contraction its own range)
     bool ws_strict = false;  // split within ws / ws_bytes, never in the context's own scratch (run_gemm_group carves that up itself)

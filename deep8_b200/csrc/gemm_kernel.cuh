@@ -160,7 +160,8 @@ struct GemmParams {
     void* C;
     long long ldc, c_batch_stride;
     float* ws;         // split-K partial tiles: total_work * 128 * BN floats
-    int* counters;     // one ticket counter per output tile, zero on entry and on exit
+    int* counters;     // one ticket word per output tile: (epoch << 8 | tickets drawn by this launch's CTAs)
+    int epoch;         // 24-bit number of this split launch on its context; ticket words of any other epoch count as zero
     int* status;
     int a_batch_mod, b_batch_mod;  // TMA: batch coordinate = b % mod
     int a_chunked, b_chunked;      // single-CTA TMA kernel: the MN-major operand comes through a 4-D {64, k, chunk, batch} map, one box per stage
@@ -1238,9 +1239,22 @@ d8k_gemm_kernel(const __grid_constant__ CUtensorMap tmA_launch, const __grid_con
                 __threadfence();
                 asm volatile("bar.sync 1, 128;" ::: "memory");
                 if (threadIdx.x == 0) {
-                    int ticket = atomicAdd(p.counters + it.tile, 1);
-                    s_last = (ticket == p.splits - 1);
-                    if (s_last) p.counters[it.tile] = 0;
+                    // A ticket word is (launch epoch << 8 | tickets drawn).  A word left by another launch - finished, or one that
+                    // gave up on a wait half-way - carries another epoch and counts as zero, so tickets are never cleared.
+                    unsigned* word = reinterpret_cast<unsigned*>(p.counters + it.tile);
+                    const unsigned fresh = static_cast<unsigned>(p_launch.epoch) << 8;
+                    unsigned cur = *reinterpret_cast<volatile unsigned*>(word);
+                    unsigned drawn;
+                    for (;;) {
+                        const unsigned want = ((cur & 0xffffff00u) == fresh ? cur : fresh) + 1u;
+                        const unsigned old = atomicCAS(word, cur, want);
+                        if (old == cur) {
+                            drawn = want & 0xffu;
+                            break;
+                        }
+                        cur = old;
+                    }
+                    s_last = (static_cast<int>(drawn) == p.splits);
                 }
                 asm volatile("bar.sync 1, 128;" ::: "memory");
                 if (s_last) {

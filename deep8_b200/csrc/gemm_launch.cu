@@ -335,9 +335,10 @@ Plan make_plan(const Ctx* ctx, const GemmProblem& g, size_t scratch_limit) {
     int splits = 1;
     if (pl.tiles * 2 <= ctx->num_sms && pl.total_kb >= 8 && pl.tiles <= kMaxCounters) {
         splits = ctx->num_sms / pl.tiles;
-        // a split costs about a dozen k-blocks' time (clearing the tickets, the partial tiles, the reduction): at least 16 k-blocks
-        // per split (measured: a 256 x 512 x 128 fp32 product ran in 22.5 us with 4 splits of 4 k-blocks, in 17.4 us unsplit)
-        if (splits > pl.total_kb / 16) splits = pl.total_kb / 16;
+        // a split costs about a dozen k-blocks' time (partial tiles, tickets, the reduction): at least 24 k-blocks per split
+        // (measured: a 256 x 512 x 128 fp32 product ran in 22.5 us with 4 splits of 4 k-blocks, in 17.4 us unsplit; the filter
+        // gradient of 64 x [128 x 256] * [256 x 256] in 50 us with 16 splits of 16 k-blocks, in 46 us with 8 to 12)
+        if (splits > pl.total_kb / 24) splits = pl.total_kb / 24;
     }
     int forced = env_int("D8K_SPLITS", 0);
     if (forced <= 0) forced = g.force_splits;
@@ -345,6 +346,7 @@ Plan make_plan(const Ctx* ctx, const GemmProblem& g, size_t scratch_limit) {
     size_t per_split = static_cast<size_t>(pl.tiles) * kBM * pl.bn * sizeof(float);
     if (splits > 1 && per_split * splits > scratch_limit) splits = static_cast<int>(scratch_limit / per_split);
     if (splits < 1) splits = 1;
+    if (splits > 255) splits = 255;  // a tile's ticket word counts its splits in eight bits
     pl.kb_per_split = (pl.total_kb + splits - 1) / splits;
     pl.splits = (pl.total_kb + pl.kb_per_split - 1) / pl.kb_per_split;
     pl.scratch = pl.splits > 1 ? per_split * pl.splits : 0;
@@ -419,6 +421,17 @@ size_t gemm_scratch_need(const Ctx* ctx, const GemmProblem& g) {
 bool gemm_goes_through_tma(const Ctx* ctx, const GemmProblem& g) {
     Plan pl = make_plan(ctx, g, ~static_cast<size_t>(0));
     return pl.tma;
+}
+
+// The epoch of the context's next split launch: 1 .. 2^24 - 1, then round again.  At the wrap every ticket word is cleared once,
+// so that a word written 2^24 launches ago cannot pass for a current one.
+static int next_epoch(Ctx* ctx) {
+    ctx->epoch_counter = (ctx->epoch_counter + 1) & 0xffffffu;
+    if (ctx->epoch_counter == 0) {
+        cudaMemsetAsync(ctx->counters, 0, static_cast<size_t>(kMaxCounters) * sizeof(int), ctx->stream);
+        ctx->epoch_counter = 1;
+    }
+    return static_cast<int>(ctx->epoch_counter);
 }
 
 int run_gemm(Ctx* ctx, const GemmProblem& g, PreparedGemm* capture) {
@@ -631,13 +644,7 @@ int run_gemm(Ctx* ctx, const GemmProblem& g, PreparedGemm* capture) {
         capture->text = text;
         return 0;
     }
-    if ((pl.splits > 1 && g.tickets == 0) || g.tickets == 1) {
-        // Tile tickets must start at zero.  A kernel that gave up on a bounded wait leaves them half-counted, and the status
-        // word that says so may not have been read yet: clear the tickets this launch uses on the stream, every time.
-        const size_t count = g.tickets == 1 ? static_cast<size_t>(kMaxCounters) : static_cast<size_t>(pl.tiles);
-        cudaError_t ce = cudaMemsetAsync(ctx->counters + (g.tickets == 1 ? 0 : g.ticket_base), 0, count * sizeof(int), ctx->stream);
-        if (ce != cudaSuccess) return fail(2, std::string("gemm: cudaMemsetAsync: ") + cudaGetErrorString(ce));
-    }
+    if (pl.splits > 1) p.epoch = next_epoch(ctx);
     cudaError_t e = fn(grid, ctx->stream, ta, tb, p);
     if (e != cudaSuccess) return fail(2, std::string("gemm: launch failed: ") + cudaGetErrorString(e));
     count_launch();
@@ -668,7 +675,7 @@ int run_gemm_group(Ctx* ctx, std::vector<GemmProblem>& parts) {
             }
         }
         group_splits = (all_tiles > 0 && all_tiles * 2 <= ctx->num_sms) ? static_cast<int>(ctx->num_sms / all_tiles) : 1;
-        if (group_splits > min_kb / 16) group_splits = min_kb / 16;  // at least 16 k-blocks per split, as in a single launch's plan
+        if (group_splits > min_kb / 24) group_splits = min_kb / 24;  // at least 24 k-blocks per split, as in a single launch's plan
         if (group_splits < 1) group_splits = 1;
     }
     if (grouped) {
@@ -690,12 +697,8 @@ int run_gemm_group(Ctx* ctx, std::vector<GemmProblem>& parts) {
         }
     }
     if (!grouped) {
-        bool first = true;
-        for (GemmProblem& g : parts) {
-            g.tickets = first ? 1 : 2;  // one clearing of the tile tickets serves all the parts (each launch leaves them zero)
-            first = false;
+        for (GemmProblem& g : parts)
             if (int rc = run_gemm(ctx, g)) return rc;
-        }
         return 0;
     }
     std::vector<GroupEntry> entries(n);
@@ -709,9 +712,9 @@ int run_gemm_group(Ctx* ctx, std::vector<GemmProblem>& parts) {
         total += prep[i].p.total_work;
     }
     cudaError_t e = cudaMemcpyAsync(ctx->group_buf, entries.data(), sizeof(GroupEntry) * n, cudaMemcpyHostToDevice, ctx->stream);
-    if (e == cudaSuccess) e = cudaMemsetAsync(ctx->counters, 0, static_cast<size_t>(tickets) * sizeof(int), ctx->stream);
     if (e != cudaSuccess) return fail(2, std::string("gemm: preparing a grouped launch: ") + cudaGetErrorString(e));
     GemmParams launch = prep[0].p;
+    launch.epoch = next_epoch(ctx);
     launch.group_count = n;
     launch.groups = ctx->group_buf;
     launch.total_work = total;
