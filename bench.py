@@ -17,7 +17,8 @@ Prints ONE JSON line.  `value` is the aggregate TFLOP/s over all GPUs with input
 of the same step, with NVML clock samples taken inside the timed region; `e2e` is the same metric with X and dY copied from
 pinned host memory and Y copied back inside every step (plus the same copies without kernels, and the step through the C++
 interface, with synchronous feed / fetch and with its copies on Deep8::CopyStream); `roofline` is for the contraction kernel (tensor bound) against the measured cuBLAS bf16 peak of this pool;
-`contractions` and `ranks` say where the step's time went on every rank; `exchange_check` compares the exchanged gradients
+`contractions` and `ranks` say where the step's time went on every rank (measured in a short pass with events around every
+contraction right after the timed region, which itself carries no events between kernels); `exchange_check` compares the exchanged gradients
 with the sum of the ranks' partial gradients; `cpu_baseline` is the reference's own CPU code on a row slice of the same
 workload; `aux` reports the four fp32 operator configurations (`--config 1..4`) and `hbm_kernels` the HBM-bound neighbours
 (matrix-vector products, Linear, AdamUpdate) against the measured copy bandwidth.  `--impl reference` times only that CPU code.
@@ -725,13 +726,26 @@ def run_gpu_arm(args):
     t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     t0.record()
     for _ in range(args.steps):
-        mlp.step(step_dist, timed=True)
-    mlp.drain(timed=True)
+        mlp.step(step_dist)
+    mlp.drain()
     t1.record()
     torch.cuda.synchronize()
     host_t1 = time.perf_counter()
     barrier()
     launches = ctx.launch_count() - launches0
+    # ---- the same step with CUDA events around every contraction, right after and outside the timed region: where the time
+    # goes on every rank.  (Inside the region the events cost 4-5 %: an event between two kernels keeps the next one's first CTAs
+    # from starting while the previous one's last, partly filled wave of tiles drains.)
+    inst_steps = max(1, min(args.steps, 10))
+    i0, i1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    i0.record()
+    for _ in range(inst_steps):
+        mlp.step(step_dist, timed=True)
+    mlp.drain(timed=True)
+    i1.record()
+    torch.cuda.synchronize()
+    barrier()
+    inst_ms = i0.elapsed_time(i1) / inst_steps
     clocks = None
     if sampler is not None:
         sampler.stop()
@@ -747,10 +761,10 @@ def run_gpu_arm(args):
     gemm_ms = [a.elapsed_time(b) for a, b in mlp.gemm_events]
     mlp.gemm_events = []
     per_gemm = [sum(gemm_ms[i::6]) / max(1, len(gemm_ms[i::6])) for i in range(6)]   # mean of each of the six contractions
-    tail_ms = sum(a.elapsed_time(b) for a, b in mlp.tail_events) / args.steps
+    tail_ms = sum(a.elapsed_time(b) for a, b in mlp.tail_events) / inst_steps
     mlp.tail_events = []
     # every rank's step, contraction and exchange-wait times, so that the line shows the spread between GPUs
-    mine = torch.tensor([my_ms, sum(gemm_ms) / args.steps, tail_ms] + per_gemm, device=device, dtype=torch.float64)
+    mine = torch.tensor([my_ms, sum(gemm_ms) / inst_steps, tail_ms] + per_gemm, device=device, dtype=torch.float64)
     if dist is not None:
         allr = [torch.empty_like(mine) for _ in range(world)]
         dist.all_gather(allr, mine)
@@ -759,7 +773,7 @@ def run_gpu_arm(args):
         table = mine.cpu().numpy()[None, :]
     if os.environ.get("D8_BENCH_DIAG"):  # per rank: where the step's time went
         print("rank %d: step %.3f ms, contractions %.3f ms (%s), waiting for the exchange %.3f ms" %
-              (rank, my_ms, sum(gemm_ms) / args.steps, " ".join("%.3f" % v for v in per_gemm), tail_ms), file=sys.stderr, flush=True)
+              (rank, my_ms, sum(gemm_ms) / inst_steps, " ".join("%.3f" % v for v in per_gemm), tail_ms), file=sys.stderr, flush=True)
     if not status_ok():
         raise SystemExit("kernel status non-zero after the timed region")
 
@@ -834,7 +848,10 @@ def run_gpu_arm(args):
         main.wait_stream(s_in)
 
     def timed_loop(compute):
-        e2e_loop(2, compute)
+        # the compute leg is pre-heated like the device-resident region (the checks in between let the GPU cool, and a cold
+        # start runs 8-10 % faster on boost clocks: not a sustained figure)
+        heat = max(2, int(args.preheat * 1e3 / max(ms_step, 0.1))) if compute and not args.profile else 2
+        e2e_loop(heat, compute)
         barrier()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
@@ -870,14 +887,17 @@ def run_gpu_arm(args):
                          "traffic": TRAFFIC_BYTES_PER_LAUNCH, "kernel": "d8k_gemm_pair_kernel (TMA-fed fp16, CTA pairs on 256x256 tiles)",
                          "peak_source": peak_src, "flop_per_launch": flop_per_launch, "avg_launch_ms": avg_gemm_ms,
                          "mcycles_per_launch": (avg_gemm_ms * 1e-3 * sm_mhz) if sm_mhz else None,
-                         "gemm_share_of_step": sum(gemm_ms) / (my_ms * args.steps)},
+                         "measured_in": "the instrumented pass right after the timed region (%d steps with CUDA events around every "
+                                        "contraction: %.3f ms per step on rank 0)" % (inst_steps, inst_ms),
+                         "gemm_share_of_step": sum(gemm_ms) / (inst_ms * inst_steps)},
             "contractions": contractions,
             "ranks": {"step_ms": [float(table[:, 0].min()), float(table[:, 0].max())],
                       "contractions_ms": [float(table[:, 1].min()), float(table[:, 1].max())],
                       "waiting_for_exchange_ms": [float(table[:, 2].min()), float(table[:, 2].max())],
-                      "note": "[min, max] over ranks of each rank's own per-step means; a step's exchange is waited for inside the next step"},
+                      "note": "[min, max] over ranks of each rank's own per-step means; step_ms from the timed region, the other two from the "
+                              "instrumented pass after it; a step's exchange is waited for inside the next step"},
             "e2e": {"value": FLOP_PER_STEP * world / (e2e_ms * 1e-3) / 1e12, "unit": UNIT, "h2d_bytes_per_step": h2d,
-                    "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms, "steps": e2e_steps,
+                    "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms, "steps": e2e_steps, "preheat_s": args.preheat,
                     "overlap": "copies on side streams, double-buffered inputs and outputs", "host_numa_node_rank0": numa_node,
                     "copy_only_ms": copy_ms, "copy_only_gbs_per_gpu": (h2d + d2h) / (copy_ms * 1e-3) / 1e9,
                     "copy_only_gbs_aggregate": world * (h2d + d2h) / (copy_ms * 1e-3) / 1e9,
@@ -902,7 +922,8 @@ def run_gpu_arm(args):
                 torch.cuda.empty_cache()
                 for key, extra in (("cpp_api", []), ("cpp_api_overlapped", ["overlap"])):
                     try:
-                        r = subprocess.run([exe, "10", str(M_PER_GPU)] + extra, capture_output=True, text=True, timeout=300)
+                        # 200 steps (1 to 2 s): long enough for the power limit to set the clock, as in the legs above
+                        r = subprocess.run([exe, "200", str(M_PER_GPU)] + extra, capture_output=True, text=True, timeout=300)
                         line["e2e"][key] = json.loads(r.stdout.strip().splitlines()[-1])
                     except Exception as exc:  # the figure is auxiliary: its absence must not cost the line
                         line["e2e"][key] = {"error": str(exc)[:200]}
