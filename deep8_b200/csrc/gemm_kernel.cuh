@@ -19,8 +19,9 @@
 //                          with a divisor); fp32 is split into tf32 hi and lo on the way.
 //
 // Split-K: when the output has few tiles and K is long, `splits` CTAs share one tile.  Each writes its fp32 partial
-// tile to scratch memory, takes a ticket with atomicAdd, and the CTA that draws the last ticket sums the partials
-// in split order (so the result does not depend on arrival order), applies beta and stores.  Nobody waits on another CTA.
+// tile to scratch memory, takes a ticket (a compare-and-swap on the tile's epoch-stamped word), and the CTA that draws
+// the last ticket sums the partials in split order (so the result does not depend on arrival order), applies beta and
+// stores.  Nobody waits on another CTA.
 //
 // Two forms beyond one CTA per SM with one thread per role (GemmCfg's last parameter): DUAL - two CTAs per SM, each with
 // half the stages, one accumulator buffer and one converter group, for fp32 launches with more tiles than SMs and no
