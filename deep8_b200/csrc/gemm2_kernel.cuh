@@ -343,17 +343,27 @@ d8k_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
             const bool prefetch = coalesced && p.epi == 2, prefetch_c = coalesced && p.beta != 0;
             auto issue_e1 = [&](int c) {
                 const int pc0 = it.n0 + c * 32;
-                if ((!prefetch && !prefetch_c) || pc0 + 32 > p.N) return;
+                if (!prefetch || pc0 + 32 > p.N) return;
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
                     const int rr = 8 * i + lr;
-                    if (warp_row0 + rr < p.M) {
-                        const long long e = warp_off + static_cast<long long>(rr) * p.ldc + pc0 + lc * 8;
-                        if (prefetch) pre[i] = __ldcs(reinterpret_cast<const uint4*>(reinterpret_cast<const OutT*>(p.E1) + e));
-                        if (prefetch_c) pre_c[i] = *reinterpret_cast<const uint4*>(reinterpret_cast<const OutT*>(p.C) + e);
-                    }
+                    if (warp_row0 + rr < p.M)
+                        pre[i] = __ldcs(reinterpret_cast<const uint4*>(reinterpret_cast<const OutT*>(p.E1) + warp_off + static_cast<long long>(rr) * p.ldc +
+                                                                       pc0 + lc * 8));
                 }
             };
+            auto issue_c = [&](int c) {
+                const int pc0 = it.n0 + c * 32;
+                if (!prefetch_c || pc0 + 32 > p.N) return;
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const int rr = 8 * i + lr;
+                    if (warp_row0 + rr < p.M)
+                        pre_c[i] = *reinterpret_cast<const uint4*>(reinterpret_cast<const OutT*>(p.C) + warp_off + static_cast<long long>(rr) * p.ldc + pc0 +
+                                                                   lc * 8);
+                }
+            };
+            issue_c(0);
             issue_e1(0);
             const long long tw = p.prof ? clock64() : 0;
             ok = wait_bar(tfull_bar(acc), acc_phase, &s_abort, p.status, (kRoleEpilogue << 8) | 3, static_cast<unsigned>(p.epi_backoff_ns));
@@ -386,7 +396,10 @@ d8k_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
                                 }
                             }
                         }
-                        if (c + 1 < 256 / 32) issue_e1(c + 1);
+                        if (c + 1 < 256 / 32) {
+                            issue_e1(c + 1);
+                            issue_c(c + 1);
+                        }
                         __syncwarp();
                     }
                     using V = EpiVec<OutT>;
